@@ -1,0 +1,150 @@
+"""ctypes binding of ``libb200moe.so`` (C ABI declared in ``include/b200moe.h``).
+
+There is no fallback: if the shared library is missing or fails to load, every operator that
+needs it raises.  Build it with ``python -m b12x_b200._build`` (needs nvcc).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parents[1] / "csrc" / "libb200moe.so"
+_lib = None
+
+RECIPES = {"nvfp4": 0, "w4a8_mx": 1, "w4a16": 2}
+ACTIVATIONS = {"silu": 0, "relu2": 1, "swigluoai": 2}
+ROUTE_MODES = {"softmax_topk": 0, "raw": 1, "sigmoid": 2}
+
+OK, EINVAL, ECAPACITY, ECUDA, EUNSUPPORTED, EALIGN = 0, -1, -2, -3, -4, -5
+
+
+class DeviceInfo(C.Structure):
+    _fields_ = [("sm_major", C.c_int32), ("sm_minor", C.c_int32), ("num_sms", C.c_int32),
+                ("max_smem_optin", C.c_int32), ("total_mem", C.c_int64)]
+
+
+class CapsC(C.Structure):
+    _fields_ = [("max_tokens", C.c_int32), ("num_topk", C.c_int32), ("num_experts", C.c_int32),
+                ("hidden_size", C.c_int32), ("intermediate", C.c_int32), ("recipe", C.c_int32),
+                ("activation", C.c_int32), ("reserved", C.c_int32)]
+
+
+class ScratchLayout(C.Structure):
+    _fields_ = [(n, C.c_int64) for n in (
+        "total_nbytes", "status", "expert_counts", "expert_offsets", "tile_base", "mtile_expert",
+        "mtile_row0", "mtile_rows", "sorted_route_ids", "inv_perm", "act_q", "act_sf", "mid_q",
+        "mid_sf", "routed")] + [("rows", C.c_int32), ("mtile_cap", C.c_int32)]
+
+
+class RouteArgs(C.Structure):
+    _fields_ = [("logits", C.c_void_p), ("bias", C.c_void_p), ("topk_logits", C.c_void_p),
+                ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p),
+                ("logits_row_stride", C.c_int64),
+                ("num_tokens", C.c_int32), ("num_experts", C.c_int32), ("num_topk", C.c_int32),
+                ("logits_dtype", C.c_int32), ("mode", C.c_int32), ("renormalize", C.c_int32),
+                ("route_scale", C.c_float), ("reserved", C.c_int32)]
+
+
+class SortArgs(C.Structure):
+    _fields_ = [("topk_ids", C.c_void_p), ("expert_map", C.c_void_p), ("scratch", C.c_void_p),
+                ("layout", C.POINTER(ScratchLayout)),
+                ("num_tokens", C.c_int32), ("num_topk", C.c_int32), ("num_experts", C.c_int32),
+                ("expert_map_len", C.c_int32)]
+
+
+class QuantArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("a1_gscale", C.c_void_p), ("scratch", C.c_void_p),
+                ("layout", C.POINTER(ScratchLayout)), ("x_row_stride", C.c_int64),
+                ("num_tokens", C.c_int32), ("num_topk", C.c_int32), ("num_experts", C.c_int32),
+                ("hidden_size", C.c_int32), ("gscale_len", C.c_int32), ("reserved", C.c_int32)]
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [("w13", C.c_void_p), ("w13_sf", C.c_void_p), ("w1_alphas", C.c_void_p),
+                ("w2", C.c_void_p), ("w2_sf", C.c_void_p), ("w2_alphas", C.c_void_p),
+                ("a2_gscale", C.c_void_p), ("x", C.c_void_p), ("scratch", C.c_void_p),
+                ("layout", C.POINTER(ScratchLayout)), ("fc1_tap", C.c_void_p),
+                ("x_row_stride", C.c_int64),
+                ("num_tokens", C.c_int32), ("num_topk", C.c_int32), ("num_experts", C.c_int32),
+                ("hidden_size", C.c_int32), ("intermediate", C.c_int32),
+                ("recipe", C.c_int32), ("activation", C.c_int32), ("gate_first", C.c_int32),
+                ("gscale_len", C.c_int32), ("swiglu_limit", C.c_float),
+                ("swiglu_alpha", C.c_float), ("swiglu_beta", C.c_float),
+                ("num_sms", C.c_int32), ("reserved", C.c_int32)]
+
+
+class CombineArgs(C.Structure):
+    _fields_ = [("topk_weights", C.c_void_p), ("out", C.c_void_p), ("scratch", C.c_void_p),
+                ("layout", C.POINTER(ScratchLayout)), ("out_row_stride", C.c_int64),
+                ("num_tokens", C.c_int32), ("num_topk", C.c_int32), ("hidden_size", C.c_int32),
+                ("out_f32", C.c_int32), ("output_scale", C.c_float), ("reserved", C.c_int32)]
+
+
+# every symbol include/b200moe.h declares, with its argument types
+EXPORTS = {
+    "b200moe_abi_version": ([], C.c_int),
+    "b200moe_strerror": ([C.c_int], C.c_char_p),
+    "b200moe_query_device": ([C.c_int, C.POINTER(DeviceInfo)], C.c_int),
+    "b200moe_scratch_nbytes": ([C.POINTER(CapsC), C.POINTER(ScratchLayout)], C.c_int),
+    "b200moe_route_topk": ([C.POINTER(RouteArgs), C.c_void_p], C.c_int),
+    "b200moe_expert_sort": ([C.POINTER(SortArgs), C.c_void_p], C.c_int),
+    "b200moe_permute_quant_nvfp4": ([C.POINTER(QuantArgs), C.c_void_p], C.c_int),
+    "b200moe_permute_quant_mxfp8": ([C.POINTER(QuantArgs), C.c_void_p], C.c_int),
+    "b200moe_grouped_gemm1_act": ([C.POINTER(GemmArgs), C.c_void_p], C.c_int),
+    "b200moe_grouped_gemm2": ([C.POINTER(GemmArgs), C.c_void_p], C.c_int),
+    "b200moe_combine": ([C.POINTER(CombineArgs), C.c_void_p], C.c_int),
+}
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def load():
+    """Load the extension (once).  Raises RuntimeError if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        raise RuntimeError(
+            f"{_LIB_PATH} is missing: the sm_100a extension is not built and there is no other "
+            "implementation of this operator (run `python -m b12x_b200._build`)")
+    lib = C.CDLL(str(_LIB_PATH))
+    for name, (argtypes, restype) in EXPORTS.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = restype
+    if lib.b200moe_abi_version() != 1:
+        raise RuntimeError("libb200moe.so ABI version mismatch; rebuild it")
+    _lib = lib
+    return lib
+
+
+def is_loaded() -> bool:
+    return _lib is not None
+
+
+def strerror(code: int) -> str:
+    return load().b200moe_strerror(code).decode()
+
+
+def check(code: int, what: str) -> None:
+    """Map a negative status to the exception type the reference raises for that situation."""
+    if code == OK:
+        return
+    msg = f"{what}: {strerror(code)} (status {code})"
+    if code in (EINVAL, EALIGN):
+        raise ValueError(msg)
+    if code == EUNSUPPORTED:
+        raise NotImplementedError(msg)
+    raise RuntimeError(msg)
+
+
+def scratch_layout(max_tokens: int, num_topk: int, num_experts: int, hidden: int, intermediate: int,
+                   recipe: str, activation: str) -> ScratchLayout:
+    caps = CapsC(max_tokens, num_topk, num_experts, hidden, intermediate, RECIPES[recipe],
+                 ACTIVATIONS[activation], 0)
+    out = ScratchLayout()
+    check(load().b200moe_scratch_nbytes(C.byref(caps), C.byref(out)), "scratch layout")
+    return out

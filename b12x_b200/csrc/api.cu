@@ -1,0 +1,142 @@
+// Host-only part of the C ABI: scratch layout, device query, error strings and the recipe
+// dispatch of the two GEMM entry points.
+#include "common.cuh"
+
+namespace b200moe {
+int nvfp4_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
+int nvfp4_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
+int mx_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
+int mx_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
+int w4a16_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
+int w4a16_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
+}  // namespace b200moe
+
+static inline int64_t align_up64(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+extern "C" int b200moe_abi_version(void) { return B200MOE_ABI_VERSION; }
+
+extern "C" const char* b200moe_strerror(int code) {
+  switch (code) {
+    case B200MOE_OK: return "ok";
+    case B200MOE_EINVAL: return "invalid argument or unsupported shape";
+    case B200MOE_ECAPACITY: return "problem exceeds the planned scratch capacity";
+    case B200MOE_ECUDA: return "CUDA runtime or driver call failed";
+    case B200MOE_EUNSUPPORTED: return "recipe/activation combination not implemented";
+    case B200MOE_EALIGN: return "pointer or stride not aligned for TMA / vector access";
+    default: return "unknown b200moe status";
+  }
+}
+
+extern "C" int b200moe_query_device(int device, b200moe_device_info* out) {
+  if (out == nullptr) return B200MOE_EINVAL;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return B200MOE_ECUDA;
+  out->sm_major = prop.major;
+  out->sm_minor = prop.minor;
+  out->num_sms = prop.multiProcessorCount;
+  out->max_smem_optin = static_cast<int32_t>(prop.sharedMemPerBlockOptin);
+  out->total_mem = static_cast<int64_t>(prop.totalGlobalMem);
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_scratch_nbytes(const b200moe_caps* c, b200moe_scratch_layout* L) {
+  if (c == nullptr || L == nullptr) return B200MOE_EINVAL;
+  if (c->max_tokens <= 0 || c->num_topk <= 0 || c->num_experts <= 0 || c->num_experts > 1024 ||
+      c->hidden_size <= 0 || c->intermediate <= 0)
+    return B200MOE_EINVAL;
+  const int64_t T = c->max_tokens, k = c->num_topk, E = c->num_experts;
+  const int64_t K = c->hidden_size, I = c->intermediate;
+  const int64_t rows64 = T * k;
+  if (rows64 > (1 << 30)) return B200MOE_EINVAL;
+  const int64_t mtile_cap = (rows64 + 127) / 128 + (E < rows64 ? E : rows64);
+  int64_t act_row = 0, mid_row = 0, act_atoms = 0, mid_atoms = 0;
+  switch (c->recipe) {
+    case B200MOE_RECIPE_NVFP4:
+      if (K % 64 != 0 || I % 64 != 0) return B200MOE_EINVAL;
+      act_row = K / 2; mid_row = I / 2;
+      act_atoms = (K + 63) / 64; mid_atoms = (I + 63) / 64;
+      break;
+    case B200MOE_RECIPE_W4A8_MX:
+      if (K % 32 != 0 || I % 32 != 0) return B200MOE_EINVAL;
+      act_row = K; mid_row = I;
+      act_atoms = (K + 127) / 128; mid_atoms = (I + 127) / 128;
+      break;
+    case B200MOE_RECIPE_W4A16:
+      if (K % 32 != 0 || I % 32 != 0) return B200MOE_EINVAL;
+      act_row = 0; mid_row = I * 2;   // bf16 intermediate, A of FC1 is gathered from x
+      break;
+    default:
+      return B200MOE_EINVAL;
+  }
+  int64_t off = 0;
+  auto take = [&](int64_t nbytes) {
+    const int64_t o = off;
+    off = align_up64(off + nbytes, 1024);
+    return o;
+  };
+  L->status = take(16 * 4);
+  L->expert_counts = take(E * 4);
+  L->expert_offsets = take((E + 1) * 4);
+  L->tile_base = take((E + 1) * 4);
+  L->mtile_expert = take(mtile_cap * 4);
+  L->mtile_row0 = take(mtile_cap * 4);
+  L->mtile_rows = take(mtile_cap * 4);
+  L->sorted_route_ids = take(rows64 * 4);
+  L->inv_perm = take(rows64 * 4);
+  L->act_q = take(rows64 * act_row);
+  L->act_sf = take(mtile_cap * act_atoms * 512);
+  L->mid_q = take(rows64 * mid_row);
+  L->mid_sf = take(mtile_cap * mid_atoms * 512);
+  L->routed = take(rows64 * K * 4);
+  L->total_nbytes = off;
+  L->rows = static_cast<int32_t>(rows64);
+  L->mtile_cap = static_cast<int32_t>(mtile_cap);
+  return B200MOE_OK;
+}
+
+static int check_gemm_args(const b200moe_gemm_args* a) {
+  if (a == nullptr || a->scratch == nullptr || a->layout == nullptr || a->w13 == nullptr ||
+      a->w2 == nullptr || a->w1_alphas == nullptr || a->w2_alphas == nullptr)
+    return B200MOE_EINVAL;
+  if (a->num_tokens < 0 || a->num_topk <= 0 || a->num_experts <= 0) return B200MOE_EINVAL;
+  if (a->num_tokens * a->num_topk > a->layout->rows) return B200MOE_ECAPACITY;
+  if (a->activation < B200MOE_ACT_SILU || a->activation > B200MOE_ACT_SWIGLUOAI)
+    return B200MOE_EINVAL;
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_grouped_gemm1_act(const b200moe_gemm_args* a, void* stream) {
+  const int rc = check_gemm_args(a);
+  if (rc != B200MOE_OK) return rc;
+  if (a->num_tokens == 0) return B200MOE_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (a->recipe) {
+    case B200MOE_RECIPE_NVFP4:
+      if (a->w13_sf == nullptr || a->a2_gscale == nullptr) return B200MOE_EINVAL;
+      return b200moe::nvfp4_gemm1(a, s);
+    case B200MOE_RECIPE_W4A8_MX:
+      return b200moe::mx_gemm1(a, s);
+    case B200MOE_RECIPE_W4A16:
+      return b200moe::w4a16_gemm1(a, s);
+    default:
+      return B200MOE_EINVAL;
+  }
+}
+
+extern "C" int b200moe_grouped_gemm2(const b200moe_gemm_args* a, void* stream) {
+  const int rc = check_gemm_args(a);
+  if (rc != B200MOE_OK) return rc;
+  if (a->num_tokens == 0) return B200MOE_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (a->recipe) {
+    case B200MOE_RECIPE_NVFP4:
+      if (a->w2_sf == nullptr) return B200MOE_EINVAL;
+      return b200moe::nvfp4_gemm2(a, s);
+    case B200MOE_RECIPE_W4A8_MX:
+      return b200moe::mx_gemm2(a, s);
+    case B200MOE_RECIPE_W4A16:
+      return b200moe::w4a16_gemm2(a, s);
+    default:
+      return B200MOE_EINVAL;
+  }
+}

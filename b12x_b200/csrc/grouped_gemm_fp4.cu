@@ -1,0 +1,554 @@
+// Stages 4 and 5: grouped block-scaled expert GEMMs on tcgen05 (sm_100a).
+//
+//   FC1:  acc[128 x 256] = Xq[128 rows of one expert] . W13q[128 up rows ; 128 gate rows]^T
+//         epilogue: x alpha1 -> gated activation (fp32) -> round to bf16 -> NVFP4 re-quantise with
+//         a2_gscale -> codes + scale atoms of the FC2 A operand
+//   FC2:  acc[128 x 256] = Hq . W2q[256 rows]^T ; epilogue: x alpha2 -> float32 routed rows
+//
+// One persistent CTA per SM walks the (expert, n-tile, m-tile) work list that the sort kernel
+// left in the scratch arena.  Warp 0 feeds a 4-stage TMA pipeline (SWIZZLE_128B operand tiles +
+// plain bulk copies of the 512-byte scale atoms), warp 1 copies the scale atoms into TMEM with
+// tcgen05.cp and issues tcgen05.mma.kind::mxf4nvf4.block_scale (scale_vec::4X), warps 2..5 drain
+// the TMEM accumulator.  Every wait is bounded; a wait that runs out marks the status block and
+// every role leaves its loop.
+#include "common.cuh"
+
+namespace b200moe {
+
+constexpr int kBM = 128;            // tile rows (MMA M)
+constexpr int kBN = 256;            // MMA N = two 128-row weight sub-tiles
+constexpr int kStages = 4;
+constexpr int kRowBytes = 128;      // one swizzled operand row per stage = 256 FP4 values
+constexpr int kKPerStage = 256;     // reduction elements per stage
+constexpr int kKPerMma = 64;
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kTmemSfa = 256;       // 4 stages x 16 columns
+constexpr int kTmemSfb = 320;       // 4 stages x 32 columns
+
+constexpr int kSmemA = kBM * kRowBytes;        // 16 KiB
+constexpr int kSmemB = kBN * kRowBytes;        // 32 KiB
+constexpr int kSmemSfa = 4 * 512;              // 4 k-steps x one atom
+constexpr int kSmemSfb = 2 * 4 * 512;          // 2 sub-tiles x 4 k-steps
+constexpr int kMaxExperts = 1024;
+
+struct __align__(8) GemmSmemTail {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full;
+  uint64_t tmem_empty;
+  uint32_t tmem_base;
+  int abort_flag;
+  int32_t tile_base[kMaxExperts + 1];
+};
+constexpr int kGemmSmemBytes =
+    1024 + kStages * (kSmemA + kSmemB + kSmemSfa + kSmemSfb) + static_cast<int>(sizeof(GemmSmemTail));
+
+enum { EPI_FC1_GATED = 0, EPI_FC1_RELU2 = 1, EPI_FC2 = 2 };
+
+struct GemmParams {
+  const uint8_t* sfa;            // activation scale atoms [mtile][atoms_k][512]
+  const uint8_t* sfb;            // weight scale atoms [E][rowgroups][atoms_k][512]
+  const int32_t* tile_base;      // [E+1]
+  const int32_t* mtile_expert;
+  const int32_t* mtile_row0;
+  const int32_t* mtile_rows;
+  int32_t* status;
+  const float* alphas;           // [E]
+  const float* gscale2;          // FC1 epilogue: reciprocal FC2-input scale
+  uint8_t* out_q;                // FC1: codes [rows][out_cols/2]
+  uint8_t* out_sf;               // FC1: scale atoms [mtile][out_atoms][512]
+  float* out_f32;                // FC2: routed rows [rows][out_cols]
+  float* tap;                    // FC1 debug tap [rows][w_rows] or null
+  int E, n_tiles, kdim, k_blocks, atoms_k;
+  int sfb_rowgroups;             // per expert
+  int w_rows;                    // weight rows per expert
+  int sub0_base, sub1_base;      // first weight row of the two sub-tiles at n-tile 0
+  int n_step;                    // weight rows advanced per n-tile
+  int out_cols;                  // I (FC1) or K (FC2)
+  int out_atoms;                 // FC1: scale atoms per tile of the output
+  int gscale_len;
+  float limit, act_alpha, act_beta;
+  int swigluoai;
+};
+
+struct TileCoord {
+  int e, mt, nt;
+};
+// work id -> (expert, m-tile, n-tile); expert-major, then n-tile, m-tile fastest, so that the CTAs
+// running at the same time share weight tiles through L2.
+__device__ __forceinline__ TileCoord decode_tile(int w, int n_tiles, const int32_t* tb, int E) {
+  const int q = w / n_tiles;
+  int lo = 0, hi = E;  // e = number of i in [1,E] with tb[i] <= q
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (tb[mid + 1] <= q) lo = mid + 1; else hi = mid;
+  }
+  TileCoord c;
+  c.e = lo;
+  const int me = tb[lo + 1] - tb[lo];
+  const int local = w - tb[lo] * n_tiles;
+  c.nt = local / me;
+  c.mt = tb[lo] + local % me;
+  return c;
+}
+
+__device__ __forceinline__ float act_gated(float gate, float up, const GemmParams& p) {
+  if (p.limit > 0.f) {
+    gate = fminf(gate, p.limit);
+    up = fminf(fmaxf(up, -p.limit), p.limit);
+  }
+  if (p.swigluoai) {
+    const float s = __fdiv_rn(1.0f, 1.0f + expf(-(p.act_alpha * gate)));
+    return (gate * s) * (up + p.act_beta);
+  }
+  const float s = __fdiv_rn(1.0f, 1.0f + expf(-gate));
+  return (gate * s) * up;
+}
+
+__device__ __forceinline__ float round_bf16(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// same arithmetic as quant_block16 in the activation quantiser
+__device__ __forceinline__ void requant_block16(const float (&v)[16], float gs, uint32_t& lo,
+                                                uint32_t& hi, uint8_t& sf_byte) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const float raw = fminf(__fdiv_rn(__fmul_rn(amax, gs), 6.0f), 448.0f);
+  sf_byte = f32_to_e4m3_rn_sat(raw);
+  const float sf = e4m3_to_f32(sf_byte);
+  const float denom = fmaxf(__fdiv_rn(sf, gs), 1e-30f);
+  float q0[8], q1[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    q0[i] = __fdiv_rn(v[i], denom);
+    q1[i] = __fdiv_rn(v[8 + i], denom);
+  }
+  lo = pack_e2m1x8(q0);
+  hi = pack_e2m1x8(q1);
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA,
+                          const __grid_constant__ CUtensorMap tmA_small,
+                          const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + kStages * kSmemA;
+  uint8_t* sSfa = sB + kStages * kSmemB;
+  uint8_t* sSfb = sSfa + kStages * kSmemSfa;
+  GemmSmemTail* tail = reinterpret_cast<GemmSmemTail*>(sSfb + kStages * kSmemSfb);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->empty[s], 1);
+    }
+    mbar_init(&tail->tmem_full, 1);
+    mbar_init(&tail->tmem_empty, 4);
+    tail->abort_flag = 0;
+    fence_mbar_init();
+  }
+  for (int i = threadIdx.x; i <= p.E; i += blockDim.x) tail->tile_base[i] = p.tile_base[i];
+  if (warp == 1) {
+    tmem_alloc(&tail->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  const uint32_t tmem_base = tail->tmem_base;
+  volatile int* abort_flag = &tail->abort_flag;
+  const int total_work = tail->tile_base[p.E] * p.n_tiles;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmA_small);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
+        const int row0 = p.mtile_row0[c.mt];
+        // tiles of a decode batch hold a few rows: fetch 32 activation rows instead of 128 (the
+        // other rows of the shared-memory tile keep stale data; MMA rows are independent)
+        const bool small_a = p.mtile_rows[c.mt] <= 32;
+        const CUtensorMap* tma_a = small_a ? &tmA_small : &tmA;
+        const uint32_t a_bytes = (small_a ? 32u : 128u) * kRowBytes;
+        const int r0 = p.sub0_base + c.nt * p.n_step;   // weight row inside the expert
+        int r1 = p.sub1_base + c.nt * p.n_step;
+        if (r1 >= p.w_rows) r1 = r0;                    // half-empty last tile: reload sub-tile 0
+        const uint8_t* sfa_src = p.sfa + static_cast<size_t>(c.mt) * p.atoms_k * 512;
+        const uint8_t* sfb0 =
+            p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + (r0 >> 7)) * p.atoms_k * 512;
+        const uint8_t* sfb1 =
+            p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + (r1 >> 7)) * p.atoms_k * 512;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status,
+                                 WAIT_SMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const int ksteps = min(4, (p.kdim - kb * kKPerStage) / kKPerMma);
+          const uint32_t sf_bytes = static_cast<uint32_t>(ksteps) * 512u;
+          uint64_t* bar = &tail->full[stage];
+          mbar_expect_tx(bar, a_bytes + kSmemB + 3u * sf_bytes);
+          tma_load_2d(sA + stage * kSmemA, tma_a, bar, kb * kRowBytes, row0);
+          tma_load_2d(sB + stage * kSmemB, &tmB, bar, kb * kRowBytes, c.e * p.w_rows + r0);
+          tma_load_2d(sB + stage * kSmemB + kSmemB / 2, &tmB, bar, kb * kRowBytes,
+                      c.e * p.w_rows + r1);
+          bulk_load(sSfa + stage * kSmemSfa, sfa_src + static_cast<size_t>(kb) * 2048, sf_bytes, bar);
+          bulk_load(sSfb + stage * kSmemSfb, sfb0 + static_cast<size_t>(kb) * 2048, sf_bytes, bar);
+          bulk_load(sSfb + stage * kSmemSfb + 2048, sfb1 + static_cast<size_t>(kb) * 2048, sf_bytes,
+                    bar);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // give copies that are still in flight time to land before the CTA leaves
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_block_scaled(kBM, kBN, /*a*/ 1, /*b*/ 1, /*ue4m3*/ 0);
+      int stage = 0;
+      uint32_t phase = 0, tile_phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        if (!mbar_wait_bounded(&tail->tmem_empty, tile_phase ^ 1, abort_flag, p.status,
+                               WAIT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const int ksteps = min(4, (p.kdim - kb * kKPerStage) / kKPerMma);
+          const uint32_t sfa_t = tmem_base + kTmemSfa + stage * 16;
+          const uint32_t sfb_t = tmem_base + kTmemSfb + stage * 32;
+          const uint32_t sfa_s = smem_u32(sSfa + stage * kSmemSfa);
+          const uint32_t sfb_s = smem_u32(sSfb + stage * kSmemSfb);
+          for (int j = 0; j < ksteps; ++j) {
+            tc_cp_32x128b_warpx4(sfa_t + 4 * j, make_desc_sf(sfa_s + 512 * j));
+            tc_cp_32x128b_warpx4(sfb_t + 8 * j, make_desc_sf(sfb_s + 512 * j));
+            tc_cp_32x128b_warpx4(sfb_t + 8 * j + 4, make_desc_sf(sfb_s + 2048 + 512 * j));
+          }
+          const uint64_t adesc = make_desc_sw128(smem_u32(sA + stage * kSmemA));
+          const uint64_t bdesc = make_desc_sw128(smem_u32(sB + stage * kSmemB));
+          for (int j = 0; j < ksteps; ++j) {
+            // 64 FP4 values = 32 bytes further along the swizzled row -> +2 in 16-byte units
+            mma_nvf4_4x(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j, sfb_t + 8 * j,
+                        (kb > 0 || j > 0) ? 1u : 0u);
+          }
+          tc_commit(&tail->empty[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(&tail->tmem_full);
+        tile_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int sub = warp & 3;                 // TMEM sub-partition this warp may read
+    const int m = sub * 32 + lane;            // tile row = TMEM lane
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(sub * 32) << 16);
+    uint32_t tile_phase = 0;
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+      const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
+      const int row0 = p.mtile_row0[c.mt];
+      const int nrows = p.mtile_rows[c.mt];
+      const float alpha = p.alphas[c.e];
+      if (!mbar_wait_bounded(&tail->tmem_full, tile_phase, abort_flag, p.status, WAIT_TMEM_FULL))
+        break;
+      tile_phase ^= 1;
+      tc_fence_after();
+      const bool valid = m < nrows;
+      const size_t pos = static_cast<size_t>(row0 + m);
+
+      if (EPI == EPI_FC1_GATED) {
+        const float gs2 = p.gscale2[p.gscale_len > 1 ? c.e : 0];
+        const int col0 = c.nt * 128;          // first intermediate column of this tile
+        uint32_t codes[16];
+        uint32_t sfw[2] = {0u, 0u};
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t ru[16], rg[16];
+          tc_ld_32x32b_x16(t_lane + ch * 16, ru);
+          tc_ld_32x32b_x16(t_lane + 128 + ch * 16, rg);
+          tc_wait_ld();
+          float h[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float up = __fmul_rn(__uint_as_float(ru[i]), alpha);
+            const float gate = __fmul_rn(__uint_as_float(rg[i]), alpha);
+            if (p.tap != nullptr && valid) {
+              float* trow = p.tap + pos * p.w_rows;
+              trow[p.sub0_base + col0 + ch * 16 + i] = up;
+              trow[p.sub1_base + col0 + ch * 16 + i] = gate;
+            }
+            h[i] = round_bf16(act_gated(gate, up, p));
+          }
+          uint8_t sfb;
+          requant_block16(h, gs2, codes[2 * ch], codes[2 * ch + 1], sfb);
+          sfw[ch >> 2] |= static_cast<uint32_t>(sfb) << (8 * (ch & 3));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->tmem_empty);
+        if (valid) {
+          uint4* dst = reinterpret_cast<uint4*>(p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1));
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            dst[q] = make_uint4(codes[4 * q], codes[4 * q + 1], codes[4 * q + 2], codes[4 * q + 3]);
+        }
+        // scale atoms are per tile: padding rows are written too (their values are never used)
+        uint8_t* sft = p.out_sf + static_cast<size_t>(c.mt) * p.out_atoms * 512;
+        *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 8)) = sfw[0];
+        *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 8 + 4)) = sfw[1];
+      } else if (EPI == EPI_FC1_RELU2) {
+        const float gs2 = p.gscale2[p.gscale_len > 1 ? c.e : 0];
+        const int col0 = c.nt * 256;
+        uint8_t* sft = p.out_sf + static_cast<size_t>(c.mt) * p.out_atoms * 512;
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          if (col0 + half * 128 >= p.out_cols) break;
+          uint32_t codes[16];
+          uint32_t sfw[2] = {0u, 0u};
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            uint32_t rr[16];
+            tc_ld_32x32b_x16(t_lane + half * 128 + ch * 16, rr);
+            tc_wait_ld();
+            float h[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float v = __fmul_rn(__uint_as_float(rr[i]), alpha);
+              if (p.tap != nullptr && valid)
+                p.tap[pos * p.w_rows + col0 + half * 128 + ch * 16 + i] = v;
+              const float r = fmaxf(v, 0.f);
+              h[i] = round_bf16(__fmul_rn(r, r));
+            }
+            uint8_t sfb;
+            requant_block16(h, gs2, codes[2 * ch], codes[2 * ch + 1], sfb);
+            sfw[ch >> 2] |= static_cast<uint32_t>(sfb) << (8 * (ch & 3));
+          }
+          if (valid) {
+            uint4* dst = reinterpret_cast<uint4*>(p.out_q + pos * (p.out_cols >> 1) +
+                                                  ((col0 + half * 128) >> 1));
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              dst[q] = make_uint4(codes[4 * q], codes[4 * q + 1], codes[4 * q + 2], codes[4 * q + 3]);
+          }
+          *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 16 + half * 8)) = sfw[0];
+          *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 16 + half * 8 + 4)) = sfw[1];
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->tmem_empty);
+      } else {
+        const int col0 = c.nt * 256;
+        float* orow = p.out_f32 + pos * p.out_cols + col0;
+#pragma unroll 1
+        for (int ch = 0; ch < 16; ++ch) {
+          uint32_t rr[16];
+          tc_ld_32x32b_x16(t_lane + ch * 16, rr);
+          tc_wait_ld();
+          if (valid && col0 + ch * 16 < p.out_cols) {
+            float4* dst = reinterpret_cast<float4*>(orow + ch * 16);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              dst[q] = make_float4(__fmul_rn(__uint_as_float(rr[4 * q]), alpha),
+                                   __fmul_rn(__uint_as_float(rr[4 * q + 1]), alpha),
+                                   __fmul_rn(__uint_as_float(rr[4 * q + 2]), alpha),
+                                   __fmul_rn(__uint_as_float(rr[4 * q + 3]), alpha));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->tmem_empty);
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------ host side ---------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D byte matrix [rows][row_bytes], box = box_rows x 128 bytes, 128-byte swizzle.
+int make_tmap_bytes_2d(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,
+                       uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return B200MOE_ECUDA;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_bytes & 15) != 0) return B200MOE_EALIGN;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {128, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r =
+      fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+static int num_sms_cached() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int EPI>
+static int launch_nvfp4(const CUtensorMap& tmA, const CUtensorMap& tmA_small,
+                        const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t s) {
+  auto kern = grouped_gemm_nvfp4_kernel<EPI>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes) !=
+      cudaSuccess)
+    return B200MOE_ECUDA;
+  kern<<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmA, tmA_small, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+int nvfp4_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
+  const b200moe_scratch_layout& L = *a->layout;
+  const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
+  const bool gated = a->activation != B200MOE_ACT_RELU2;
+  if (K % 64 != 0 || I % 128 != 0 || E > kMaxExperts) return B200MOE_EINVAL;
+  const int w_rows = gated ? 2 * I : I;
+  char* base = static_cast<char*>(a->scratch);
+  CUtensorMap tmA, tmA_small, tmB;
+  int rc = make_tmap_bytes_2d(&tmA, base + L.act_q, K / 2, L.rows, 128);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_tmap_bytes_2d(&tmA_small, base + L.act_q, K / 2, L.rows, 32);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_tmap_bytes_2d(&tmB, a->w13, K / 2, static_cast<uint64_t>(E) * w_rows, 128);
+  if (rc != B200MOE_OK) return rc;
+  GemmParams p = {};
+  p.sfa = reinterpret_cast<const uint8_t*>(base + L.act_sf);
+  p.sfb = a->w13_sf;
+  p.tile_base = reinterpret_cast<const int32_t*>(base + L.tile_base);
+  p.mtile_expert = reinterpret_cast<const int32_t*>(base + L.mtile_expert);
+  p.mtile_row0 = reinterpret_cast<const int32_t*>(base + L.mtile_row0);
+  p.mtile_rows = reinterpret_cast<const int32_t*>(base + L.mtile_rows);
+  p.status = reinterpret_cast<int32_t*>(base + L.status);
+  p.alphas = a->w1_alphas;
+  p.gscale2 = a->a2_gscale;
+  p.out_q = reinterpret_cast<uint8_t*>(base + L.mid_q);
+  p.out_sf = reinterpret_cast<uint8_t*>(base + L.mid_sf);
+  p.tap = a->fc1_tap;
+  p.E = E;
+  p.kdim = K;
+  p.k_blocks = ceil_div_i(K, kKPerStage);
+  p.atoms_k = ceil_div_i(K, 64);
+  p.w_rows = w_rows;
+  p.sfb_rowgroups = ceil_div_i(w_rows, 128);
+  p.out_cols = I;
+  p.out_atoms = ceil_div_i(I, 64);
+  p.gscale_len = a->gscale_len;
+  p.limit = a->swiglu_limit;
+  p.act_alpha = a->swiglu_alpha;
+  p.act_beta = a->swiglu_beta;
+  p.swigluoai = a->activation == B200MOE_ACT_SWIGLUOAI;
+  const int grid = a->num_sms > 0 ? a->num_sms : num_sms_cached();
+  if (gated) {
+    p.n_tiles = I / 128;
+    p.n_step = 128;
+    p.sub0_base = a->gate_first ? I : 0;   // sub-tile 0 = up rows
+    p.sub1_base = a->gate_first ? 0 : I;   // sub-tile 1 = gate rows
+    return launch_nvfp4<EPI_FC1_GATED>(tmA, tmA_small, tmB, p, grid, stream);
+  }
+  p.n_tiles = ceil_div_i(I, 256);
+  p.n_step = 256;
+  p.sub0_base = 0;
+  p.sub1_base = 128;
+  return launch_nvfp4<EPI_FC1_RELU2>(tmA, tmA_small, tmB, p, grid, stream);
+}
+
+int nvfp4_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
+  const b200moe_scratch_layout& L = *a->layout;
+  const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
+  if (I % 64 != 0 || K % 128 != 0 || E > kMaxExperts) return B200MOE_EINVAL;
+  char* base = static_cast<char*>(a->scratch);
+  CUtensorMap tmA, tmA_small, tmB;
+  int rc = make_tmap_bytes_2d(&tmA, base + L.mid_q, I / 2, L.rows, 128);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_tmap_bytes_2d(&tmA_small, base + L.mid_q, I / 2, L.rows, 32);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_tmap_bytes_2d(&tmB, a->w2, I / 2, static_cast<uint64_t>(E) * K, 128);
+  if (rc != B200MOE_OK) return rc;
+  GemmParams p = {};
+  p.sfa = reinterpret_cast<const uint8_t*>(base + L.mid_sf);
+  p.sfb = a->w2_sf;
+  p.tile_base = reinterpret_cast<const int32_t*>(base + L.tile_base);
+  p.mtile_expert = reinterpret_cast<const int32_t*>(base + L.mtile_expert);
+  p.mtile_row0 = reinterpret_cast<const int32_t*>(base + L.mtile_row0);
+  p.mtile_rows = reinterpret_cast<const int32_t*>(base + L.mtile_rows);
+  p.status = reinterpret_cast<int32_t*>(base + L.status);
+  p.alphas = a->w2_alphas;
+  p.out_f32 = reinterpret_cast<float*>(base + L.routed);
+  p.E = E;
+  p.kdim = I;
+  p.k_blocks = ceil_div_i(I, kKPerStage);
+  p.atoms_k = ceil_div_i(I, 64);
+  p.w_rows = K;
+  p.sfb_rowgroups = ceil_div_i(K, 128);
+  p.out_cols = K;
+  p.n_tiles = ceil_div_i(K, 256);
+  p.n_step = 256;
+  p.sub0_base = 0;
+  p.sub1_base = 128;
+  const int grid = a->num_sms > 0 ? a->num_sms : num_sms_cached();
+  return launch_nvfp4<EPI_FC2>(tmA, tmA_small, tmB, p, grid, stream);
+}
+
+}  // namespace b200moe

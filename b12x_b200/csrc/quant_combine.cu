@@ -1,0 +1,299 @@
+// Stage 3 (permute + activation quantisation) and stage 6 (top-k weighted combine).
+// Both are HBM-bound streaming kernels: 16-byte vector accesses, one warp per row.
+#include "common.cuh"
+
+namespace b200moe {
+
+// ------------------------------------------------------------------------------------------
+// NVFP4 activation quantiser, exact ("direct division") variant of the reference oracle
+// (b12x/moe/_shared/kernels/reference.py:269-300):
+//   sf    = e4m3_rn(min(amax * gs / 6, 448))
+//   code  = e2m1_rte(x / max(sf / gs, 1e-30))
+// One lane owns one 16-element block at a time.  Codes go to act_q[pos][K/2]; scales go to the
+// 512-byte atoms of the row's 128-row tile, which is the layout tcgen05 block-scaled MMA reads.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void quant_block16(const float (&v)[16], float gs, uint32_t& lo,
+                                              uint32_t& hi, uint8_t& sf_byte) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const float raw = fminf(__fdiv_rn(__fmul_rn(amax, gs), 6.0f), 448.0f);
+  sf_byte = f32_to_e4m3_rn_sat(raw);
+  const float sf = e4m3_to_f32(sf_byte);
+  const float denom = fmaxf(__fdiv_rn(sf, gs), 1e-30f);
+  float q0[8], q1[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    q0[i] = __fdiv_rn(v[i], denom);
+    q1[i] = __fdiv_rn(v[8 + i], denom);
+  }
+  lo = pack_e2m1x8(q0);
+  hi = pack_e2m1x8(q1);
+}
+
+__global__ void __launch_bounds__(256) permute_quant_nvfp4_kernel(
+    const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, const float* __restrict__ gscale,
+    int gscale_len, int num_topk, int K, const int32_t* __restrict__ tile_base, int E,
+    const int32_t* __restrict__ mtile_expert, const int32_t* __restrict__ mtile_row0,
+    const int32_t* __restrict__ mtile_rows, const int32_t* __restrict__ sorted_route_ids,
+    uint8_t* __restrict__ act_q, uint8_t* __restrict__ act_sf) {
+  const int mt = blockIdx.x;
+  if (mt >= tile_base[E]) return;
+  const int e = mtile_expert[mt];
+  const int row0 = mtile_row0[mt];
+  const int nrows = mtile_rows[mt];
+  const float gs = gscale[gscale_len > 1 ? e : 0];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nblk = K >> 4;                    // 16-element blocks per row
+  const int atoms = (nblk + 3) >> 2;          // 512-byte scale atoms per tile
+  uint8_t* sf_tile = act_sf + static_cast<size_t>(mt) * atoms * 512;
+
+  for (int i = blockIdx.y * 8 + warp; i < nrows; i += gridDim.y * 8) {
+    const int pos = row0 + i;
+    const int r = sorted_route_ids[pos];
+    const int t = r / num_topk;
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(t) * x_row_stride);
+    uint2* dst = reinterpret_cast<uint2*>(act_q + static_cast<size_t>(pos) * (K >> 1));
+    for (int b0 = 0; b0 < nblk; b0 += 32) {
+      const int b = b0 + lane;
+      uint8_t sfb = 0;
+      if (b < nblk) {
+        const uint4 p0 = __ldg(src + 2 * b), p1 = __ldg(src + 2 * b + 1);
+        const uint32_t w[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[2 * j] = __uint_as_float(w[j] << 16);
+          v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+        uint32_t lo, hi;
+        quant_block16(v, gs, lo, hi, sfb);
+        dst[b] = make_uint2(lo, hi);
+      }
+      // four neighbouring lanes hold the four scales of one 32-bit word of the atom
+      uint32_t word = sfb;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 1) << 8;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 2) << 16;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 3) << 24;
+      if ((lane & 3) == 0 && b < nblk) {
+        *reinterpret_cast<uint32_t*>(sf_tile + sf_atom_offset(i, b)) = word;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// MXFP8 activation quantiser (b12x/_lib/intrinsics.py:223-265): per 32 elements
+//   byte  = exponent of pow2_ceil(amax * (1/448))   (mantissa != 0 -> exponent + 1; 0 -> byte 0)
+//   code  = e4m3_rn_sat(x * 2^(127 - byte))
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint8_t ue8m0_ceil_byte(float s) {
+  uint32_t bits = __float_as_uint(s);
+  if (bits & 0x007fffffu) bits = (bits + 0x00800000u) & 0x7f800000u;
+  return static_cast<uint8_t>((bits >> 23) & 0xffu);
+}
+__device__ __forceinline__ float ue8m0_inv_scale(uint8_t byte) {
+  if (byte == 0) return 0.f;
+  const int ex = 254 - static_cast<int>(byte);
+  return __uint_as_float(static_cast<uint32_t>(ex < 0 ? 0 : ex) << 23);
+}
+
+__global__ void __launch_bounds__(256) permute_quant_mxfp8_kernel(
+    const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, int num_topk, int K,
+    const int32_t* __restrict__ tile_base, int E, const int32_t* __restrict__ mtile_row0,
+    const int32_t* __restrict__ mtile_rows, const int32_t* __restrict__ sorted_route_ids,
+    uint8_t* __restrict__ act_q, uint8_t* __restrict__ act_sf) {
+  const int mt = blockIdx.x;
+  if (mt >= tile_base[E]) return;
+  const int row0 = mtile_row0[mt];
+  const int nrows = mtile_rows[mt];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nblk = K >> 5;            // 32-element blocks per row
+  const int atoms = (nblk + 3) >> 2;
+  uint8_t* sf_tile = act_sf + static_cast<size_t>(mt) * atoms * 512;
+
+  for (int i = blockIdx.y * 8 + warp; i < nrows; i += gridDim.y * 8) {
+    const int pos = row0 + i;
+    const int r = sorted_route_ids[pos];
+    const int t = r / num_topk;
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(t) * x_row_stride);
+    uint4* dst = reinterpret_cast<uint4*>(act_q + static_cast<size_t>(pos) * K);
+    for (int b0 = 0; b0 < nblk; b0 += 32) {
+      const int b = b0 + lane;
+      uint8_t sfb = 0;
+      if (b < nblk) {
+        float v[32];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 p = __ldg(src + 4 * b + q);
+          const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            v[q * 8 + 2 * j] = __uint_as_float(w[j] << 16);
+            v[q * 8 + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+          }
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        sfb = ue8m0_ceil_byte(__fmul_rn(amax, 1.0f / 448.0f));
+        const float inv = ue8m0_inv_scale(sfb);
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t acc = 0;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float s = fminf(fmaxf(__fmul_rn(v[4 * j + k], inv), -448.f), 448.f);
+            acc |= static_cast<uint32_t>(f32_to_e4m3_rn_sat(s)) << (8 * k);
+          }
+          o[j] = acc;
+        }
+        dst[2 * b] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[2 * b + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+      uint32_t word = sfb;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 1) << 8;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 2) << 16;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 3) << 24;
+      if ((lane & 3) == 0 && b < nblk) {
+        *reinterpret_cast<uint32_t*>(sf_tile + sf_atom_offset(i, b)) = word;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// combine: out[t] = sum over slots (slot order) of w[t,slot] * routed[pos(t,slot)], each product
+// and each sum rounded to fp32 separately (no fused multiply-add), one final rounding to bf16.
+// This is the accumulation of the reference oracle (reference.py:408-411, 988-990).
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) combine_kernel(
+    const float* __restrict__ routed, const int32_t* __restrict__ inv_perm,
+    const float* __restrict__ topk_weights, void* __restrict__ out, int64_t out_row_stride,
+    int num_topk, int K, int out_f32, float output_scale) {
+  const int t = blockIdx.x;
+  extern __shared__ int32_t sm[];
+  int32_t* pos = sm;
+  float* w = reinterpret_cast<float*>(sm + num_topk);
+  for (int s = threadIdx.x; s < num_topk; s += blockDim.x) {
+    pos[s] = inv_perm[static_cast<int64_t>(t) * num_topk + s];
+    w[s] = topk_weights[static_cast<int64_t>(t) * num_topk + s];
+  }
+  __syncthreads();
+  const int nvec = K >> 2;
+  for (int j = threadIdx.x; j < nvec; j += blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < num_topk; ++s) {
+      const int p = pos[s];
+      if (p < 0) continue;
+      const float4 v = __ldg(reinterpret_cast<const float4*>(routed + static_cast<size_t>(p) * K) + j);
+      const float ws = w[s];
+      acc.x = __fadd_rn(acc.x, __fmul_rn(ws, v.x));
+      acc.y = __fadd_rn(acc.y, __fmul_rn(ws, v.y));
+      acc.z = __fadd_rn(acc.z, __fmul_rn(ws, v.z));
+      acc.w = __fadd_rn(acc.w, __fmul_rn(ws, v.w));
+    }
+    if (out_f32) {
+      float* o = reinterpret_cast<float*>(out) + static_cast<int64_t>(t) * out_row_stride;
+      if (output_scale != 1.0f) {
+        acc.x = __fmul_rn(acc.x, output_scale);
+        acc.y = __fmul_rn(acc.y, output_scale);
+        acc.z = __fmul_rn(acc.z, output_scale);
+        acc.w = __fmul_rn(acc.w, output_scale);
+      }
+      reinterpret_cast<float4*>(o)[j] = acc;
+    } else {
+      __nv_bfloat16 b[4] = {__float2bfloat16_rn(acc.x), __float2bfloat16_rn(acc.y),
+                            __float2bfloat16_rn(acc.z), __float2bfloat16_rn(acc.w)};
+      if (output_scale != 1.0f) {
+        // the caller-visible scaling is an in-place multiply of the bf16 output
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          b[q] = __float2bfloat16_rn(__fmul_rn(__bfloat162float(b[q]), output_scale));
+      }
+      __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + static_cast<int64_t>(t) * out_row_stride;
+      uint2 pk;
+      pk.x = static_cast<uint32_t>(__bfloat16_as_ushort(b[0])) |
+             (static_cast<uint32_t>(__bfloat16_as_ushort(b[1])) << 16);
+      pk.y = static_cast<uint32_t>(__bfloat16_as_ushort(b[2])) |
+             (static_cast<uint32_t>(__bfloat16_as_ushort(b[3])) << 16);
+      reinterpret_cast<uint2*>(o)[j] = pk;
+    }
+  }
+}
+
+}  // namespace b200moe
+
+using namespace b200moe;
+
+static int check_quant_args(const b200moe_quant_args* a, int block) {
+  if (a == nullptr || a->x == nullptr || a->scratch == nullptr || a->layout == nullptr)
+    return B200MOE_EINVAL;
+  if (a->hidden_size <= 0 || a->hidden_size % block != 0 || a->hidden_size % 8 != 0)
+    return B200MOE_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(a->x) & 15) != 0 || (a->x_row_stride % 8) != 0)
+    return B200MOE_EALIGN;
+  if (a->num_tokens * a->num_topk > a->layout->rows) return B200MOE_ECAPACITY;
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_permute_quant_nvfp4(const b200moe_quant_args* a, void* stream) {
+  const int rc = check_quant_args(a, 16);
+  if (rc != B200MOE_OK) return rc;
+  if (a->a1_gscale == nullptr || (a->gscale_len != 1 && a->gscale_len != a->num_experts))
+    return B200MOE_EINVAL;
+  if (a->num_tokens == 0) return B200MOE_OK;
+  const b200moe_scratch_layout& L = *a->layout;
+  char* base = static_cast<char*>(a->scratch);
+  const int rows = a->num_tokens * a->num_topk;
+  const int mtiles = (rows + 127) / 128 + (a->num_experts < rows ? a->num_experts : rows);
+  // tiles of a decode batch hold few rows: one CTA per tile; large batches: 4 CTAs per tile
+  const dim3 grid(mtiles < L.mtile_cap ? mtiles : L.mtile_cap, a->num_tokens >= 256 ? 4 : 1);
+  permute_quant_nvfp4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride, a->a1_gscale, a->gscale_len,
+      a->num_topk, a->hidden_size, reinterpret_cast<const int32_t*>(base + L.tile_base),
+      a->num_experts, reinterpret_cast<const int32_t*>(base + L.mtile_expert),
+      reinterpret_cast<const int32_t*>(base + L.mtile_row0),
+      reinterpret_cast<const int32_t*>(base + L.mtile_rows),
+      reinterpret_cast<const int32_t*>(base + L.sorted_route_ids),
+      reinterpret_cast<uint8_t*>(base + L.act_q), reinterpret_cast<uint8_t*>(base + L.act_sf));
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+extern "C" int b200moe_permute_quant_mxfp8(const b200moe_quant_args* a, void* stream) {
+  const int rc = check_quant_args(a, 32);
+  if (rc != B200MOE_OK) return rc;
+  if (a->num_tokens == 0) return B200MOE_OK;
+  const b200moe_scratch_layout& L = *a->layout;
+  char* base = static_cast<char*>(a->scratch);
+  const int rows = a->num_tokens * a->num_topk;
+  const int mtiles = (rows + 127) / 128 + (a->num_experts < rows ? a->num_experts : rows);
+  const dim3 grid(mtiles < L.mtile_cap ? mtiles : L.mtile_cap, a->num_tokens >= 256 ? 4 : 1);
+  permute_quant_mxfp8_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride, a->num_topk, a->hidden_size,
+      reinterpret_cast<const int32_t*>(base + L.tile_base), a->num_experts,
+      reinterpret_cast<const int32_t*>(base + L.mtile_row0),
+      reinterpret_cast<const int32_t*>(base + L.mtile_rows),
+      reinterpret_cast<const int32_t*>(base + L.sorted_route_ids),
+      reinterpret_cast<uint8_t*>(base + L.act_q), reinterpret_cast<uint8_t*>(base + L.act_sf));
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+extern "C" int b200moe_combine(const b200moe_combine_args* a, void* stream) {
+  if (a == nullptr || a->topk_weights == nullptr || a->out == nullptr || a->scratch == nullptr ||
+      a->layout == nullptr)
+    return B200MOE_EINVAL;
+  if (a->hidden_size <= 0 || a->hidden_size % 4 != 0 || a->num_topk <= 0) return B200MOE_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(a->out) & 15) != 0 || (a->out_row_stride % 4) != 0)
+    return B200MOE_EALIGN;
+  if (a->num_tokens * a->num_topk > a->layout->rows) return B200MOE_ECAPACITY;
+  if (a->num_tokens == 0) return B200MOE_OK;
+  const b200moe_scratch_layout& L = *a->layout;
+  char* base = static_cast<char*>(a->scratch);
+  combine_kernel<<<a->num_tokens, 256, a->num_topk * 8, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float*>(base + L.routed),
+      reinterpret_cast<const int32_t*>(base + L.inv_perm), a->topk_weights, a->out,
+      a->out_row_stride, a->num_topk, a->hidden_size, a->out_f32, a->output_scale);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}

@@ -1,0 +1,299 @@
+// Stage 1 (top-k routing) and stage 2 (stable expert sort) of the fused MoE layer.
+// Both are tiny integer/compare kernels; the sort is a single-CTA stable counting sort so that
+// the permutation is canonical: positions ordered by (expert asc, flat route id asc).
+#include "common.cuh"
+
+namespace b200moe {
+
+// ------------------------------------------------------------------------------------------
+// route_topk: one warp per token.  Lane l holds experts l, l+32, ... (E <= 1024 -> 32 values).
+// Selection repeats "max, ties to the LARGEST expert index" k times, which is the tie rule of
+// the reference router (b12x/moe/_shared/routing.py:38-46).
+// ------------------------------------------------------------------------------------------
+constexpr int kRouteMaxPerLane = 32;  // 1024 experts
+
+template <int MODE>
+__global__ void __launch_bounds__(128) route_topk_kernel(b200moe_route_args a) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= a.num_tokens) return;
+  const int E = a.num_experts;
+  const int per_lane = (E + 31) >> 5;
+  const float NEG_INF = __int_as_float(0xff800000);
+
+  float raw[kRouteMaxPerLane];  // raw logit
+  float sel[kRouteMaxPerLane];  // value used for selection
+#pragma unroll
+  for (int i = 0; i < kRouteMaxPerLane; ++i) {
+    raw[i] = NEG_INF;
+    sel[i] = NEG_INF;
+    if (i < per_lane) {
+      const int e = i * 32 + lane;
+      if (e < E) {
+        float v;
+        if (a.logits_dtype == B200MOE_DT_BF16) {
+          v = __bfloat162float(
+              reinterpret_cast<const __nv_bfloat16*>(a.logits)[warp * a.logits_row_stride + e]);
+        } else {
+          v = reinterpret_cast<const float*>(a.logits)[warp * a.logits_row_stride + e];
+        }
+        raw[i] = v;
+        if (MODE == B200MOE_ROUTE_SIGMOID) {
+          const float s = 1.0f / (1.0f + expf(-v));
+          raw[i] = s;  // "original score"
+          sel[i] = a.bias ? s + a.bias[e] : s;
+        } else {
+          sel[i] = v;
+        }
+      }
+    }
+  }
+
+  float my_val = 0.f;   // lane `slot` keeps the slot's weight source (k <= 32 per pass)
+  float my_logit = 0.f;
+  int my_id = 0;
+  for (int slot = 0; slot < a.num_topk; ++slot) {
+    // lane-local best (ties -> larger index: scan ascending with >=)
+    float best = NEG_INF;
+    int best_e = -1;
+#pragma unroll
+    for (int i = 0; i < kRouteMaxPerLane; ++i) {
+      if (i < per_lane) {
+        const int e = i * 32 + lane;
+        if (e < E && sel[i] >= best) {
+          best = sel[i];
+          best_e = e;
+        }
+      }
+    }
+    // warp arg-max with the same tie rule
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+      if (ob > best || (ob == best && oe > best_e)) {
+        best = ob;
+        best_e = oe;
+      }
+    }
+    // fetch the weight source of the winner and retire it
+    float win_raw = 0.f;
+    if (best_e >= 0 && (best_e & 31) == lane) {
+      const int i = best_e >> 5;
+#pragma unroll
+      for (int j = 0; j < kRouteMaxPerLane; ++j) {
+        if (j == i) {
+          win_raw = raw[j];
+          sel[j] = NEG_INF;
+          raw[j] = NEG_INF;
+        }
+      }
+    }
+    win_raw = __shfl_sync(0xffffffffu, win_raw, best_e >= 0 ? (best_e & 31) : 0);
+    if ((slot & 31) == lane) {
+      my_val = win_raw;
+      my_logit = (MODE == B200MOE_ROUTE_SIGMOID) ? win_raw : best;
+      my_id = best_e < 0 ? 0 : best_e;
+    }
+    // write out (k <= 32, so this runs once, after the last slot)
+    if ((slot & 31) == 31 || slot == a.num_topk - 1) {
+      const int base = slot & ~31;
+      const int n_here = slot - base + 1;
+      const bool active = lane < n_here;
+      float w = my_val;
+      if (MODE == B200MOE_ROUTE_SOFTMAX_TOPK) {
+        // softmax over the selected logits, max-shifted (slot 0 holds the maximum)
+        const float mx = __shfl_sync(0xffffffffu, my_val, 0);
+        float ex = active ? expf(my_val - mx) : 0.f;
+        float sum = ex;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        w = ex / sum;
+      } else if (MODE == B200MOE_ROUTE_SIGMOID) {
+        float sum = active ? my_val : 0.f;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        if (a.renormalize) w = my_val / fmaxf(sum, 1e-20f);
+        w = w * a.route_scale;
+      }
+      if (active) {
+        const int64_t o = static_cast<int64_t>(warp) * a.num_topk + base + lane;
+        a.topk_ids[o] = my_id;
+        a.topk_weights[o] = w;
+        if (a.topk_logits) a.topk_logits[o] = my_logit;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// expert_sort: one CTA, up to 32 warps.  Warp w owns the contiguous route range
+// [w*chunk, (w+1)*chunk).  Pass 1 counts per (warp, expert) in shared memory, a scan over
+// warps then experts gives every (warp, expert) its first position, pass 2 walks the range
+// again 32 routes at a time and ranks equal experts inside the step with match_any, which
+// keeps the order of flat route ids.
+// ------------------------------------------------------------------------------------------
+constexpr int kSortThreads = 1024;
+
+__global__ void __launch_bounds__(kSortThreads) expert_sort_kernel(
+    const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map,
+    int expert_map_len, int rows, int E, int32_t* __restrict__ status,
+    int32_t* __restrict__ expert_counts, int32_t* __restrict__ expert_offsets,
+    int32_t* __restrict__ tile_base, int32_t* __restrict__ mtile_expert,
+    int32_t* __restrict__ mtile_row0, int32_t* __restrict__ mtile_rows,
+    int32_t* __restrict__ sorted_route_ids, int32_t* __restrict__ inv_perm, int mtile_cap) {
+  extern __shared__ int32_t smem[];
+  const int nwarps = blockDim.x >> 5;
+  int32_t* wcount = smem;                 // [nwarps][E]
+  int32_t* etotal = smem + nwarps * E;    // [E]
+  int32_t* eoffs = etotal + E;            // [E+1]
+  int32_t* tbase = eoffs + (E + 1);       // [E+1]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) wcount[i] = 0;
+  if (threadIdx.x < 16) status[threadIdx.x] = 0;  // the sort opens every layer call
+  __syncthreads();
+
+  // routes per warp, a multiple of 32 so that steps never straddle two warps
+  const int chunk = ((rows + nwarps - 1) / nwarps + 31) & ~31;
+  const int r_begin = warp * chunk;
+  const int r_end = min(rows, r_begin + chunk);
+
+  auto local_expert = [&](int r) -> int {
+    int e = topk_ids[r];
+    if (expert_map != nullptr) e = (e >= 0 && e < expert_map_len) ? expert_map[e] : -1;
+    return (e >= 0 && e < E) ? e : -1;
+  };
+
+  for (int r0 = r_begin; r0 < r_end; r0 += 32) {
+    const int r = r0 + lane;
+    const int e = (r < r_end) ? local_expert(r) : -1;
+    if (e >= 0) atomicAdd(&wcount[warp * E + e], 1);
+  }
+  __syncthreads();
+
+  // per expert: exclusive scan over warps (turn counts into within-expert bases)
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < nwarps; ++w) {
+      const int c = wcount[w * E + e];
+      wcount[w * E + e] = run;
+      run += c;
+    }
+    etotal[e] = run;
+  }
+  __syncthreads();
+  // scan over experts (E <= 1024: a single thread is enough and keeps this simple)
+  if (threadIdx.x == 0) {
+    int pos = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      eoffs[e] = pos;
+      tbase[e] = tiles;
+      pos += etotal[e];
+      tiles += (etotal[e] + 127) >> 7;
+    }
+    eoffs[E] = pos;
+    tbase[E] = tiles;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+    expert_offsets[e] = eoffs[e];
+    tile_base[e] = tbase[e];
+    if (e < E) {
+      expert_counts[e] = etotal[e];
+      const int nt = (etotal[e] + 127) >> 7;
+      for (int t = 0; t < nt; ++t) {
+        const int mt = tbase[e] + t;
+        if (mt < mtile_cap) {
+          mtile_expert[mt] = e;
+          mtile_row0[mt] = eoffs[e] + t * 128;
+          mtile_rows[mt] = min(128, etotal[e] - t * 128);
+        }
+      }
+    }
+  }
+
+  // pass 2: stable positions
+  for (int r0 = r_begin; r0 < r_end; r0 += 32) {
+    const int r = r0 + lane;
+    const int e = (r < r_end) ? local_expert(r) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    if (r < r_end) {
+      if (e >= 0) {
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        const int base = wcount[warp * E + e];  // read before the leader bumps it
+        const int pos = eoffs[e] + base + rank;
+        sorted_route_ids[pos] = r;
+        inv_perm[r] = pos;
+      } else {
+        inv_perm[r] = -1;
+      }
+    }
+    __syncwarp();
+    if (e >= 0 && r < r_end && (peers & ((1u << lane) - 1u)) == 0) {
+      wcount[warp * E + e] += __popc(peers);
+    }
+    __syncwarp();
+  }
+}
+
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" int b200moe_route_topk(const b200moe_route_args* a, void* stream) {
+  if (a == nullptr || a->logits == nullptr || a->topk_ids == nullptr || a->topk_weights == nullptr)
+    return B200MOE_EINVAL;
+  if (a->num_experts <= 0 || a->num_experts > 1024) return B200MOE_EINVAL;
+  if (a->num_topk <= 0 || a->num_topk > a->num_experts || a->num_topk > 32) return B200MOE_EINVAL;
+  if (a->num_tokens < 0) return B200MOE_EINVAL;
+  if (a->num_tokens == 0) return B200MOE_OK;
+  const int warps_per_block = 4;
+  const dim3 grid((a->num_tokens + warps_per_block - 1) / warps_per_block);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (a->mode) {
+    case B200MOE_ROUTE_SOFTMAX_TOPK:
+      route_topk_kernel<B200MOE_ROUTE_SOFTMAX_TOPK><<<grid, 128, 0, s>>>(*a);
+      break;
+    case B200MOE_ROUTE_RAW:
+      route_topk_kernel<B200MOE_ROUTE_RAW><<<grid, 128, 0, s>>>(*a);
+      break;
+    case B200MOE_ROUTE_SIGMOID:
+      route_topk_kernel<B200MOE_ROUTE_SIGMOID><<<grid, 128, 0, s>>>(*a);
+      break;
+    default:
+      return B200MOE_EINVAL;
+  }
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+extern "C" int b200moe_expert_sort(const b200moe_sort_args* a, void* stream) {
+  if (a == nullptr || a->topk_ids == nullptr || a->scratch == nullptr || a->layout == nullptr)
+    return B200MOE_EINVAL;
+  const b200moe_scratch_layout& L = *a->layout;
+  const int rows = a->num_tokens * a->num_topk;
+  const int E = a->num_experts;
+  if (E <= 0 || E > 1024 || rows < 0) return B200MOE_EINVAL;
+  if (rows > L.rows) return B200MOE_ECAPACITY;
+  char* base = static_cast<char*>(a->scratch);
+  // fewer warps for small problems keeps the shared-memory clear short
+  int nwarps = (rows + 31) / 32;
+  nwarps = nwarps < 1 ? 1 : (nwarps > 32 ? 32 : nwarps);
+  const size_t smem = (static_cast<size_t>(nwarps) * E + 3 * static_cast<size_t>(E) + 2) * 4;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(expert_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (32 * 1024 + 3 * 1024 + 2) * 4) != cudaSuccess)
+    return B200MOE_ECUDA;
+  expert_sort_kernel<<<1, nwarps * 32, smem, static_cast<cudaStream_t>(stream)>>>(
+      a->topk_ids, a->expert_map, a->expert_map_len, rows, E,
+      reinterpret_cast<int32_t*>(base + L.status),
+      reinterpret_cast<int32_t*>(base + L.expert_counts),
+      reinterpret_cast<int32_t*>(base + L.expert_offsets),
+      reinterpret_cast<int32_t*>(base + L.tile_base),
+      reinterpret_cast<int32_t*>(base + L.mtile_expert),
+      reinterpret_cast<int32_t*>(base + L.mtile_row0),
+      reinterpret_cast<int32_t*>(base + L.mtile_rows),
+      reinterpret_cast<int32_t*>(base + L.sorted_route_ids),
+      reinterpret_cast<int32_t*>(base + L.inv_perm), L.mtile_cap);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}

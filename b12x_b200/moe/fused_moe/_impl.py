@@ -1,0 +1,739 @@
+"""Planner and launch glue of ``moe.fused_moe`` for B200 (sm_100a).
+
+Host-side mirror of the reference's ``b12x/moe/fused_moe/_impl.py``: the same lifecycle
+(``plan_weights`` -> ``prepare_weights`` -> ``plan(Caps)`` -> ``bind`` -> ``run``), the same
+contracts (one caller-owned uint8 scratch tensor, ``bind`` only creates views, ``run`` launches on
+the current stream without allocating or synchronising when ``output`` is given), and the same
+exception types.  The work itself is six C-ABI launches into ``libb200moe.so``:
+expert sort -> permute+quantise -> grouped FC1+activation -> grouped FC2 -> combine
+(plus ``route_topk`` when routing is requested).  There is no other implementation behind this
+module: without the extension every call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from collections.abc import Mapping, Sequence
+from dataclasses import dataclass, field
+
+import torch
+
+from ..._lib import ext
+from ..._lib.scratch import ScratchBufferSpec, scratch_buffer_spec, scratch_tensor
+from .._shared.execution import (
+    SWIGLUOAI,
+    MoEWeightPreparationPlan,
+    WeightPreparationTransform,
+    is_gated_moe_activation,
+    make_moe_spec,
+    normalize_moe_activation,
+    normalize_swiglu_params,
+    normalize_w13_layout,
+    plan_moe_weight_preparation,
+)
+from .._shared.routing import route_topk
+
+_ACT_CODE = {"silu": "silu", "relu2": "relu2", SWIGLUOAI: "swigluoai"}
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _align_up(v: int, a: int) -> int:
+    return (v + a - 1) // a * a
+
+
+# =============================================================================================
+# weights
+# =============================================================================================
+def plan_b12x_fp4_moe_weights(
+    *,
+    quant_modes: str | Sequence[str],
+    source_format: str,
+    activation: str,
+    params_dtype: torch.dtype,
+    num_experts: int,
+    hidden_size: int,
+    intermediate_size: int,
+    w13_layout: str = "w13",
+) -> MoEWeightPreparationPlan:
+    """Plan the one canonical weight allocation used by the selected recipes.
+
+    Reference: ``plan_b12x_fp4_moe_weights`` (b12x/moe/fused_moe/_impl.py:4992-5042)."""
+    activation = normalize_moe_activation(activation)
+    modes = (quant_modes,) if isinstance(quant_modes, str) else tuple(quant_modes)
+    if not modes:
+        raise ValueError("quant_modes must contain at least one recipe")
+    specs = tuple(
+        make_moe_spec(quant_mode=m, source_format=source_format, activation=activation,
+                      io_dtype=str(params_dtype).removeprefix("torch."), w13_layout=w13_layout)
+        for m in modes)
+    return plan_moe_weight_preparation(specs, num_experts=num_experts, hidden_size=hidden_size,
+                                       intermediate_size=intermediate_size)
+
+
+@dataclass(frozen=True, kw_only=True)
+class B12XFP4ExpertWeights:
+    """Sole owner of the expert weights at run time (reference _impl.py:407-581).
+
+    ``w*_fp4`` are the checkpoint tensors themselves (two E2M1 per byte); ``w*_blockscale`` are
+    128x4-swizzled scale atoms (E4M3 per 16 for nvfp4 / w4a16, E8M0 per 32 for w4a8_mx, the
+    latter produced from the plain checkpoint grids by ``prepare_weights``)."""
+
+    plan: MoEWeightPreparationPlan
+    a1_gscale: torch.Tensor
+    w1_fp4: torch.Tensor
+    w1_blockscale: torch.Tensor
+    w1_alphas: torch.Tensor
+    a2_gscale: torch.Tensor
+    w2_fp4: torch.Tensor
+    w2_blockscale: torch.Tensor
+    w2_alphas: torch.Tensor
+
+    def __post_init__(self) -> None:
+        if not isinstance(self.plan, MoEWeightPreparationPlan):
+            raise TypeError("plan must be a MoEWeightPreparationPlan")
+        for name in ("a1_gscale", "w1_fp4", "w1_blockscale", "w1_alphas", "a2_gscale", "w2_fp4",
+                     "w2_blockscale", "w2_alphas"):
+            if not isinstance(getattr(self, name), torch.Tensor):
+                raise TypeError(f"{name} must be a torch.Tensor")
+        p = self.plan
+        if tuple(self.w1_fp4.shape) != (p.num_experts, p.w1_rows, p.hidden_size // 2):
+            raise ValueError(
+                f"w1_fp4 shape {tuple(self.w1_fp4.shape)} does not match the weight plan "
+                f"{(p.num_experts, p.w1_rows, p.hidden_size // 2)}")
+        if tuple(self.w2_fp4.shape) != (p.num_experts, p.hidden_size, p.intermediate_size // 2):
+            raise ValueError(
+                f"w2_fp4 shape {tuple(self.w2_fp4.shape)} does not match the weight plan "
+                f"{(p.num_experts, p.hidden_size, p.intermediate_size // 2)}")
+        for name in ("w1_fp4", "w2_fp4", "w1_blockscale", "w2_blockscale"):
+            if not getattr(self, name).is_contiguous():
+                raise ValueError(f"{name} must be contiguous")
+
+
+def _expert_vector(t: torch.Tensor, num_experts: int, name: str) -> torch.Tensor:
+    t = t.to(torch.float32).reshape(-1)
+    if t.numel() == 1:
+        t = t.expand(num_experts)
+    if t.numel() != num_experts:
+        raise ValueError(f"{name} must have 1 or {num_experts} elements, got {t.numel()}")
+    return t.contiguous()
+
+
+def _swizzle_scale_grid(grid: torch.Tensor) -> torch.Tensor:
+    """[E, rows, cols] bytes -> [E, pad128(rows), pad4(cols)] 128x4-swizzled atoms
+    (layout of b12x/_lib/intrinsics.py:62-82)."""
+    e, rows, cols = grid.shape
+    rp, cp = _align_up(rows, 128), _align_up(cols, 4)
+    padded = torch.zeros((e, rp, cp), dtype=torch.uint8, device=grid.device)
+    padded[:, :rows, :cols] = grid.view(torch.uint8)
+    sw = padded.reshape(e, rp // 128, 4, 32, cp // 4, 4).permute(0, 1, 4, 3, 2, 5).contiguous()
+    return sw.reshape(e, rp, cp)
+
+
+def prepare_b12x_fp4_moe_weights(
+    *,
+    plan: MoEWeightPreparationPlan,
+    params_dtype: torch.dtype,
+    w1_fp4: torch.Tensor | None = None,
+    w2_fp4: torch.Tensor | None = None,
+    w1_global_scale: torch.Tensor | None = None,
+    w2_global_scale: torch.Tensor | None = None,
+    w1_blockscale: torch.Tensor | None = None,
+    w2_blockscale: torch.Tensor | None = None,
+    a1_gscale: torch.Tensor | None = None,
+    a2_gscale: torch.Tensor | None = None,
+) -> B12XFP4ExpertWeights:
+    """Transfer source tensors into the planner-selected runtime owner.
+
+    Reference: ``prepare_b12x_fp4_moe_weights`` (_impl.py:5045-5365).  For nvfp4 the runtime
+    alphas are ``w_global_scale / a_gscale`` (``a*_gscale`` are RECIPROCAL input scales,
+    _impl.py:4955-4989); weights and E4M3 scales are used where they lie.  For w4a8_mx the plain
+    ``[E, rows, cols/32]`` E8M0 grids are re-laid once into 128x4 atoms."""
+    if not isinstance(plan, MoEWeightPreparationPlan):
+        raise TypeError("plan must be a MoEWeightPreparationPlan")
+    actual = str(params_dtype).removeprefix("torch.")
+    if actual != plan.io_dtype:
+        raise ValueError(f"params_dtype={actual!r} does not match plan dtype={plan.io_dtype!r}")
+    for name, t in (("w1_fp4", w1_fp4), ("w2_fp4", w2_fp4), ("w1_blockscale", w1_blockscale),
+                    ("w2_blockscale", w2_blockscale)):
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"{name} is required")
+    e = plan.num_experts
+    dev = w1_fp4.device
+    ones = torch.ones(e, dtype=torch.float32, device=dev)
+    a1 = ones if a1_gscale is None else _expert_vector(a1_gscale, e, "a1_gscale").to(dev)
+    a2 = ones if a2_gscale is None else _expert_vector(a2_gscale, e, "a2_gscale").to(dev)
+    g1 = ones if w1_global_scale is None else _expert_vector(w1_global_scale, e, "w1_global_scale").to(dev)
+    g2 = ones if w2_global_scale is None else _expert_vector(w2_global_scale, e, "w2_global_scale").to(dev)
+    if "nvfp4" in plan.quant_modes:
+        if a1_gscale is None or a2_gscale is None or w1_global_scale is None or w2_global_scale is None:
+            raise ValueError("nvfp4 needs w*_global_scale and a*_gscale")
+        alphas1, alphas2 = torch.div(g1, a1), torch.div(g2, a2)
+    else:
+        alphas1, alphas2 = g1.clone(), g2.clone()
+    s1, s2 = w1_blockscale, w2_blockscale
+    if WeightPreparationTransform.SWIZZLE_MX_SCALES in plan.transforms:
+        if tuple(s1.shape) != (e, plan.w1_rows, plan.hidden_size // 32):
+            raise ValueError("fp4_e8m0_k32 w1_blockscale must be [E, w1_rows, K/32] E8M0 bytes")
+        if tuple(s2.shape) != (e, plan.hidden_size, plan.intermediate_size // 32):
+            raise ValueError("fp4_e8m0_k32 w2_blockscale must be [E, K, I/32] E8M0 bytes")
+        s1, s2 = _swizzle_scale_grid(s1), _swizzle_scale_grid(s2)
+    else:
+        exp1 = (e, _align_up(plan.w1_rows, 128), _align_up(plan.hidden_size // 16, 4))
+        exp2 = (e, _align_up(plan.hidden_size, 128), _align_up(plan.intermediate_size // 16, 4))
+        if s1.numel() != exp1[0] * exp1[1] * exp1[2] or s2.numel() != exp2[0] * exp2[1] * exp2[2]:
+            raise ValueError(
+                "modelopt_nvfp4 block scales must be 128x4-swizzled "
+                f"{exp1} / {exp2}, got {tuple(s1.shape)} / {tuple(s2.shape)}")
+        s1, s2 = s1.view(torch.uint8), s2.view(torch.uint8)
+    return B12XFP4ExpertWeights(
+        plan=plan, a1_gscale=a1, w1_fp4=w1_fp4.view(torch.uint8), w1_blockscale=s1.contiguous(),
+        w1_alphas=alphas1.contiguous(), a2_gscale=a2, w2_fp4=w2_fp4.view(torch.uint8),
+        w2_blockscale=s2.contiguous(), w2_alphas=alphas2.contiguous())
+
+
+# =============================================================================================
+# caps / plan / binding
+# =============================================================================================
+@dataclass(frozen=True, kw_only=True)
+class TPMoEScratchCaps:
+    """Capacity and options of one scratch plan (reference _impl.py:747-860, same field names)."""
+
+    max_tokens: int
+    num_topk: int
+    device: torch.device | str
+    weight_plan: MoEWeightPreparationPlan
+    quant_mode: str
+    core_token_counts: tuple[int, ...] | None = None
+    route_num_experts: int | None = None
+    route_logits_dtype: torch.dtype | None = None
+    apply_router_weight_on_input: bool = False
+    swiglu_limit: float | None = None
+    swiglu_alpha: float | None = None
+    swiglu_beta: float | None = None
+    collect_activation_amax: bool = False
+    deterministic_output: bool | None = None
+    w4a16_block_size_m: int | None = None
+    w4a16_fast_math: bool = True
+    frozen: bool = True
+
+    def __post_init__(self) -> None:
+        object.__setattr__(self, "max_tokens", max(int(self.max_tokens), 1))
+        object.__setattr__(self, "num_topk", max(int(self.num_topk), 1))
+        object.__setattr__(self, "device", torch.device(self.device))
+        if not isinstance(self.weight_plan, MoEWeightPreparationPlan):
+            raise TypeError("weight_plan must be a MoEWeightPreparationPlan")
+        mode = str(self.quant_mode).lower()
+        if mode not in self.weight_plan.quant_modes:
+            raise ValueError(f"quant_mode={mode!r} is absent from the weight plan")
+        object.__setattr__(self, "quant_mode", mode)
+        if self.core_token_counts is not None:
+            object.__setattr__(self, "core_token_counts",
+                               tuple(max(int(c), 1) for c in self.core_token_counts))
+        if self.route_num_experts is not None:
+            object.__setattr__(self, "route_num_experts", max(int(self.route_num_experts), 0))
+        limit, alpha, beta = normalize_swiglu_params(self.activation, self.swiglu_limit,
+                                                     self.swiglu_alpha, self.swiglu_beta)
+        object.__setattr__(self, "swiglu_limit", limit)
+        object.__setattr__(self, "swiglu_alpha", alpha)
+        object.__setattr__(self, "swiglu_beta", beta)
+        if self.apply_router_weight_on_input:
+            raise NotImplementedError("apply_router_weight_on_input is not built")
+        if self.collect_activation_amax:
+            raise NotImplementedError("collect_activation_amax is not built")
+        if self.num_topk > 32:
+            raise ValueError("num_topk > 32 is not supported")
+
+    @property
+    def weight_E(self) -> int:
+        return self.weight_plan.num_experts
+
+    @property
+    def k(self) -> int:
+        return self.weight_plan.hidden_size
+
+    @property
+    def n(self) -> int:
+        return self.weight_plan.intermediate_size
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return {"bfloat16": torch.bfloat16}[self.weight_plan.io_dtype]
+
+    @property
+    def activation(self) -> str:
+        return self.weight_plan.activation
+
+    @property
+    def source_format(self) -> str:
+        return self.weight_plan.source_format
+
+    @property
+    def w13_layout(self) -> str:
+        return self.weight_plan.w13_layout
+
+
+@dataclass(frozen=True, kw_only=True)
+class TPMoEArenaLayout:
+    route_workspace_nbytes: int
+    core_workspace_nbytes: int
+    total_nbytes: int
+    core_token_counts: tuple[int, ...] = ()
+
+
+@dataclass(frozen=True, kw_only=True)
+class TPMoEPlan:
+    """What will be launched for a token count (reference ``TPMoEPlan`` _impl.py:717-744)."""
+
+    implementation: str      # always "tcgen05_grouped"
+    quant_mode: str
+    activation: str
+    swiglu_limit: float | None
+    swiglu_alpha: float
+    swiglu_beta: float
+    weight_E: int
+    routed_rows: int
+    max_rows: int
+    k: int
+    n: int
+    num_topk: int
+    device: torch.device
+    dtype: torch.dtype
+    tile_m: int = 128
+    tile_n: int = 256
+    max_m_tiles: int = 0
+    deterministic_output: bool = True
+
+
+_ROUTE_ALIGN = 1024
+
+
+def _route_workspace_nbytes(caps: TPMoEScratchCaps) -> int:
+    """Router logits (when a gate GEMM is requested) + top-k logits/ids/weights."""
+    e = caps.route_num_experts or 0
+    if e <= 0:
+        return 0
+    t, k = caps.max_tokens, caps.num_topk
+    return (_align_up(t * e * 4, _ROUTE_ALIGN) + 3 * _align_up(t * k * 4, _ROUTE_ALIGN))
+
+
+def _layout_for(caps: TPMoEScratchCaps) -> ext.ScratchLayout:
+    return ext.scratch_layout(caps.max_tokens, caps.num_topk, caps.weight_E, caps.k, caps.n,
+                              caps.quant_mode, _ACT_CODE[caps.activation])
+
+
+def plan_tp_moe_execution(caps: TPMoEScratchCaps, num_tokens: int | None = None) -> TPMoEPlan:
+    """Regime / tile choice for a token count (reference ``plan_tp_moe_execution``
+    _impl.py:5647-5840).  One regime here: grouped tcgen05 GEMMs with 128-row tiles; the bound on
+    m-tiles is ceil(rows/128) + min(E, rows) (reference _impl.py:2134-2152)."""
+    t = caps.max_tokens if num_tokens is None else int(num_tokens)
+    if t > caps.max_tokens:
+        raise ValueError(f"{t} tokens exceed the planned capacity {caps.max_tokens}")
+    rows = t * caps.num_topk
+    return TPMoEPlan(
+        implementation="tcgen05_grouped", quant_mode=caps.quant_mode, activation=caps.activation,
+        swiglu_limit=caps.swiglu_limit, swiglu_alpha=caps.swiglu_alpha, swiglu_beta=caps.swiglu_beta,
+        weight_E=caps.weight_E, routed_rows=rows, max_rows=caps.max_tokens * caps.num_topk,
+        k=caps.k, n=caps.n, num_topk=caps.num_topk, device=caps.device, dtype=caps.dtype,
+        max_m_tiles=(rows + 127) // 128 + min(caps.weight_E, rows))
+
+
+def tp_moe_required_nbytes(caps: TPMoEScratchCaps) -> int:
+    """Bytes of scratch ``plan(caps)`` will ask for (reference _impl.py:6781-6783)."""
+    return _route_workspace_nbytes(caps) + int(_layout_for(caps).total_nbytes)
+
+
+@dataclass(frozen=True)
+class TPMoEScratchPlan:
+    caps: TPMoEScratchCaps
+    layout: TPMoEArenaLayout
+    launch_plan: TPMoEPlan
+    _core_layout: ext.ScratchLayout = field(repr=False)
+    _scratch_specs: tuple[ScratchBufferSpec, ...] = ()
+
+    def scratch_specs(self) -> tuple[ScratchBufferSpec, ...]:
+        return self._scratch_specs
+
+    def shapes_and_dtypes(self):
+        return tuple((spec.shape, spec.dtype) for spec in self._scratch_specs)
+
+    def bind(
+        self,
+        *,
+        scratch: torch.Tensor | Mapping[str, torch.Tensor] | Sequence[torch.Tensor],
+        a: torch.Tensor,
+        experts: B12XFP4ExpertWeights,
+        topk_weights: torch.Tensor,
+        topk_ids: torch.Tensor,
+        output: torch.Tensor | None = None,
+        input_scales_static: bool = False,
+        fast_math: bool | None = None,
+        route_expert_map: torch.Tensor | None = None,
+        fc1_tap: torch.Tensor | None = None,
+        output_f32: torch.Tensor | None = None,
+        output_scale: float = 1.0,
+    ) -> "TPMoEFP4Binding":
+        """Validate the call and map the caller's scratch into kernel-argument views.
+
+        Views only: nothing is allocated, copied or launched (reference
+        ``TPMoEScratchPlan.bind`` _impl.py:888-966).  ``route_expert_map`` ([global E] -> local id
+        or -1) makes non-local routes inactive, as ``ep_moe`` does in the reference."""
+        caps = self.caps
+        if not isinstance(experts, B12XFP4ExpertWeights):
+            raise TypeError("experts must come from prepare_b12x_fp4_moe_weights")
+        if experts.plan != caps.weight_plan:
+            raise ValueError("experts do not match the plan used to size TP MoE scratch")
+        if a.ndim != 2 or topk_ids.ndim != 2 or topk_weights.ndim != 2:
+            raise ValueError("a, topk_ids and topk_weights must have rank 2")
+        tokens = int(a.shape[0])
+        if tokens > caps.max_tokens:
+            raise ValueError(f"input tokens {tokens} exceed TP MoE scratch capacity {caps.max_tokens}")
+        if int(a.shape[1]) != caps.k:
+            raise ValueError(f"input hidden size {int(a.shape[1])} does not match TP MoE scratch K={caps.k}")
+        if int(topk_ids.shape[1]) != caps.num_topk:
+            raise ValueError(f"top-k {int(topk_ids.shape[1])} does not match TP MoE scratch top-k={caps.num_topk}")
+        if tuple(topk_ids.shape) != (tokens, caps.num_topk) or tuple(topk_weights.shape) != (tokens, caps.num_topk):
+            raise ValueError("topk_ids / topk_weights must be [tokens, top_k]")
+        if a.dtype != caps.dtype:
+            raise TypeError(f"a must be {caps.dtype}, got {a.dtype}")
+        if topk_ids.dtype != torch.int32:
+            raise TypeError(f"topk_ids must be int32, got {topk_ids.dtype}")
+        if topk_weights.dtype != torch.float32:
+            raise TypeError(f"topk_weights must be float32, got {topk_weights.dtype}")
+        for name, t in (("a", a), ("topk_ids", topk_ids), ("topk_weights", topk_weights)):
+            if t.device != caps.device:
+                raise ValueError(f"{name} is on {t.device}, the plan is for {caps.device}")
+        if a.stride(1) != 1 or not topk_ids.is_contiguous() or not topk_weights.is_contiguous():
+            raise ValueError("a must be row-contiguous; topk_ids / topk_weights contiguous")
+        if output is not None:
+            if tuple(output.shape) != (tokens, caps.k) or output.dtype != caps.dtype or output.stride(1) != 1:
+                raise ValueError("output must be [tokens, K] in the plan dtype, row-contiguous")
+        storage = scratch_tensor(scratch, self._scratch_specs, owner="TP MoE")
+        core = storage.narrow(0, self.layout.route_workspace_nbytes, self.layout.core_workspace_nbytes)
+        if core.data_ptr() % 1024 != 0:
+            raise ValueError("scratch must be 1024-byte aligned")
+        return TPMoEFP4Binding(
+            a=a, experts=experts, topk_weights=topk_weights, topk_ids=topk_ids,
+            implementation=self.launch_plan.implementation, weight_E=caps.weight_E,
+            max_rows=caps.max_tokens * caps.num_topk, k=caps.k, n=caps.n, num_topk=caps.num_topk,
+            device=caps.device, dtype=caps.dtype, output=output,
+            input_scales_static=bool(input_scales_static), fast_math=fast_math,
+            quant_mode=caps.quant_mode, activation=caps.activation, w13_layout=caps.w13_layout,
+            swiglu_limit=caps.swiglu_limit, swiglu_alpha=caps.swiglu_alpha,
+            swiglu_beta=caps.swiglu_beta, route_expert_map=route_expert_map,
+            kernel_workspace=core, core_layout=self._core_layout, fc1_tap=fc1_tap,
+            output_f32=output_f32, output_scale=float(output_scale))
+
+
+def plan_tp_moe_scratch(caps: TPMoEScratchCaps) -> TPMoEScratchPlan:
+    """Scratch plan for ``caps``: ONE opaque uint8 buffer (reference _impl.py:6786-6863)."""
+    if not isinstance(caps, TPMoEScratchCaps):
+        raise TypeError("caps must be a TPMoEScratchCaps")
+    core = _layout_for(caps)
+    route = _route_workspace_nbytes(caps)
+    total = route + int(core.total_nbytes)
+    layout = TPMoEArenaLayout(route_workspace_nbytes=route, core_workspace_nbytes=int(core.total_nbytes),
+                              total_nbytes=total,
+                              core_token_counts=caps.core_token_counts or (caps.max_tokens,))
+    spec = scratch_buffer_spec("tp_moe.scratch", nbytes=total, device=caps.device)
+    return TPMoEScratchPlan(caps, layout, plan_tp_moe_execution(caps), core, (spec,))
+
+
+def _view(core: torch.Tensor, offset: int, count: int, dtype: torch.dtype) -> torch.Tensor:
+    nbytes = count * torch.empty((), dtype=dtype).element_size()
+    return core.narrow(0, offset, nbytes).view(dtype)
+
+
+@dataclass(frozen=True, kw_only=True)
+class TPMoEFP4Binding:
+    """Caller tensors plus scratch views for one call (reference ``TPMoEFP4Binding``
+    _impl.py:969-1056).  The scratch-view properties expose what the kernels left behind; they are
+    what the parity tests read."""
+
+    a: torch.Tensor
+    experts: B12XFP4ExpertWeights
+    topk_weights: torch.Tensor
+    topk_ids: torch.Tensor
+    implementation: str
+    weight_E: int
+    max_rows: int
+    k: int
+    n: int
+    num_topk: int
+    device: torch.device
+    dtype: torch.dtype
+    output: torch.Tensor | None = None
+    input_scales_static: bool = False
+    fast_math: bool | None = None
+    quant_mode: str | None = None
+    activation: str = "silu"
+    w13_layout: str = "w13"
+    deterministic_output: bool = True
+    swiglu_limit: float | None = None
+    swiglu_alpha: float | None = None
+    swiglu_beta: float | None = None
+    route_expert_map: torch.Tensor | None = None
+    kernel_workspace: torch.Tensor | None = None
+    core_layout: ext.ScratchLayout | None = field(default=None, repr=False)
+    fc1_tap: torch.Tensor | None = None
+    output_f32: torch.Tensor | None = None
+    output_scale: float = 1.0
+
+    # ---- scratch views (valid after run) ----
+    def _v(self, name: str, count: int, dtype: torch.dtype) -> torch.Tensor:
+        return _view(self.kernel_workspace, int(getattr(self.core_layout, name)), count, dtype)
+
+    @property
+    def tokens(self) -> int:
+        return int(self.a.shape[0])
+
+    @property
+    def status(self) -> torch.Tensor:
+        return self._v("status", 16, torch.int32)
+
+    @property
+    def expert_counts(self) -> torch.Tensor:
+        return self._v("expert_counts", self.weight_E, torch.int32)
+
+    @property
+    def expert_offsets(self) -> torch.Tensor:
+        return self._v("expert_offsets", self.weight_E + 1, torch.int32)
+
+    @property
+    def expert_tile_base(self) -> torch.Tensor:
+        return self._v("tile_base", self.weight_E + 1, torch.int32)
+
+    @property
+    def packed_route_indices(self) -> torch.Tensor:
+        return self._v("sorted_route_ids", self.tokens * self.num_topk, torch.int32)
+
+    @property
+    def inv_perm(self) -> torch.Tensor:
+        return self._v("inv_perm", self.tokens * self.num_topk, torch.int32)
+
+    @property
+    def packed_input(self) -> torch.Tensor:
+        row = {"nvfp4": self.k // 2, "w4a8_mx": self.k, "w4a16": 0}[self.quant_mode]
+        return self._v("act_q", self.max_rows * row, torch.uint8).view(self.max_rows, row)
+
+    @property
+    def packed_input_scale(self) -> torch.Tensor:
+        per = {"nvfp4": 64, "w4a8_mx": 128, "w4a16": 64}[self.quant_mode]
+        atoms = (self.k + per - 1) // per
+        return self._v("act_sf", self.core_layout.mtile_cap * atoms * 512, torch.uint8)
+
+    @property
+    def materialized_intermediate(self) -> torch.Tensor:
+        row = {"nvfp4": self.n // 2, "w4a8_mx": self.n, "w4a16": self.n * 2}[self.quant_mode]
+        return self._v("mid_q", self.max_rows * row, torch.uint8).view(self.max_rows, row)
+
+    @property
+    def intermediate_scale(self) -> torch.Tensor:
+        per = {"nvfp4": 64, "w4a8_mx": 128, "w4a16": 64}[self.quant_mode]
+        atoms = (self.n + per - 1) // per
+        return self._v("mid_sf", self.core_layout.mtile_cap * atoms * 512, torch.uint8)
+
+    @property
+    def route_output(self) -> torch.Tensor:
+        return self._v("routed", self.max_rows * self.k, torch.float32).view(self.max_rows, self.k)
+
+    def run(self) -> torch.Tensor:
+        return b12x_moe_fp4(binding=self)
+
+
+# =============================================================================================
+# run
+# =============================================================================================
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def b12x_moe_fp4(*, binding: TPMoEFP4Binding) -> torch.Tensor:
+    """Run the layer for one binding on the current CUDA stream and return ``[tokens, K]``.
+
+    Reference: ``b12x_moe_fp4`` (_impl.py:10446-11012).  With ``binding.output`` set nothing is
+    allocated and nothing synchronises, so the call can be captured in a CUDA graph."""
+    if not isinstance(binding, TPMoEFP4Binding):
+        raise TypeError("binding must come from Plan.bind")
+    b = binding
+    if b.device.type != "cuda":
+        raise RuntimeError("moe.fused_moe runs on CUDA devices only; there is no CPU path")
+    lib = ext.load()
+    tokens = b.tokens
+    out = b.output
+    if out is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("output must be provided during CUDA graph capture")
+        out = torch.empty((tokens, b.k), dtype=b.dtype, device=b.device)
+    if tokens == 0:
+        return out
+    ex = b.experts
+    L = b.core_layout
+    lp = C.pointer(L)
+    scratch = b.kernel_workspace.data_ptr()
+    stream = _stream_ptr(b.device)
+    recipe = ext.RECIPES[b.quant_mode]
+    act = ext.ACTIVATIONS[_ACT_CODE[b.activation]]
+
+    emap = b.route_expert_map
+    sort_args = ext.SortArgs(b.topk_ids.data_ptr(), _ptr(emap), scratch, lp, tokens, b.num_topk,
+                             b.weight_E, 0 if emap is None else int(emap.numel()))
+    ext.check(lib.b200moe_expert_sort(C.byref(sort_args), stream), "expert_sort")
+
+    if b.quant_mode in ("nvfp4", "w4a8_mx"):
+        qargs = ext.QuantArgs(b.a.data_ptr(), ex.a1_gscale.data_ptr(), scratch, lp, b.a.stride(0),
+                              tokens, b.num_topk, b.weight_E, b.k, int(ex.a1_gscale.numel()), 0)
+        fn = lib.b200moe_permute_quant_nvfp4 if b.quant_mode == "nvfp4" else lib.b200moe_permute_quant_mxfp8
+        ext.check(fn(C.byref(qargs), stream), "permute_quant")
+
+    gargs = ext.GemmArgs(
+        ex.w1_fp4.data_ptr(), ex.w1_blockscale.data_ptr(), ex.w1_alphas.data_ptr(),
+        ex.w2_fp4.data_ptr(), ex.w2_blockscale.data_ptr(), ex.w2_alphas.data_ptr(),
+        ex.a2_gscale.data_ptr(), b.a.data_ptr(), scratch, lp, _ptr(b.fc1_tap), b.a.stride(0),
+        tokens, b.num_topk, b.weight_E, b.k, b.n, recipe, act,
+        1 if (b.w13_layout == "w31" and is_gated_moe_activation(b.activation)) else 0,
+        int(ex.a2_gscale.numel()),
+        float(b.swiglu_limit) if b.swiglu_limit is not None else 0.0,
+        float(b.swiglu_alpha if b.swiglu_alpha is not None else 1.0),
+        float(b.swiglu_beta if b.swiglu_beta is not None else 0.0), 0, 0)
+    ext.check(lib.b200moe_grouped_gemm1_act(C.byref(gargs), stream), "grouped_gemm1_act")
+    ext.check(lib.b200moe_grouped_gemm2(C.byref(gargs), stream), "grouped_gemm2")
+
+    cargs = ext.CombineArgs(b.topk_weights.data_ptr(), out.data_ptr(), scratch, lp, out.stride(0),
+                            tokens, b.num_topk, b.k, 0, float(b.output_scale), 0)
+    ext.check(lib.b200moe_combine(C.byref(cargs), stream), "combine")
+    if b.output_f32 is not None:
+        targs = ext.CombineArgs(b.topk_weights.data_ptr(), b.output_f32.data_ptr(), scratch, lp,
+                                b.output_f32.stride(0), tokens, b.num_topk, b.k, 1,
+                                float(b.output_scale), 0)
+        ext.check(lib.b200moe_combine(C.byref(targs), stream), "combine(f32 tap)")
+    return out
+
+
+def check_device_status(binding: TPMoEFP4Binding) -> None:
+    """Synchronise and raise if a device-side bounded wait ran out during the last run."""
+    st = binding.status.cpu()
+    if int(st[0]) != 0:
+        raise RuntimeError(f"moe.fused_moe kernel gave up waiting (site {int(st[1])}); results are invalid")
+
+
+# =============================================================================================
+# routing wrappers
+# =============================================================================================
+@dataclass(frozen=True, kw_only=True)
+class B12XTopKRouting:
+    """Top-k routing selection (reference _impl.py:644-652)."""
+
+    topk_weights: torch.Tensor
+    topk_ids: torch.Tensor
+    router_logits: torch.Tensor | None = None
+    flat_ids: torch.Tensor | None = None
+    flat_weights: torch.Tensor | None = None
+
+
+@dataclass(frozen=True, kw_only=True)
+class TPMoERouteBinding:
+    """Reference ``TPMoERouteBinding`` (_impl.py:1059-1070) plus the score-function options the
+    reference only has in its benchmark (benchmarks/benchmark_moe.py:1282-1322)."""
+
+    hidden_states: torch.Tensor
+    top_k: int
+    scratch: torch.Tensor | None = None
+    gate_weight: torch.Tensor | None = None
+    gate_bias: torch.Tensor | None = None
+    router_logits: torch.Tensor | None = None
+    renormalize: bool = True
+    score_func: str = "softmax"          # "softmax" | "sigmoid"
+    selection_bias: torch.Tensor | None = None
+    route_scale: float = 1.0
+
+    def run(self) -> B12XTopKRouting:
+        return b12x_route_experts_fast(binding=self)
+
+
+def build_tp_moe_route_binding(**kwargs) -> TPMoERouteBinding:
+    return TPMoERouteBinding(**kwargs)
+
+
+def b12x_route_experts_fast(*, binding: TPMoERouteBinding) -> B12XTopKRouting:
+    """Gate GEMM (optional, ``torch.mm``) then the top-k kernel (reference _impl.py:11356-11490)."""
+    b = binding
+    hs = b.hidden_states
+    if hs.ndim != 2:
+        raise ValueError(f"expected hidden_states with rank 2, got shape {tuple(hs.shape)}")
+    if b.top_k <= 0:
+        raise ValueError(f"top_k must be positive, got {b.top_k}")
+    if b.router_logits is not None and b.gate_weight is not None:
+        raise ValueError("pass either router_logits or gate_weight, not both")
+    if b.router_logits is None and b.gate_weight is None:
+        raise ValueError("expected router_logits or gate_weight")
+    if b.router_logits is None:
+        gw = b.gate_weight
+        if gw.ndim != 2 or gw.shape[1] != hs.shape[1]:
+            raise ValueError("gate_weight must be [experts, hidden]")
+        logits = torch.mm(hs, gw.t())
+        if b.gate_bias is not None:
+            logits = logits + b.gate_bias
+    else:
+        logits = b.router_logits
+        if logits.ndim != 2 or logits.shape[0] != hs.shape[0]:
+            raise ValueError("router_logits must be [tokens, experts]")
+    if b.top_k > logits.shape[1]:
+        raise ValueError(f"top_k={b.top_k} exceeds num_experts={logits.shape[1]}")
+    t = logits.shape[0]
+    dev = logits.device
+    tl = torch.empty((t, b.top_k), dtype=torch.float32, device=dev)
+    ti = torch.empty((t, b.top_k), dtype=torch.int32, device=dev)
+    tw = torch.empty((t, b.top_k), dtype=torch.float32, device=dev)
+    lg = logits if logits.dtype in (torch.float32, torch.bfloat16) else logits.float()
+    route_topk(lg, tl, ti, tw, renormalize=b.renormalize, score_func=b.score_func,
+               selection_bias=b.selection_bias, route_scale=b.route_scale)
+    return B12XTopKRouting(topk_weights=tw, topk_ids=ti, router_logits=logits,
+                           flat_ids=ti.view(-1), flat_weights=tw.view(-1))
+
+
+@dataclass(frozen=True, kw_only=True)
+class TPMoESparseFP4Binding:
+    """Route + experts in one binding (reference ``TPMoESparseFP4Binding`` _impl.py:1073)."""
+
+    plan: TPMoEScratchPlan
+    scratch: torch.Tensor
+    hidden_states: torch.Tensor
+    experts: B12XFP4ExpertWeights
+    top_k: int
+    gate_weight: torch.Tensor | None = None
+    gate_bias: torch.Tensor | None = None
+    router_logits: torch.Tensor | None = None
+    renormalize: bool = True
+    score_func: str = "softmax"
+    selection_bias: torch.Tensor | None = None
+    route_scale: float = 1.0
+    routed_scaling_factor: float = 1.0
+    output: torch.Tensor | None = None
+
+    def run(self) -> torch.Tensor:
+        return b12x_sparse_moe_fp4(binding=self)
+
+
+def build_tp_moe_sparse_fp4_binding(**kwargs) -> TPMoESparseFP4Binding:
+    return TPMoESparseFP4Binding(**kwargs)
+
+
+def b12x_sparse_moe_fp4(*, binding: TPMoESparseFP4Binding) -> torch.Tensor:
+    """route -> bind -> run -> multiply by ``routed_scaling_factor`` (reference _impl.py:11493-11575)."""
+    b = binding
+    routing = b12x_route_experts_fast(binding=TPMoERouteBinding(
+        hidden_states=b.hidden_states, top_k=b.top_k, gate_weight=b.gate_weight,
+        gate_bias=b.gate_bias, router_logits=b.router_logits, renormalize=b.renormalize,
+        score_func=b.score_func, selection_bias=b.selection_bias, route_scale=b.route_scale))
+    core = b.plan.bind(scratch=b.scratch, a=b.hidden_states, experts=b.experts,
+                       topk_weights=routing.topk_weights, topk_ids=routing.topk_ids,
+                       output=b.output, output_scale=b.routed_scaling_factor)
+    return b12x_moe_fp4(binding=core)
+
+
+def clear_tp_moe_caches() -> None:
+    """Nothing is cached per shape here (kernels are compiled ahead of time)."""
+    return None

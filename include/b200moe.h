@@ -1,0 +1,204 @@
+/*
+ * b200moe.h -- C ABI of the B200 (sm_100a) fused mixture-of-experts layer.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, launches on
+ * the stream it is given, never allocates, never synchronises, and returns 0 or
+ * a negative B200MOE_E* code (see b200moe_strerror).  All data pointers are
+ * DEVICE pointers unless a comment says otherwise.  Problems that only the
+ * device can see (a bounded wait that ran out) are written to the int32
+ * status block at the start of the scratch arena (word 0 != 0).
+ *
+ * The Python facade `b12x_b200.moe.fused_moe` binds these with ctypes; each
+ * comment names the routine of the reference library (b12x 1.2.6, paths
+ * relative to its repository root) whose role the entry point takes over.
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_ABI_VERSION 1
+
+/* ---- status codes ------------------------------------------------------ */
+#define B200MOE_OK            0
+#define B200MOE_EINVAL       -1   /* bad argument / unsupported shape          */
+#define B200MOE_ECAPACITY    -2   /* problem larger than the planned scratch   */
+#define B200MOE_ECUDA        -3   /* a CUDA runtime / driver call failed       */
+#define B200MOE_EUNSUPPORTED -4   /* recipe x activation not implemented       */
+#define B200MOE_EALIGN       -5   /* pointer or stride not aligned for TMA     */
+
+/* ---- enums (int32 in the structs) --------------------------------------- */
+enum { B200MOE_RECIPE_NVFP4 = 0, B200MOE_RECIPE_W4A8_MX = 1, B200MOE_RECIPE_W4A16 = 2 };
+enum { B200MOE_ACT_SILU = 0, B200MOE_ACT_RELU2 = 1, B200MOE_ACT_SWIGLUOAI = 2 };
+/* score function of the router */
+enum {
+  B200MOE_ROUTE_SOFTMAX_TOPK = 0, /* top-k on raw logits, softmax over the k selected */
+  B200MOE_ROUTE_RAW          = 1, /* top-k on raw logits, weights = the logits        */
+  B200MOE_ROUTE_SIGMOID      = 2  /* sigmoid scores (+bias for selection), renorm, scale */
+};
+enum { B200MOE_DT_F32 = 0, B200MOE_DT_BF16 = 1 };
+
+/* ---- device / scratch planning ----------------------------------------- */
+typedef struct {
+  int32_t sm_major, sm_minor, num_sms, max_smem_optin;
+  int64_t total_mem;
+} b200moe_device_info;
+
+/* Capacity of one plan.  Mirrors the tensor-free part of the reference's
+ * TPMoEScratchCaps (b12x/moe/fused_moe/_impl.py:747-860). */
+typedef struct {
+  int32_t max_tokens;    /* T capacity                                        */
+  int32_t num_topk;      /* k                                                 */
+  int32_t num_experts;   /* E (weights held by this rank)                     */
+  int32_t hidden_size;   /* K                                                 */
+  int32_t intermediate;  /* I                                                 */
+  int32_t recipe;        /* B200MOE_RECIPE_*                                  */
+  int32_t activation;    /* B200MOE_ACT_*                                     */
+  int32_t reserved;
+} b200moe_caps;
+
+/* Byte offsets of every view inside the single uint8 scratch arena.  The
+ * reference prices the same kind of layout in _plan_core_workspace
+ * (b12x/moe/fused_moe/_impl.py:2525-3090). */
+typedef struct {
+  int64_t total_nbytes;
+  int64_t status;            /* int32[16]; word 0: device error, word 1: where  */
+  int64_t expert_counts;     /* int32[E]                                        */
+  int64_t expert_offsets;    /* int32[E+1]  first sorted position per expert    */
+  int64_t tile_base;         /* int32[E+1]  first 128-row tile per expert       */
+  int64_t mtile_expert;      /* int32[mtile_cap]                                */
+  int64_t mtile_row0;        /* int32[mtile_cap] sorted position of tile row 0  */
+  int64_t mtile_rows;        /* int32[mtile_cap] valid rows (1..128)            */
+  int64_t sorted_route_ids;  /* int32[rows]  flat route id (t*k+slot) per position */
+  int64_t inv_perm;          /* int32[rows]  position per flat route id, -1 = dropped */
+  int64_t act_q;             /* FC1 input codes  [rows][K/2] (nvfp4) / [rows][K] (mxfp8) / unused (w4a16) */
+  int64_t act_sf;            /* FC1 input scales, 512-byte atoms [mtile_cap][ceil(K/64|128)]  */
+  int64_t mid_q;             /* FC2 input codes  [rows][I/2] / [rows][I] / bf16 [rows][I]     */
+  int64_t mid_sf;            /* FC2 input scales atoms                                         */
+  int64_t routed;            /* float32 [rows][K] per-route FC2 output (alpha applied)         */
+  int32_t rows;              /* T*k                                             */
+  int32_t mtile_cap;         /* ceil(rows/128) + min(E, rows)                   */
+} b200moe_scratch_layout;
+
+int b200moe_abi_version(void);
+const char* b200moe_strerror(int code);
+/* HOST pointer out. */
+int b200moe_query_device(int device, b200moe_device_info* out);
+/* HOST pointers.  Replaces tp_moe_required_nbytes / plan_tp_moe_scratch sizing
+ * (b12x/moe/fused_moe/_impl.py:6781-6863). */
+int b200moe_scratch_nbytes(const b200moe_caps* caps, b200moe_scratch_layout* out);
+
+/* ---- stage 1: top-k routing -------------------------------------------- */
+/* Replaces route_topk / _route_topk_kernel (b12x/moe/_shared/routing.py:8-134)
+ * and, for B200MOE_ROUTE_SIGMOID, the host-side scoring of
+ * compute_model_gate_routing (benchmarks/benchmark_moe.py:1282-1322).
+ * Ties go to the larger expert index; slot order = descending score. */
+typedef struct {
+  const void* logits;        /* [T][row_stride] f32 or bf16                     */
+  const float* bias;         /* [E] added to scores for SELECTION only, or NULL */
+  float* topk_logits;        /* [T][k] selected raw logits (may be NULL)        */
+  int32_t* topk_ids;         /* [T][k]                                          */
+  float* topk_weights;       /* [T][k]                                          */
+  int64_t logits_row_stride; /* elements                                        */
+  int32_t num_tokens, num_experts, num_topk;
+  int32_t logits_dtype;      /* B200MOE_DT_*                                    */
+  int32_t mode;              /* B200MOE_ROUTE_*                                 */
+  int32_t renormalize;       /* SIGMOID mode: divide by the sum of the k scores */
+  float route_scale;         /* SIGMOID mode: final multiplier                  */
+  int32_t reserved;
+} b200moe_route_args;
+int b200moe_route_topk(const b200moe_route_args* a, void* stream);
+
+/* ---- stage 2: expert sort / permutation -------------------------------- */
+/* Replaces the histogram / prefix / route-pack phases of the reference's
+ * dynamic kernel (b12x/moe/_shared/kernels/dynamic.py:2881-3160) and the W4A16
+ * route pack (b12x/moe/_shared/kernels/w4a16/route_pack.py:288-523) with a
+ * STABLE counting sort: position order = (expert asc, flat route id asc).
+ * Ids outside [0,E) are dropped (inv_perm = -1), like ep_moe's -1 map entries. */
+typedef struct {
+  const int32_t* topk_ids;   /* [T*k] flat                                      */
+  const int32_t* expert_map; /* optional [global E] -> local id or -1, or NULL  */
+  void* scratch;             /* arena base                                      */
+  const b200moe_scratch_layout* layout; /* HOST pointer                        */
+  int32_t num_tokens, num_topk, num_experts, expert_map_len;
+} b200moe_sort_args;
+int b200moe_expert_sort(const b200moe_sort_args* a, void* stream);
+
+/* ---- stage 3: permute + activation quantisation ------------------------ */
+/* Replaces quantize_block_fp4 / quantize_block_fp8_mx as used by the dynamic
+ * kernel's route/pack phase (b12x/moe/_shared/kernels/dynamic.py:3059-3850;
+ * b12x/_lib/intrinsics.py:5846-5890, 5973-6005), exact ("direct division")
+ * variant.  Output rows are in sorted-position order. */
+typedef struct {
+  const void* x;             /* bf16 [T][x_row_stride]                          */
+  const float* a1_gscale;    /* [E] or [1] reciprocal input scale (nvfp4 only)  */
+  void* scratch;
+  const b200moe_scratch_layout* layout; /* HOST pointer                        */
+  int64_t x_row_stride;      /* elements                                        */
+  int32_t num_tokens, num_topk, num_experts, hidden_size;
+  int32_t gscale_len;        /* 1 or E                                          */
+  int32_t reserved;
+} b200moe_quant_args;
+int b200moe_permute_quant_nvfp4(const b200moe_quant_args* a, void* stream);
+int b200moe_permute_quant_mxfp8(const b200moe_quant_args* a, void* stream);
+
+/* ---- stage 4/5: grouped expert GEMMs ----------------------------------- */
+/* Weights in the checkpoint layout the reference consumes
+ * (b12x/moe/fused_moe/_impl.py:407-431): w13 [E][w1_rows][K/2] u8, two E2M1 per
+ * byte (low nibble = even k); block scales 128x4-swizzled
+ * [E][pad128(rows)][pad4(cols/16)] E4M3 (nvfp4, w4a16) or plain row-major
+ * [E][rows][cols/32] E8M0 (w4a8_mx, converted once at prepare time into the
+ * swizzled form); per-expert alphas.  Replaces the FC1 mainloop + activation +
+ * requantisation epilogue (dynamic.py:1112-1160, 1467-1497, 6700-6905) and the
+ * FC2 mainloop (dynamic.py:6905-7760) of the reference's dynamic kernel, and the
+ * W4A16 fused kernel (w4a16/kernel.py:5514). */
+typedef struct {
+  const uint8_t* w13;        /* FC1 weights                                     */
+  const uint8_t* w13_sf;     /* FC1 block scales (swizzled atoms)               */
+  const float* w1_alphas;    /* [E]                                             */
+  const uint8_t* w2;         /* FC2 weights [E][K][I/2]                         */
+  const uint8_t* w2_sf;
+  const float* w2_alphas;    /* [E]                                             */
+  const float* a2_gscale;    /* [E] or [1] reciprocal FC2-input scale (nvfp4)   */
+  const void* x;             /* bf16 [T][K] (w4a16 only: A operand gathers rows)*/
+  void* scratch;
+  const b200moe_scratch_layout* layout; /* HOST pointer                        */
+  float* fc1_tap;            /* optional f32 [rows][w1_rows] alpha-scaled FC1 output (debug tap), or NULL */
+  int64_t x_row_stride;
+  int32_t num_tokens, num_topk, num_experts, hidden_size, intermediate;
+  int32_t recipe, activation;
+  int32_t gate_first;        /* 1: FC1 rows [gate;up] (SwiGLU-OAI), 0: [up;gate] */
+  int32_t gscale_len;
+  float swiglu_limit;        /* <=0: none                                       */
+  float swiglu_alpha, swiglu_beta;
+  int32_t num_sms;           /* persistent grid size, 0 = all SMs               */
+  int32_t reserved;
+} b200moe_gemm_args;
+int b200moe_grouped_gemm1_act(const b200moe_gemm_args* a, void* stream);
+int b200moe_grouped_gemm2(const b200moe_gemm_args* a, void* stream);
+
+/* ---- stage 6: top-k weighted combine ----------------------------------- */
+/* Replaces the bf16 atomic scatter / deterministic top-k sum of the reference
+ * (dynamic.py:7737-7750; w4a16/kernel.py:7733-7790): out[t] = sum over slots
+ * in slot order of w[t,slot] * routed[pos(t,slot)], fp32, one rounding. */
+typedef struct {
+  const float* topk_weights; /* [T][k]                                          */
+  void* out;                 /* bf16 [T][out_row_stride] or f32 when out_f32    */
+  void* scratch;
+  const b200moe_scratch_layout* layout; /* HOST pointer                        */
+  int64_t out_row_stride;
+  int32_t num_tokens, num_topk, hidden_size;
+  int32_t out_f32;           /* 1: write un-rounded float32 (parity tap)        */
+  float output_scale;        /* multiplies the sum (routed_scaling_factor), 1.0 = none */
+  int32_t reserved;
+} b200moe_combine_args;
+int b200moe_combine(const b200moe_combine_args* a, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */
