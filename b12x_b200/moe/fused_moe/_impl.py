@@ -222,7 +222,10 @@ class TPMoEScratchCaps:
     def __post_init__(self) -> None:
         object.__setattr__(self, "max_tokens", max(int(self.max_tokens), 1))
         object.__setattr__(self, "num_topk", max(int(self.num_topk), 1))
-        object.__setattr__(self, "device", torch.device(self.device))
+        dev = torch.device(self.device)
+        if dev.type == "cuda" and dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device() if torch.cuda.is_available() else 0)
+        object.__setattr__(self, "device", dev)
         if not isinstance(self.weight_plan, MoEWeightPreparationPlan):
             raise TypeError("weight_plan must be a MoEWeightPreparationPlan")
         mode = str(self.quant_mode).lower()
@@ -412,8 +415,8 @@ class TPMoEScratchPlan:
                 raise ValueError("output must be [tokens, K] in the plan dtype, row-contiguous")
         storage = scratch_tensor(scratch, self._scratch_specs, owner="TP MoE")
         core = storage.narrow(0, self.layout.route_workspace_nbytes, self.layout.core_workspace_nbytes)
-        if core.data_ptr() % 1024 != 0:
-            raise ValueError("scratch must be 1024-byte aligned")
+        if core.data_ptr() % 256 != 0:
+            raise ValueError("scratch must be 256-byte aligned")
         return TPMoEFP4Binding(
             a=a, experts=experts, topk_weights=topk_weights, topk_ids=topk_ids,
             implementation=self.launch_plan.implementation, weight_E=caps.weight_E,
