@@ -60,6 +60,14 @@ class QuantArgs(C.Structure):
                 ("hidden_size", C.c_int32), ("gscale_len", C.c_int32), ("reserved", C.c_int32)]
 
 
+class GatherArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("topk_ids", C.c_void_p), ("out_rows", C.c_void_p),
+                ("out_ids", C.c_void_p), ("scratch", C.c_void_p), ("layout", C.POINTER(ScratchLayout)),
+                ("x_row_stride", C.c_int64),
+                ("num_tokens", C.c_int32), ("num_topk", C.c_int32), ("num_groups", C.c_int32),
+                ("hidden_size", C.c_int32), ("local_modulus", C.c_int32), ("reserved", C.c_int32)]
+
+
 class GemmArgs(C.Structure):
     _fields_ = [("w13", C.c_void_p), ("w13_sf", C.c_void_p), ("w1_alphas", C.c_void_p),
                 ("w2", C.c_void_p), ("w2_sf", C.c_void_p), ("w2_alphas", C.c_void_p),
@@ -91,6 +99,7 @@ EXPORTS = {
     "b200moe_expert_sort": ([C.POINTER(SortArgs), C.c_void_p], C.c_int),
     "b200moe_permute_quant_nvfp4": ([C.POINTER(QuantArgs), C.c_void_p], C.c_int),
     "b200moe_permute_quant_mxfp8": ([C.POINTER(QuantArgs), C.c_void_p], C.c_int),
+    "b200moe_gather_rows": ([C.POINTER(GatherArgs), C.c_void_p], C.c_int),
     "b200moe_grouped_gemm1_act": ([C.POINTER(GemmArgs), C.c_void_p], C.c_int),
     "b200moe_grouped_gemm2": ([C.POINTER(GemmArgs), C.c_void_p], C.c_int),
     "b200moe_combine": ([C.POINTER(CombineArgs), C.c_void_p], C.c_int),

@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(256) permute_quant_mxfp8_kernel(
         float amax = 0.f;
 #pragma unroll
         for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
-        sfb = ue8m0_ceil_byte(__fmul_rn(amax, 1.0f / 448.0f));
+        sfb = ue8m0_ceil_byte(__fmul_rn(amax, static_cast<float>(1.0 / 448.0)));
         const float inv = ue8m0_inv_scale(sfb);
         uint32_t o[8];
 #pragma unroll
@@ -223,9 +223,54 @@ __global__ void __launch_bounds__(256) combine_kernel(
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// gather_rows: send-side packing of the expert-parallel dispatch (one warp per row, 16-byte
+// vectors).  Rows are ordered by the preceding sort (destination rank, then flat route id).
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gather_rows_kernel(
+    const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, const int32_t* __restrict__ topk_ids,
+    const int32_t* __restrict__ expert_offsets, int num_groups,
+    const int32_t* __restrict__ sorted_route_ids, int num_topk, int K, int local_modulus,
+    __nv_bfloat16* __restrict__ out_rows, int32_t* __restrict__ out_ids) {
+  const int total = expert_offsets[num_groups];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int pos = blockIdx.x * 8 + warp; pos < total; pos += gridDim.x * 8) {
+    const int r = sorted_route_ids[pos];
+    const int t = r / num_topk;
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(t) * x_row_stride);
+    uint4* dst = reinterpret_cast<uint4*>(out_rows + static_cast<size_t>(pos) * K);
+    for (int j = lane; j < (K >> 3); j += 32) dst[j] = __ldg(src + j);
+    if (lane == 0) out_ids[pos] = topk_ids[r] % local_modulus;
+  }
+}
+
 }  // namespace b200moe
 
 using namespace b200moe;
+
+extern "C" int b200moe_gather_rows(const b200moe_gather_args* a, void* stream) {
+  if (a == nullptr || a->x == nullptr || a->topk_ids == nullptr || a->out_rows == nullptr ||
+      a->out_ids == nullptr || a->scratch == nullptr || a->layout == nullptr)
+    return B200MOE_EINVAL;
+  if (a->hidden_size <= 0 || a->hidden_size % 8 != 0 || a->local_modulus <= 0 || a->num_groups <= 0)
+    return B200MOE_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(a->x) & 15) != 0 || (a->x_row_stride % 8) != 0 ||
+      (reinterpret_cast<uintptr_t>(a->out_rows) & 15) != 0)
+    return B200MOE_EALIGN;
+  const int rows = a->num_tokens * a->num_topk;
+  if (rows > a->layout->rows) return B200MOE_ECAPACITY;
+  if (rows == 0) return B200MOE_OK;
+  const b200moe_scratch_layout& L = *a->layout;
+  char* base = static_cast<char*>(a->scratch);
+  int grid = (rows + 7) / 8;
+  if (grid > 148 * 8) grid = 148 * 8;
+  gather_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride, a->topk_ids,
+      reinterpret_cast<const int32_t*>(base + L.expert_offsets), a->num_groups,
+      reinterpret_cast<const int32_t*>(base + L.sorted_route_ids), a->num_topk, a->hidden_size,
+      a->local_modulus, static_cast<__nv_bfloat16*>(a->out_rows), a->out_ids);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
 
 static int check_quant_args(const b200moe_quant_args* a, int block) {
   if (a == nullptr || a->x == nullptr || a->scratch == nullptr || a->layout == nullptr)

@@ -1,0 +1,233 @@
+"""Multi-GPU partitioning of the MoE layer: one process per GPU, NCCL over NVLink.
+
+* ``ExpertParallelMoE``: experts are block-partitioned over the ranks, every rank routes its own
+  tokens, rows travel to the rank that owns their expert (all-to-all-v), the per-route FC2 rows
+  travel back as fp32 and are combined on the home rank in slot order -- so the result is
+  bit-identical to the single-GPU layer.  With one rank it is the plain layer.
+* ``TensorParallelMoE``: every rank holds an ``I / n`` slice of every expert (FC1 rows of both
+  halves, FC2 columns), inputs and routing are replicated, partial outputs are summed with an
+  all-reduce -- the contract of the reference's "tensor-parallel" use of fused_moe
+  (b12x/moe/__init__.py:3-8).
+
+The reference has no token all-to-all: its ``ep_moe`` replicates the input on every rank and lets
+the caller sum partial outputs (b12x/moe/ep_moe/_impl.py:1-14).
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import replace
+
+import torch
+import torch.distributed as dist
+
+from .. import synth
+from . import fused_moe
+from .fused_moe.stages import StageArena
+
+_ACT_API = {"silu": "silu", "relu2": "relu2", "swigluoai": "swigluoai_uninterleave"}
+_SOURCE = {"nvfp4": "modelopt_nvfp4", "w4a16": "modelopt_nvfp4", "w4a8_mx": "fp4_e8m0_k32"}
+
+
+def init_process_group(device: torch.device) -> None:
+    if dist.is_initialized():
+        return
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    backend = "nccl" if device.type == "cuda" else "gloo"
+    kw = {"device_id": device} if device.type == "cuda" else {}
+    dist.init_process_group(backend=backend, **kw)
+
+
+def prepare_experts(inp: synth.MoEInputs, dev: torch.device):
+    """``plan_weights`` + ``prepare_weights`` for synthetic inputs."""
+    shp = inp.shape
+    wp = fused_moe.plan_weights(
+        quant_modes=shp.recipe, source_format=_SOURCE[shp.recipe], activation=_ACT_API[shp.activation],
+        params_dtype=torch.bfloat16, num_experts=inp.w1_fp4.shape[0], hidden_size=shp.hidden,
+        intermediate_size=inp.w2_fp4.shape[2] * 2)
+    kw = dict(plan=wp, params_dtype=torch.bfloat16, w1_fp4=inp.w1_fp4.to(dev), w2_fp4=inp.w2_fp4.to(dev),
+              w1_blockscale=inp.w1_blockscale.to(dev), w2_blockscale=inp.w2_blockscale.to(dev))
+    if shp.recipe == "nvfp4":
+        kw.update(w1_global_scale=inp.w1_global_scale.to(dev), w2_global_scale=inp.w2_global_scale.to(dev),
+                  a1_gscale=inp.a1_gscale.to(dev), a2_gscale=inp.a2_gscale.to(dev))
+    elif shp.recipe == "w4a16":
+        kw.update(w1_global_scale=inp.w1_global_scale.to(dev), w2_global_scale=inp.w2_global_scale.to(dev))
+    return fused_moe.prepare_weights(**kw)
+
+
+def split_counts_exchange(send_counts: torch.Tensor, group=None) -> torch.Tensor:
+    """recv_counts[r] = rows rank r will send to this rank (tiny all-to-all of int32)."""
+    recv = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv, send_counts, group=group)
+    return recv
+
+
+class _LayerBase:
+    kernels_per_step = 6
+
+    def __init__(self, shp: synth.MoEShape, inputs: synth.MoEInputs, experts, dev, rank: int, world: int):
+        self.shape, self.inputs, self.experts = shp, inputs, experts
+        self.dev, self.rank, self.world = dev, rank, world
+        t, k = shp.tokens, shp.topk
+        self.topk_logits = torch.empty((t, k), dtype=torch.float32, device=dev)
+        self.topk_ids = torch.empty((t, k), dtype=torch.int32, device=dev)
+        self.topk_weights = torch.empty((t, k), dtype=torch.float32, device=dev)
+        self.out = torch.empty((t, shp.hidden), dtype=torch.bfloat16, device=dev)
+        self.x_stage = torch.empty((t, shp.hidden), dtype=torch.bfloat16, device=dev)
+        self.lg_stage = torch.empty((t, shp.experts), dtype=torch.float32, device=dev)
+        self.last_binding = None
+
+    def route(self, logits: torch.Tensor) -> None:
+        shp = self.shape
+        if shp.router == "sigmoid":
+            fused_moe.route_topk(logits, self.topk_logits, self.topk_ids, self.topk_weights, renormalize=True,
+                                 score_func="sigmoid", route_scale=shp.route_scale)
+        else:
+            fused_moe.route_topk(logits, self.topk_logits, self.topk_ids, self.topk_weights, renormalize=True)
+
+    def forward_host(self, x_host: torch.Tensor, logits_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        """Host buffers in, host buffer out: H2D copies, the layer, D2H copy, all on the current stream."""
+        self.x_stage.copy_(x_host, non_blocking=True)
+        self.lg_stage.copy_(logits_host, non_blocking=True)
+        out = self.forward(self.x_stage, self.lg_stage)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream(self.dev).synchronize()
+
+    def check_status(self) -> None:
+        if self.last_binding is not None:
+            fused_moe.check_device_status(self.last_binding)
+
+    def _local_plan(self, max_tokens: int, topk: int):
+        caps = fused_moe.Caps(max_tokens=max_tokens, num_topk=topk, device=self.dev,
+                              weight_plan=self.experts.plan, quant_mode=self.shape.recipe)
+        plan = fused_moe.plan(caps)
+        spec = plan.scratch_specs()[0]
+        return plan, torch.empty(spec.shape, dtype=spec.dtype, device=self.dev)
+
+    def _dominant(self, local_shape: synth.MoEShape, active_experts: int, rows: int) -> dict:
+        """Algorithmic bytes / flops of the FC1 launch (the largest kernel of the layer)."""
+        k, i = local_shape.hidden, local_shape.intermediate
+        g = 32 if local_shape.recipe == "w4a8_mx" else 16
+        w1_rows = i if local_shape.activation == "relu2" else 2 * i
+        a_bytes = {"nvfp4": k / 2 + k / 16, "w4a8_mx": k + k / 32, "w4a16": 2.0 * k}[local_shape.recipe]
+        o_bytes = {"nvfp4": i / 2 + i / 16, "w4a8_mx": i + i / 32, "w4a16": 2.0 * i}[local_shape.recipe]
+        weight_bytes = active_experts * w1_rows * k * (0.5 + 1.0 / g)
+        total_bytes = weight_bytes + rows * (a_bytes + o_bytes)
+        flops = 2.0 * rows * w1_rows * k
+        # the layer is weight-streaming bound while the rows per expert are few
+        intensity = flops / max(total_bytes, 1.0)
+        bound = "hbm" if intensity < 1000 else "tensor"
+        peak_tf = {"nvfp4": 9000.0, "w4a8_mx": 4500.0, "w4a16": 2250.0}[local_shape.recipe]
+        return {"kernel": "grouped_gemm1_act", "stage": "gemm1", "bound": bound, "bytes": total_bytes,
+                "flops": flops, "peak_tflops": peak_tf,
+                "peak_note": "" if bound == "hbm" else " (tensor peak: nominal dense figure for the operand type)"}
+
+
+class ExpertParallelMoE(_LayerBase):
+    def __init__(self, shp, inputs, experts, dev, rank=0, world=1, *, recv_capacity_factor: float | None = None):
+        super().__init__(shp, inputs, experts, dev, rank, world)
+        self.e_local = shp.experts // world
+        if shp.experts % world:
+            raise ValueError("experts must divide evenly over the ranks")
+        t, k = shp.tokens, shp.topk
+        if world == 1:
+            self.plan, self.scratch = self._local_plan(t, k)
+            return
+        # home side: sort routes by destination rank, pack rows, later combine returned rows
+        self.home = StageArena(t, k, world, shp.hidden, dev)
+        self.rank_of_expert = (torch.arange(shp.experts, dtype=torch.int32, device=dev) // self.e_local).contiguous()
+        rows = t * k
+        self.send_rows = torch.empty((rows, shp.hidden), dtype=torch.bfloat16, device=dev)
+        self.send_ids = torch.empty((rows,), dtype=torch.int32, device=dev)
+        # expert side: worst case every route of every rank lands here
+        cap = rows * world if recv_capacity_factor is None else int(rows * recv_capacity_factor)
+        self.recv_cap = cap
+        self.recv_rows = torch.empty((cap, shp.hidden), dtype=torch.bfloat16, device=dev)
+        self.recv_ids = torch.empty((cap, 1), dtype=torch.int32, device=dev)
+        self.recv_ones = torch.ones((cap, 1), dtype=torch.float32, device=dev)
+        self.recv_out = torch.empty((cap, shp.hidden), dtype=torch.float32, device=dev)
+        self.plan, self.scratch = self._local_plan(cap, 1)
+        self.kernels_per_step = 9  # route, rank sort, gather, expert sort, quant, gemm1, gemm2, un-permute, combine
+
+    @classmethod
+    def from_synthetic(cls, shp: synth.MoEShape, dev, rank: int, world: int):
+        e_local = shp.experts // world
+        inp = synth.make_inputs(shp, seed=1000 + rank, device=dev, experts=e_local)
+        return cls(shp, inp, prepare_experts(inp, dev), dev, rank, world)
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, stage_timer=None) -> torch.Tensor:
+        self.route(logits)
+        if self.world == 1:
+            b = fused_moe.bind(self.plan, scratch=self.scratch, a=x, experts=self.experts,
+                               topk_weights=self.topk_weights, topk_ids=self.topk_ids, output=self.out)
+            self.last_binding = b
+            return fused_moe.run(binding=b, stage_timer=stage_timer)
+        shp = self.shape
+        home = self.home
+        home.sort(self.topk_ids, self.rank_of_expert)
+        send_counts = home.group_counts
+        recv_counts = split_counts_exchange(send_counts)
+        home.gather_rows(x, self.topk_ids, self.send_rows, self.send_ids, self.e_local)
+        counts = torch.stack([send_counts, recv_counts]).cpu()     # the one host sync of the step
+        sc, rc = counts[0].tolist(), counts[1].tolist()
+        n_send, n_recv = sum(sc), sum(rc)
+        if n_recv > self.recv_cap:
+            raise RuntimeError(f"received {n_recv} rows, capacity {self.recv_cap}")
+        dist.all_to_all_single(self.recv_rows[:n_recv], self.send_rows[:n_send], rc, sc)
+        dist.all_to_all_single(self.recv_ids.view(-1)[:n_recv], self.send_ids[:n_send], rc, sc)
+        if n_recv > 0:
+            b = fused_moe.bind(self.plan, scratch=self.scratch, a=self.recv_rows[:n_recv], experts=self.experts,
+                               topk_weights=self.recv_ones[:n_recv], topk_ids=self.recv_ids[:n_recv],
+                               output_f32=self.recv_out[:n_recv], f32_only=True)
+            self.last_binding = b
+            fused_moe.run(binding=b, stage_timer=stage_timer)
+        dist.all_to_all_single(home.routed[:n_send], self.recv_out[:n_recv], sc, rc)
+        home.combine(self.topk_weights, self.out)
+        return self.out
+
+    def work_stats(self) -> dict:
+        b = self.last_binding
+        counts = b.expert_counts.cpu()
+        active = int((counts > 0).sum())
+        rows = int(counts.sum())
+        local = replace(self.shape, experts=self.e_local)
+        return {"dominant": self._dominant(local, active, rows), "active_experts": active, "rows": rows}
+
+
+class TensorParallelMoE(_LayerBase):
+    def __init__(self, shp, inputs, experts, dev, rank=0, world=1):
+        super().__init__(shp, inputs, experts, dev, rank, world)
+        self.local_shape = replace(shp, intermediate=inputs.w2_fp4.shape[2] * 2)
+        self.plan, self.scratch = self._local_plan(shp.tokens, shp.topk)
+        self.partial = torch.empty((shp.tokens, shp.hidden), dtype=torch.float32, device=dev)
+        self.kernels_per_step = 6
+
+    @classmethod
+    def from_synthetic(cls, shp: synth.MoEShape, dev, rank: int, world: int):
+        if shp.intermediate % world:
+            raise ValueError("intermediate size must divide evenly over the ranks")
+        local = replace(shp, intermediate=shp.intermediate // world)
+        inp = synth.make_inputs(local, seed=2000 + rank, device=dev)
+        # tokens and router logits are replicated: every rank draws them from the same seed
+        rep = synth.make_inputs(replace(local, experts=shp.experts), seed=7, device=dev, experts=0)
+        inp.x, inp.router_logits = rep.x, rep.router_logits
+        inp.shape = shp
+        return cls(shp, inp, prepare_experts(inp, dev), dev, rank, world)
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, stage_timer=None) -> torch.Tensor:
+        self.route(logits)
+        b = fused_moe.bind(self.plan, scratch=self.scratch, a=x, experts=self.experts,
+                           topk_weights=self.topk_weights, topk_ids=self.topk_ids,
+                           output_f32=self.partial, f32_only=True)
+        self.last_binding = b
+        fused_moe.run(binding=b, stage_timer=stage_timer)
+        if self.world > 1:
+            dist.all_reduce(self.partial)
+        self.out.copy_(self.partial)
+        return self.out
+
+    def work_stats(self) -> dict:
+        counts = self.last_binding.expert_counts.cpu()
+        active = int((counts > 0).sum())
+        rows = int(counts.sum())
+        return {"dominant": self._dominant(self.local_shape, active, rows), "active_experts": active, "rows": rows}

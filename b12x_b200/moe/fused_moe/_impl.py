@@ -377,6 +377,7 @@ class TPMoEScratchPlan:
         fc1_tap: torch.Tensor | None = None,
         output_f32: torch.Tensor | None = None,
         output_scale: float = 1.0,
+        f32_only: bool = False,
     ) -> "TPMoEFP4Binding":
         """Validate the call and map the caller's scratch into kernel-argument views.
 
@@ -415,8 +416,8 @@ class TPMoEScratchPlan:
                 raise ValueError("output must be [tokens, K] in the plan dtype, row-contiguous")
         storage = scratch_tensor(scratch, self._scratch_specs, owner="TP MoE")
         core = storage.narrow(0, self.layout.route_workspace_nbytes, self.layout.core_workspace_nbytes)
-        if core.data_ptr() % 256 != 0:
-            raise ValueError("scratch must be 256-byte aligned")
+        if core.data_ptr() % 16 != 0:
+            raise ValueError("scratch must be 16-byte aligned")
         return TPMoEFP4Binding(
             a=a, experts=experts, topk_weights=topk_weights, topk_ids=topk_ids,
             implementation=self.launch_plan.implementation, weight_E=caps.weight_E,
@@ -427,7 +428,7 @@ class TPMoEScratchPlan:
             swiglu_limit=caps.swiglu_limit, swiglu_alpha=caps.swiglu_alpha,
             swiglu_beta=caps.swiglu_beta, route_expert_map=route_expert_map,
             kernel_workspace=core, core_layout=self._core_layout, fc1_tap=fc1_tap,
-            output_f32=output_f32, output_scale=float(output_scale))
+            output_f32=output_f32, output_scale=float(output_scale), f32_only=bool(f32_only))
 
 
 def plan_tp_moe_scratch(caps: TPMoEScratchCaps) -> TPMoEScratchPlan:
@@ -483,6 +484,7 @@ class TPMoEFP4Binding:
     fc1_tap: torch.Tensor | None = None
     output_f32: torch.Tensor | None = None
     output_scale: float = 1.0
+    f32_only: bool = False     # write only ``output_f32`` (un-rounded sums), skip the bf16 output
 
     # ---- scratch views (valid after run) ----
     def _v(self, name: str, count: int, dtype: torch.dtype) -> torch.Tensor:
@@ -553,11 +555,13 @@ def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
-def b12x_moe_fp4(*, binding: TPMoEFP4Binding) -> torch.Tensor:
+def b12x_moe_fp4(*, binding: TPMoEFP4Binding, stage_timer=None) -> torch.Tensor:
     """Run the layer for one binding on the current CUDA stream and return ``[tokens, K]``.
 
     Reference: ``b12x_moe_fp4`` (_impl.py:10446-11012).  With ``binding.output`` set nothing is
-    allocated and nothing synchronises, so the call can be captured in a CUDA graph."""
+    allocated and nothing synchronises, so the call can be captured in a CUDA graph.
+    ``stage_timer`` (optional) is called with a stage name at every stage boundary; a benchmark
+    uses it to record CUDA events around single kernels."""
     if not isinstance(binding, TPMoEFP4Binding):
         raise TypeError("binding must come from Plan.bind")
     b = binding
@@ -566,7 +570,11 @@ def b12x_moe_fp4(*, binding: TPMoEFP4Binding) -> torch.Tensor:
     lib = ext.load()
     tokens = b.tokens
     out = b.output
-    if out is None:
+    if b.f32_only:
+        if b.output_f32 is None:
+            raise ValueError("f32_only needs output_f32")
+        out = b.output_f32
+    elif out is None:
         if torch.cuda.is_current_stream_capturing():
             raise RuntimeError("output must be provided during CUDA graph capture")
         out = torch.empty((tokens, b.k), dtype=b.dtype, device=b.device)
@@ -580,16 +588,20 @@ def b12x_moe_fp4(*, binding: TPMoEFP4Binding) -> torch.Tensor:
     recipe = ext.RECIPES[b.quant_mode]
     act = ext.ACTIVATIONS[_ACT_CODE[b.activation]]
 
+    mark = stage_timer if stage_timer is not None else (lambda _name: None)
+    mark("begin")
     emap = b.route_expert_map
     sort_args = ext.SortArgs(b.topk_ids.data_ptr(), _ptr(emap), scratch, lp, tokens, b.num_topk,
                              b.weight_E, 0 if emap is None else int(emap.numel()))
     ext.check(lib.b200moe_expert_sort(C.byref(sort_args), stream), "expert_sort")
+    mark("sort")
 
     if b.quant_mode in ("nvfp4", "w4a8_mx"):
         qargs = ext.QuantArgs(b.a.data_ptr(), ex.a1_gscale.data_ptr(), scratch, lp, b.a.stride(0),
                               tokens, b.num_topk, b.weight_E, b.k, int(ex.a1_gscale.numel()), 0)
         fn = lib.b200moe_permute_quant_nvfp4 if b.quant_mode == "nvfp4" else lib.b200moe_permute_quant_mxfp8
         ext.check(fn(C.byref(qargs), stream), "permute_quant")
+    mark("quant")
 
     gargs = ext.GemmArgs(
         ex.w1_fp4.data_ptr(), ex.w1_blockscale.data_ptr(), ex.w1_alphas.data_ptr(),
@@ -602,16 +614,22 @@ def b12x_moe_fp4(*, binding: TPMoEFP4Binding) -> torch.Tensor:
         float(b.swiglu_alpha if b.swiglu_alpha is not None else 1.0),
         float(b.swiglu_beta if b.swiglu_beta is not None else 0.0), 0, 0)
     ext.check(lib.b200moe_grouped_gemm1_act(C.byref(gargs), stream), "grouped_gemm1_act")
+    mark("gemm1")
     ext.check(lib.b200moe_grouped_gemm2(C.byref(gargs), stream), "grouped_gemm2")
+    mark("gemm2")
 
-    cargs = ext.CombineArgs(b.topk_weights.data_ptr(), out.data_ptr(), scratch, lp, out.stride(0),
-                            tokens, b.num_topk, b.k, 0, float(b.output_scale), 0)
-    ext.check(lib.b200moe_combine(C.byref(cargs), stream), "combine")
+    if not b.f32_only:
+        cargs = ext.CombineArgs(b.topk_weights.data_ptr(), out.data_ptr(), scratch, lp, out.stride(0),
+                                tokens, b.num_topk, b.k, 0, float(b.output_scale), 0)
+        ext.check(lib.b200moe_combine(C.byref(cargs), stream), "combine")
+        mark("combine")
     if b.output_f32 is not None:
         targs = ext.CombineArgs(b.topk_weights.data_ptr(), b.output_f32.data_ptr(), scratch, lp,
                                 b.output_f32.stride(0), tokens, b.num_topk, b.k, 1,
                                 float(b.output_scale), 0)
         ext.check(lib.b200moe_combine(C.byref(targs), stream), "combine(f32 tap)")
+        if b.f32_only:
+            mark("combine")
     return out
 
 

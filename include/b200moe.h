@@ -146,6 +146,25 @@ typedef struct {
 int b200moe_permute_quant_nvfp4(const b200moe_quant_args* a, void* stream);
 int b200moe_permute_quant_mxfp8(const b200moe_quant_args* a, void* stream);
 
+/* Expert-parallel dispatch helper: copies the bf16 rows of x into sorted-position order
+ * (out_rows[pos] = x[route / k]) and emits each route's destination-local expert id
+ * (topk_ids[route] % local_modulus).  The sort that precedes it ranks routes by destination rank.
+ * The reference has no token all-to-all (b12x/moe/ep_moe/_impl.py:1-14 replicates the input);
+ * this is the send-side packing of the NCCL dispatch that replaces it. */
+typedef struct {
+  const void* x;             /* bf16 [T][x_row_stride]                          */
+  const int32_t* topk_ids;   /* [T*k]                                           */
+  void* out_rows;            /* bf16 [rows][hidden]                             */
+  int32_t* out_ids;          /* [rows]                                          */
+  void* scratch;
+  const b200moe_scratch_layout* layout; /* HOST pointer                        */
+  int64_t x_row_stride;
+  int32_t num_tokens, num_topk, num_groups, hidden_size;
+  int32_t local_modulus;     /* experts per rank                                */
+  int32_t reserved;
+} b200moe_gather_args;
+int b200moe_gather_rows(const b200moe_gather_args* a, void* stream);
+
 /* ---- stage 4/5: grouped expert GEMMs ----------------------------------- */
 /* Weights in the checkpoint layout the reference consumes
  * (b12x/moe/fused_moe/_impl.py:407-431): w13 [E][w1_rows][K/2] u8, two E2M1 per
