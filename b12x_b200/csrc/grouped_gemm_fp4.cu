@@ -8,7 +8,7 @@
 // One persistent CTA per SM walks the (expert, n-tile, m-tile) work list that the sort kernel
 // left in the scratch arena.  Warp 0 feeds a 4-stage TMA pipeline (SWIZZLE_128B operand tiles +
 // plain bulk copies of the 512-byte scale atoms), warp 1 copies the scale atoms into TMEM with
-// tcgen05.cp and issues tcgen05.mma.kind::mxf4nvf4.block_scale (scale_vec::4X), warps 2..5 drain
+// tcgen05.cp and issues tcgen05.mma.kind::mxf4nvf4.block_scale (scale_vec::4X), warps 2..9 drain
 // the TMEM accumulator.  Every wait is bounded; a wait that runs out marks the status block and
 // every role leaves its loop.
 #include "common.cuh"
@@ -21,7 +21,7 @@ constexpr int kStages = 4;
 constexpr int kRowBytes = 128;      // one swizzled operand row per stage = 256 FP4 values
 constexpr int kKPerStage = 256;     // reduction elements per stage
 constexpr int kKPerMma = 64;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kTmemCols = 512;
 constexpr int kTmemSfa = 256;       // 4 stages x 16 columns
 constexpr int kTmemSfb = 320;       // 4 stages x 32 columns
@@ -99,10 +99,10 @@ __device__ __forceinline__ float act_gated(float gate, float up, const GemmParam
     up = fminf(fmaxf(up, -p.limit), p.limit);
   }
   if (p.swigluoai) {
-    const float s = __fdiv_rn(1.0f, 1.0f + expf(-(p.act_alpha * gate)));
+    const float s = __frcp_rn(1.0f + expf(-(p.act_alpha * gate)));
     return (gate * s) * (up + p.act_beta);
   }
-  const float s = __fdiv_rn(1.0f, 1.0f + expf(-gate));
+  const float s = __frcp_rn(1.0f + expf(-gate));
   return (gate * s) * up;
 }
 
@@ -110,7 +110,10 @@ __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
 
-// same arithmetic as quant_block16 in the activation quantiser
+// Same arithmetic as quant_block16 in the activation quantiser, with a cheap common path: the
+// quotient x / denom is first approximated by x * rcp(denom) (error < 2 ulp); if the values 2^-21
+// below and above it round to the same E2M1 code, the correctly rounded quotient does too.
+// Only a block with a value that close to a rounding boundary takes the exact division.
 __device__ __forceinline__ void requant_block16(const float (&v)[16], float gs, uint32_t& lo,
                                                 uint32_t& hi, uint8_t& sf_byte) {
   float amax = 0.f;
@@ -120,14 +123,28 @@ __device__ __forceinline__ void requant_block16(const float (&v)[16], float gs, 
   sf_byte = f32_to_e4m3_rn_sat(raw);
   const float sf = e4m3_to_f32(sf_byte);
   const float denom = fmaxf(__fdiv_rn(sf, gs), 1e-30f);
-  float q0[8], q1[8];
+  const float r = __frcp_rn(denom);
+  float a0[8], a1[8], b0[8], b1[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    q0[i] = __fdiv_rn(v[i], denom);
-    q1[i] = __fdiv_rn(v[8 + i], denom);
+    const float q0 = __fmul_rn(v[i], r), q1 = __fmul_rn(v[8 + i], r);
+    a0[i] = __fmul_rn(q0, 1.0f - 4.76837158e-7f);
+    b0[i] = __fmul_rn(q0, 1.0f + 4.76837158e-7f);
+    a1[i] = __fmul_rn(q1, 1.0f - 4.76837158e-7f);
+    b1[i] = __fmul_rn(q1, 1.0f + 4.76837158e-7f);
   }
-  lo = pack_e2m1x8(q0);
-  hi = pack_e2m1x8(q1);
+  lo = pack_e2m1x8(a0);
+  hi = pack_e2m1x8(a1);
+  if (lo != pack_e2m1x8(b0) || hi != pack_e2m1x8(b1)) {
+    float q0[8], q1[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      q0[i] = __fdiv_rn(v[i], denom);
+      q1[i] = __fdiv_rn(v[8 + i], denom);
+    }
+    lo = pack_e2m1x8(q0);
+    hi = pack_e2m1x8(q1);
+  }
 }
 
 template <int EPI>
@@ -152,7 +169,7 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA,
       mbar_init(&tail->empty[s], 1);
     }
     mbar_init(&tail->tmem_full, 1);
-    mbar_init(&tail->tmem_empty, 4);
+    mbar_init(&tail->tmem_empty, 8);
     tail->abort_flag = 0;
     fence_mbar_init();
   }
@@ -272,7 +289,10 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA,
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
-    const int sub = warp & 3;                 // TMEM sub-partition this warp may read
+    // Eight warps.  Warp w may only read TMEM sub-partition (w & 3), i.e. tile rows
+    // 32*(w&3) .. +31; the two warps that share a sub-partition split the tile's columns.
+    const int sub = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int m = sub * 32 + lane;            // tile row = TMEM lane
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(sub * 32) << 16);
     uint32_t tile_phase = 0;
@@ -290,14 +310,14 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA,
 
       if (EPI == EPI_FC1_GATED) {
         const float gs2 = p.gscale2[p.gscale_len > 1 ? c.e : 0];
-        const int col0 = c.nt * 128;          // first intermediate column of this tile
-        uint32_t codes[16];
-        uint32_t sfw[2] = {0u, 0u};
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
+        const int col0 = c.nt * 128 + half * 64;   // first intermediate column of this warp
+        uint8_t* qrow = p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1);
+        uint32_t sfw = 0u;
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
           uint32_t ru[16], rg[16];
-          tc_ld_32x32b_x16(t_lane + ch * 16, ru);
-          tc_ld_32x32b_x16(t_lane + 128 + ch * 16, rg);
+          tc_ld_32x32b_x16(t_lane + half * 64 + ch * 16, ru);
+          tc_ld_32x32b_x16(t_lane + 128 + half * 64 + ch * 16, rg);
           tc_wait_ld();
           float h[16];
 #pragma unroll
@@ -311,33 +331,26 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA,
             }
             h[i] = round_bf16(act_gated(gate, up, p));
           }
+          uint32_t lo, hi;
           uint8_t sfb;
-          requant_block16(h, gs2, codes[2 * ch], codes[2 * ch + 1], sfb);
-          sfw[ch >> 2] |= static_cast<uint32_t>(sfb) << (8 * (ch & 3));
+          requant_block16(h, gs2, lo, hi, sfb);
+          if (valid) *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
+          sfw |= static_cast<uint32_t>(sfb) << (8 * ch);
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tail->tmem_empty);
-        if (valid) {
-          uint4* dst = reinterpret_cast<uint4*>(p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1));
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            dst[q] = make_uint4(codes[4 * q], codes[4 * q + 1], codes[4 * q + 2], codes[4 * q + 3]);
-        }
         // scale atoms are per tile: padding rows are written too (their values are never used)
         uint8_t* sft = p.out_sf + static_cast<size_t>(c.mt) * p.out_atoms * 512;
-        *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 8)) = sfw[0];
-        *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 8 + 4)) = sfw[1];
+        *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 8 + half * 4)) = sfw;
       } else if (EPI == EPI_FC1_RELU2) {
         const float gs2 = p.gscale2[p.gscale_len > 1 ? c.e : 0];
-        const int col0 = c.nt * 256;
+        const int col0 = c.nt * 256 + half * 128;
         uint8_t* sft = p.out_sf + static_cast<size_t>(c.mt) * p.out_atoms * 512;
-#pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          if (col0 + half * 128 >= p.out_cols) break;
-          uint32_t codes[16];
+        if (col0 < p.out_cols) {
+          uint8_t* qrow = p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1);
           uint32_t sfw[2] = {0u, 0u};
-#pragma unroll
+#pragma unroll 1
           for (int ch = 0; ch < 8; ++ch) {
             uint32_t rr[16];
             tc_ld_32x32b_x16(t_lane + half * 128 + ch * 16, rr);
@@ -346,21 +359,16 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const float v = __fmul_rn(__uint_as_float(rr[i]), alpha);
-              if (p.tap != nullptr && valid)
-                p.tap[pos * p.w_rows + col0 + half * 128 + ch * 16 + i] = v;
+              if (p.tap != nullptr && valid) p.tap[pos * p.w_rows + col0 + ch * 16 + i] = v;
               const float r = fmaxf(v, 0.f);
               h[i] = round_bf16(__fmul_rn(r, r));
             }
+            uint32_t lo, hi;
             uint8_t sfb;
-            requant_block16(h, gs2, codes[2 * ch], codes[2 * ch + 1], sfb);
-            sfw[ch >> 2] |= static_cast<uint32_t>(sfb) << (8 * (ch & 3));
-          }
-          if (valid) {
-            uint4* dst = reinterpret_cast<uint4*>(p.out_q + pos * (p.out_cols >> 1) +
-                                                  ((col0 + half * 128) >> 1));
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              dst[q] = make_uint4(codes[4 * q], codes[4 * q + 1], codes[4 * q + 2], codes[4 * q + 3]);
+            requant_block16(h, gs2, lo, hi, sfb);
+            if (valid) *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
+            if (ch < 4) sfw[0] |= static_cast<uint32_t>(sfb) << (8 * ch);
+            else sfw[1] |= static_cast<uint32_t>(sfb) << (8 * (ch - 4));
           }
           *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 16 + half * 8)) = sfw[0];
           *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 16 + half * 8 + 4)) = sfw[1];
@@ -369,12 +377,12 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA,
         __syncwarp();
         if (lane == 0) mbar_arrive(&tail->tmem_empty);
       } else {
-        const int col0 = c.nt * 256;
+        const int col0 = c.nt * 256 + half * 128;
         float* orow = p.out_f32 + pos * p.out_cols + col0;
 #pragma unroll 1
-        for (int ch = 0; ch < 16; ++ch) {
+        for (int ch = 0; ch < 8; ++ch) {
           uint32_t rr[16];
-          tc_ld_32x32b_x16(t_lane + ch * 16, rr);
+          tc_ld_32x32b_x16(t_lane + half * 128 + ch * 16, rr);
           tc_wait_ld();
           if (valid && col0 + ch * 16 < p.out_cols) {
             float4* dst = reinterpret_cast<float4*>(orow + ch * 16);

@@ -42,6 +42,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="c2", choices=sorted(synth.SHAPES))
     ap.add_argument("--tokens", type=int, default=None, help="tokens per GPU (default: the workload's)")
+    ap.add_argument("--experts", type=int, default=None, help="override the expert count (small profiling cases)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-experts", type=int, default=8, help="experts in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -210,8 +211,14 @@ def config_of(shp, n_gpus: int) -> dict:
 def main():
     args = parse_args()
     shp = synth.shape(args.workload)
+    over = {}
     if args.tokens is not None:
-        shp = synth.shape(args.workload, tokens=args.tokens)
+        over["tokens"] = args.tokens
+    if args.experts is not None:
+        over["experts"] = args.experts
+        over["name"] = f"{shp.name}_e{args.experts}"
+    if over:
+        shp = synth.shape(args.workload, **over)
     if args.impl == "reference":
         run_reference(args, shp)
         return
