@@ -97,6 +97,8 @@ EXPORTS = {
     "b200moe_scratch_nbytes": ([C.POINTER(CapsC), C.POINTER(ScratchLayout)], C.c_int),
     "b200moe_route_topk": ([C.POINTER(RouteArgs), C.c_void_p], C.c_int),
     "b200moe_expert_sort": ([C.POINTER(SortArgs), C.c_void_p], C.c_int),
+    "b200moe_expert_sort_static": ([C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p], C.c_int),
     "b200moe_permute_quant_nvfp4": ([C.POINTER(QuantArgs), C.c_void_p], C.c_int),
     "b200moe_permute_quant_mxfp8": ([C.POINTER(QuantArgs), C.c_void_p], C.c_int),
     "b200moe_gather_rows": ([C.POINTER(GatherArgs), C.c_void_p], C.c_int),

@@ -297,3 +297,80 @@ extern "C" int b200moe_expert_sort(const b200moe_sort_args* a, void* stream) {
       reinterpret_cast<int32_t*>(base + L.inv_perm), L.mtile_cap);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
+
+// ------------------------------------------------------------------------------------------
+// b200moe_expert_sort_static: the same sort kernel, but the tables it needs besides its inputs
+// and outputs (status words, per-expert counts, tile tables) live in a fixed array that is part
+// of the library image instead of in memory the caller had to allocate.
+//
+// Who needs this: callers that must not, or cannot, obtain device memory at the point of the
+// call -- a serving process that handed the whole GPU to its own pool at start-up, code running
+// between a graph capture's begin and end, or a latency-critical loop that has to stay clear of
+// the allocator's device-wide synchronisation.  They pass only the routes in and the three
+// result arrays out.
+//
+// The array is one per GPU and shared by every call on that GPU: it still holds what the
+// previous call left there (the kernel rewrites everything it later reads, including the status
+// words, so nothing has to be cleared by the caller), and two calls whose kernels overlap on the
+// GPU -- different streams, no ordering between them -- race on it.  Every GPU on which the
+// library is loaded keeps these 32 KiB reserved until the process exits.
+//
+// The array's name is only a host-side handle, not an address a kernel could use; the device
+// address is looked up with cudaGetSymbolAddress the first time the entry point runs on a device
+// (with that device current) and cached per device.  Make that first call outside any stream
+// capture.  Nothing here calls cudaMalloc, cudaFree or any allocating routine.
+// ------------------------------------------------------------------------------------------
+namespace b200moe {
+constexpr int kStaticSortMaxRoutes = 65536;
+constexpr int kStaticSortMaxExperts = 1024;
+constexpr int kStaticSortMtileCap = kStaticSortMaxRoutes / 128 + kStaticSortMaxExperts;  // 1536
+constexpr int kStaticOffStatus = 0;                                        // int32 words
+constexpr int kStaticOffCounts = 16;
+constexpr int kStaticOffTileBase = kStaticOffCounts + kStaticSortMaxExperts;
+constexpr int kStaticOffMtileExpert = kStaticOffTileBase + kStaticSortMaxExperts + 8;
+constexpr int kStaticOffMtileRow0 = kStaticOffMtileExpert + kStaticSortMtileCap;
+constexpr int kStaticOffMtileRows = kStaticOffMtileRow0 + kStaticSortMtileCap;
+constexpr int kStaticSortWords = kStaticOffMtileRows + kStaticSortMtileCap;
+constexpr int kStaticSortBytes = 32 * 1024;
+static_assert(kStaticSortWords * 4 <= kStaticSortBytes, "static sort scratch too small");
+constexpr int kMaxDevices = 64;
+}  // namespace b200moe
+
+static __device__ __align__(256) unsigned char g_static_sort_scratch[b200moe::kStaticSortBytes];
+static int32_t* g_static_sort_ptr[b200moe::kMaxDevices] = {};
+
+extern "C" int b200moe_expert_sort_static(const int32_t* topk_ids, const int32_t* expert_map,
+                                          int32_t expert_map_len, int32_t num_tokens,
+                                          int32_t num_topk, int32_t num_experts,
+                                          int32_t* expert_offsets, int32_t* sorted_route_ids,
+                                          int32_t* inv_perm, void* stream) {
+  if (topk_ids == nullptr || expert_offsets == nullptr || sorted_route_ids == nullptr ||
+      inv_perm == nullptr || num_tokens < 0 || num_topk <= 0 || num_experts <= 0)
+    return B200MOE_EINVAL;
+  const long long rows64 = static_cast<long long>(num_tokens) * num_topk;
+  if (rows64 > kStaticSortMaxRoutes || num_experts > kStaticSortMaxExperts)
+    return B200MOE_ECAPACITY;  // beyond the fixed size of the built-in array
+  const int rows = static_cast<int>(rows64);
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200MOE_ECUDA;
+  if (g_static_sort_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_sort_scratch) != cudaSuccess || p == nullptr)
+      return B200MOE_ECUDA;
+    g_static_sort_ptr[dev] = static_cast<int32_t*>(p);
+  }
+  int32_t* w = g_static_sort_ptr[dev];
+  int nwarps = (rows + 31) / 32;
+  nwarps = nwarps < 1 ? 1 : (nwarps > 32 ? 32 : nwarps);
+  const size_t smem = (static_cast<size_t>(nwarps) * num_experts + 3 * static_cast<size_t>(num_experts) + 2) * 4;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(expert_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (32 * 1024 + 3 * 1024 + 2) * 4) != cudaSuccess)
+    return B200MOE_ECUDA;
+  expert_sort_kernel<<<1, nwarps * 32, smem, static_cast<cudaStream_t>(stream)>>>(
+      topk_ids, expert_map, expert_map_len, rows, num_experts, w + kStaticOffStatus,
+      w + kStaticOffCounts, expert_offsets, w + kStaticOffTileBase, w + kStaticOffMtileExpert,
+      w + kStaticOffMtileRow0, w + kStaticOffMtileRows, sorted_route_ids, inv_perm,
+      kStaticSortMtileCap);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}

@@ -128,6 +128,21 @@ typedef struct {
 } b200moe_sort_args;
 int b200moe_expert_sort(const b200moe_sort_args* a, void* stream);
 
+/* The same sort for callers that cannot hand over scratch memory.  It has no counterpart in the
+ * reference.  Inputs are the routes (and the optional expert map); outputs are the three arrays
+ * the caller passes: expert_offsets [num_experts + 1], sorted_route_ids [num_tokens * num_topk],
+ * inv_perm [num_tokens * num_topk].  Everything else the kernel needs sits in a 32 KiB array built
+ * into the library (held by every GPU that loads it, until exit), so the call allocates nothing.
+ * Limits: num_tokens * num_topk <= 65536 and num_experts <= 1024, otherwise B200MOE_ECAPACITY.
+ * The built-in array is shared by all calls on a GPU and keeps the previous call's contents; the
+ * kernel rewrites what it reads, but calls whose kernels can overlap on the GPU race on it.
+ * The first call on each device looks up the array's device address: make it before any stream
+ * capture, with the device current. */
+int b200moe_expert_sort_static(const int32_t* topk_ids, const int32_t* expert_map,
+                               int32_t expert_map_len, int32_t num_tokens, int32_t num_topk,
+                               int32_t num_experts, int32_t* expert_offsets,
+                               int32_t* sorted_route_ids, int32_t* inv_perm, void* stream);
+
 /* ---- stage 3: permute + activation quantisation ------------------------ */
 /* Replaces quantize_block_fp4 / quantize_block_fp8_mx as used by the dynamic
  * kernel's route/pack phase (b12x/moe/_shared/kernels/dynamic.py:3059-3850;
