@@ -155,6 +155,17 @@ class ExpertParallelMoE(_LayerBase):
         inp = synth.make_inputs(shp, seed=1000 + rank, device=dev, experts=e_local)
         return cls(shp, inp, prepare_experts(inp, dev), dev, rank, world)
 
+    @classmethod
+    def from_global(cls, full: synth.MoEInputs, dev, rank: int, world: int, tokens_per_rank: int):
+        """Shard a global problem: experts [rank*E/n, (rank+1)*E/n) and this rank's token slice."""
+        shp = replace(full.shape, tokens=tokens_per_rank)
+        e_local = shp.experts // world
+        local = synth.slice_experts(full, rank * e_local, (rank + 1) * e_local)
+        lo = rank * tokens_per_rank
+        local = replace(local, shape=shp, x=full.x[lo:lo + tokens_per_rank].contiguous(),
+                        router_logits=full.router_logits[lo:lo + tokens_per_rank].contiguous())
+        return cls(shp, local, prepare_experts(local, dev), dev, rank, world)
+
     def forward(self, x: torch.Tensor, logits: torch.Tensor, stage_timer=None) -> torch.Tensor:
         self.route(logits)
         if self.world == 1:
@@ -213,6 +224,13 @@ class TensorParallelMoE(_LayerBase):
         inp.x, inp.router_logits = rep.x, rep.router_logits
         inp.shape = shp
         return cls(shp, inp, prepare_experts(inp, dev), dev, rank, world)
+
+    @classmethod
+    def from_global(cls, full: synth.MoEInputs, dev, rank: int, world: int):
+        """Shard a global problem on the intermediate dimension; tokens and routing replicated."""
+        local = synth.slice_intermediate(full, rank, world)
+        local = replace(local, shape=full.shape)
+        return cls(full.shape, local, prepare_experts(local, dev), dev, rank, world)
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, stage_timer=None) -> torch.Tensor:
         self.route(logits)

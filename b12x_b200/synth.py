@@ -213,3 +213,50 @@ def make_inputs(shp: MoEShape, *, seed: int = 0, device: str | torch.device = "c
         a1 = torch.ones(e, dtype=torch.float32, device=dev)
         a2 = torch.ones(e, dtype=torch.float32, device=dev)
     return MoEInputs(shp, x, logits, bias, w1, s1, g1, w2, s2, g2, a1, a2)
+
+
+# ---------------------------------------------------------------------------------------------
+# sharding of a global problem (what a model loader does for expert / tensor parallelism)
+# ---------------------------------------------------------------------------------------------
+def unswizzle_block_scale(sw: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
+    rp, cp = (rows + 127) // 128 * 128, (cols + 3) // 4 * 4
+    u = sw.reshape(-1)[: rp * cp].reshape(rp // 128, cp // 4, 32, 4, 4).permute(0, 3, 2, 1, 4)
+    return u.contiguous().reshape(rp, cp)[:rows, :cols]
+
+
+def slice_experts(inp: MoEInputs, lo: int, hi: int) -> MoEInputs:
+    """The experts [lo, hi) of ``inp`` (an expert-parallel rank's share); tokens unchanged."""
+    return replace(inp, w1_fp4=inp.w1_fp4[lo:hi].contiguous(), w1_blockscale=inp.w1_blockscale[lo:hi].contiguous(),
+                   w1_global_scale=inp.w1_global_scale[lo:hi].contiguous(), w2_fp4=inp.w2_fp4[lo:hi].contiguous(),
+                   w2_blockscale=inp.w2_blockscale[lo:hi].contiguous(),
+                   w2_global_scale=inp.w2_global_scale[lo:hi].contiguous(),
+                   a1_gscale=inp.a1_gscale[lo:hi].contiguous(), a2_gscale=inp.a2_gscale[lo:hi].contiguous())
+
+
+def slice_intermediate(inp: MoEInputs, rank: int, world: int) -> MoEInputs:
+    """Tensor-parallel shard ``rank`` of ``world``: FC1 rows [r*I/n, (r+1)*I/n) of both halves and the
+    matching FC2 columns, block scales re-laid for the shard (b12x/moe/__init__.py:3-8)."""
+    shp = inp.shape
+    i, k = shp.intermediate, shp.hidden
+    il = i // world
+    lo, hi = rank * il, (rank + 1) * il
+    gated = shp.activation != "relu2"
+    mx = shp.recipe == "w4a8_mx"
+    g = 32 if mx else 16
+    e = inp.w1_fp4.shape[0]
+    rows1 = [slice(lo, hi), slice(i + lo, i + hi)] if gated else [slice(lo, hi)]
+    w1 = torch.cat([inp.w1_fp4[:, r] for r in rows1], dim=1).contiguous()
+    w2 = inp.w2_fp4[:, :, lo // 2: hi // 2].contiguous()
+    if mx:
+        s1 = torch.cat([inp.w1_blockscale[:, r] for r in rows1], dim=1).contiguous()
+        s2 = inp.w2_blockscale[:, :, lo // g: hi // g].contiguous()
+    else:
+        w1_rows = inp.w1_fp4.shape[1]
+        s1l, s2l = [], []
+        for ei in range(e):
+            u1 = unswizzle_block_scale(inp.w1_blockscale[ei], w1_rows, k // g)
+            s1l.append(swizzle_block_scale(torch.cat([u1[r] for r in rows1], dim=0).contiguous()))
+            u2 = unswizzle_block_scale(inp.w2_blockscale[ei], k, i // g)
+            s2l.append(swizzle_block_scale(u2[:, lo // g: hi // g].contiguous()))
+        s1, s2 = torch.stack(s1l), torch.stack(s2l)
+    return replace(inp, shape=replace(shp, intermediate=il), w1_fp4=w1, w1_blockscale=s1, w2_fp4=w2, w2_blockscale=s2)
