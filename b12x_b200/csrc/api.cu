@@ -63,7 +63,7 @@ extern "C" int b200moe_scratch_nbytes(const b200moe_caps* c, b200moe_scratch_lay
       break;
     case B200MOE_RECIPE_W4A16:
       if (K % 32 != 0 || I % 32 != 0) return B200MOE_EINVAL;
-      act_row = 0; mid_row = I * 2;   // bf16 intermediate, A of FC1 is gathered from x
+      act_row = K * 2; mid_row = I * 2;   // bf16 rows in sorted order, bf16 intermediate
       break;
     default:
       return B200MOE_EINVAL;

@@ -45,6 +45,10 @@ constexpr int kGemmSmemBytes =
     1024 + kStages * (kSmemA + kSmemB + kSmemSfa + kSmemSfb) + static_cast<int>(sizeof(GemmSmemTail));
 
 enum { EPI_FC1_GATED = 0, EPI_FC1_RELU2 = 1, EPI_FC2 = 2 };
+// KIND_NVFP4: A and B packed E2M1, E4M3 scale per 16, kind::mxf4nvf4 (K = 64 per MMA, 256 per stage).
+// KIND_MX:    A E4M3 bytes, B E2M1 expanded by TMA to one value per byte slot, E8M0 scale per 32,
+//             kind::mxf8f6f4 (K = 32 per MMA, 128 per stage; one scale atom per stage).
+enum { KIND_NVFP4 = 0, KIND_MX = 1 };
 
 struct GemmParams {
   const uint8_t* sfa;            // activation scale atoms [mtile][atoms_k][512]
@@ -62,6 +66,7 @@ struct GemmParams {
   float* tap;                    // FC1 debug tap [rows][w_rows] or null
   int E, n_tiles, kdim, k_blocks, atoms_k;
   int sfb_rowgroups;             // per expert
+  int sfb_rg0, sfb_rg1, rg_step; // scale row-group of the two sub-tiles at n-tile 0, step per n-tile
   int w_rows;                    // weight rows per expert
   int sub0_base, sub1_base;      // first weight row of the two sub-tiles at n-tile 0
   int n_step;                    // weight rows advanced per n-tile
@@ -147,9 +152,33 @@ __device__ __forceinline__ void requant_block16(const float (&v)[16], float gs, 
   }
 }
 
-template <int EPI>
+// MXFP8 quantisation of 32 values (b12x/_lib/intrinsics.py:223-265): E8M0 byte = exponent of
+// pow2_ceil(amax / 448), payload = e4m3_rn_sat(x * 2^(127 - byte)).
+__device__ __forceinline__ void requant_block32_mx(const float (&v)[32], uint32_t (&o)[8],
+                                                   uint8_t& sf_byte) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  uint32_t bits = __float_as_uint(__fmul_rn(amax, static_cast<float>(1.0 / 448.0)));
+  if (bits & 0x007fffffu) bits = (bits + 0x00800000u) & 0x7f800000u;
+  sf_byte = static_cast<uint8_t>((bits >> 23) & 0xffu);
+  const int ex = 254 - static_cast<int>(sf_byte);
+  const float inv = sf_byte == 0 ? 0.f : __uint_as_float(static_cast<uint32_t>(ex < 0 ? 0 : ex) << 23);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint32_t acc = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float q = fminf(fmaxf(__fmul_rn(v[4 * j + k], inv), -448.f), 448.f);
+      acc |= static_cast<uint32_t>(f32_to_e4m3_rn_sat(q)) << (8 * k);
+    }
+    o[j] = acc;
+  }
+}
+
+template <int KIND, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA,
+grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
                           const __grid_constant__ CUtensorMap tmA_small,
                           const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -182,6 +211,8 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA,
   __syncthreads();
   tc_fence_after();
 
+  constexpr int kPerStage = KIND == KIND_MX ? 128 : kKPerStage;
+  constexpr int kPerMma = KIND == KIND_MX ? 32 : kKPerMma;
   const uint32_t tmem_base = tail->tmem_base;
   volatile int* abort_flag = &tail->abort_flag;
   const int total_work = tail->tile_base[p.E] * p.n_tiles;
@@ -205,30 +236,38 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA,
         const uint32_t a_bytes = (small_a ? 32u : 128u) * kRowBytes;
         const int r0 = p.sub0_base + c.nt * p.n_step;   // weight row inside the expert
         int r1 = p.sub1_base + c.nt * p.n_step;
-        if (r1 >= p.w_rows) r1 = r0;                    // half-empty last tile: reload sub-tile 0
+        const int rg0 = p.sfb_rg0 + c.nt * p.rg_step;
+        int rg1 = p.sfb_rg1 + c.nt * p.rg_step;
+        if (r1 >= p.w_rows) {                           // half-empty last tile: reload sub-tile 0
+          r1 = r0;
+          rg1 = rg0;
+        }
         const uint8_t* sfa_src = p.sfa + static_cast<size_t>(c.mt) * p.atoms_k * 512;
         const uint8_t* sfb0 =
-            p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + (r0 >> 7)) * p.atoms_k * 512;
+            p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + rg0) * p.atoms_k * 512;
         const uint8_t* sfb1 =
-            p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + (r1 >> 7)) * p.atoms_k * 512;
+            p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + rg1) * p.atoms_k * 512;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status,
                                  WAIT_SMEM_EMPTY)) {
             ok = false;
             break;
           }
-          const int ksteps = min(4, (p.kdim - kb * kKPerStage) / kKPerMma);
-          const uint32_t sf_bytes = static_cast<uint32_t>(ksteps) * 512u;
+          const int ksteps = min(4, (p.kdim - kb * kPerStage) / kPerMma);
+          // NVFP4: one scale atom per MMA step; MX: one atom covers the whole stage
+          const uint32_t sf_bytes = KIND == KIND_MX ? 512u : static_cast<uint32_t>(ksteps) * 512u;
+          const size_t sf_off = static_cast<size_t>(kb) * (KIND == KIND_MX ? 512 : 2048);
+          // the unpacking TMA type counts the packed bytes it reads (64 per 128-value row)
+          const uint32_t b_bytes = KIND == KIND_MX ? kSmemB / 2 : kSmemB;
           uint64_t* bar = &tail->full[stage];
-          mbar_expect_tx(bar, a_bytes + kSmemB + 3u * sf_bytes);
+          mbar_expect_tx(bar, a_bytes + b_bytes + 3u * sf_bytes);
           tma_load_2d(sA + stage * kSmemA, tma_a, bar, kb * kRowBytes, row0);
           tma_load_2d(sB + stage * kSmemB, &tmB, bar, kb * kRowBytes, c.e * p.w_rows + r0);
           tma_load_2d(sB + stage * kSmemB + kSmemB / 2, &tmB, bar, kb * kRowBytes,
                       c.e * p.w_rows + r1);
-          bulk_load(sSfa + stage * kSmemSfa, sfa_src + static_cast<size_t>(kb) * 2048, sf_bytes, bar);
-          bulk_load(sSfb + stage * kSmemSfb, sfb0 + static_cast<size_t>(kb) * 2048, sf_bytes, bar);
-          bulk_load(sSfb + stage * kSmemSfb + 2048, sfb1 + static_cast<size_t>(kb) * 2048, sf_bytes,
-                    bar);
+          bulk_load(sSfa + stage * kSmemSfa, sfa_src + sf_off, sf_bytes, bar);
+          bulk_load(sSfb + stage * kSmemSfb, sfb0 + sf_off, sf_bytes, bar);
+          bulk_load(sSfb + stage * kSmemSfb + 2048, sfb1 + sf_off, sf_bytes, bar);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -243,7 +282,9 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA,
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_block_scaled(kBM, kBN, /*a*/ 1, /*b*/ 1, /*ue4m3*/ 0);
+      constexpr uint32_t idesc =
+          KIND == KIND_MX ? make_idesc_block_scaled(kBM, kBN, /*a e4m3*/ 0, /*b e2m1*/ 5, /*ue8m0*/ 1)
+                          : make_idesc_block_scaled(kBM, kBN, /*a*/ 1, /*b*/ 1, /*ue4m3*/ 0);
       int stage = 0;
       uint32_t phase = 0, tile_phase = 0;
       bool ok = true;
@@ -260,22 +301,35 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA,
             break;
           }
           tc_fence_after();
-          const int ksteps = min(4, (p.kdim - kb * kKPerStage) / kKPerMma);
+          const int ksteps = min(4, (p.kdim - kb * kPerStage) / kPerMma);
           const uint32_t sfa_t = tmem_base + kTmemSfa + stage * 16;
           const uint32_t sfb_t = tmem_base + kTmemSfb + stage * 32;
           const uint32_t sfa_s = smem_u32(sSfa + stage * kSmemSfa);
           const uint32_t sfb_s = smem_u32(sSfb + stage * kSmemSfb);
-          for (int j = 0; j < ksteps; ++j) {
-            tc_cp_32x128b_warpx4(sfa_t + 4 * j, make_desc_sf(sfa_s + 512 * j));
-            tc_cp_32x128b_warpx4(sfb_t + 8 * j, make_desc_sf(sfb_s + 512 * j));
-            tc_cp_32x128b_warpx4(sfb_t + 8 * j + 4, make_desc_sf(sfb_s + 2048 + 512 * j));
-          }
           const uint64_t adesc = make_desc_sw128(smem_u32(sA + stage * kSmemA));
           const uint64_t bdesc = make_desc_sw128(smem_u32(sB + stage * kSmemB));
-          for (int j = 0; j < ksteps; ++j) {
-            // 64 FP4 values = 32 bytes further along the swizzled row -> +2 in 16-byte units
-            mma_nvf4_4x(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j, sfb_t + 8 * j,
-                        (kb > 0 || j > 0) ? 1u : 0u);
+          if (KIND == KIND_MX) {
+            // one atom = the four per-32 scales of this stage; MMA step j uses byte j of each word
+            tc_cp_32x128b_warpx4(sfa_t, make_desc_sf(sfa_s));
+            tc_cp_32x128b_warpx4(sfb_t, make_desc_sf(sfb_s));
+            tc_cp_32x128b_warpx4(sfb_t + 4, make_desc_sf(sfb_s + 2048));
+            for (int j = 0; j < ksteps; ++j) {
+              const uint32_t ju = static_cast<uint32_t>(j);
+              // 32 one-byte slots further along the swizzled row -> +2 in 16-byte units
+              mma_mxf8f6f4(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc | (ju << 29) | (ju << 4),
+                           sfa_t + (ju << 30), sfb_t + (ju << 30), (kb > 0 || j > 0) ? 1u : 0u);
+            }
+          } else {
+            for (int j = 0; j < ksteps; ++j) {
+              tc_cp_32x128b_warpx4(sfa_t + 4 * j, make_desc_sf(sfa_s + 512 * j));
+              tc_cp_32x128b_warpx4(sfb_t + 8 * j, make_desc_sf(sfb_s + 512 * j));
+              tc_cp_32x128b_warpx4(sfb_t + 8 * j + 4, make_desc_sf(sfb_s + 2048 + 512 * j));
+            }
+            for (int j = 0; j < ksteps; ++j) {
+              // 64 FP4 values = 32 bytes further along the swizzled row -> +2 in 16-byte units
+              mma_nvf4_4x(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j,
+                          sfb_t + 8 * j, (kb > 0 || j > 0) ? 1u : 0u);
+            }
           }
           tc_commit(&tail->empty[stage]);
           if (++stage == kStages) {
@@ -308,7 +362,90 @@ grouped_gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA,
       const bool valid = m < nrows;
       const size_t pos = static_cast<size_t>(row0 + m);
 
-      if (EPI == EPI_FC1_GATED) {
+      if (KIND == KIND_MX && EPI == EPI_FC1_GATED) {
+        // w4a8_mx: the activation output goes straight into the MXFP8 quantiser (no bf16 staging)
+        const int col0 = c.nt * 128 + half * 64;
+        uint8_t* qrow = p.out_q + pos * p.out_cols + col0;
+        uint32_t sfw = 0u;
+        const bool cols_ok = col0 < p.out_cols;
+#pragma unroll 1
+        for (int blk = 0; blk < 2; ++blk) {
+          float h[32];
+#pragma unroll
+          for (int c2 = 0; c2 < 2; ++c2) {
+            uint32_t ru[16], rg[16];
+            tc_ld_32x32b_x16(t_lane + half * 64 + blk * 32 + c2 * 16, ru);
+            tc_ld_32x32b_x16(t_lane + 128 + half * 64 + blk * 32 + c2 * 16, rg);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float up = __fmul_rn(__uint_as_float(ru[i]), alpha);
+              const float gate = __fmul_rn(__uint_as_float(rg[i]), alpha);
+              if (p.tap != nullptr && valid && cols_ok) {
+                float* trow = p.tap + pos * p.w_rows;
+                trow[p.sub0_base + col0 + blk * 32 + c2 * 16 + i] = up;
+                trow[p.sub1_base + col0 + blk * 32 + c2 * 16 + i] = gate;
+              }
+              h[c2 * 16 + i] = act_gated(gate, up, p);
+            }
+          }
+          uint32_t o[8];
+          uint8_t sfb;
+          requant_block32_mx(h, o, sfb);
+          if (valid && cols_ok) {
+            uint4* dst = reinterpret_cast<uint4*>(qrow + blk * 32);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          }
+          sfw |= static_cast<uint32_t>(sfb) << (8 * blk);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->tmem_empty);
+        if (cols_ok) {
+          uint8_t* sft = p.out_sf + static_cast<size_t>(c.mt) * p.out_atoms * 512;
+          *reinterpret_cast<uint16_t*>(sft + sf_atom_offset(m, c.nt * 4 + half * 2)) =
+              static_cast<uint16_t>(sfw);
+        }
+      } else if (KIND == KIND_MX && EPI == EPI_FC1_RELU2) {
+        const int col0 = c.nt * 256 + half * 128;
+        if (col0 < p.out_cols) {
+          uint8_t* qrow = p.out_q + pos * p.out_cols + col0;
+          uint32_t sfw = 0u;
+#pragma unroll 1
+          for (int blk = 0; blk < 4; ++blk) {
+            float h[32];
+#pragma unroll
+            for (int c2 = 0; c2 < 2; ++c2) {
+              uint32_t rr[16];
+              tc_ld_32x32b_x16(t_lane + half * 128 + blk * 32 + c2 * 16, rr);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const float v = __fmul_rn(__uint_as_float(rr[i]), alpha);
+                if (p.tap != nullptr && valid)
+                  p.tap[pos * p.w_rows + col0 + blk * 32 + c2 * 16 + i] = v;
+                const float r = fmaxf(v, 0.f);
+                h[c2 * 16 + i] = __fmul_rn(r, r);
+              }
+            }
+            uint32_t o[8];
+            uint8_t sfb;
+            requant_block32_mx(h, o, sfb);
+            if (valid && col0 + blk * 32 < p.out_cols) {
+              uint4* dst = reinterpret_cast<uint4*>(qrow + blk * 32);
+              dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+              dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+            }
+            sfw |= static_cast<uint32_t>(sfb) << (8 * blk);
+          }
+          uint8_t* sft = p.out_sf + static_cast<size_t>(c.mt) * p.out_atoms * 512;
+          *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 8 + half * 4)) = sfw;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->tmem_empty);
+      } else if (EPI == EPI_FC1_GATED) {
         const float gs2 = p.gscale2[p.gscale_len > 1 ? c.e : 0];
         const int col0 = c.nt * 128 + half * 64;   // first intermediate column of this warp
         uint8_t* qrow = p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1);
@@ -456,10 +593,10 @@ static int num_sms_cached() {
   return n;
 }
 
-template <int EPI>
-static int launch_nvfp4(const CUtensorMap& tmA, const CUtensorMap& tmA_small,
-                        const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t s) {
-  auto kern = grouped_gemm_nvfp4_kernel<EPI>;
+template <int KIND, int EPI>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmA_small,
+                       const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t s) {
+  auto kern = grouped_gemm_blockscaled_kernel<KIND, EPI>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes) !=
       cudaSuccess)
     return B200MOE_ECUDA;
@@ -513,13 +650,19 @@ int nvfp4_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
     p.n_step = 128;
     p.sub0_base = a->gate_first ? I : 0;   // sub-tile 0 = up rows
     p.sub1_base = a->gate_first ? 0 : I;   // sub-tile 1 = gate rows
-    return launch_nvfp4<EPI_FC1_GATED>(tmA, tmA_small, tmB, p, grid, stream);
+    p.sfb_rg0 = p.sub0_base / 128;
+    p.sfb_rg1 = p.sub1_base / 128;
+    p.rg_step = 1;
+    return launch_gemm<KIND_NVFP4, EPI_FC1_GATED>(tmA, tmA_small, tmB, p, grid, stream);
   }
   p.n_tiles = ceil_div_i(I, 256);
   p.n_step = 256;
   p.sub0_base = 0;
   p.sub1_base = 128;
-  return launch_nvfp4<EPI_FC1_RELU2>(tmA, tmA_small, tmB, p, grid, stream);
+  p.sfb_rg0 = 0;
+  p.sfb_rg1 = 1;
+  p.rg_step = 2;
+  return launch_gemm<KIND_NVFP4, EPI_FC1_RELU2>(tmA, tmA_small, tmB, p, grid, stream);
 }
 
 int nvfp4_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
@@ -555,8 +698,136 @@ int nvfp4_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
   p.n_step = 256;
   p.sub0_base = 0;
   p.sub1_base = 128;
+  p.sfb_rg0 = 0;
+  p.sfb_rg1 = 1;
+  p.rg_step = 2;
   const int grid = a->num_sms > 0 ? a->num_sms : num_sms_cached();
-  return launch_nvfp4<EPI_FC2>(tmA, tmA_small, tmB, p, grid, stream);
+  return launch_gemm<KIND_NVFP4, EPI_FC2>(tmA, tmA_small, tmB, p, grid, stream);
+}
+
+// 2-D matrix of packed E2M1 values [rows][cols/2 bytes]; the TMA expands every 16 values (8 bytes)
+// to a 16-byte slot, which is the operand form kind::mxf8f6f4 reads.  Box = box_rows x 128 values.
+// The inner extent is declared rounded up to 128 values (a requirement of this TMA type); the
+// columns beyond the real row are never multiplied (the K loop stops at the real K).
+int make_tmap_fp4_unpack_2d(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows,
+                            uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return B200MOE_ECUDA;
+  const uint64_t row_bytes = cols / 2;
+  if ((reinterpret_cast<uintptr_t>(base) & 31) != 0 || (row_bytes & 31) != 0) return B200MOE_EALIGN;
+  const cuuint64_t dims[2] = {(cols + 127) / 128 * 128, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {128, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+static void fill_common(GemmParams& p, const b200moe_gemm_args* a, char* base) {
+  const b200moe_scratch_layout& L = *a->layout;
+  p.tile_base = reinterpret_cast<const int32_t*>(base + L.tile_base);
+  p.mtile_expert = reinterpret_cast<const int32_t*>(base + L.mtile_expert);
+  p.mtile_row0 = reinterpret_cast<const int32_t*>(base + L.mtile_row0);
+  p.mtile_rows = reinterpret_cast<const int32_t*>(base + L.mtile_rows);
+  p.status = reinterpret_cast<int32_t*>(base + L.status);
+  p.E = a->num_experts;
+  p.gscale_len = a->gscale_len;
+  p.limit = a->swiglu_limit;
+  p.act_alpha = a->swiglu_alpha;
+  p.act_beta = a->swiglu_beta;
+  p.swigluoai = a->activation == B200MOE_ACT_SWIGLUOAI;
+}
+
+// w4a8_mx FC1.  Weight scales: E8M0 atoms [E][row-groups][ceil(K/128)][512] where, for a gated
+// activation, each half of W13 is padded to a multiple of 128 rows on its own (prepare_weights
+// builds this), so that every 128-row sub-tile starts on an atom boundary even when I % 128 != 0.
+int mx_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
+  const b200moe_scratch_layout& L = *a->layout;
+  const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
+  const bool gated = a->activation != B200MOE_ACT_RELU2;
+  if (K % 64 != 0 || I % 32 != 0 || E > kMaxExperts || a->w13_sf == nullptr) return B200MOE_EINVAL;
+  const int w_rows = gated ? 2 * I : I;
+  const int half_groups = ceil_div_i(I, 128);
+  char* base = static_cast<char*>(a->scratch);
+  CUtensorMap tmA, tmA_small, tmB;
+  int rc = make_tmap_bytes_2d(&tmA, base + L.act_q, K, L.rows, 128);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_tmap_bytes_2d(&tmA_small, base + L.act_q, K, L.rows, 32);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_tmap_fp4_unpack_2d(&tmB, a->w13, K, static_cast<uint64_t>(E) * w_rows, 128);
+  if (rc != B200MOE_OK) return rc;
+  GemmParams p = {};
+  fill_common(p, a, base);
+  p.sfa = reinterpret_cast<const uint8_t*>(base + L.act_sf);
+  p.sfb = a->w13_sf;
+  p.alphas = a->w1_alphas;
+  p.out_q = reinterpret_cast<uint8_t*>(base + L.mid_q);
+  p.out_sf = reinterpret_cast<uint8_t*>(base + L.mid_sf);
+  p.tap = a->fc1_tap;
+  p.kdim = K;
+  p.k_blocks = ceil_div_i(K, 128);
+  p.atoms_k = ceil_div_i(K, 128);
+  p.w_rows = w_rows;
+  p.out_cols = I;
+  p.out_atoms = ceil_div_i(I, 128);
+  const int grid = a->num_sms > 0 ? a->num_sms : num_sms_cached();
+  if (gated) {
+    p.sfb_rowgroups = 2 * half_groups;
+    p.n_tiles = half_groups;
+    p.n_step = 128;
+    p.sub0_base = a->gate_first ? I : 0;
+    p.sub1_base = a->gate_first ? 0 : I;
+    p.sfb_rg0 = a->gate_first ? half_groups : 0;
+    p.sfb_rg1 = a->gate_first ? 0 : half_groups;
+    p.rg_step = 1;
+    return launch_gemm<KIND_MX, EPI_FC1_GATED>(tmA, tmA_small, tmB, p, grid, stream);
+  }
+  p.sfb_rowgroups = half_groups;
+  p.n_tiles = ceil_div_i(I, 256);
+  p.n_step = 256;
+  p.sub0_base = 0;
+  p.sub1_base = 128;
+  p.sfb_rg0 = 0;
+  p.sfb_rg1 = 1;
+  p.rg_step = 2;
+  return launch_gemm<KIND_MX, EPI_FC1_RELU2>(tmA, tmA_small, tmB, p, grid, stream);
+}
+
+int mx_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
+  const b200moe_scratch_layout& L = *a->layout;
+  const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
+  if (I % 64 != 0 || K % 16 != 0 || E > kMaxExperts || a->w2_sf == nullptr) return B200MOE_EINVAL;
+  char* base = static_cast<char*>(a->scratch);
+  CUtensorMap tmA, tmA_small, tmB;
+  int rc = make_tmap_bytes_2d(&tmA, base + L.mid_q, I, L.rows, 128);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_tmap_bytes_2d(&tmA_small, base + L.mid_q, I, L.rows, 32);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_tmap_fp4_unpack_2d(&tmB, a->w2, I, static_cast<uint64_t>(E) * K, 128);
+  if (rc != B200MOE_OK) return rc;
+  GemmParams p = {};
+  fill_common(p, a, base);
+  p.sfa = reinterpret_cast<const uint8_t*>(base + L.mid_sf);
+  p.sfb = a->w2_sf;
+  p.alphas = a->w2_alphas;
+  p.out_f32 = reinterpret_cast<float*>(base + L.routed);
+  p.kdim = I;
+  p.k_blocks = ceil_div_i(I, 128);
+  p.atoms_k = ceil_div_i(I, 128);
+  p.w_rows = K;
+  p.sfb_rowgroups = ceil_div_i(K, 128);
+  p.out_cols = K;
+  p.n_tiles = ceil_div_i(K, 256);
+  p.n_step = 256;
+  p.sub0_base = 0;
+  p.sub1_base = 128;
+  p.sfb_rg0 = 0;
+  p.sfb_rg1 = 1;
+  p.rg_step = 2;
+  const int grid = a->num_sms > 0 ? a->num_sms : num_sms_cached();
+  return launch_gemm<KIND_MX, EPI_FC2>(tmA, tmA_small, tmB, p, grid, stream);
 }
 
 }  // namespace b200moe

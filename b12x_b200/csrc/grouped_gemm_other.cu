@@ -1,9 +1,587 @@
-// Grouped GEMMs of the w4a8_mx and w4a16 recipes.
+// Grouped expert GEMMs of the w4a16 recipe: BF16 activations x NVFP4 weights that are expanded to
+// BF16 on the fly, on tcgen05.mma.kind::f16 with FP32 accumulation in TMEM.
+//
+// The tensor core cannot read 4-bit operands next to 16-bit ones, so each pipeline stage has a
+// conversion step: the TMA producer lands the packed codes (128 rows x 32 bytes per sub-tile) and the
+// E4M3 scale atoms in a staging area, eight converter warps expand them to BF16 (code value x block
+// scale is exact in BF16: 2 + 4 significant bits) straight into the 128-byte-swizzled operand tile
+// the MMA reads, and hand the stage to the MMA warp through an mbarrier.  The accumulator is double
+// buffered in TMEM (2 x 256 columns), so the epilogue of one tile overlaps the main loop of the next.
+//
+// Numerics follow the reference's W4A16 oracle (tests/_reference/w4a16_reference.py:266-359):
+// weights de-quantised then held in BF16, x in BF16, FP32 accumulation, activation in FP32, BF16
+// intermediate.
 #include "common.cuh"
 
 namespace b200moe {
-int mx_gemm1(const b200moe_gemm_args*, cudaStream_t) { return B200MOE_EUNSUPPORTED; }
-int mx_gemm2(const b200moe_gemm_args*, cudaStream_t) { return B200MOE_EUNSUPPORTED; }
-int w4a16_gemm1(const b200moe_gemm_args*, cudaStream_t) { return B200MOE_EUNSUPPORTED; }
-int w4a16_gemm2(const b200moe_gemm_args*, cudaStream_t) { return B200MOE_EUNSUPPORTED; }
+
+int make_tmap_bytes_2d(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,
+                       uint32_t box_rows);
+
+namespace w4a16 {
+
+constexpr int kStages = 3;
+constexpr int kKPerStage = 64;              // BF16 elements per 128-byte operand row
+constexpr int kThreads = 18 * 32;           // TMA, MMA, 8 converter warps, 8 epilogue warps
+constexpr int kSmemA = 128 * 128;           // 16 KiB
+constexpr int kSmemB = 256 * 128;           // 32 KiB
+constexpr int kSmemRaw = 2 * 128 * 32;      // packed codes of the two sub-tiles
+constexpr int kSmemSf = 4 * 512;            // two scale atoms per sub-tile (a sub-tile may straddle)
+constexpr int kStageBytes = kSmemA + kSmemB + kSmemRaw + kSmemSf;
+constexpr int kMaxExperts = 1024;
+
+struct __align__(8) SmemTail {
+  uint64_t full[kStages];
+  uint64_t conv[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int32_t tile_base[kMaxExperts + 1];
+};
+constexpr int kSmemBytes = 1024 + kStages * kStageBytes + static_cast<int>(sizeof(SmemTail));
+
+enum { EPI_FC1_GATED = 0, EPI_FC1_RELU2 = 1, EPI_FC2 = 2 };
+
+struct Params {
+  const uint8_t* sf;             // weight scale storage, 128x4-swizzled [E][sf_rowgroups][atoms_k][512]
+  const int32_t* tile_base;
+  const int32_t* mtile_row0;
+  const int32_t* mtile_rows;
+  int32_t* status;
+  const float* alphas;
+  __nv_bfloat16* out_bf16;       // FC1: intermediate [rows][out_cols]
+  float* out_f32;                // FC2: routed rows [rows][out_cols]
+  float* tap;
+  int E, n_tiles, kdim, k_blocks, atoms_k, sf_rowgroups, w_rows;
+  int sub0_base, sub1_base, n_step, out_cols;
+  float limit, act_alpha, act_beta;
+  int swigluoai;
+};
+
+struct TileCoord {
+  int e, mt, nt;
+};
+__device__ __forceinline__ TileCoord decode_tile(int w, int n_tiles, const int32_t* tb, int E) {
+  const int q = w / n_tiles;
+  int lo = 0, hi = E;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (tb[mid + 1] <= q) lo = mid + 1; else hi = mid;
+  }
+  TileCoord c;
+  c.e = lo;
+  const int me = tb[lo + 1] - tb[lo];
+  const int local = w - tb[lo] * n_tiles;
+  c.nt = local / me;
+  c.mt = tb[lo] + local % me;
+  return c;
+}
+
+__device__ __forceinline__ float act_gated(float gate, float up, const Params& p) {
+  if (p.limit > 0.f) {
+    gate = fminf(gate, p.limit);
+    up = fminf(fmaxf(up, -p.limit), p.limit);
+  }
+  if (p.swigluoai) {
+    const float s = __frcp_rn(1.0f + expf(-(p.act_alpha * gate)));
+    return (gate * s) * (up + p.act_beta);
+  }
+  const float s = __frcp_rn(1.0f + expf(-gate));
+  return (gate * s) * up;
+}
+
+// Eight E2M1 codes (one 32-bit word, element 0 in the low nibble) -> four bf16x2 words, each value
+// multiplied by the bf16 scale pair `sc`.  The magnitude (3 bits) indexes two 8-entry byte tables
+// with prmt; the sign bit is moved to bit 15 of each half.
+__device__ __forceinline__ void cvt_e2m1x8_bf16(uint32_t w, __nv_bfloat162 sc, uint32_t (&out)[4]) {
+  // bf16 of {0, .5, 1, 1.5, 2, 3, 4, 6}: 0000 3F00 3F80 3FC0 4000 4040 4080 40C0
+  constexpr uint32_t kHiA = 0x3F3F3F00u, kHiB = 0x40404040u;   // high bytes, entries 0-3 / 4-7
+  constexpr uint32_t kLoA = 0xC0800000u, kLoB = 0xC0804000u;   // low bytes
+  const uint32_t sel0 = w & 0x7777u, sel1 = (w >> 16) & 0x7777u;
+  const uint32_t hi0 = __byte_perm(kHiA, kHiB, sel0), lo0 = __byte_perm(kLoA, kLoB, sel0);
+  const uint32_t hi1 = __byte_perm(kHiA, kHiB, sel1), lo1 = __byte_perm(kLoA, kLoB, sel1);
+  uint32_t v[4];
+  v[0] = __byte_perm(lo0, hi0, 0x5140);   // elements 0,1
+  v[1] = __byte_perm(lo0, hi0, 0x7362);   // elements 2,3
+  v[2] = __byte_perm(lo1, hi1, 0x5140);   // elements 4,5
+  v[3] = __byte_perm(lo1, hi1, 0x7362);   // elements 6,7
+  // sign bits: nibble bit 3 of element 2j -> bit 15, of element 2j+1 -> bit 31
+  v[0] |= ((w << 12) & 0x8000u) | ((w << 24) & 0x80000000u);
+  v[1] |= ((w << 4) & 0x8000u) | ((w << 16) & 0x80000000u);
+  v[2] |= ((w >> 4) & 0x8000u) | ((w << 8) & 0x80000000u);
+  v[3] |= ((w >> 12) & 0x8000u) | (w & 0x80000000u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&v[j]);
+    x = __hmul2(x, sc);
+    out[j] = *reinterpret_cast<uint32_t*>(&x);
+  }
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
+                          const __grid_constant__ CUtensorMap tmW, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + kStages * kSmemA;
+  uint8_t* sRaw = sB + kStages * kSmemB;
+  uint8_t* sSf = sRaw + kStages * kSmemRaw;
+  SmemTail* tail = reinterpret_cast<SmemTail*>(sSf + kStages * kSmemSf);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->conv[s], 8);
+      mbar_init(&tail->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tail->tmem_full[b], 1);
+      mbar_init(&tail->tmem_empty[b], 8);
+    }
+    tail->abort_flag = 0;
+    fence_mbar_init();
+  }
+  for (int i = threadIdx.x; i <= p.E; i += blockDim.x) tail->tile_base[i] = p.tile_base[i];
+  if (warp == 1) {
+    tmem_alloc(&tail->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  const uint32_t tmem_base = tail->tmem_base;
+  volatile int* abort_flag = &tail->abort_flag;
+  const int total_work = tail->tile_base[p.E] * p.n_tiles;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmW);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
+        const int row0 = p.mtile_row0[c.mt];
+        const int r0 = p.sub0_base + c.nt * p.n_step;
+        int r1 = p.sub1_base + c.nt * p.n_step;
+        if (r1 >= p.w_rows) r1 = r0;
+        const uint8_t* sf_e = p.sf + static_cast<size_t>(c.e) * p.sf_rowgroups * p.atoms_k * 512;
+        // a 128-row sub-tile starting at row r touches scale row-groups r/128 and (r+127)/128
+        const int g[4] = {r0 >> 7, min((r0 + 127) >> 7, p.sf_rowgroups - 1), r1 >> 7,
+                          min((r1 + 127) >> 7, p.sf_rowgroups - 1)};
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status,
+                                 WAIT_SMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint64_t* bar = &tail->full[stage];
+          mbar_expect_tx(bar, kSmemA + kSmemRaw + kSmemSf);
+          tma_load_2d(sA + stage * kSmemA, &tmA, bar, kb * kKPerStage, row0);
+          tma_load_2d(sRaw + stage * kSmemRaw, &tmW, bar, kb * 32, c.e * p.w_rows + r0);
+          tma_load_2d(sRaw + stage * kSmemRaw + 128 * 32, &tmW, bar, kb * 32, c.e * p.w_rows + r1);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            bulk_load(sSf + stage * kSmemSf + q * 512,
+                      sf_e + (static_cast<size_t>(g[q]) * p.atoms_k + kb) * 512, 512, bar);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, 256);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int buf = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        if (!mbar_wait_bounded(&tail->tmem_empty[buf], acc_phase[buf] ^ 1, abort_flag, p.status,
+                               WAIT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * 256;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL) ||
+              !mbar_wait_bounded(&tail->conv[stage], phase, abort_flag, p.status, WAIT_CONVERT)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t adesc = make_desc_sw128(smem_u32(sA + stage * kSmemA));
+          const uint64_t bdesc = make_desc_sw128(smem_u32(sB + stage * kSmemB));
+#pragma unroll
+          for (int j = 0; j < 4; ++j)   // 16 bf16 = 32 bytes per MMA step
+            mma_bf16(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          tc_commit(&tail->empty[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(&tail->tmem_full[buf]);
+        acc_phase[buf] ^= 1;
+        buf ^= 1;
+      }
+    }
+  } else if (warp < 10) {
+    // ------------------------------ converters --------------------------------
+    // thread t expands weight row t of the 256-row operand tile: 64 codes -> 64 bf16 = 128 bytes
+    const int t = threadIdx.x - 64;
+    const int sub_tile = t >> 7, rr = t & 127;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+      const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
+      const int r0 = p.sub0_base + c.nt * p.n_step;
+      int r1 = p.sub1_base + c.nt * p.n_step;
+      if (r1 >= p.w_rows) r1 = r0;
+      const int wrow = (sub_tile ? r1 : r0) + rr;          // weight row inside the expert
+      const int first_group = (sub_tile ? r1 : r0) >> 7;
+      // scale bytes of this row inside the two staged atoms of its sub-tile
+      const int atom_sel = (wrow >> 7) - first_group;       // 0 or 1
+      const uint32_t sf_off = sub_tile * 1024 + atom_sel * 512 + (wrow & 31) * 16 + ((wrow >> 5) & 3) * 4;
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_CONVERT)) {
+          ok = false;
+          break;
+        }
+        const uint4* raw = reinterpret_cast<const uint4*>(sRaw + stage * kSmemRaw + t * 32);
+        const uint4 c0 = raw[0], c1 = raw[1];
+        const uint32_t sfw = *reinterpret_cast<const uint32_t*>(sSf + stage * kSmemSf + sf_off);
+        const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        uint8_t* brow = sB + stage * kSmemB + t * 128;
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk) {                 // 16 values per scale
+          const __nv_bfloat16 s = __float2bfloat16_rn(e4m3_to_f32((sfw >> (8 * blk)) & 0xffu));
+          const __nv_bfloat162 sc = __halves2bfloat162(s, s);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t o[4];
+            cvt_e2m1x8_bf16(words[blk * 2 + h], sc, o);
+            const int chunk = blk * 2 + h;                   // 16-byte chunk of the 128-byte row
+            *reinterpret_cast<uint4*>(brow + ((chunk ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+        fence_proxy_async_smem();                            // generic writes -> tensor-core reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->conv[stage]);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int sub = warp & 3;
+    const int half = (warp - 10) >> 2;
+    const int m = sub * 32 + lane;
+    uint32_t acc_phase[2] = {0, 0};
+    int buf = 0;
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+      const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
+      const int row0 = p.mtile_row0[c.mt];
+      const int nrows = p.mtile_rows[c.mt];
+      const float alpha = p.alphas[c.e];
+      if (!mbar_wait_bounded(&tail->tmem_full[buf], acc_phase[buf], abort_flag, p.status,
+                             WAIT_TMEM_FULL))
+        break;
+      acc_phase[buf] ^= 1;
+      tc_fence_after();
+      const uint32_t t_lane = tmem_base + buf * 256 + (static_cast<uint32_t>(sub * 32) << 16);
+      const bool valid = m < nrows;
+      const size_t pos = static_cast<size_t>(row0 + m);
+      if (EPI == EPI_FC1_GATED) {
+        const int col0 = c.nt * 128 + half * 64;
+        __nv_bfloat16* orow = p.out_bf16 + pos * p.out_cols + col0;
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t ru[16], rg[16];
+          tc_ld_32x32b_x16(t_lane + half * 64 + ch * 16, ru);
+          tc_ld_32x32b_x16(t_lane + 128 + half * 64 + ch * 16, rg);
+          tc_wait_ld();
+          uint32_t o[8];
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            float h2[2];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              const float up = __fmul_rn(__uint_as_float(ru[i + q]), alpha);
+              const float gate = __fmul_rn(__uint_as_float(rg[i + q]), alpha);
+              if (p.tap != nullptr && valid && col0 + ch * 16 < p.out_cols) {
+                float* trow = p.tap + pos * p.w_rows;
+                trow[p.sub0_base + col0 + ch * 16 + i + q] = up;
+                trow[p.sub1_base + col0 + ch * 16 + i + q] = gate;
+              }
+              h2[q] = act_gated(gate, up, p);
+            }
+            const __nv_bfloat162 b2 = __floats2bfloat162_rn(h2[0], h2[1]);
+            o[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+          }
+          if (valid && col0 + ch * 16 < p.out_cols) {
+            uint4* dst = reinterpret_cast<uint4*>(orow + ch * 16);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          }
+        }
+      } else if (EPI == EPI_FC1_RELU2) {
+        const int col0 = c.nt * 256 + half * 128;
+        __nv_bfloat16* orow = p.out_bf16 + pos * p.out_cols + col0;
+#pragma unroll 1
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t rr2[16];
+          tc_ld_32x32b_x16(t_lane + half * 128 + ch * 16, rr2);
+          tc_wait_ld();
+          uint32_t o[8];
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            float h2[2];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              const float v = __fmul_rn(__uint_as_float(rr2[i + q]), alpha);
+              if (p.tap != nullptr && valid && col0 + ch * 16 < p.out_cols)
+                p.tap[pos * p.w_rows + col0 + ch * 16 + i + q] = v;
+              const float r = fmaxf(v, 0.f);
+              h2[q] = __fmul_rn(r, r);
+            }
+            const __nv_bfloat162 b2 = __floats2bfloat162_rn(h2[0], h2[1]);
+            o[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+          }
+          if (valid && col0 + ch * 16 < p.out_cols) {
+            uint4* dst = reinterpret_cast<uint4*>(orow + ch * 16);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          }
+        }
+      } else {
+        const int col0 = c.nt * 256 + half * 128;
+        float* orow = p.out_f32 + pos * p.out_cols + col0;
+#pragma unroll 1
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t rr2[16];
+          tc_ld_32x32b_x16(t_lane + half * 128 + ch * 16, rr2);
+          tc_wait_ld();
+          if (valid && col0 + ch * 16 < p.out_cols) {
+            float4* dst = reinterpret_cast<float4*>(orow + ch * 16);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              dst[q] = make_float4(__fmul_rn(__uint_as_float(rr2[4 * q]), alpha),
+                                   __fmul_rn(__uint_as_float(rr2[4 * q + 1]), alpha),
+                                   __fmul_rn(__uint_as_float(rr2[4 * q + 2]), alpha),
+                                   __fmul_rn(__uint_as_float(rr2[4 * q + 3]), alpha));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
+      buf ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// x rows -> sorted-position order (the A operand of FC1), one warp per row
+__global__ void __launch_bounds__(256) permute_rows_bf16_kernel(
+    const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, const int32_t* __restrict__ expert_offsets,
+    int E, const int32_t* __restrict__ sorted_route_ids, int num_topk, int K,
+    __nv_bfloat16* __restrict__ out) {
+  const int total = expert_offsets[E];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int pos = blockIdx.x * 8 + warp; pos < total; pos += gridDim.x * 8) {
+    const int tkn = sorted_route_ids[pos] / num_topk;
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(tkn) * x_row_stride);
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(pos) * K);
+    for (int j = lane; j < (K >> 3); j += 32) dst[j] = __ldg(src + j);
+  }
+}
+
+// 2-D bf16 matrix [rows][cols], box = box_rows x 64 elements (128 bytes), 128-byte swizzle
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+static int make_tmap_bf16(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows,
+                          uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return B200MOE_ECUDA;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((cols * 2) & 15) != 0) return B200MOE_EALIGN;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200MOE_OK : B200MOE_ECUDA;
+}
+// packed weight codes [rows][row_bytes], box = 128 rows x 32 bytes, no swizzle (staging only)
+static int make_tmap_codes(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return B200MOE_ECUDA;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_bytes & 15) != 0) return B200MOE_EALIGN;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {32, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
+                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int EPI>
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmW, const Params& p, int grid,
+                  cudaStream_t s) {
+  auto kern = grouped_gemm_w4a16_kernel<EPI>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+    return B200MOE_ECUDA;
+  kern<<<grid, kThreads, kSmemBytes, s>>>(tmA, tmW, p);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+static void fill_common(Params& p, const b200moe_gemm_args* a, char* base) {
+  const b200moe_scratch_layout& L = *a->layout;
+  p.tile_base = reinterpret_cast<const int32_t*>(base + L.tile_base);
+  p.mtile_row0 = reinterpret_cast<const int32_t*>(base + L.mtile_row0);
+  p.mtile_rows = reinterpret_cast<const int32_t*>(base + L.mtile_rows);
+  p.status = reinterpret_cast<int32_t*>(base + L.status);
+  p.E = a->num_experts;
+  p.limit = a->swiglu_limit;
+  p.act_alpha = a->swiglu_alpha;
+  p.act_beta = a->swiglu_beta;
+  p.swigluoai = a->activation == B200MOE_ACT_SWIGLUOAI;
+}
+
+}  // namespace w4a16
+
+int w4a16_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
+  using namespace w4a16;
+  const b200moe_scratch_layout& L = *a->layout;
+  const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
+  const bool gated = a->activation != B200MOE_ACT_RELU2;
+  if (K % 64 != 0 || I % 16 != 0 || E > kMaxExperts || a->w13_sf == nullptr || a->x == nullptr)
+    return B200MOE_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(a->x) & 15) != 0 || (a->x_row_stride % 8) != 0) return B200MOE_EALIGN;
+  const int w_rows = gated ? 2 * I : I;
+  char* base = static_cast<char*>(a->scratch);
+  const int rows = a->num_tokens * a->num_topk;
+  int ggrid = (rows + 7) / 8;
+  if (ggrid > 148 * 8) ggrid = 148 * 8;
+  permute_rows_bf16_kernel<<<ggrid, 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride,
+      reinterpret_cast<const int32_t*>(base + L.expert_offsets), E,
+      reinterpret_cast<const int32_t*>(base + L.sorted_route_ids), a->num_topk, K,
+      reinterpret_cast<__nv_bfloat16*>(base + L.act_q));
+  CUtensorMap tmA, tmW;
+  int rc = make_tmap_bf16(&tmA, base + L.act_q, K, L.rows, 128);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_tmap_codes(&tmW, a->w13, K / 2, static_cast<uint64_t>(E) * w_rows);
+  if (rc != B200MOE_OK) return rc;
+  Params p = {};
+  fill_common(p, a, base);
+  p.sf = a->w13_sf;
+  p.alphas = a->w1_alphas;
+  p.out_bf16 = reinterpret_cast<__nv_bfloat16*>(base + L.mid_q);
+  p.tap = a->fc1_tap;
+  p.kdim = K;
+  p.k_blocks = K / kKPerStage;
+  p.atoms_k = ceil_div_i(K, 64);
+  p.sf_rowgroups = ceil_div_i(w_rows, 128);
+  p.w_rows = w_rows;
+  p.out_cols = I;
+  const int grid = a->num_sms > 0 ? a->num_sms : sm_count();
+  if (gated) {
+    p.n_tiles = ceil_div_i(I, 128);
+    p.n_step = 128;
+    p.sub0_base = a->gate_first ? I : 0;
+    p.sub1_base = a->gate_first ? 0 : I;
+    return launch<EPI_FC1_GATED>(tmA, tmW, p, grid, stream);
+  }
+  p.n_tiles = ceil_div_i(I, 256);
+  p.n_step = 256;
+  p.sub0_base = 0;
+  p.sub1_base = 128;
+  return launch<EPI_FC1_RELU2>(tmA, tmW, p, grid, stream);
+}
+
+int w4a16_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
+  using namespace w4a16;
+  const b200moe_scratch_layout& L = *a->layout;
+  const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
+  if (I % 64 != 0 || K % 16 != 0 || E > kMaxExperts || a->w2_sf == nullptr) return B200MOE_EINVAL;
+  char* base = static_cast<char*>(a->scratch);
+  CUtensorMap tmA, tmW;
+  int rc = make_tmap_bf16(&tmA, base + L.mid_q, I, L.rows, 128);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_tmap_codes(&tmW, a->w2, I / 2, static_cast<uint64_t>(E) * K);
+  if (rc != B200MOE_OK) return rc;
+  Params p = {};
+  fill_common(p, a, base);
+  p.sf = a->w2_sf;
+  p.alphas = a->w2_alphas;
+  p.out_f32 = reinterpret_cast<float*>(base + L.routed);
+  p.kdim = I;
+  p.k_blocks = I / kKPerStage;
+  p.atoms_k = ceil_div_i(I, 64);
+  p.sf_rowgroups = ceil_div_i(K, 128);
+  p.w_rows = K;
+  p.out_cols = K;
+  p.n_tiles = ceil_div_i(K, 256);
+  p.n_step = 256;
+  p.sub0_base = 0;
+  p.sub1_base = 128;
+  const int grid = a->num_sms > 0 ? a->num_sms : sm_count();
+  return launch<EPI_FC2>(tmA, tmW, p, grid, stream);
+}
+
 }  // namespace b200moe

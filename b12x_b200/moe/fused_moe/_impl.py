@@ -132,6 +132,14 @@ def _swizzle_scale_grid(grid: torch.Tensor) -> torch.Tensor:
     return sw.reshape(e, rp, cp)
 
 
+def _with_tail_slack(w: torch.Tensor, cols: int) -> torch.Tensor:
+    if cols % 128 == 0:
+        return w
+    flat = torch.empty(w.numel() + 256, dtype=torch.uint8, device=w.device)
+    flat[: w.numel()].copy_(w.reshape(-1).view(torch.uint8))
+    return flat[: w.numel()].view(w.shape)
+
+
 def prepare_b12x_fp4_moe_weights(
     *,
     plan: MoEWeightPreparationPlan,
@@ -179,7 +187,19 @@ def prepare_b12x_fp4_moe_weights(
             raise ValueError("fp4_e8m0_k32 w1_blockscale must be [E, w1_rows, K/32] E8M0 bytes")
         if tuple(s2.shape) != (e, plan.hidden_size, plan.intermediate_size // 32):
             raise ValueError("fp4_e8m0_k32 w2_blockscale must be [E, K, I/32] E8M0 bytes")
-        s1, s2 = _swizzle_scale_grid(s1), _swizzle_scale_grid(s2)
+        if is_gated_moe_activation(plan.activation):
+            # each half of W13 gets its own 128-row padding, so a 128-row weight tile of either
+            # half starts on an atom boundary even when I is not a multiple of 128
+            i = plan.intermediate_size
+            s1 = torch.cat([_swizzle_scale_grid(s1[:, :i]), _swizzle_scale_grid(s1[:, i:])], dim=1)
+        else:
+            s1 = _swizzle_scale_grid(s1)
+        s2 = _swizzle_scale_grid(s2)
+        # the 4-bit unpacking TMA reads whole 128-value groups: a row whose length is not a
+        # multiple of 128 values lets the last row's read run 32 bytes past the tensor; re-home
+        # such tensors into storage with slack (one-time copy, the source may be freed)
+        w1_fp4 = _with_tail_slack(w1_fp4, plan.hidden_size)
+        w2_fp4 = _with_tail_slack(w2_fp4, plan.intermediate_size)
     else:
         exp1 = (e, _align_up(plan.w1_rows, 128), _align_up(plan.hidden_size // 16, 4))
         exp2 = (e, _align_up(plan.hidden_size, 128), _align_up(plan.intermediate_size // 16, 4))
@@ -520,7 +540,7 @@ class TPMoEFP4Binding:
 
     @property
     def packed_input(self) -> torch.Tensor:
-        row = {"nvfp4": self.k // 2, "w4a8_mx": self.k, "w4a16": 0}[self.quant_mode]
+        row = {"nvfp4": self.k // 2, "w4a8_mx": self.k, "w4a16": self.k * 2}[self.quant_mode]
         return self._v("act_q", self.max_rows * row, torch.uint8).view(self.max_rows, row)
 
     @property

@@ -75,7 +75,7 @@ typedef struct {
   int64_t mtile_rows;        /* int32[mtile_cap] valid rows (1..128)            */
   int64_t sorted_route_ids;  /* int32[rows]  flat route id (t*k+slot) per position */
   int64_t inv_perm;          /* int32[rows]  position per flat route id, -1 = dropped */
-  int64_t act_q;             /* FC1 input codes  [rows][K/2] (nvfp4) / [rows][K] (mxfp8) / unused (w4a16) */
+  int64_t act_q;             /* FC1 input: codes [rows][K/2] (nvfp4) / [rows][K] (mxfp8) / bf16 [rows][K] (w4a16) */
   int64_t act_sf;            /* FC1 input scales, 512-byte atoms [mtile_cap][ceil(K/64|128)]  */
   int64_t mid_q;             /* FC2 input codes  [rows][I/2] / [rows][I] / bf16 [rows][I]     */
   int64_t mid_sf;            /* FC2 input scales atoms                                         */

@@ -196,3 +196,97 @@ def test_repeat_runs_are_bitwise_identical():
     a = run_layer(inp, poison=0x00)
     b = run_layer(inp, poison=0xFF)
     assert torch.equal(a.out, b.out) and torch.equal(a.out_f32, b.out_f32)
+
+
+# ------------------------------------------------------------------------------------------------
+# w4a8_mx: MXFP8 activations x MXFP4 weights (kind::mxf8f6f4)
+# ------------------------------------------------------------------------------------------------
+def _mx(**kw):
+    base = dict(name="mx", tokens=24, hidden=256, intermediate=128, experts=4, topk=2, activation="silu")
+    base.update(kw)
+    return synth.shape("c5", **base)
+
+
+def _check_mx_layer(run, *, expert_map=None):
+    shp = run.inp.shape
+    ref, taps = oracle_layer(run.inp, run.topk_ids, run.topk_weights, expert_map)
+    b, s = run.binding, taps.sort
+    rows = _check_sort(run, taps)
+    assert torch.equal(b.packed_input.cpu()[:rows], taps.act_codes), "MXFP8 activation codes differ"
+    sf = b.packed_input_scale.cpu()
+    atoms = (shp.hidden + 127) // 128
+    for mt in range(int(s.tile_base[-1])):
+        r0, nr = int(s.mtile_row0[mt]), int(s.mtile_rows[mt])
+        assert torch.equal(atoms_to_rows(sf, mt, atoms, nr, shp.hidden // 32), taps.act_scales[r0:r0 + nr])
+    d = (run.fc1[:rows] - taps.fc1).abs().max().item()
+    assert d <= FC1_TOL * taps.fc1.abs().max().item(), f"FC1 tap off by {d}"
+    flips = (b.materialized_intermediate.cpu()[:rows] != taps.mid_codes).float().mean().item()
+    assert flips <= FLIP_TOL, f"{flips:.3%} of the intermediate code bytes differ"
+    rms = taps.out_f32.square().mean().sqrt().item()
+    err = (run.out_f32 - taps.out_f32).abs().max().item()
+    assert err <= OUT_TOL * rms, f"output max-abs error {err:.3e} > {OUT_TOL} x rms {rms:.3e}"
+
+
+@pytest.mark.parametrize("tokens,hidden,inter,act", [
+    (24, 256, 128, "silu"), (150, 512, 256, "swigluoai"), (40, 256, 256, "relu2"),
+    (33, 320, 192, "swigluoai"),      # K and I with a half tile left over, like hidden 2880
+    (1, 384, 128, "silu")])
+def test_w4a8_mx_layer(tokens, hidden, inter, act):
+    inp = synth.make_inputs(_mx(tokens=tokens, hidden=hidden, intermediate=inter, activation=act), seed=tokens + hidden)
+    _check_mx_layer(run_layer(inp))
+
+
+def test_w4a8_mx_matches_reference_golden():
+    g = load_golden("tiny_w4a8_mx.npz")
+    shp = _mx(tokens=8)
+    inp = synth.make_inputs(shp, seed=4)
+    assert torch.equal(inp.w1_fp4, t(g["w1_fp4"])) and torch.equal(inp.w1_blockscale, t(g["w1_e8m0"]))
+    run = run_layer(inp, topk_ids=t(g["topk_ids"]), topk_weights=t(g["topk_weights"]))
+    ref = t(g["out_f32"])
+    assert (run.out_f32 - ref).abs().max().item() <= OUT_TOL * ref.square().mean().sqrt().item()
+
+
+# ------------------------------------------------------------------------------------------------
+# w4a16: BF16 activations x NVFP4 weights expanded to BF16 inside the kernel (kind::f16)
+# ------------------------------------------------------------------------------------------------
+def _w16(**kw):
+    base = dict(name="w16", tokens=24, hidden=256, intermediate=128, experts=4, topk=2, activation="silu")
+    base.update(kw)
+    return synth.shape("c3", **base)
+
+
+def _check_w4a16_layer(run, *, expert_map=None):
+    ref, taps = oracle_layer(run.inp, run.topk_ids, run.topk_weights, expert_map)
+    b = run.binding
+    rows = _check_sort(run, taps)
+    d = (run.fc1[:rows] - taps.fc1).abs().max().item()
+    assert d <= FC1_TOL * taps.fc1.abs().max().item(), f"FC1 tap off by {d}"
+    mid = b.materialized_intermediate.cpu()[:rows].view(torch.bfloat16).float()
+    flips = (mid != taps.mid).float().mean().item()
+    assert flips <= FLIP_TOL, f"{flips:.3%} of the bf16 intermediate differs"
+    assert (mid - taps.mid).abs().max().item() <= 2.0 ** -7 * taps.mid.abs().max().item()
+    rms = taps.out_f32.square().mean().sqrt().item()
+    err = (run.out_f32 - taps.out_f32).abs().max().item()
+    assert err <= OUT_TOL * rms, f"output max-abs error {err:.3e} > {OUT_TOL} x rms {rms:.3e}"
+
+
+@pytest.mark.parametrize("tokens,hidden,inter,act", [
+    (24, 256, 128, "silu"), (200, 512, 384, "silu"), (40, 256, 256, "relu2"),
+    (33, 320, 192, "silu"),           # gate half starts mid-way through a scale atom (I % 128 != 0)
+    (1, 384, 128, "silu")])
+def test_w4a16_layer(tokens, hidden, inter, act):
+    inp = synth.make_inputs(_w16(tokens=tokens, hidden=hidden, intermediate=inter, activation=act), seed=tokens + inter)
+    _check_w4a16_layer(run_layer(inp))
+
+
+def test_w4a16_matches_reference_golden():
+    g = load_golden("tiny_w4a16.npz")
+    inp = synth.make_inputs(_w16(tokens=8), seed=3)
+    assert torch.equal(inp.w1_fp4, t(g["w1_fp4"])) and torch.equal(inp.w1_blockscale, t(g["w1_blockscale"]))
+    run = run_layer(inp, topk_ids=t(g["topk_ids"]), topk_weights=t(g["topk_weights"]))
+    inv = run.binding.inv_perm.cpu().reshape(8, 2).long()
+    fc1_ref = t(g["fc1"])
+    assert (run.fc1[inv] - fc1_ref).abs().max().item() <= FC1_TOL * fc1_ref.abs().max().item()
+    ref = t(g["out_bf16"], torch.bfloat16).float()
+    # the reference rounds every route's contribution to bf16 and sums in bf16 (w4a16_reference.py:619-621)
+    assert (run.out.float() - ref).abs().max().item() <= 4 * 2.0 ** -8 * ref.abs().max().item()
