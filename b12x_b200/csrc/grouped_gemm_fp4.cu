@@ -44,7 +44,7 @@ struct __align__(8) GemmSmemTail {
 constexpr int kGemmSmemBytes =
     1024 + kStages * (kSmemA + kSmemB + kSmemSfa + kSmemSfb) + static_cast<int>(sizeof(GemmSmemTail));
 
-enum { EPI_FC1_GATED = 0, EPI_FC1_RELU2 = 1, EPI_FC2 = 2 };
+enum { EPI_FC1_GATED = 0, EPI_FC1_RELU2 = 1, EPI_FC2 = 2, EPI_FC1_SILU = 3 };
 // KIND_NVFP4: A and B packed E2M1, E4M3 scale per 16, kind::mxf4nvf4 (K = 64 per MMA, 256 per stage).
 // KIND_MX:    A E4M3 bytes, B E2M1 expanded by TMA to one value per byte slot, E8M0 scale per 32,
 //             kind::mxf8f6f4 (K = 32 per MMA, 128 per stage; one scale atom per stage).
@@ -98,16 +98,42 @@ __device__ __forceinline__ TileCoord decode_tile(int w, int n_tiles, const int32
   return c;
 }
 
+// Branch-free reciprocal and division for the epilogues (a call with a slow-path branch per
+// element keeps the compiler from interleaving the 16 independent element chains of a chunk).
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+// 1/x for normal x: hardware approximation + one Newton step (error <= 0.5 ulp + 2^-46)
+__device__ __forceinline__ float rcp_newton(float x) {
+  const float r = rcp_approx(x);
+  return __fmaf_rn(r, __fmaf_rn(-x, r, 1.0f), r);
+}
+// a / b, correctly rounded when the quotient is a normal number or zero; rb = RN(1 / b).
+// Two residual corrections with exact fma residuals (Markstein).
+__device__ __forceinline__ float div_rn_normal(float a, float b, float rb) {
+  float q = __fmul_rn(a, rb);
+  q = __fmaf_rn(__fmaf_rn(-b, q, a), rb, q);
+  q = __fmaf_rn(__fmaf_rn(-b, q, a), rb, q);
+  return q;
+}
+
+// GENERIC = false: plain SwiGLU (no clamp); true: clamp and/or the SwiGLU-OAI form, chosen at run time.
+template <bool GENERIC>
 __device__ __forceinline__ float act_gated(float gate, float up, const GemmParams& p) {
-  if (p.limit > 0.f) {
-    gate = fminf(gate, p.limit);
-    up = fminf(fmaxf(up, -p.limit), p.limit);
+  if (GENERIC) {
+    if (p.limit > 0.f) {
+      gate = fminf(gate, p.limit);
+      up = fminf(fmaxf(up, -p.limit), p.limit);
+    }
+    if (p.swigluoai) {
+      const float s = rcp_newton(1.0f + expf(fminf(-(p.act_alpha * gate), 80.0f)));
+      return (gate * s) * (up + p.act_beta);
+    }
   }
-  if (p.swigluoai) {
-    const float s = __frcp_rn(1.0f + expf(-(p.act_alpha * gate)));
-    return (gate * s) * (up + p.act_beta);
-  }
-  const float s = __frcp_rn(1.0f + expf(-gate));
+  // the exponent is capped so that 1 + e stays finite (sigmoid below 2e-35 instead of 0)
+  const float s = rcp_newton(1.0f + expf(fminf(-gate, 80.0f)));
   return (gate * s) * up;
 }
 
@@ -119,16 +145,17 @@ __device__ __forceinline__ float round_bf16(float v) {
 // quotient x / denom is first approximated by x * rcp(denom) (error < 2 ulp); if the values 2^-21
 // below and above it round to the same E2M1 code, the correctly rounded quotient does too.
 // Only a block with a value that close to a rounding boundary takes the exact division.
-__device__ __forceinline__ void requant_block16(const float (&v)[16], float gs, uint32_t& lo,
+// `rgs` = RN(1 / gs), computed once per tile.
+__device__ __forceinline__ void requant_block16(const float (&v)[16], float gs, float rgs, uint32_t& lo,
                                                 uint32_t& hi, uint8_t& sf_byte) {
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  const float raw = fminf(__fdiv_rn(__fmul_rn(amax, gs), 6.0f), 448.0f);
+  const float raw = fminf(div_rn_normal(__fmul_rn(amax, gs), 6.0f, 0.16666667163372039794921875f), 448.0f);
   sf_byte = f32_to_e4m3_rn_sat(raw);
   const float sf = e4m3_to_f32(sf_byte);
-  const float denom = fmaxf(__fdiv_rn(sf, gs), 1e-30f);
-  const float r = __frcp_rn(denom);
+  const float denom = fmaxf(div_rn_normal(sf, gs, rgs), 1e-30f);
+  const float r = rcp_approx(denom);
   float a0[8], a1[8], b0[8], b1[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -362,7 +389,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
       const bool valid = m < nrows;
       const size_t pos = static_cast<size_t>(row0 + m);
 
-      if (KIND == KIND_MX && EPI == EPI_FC1_GATED) {
+      if (KIND == KIND_MX && (EPI == EPI_FC1_GATED || EPI == EPI_FC1_SILU)) {
         // w4a8_mx: the activation output goes straight into the MXFP8 quantiser (no bf16 staging)
         const int col0 = c.nt * 128 + half * 64;
         uint8_t* qrow = p.out_q + pos * p.out_cols + col0;
@@ -386,7 +413,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
                 trow[p.sub0_base + col0 + blk * 32 + c2 * 16 + i] = up;
                 trow[p.sub1_base + col0 + blk * 32 + c2 * 16 + i] = gate;
               }
-              h[c2 * 16 + i] = act_gated(gate, up, p);
+              h[c2 * 16 + i] = act_gated<EPI == EPI_FC1_GATED>(gate, up, p);
             }
           }
           uint32_t o[8];
@@ -445,32 +472,38 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tail->tmem_empty);
-      } else if (EPI == EPI_FC1_GATED) {
+      } else if (EPI == EPI_FC1_GATED || EPI == EPI_FC1_SILU) {
         const float gs2 = p.gscale2[p.gscale_len > 1 ? c.e : 0];
+        const float rgs2 = __frcp_rn(gs2);
         const int col0 = c.nt * 128 + half * 64;   // first intermediate column of this warp
         uint8_t* qrow = p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1);
         uint32_t sfw = 0u;
-#pragma unroll 1
+#pragma unroll 2
         for (int ch = 0; ch < 4; ++ch) {
           uint32_t ru[16], rg[16];
           tc_ld_32x32b_x16(t_lane + half * 64 + ch * 16, ru);
           tc_ld_32x32b_x16(t_lane + 128 + half * 64 + ch * 16, rg);
           tc_wait_ld();
-          float h[16];
+          float up[16], gate[16], h[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float up = __fmul_rn(__uint_as_float(ru[i]), alpha);
-            const float gate = __fmul_rn(__uint_as_float(rg[i]), alpha);
-            if (p.tap != nullptr && valid) {
-              float* trow = p.tap + pos * p.w_rows;
-              trow[p.sub0_base + col0 + ch * 16 + i] = up;
-              trow[p.sub1_base + col0 + ch * 16 + i] = gate;
-            }
-            h[i] = round_bf16(act_gated(gate, up, p));
+            up[i] = __fmul_rn(__uint_as_float(ru[i]), alpha);
+            gate[i] = __fmul_rn(__uint_as_float(rg[i]), alpha);
           }
+          if (p.tap != nullptr && valid) {
+            float* trow = p.tap + pos * p.w_rows + col0 + ch * 16;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              trow[p.sub0_base + i] = up[i];
+              trow[p.sub1_base + i] = gate[i];
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            h[i] = round_bf16(act_gated<EPI == EPI_FC1_GATED>(gate[i], up[i], p));
           uint32_t lo, hi;
           uint8_t sfb;
-          requant_block16(h, gs2, lo, hi, sfb);
+          requant_block16(h, gs2, rgs2, lo, hi, sfb);
           if (valid) *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
           sfw |= static_cast<uint32_t>(sfb) << (8 * ch);
         }
@@ -482,6 +515,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 8 + half * 4)) = sfw;
       } else if (EPI == EPI_FC1_RELU2) {
         const float gs2 = p.gscale2[p.gscale_len > 1 ? c.e : 0];
+        const float rgs2 = __frcp_rn(gs2);
         const int col0 = c.nt * 256 + half * 128;
         uint8_t* sft = p.out_sf + static_cast<size_t>(c.mt) * p.out_atoms * 512;
         if (col0 < p.out_cols) {
@@ -502,7 +536,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
             }
             uint32_t lo, hi;
             uint8_t sfb;
-            requant_block16(h, gs2, lo, hi, sfb);
+            requant_block16(h, gs2, rgs2, lo, hi, sfb);
             if (valid) *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
             if (ch < 4) sfw[0] |= static_cast<uint32_t>(sfb) << (8 * ch);
             else sfw[1] |= static_cast<uint32_t>(sfb) << (8 * (ch - 4));
@@ -653,6 +687,8 @@ int nvfp4_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
     p.sfb_rg0 = p.sub0_base / 128;
     p.sfb_rg1 = p.sub1_base / 128;
     p.rg_step = 1;
+    if (!p.swigluoai && !(p.limit > 0.f))
+      return launch_gemm<KIND_NVFP4, EPI_FC1_SILU>(tmA, tmA_small, tmB, p, grid, stream);
     return launch_gemm<KIND_NVFP4, EPI_FC1_GATED>(tmA, tmA_small, tmB, p, grid, stream);
   }
   p.n_tiles = ceil_div_i(I, 256);
@@ -782,6 +818,8 @@ int mx_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
     p.sfb_rg0 = a->gate_first ? half_groups : 0;
     p.sfb_rg1 = a->gate_first ? 0 : half_groups;
     p.rg_step = 1;
+    if (!p.swigluoai && !(p.limit > 0.f))
+      return launch_gemm<KIND_MX, EPI_FC1_SILU>(tmA, tmA_small, tmB, p, grid, stream);
     return launch_gemm<KIND_MX, EPI_FC1_GATED>(tmA, tmA_small, tmB, p, grid, stream);
   }
   p.sfb_rowgroups = half_groups;
