@@ -17,7 +17,7 @@ SOURCES = (
     "api.cu",
     "route_sort.cu",
     "quant_combine.cu",
-    "grouped_gemm_fp4.cu",
+    "grouped_gemm_bs.cu",
     "grouped_gemm_other.cu",
 )
 NVCC_FLAGS = (

@@ -83,13 +83,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
                                                   volatile int* cta_abort, int* status,
                                                   int site) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_timer_ns();
+  // The limit is only looked at every 1024 failed polls, and the clock is first read then: a
+  // wait that ends within a few polls never touches the (slow) global timer.
+  unsigned long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ffu) == 0) {
       if (*cta_abort) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      const unsigned long long now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitNs) {
         *cta_abort = 1;
         if (status != nullptr) {
           atomicCAS(status, 0, 1);

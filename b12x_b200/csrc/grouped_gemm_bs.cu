@@ -1,48 +1,62 @@
-// Stages 4 and 5: grouped block-scaled expert GEMMs on tcgen05 (sm_100a).
+// Stages 4 and 5: grouped block-scaled expert GEMMs on tcgen05 (sm_100a), recipes nvfp4 and w4a8_mx.
 //
-//   FC1:  acc[128 x 256] = Xq[128 rows of one expert] . W13q[128 up rows ; 128 gate rows]^T
-//         epilogue: x alpha1 -> gated activation (fp32) -> round to bf16 -> NVFP4 re-quantise with
-//         a2_gscale -> codes + scale atoms of the FC2 A operand
-//   FC2:  acc[128 x 256] = Hq . W2q[256 rows]^T ; epilogue: x alpha2 -> float32 routed rows
+//   FC1:  acc[128 x BN] = Xq[128 rows of one expert] . W13q[BN/2 up rows ; BN/2 gate rows]^T
+//         epilogue: x alpha1 -> gated activation (fp32) -> (nvfp4: round to bf16) -> re-quantise
+//         -> codes + scale atoms of the FC2 A operand
+//   FC2:  acc[128 x BN] = Hq . W2q[BN rows]^T ; epilogue: x alpha2 -> float32 routed rows
 //
-// One persistent CTA per SM walks the (expert, n-tile, m-tile) work list that the sort kernel
-// left in the scratch arena.  Warp 0 feeds a 4-stage TMA pipeline (SWIZZLE_128B operand tiles +
-// plain bulk copies of the 512-byte scale atoms), warp 1 copies the scale atoms into TMEM with
-// tcgen05.cp and issues tcgen05.mma.kind::mxf4nvf4.block_scale (scale_vec::4X), warps 2..9 drain
-// the TMEM accumulator.  Every wait is bounded; a wait that runs out marks the status block and
-// every role leaves its loop.
+// One persistent CTA per SM walks the (expert, n-tile, m-tile) work list that the sort kernel left
+// in the scratch arena.  Warp 0 feeds a TMA pipeline (SWIZZLE_128B operand tiles + plain bulk
+// copies of the 512-byte scale atoms), warp 1 copies the scale atoms into TMEM with tcgen05.cp and
+// issues the block-scaled tcgen05.mma, warps 2..9 drain the TMEM accumulator.
+//
+// Two tile shapes: BN = 128 (six pipeline stages, the accumulator double-buffered in TMEM so the
+// epilogue of one tile runs under the main loop of the next) and BN = 256 (four stages, one
+// accumulator).  Every wait is bounded; a wait that runs out marks the status block and every role
+// leaves its loop.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace b200moe {
 
 constexpr int kBM = 128;            // tile rows (MMA M)
-constexpr int kBN = 256;            // MMA N = two 128-row weight sub-tiles
-constexpr int kStages = 4;
-constexpr int kRowBytes = 128;      // one swizzled operand row per stage = 256 FP4 values
-constexpr int kKPerStage = 256;     // reduction elements per stage
+constexpr int kRowBytes = 128;      // one swizzled operand row per stage
+constexpr int kKPerStage = 256;     // nvfp4: reduction elements per stage
 constexpr int kKPerMma = 64;
 constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kTmemCols = 512;
-constexpr int kTmemSfa = 256;       // 4 stages x 16 columns
-constexpr int kTmemSfb = 320;       // 4 stages x 32 columns
-
+constexpr int kTmemSf = 256;        // first scale column (accumulators use columns 0..255)
+constexpr int kMaxStages = 6;
 constexpr int kSmemA = kBM * kRowBytes;        // 16 KiB
-constexpr int kSmemB = kBN * kRowBytes;        // 32 KiB
-constexpr int kSmemSfa = 4 * 512;              // 4 k-steps x one atom
-constexpr int kSmemSfb = 2 * 4 * 512;          // 2 sub-tiles x 4 k-steps
+constexpr int kSmemSfa = 4 * 512;              // up to 4 scale atoms per stage
 constexpr int kMaxExperts = 1024;
 
+template <int BN>
+struct TileCfg {
+  static constexpr int kStages = BN == 128 ? 6 : 4;
+  static constexpr int kBufs = BN == 128 ? 2 : 1;       // accumulators in TMEM
+  static constexpr int kSmemB = BN * kRowBytes;
+  static constexpr int kSfbChains = BN / 128;           // scale-atom chains per stage for B
+  static constexpr int kSmemSfb = kSfbChains * 4 * 512;
+  static constexpr int kSfCols = 16 + 4 * (BN / 32);    // TMEM scale columns per stage
+  static constexpr int kStageBytes = kSmemA + kSmemB + kSmemSfa + kSmemSfb;
+};
+
 struct __align__(8) GemmSmemTail {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
-  uint64_t tmem_full;
-  uint64_t tmem_empty;
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
   int32_t tile_base[kMaxExperts + 1];
 };
-constexpr int kGemmSmemBytes =
-    1024 + kStages * (kSmemA + kSmemB + kSmemSfa + kSmemSfb) + static_cast<int>(sizeof(GemmSmemTail));
+template <int BN>
+constexpr int gemm_smem_bytes() {
+  return 1024 + TileCfg<BN>::kStages * TileCfg<BN>::kStageBytes +
+         static_cast<int>(sizeof(GemmSmemTail));
+}
 
 enum { EPI_FC1_GATED = 0, EPI_FC1_RELU2 = 1, EPI_FC2 = 2, EPI_FC1_SILU = 3 };
 // KIND_NVFP4: A and B packed E2M1, E4M3 scale per 16, kind::mxf4nvf4 (K = 64 per MMA, 256 per stage).
@@ -66,7 +80,6 @@ struct GemmParams {
   float* tap;                    // FC1 debug tap [rows][w_rows] or null
   int E, n_tiles, kdim, k_blocks, atoms_k;
   int sfb_rowgroups;             // per expert
-  int sfb_rg0, sfb_rg1, rg_step; // scale row-group of the two sub-tiles at n-tile 0, step per n-tile
   int w_rows;                    // weight rows per expert
   int sub0_base, sub1_base;      // first weight row of the two sub-tiles at n-tile 0
   int n_step;                    // weight rows advanced per n-tile
@@ -203,11 +216,25 @@ __device__ __forceinline__ void requant_block32_mx(const float (&v)[32], uint32_
   }
 }
 
-template <int KIND, int EPI>
+// n scale bytes (n = 1, 2 or 4, packed in `word`) -> the tile's atom chain at scale column `col`
+template <int N>
+__device__ __forceinline__ void store_sf(uint8_t* sf_tile, uint32_t m, uint32_t col, uint32_t word) {
+  uint8_t* dst = sf_tile + sf_atom_offset(m, col);
+  if (N == 4) *reinterpret_cast<uint32_t*>(dst) = word;
+  else if (N == 2) *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(word);
+  else *dst = static_cast<uint8_t>(word);
+}
+
+template <int KIND, int EPI, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
-                          const __grid_constant__ CUtensorMap tmA_small,
-                          const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+                                const __grid_constant__ CUtensorMap tmA_small,
+                                const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using Cfg = TileCfg<BN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kSmemB = Cfg::kSmemB;
+  constexpr int kSmemSfb = Cfg::kSmemSfb;
+  constexpr bool kGated = EPI == EPI_FC1_GATED || EPI == EPI_FC1_SILU;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -224,8 +251,10 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
       mbar_init(&tail->full[s], 1);
       mbar_init(&tail->empty[s], 1);
     }
-    mbar_init(&tail->tmem_full, 1);
-    mbar_init(&tail->tmem_empty, 8);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tail->tmem_full[b], 1);
+      mbar_init(&tail->tmem_empty[b], 8);
+    }
     tail->abort_flag = 0;
     fence_mbar_init();
   }
@@ -246,10 +275,17 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      tma_prefetch_desc(&tmA);
-      tma_prefetch_desc(&tmA_small);
-      tma_prefetch_desc(&tmB);
+    // A few lanes walk the same loop and each issues ONE of the stage's copies: lane 0 arms the
+    // barrier and fetches A, lanes 1..kBoxes fetch the 64-row weight boxes, then one lane for the
+    // activation scale atoms and one per weight scale chain.
+    constexpr int kBoxes = BN / 64;
+    constexpr int kLanes = 2 + kBoxes + Cfg::kSfbChains;
+    if (lane < kLanes) {
+      if (lane == 0) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmA_small);
+        tma_prefetch_desc(&tmB);
+      }
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -261,19 +297,26 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         const bool small_a = p.mtile_rows[c.mt] <= 32;
         const CUtensorMap* tma_a = small_a ? &tmA_small : &tmA;
         const uint32_t a_bytes = (small_a ? 32u : 128u) * kRowBytes;
-        const int r0 = p.sub0_base + c.nt * p.n_step;   // weight row inside the expert
-        int r1 = p.sub1_base + c.nt * p.n_step;
-        const int rg0 = p.sfb_rg0 + c.nt * p.rg_step;
-        int rg1 = p.sfb_rg1 + c.nt * p.rg_step;
-        if (r1 >= p.w_rows) {                           // half-empty last tile: reload sub-tile 0
-          r1 = r0;
-          rg1 = rg0;
+        // weight rows of this lane's box / scale chain of this lane.  A gated tile is BN/128 pair
+        // groups: box 2g = 64 up rows, box 2g+1 = the 64 gate rows of the same columns; its scale
+        // chain g is the pair atom of those columns.  A plain tile is BN consecutive rows.
+        int my_row = 0;
+        const uint8_t* my_sf = p.sfa + static_cast<size_t>(c.mt) * p.atoms_k * 512;
+        if (lane >= 1 && lane <= kBoxes) {
+          const int b = lane - 1;
+          if (kGated) {
+            int g = b >> 1;
+            if (c.nt * p.n_step + g * 64 >= p.out_cols) g = 0;       // half-empty last tile
+            my_row = ((b & 1) ? p.sub1_base : p.sub0_base) + c.nt * p.n_step + g * 64;
+          } else {
+            my_row = c.nt * p.n_step + b * 64;
+            if (my_row >= p.w_rows) my_row = c.nt * p.n_step;
+          }
+        } else if (lane > kBoxes + 1) {
+          int rg = c.nt * Cfg::kSfbChains + (lane - kBoxes - 2);
+          if (rg >= p.sfb_rowgroups) rg = c.nt * Cfg::kSfbChains;
+          my_sf = p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + rg) * p.atoms_k * 512;
         }
-        const uint8_t* sfa_src = p.sfa + static_cast<size_t>(c.mt) * p.atoms_k * 512;
-        const uint8_t* sfb0 =
-            p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + rg0) * p.atoms_k * 512;
-        const uint8_t* sfb1 =
-            p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + rg1) * p.atoms_k * 512;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status,
                                  WAIT_SMEM_EMPTY)) {
@@ -287,14 +330,17 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
           // the unpacking TMA type counts the packed bytes it reads (64 per 128-value row)
           const uint32_t b_bytes = KIND == KIND_MX ? kSmemB / 2 : kSmemB;
           uint64_t* bar = &tail->full[stage];
-          mbar_expect_tx(bar, a_bytes + b_bytes + 3u * sf_bytes);
-          tma_load_2d(sA + stage * kSmemA, tma_a, bar, kb * kRowBytes, row0);
-          tma_load_2d(sB + stage * kSmemB, &tmB, bar, kb * kRowBytes, c.e * p.w_rows + r0);
-          tma_load_2d(sB + stage * kSmemB + kSmemB / 2, &tmB, bar, kb * kRowBytes,
-                      c.e * p.w_rows + r1);
-          bulk_load(sSfa + stage * kSmemSfa, sfa_src + sf_off, sf_bytes, bar);
-          bulk_load(sSfb + stage * kSmemSfb, sfb0 + sf_off, sf_bytes, bar);
-          bulk_load(sSfb + stage * kSmemSfb + 2048, sfb1 + sf_off, sf_bytes, bar);
+          if (lane == 0) {
+            mbar_expect_tx(bar, a_bytes + b_bytes + (1u + Cfg::kSfbChains) * sf_bytes);
+            tma_load_2d(sA + stage * kSmemA, tma_a, bar, kb * kRowBytes, row0);
+          } else if (lane <= kBoxes) {
+            tma_load_2d(sB + stage * kSmemB + (lane - 1) * 64 * kRowBytes, &tmB, bar, kb * kRowBytes,
+                        c.e * p.w_rows + my_row);
+          } else if (lane == kBoxes + 1) {
+            bulk_load(sSfa + stage * kSmemSfa, my_sf + sf_off, sf_bytes, bar);
+          } else {
+            bulk_load(sSfb + stage * kSmemSfb + (lane - kBoxes - 2) * 2048, my_sf + sf_off, sf_bytes, bar);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -310,18 +356,22 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc =
-          KIND == KIND_MX ? make_idesc_block_scaled(kBM, kBN, /*a e4m3*/ 0, /*b e2m1*/ 5, /*ue8m0*/ 1)
-                          : make_idesc_block_scaled(kBM, kBN, /*a*/ 1, /*b*/ 1, /*ue4m3*/ 0);
+          KIND == KIND_MX ? make_idesc_block_scaled(kBM, BN, /*a e4m3*/ 0, /*b e2m1*/ 5, /*ue8m0*/ 1)
+                          : make_idesc_block_scaled(kBM, BN, /*a*/ 1, /*b*/ 1, /*ue4m3*/ 0);
       int stage = 0;
-      uint32_t phase = 0, tile_phase = 0;
+      constexpr int kSfbStep = 4 * (BN / 128);   // scale columns of B per MMA step
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int buf = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-        if (!mbar_wait_bounded(&tail->tmem_empty, tile_phase ^ 1, abort_flag, p.status,
+        if (!mbar_wait_bounded(&tail->tmem_empty[buf], acc_phase[buf] ^ 1, abort_flag, p.status,
                                WAIT_TMEM_EMPTY)) {
           ok = false;
           break;
         }
         tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL)) {
             ok = false;
@@ -329,8 +379,8 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           tc_fence_after();
           const int ksteps = min(4, (p.kdim - kb * kPerStage) / kPerMma);
-          const uint32_t sfa_t = tmem_base + kTmemSfa + stage * 16;
-          const uint32_t sfb_t = tmem_base + kTmemSfb + stage * 32;
+          const uint32_t sfa_t = tmem_base + kTmemSf + stage * Cfg::kSfCols;
+          const uint32_t sfb_t = sfa_t + 16;
           const uint32_t sfa_s = smem_u32(sSfa + stage * kSmemSfa);
           const uint32_t sfb_s = smem_u32(sSfb + stage * kSmemSfb);
           const uint64_t adesc = make_desc_sw128(smem_u32(sA + stage * kSmemA));
@@ -339,23 +389,24 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
             // one atom = the four per-32 scales of this stage; MMA step j uses byte j of each word
             tc_cp_32x128b_warpx4(sfa_t, make_desc_sf(sfa_s));
             tc_cp_32x128b_warpx4(sfb_t, make_desc_sf(sfb_s));
-            tc_cp_32x128b_warpx4(sfb_t + 4, make_desc_sf(sfb_s + 2048));
+            if (Cfg::kSfbChains == 2) tc_cp_32x128b_warpx4(sfb_t + 4, make_desc_sf(sfb_s + 2048));
             for (int j = 0; j < ksteps; ++j) {
               const uint32_t ju = static_cast<uint32_t>(j);
               // 32 one-byte slots further along the swizzled row -> +2 in 16-byte units
-              mma_mxf8f6f4(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc | (ju << 29) | (ju << 4),
+              mma_mxf8f6f4(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc | (ju << 29) | (ju << 4),
                            sfa_t + (ju << 30), sfb_t + (ju << 30), (kb > 0 || j > 0) ? 1u : 0u);
             }
           } else {
             for (int j = 0; j < ksteps; ++j) {
               tc_cp_32x128b_warpx4(sfa_t + 4 * j, make_desc_sf(sfa_s + 512 * j));
-              tc_cp_32x128b_warpx4(sfb_t + 8 * j, make_desc_sf(sfb_s + 512 * j));
-              tc_cp_32x128b_warpx4(sfb_t + 8 * j + 4, make_desc_sf(sfb_s + 2048 + 512 * j));
+              tc_cp_32x128b_warpx4(sfb_t + kSfbStep * j, make_desc_sf(sfb_s + 512 * j));
+              if (Cfg::kSfbChains == 2)
+                tc_cp_32x128b_warpx4(sfb_t + kSfbStep * j + 4, make_desc_sf(sfb_s + 2048 + 512 * j));
             }
             for (int j = 0; j < ksteps; ++j) {
               // 64 FP4 values = 32 bytes further along the swizzled row -> +2 in 16-byte units
-              mma_nvf4_4x(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j,
-                          sfb_t + 8 * j, (kb > 0 || j > 0) ? 1u : 0u);
+              mma_nvf4_4x(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j,
+                          sfb_t + kSfbStep * j, (kb > 0 || j > 0) ? 1u : 0u);
             }
           }
           tc_commit(&tail->empty[stage]);
@@ -364,57 +415,72 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
             phase ^= 1;
           }
         }
-        if (ok) tc_commit(&tail->tmem_full);
-        tile_phase ^= 1;
+        if (ok) tc_commit(&tail->tmem_full[buf]);
+        acc_phase[buf] ^= 1;
+        if (Cfg::kBufs == 2) buf ^= 1;
       }
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
     // Eight warps.  Warp w may only read TMEM sub-partition (w & 3), i.e. tile rows
     // 32*(w&3) .. +31; the two warps that share a sub-partition split the tile's columns.
+    constexpr int kPairs = BN / 2;                  // gated: output columns per tile
+    constexpr int kGatedChunks = kPairs / 32;       // 16-column chunks per warp (gated)
+    constexpr int kPlainChunks = BN / 32;           // 16-column chunks per warp (FC2 / relu2)
     const int sub = warp & 3;
     const int half = (warp - 2) >> 2;
     const int m = sub * 32 + lane;            // tile row = TMEM lane
-    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(sub * 32) << 16);
-    uint32_t tile_phase = 0;
+    uint32_t acc_phase[2] = {0, 0};
+    int buf = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
       const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
       const int row0 = p.mtile_row0[c.mt];
       const int nrows = p.mtile_rows[c.mt];
       const float alpha = p.alphas[c.e];
-      if (!mbar_wait_bounded(&tail->tmem_full, tile_phase, abort_flag, p.status, WAIT_TMEM_FULL))
+      if (!mbar_wait_bounded(&tail->tmem_full[buf], acc_phase[buf], abort_flag, p.status,
+                             WAIT_TMEM_FULL))
         break;
-      tile_phase ^= 1;
+      acc_phase[buf] ^= 1;
       tc_fence_after();
+      const uint32_t t_lane = tmem_base + buf * BN + (static_cast<uint32_t>(sub * 32) << 16);
       const bool valid = m < nrows;
       const size_t pos = static_cast<size_t>(row0 + m);
+      uint8_t* sft = p.out_sf + static_cast<size_t>(c.mt) * p.out_atoms * 512;
 
-      if (KIND == KIND_MX && (EPI == EPI_FC1_GATED || EPI == EPI_FC1_SILU)) {
+      if (KIND == KIND_MX && kGated) {
         // w4a8_mx: the activation output goes straight into the MXFP8 quantiser (no bf16 staging)
-        const int col0 = c.nt * 128 + half * 64;
+        constexpr int kBlocks = kPairs / 64;      // 32-column blocks per warp
+        constexpr int kUpCol = BN == 256 ? 128 : 32;   // TMEM column of this warp's up values, per half
+        const int col0 = c.nt * kPairs + half * (kPairs / 2);
         uint8_t* qrow = p.out_q + pos * p.out_cols + col0;
         uint32_t sfw = 0u;
         const bool cols_ok = col0 < p.out_cols;
 #pragma unroll 1
-        for (int blk = 0; blk < 2; ++blk) {
+        for (int blk = 0; blk < kBlocks; ++blk) {
           float h[32];
 #pragma unroll
           for (int c2 = 0; c2 < 2; ++c2) {
             uint32_t ru[16], rg[16];
-            tc_ld_32x32b_x16(t_lane + half * 64 + blk * 32 + c2 * 16, ru);
-            tc_ld_32x32b_x16(t_lane + 128 + half * 64 + blk * 32 + c2 * 16, rg);
+            tc_ld_32x32b_x16(t_lane + half * kUpCol + blk * 32 + c2 * 16, ru);
+            tc_ld_32x32b_x16(t_lane + half * kUpCol + 64 + blk * 32 + c2 * 16, rg);
             tc_wait_ld();
+            float up[16], gate[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float up = __fmul_rn(__uint_as_float(ru[i]), alpha);
-              const float gate = __fmul_rn(__uint_as_float(rg[i]), alpha);
-              if (p.tap != nullptr && valid && cols_ok) {
-                float* trow = p.tap + pos * p.w_rows;
-                trow[p.sub0_base + col0 + blk * 32 + c2 * 16 + i] = up;
-                trow[p.sub1_base + col0 + blk * 32 + c2 * 16 + i] = gate;
-              }
-              h[c2 * 16 + i] = act_gated<EPI == EPI_FC1_GATED>(gate, up, p);
+              up[i] = __fmul_rn(__uint_as_float(ru[i]), alpha);
+              gate[i] = __fmul_rn(__uint_as_float(rg[i]), alpha);
             }
+            if (p.tap != nullptr && valid && cols_ok) {
+              float* trow = p.tap + pos * p.w_rows + col0 + blk * 32 + c2 * 16;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                trow[p.sub0_base + i] = up[i];
+                trow[p.sub1_base + i] = gate[i];
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              h[c2 * 16 + i] = act_gated<EPI == EPI_FC1_GATED>(gate[i], up[i], p);
           }
           uint32_t o[8];
           uint8_t sfb;
@@ -428,29 +494,26 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tail->tmem_empty);
-        if (cols_ok) {
-          uint8_t* sft = p.out_sf + static_cast<size_t>(c.mt) * p.out_atoms * 512;
-          *reinterpret_cast<uint16_t*>(sft + sf_atom_offset(m, c.nt * 4 + half * 2)) =
-              static_cast<uint16_t>(sfw);
-        }
+        if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
+        if (cols_ok) store_sf<kBlocks>(sft, m, col0 >> 5, sfw);
       } else if (KIND == KIND_MX && EPI == EPI_FC1_RELU2) {
-        const int col0 = c.nt * 256 + half * 128;
+        constexpr int kBlocks = BN / 64;
+        const int col0 = c.nt * BN + half * (BN / 2);
         if (col0 < p.out_cols) {
           uint8_t* qrow = p.out_q + pos * p.out_cols + col0;
           uint32_t sfw = 0u;
 #pragma unroll 1
-          for (int blk = 0; blk < 4; ++blk) {
+          for (int blk = 0; blk < kBlocks; ++blk) {
             float h[32];
 #pragma unroll
             for (int c2 = 0; c2 < 2; ++c2) {
               uint32_t rr[16];
-              tc_ld_32x32b_x16(t_lane + half * 128 + blk * 32 + c2 * 16, rr);
+              tc_ld_32x32b_x16(t_lane + half * (BN / 2) + blk * 32 + c2 * 16, rr);
               tc_wait_ld();
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
                 const float v = __fmul_rn(__uint_as_float(rr[i]), alpha);
-                if (p.tap != nullptr && valid)
+                if (p.tap != nullptr && valid && col0 + blk * 32 < p.out_cols)
                   p.tap[pos * p.w_rows + col0 + blk * 32 + c2 * 16 + i] = v;
                 const float r = fmaxf(v, 0.f);
                 h[c2 * 16 + i] = __fmul_rn(r, r);
@@ -466,23 +529,24 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
             }
             sfw |= static_cast<uint32_t>(sfb) << (8 * blk);
           }
-          uint8_t* sft = p.out_sf + static_cast<size_t>(c.mt) * p.out_atoms * 512;
-          *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 8 + half * 4)) = sfw;
+          store_sf<kBlocks>(sft, m, col0 >> 5, sfw);
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tail->tmem_empty);
-      } else if (EPI == EPI_FC1_GATED || EPI == EPI_FC1_SILU) {
+        if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
+      } else if (kGated) {
         const float gs2 = p.gscale2[p.gscale_len > 1 ? c.e : 0];
         const float rgs2 = __frcp_rn(gs2);
-        const int col0 = c.nt * 128 + half * 64;   // first intermediate column of this warp
+        // TMEM columns of a pair group: 64 up values then the 64 gate values of the same columns
+        constexpr int kUpCol = BN == 256 ? 128 : 32;
+        const int col0 = c.nt * kPairs + half * (kPairs / 2);   // first intermediate column of this warp
         uint8_t* qrow = p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1);
         uint32_t sfw = 0u;
 #pragma unroll 2
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < kGatedChunks; ++ch) {
           uint32_t ru[16], rg[16];
-          tc_ld_32x32b_x16(t_lane + half * 64 + ch * 16, ru);
-          tc_ld_32x32b_x16(t_lane + 128 + half * 64 + ch * 16, rg);
+          tc_ld_32x32b_x16(t_lane + half * kUpCol + ch * 16, ru);
+          tc_ld_32x32b_x16(t_lane + half * kUpCol + 64 + ch * 16, rg);
           tc_wait_ld();
           float up[16], gate[16], h[16];
 #pragma unroll
@@ -490,7 +554,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
             up[i] = __fmul_rn(__uint_as_float(ru[i]), alpha);
             gate[i] = __fmul_rn(__uint_as_float(rg[i]), alpha);
           }
-          if (p.tap != nullptr && valid) {
+          if (p.tap != nullptr && valid && col0 < p.out_cols) {
             float* trow = p.tap + pos * p.w_rows + col0 + ch * 16;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -504,56 +568,56 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
           uint32_t lo, hi;
           uint8_t sfb;
           requant_block16(h, gs2, rgs2, lo, hi, sfb);
-          if (valid) *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
+          if (valid && col0 < p.out_cols) *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
           sfw |= static_cast<uint32_t>(sfb) << (8 * ch);
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tail->tmem_empty);
+        if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
         // scale atoms are per tile: padding rows are written too (their values are never used)
-        uint8_t* sft = p.out_sf + static_cast<size_t>(c.mt) * p.out_atoms * 512;
-        *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 8 + half * 4)) = sfw;
+        if (col0 < p.out_cols) store_sf<kGatedChunks>(sft, m, col0 >> 4, sfw);
       } else if (EPI == EPI_FC1_RELU2) {
         const float gs2 = p.gscale2[p.gscale_len > 1 ? c.e : 0];
         const float rgs2 = __frcp_rn(gs2);
-        const int col0 = c.nt * 256 + half * 128;
-        uint8_t* sft = p.out_sf + static_cast<size_t>(c.mt) * p.out_atoms * 512;
+        const int col0 = c.nt * BN + half * (BN / 2);
         if (col0 < p.out_cols) {
           uint8_t* qrow = p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1);
           uint32_t sfw[2] = {0u, 0u};
 #pragma unroll 1
-          for (int ch = 0; ch < 8; ++ch) {
+          for (int ch = 0; ch < kPlainChunks; ++ch) {
             uint32_t rr[16];
-            tc_ld_32x32b_x16(t_lane + half * 128 + ch * 16, rr);
+            tc_ld_32x32b_x16(t_lane + half * (BN / 2) + ch * 16, rr);
             tc_wait_ld();
             float h[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const float v = __fmul_rn(__uint_as_float(rr[i]), alpha);
-              if (p.tap != nullptr && valid) p.tap[pos * p.w_rows + col0 + ch * 16 + i] = v;
+              if (p.tap != nullptr && valid && col0 + ch * 16 < p.out_cols)
+                p.tap[pos * p.w_rows + col0 + ch * 16 + i] = v;
               const float r = fmaxf(v, 0.f);
               h[i] = round_bf16(__fmul_rn(r, r));
             }
             uint32_t lo, hi;
             uint8_t sfb;
             requant_block16(h, gs2, rgs2, lo, hi, sfb);
-            if (valid) *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
+            if (valid && col0 + ch * 16 < p.out_cols)
+              *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
             if (ch < 4) sfw[0] |= static_cast<uint32_t>(sfb) << (8 * ch);
             else sfw[1] |= static_cast<uint32_t>(sfb) << (8 * (ch - 4));
           }
-          *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 16 + half * 8)) = sfw[0];
-          *reinterpret_cast<uint32_t*>(sft + sf_atom_offset(m, c.nt * 16 + half * 8 + 4)) = sfw[1];
+          store_sf<4>(sft, m, col0 >> 4, sfw[0]);
+          if (kPlainChunks == 8 && col0 + 64 < p.out_cols) store_sf<4>(sft, m, (col0 >> 4) + 4, sfw[1]);
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tail->tmem_empty);
+        if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
       } else {
-        const int col0 = c.nt * 256 + half * 128;
+        const int col0 = c.nt * BN + half * (BN / 2);
         float* orow = p.out_f32 + pos * p.out_cols + col0;
-#pragma unroll 1
-        for (int ch = 0; ch < 8; ++ch) {
+#pragma unroll 2
+        for (int ch = 0; ch < kPlainChunks; ++ch) {
           uint32_t rr[16];
-          tc_ld_32x32b_x16(t_lane + half * 128 + ch * 16, rr);
+          tc_ld_32x32b_x16(t_lane + half * (BN / 2) + ch * 16, rr);
           tc_wait_ld();
           if (valid && col0 + ch * 16 < p.out_cols) {
             float4* dst = reinterpret_cast<float4*>(orow + ch * 16);
@@ -567,8 +631,9 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tail->tmem_empty);
+        if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
       }
+      if (Cfg::kBufs == 2) buf ^= 1;
     }
   }
 
@@ -627,120 +692,6 @@ static int num_sms_cached() {
   return n;
 }
 
-template <int KIND, int EPI>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmA_small,
-                       const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t s) {
-  auto kern = grouped_gemm_blockscaled_kernel<KIND, EPI>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes) !=
-      cudaSuccess)
-    return B200MOE_ECUDA;
-  kern<<<grid, kGemmThreads, kGemmSmemBytes, s>>>(tmA, tmA_small, tmB, p);
-  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
-}
-
-int nvfp4_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
-  const b200moe_scratch_layout& L = *a->layout;
-  const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
-  const bool gated = a->activation != B200MOE_ACT_RELU2;
-  if (K % 64 != 0 || I % 128 != 0 || E > kMaxExperts) return B200MOE_EINVAL;
-  const int w_rows = gated ? 2 * I : I;
-  char* base = static_cast<char*>(a->scratch);
-  CUtensorMap tmA, tmA_small, tmB;
-  int rc = make_tmap_bytes_2d(&tmA, base + L.act_q, K / 2, L.rows, 128);
-  if (rc != B200MOE_OK) return rc;
-  rc = make_tmap_bytes_2d(&tmA_small, base + L.act_q, K / 2, L.rows, 32);
-  if (rc != B200MOE_OK) return rc;
-  rc = make_tmap_bytes_2d(&tmB, a->w13, K / 2, static_cast<uint64_t>(E) * w_rows, 128);
-  if (rc != B200MOE_OK) return rc;
-  GemmParams p = {};
-  p.sfa = reinterpret_cast<const uint8_t*>(base + L.act_sf);
-  p.sfb = a->w13_sf;
-  p.tile_base = reinterpret_cast<const int32_t*>(base + L.tile_base);
-  p.mtile_expert = reinterpret_cast<const int32_t*>(base + L.mtile_expert);
-  p.mtile_row0 = reinterpret_cast<const int32_t*>(base + L.mtile_row0);
-  p.mtile_rows = reinterpret_cast<const int32_t*>(base + L.mtile_rows);
-  p.status = reinterpret_cast<int32_t*>(base + L.status);
-  p.alphas = a->w1_alphas;
-  p.gscale2 = a->a2_gscale;
-  p.out_q = reinterpret_cast<uint8_t*>(base + L.mid_q);
-  p.out_sf = reinterpret_cast<uint8_t*>(base + L.mid_sf);
-  p.tap = a->fc1_tap;
-  p.E = E;
-  p.kdim = K;
-  p.k_blocks = ceil_div_i(K, kKPerStage);
-  p.atoms_k = ceil_div_i(K, 64);
-  p.w_rows = w_rows;
-  p.sfb_rowgroups = ceil_div_i(w_rows, 128);
-  p.out_cols = I;
-  p.out_atoms = ceil_div_i(I, 64);
-  p.gscale_len = a->gscale_len;
-  p.limit = a->swiglu_limit;
-  p.act_alpha = a->swiglu_alpha;
-  p.act_beta = a->swiglu_beta;
-  p.swigluoai = a->activation == B200MOE_ACT_SWIGLUOAI;
-  const int grid = a->num_sms > 0 ? a->num_sms : num_sms_cached();
-  if (gated) {
-    p.n_tiles = I / 128;
-    p.n_step = 128;
-    p.sub0_base = a->gate_first ? I : 0;   // sub-tile 0 = up rows
-    p.sub1_base = a->gate_first ? 0 : I;   // sub-tile 1 = gate rows
-    p.sfb_rg0 = p.sub0_base / 128;
-    p.sfb_rg1 = p.sub1_base / 128;
-    p.rg_step = 1;
-    if (!p.swigluoai && !(p.limit > 0.f))
-      return launch_gemm<KIND_NVFP4, EPI_FC1_SILU>(tmA, tmA_small, tmB, p, grid, stream);
-    return launch_gemm<KIND_NVFP4, EPI_FC1_GATED>(tmA, tmA_small, tmB, p, grid, stream);
-  }
-  p.n_tiles = ceil_div_i(I, 256);
-  p.n_step = 256;
-  p.sub0_base = 0;
-  p.sub1_base = 128;
-  p.sfb_rg0 = 0;
-  p.sfb_rg1 = 1;
-  p.rg_step = 2;
-  return launch_gemm<KIND_NVFP4, EPI_FC1_RELU2>(tmA, tmA_small, tmB, p, grid, stream);
-}
-
-int nvfp4_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
-  const b200moe_scratch_layout& L = *a->layout;
-  const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
-  if (I % 64 != 0 || K % 128 != 0 || E > kMaxExperts) return B200MOE_EINVAL;
-  char* base = static_cast<char*>(a->scratch);
-  CUtensorMap tmA, tmA_small, tmB;
-  int rc = make_tmap_bytes_2d(&tmA, base + L.mid_q, I / 2, L.rows, 128);
-  if (rc != B200MOE_OK) return rc;
-  rc = make_tmap_bytes_2d(&tmA_small, base + L.mid_q, I / 2, L.rows, 32);
-  if (rc != B200MOE_OK) return rc;
-  rc = make_tmap_bytes_2d(&tmB, a->w2, I / 2, static_cast<uint64_t>(E) * K, 128);
-  if (rc != B200MOE_OK) return rc;
-  GemmParams p = {};
-  p.sfa = reinterpret_cast<const uint8_t*>(base + L.mid_sf);
-  p.sfb = a->w2_sf;
-  p.tile_base = reinterpret_cast<const int32_t*>(base + L.tile_base);
-  p.mtile_expert = reinterpret_cast<const int32_t*>(base + L.mtile_expert);
-  p.mtile_row0 = reinterpret_cast<const int32_t*>(base + L.mtile_row0);
-  p.mtile_rows = reinterpret_cast<const int32_t*>(base + L.mtile_rows);
-  p.status = reinterpret_cast<int32_t*>(base + L.status);
-  p.alphas = a->w2_alphas;
-  p.out_f32 = reinterpret_cast<float*>(base + L.routed);
-  p.E = E;
-  p.kdim = I;
-  p.k_blocks = ceil_div_i(I, kKPerStage);
-  p.atoms_k = ceil_div_i(I, 64);
-  p.w_rows = K;
-  p.sfb_rowgroups = ceil_div_i(K, 128);
-  p.out_cols = K;
-  p.n_tiles = ceil_div_i(K, 256);
-  p.n_step = 256;
-  p.sub0_base = 0;
-  p.sub1_base = 128;
-  p.sfb_rg0 = 0;
-  p.sfb_rg1 = 1;
-  p.rg_step = 2;
-  const int grid = a->num_sms > 0 ? a->num_sms : num_sms_cached();
-  return launch_gemm<KIND_NVFP4, EPI_FC2>(tmA, tmA_small, tmB, p, grid, stream);
-}
-
 // 2-D matrix of packed E2M1 values [rows][cols/2 bytes]; the TMA expands every 16 values (8 bytes)
 // to a 16-byte slot, which is the operand form kind::mxf8f6f4 reads.  Box = box_rows x 128 values.
 // The inner extent is declared rounded up to 128 values (a requirement of this TMA type); the
@@ -761,6 +712,17 @@ int make_tmap_fp4_unpack_2d(CUtensorMap* out, const void* base, uint64_t cols, u
   return r == CUDA_SUCCESS ? B200MOE_OK : B200MOE_ECUDA;
 }
 
+template <int KIND, int EPI, int BN>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmA_small,
+                       const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t s) {
+  auto kern = grouped_gemm_blockscaled_kernel<KIND, EPI, BN>;
+  constexpr int smem = gemm_smem_bytes<BN>();
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return B200MOE_ECUDA;
+  kern<<<grid, kGemmThreads, smem, s>>>(tmA, tmA_small, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
 static void fill_common(GemmParams& p, const b200moe_gemm_args* a, char* base) {
   const b200moe_scratch_layout& L = *a->layout;
   p.tile_base = reinterpret_cast<const int32_t*>(base + L.tile_base);
@@ -776,74 +738,96 @@ static void fill_common(GemmParams& p, const b200moe_gemm_args* a, char* base) {
   p.swigluoai = a->activation == B200MOE_ACT_SWIGLUOAI;
 }
 
-// w4a8_mx FC1.  Weight scales: E8M0 atoms [E][row-groups][ceil(K/128)][512] where, for a gated
-// activation, each half of W13 is padded to a multiple of 128 rows on its own (prepare_weights
-// builds this), so that every 128-row sub-tile starts on an atom boundary even when I % 128 != 0.
-int mx_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
+// Tile width: 256 unless the shape does not allow it (a gated FC1 needs I % 128 == 0 for it) or
+// B200MOE_TILE_N=128 asks for the narrow, double-buffered tile.
+static int preferred_tile_n() {
+  static int v = 0;
+  if (v == 0) {
+    const char* e = getenv("B200MOE_TILE_N");
+    v = (e != nullptr && atoi(e) == 128) ? 128 : 256;
+  }
+  return v;
+}
+
+template <int KIND, int EPI>
+static int launch_any(int bn, const CUtensorMap& tmA, const CUtensorMap& tmA_small,
+                      const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t s) {
+  if (bn == 256) return launch_gemm<KIND, EPI, 256>(tmA, tmA_small, tmB, p, grid, s);
+  return launch_gemm<KIND, EPI, 128>(tmA, tmA_small, tmB, p, grid, s);
+}
+
+// The first projection.  Gated activations: the weight scales are stored as PAIR atoms -- for every
+// block of 64 intermediate columns one 128-row atom chain holding the 64 up rows followed by the 64
+// gate rows (prepare_weights builds this from the checkpoint's scale tensor) -- so a tile is made of
+// pair groups (64 up rows + 64 gate rows) whose scales are one atom per MMA step.  The weight codes
+// are read where the checkpoint left them, with 64-row TMA boxes.
+template <int KIND>
+static int gemm1_any(const b200moe_gemm_args* a, cudaStream_t stream) {
   const b200moe_scratch_layout& L = *a->layout;
   const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
   const bool gated = a->activation != B200MOE_ACT_RELU2;
-  if (K % 64 != 0 || I % 32 != 0 || E > kMaxExperts || a->w13_sf == nullptr) return B200MOE_EINVAL;
+  const bool mx = KIND == KIND_MX;
+  if (K % 64 != 0 || I % 64 != 0 || E > kMaxExperts || a->w13_sf == nullptr) return B200MOE_EINVAL;
+  if (!mx && a->a2_gscale == nullptr) return B200MOE_EINVAL;
   const int w_rows = gated ? 2 * I : I;
-  const int half_groups = ceil_div_i(I, 128);
   char* base = static_cast<char*>(a->scratch);
   CUtensorMap tmA, tmA_small, tmB;
-  int rc = make_tmap_bytes_2d(&tmA, base + L.act_q, K, L.rows, 128);
+  const uint64_t a_row = mx ? K : K / 2;
+  int rc = make_tmap_bytes_2d(&tmA, base + L.act_q, a_row, L.rows, 128);
   if (rc != B200MOE_OK) return rc;
-  rc = make_tmap_bytes_2d(&tmA_small, base + L.act_q, K, L.rows, 32);
+  rc = make_tmap_bytes_2d(&tmA_small, base + L.act_q, a_row, L.rows, 32);
   if (rc != B200MOE_OK) return rc;
-  rc = make_tmap_fp4_unpack_2d(&tmB, a->w13, K, static_cast<uint64_t>(E) * w_rows, 128);
+  rc = mx ? make_tmap_fp4_unpack_2d(&tmB, a->w13, K, static_cast<uint64_t>(E) * w_rows, 64)
+          : make_tmap_bytes_2d(&tmB, a->w13, K / 2, static_cast<uint64_t>(E) * w_rows, 64);
   if (rc != B200MOE_OK) return rc;
   GemmParams p = {};
   fill_common(p, a, base);
   p.sfa = reinterpret_cast<const uint8_t*>(base + L.act_sf);
   p.sfb = a->w13_sf;
   p.alphas = a->w1_alphas;
+  p.gscale2 = a->a2_gscale;
   p.out_q = reinterpret_cast<uint8_t*>(base + L.mid_q);
   p.out_sf = reinterpret_cast<uint8_t*>(base + L.mid_sf);
   p.tap = a->fc1_tap;
   p.kdim = K;
-  p.k_blocks = ceil_div_i(K, 128);
-  p.atoms_k = ceil_div_i(K, 128);
+  p.k_blocks = ceil_div_i(K, mx ? 128 : 256);
+  p.atoms_k = ceil_div_i(K, mx ? 128 : 64);
   p.w_rows = w_rows;
   p.out_cols = I;
-  p.out_atoms = ceil_div_i(I, 128);
+  p.out_atoms = ceil_div_i(I, mx ? 128 : 64);
   const int grid = a->num_sms > 0 ? a->num_sms : num_sms_cached();
+  int bn = preferred_tile_n();
   if (gated) {
-    p.sfb_rowgroups = 2 * half_groups;
-    p.n_tiles = half_groups;
-    p.n_step = 128;
-    p.sub0_base = a->gate_first ? I : 0;
-    p.sub1_base = a->gate_first ? 0 : I;
-    p.sfb_rg0 = a->gate_first ? half_groups : 0;
-    p.sfb_rg1 = a->gate_first ? 0 : half_groups;
-    p.rg_step = 1;
+    p.sfb_rowgroups = I / 64;              // pair atoms
+    p.n_step = bn / 2;                     // intermediate columns per tile
+    p.n_tiles = ceil_div_i(I, p.n_step);
+    p.sub0_base = a->gate_first ? I : 0;   // up rows
+    p.sub1_base = a->gate_first ? 0 : I;   // gate rows
     if (!p.swigluoai && !(p.limit > 0.f))
-      return launch_gemm<KIND_MX, EPI_FC1_SILU>(tmA, tmA_small, tmB, p, grid, stream);
-    return launch_gemm<KIND_MX, EPI_FC1_GATED>(tmA, tmA_small, tmB, p, grid, stream);
+      return launch_any<KIND, EPI_FC1_SILU>(bn, tmA, tmA_small, tmB, p, grid, stream);
+    return launch_any<KIND, EPI_FC1_GATED>(bn, tmA, tmA_small, tmB, p, grid, stream);
   }
-  p.sfb_rowgroups = half_groups;
-  p.n_tiles = ceil_div_i(I, 256);
-  p.n_step = 256;
-  p.sub0_base = 0;
-  p.sub1_base = 128;
-  p.sfb_rg0 = 0;
-  p.sfb_rg1 = 1;
-  p.rg_step = 2;
-  return launch_gemm<KIND_MX, EPI_FC1_RELU2>(tmA, tmA_small, tmB, p, grid, stream);
+  p.sfb_rowgroups = ceil_div_i(I, 128);
+  p.n_step = bn;
+  p.n_tiles = ceil_div_i(I, bn);
+  return launch_any<KIND, EPI_FC1_RELU2>(bn, tmA, tmA_small, tmB, p, grid, stream);
 }
 
-int mx_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
+template <int KIND>
+static int gemm2_any(const b200moe_gemm_args* a, cudaStream_t stream) {
   const b200moe_scratch_layout& L = *a->layout;
   const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
+  const bool mx = KIND == KIND_MX;
   if (I % 64 != 0 || K % 16 != 0 || E > kMaxExperts || a->w2_sf == nullptr) return B200MOE_EINVAL;
   char* base = static_cast<char*>(a->scratch);
   CUtensorMap tmA, tmA_small, tmB;
-  int rc = make_tmap_bytes_2d(&tmA, base + L.mid_q, I, L.rows, 128);
+  const uint64_t a_row = mx ? I : I / 2;
+  int rc = make_tmap_bytes_2d(&tmA, base + L.mid_q, a_row, L.rows, 128);
   if (rc != B200MOE_OK) return rc;
-  rc = make_tmap_bytes_2d(&tmA_small, base + L.mid_q, I, L.rows, 32);
+  rc = make_tmap_bytes_2d(&tmA_small, base + L.mid_q, a_row, L.rows, 32);
   if (rc != B200MOE_OK) return rc;
-  rc = make_tmap_fp4_unpack_2d(&tmB, a->w2, I, static_cast<uint64_t>(E) * K, 128);
+  rc = mx ? make_tmap_fp4_unpack_2d(&tmB, a->w2, I, static_cast<uint64_t>(E) * K, 64)
+          : make_tmap_bytes_2d(&tmB, a->w2, I / 2, static_cast<uint64_t>(E) * K, 64);
   if (rc != B200MOE_OK) return rc;
   GemmParams p = {};
   fill_common(p, a, base);
@@ -852,20 +836,21 @@ int mx_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
   p.alphas = a->w2_alphas;
   p.out_f32 = reinterpret_cast<float*>(base + L.routed);
   p.kdim = I;
-  p.k_blocks = ceil_div_i(I, 128);
-  p.atoms_k = ceil_div_i(I, 128);
+  p.k_blocks = ceil_div_i(I, mx ? 128 : 256);
+  p.atoms_k = ceil_div_i(I, mx ? 128 : 64);
   p.w_rows = K;
   p.sfb_rowgroups = ceil_div_i(K, 128);
   p.out_cols = K;
-  p.n_tiles = ceil_div_i(K, 256);
-  p.n_step = 256;
-  p.sub0_base = 0;
-  p.sub1_base = 128;
-  p.sfb_rg0 = 0;
-  p.sfb_rg1 = 1;
-  p.rg_step = 2;
+  const int bn = preferred_tile_n();
+  p.n_step = bn;
+  p.n_tiles = ceil_div_i(K, bn);
   const int grid = a->num_sms > 0 ? a->num_sms : num_sms_cached();
-  return launch_gemm<KIND_MX, EPI_FC2>(tmA, tmA_small, tmB, p, grid, stream);
+  return launch_any<KIND, EPI_FC2>(bn, tmA, tmA_small, tmB, p, grid, stream);
 }
+
+int nvfp4_gemm1(const b200moe_gemm_args* a, cudaStream_t s) { return gemm1_any<KIND_NVFP4>(a, s); }
+int nvfp4_gemm2(const b200moe_gemm_args* a, cudaStream_t s) { return gemm2_any<KIND_NVFP4>(a, s); }
+int mx_gemm1(const b200moe_gemm_args* a, cudaStream_t s) { return gemm1_any<KIND_MX>(a, s); }
+int mx_gemm2(const b200moe_gemm_args* a, cudaStream_t s) { return gemm2_any<KIND_MX>(a, s); }
 
 }  // namespace b200moe

@@ -162,9 +162,12 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      tma_prefetch_desc(&tmA);
-      tma_prefetch_desc(&tmW);
+    // seven lanes walk the same loop, each issues one of the stage's seven copies
+    if (lane < 7) {
+      if (lane == 0) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmW);
+      }
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -185,14 +188,18 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
             break;
           }
           uint64_t* bar = &tail->full[stage];
-          mbar_expect_tx(bar, kSmemA + kSmemRaw + kSmemSf);
-          tma_load_2d(sA + stage * kSmemA, &tmA, bar, kb * kKPerStage, row0);
-          tma_load_2d(sRaw + stage * kSmemRaw, &tmW, bar, kb * 32, c.e * p.w_rows + r0);
-          tma_load_2d(sRaw + stage * kSmemRaw + 128 * 32, &tmW, bar, kb * 32, c.e * p.w_rows + r1);
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
+          if (lane == 0) {
+            mbar_expect_tx(bar, kSmemA + kSmemRaw + kSmemSf);
+            tma_load_2d(sA + stage * kSmemA, &tmA, bar, kb * kKPerStage, row0);
+          } else if (lane == 1) {
+            tma_load_2d(sRaw + stage * kSmemRaw, &tmW, bar, kb * 32, c.e * p.w_rows + r0);
+          } else if (lane == 2) {
+            tma_load_2d(sRaw + stage * kSmemRaw + 128 * 32, &tmW, bar, kb * 32, c.e * p.w_rows + r1);
+          } else {
+            const int q = lane - 3;
             bulk_load(sSf + stage * kSmemSf + q * 512,
                       sf_e + (static_cast<size_t>(g[q]) * p.atoms_k + kb) * 512, 512, bar);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;

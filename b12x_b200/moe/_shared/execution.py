@@ -192,8 +192,8 @@ def plan_moe_weight_preparation(specs, *, num_experts, hidden_size, intermediate
     k, n = int(hidden_size), int(intermediate_size)
     for spec in specs:
         if spec.quant_mode == "nvfp4":
-            if k % 64 != 0 or n % 128 != 0:
-                raise ValueError("nvfp4 requires hidden_size % 64 == 0 and intermediate_size % 128 == 0")
+            if k % 64 != 0 or n % 64 != 0:
+                raise ValueError("nvfp4 requires hidden_size and intermediate_size divisible by 64")
             transforms.add(WeightPreparationTransform.RUNTIME_ALPHAS)
         elif spec.quant_mode == "w4a8_mx":
             if k % 32 != 0 or n % 32 != 0:

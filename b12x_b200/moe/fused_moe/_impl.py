@@ -132,6 +132,30 @@ def _swizzle_scale_grid(grid: torch.Tensor) -> torch.Tensor:
     return sw.reshape(e, rp, cp)
 
 
+def _unswizzle_scale_grid(sw: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
+    """Inverse of :func:`_swizzle_scale_grid` for one expert: -> [rows, cols] bytes."""
+    rp, cp = _align_up(rows, 128), _align_up(cols, 4)
+    u = sw.reshape(-1)[: rp * cp].reshape(rp // 128, cp // 4, 32, 4, 4).permute(0, 3, 2, 1, 4)
+    return u.contiguous().reshape(rp, cp)[:rows, :cols]
+
+
+def _pair_scale_atoms(grid: torch.Tensor, intermediate: int, gate_first: bool) -> torch.Tensor:
+    """FC1 scales of a gated activation, re-laid as PAIR atoms.
+
+    ``grid`` is the plain ``[E, 2I, cols]`` byte grid of W13's block scales.  The FC1 kernel works on
+    tiles of 64 up rows + 64 gate rows, so the scales of such a tile must form one 128-row atom
+    chain: rows are re-ordered to [up 0..63, gate 0..63, up 64..127, gate 64..127, ...] and then
+    swizzled.  The weight codes themselves are not touched (the kernel fetches the two 64-row
+    halves with separate TMA boxes); this scale tensor is a new allocation of the source's size."""
+    e, rows, cols = grid.shape
+    i = int(intermediate)
+    if rows != 2 * i or i % 64 != 0:
+        raise ValueError("gated FC1 needs [E, 2I, cols] scales with I a multiple of 64")
+    up, gate = (grid[:, i:], grid[:, :i]) if gate_first else (grid[:, :i], grid[:, i:])
+    paired = torch.stack([up.reshape(e, i // 64, 64, cols), gate.reshape(e, i // 64, 64, cols)], dim=2)
+    return _swizzle_scale_grid(paired.reshape(e, 2 * i, cols))
+
+
 def _with_tail_slack(w: torch.Tensor, cols: int) -> torch.Tensor:
     if cols % 128 == 0:
         return w
@@ -188,10 +212,7 @@ def prepare_b12x_fp4_moe_weights(
         if tuple(s2.shape) != (e, plan.hidden_size, plan.intermediate_size // 32):
             raise ValueError("fp4_e8m0_k32 w2_blockscale must be [E, K, I/32] E8M0 bytes")
         if is_gated_moe_activation(plan.activation):
-            # each half of W13 gets its own 128-row padding, so a 128-row weight tile of either
-            # half starts on an atom boundary even when I is not a multiple of 128
-            i = plan.intermediate_size
-            s1 = torch.cat([_swizzle_scale_grid(s1[:, :i]), _swizzle_scale_grid(s1[:, i:])], dim=1)
+            s1 = _pair_scale_atoms(s1.view(torch.uint8), plan.intermediate_size, plan.w13_layout == "w31")
         else:
             s1 = _swizzle_scale_grid(s1)
         s2 = _swizzle_scale_grid(s2)
@@ -208,6 +229,13 @@ def prepare_b12x_fp4_moe_weights(
                 "modelopt_nvfp4 block scales must be 128x4-swizzled "
                 f"{exp1} / {exp2}, got {tuple(s1.shape)} / {tuple(s2.shape)}")
         s1, s2 = s1.view(torch.uint8), s2.view(torch.uint8)
+        if "nvfp4" in plan.quant_modes and is_gated_moe_activation(plan.activation):
+            if "w4a16" in plan.quant_modes:
+                raise ValueError("one weight plan cannot serve both nvfp4 and w4a16: they need "
+                                 "different FC1 scale layouts")
+            rows, cols = plan.w1_rows, plan.hidden_size // 16
+            grid = torch.stack([_unswizzle_scale_grid(s1[ei], rows, cols) for ei in range(e)])
+            s1 = _pair_scale_atoms(grid, plan.intermediate_size, plan.w13_layout == "w31")
     return B12XFP4ExpertWeights(
         plan=plan, a1_gscale=a1, w1_fp4=w1_fp4.view(torch.uint8), w1_blockscale=s1.contiguous(),
         w1_alphas=alphas1.contiguous(), a2_gscale=a2, w2_fp4=w2_fp4.view(torch.uint8),
