@@ -688,6 +688,8 @@ static int num_sms_cached() {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    const char* e = getenv("B200MOE_NUM_SMS");   // persistent grid size override (experiments)
+    if (e != nullptr && atoi(e) > 0 && atoi(e) < n) n = atoi(e);
   }
   return n;
 }

@@ -115,12 +115,14 @@ class _LayerBase:
         total_bytes = weight_bytes + rows * (a_bytes + o_bytes)
         flops = 2.0 * rows * w1_rows * k
         # the layer is weight-streaming bound while the rows per expert are few
-        intensity = flops / max(total_bytes, 1.0)
-        bound = "hbm" if intensity < 1000 else "tensor"
-        peak_tf = {"nvfp4": 9000.0, "w4a8_mx": 4500.0, "w4a16": 2250.0}[local_shape.recipe]
+        # (a 128-row tile needs ~64 rows per active expert before the tensor pipe, not HBM, limits)
+        bound = "hbm" if rows < 64 * max(active_experts, 1) else "tensor"
+        # tensor rate of the operand type relative to dense bf16 (the measured peak is a bf16 GEMM)
+        rate = {"nvfp4": 4.0, "w4a8_mx": 2.0, "w4a16": 1.0}[local_shape.recipe]
         return {"kernel": "grouped_gemm1_act", "stage": "gemm1", "bound": bound, "bytes": total_bytes,
-                "flops": flops, "peak_tflops": peak_tf,
-                "peak_note": "" if bound == "hbm" else " (tensor peak: nominal dense figure for the operand type)"}
+                "flops": flops, "bf16_rate_multiple": rate,
+                "peak_note": "" if bound == "hbm" else
+                f" bf16 GEMM peak x {rate:g} (the operand type's tensor rate relative to bf16)"}
 
 
 class ExpertParallelMoE(_LayerBase):

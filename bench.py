@@ -304,7 +304,7 @@ def main():
             peak, unit = peaks["hbm_gbs"], "GB/s"
         else:
             achieved = dom["flops"] / (dom_ms * 1e-3) / 1e12
-            peak, unit = dom["peak_tflops"], "TFLOP/s"
+            peak, unit = peaks["bf16_tflops"] * dom["bf16_rate_multiple"], "TFLOP/s"
         line = {
             "metric": "moe_layer_tokens_per_s", "value": total_tokens / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
