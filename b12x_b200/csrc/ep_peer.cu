@@ -1,0 +1,231 @@
+// Expert-parallel dispatch and combine over NVLink peer memory (one process per GPU, buffers in
+// symmetric memory so that every rank holds a device pointer to every peer's copy).
+//
+//   dispatch : each rank copies its routed rows straight into the destination ranks' receive
+//              buffers (plain peer stores), in the order of the preceding sort by destination rank;
+//              rank `r` owns the slots [r*cap, (r+1)*cap) of every receive buffer, writes the
+//              destination-local expert id of each row next to it and -1 into its unused slots,
+//              and finally raises flag[r] = epoch on every peer.
+//   wait     : a one-warp kernel that polls this rank's flags until all peers have reached `epoch`.
+//              The poll is bounded (2 s); on expiry it records an error in the status block and
+//              returns, so a missing peer never hangs the GPU.
+//   combine  : the home rank pulls the per-route FC2 rows (fp32) of its tokens from the experts'
+//              ranks with plain peer loads and sums them in slot order, exactly as the single-GPU
+//              combine does -- the return all-to-all and the weighted sum are one kernel.
+//
+// No kernel here uses multimem or cluster features; peers are only touched with ld/st.global.
+// The reference library has no counterpart (its ep_moe replicates the input and lets the caller
+// sum partial outputs, b12x/moe/ep_moe/_impl.py:1-14).
+#include "common.cuh"
+
+namespace b200moe {
+
+__device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int32_t* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+struct PeerPtrs {
+  void* p[B200MOE_MAX_RANKS];
+};
+
+__global__ void __launch_bounds__(256) ep_dispatch_kernel(
+    const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, const int32_t* __restrict__ topk_ids,
+    const int32_t* __restrict__ group_offsets, const int32_t* __restrict__ sorted_route_ids,
+    PeerPtrs rows, PeerPtrs ids, PeerPtrs flags, int32_t* done_counter, int world, int rank,
+    int num_topk, int K, int local_modulus, int cap, int epoch) {
+  __shared__ int offs[B200MOE_MAX_RANKS + 1];
+  if (threadIdx.x <= world) offs[threadIdx.x] = group_offsets[threadIdx.x];
+  __syncthreads();
+  const int total = offs[world];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int pos = blockIdx.x * 8 + warp; pos < total; pos += gridDim.x * 8) {
+    int d = 0;
+    while (d + 1 < world && pos >= offs[d + 1]) ++d;
+    const int slot = rank * cap + (pos - offs[d]);
+    const int r = sorted_route_ids[pos];
+    const int t = r / num_topk;
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(t) * x_row_stride);
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(rows.p[d]) +
+                                          static_cast<size_t>(slot) * K);
+    for (int j = lane; j < (K >> 3); j += 32) dst[j] = __ldg(src + j);
+    if (lane == 0) static_cast<int32_t*>(ids.p[d])[slot] = topk_ids[r] % local_modulus;
+  }
+  // unused slots of this rank's region on every peer: no route
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < world * cap; i += gridDim.x * blockDim.x) {
+    const int d = i / cap, j = i - d * cap;
+    if (j >= offs[d + 1] - offs[d]) static_cast<int32_t*>(ids.p[d])[rank * cap + j] = -1;
+  }
+  // last block out raises the flags: every block publishes its peer stores first
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(done_counter, 1);
+    if (prev == static_cast<int>(gridDim.x) - 1) {
+      *done_counter = 0;
+      __threadfence_system();
+      for (int d = 0; d < world; ++d) st_release_sys(static_cast<int32_t*>(flags.p[d]) + rank, epoch);
+    }
+  }
+}
+
+__global__ void ep_signal_kernel(PeerPtrs flags, int world, int rank, int epoch) {
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<int32_t*>(flags.p[threadIdx.x]) + rank, epoch);
+  }
+}
+
+__global__ void ep_wait_kernel(const int32_t* __restrict__ flags, int world, int epoch,
+                               int32_t* __restrict__ status) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  unsigned long long t0 = 0;
+  uint32_t spins = 0;
+  while (ld_acquire_sys(flags + r) < epoch) {
+    if ((++spins & 0x3ffu) == 0) {
+      const unsigned long long now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitNs) {
+        if (status != nullptr) {
+          atomicCAS(status, 0, 1);
+          atomicCAS(status + 1, 0, 16 + r);   // 16 + peer rank: that peer never arrived
+        }
+        return;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) ep_combine_pull_kernel(
+    const int32_t* __restrict__ group_offsets, const int32_t* __restrict__ inv_perm,
+    const float* __restrict__ topk_weights, PeerPtrs arenas, int64_t peer_inv_perm_off,
+    int64_t peer_routed_off, __nv_bfloat16* __restrict__ out, int64_t out_row_stride, int world,
+    int rank, int num_topk, int K, int cap, float output_scale) {
+  extern __shared__ unsigned char sm_raw[];
+  const float** rowp = reinterpret_cast<const float**>(sm_raw);
+  float* w = reinterpret_cast<float*>(sm_raw + num_topk * sizeof(float*));
+  const int t = blockIdx.x;
+  for (int s = threadIdx.x; s < num_topk; s += blockDim.x) {
+    const int pos = inv_perm[static_cast<int64_t>(t) * num_topk + s];
+    const float* rp = nullptr;
+    if (pos >= 0) {
+      int d = 0;
+      while (d + 1 < world && pos >= group_offsets[d + 1]) ++d;
+      const int slot = rank * cap + (pos - group_offsets[d]);
+      const char* arena = static_cast<const char*>(arenas.p[d]);
+      const int p = reinterpret_cast<const int32_t*>(arena + peer_inv_perm_off)[slot];
+      if (p >= 0) rp = reinterpret_cast<const float*>(arena + peer_routed_off) + static_cast<size_t>(p) * K;
+    }
+    rowp[s] = rp;
+    w[s] = topk_weights[static_cast<int64_t>(t) * num_topk + s];
+  }
+  __syncthreads();
+  const int nvec = K >> 2;
+  for (int j = threadIdx.x; j < nvec; j += blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < num_topk; ++s) {
+      if (rowp[s] == nullptr) continue;
+      const float4 v = *(reinterpret_cast<const float4*>(rowp[s]) + j);
+      const float ws = w[s];
+      acc.x = __fadd_rn(acc.x, __fmul_rn(ws, v.x));
+      acc.y = __fadd_rn(acc.y, __fmul_rn(ws, v.y));
+      acc.z = __fadd_rn(acc.z, __fmul_rn(ws, v.z));
+      acc.w = __fadd_rn(acc.w, __fmul_rn(ws, v.w));
+    }
+    __nv_bfloat16 b[4] = {__float2bfloat16_rn(acc.x), __float2bfloat16_rn(acc.y),
+                          __float2bfloat16_rn(acc.z), __float2bfloat16_rn(acc.w)};
+    if (output_scale != 1.0f) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        b[q] = __float2bfloat16_rn(__fmul_rn(__bfloat162float(b[q]), output_scale));
+    }
+    uint2 pk;
+    pk.x = static_cast<uint32_t>(__bfloat16_as_ushort(b[0])) |
+           (static_cast<uint32_t>(__bfloat16_as_ushort(b[1])) << 16);
+    pk.y = static_cast<uint32_t>(__bfloat16_as_ushort(b[2])) |
+           (static_cast<uint32_t>(__bfloat16_as_ushort(b[3])) << 16);
+    reinterpret_cast<uint2*>(out + static_cast<int64_t>(t) * out_row_stride)[j] = pk;
+  }
+}
+
+}  // namespace b200moe
+
+using namespace b200moe;
+
+static bool fill_peers(PeerPtrs& dst, void* const* src, int world) {
+  for (int i = 0; i < B200MOE_MAX_RANKS; ++i) dst.p[i] = i < world ? src[i] : nullptr;
+  for (int i = 0; i < world; ++i)
+    if (dst.p[i] == nullptr) return false;
+  return true;
+}
+
+extern "C" int b200moe_ep_dispatch(const b200moe_ep_dispatch_args* a, void* stream) {
+  if (a == nullptr || a->x == nullptr || a->topk_ids == nullptr || a->scratch == nullptr ||
+      a->layout == nullptr || a->done_counter == nullptr)
+    return B200MOE_EINVAL;
+  if (a->world < 1 || a->world > B200MOE_MAX_RANKS || a->rank < 0 || a->rank >= a->world ||
+      a->hidden_size <= 0 || a->hidden_size % 8 != 0 || a->local_modulus <= 0 || a->cap_rows <= 0)
+    return B200MOE_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(a->x) & 15) != 0 || (a->x_row_stride % 8) != 0) return B200MOE_EALIGN;
+  const int rows = a->num_tokens * a->num_topk;
+  if (rows > a->layout->rows || rows > a->cap_rows) return B200MOE_ECAPACITY;
+  PeerPtrs rows_p, ids_p, flags_p;
+  if (!fill_peers(rows_p, a->peer_rows, a->world) || !fill_peers(ids_p, a->peer_ids, a->world) ||
+      !fill_peers(flags_p, a->peer_flags, a->world))
+    return B200MOE_EINVAL;
+  const b200moe_scratch_layout& L = *a->layout;
+  char* base = static_cast<char*>(a->scratch);
+  int grid = (rows + 7) / 8;
+  grid = grid < 1 ? 1 : (grid > 148 * 2 ? 148 * 2 : grid);
+  ep_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride, a->topk_ids,
+      reinterpret_cast<const int32_t*>(base + L.expert_offsets),
+      reinterpret_cast<const int32_t*>(base + L.sorted_route_ids), rows_p, ids_p, flags_p,
+      a->done_counter, a->world, a->rank, a->num_topk, a->hidden_size, a->local_modulus, a->cap_rows,
+      a->epoch);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+extern "C" int b200moe_ep_signal(void* const* peer_flags, int32_t world, int32_t rank, int32_t epoch,
+                                 void* stream) {
+  if (peer_flags == nullptr || world < 1 || world > B200MOE_MAX_RANKS || rank < 0 || rank >= world)
+    return B200MOE_EINVAL;
+  PeerPtrs flags_p;
+  if (!fill_peers(flags_p, peer_flags, world)) return B200MOE_EINVAL;
+  ep_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags_p, world, rank, epoch);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+extern "C" int b200moe_ep_wait(const int32_t* flags, int32_t world, int32_t epoch, int32_t* status,
+                               void* stream) {
+  if (flags == nullptr || world < 1 || world > B200MOE_MAX_RANKS) return B200MOE_EINVAL;
+  ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+extern "C" int b200moe_ep_combine(const b200moe_ep_combine_args* a, void* stream) {
+  if (a == nullptr || a->topk_weights == nullptr || a->out == nullptr || a->scratch == nullptr ||
+      a->layout == nullptr)
+    return B200MOE_EINVAL;
+  if (a->world < 1 || a->world > B200MOE_MAX_RANKS || a->rank < 0 || a->rank >= a->world ||
+      a->hidden_size <= 0 || a->hidden_size % 4 != 0 || a->num_topk <= 0 || a->cap_rows <= 0)
+    return B200MOE_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(a->out) & 7) != 0 || (a->out_row_stride % 4) != 0) return B200MOE_EALIGN;
+  if (a->num_tokens * a->num_topk > a->layout->rows) return B200MOE_ECAPACITY;
+  if (a->num_tokens == 0) return B200MOE_OK;
+  PeerPtrs arenas;
+  if (!fill_peers(arenas, a->peer_scratch, a->world)) return B200MOE_EINVAL;
+  const b200moe_scratch_layout& L = *a->layout;
+  char* base = static_cast<char*>(a->scratch);
+  ep_combine_pull_kernel<<<a->num_tokens, 256, a->num_topk * 16, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const int32_t*>(base + L.expert_offsets),
+      reinterpret_cast<const int32_t*>(base + L.inv_perm), a->topk_weights, arenas,
+      a->peer_inv_perm_off, a->peer_routed_off, static_cast<__nv_bfloat16*>(a->out), a->out_row_stride,
+      a->world, a->rank, a->num_topk, a->hidden_size, a->cap_rows, a->output_scale);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}

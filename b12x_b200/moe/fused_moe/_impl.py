@@ -426,6 +426,7 @@ class TPMoEScratchPlan:
         output_f32: torch.Tensor | None = None,
         output_scale: float = 1.0,
         f32_only: bool = False,
+        skip_combine: bool = False,
     ) -> "TPMoEFP4Binding":
         """Validate the call and map the caller's scratch into kernel-argument views.
 
@@ -476,7 +477,8 @@ class TPMoEScratchPlan:
             swiglu_limit=caps.swiglu_limit, swiglu_alpha=caps.swiglu_alpha,
             swiglu_beta=caps.swiglu_beta, route_expert_map=route_expert_map,
             kernel_workspace=core, core_layout=self._core_layout, fc1_tap=fc1_tap,
-            output_f32=output_f32, output_scale=float(output_scale), f32_only=bool(f32_only))
+            output_f32=output_f32, output_scale=float(output_scale), f32_only=bool(f32_only),
+            skip_combine=bool(skip_combine))
 
 
 def plan_tp_moe_scratch(caps: TPMoEScratchCaps) -> TPMoEScratchPlan:
@@ -533,6 +535,7 @@ class TPMoEFP4Binding:
     output_f32: torch.Tensor | None = None
     output_scale: float = 1.0
     f32_only: bool = False     # write only ``output_f32`` (un-rounded sums), skip the bf16 output
+    skip_combine: bool = False  # stop after FC2: the per-route rows stay in ``route_output``
 
     # ---- scratch views (valid after run) ----
     def _v(self, name: str, count: int, dtype: torch.dtype) -> torch.Tensor:
@@ -618,7 +621,9 @@ def b12x_moe_fp4(*, binding: TPMoEFP4Binding, stage_timer=None) -> torch.Tensor:
     lib = ext.load()
     tokens = b.tokens
     out = b.output
-    if b.f32_only:
+    if b.skip_combine:
+        out = b.route_output
+    elif b.f32_only:
         if b.output_f32 is None:
             raise ValueError("f32_only needs output_f32")
         out = b.output_f32
@@ -666,6 +671,8 @@ def b12x_moe_fp4(*, binding: TPMoEFP4Binding, stage_timer=None) -> torch.Tensor:
     ext.check(lib.b200moe_grouped_gemm2(C.byref(gargs), stream), "grouped_gemm2")
     mark("gemm2")
 
+    if b.skip_combine:
+        return out
     if not b.f32_only:
         cargs = ext.CombineArgs(b.topk_weights.data_ptr(), out.data_ptr(), scratch, lp, out.stride(0),
                                 tokens, b.num_topk, b.k, 0, float(b.output_scale), 0)

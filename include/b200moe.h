@@ -232,6 +232,54 @@ typedef struct {
 } b200moe_combine_args;
 int b200moe_combine(const b200moe_combine_args* a, void* stream);
 
+/* ---- expert parallelism over NVLink peer memory --------------------------- */
+/* No counterpart in the reference (b12x/moe/ep_moe/_impl.py:1-14 replicates the input on every
+ * rank and leaves the sum of partial outputs to the caller).  One process per GPU; the buffers
+ * named peer_* live in symmetric memory, i.e. the caller holds a device pointer to every rank's
+ * copy.  Rank r owns slots [r*cap_rows, (r+1)*cap_rows) of every receive buffer.  Flags are int32
+ * arrays of B200MOE_MAX_RANKS entries per rank, zero before the first step; `epoch` must grow by
+ * one per step.  The only device-side wait (b200moe_ep_wait) is bounded: after 2 s it writes
+ * status[0] = 1, status[1] = 16 + the missing peer, and returns. */
+#define B200MOE_MAX_RANKS 16
+typedef struct {
+  const void* x;             /* bf16 [T][x_row_stride]                          */
+  const int32_t* topk_ids;   /* [T*k] global expert ids                         */
+  void* peer_rows[B200MOE_MAX_RANKS];   /* bf16 [world*cap_rows][hidden] on each rank   */
+  void* peer_ids[B200MOE_MAX_RANKS];    /* int32 [world*cap_rows] on each rank          */
+  void* peer_flags[B200MOE_MAX_RANKS];  /* int32 [B200MOE_MAX_RANKS] on each rank       */
+  int32_t* done_counter;     /* local int32, zero; the kernel leaves it zero    */
+  void* scratch;             /* home arena, already sorted by destination rank  */
+  const b200moe_scratch_layout* layout; /* HOST pointer                        */
+  int64_t x_row_stride;
+  int32_t num_tokens, num_topk, world, rank;
+  int32_t hidden_size, local_modulus, cap_rows, epoch;
+} b200moe_ep_dispatch_args;
+/* Pack rows by destination rank, store them and their local expert ids into the peers' receive
+ * buffers, mark this rank's unused slots with -1, then raise peer_flags[d][rank] = epoch. */
+int b200moe_ep_dispatch(const b200moe_ep_dispatch_args* a, void* stream);
+/* Raise peer_flags[d][rank] = epoch on every rank once the stream's earlier work is done. */
+int b200moe_ep_signal(void* const* peer_flags /* HOST array */, int32_t world, int32_t rank,
+                      int32_t epoch, void* stream);
+/* Return (on the stream) when flags[r] >= epoch for every r < world, or after the time limit. */
+int b200moe_ep_wait(const int32_t* flags, int32_t world, int32_t epoch, int32_t* status, void* stream);
+
+typedef struct {
+  const float* topk_weights; /* [T][k]                                          */
+  void* out;                 /* bf16 [T][out_row_stride]                        */
+  void* peer_scratch[B200MOE_MAX_RANKS]; /* the experts' arenas (all ranks share one layout) */
+  void* scratch;             /* home arena                                      */
+  const b200moe_scratch_layout* layout; /* HOST pointer, home arena             */
+  int64_t peer_inv_perm_off, peer_routed_off;  /* offsets inside an expert arena */
+  int64_t out_row_stride;
+  int32_t num_tokens, num_topk, world, rank;
+  int32_t hidden_size, cap_rows;
+  float output_scale;
+  int32_t reserved;
+} b200moe_ep_combine_args;
+/* out[t] = sum over slots of w[t,slot] * (FC2 row of that route, read from the rank that computed
+ * it), fp32, slot order, one bf16 rounding: the return all-to-all and the combine in one kernel. */
+int b200moe_ep_combine(const b200moe_ep_combine_args* a, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

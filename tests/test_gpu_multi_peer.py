@@ -1,0 +1,66 @@
+"""-m gpu, needs >= 2 GPUs: expert parallelism with this library's own dispatch / combine kernels
+over NVLink peer memory, against the single-process CPU oracle, several steps in a row."""
+
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from b12x_b200 import synth
+from tests.test_gpu_multi import _free_port
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank: int, world: int, port: int, ret: dict):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    from b12x_b200.moe.distributed import init_process_group
+    from b12x_b200.moe.ep_peer import PeerExpertParallelMoE
+    from oracle import moe_oracle as O
+    init_process_group(dev)
+    try:
+        tpr = 40
+        shp = synth.shape("c1", name="ep", tokens=tpr * world, hidden=512, intermediate=256, experts=8, topk=3)
+        full = synth.make_inputs(shp, seed=41)
+        layer = PeerExpertParallelMoE.from_global(full, dev, rank, world, tpr)
+        ok = True
+        for step in range(3):                 # new tokens every step: slots and flags are reused
+            g = torch.Generator().manual_seed(100 + step)
+            xs = torch.randn(tpr * world, shp.hidden, generator=g).to(torch.bfloat16)
+            lgs = torch.randn(tpr * world, shp.experts, generator=g)
+            lo = rank * tpr
+            x, lg = xs[lo:lo + tpr], lgs[lo:lo + tpr]
+            out = layer.forward(x.to(dev), lg.to(dev)).float().cpu()
+            torch.cuda.synchronize()
+            layer.check_status()
+            _, ids, w = O.route_topk(lg, shp.topk)
+            a1 = full.w1_global_scale / full.a1_gscale
+            a2 = full.w2_global_scale / full.a2_gscale
+            ref = O.moe_nvfp4(x, full.w1_fp4, full.w1_blockscale, a1, full.w2_fp4, full.w2_blockscale, a2,
+                              full.a1_gscale, full.a2_gscale, ids, w).float()
+            # fp32 rows combined in slot order, as on one GPU: the only differences to the CPU oracle
+            # are single bf16 roundings (device exp() vs host exp() in the activation)
+            same = (out - ref).abs().max().item() <= 2.0 ** -8 * ref.abs().max().item()
+            if not same:
+                print(f"rank {rank} step {step}: max abs diff {(out - ref).abs().max().item():.4e}, "
+                      f"ref max {ref.abs().max().item():.4e}, rows differing "
+                      f"{int(((out - ref).abs().amax(dim=1) > 0).sum())}/{out.shape[0]}", flush=True)
+            ok = ok and same
+        ret[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+def test_peer_memory_expert_parallel_matches_oracle():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+        assert dict(ret) == {0: True, 1: True}
