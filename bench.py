@@ -43,6 +43,8 @@ def parse_args():
     ap.add_argument("--workload", default="c2", choices=sorted(synth.SHAPES))
     ap.add_argument("--tokens", type=int, default=None, help="tokens per GPU (default: the workload's)")
     ap.add_argument("--experts", type=int, default=None, help="override the expert count (small profiling cases)")
+    ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
+                    help="expert-parallel exchange: own kernels over peer memory, or NCCL all-to-all")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-experts", type=int, default=8, help="experts in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -200,11 +202,12 @@ def dtype_of(shp) -> str:
             "w4a16": "bf16 x fp4-dequant (fp32 accumulate)"}[shp.recipe]
 
 
-def config_of(shp, n_gpus: int) -> dict:
+def config_of(shp, n_gpus: int, ep: str = "peer") -> dict:
     return {"workload": shp.name, "tokens_per_gpu": shp.tokens, "hidden": shp.hidden,
             "intermediate": shp.intermediate, "experts": shp.experts, "top_k": shp.topk,
             "recipe": shp.recipe, "activation": shp.activation, "router": shp.router,
             "parallelism": ("single" if n_gpus == 1 else f"{shp.parallelism}{n_gpus}"),
+            "exchange": ("none" if n_gpus == 1 else ("nccl all-reduce" if shp.parallelism == "tp" else ep)),
             "l2": "no flush: the expert weights read per step exceed the 126 MB L2"}
 
 
@@ -240,6 +243,10 @@ def main():
 
     if world > 1 and shp.parallelism == "tp":
         layer = TensorParallelMoE.from_synthetic(shp, dev, rank, world)
+    elif world > 1 and args.ep == "peer":
+        # dispatch / combine by this library's kernels over NVLink peer memory
+        from b12x_b200.moe.ep_peer import PeerExpertParallelMoE
+        layer = PeerExpertParallelMoE.from_synthetic(shp, dev, rank, world)
     else:
         layer = ExpertParallelMoE.from_synthetic(shp, dev, rank, world)
 
@@ -309,7 +316,7 @@ def main():
             "metric": "moe_layer_tokens_per_s", "value": total_tokens / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_of(shp),
-            "data": "synthetic", "config": config_of(shp, world), "clocks": clocks,
+            "data": "synthetic", "config": config_of(shp, world, args.ep), "clocks": clocks,
             "e2e": {"value": total_tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2 + lg_host.numel() * 4,
                     "d2h_bytes_per_step": out_host.numel() * 2},
