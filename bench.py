@@ -77,12 +77,28 @@ class ClockSampler:
             f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
             self.path = f.name
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu)], stdout=f, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
-    def stop(self) -> dict:
+    def _lines(self):
+        try:
+            return Path(self.path).read_text().splitlines()
+        except OSError:
+            return []
+
+    def wait_first(self, timeout_s: float = 4.0) -> None:
+        """Block until nvidia-smi has written its first sample (its start-up takes about a second)."""
+        t0 = time.perf_counter()
+        while self.proc is not None and not self._lines() and time.perf_counter() - t0 < timeout_s:
+            time.sleep(0.02)
+
+    def mark(self) -> int:
+        """Index of the next sample: brackets the timed region."""
+        return len(self._lines())
+
+    def stop(self, lo: int = 0, hi: int | None = None) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -90,9 +106,13 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        lines = self._lines()
+        hi = len(lines) if hi is None else hi
+        # a region shorter than the sampling period: take the samples either side of it
+        window = lines[lo:hi] if hi > lo else lines[max(lo - 1, 0):hi + 1]
         sm, smax, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in Path(self.path).read_text().splitlines():
+        for line in window:
             c = [x.strip() for x in line.split(",")]
             if len(c) < 9:
                 continue
@@ -263,20 +283,21 @@ def main():
         torch.cuda.synchronize()
 
     # ---------------- device-resident leg ----------------
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         layer.forward(x_dev, lg_dev)
     barrier()
-    sampler = ClockSampler(local_rank)
+    sampler.wait_first()
     timer = StageTimer()
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    mark_lo = sampler.mark()
     e0.record()
     for _ in range(args.steps):
         layer.forward(x_dev, lg_dev, stage_timer=timer)
     e1.record()
     barrier()
-    clocks = sampler.stop()
     ms = e0.elapsed_time(e1) / args.steps
     layer.check_status()
 
@@ -293,6 +314,7 @@ def main():
     h1.record()
     barrier()
     ms_e2e = h0.elapsed_time(h1) / e2e_steps
+    clocks = sampler.stop(mark_lo, sampler.mark())   # both timed legs run between the marks
 
     if world > 1:
         tmax = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
@@ -339,12 +361,18 @@ def main():
                 _, ids, w = O.route_topk(inp_cpu.router_logits, shp.topk, mode="sigmoid", route_scale=shp.route_scale)
             else:
                 _, ids, w = O.route_topk(inp_cpu.router_logits, shp.topk)
-            sec, kept = oracle_sample(shp, inp_cpu, ids, w, n_e)
+            # bounded sample: repeat the pass until about ten seconds of CPU work are on the clock
+            total, reps, kept = 0.0, 0, 0
+            while total < 10.0 and reps < 64:
+                sec, kept = oracle_sample(shp, inp_cpu, ids, w, n_e)
+                total += sec
+                reps += 1
+            sec = total / reps
             line["cpu_baseline"] = {
                 "value": (kept / shp.topk) / sec, "unit": "tokens/s", "cores": cores, "kind": "port",
-                "seconds": sec,
+                "seconds": total, "passes": reps,
                 "sample": f"routes of one {shp.tokens}-token batch that land on experts 0..{n_e - 1} "
-                          f"({kept} of {shp.rows} routed rows); tokens = rows / top-k"}
+                          f"({kept} of {shp.rows} routed rows), {reps} passes; tokens = rows / top-k"}
         print(json.dumps(line), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()
