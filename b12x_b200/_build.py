@@ -18,6 +18,7 @@ SOURCES = (
     "route_sort.cu",
     "quant_combine.cu",
     "grouped_gemm_bs.cu",
+    "grouped_gemm_small.cu",
     "grouped_gemm_other.cu",
     "ep_peer.cu",
 )
@@ -45,7 +46,7 @@ def needs_build() -> bool:
     if not LIB_PATH.exists():
         return True
     built = LIB_PATH.stat().st_mtime
-    deps = [CSRC / s for s in SOURCES] + [CSRC / "common.cuh", CSRC.parents[1] / "include" / "b200moe.h"]
+    deps = [CSRC / s for s in SOURCES] + [CSRC / "common.cuh", CSRC / "gemm_shared.cuh", CSRC.parents[1] / "include" / "b200moe.h"]
     return any(d.stat().st_mtime > built for d in deps)
 
 

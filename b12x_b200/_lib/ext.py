@@ -27,14 +27,15 @@ class DeviceInfo(C.Structure):
 class CapsC(C.Structure):
     _fields_ = [("max_tokens", C.c_int32), ("num_topk", C.c_int32), ("num_experts", C.c_int32),
                 ("hidden_size", C.c_int32), ("intermediate", C.c_int32), ("recipe", C.c_int32),
-                ("activation", C.c_int32), ("reserved", C.c_int32)]
+                ("activation", C.c_int32), ("tile_rows", C.c_int32)]
 
 
 class ScratchLayout(C.Structure):
     _fields_ = [(n, C.c_int64) for n in (
         "total_nbytes", "status", "expert_counts", "expert_offsets", "tile_base", "mtile_expert",
         "mtile_row0", "mtile_rows", "sorted_route_ids", "inv_perm", "act_q", "act_sf", "mid_q",
-        "mid_sf", "routed")] + [("rows", C.c_int32), ("mtile_cap", C.c_int32)]
+        "mid_sf", "routed")] + [("rows", C.c_int32), ("mtile_cap", C.c_int32),
+                                    ("tile_rows", C.c_int32), ("reserved", C.c_int32)]
 
 
 class RouteArgs(C.Structure):
@@ -69,7 +70,8 @@ class GatherArgs(C.Structure):
 
 
 class GemmArgs(C.Structure):
-    _fields_ = [("w13", C.c_void_p), ("w13_sf", C.c_void_p), ("w1_alphas", C.c_void_p),
+    _fields_ = [("w13", C.c_void_p), ("w13_sf", C.c_void_p), ("w13_sf_rows", C.c_void_p),
+                ("w1_alphas", C.c_void_p),
                 ("w2", C.c_void_p), ("w2_sf", C.c_void_p), ("w2_alphas", C.c_void_p),
                 ("a2_gscale", C.c_void_p), ("x", C.c_void_p), ("scratch", C.c_void_p),
                 ("layout", C.POINTER(ScratchLayout)), ("fc1_tap", C.c_void_p),
@@ -159,7 +161,7 @@ def load():
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = restype
-    if lib.b200moe_abi_version() != 1:
+    if lib.b200moe_abi_version() != 2:
         raise RuntimeError("libb200moe.so ABI version mismatch; rebuild it")
     _lib = lib
     return lib
@@ -186,9 +188,9 @@ def check(code: int, what: str) -> None:
 
 
 def scratch_layout(max_tokens: int, num_topk: int, num_experts: int, hidden: int, intermediate: int,
-                   recipe: str, activation: str) -> ScratchLayout:
+                   recipe: str, activation: str, tile_rows: int = 0) -> ScratchLayout:
     caps = CapsC(max_tokens, num_topk, num_experts, hidden, intermediate, RECIPES[recipe],
-                 ACTIVATIONS[activation], 0)
+                 ACTIVATIONS[activation], int(tile_rows))
     out = ScratchLayout()
     check(load().b200moe_scratch_nbytes(C.byref(caps), C.byref(out)), "scratch layout")
     return out

@@ -5,6 +5,9 @@
 namespace b200moe {
 int nvfp4_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
 int nvfp4_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
+bool nvfp4_small_batch_ok(const b200moe_gemm_args* a, bool fc1);
+int nvfp4_small_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
+int nvfp4_small_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
 int mx_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
 int mx_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
 int w4a16_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
@@ -48,7 +51,14 @@ extern "C" int b200moe_scratch_nbytes(const b200moe_caps* c, b200moe_scratch_lay
   const int64_t K = c->hidden_size, I = c->intermediate;
   const int64_t rows64 = T * k;
   if (rows64 > (1 << 30)) return B200MOE_EINVAL;
-  const int64_t mtile_cap = (rows64 + 127) / 128 + (E < rows64 ? E : rows64);
+  if (c->tile_rows != 0 && c->tile_rows != 64 && c->tile_rows != 128) return B200MOE_EINVAL;
+  // 64-row tiles go with the small-batch kernel (nvfp4, I a multiple of 128): chosen when the plan
+  // averages at most 48 routed rows per expert, or asked for by the caller
+  const bool small_ok = c->recipe == B200MOE_RECIPE_NVFP4 && I % 128 == 0 && K % 64 == 0;
+  int64_t tile_rows = c->tile_rows;
+  if (tile_rows == 0) tile_rows = (small_ok && rows64 <= 48 * E) ? 64 : 128;
+  if (tile_rows == 64 && !small_ok) tile_rows = 128;
+  const int64_t mtile_cap = (rows64 + tile_rows - 1) / tile_rows + (E < rows64 ? E : rows64);
   int64_t act_row = 0, mid_row = 0, act_atoms = 0, mid_atoms = 0;
   switch (c->recipe) {
     case B200MOE_RECIPE_NVFP4:
@@ -91,6 +101,8 @@ extern "C" int b200moe_scratch_nbytes(const b200moe_caps* c, b200moe_scratch_lay
   L->total_nbytes = off;
   L->rows = static_cast<int32_t>(rows64);
   L->mtile_cap = static_cast<int32_t>(mtile_cap);
+  L->tile_rows = static_cast<int32_t>(tile_rows);
+  L->reserved = 0;
   return B200MOE_OK;
 }
 
@@ -113,6 +125,7 @@ extern "C" int b200moe_grouped_gemm1_act(const b200moe_gemm_args* a, void* strea
   switch (a->recipe) {
     case B200MOE_RECIPE_NVFP4:
       if (a->w13_sf == nullptr || a->a2_gscale == nullptr) return B200MOE_EINVAL;
+      if (b200moe::nvfp4_small_batch_ok(a, /*fc1=*/true)) return b200moe::nvfp4_small_gemm1(a, s);
       return b200moe::nvfp4_gemm1(a, s);
     case B200MOE_RECIPE_W4A8_MX:
       return b200moe::mx_gemm1(a, s);
@@ -131,6 +144,7 @@ extern "C" int b200moe_grouped_gemm2(const b200moe_gemm_args* a, void* stream) {
   switch (a->recipe) {
     case B200MOE_RECIPE_NVFP4:
       if (a->w2_sf == nullptr) return B200MOE_EINVAL;
+      if (b200moe::nvfp4_small_batch_ok(a, /*fc1=*/false)) return b200moe::nvfp4_small_gemm2(a, s);
       return b200moe::nvfp4_gemm2(a, s);
     case B200MOE_RECIPE_W4A8_MX:
       return b200moe::mx_gemm2(a, s);

@@ -21,7 +21,8 @@ enum WaitSite : int {
   WAIT_TMEM_EMPTY = 3,   // MMA issuer waiting for the epilogue to drain the accumulator
   WAIT_TMEM_FULL = 4,    // epilogue waiting for the accumulator
   WAIT_DRAIN = 5,        // producer waiting for its own copies after an abort
-  WAIT_CONVERT = 6       // converter / MMA hand-off in the W4A16 kernel
+  WAIT_CONVERT = 6,      // converter / MMA hand-off in the W4A16 kernel
+  WAIT_SF_FULL = 7       // MMA issuer waiting for the scale atoms to reach TMEM
 };
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait, then give up

@@ -7,8 +7,8 @@
 //
 // One persistent CTA per SM walks the (expert, n-tile, m-tile) work list that the sort kernel left
 // in the scratch arena.  Warp 0 feeds a TMA pipeline (SWIZZLE_128B operand tiles + plain bulk
-// copies of the 512-byte scale atoms), warp 1 copies the scale atoms into TMEM with tcgen05.cp and
-// issues the block-scaled tcgen05.mma, warps 2..9 drain the TMEM accumulator.
+// copies of the 512-byte scale atoms), warp 1 issues the block-scaled tcgen05.mma, warps 2..9
+// drain the TMEM accumulator, warp 10 copies the scale atoms into TMEM with tcgen05.cp.
 //
 // Two tile shapes: BN = 128 (six pipeline stages, the accumulator double-buffered in TMEM so the
 // epilogue of one tile runs under the main loop of the next) and BN = 256 (four stages, one
@@ -16,7 +16,7 @@
 // leaves its loop.
 #include <stdlib.h>
 
-#include "common.cuh"
+#include "gemm_shared.cuh"
 
 namespace b200moe {
 
@@ -24,13 +24,12 @@ constexpr int kBM = 128;            // tile rows (MMA M)
 constexpr int kRowBytes = 128;      // one swizzled operand row per stage
 constexpr int kKPerStage = 256;     // nvfp4: reduction elements per stage
 constexpr int kKPerMma = 64;
-constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, 8 epilogue warps
+constexpr int kGemmThreads = 352;   // TMA warp, MMA warp, 8 epilogue warps, scale-copy warp
 constexpr int kTmemCols = 512;
 constexpr int kTmemSf = 256;        // first scale column (accumulators use columns 0..255)
 constexpr int kMaxStages = 6;
 constexpr int kSmemA = kBM * kRowBytes;        // 16 KiB
 constexpr int kSmemSfa = 4 * 512;              // up to 4 scale atoms per stage
-constexpr int kMaxExperts = 1024;
 
 template <int BN>
 struct TileCfg {
@@ -48,6 +47,7 @@ struct __align__(8) GemmSmemTail {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t sf_full[kMaxStages];   // scale atoms of the stage are in TMEM
   uint32_t tmem_base;
   int abort_flag;
   int32_t tile_base[kMaxExperts + 1];
@@ -58,101 +58,6 @@ constexpr int gemm_smem_bytes() {
          static_cast<int>(sizeof(GemmSmemTail));
 }
 
-enum { EPI_FC1_GATED = 0, EPI_FC1_RELU2 = 1, EPI_FC2 = 2, EPI_FC1_SILU = 3 };
-// KIND_NVFP4: A and B packed E2M1, E4M3 scale per 16, kind::mxf4nvf4 (K = 64 per MMA, 256 per stage).
-// KIND_MX:    A E4M3 bytes, B E2M1 expanded by TMA to one value per byte slot, E8M0 scale per 32,
-//             kind::mxf8f6f4 (K = 32 per MMA, 128 per stage; one scale atom per stage).
-enum { KIND_NVFP4 = 0, KIND_MX = 1 };
-
-struct GemmParams {
-  const uint8_t* sfa;            // activation scale atoms [mtile][atoms_k][512]
-  const uint8_t* sfb;            // weight scale atoms [E][rowgroups][atoms_k][512]
-  const int32_t* tile_base;      // [E+1]
-  const int32_t* mtile_expert;
-  const int32_t* mtile_row0;
-  const int32_t* mtile_rows;
-  int32_t* status;
-  const float* alphas;           // [E]
-  const float* gscale2;          // FC1 epilogue: reciprocal FC2-input scale
-  uint8_t* out_q;                // FC1: codes [rows][out_cols/2]
-  uint8_t* out_sf;               // FC1: scale atoms [mtile][out_atoms][512]
-  float* out_f32;                // FC2: routed rows [rows][out_cols]
-  float* tap;                    // FC1 debug tap [rows][w_rows] or null
-  int E, n_tiles, kdim, k_blocks, atoms_k;
-  int sfb_rowgroups;             // per expert
-  int w_rows;                    // weight rows per expert
-  int sub0_base, sub1_base;      // first weight row of the two sub-tiles at n-tile 0
-  int n_step;                    // weight rows advanced per n-tile
-  int out_cols;                  // I (FC1) or K (FC2)
-  int out_atoms;                 // FC1: scale atoms per tile of the output
-  int gscale_len;
-  float limit, act_alpha, act_beta;
-  int swigluoai;
-};
-
-struct TileCoord {
-  int e, mt, nt;
-};
-// work id -> (expert, m-tile, n-tile); expert-major, then n-tile, m-tile fastest, so that the CTAs
-// running at the same time share weight tiles through L2.
-__device__ __forceinline__ TileCoord decode_tile(int w, int n_tiles, const int32_t* tb, int E) {
-  const int q = w / n_tiles;
-  int lo = 0, hi = E;  // e = number of i in [1,E] with tb[i] <= q
-  while (lo < hi) {
-    const int mid = (lo + hi) >> 1;
-    if (tb[mid + 1] <= q) lo = mid + 1; else hi = mid;
-  }
-  TileCoord c;
-  c.e = lo;
-  const int me = tb[lo + 1] - tb[lo];
-  const int local = w - tb[lo] * n_tiles;
-  c.nt = local / me;
-  c.mt = tb[lo] + local % me;
-  return c;
-}
-
-// Branch-free reciprocal and division for the epilogues (a call with a slow-path branch per
-// element keeps the compiler from interleaving the 16 independent element chains of a chunk).
-__device__ __forceinline__ float rcp_approx(float x) {
-  float r;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
-  return r;
-}
-// 1/x for normal x: hardware approximation + one Newton step (error <= 0.5 ulp + 2^-46)
-__device__ __forceinline__ float rcp_newton(float x) {
-  const float r = rcp_approx(x);
-  return __fmaf_rn(r, __fmaf_rn(-x, r, 1.0f), r);
-}
-// a / b, correctly rounded when the quotient is a normal number or zero; rb = RN(1 / b).
-// Two residual corrections with exact fma residuals (Markstein).
-__device__ __forceinline__ float div_rn_normal(float a, float b, float rb) {
-  float q = __fmul_rn(a, rb);
-  q = __fmaf_rn(__fmaf_rn(-b, q, a), rb, q);
-  q = __fmaf_rn(__fmaf_rn(-b, q, a), rb, q);
-  return q;
-}
-
-// GENERIC = false: plain SwiGLU (no clamp); true: clamp and/or the SwiGLU-OAI form, chosen at run time.
-template <bool GENERIC>
-__device__ __forceinline__ float act_gated(float gate, float up, const GemmParams& p) {
-  if (GENERIC) {
-    if (p.limit > 0.f) {
-      gate = fminf(gate, p.limit);
-      up = fminf(fmaxf(up, -p.limit), p.limit);
-    }
-    if (p.swigluoai) {
-      const float s = rcp_newton(1.0f + expf(fminf(-(p.act_alpha * gate), 80.0f)));
-      return (gate * s) * (up + p.act_beta);
-    }
-  }
-  // the exponent is capped so that 1 + e stays finite (sigmoid below 2e-35 instead of 0)
-  const float s = rcp_newton(1.0f + expf(fminf(-gate, 80.0f)));
-  return (gate * s) * up;
-}
-
-__device__ __forceinline__ float round_bf16(float v) {
-  return __bfloat162float(__float2bfloat16_rn(v));
-}
 
 // Same arithmetic as quant_block16 in the activation quantiser, with a cheap common path: the
 // quotient x / denom is first approximated by x * rcp(denom) (error < 2 ulp); if the values 2^-21
@@ -250,6 +155,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&tail->full[s], 1);
       mbar_init(&tail->empty[s], 1);
+      mbar_init(&tail->sf_full[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tail->tmem_full[b], 1);
@@ -379,17 +285,18 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           tc_fence_after();
           const int ksteps = min(4, (p.kdim - kb * kPerStage) / kPerMma);
+          // the scale-copy warp has put this stage's scale atoms into TMEM
+          if (!mbar_wait_bounded(&tail->sf_full[stage], phase, abort_flag, p.status, WAIT_SF_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
           const uint32_t sfa_t = tmem_base + kTmemSf + stage * Cfg::kSfCols;
           const uint32_t sfb_t = sfa_t + 16;
-          const uint32_t sfa_s = smem_u32(sSfa + stage * kSmemSfa);
-          const uint32_t sfb_s = smem_u32(sSfb + stage * kSmemSfb);
           const uint64_t adesc = make_desc_sw128(smem_u32(sA + stage * kSmemA));
           const uint64_t bdesc = make_desc_sw128(smem_u32(sB + stage * kSmemB));
           if (KIND == KIND_MX) {
             // one atom = the four per-32 scales of this stage; MMA step j uses byte j of each word
-            tc_cp_32x128b_warpx4(sfa_t, make_desc_sf(sfa_s));
-            tc_cp_32x128b_warpx4(sfb_t, make_desc_sf(sfb_s));
-            if (Cfg::kSfbChains == 2) tc_cp_32x128b_warpx4(sfb_t + 4, make_desc_sf(sfb_s + 2048));
             for (int j = 0; j < ksteps; ++j) {
               const uint32_t ju = static_cast<uint32_t>(j);
               // 32 one-byte slots further along the swizzled row -> +2 in 16-byte units
@@ -397,12 +304,6 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
                            sfa_t + (ju << 30), sfb_t + (ju << 30), (kb > 0 || j > 0) ? 1u : 0u);
             }
           } else {
-            for (int j = 0; j < ksteps; ++j) {
-              tc_cp_32x128b_warpx4(sfa_t + 4 * j, make_desc_sf(sfa_s + 512 * j));
-              tc_cp_32x128b_warpx4(sfb_t + kSfbStep * j, make_desc_sf(sfb_s + 512 * j));
-              if (Cfg::kSfbChains == 2)
-                tc_cp_32x128b_warpx4(sfb_t + kSfbStep * j + 4, make_desc_sf(sfb_s + 2048 + 512 * j));
-            }
             for (int j = 0; j < ksteps; ++j) {
               // 64 FP4 values = 32 bytes further along the swizzled row -> +2 in 16-byte units
               mma_nvf4_4x(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j,
@@ -418,6 +319,50 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         if (ok) tc_commit(&tail->tmem_full[buf]);
         acc_phase[buf] ^= 1;
         if (Cfg::kBufs == 2) buf ^= 1;
+      }
+    }
+  } else if (warp == 10) {
+    // ------------------------------ scale copies -------------------------------
+    // One thread moves the scale atoms of every landed stage from shared memory into TMEM
+    // (tcgen05.cp) and commits them to a barrier of their own.  An MMA that follows a
+    // tcgen05.cp in the SAME thread's instruction stream waits out the copy's latency in the
+    // tensor pipe (about 0.15 us per dependent MMA, measured); from this thread the copies run
+    // stages ahead of the MMA issuer.
+    if (lane == 0) {
+      constexpr int kSfbStep = 4 * (BN / 128);   // scale columns of B per MMA step
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const int ksteps = min(4, (p.kdim - kb * kPerStage) / kPerMma);
+          const uint32_t sfa_t = tmem_base + kTmemSf + stage * Cfg::kSfCols;
+          const uint32_t sfb_t = sfa_t + 16;
+          const uint32_t sfa_s = smem_u32(sSfa + stage * kSmemSfa);
+          const uint32_t sfb_s = smem_u32(sSfb + stage * kSmemSfb);
+          if (KIND == KIND_MX) {
+            tc_cp_32x128b_warpx4(sfa_t, make_desc_sf(sfa_s));
+            tc_cp_32x128b_warpx4(sfb_t, make_desc_sf(sfb_s));
+            if (Cfg::kSfbChains == 2) tc_cp_32x128b_warpx4(sfb_t + 4, make_desc_sf(sfb_s + 2048));
+          } else {
+            for (int j = 0; j < ksteps; ++j) {
+              tc_cp_32x128b_warpx4(sfa_t + 4 * j, make_desc_sf(sfa_s + 512 * j));
+              tc_cp_32x128b_warpx4(sfb_t + kSfbStep * j, make_desc_sf(sfb_s + 512 * j));
+              if (Cfg::kSfbChains == 2)
+                tc_cp_32x128b_warpx4(sfb_t + kSfbStep * j + 4, make_desc_sf(sfb_s + 2048 + 512 * j));
+            }
+          }
+          tc_commit(&tail->sf_full[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
       }
     }
   } else {
@@ -682,7 +627,7 @@ int make_tmap_bytes_2d(CUtensorMap* out, const void* base, uint64_t row_bytes, u
   return r == CUDA_SUCCESS ? B200MOE_OK : B200MOE_ECUDA;
 }
 
-static int num_sms_cached() {
+int num_sms_cached() {
   static int n = 0;
   if (n == 0) {
     int dev = 0;
@@ -725,7 +670,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmA_small,
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 
-static void fill_common(GemmParams& p, const b200moe_gemm_args* a, char* base) {
+void fill_common(GemmParams& p, const b200moe_gemm_args* a, char* base) {
   const b200moe_scratch_layout& L = *a->layout;
   p.tile_base = reinterpret_cast<const int32_t*>(base + L.tile_base);
   p.mtile_expert = reinterpret_cast<const int32_t*>(base + L.mtile_expert);

@@ -292,7 +292,8 @@ extern "C" int b200moe_permute_quant_nvfp4(const b200moe_quant_args* a, void* st
   const b200moe_scratch_layout& L = *a->layout;
   char* base = static_cast<char*>(a->scratch);
   const int rows = a->num_tokens * a->num_topk;
-  const int mtiles = (rows + 127) / 128 + (a->num_experts < rows ? a->num_experts : rows);
+  const int tr = L.tile_rows == 64 ? 64 : 128;
+  const int mtiles = (rows + tr - 1) / tr + (a->num_experts < rows ? a->num_experts : rows);
   // tiles of a decode batch hold few rows: one CTA per tile; large batches: 4 CTAs per tile
   const dim3 grid(mtiles < L.mtile_cap ? mtiles : L.mtile_cap, a->num_tokens >= 256 ? 4 : 1);
   permute_quant_nvfp4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -313,7 +314,8 @@ extern "C" int b200moe_permute_quant_mxfp8(const b200moe_quant_args* a, void* st
   const b200moe_scratch_layout& L = *a->layout;
   char* base = static_cast<char*>(a->scratch);
   const int rows = a->num_tokens * a->num_topk;
-  const int mtiles = (rows + 127) / 128 + (a->num_experts < rows ? a->num_experts : rows);
+  const int tr = L.tile_rows == 64 ? 64 : 128;
+  const int mtiles = (rows + tr - 1) / tr + (a->num_experts < rows ? a->num_experts : rows);
   const dim3 grid(mtiles < L.mtile_cap ? mtiles : L.mtile_cap, a->num_tokens >= 256 ? 4 : 1);
   permute_quant_mxfp8_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride, a->num_topk, a->hidden_size,

@@ -141,7 +141,8 @@ __global__ void __launch_bounds__(kSortThreads) expert_sort_kernel(
     int32_t* __restrict__ expert_counts, int32_t* __restrict__ expert_offsets,
     int32_t* __restrict__ tile_base, int32_t* __restrict__ mtile_expert,
     int32_t* __restrict__ mtile_row0, int32_t* __restrict__ mtile_rows,
-    int32_t* __restrict__ sorted_route_ids, int32_t* __restrict__ inv_perm, int mtile_cap) {
+    int32_t* __restrict__ sorted_route_ids, int32_t* __restrict__ inv_perm, int mtile_cap,
+    int tile_rows) {
   extern __shared__ int32_t smem[];
   const int nwarps = blockDim.x >> 5;
   int32_t* wcount = smem;                 // [nwarps][E]
@@ -149,6 +150,7 @@ __global__ void __launch_bounds__(kSortThreads) expert_sort_kernel(
   int32_t* eoffs = etotal + E;            // [E+1]
   int32_t* tbase = eoffs + (E + 1);       // [E+1]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_shift = tile_rows == 64 ? 6 : 7;   // tile_rows is 64 or 128
 
   for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) wcount[i] = 0;
   if (threadIdx.x < 16) status[threadIdx.x] = 0;  // the sort opens every layer call
@@ -190,7 +192,7 @@ __global__ void __launch_bounds__(kSortThreads) expert_sort_kernel(
       eoffs[e] = pos;
       tbase[e] = tiles;
       pos += etotal[e];
-      tiles += (etotal[e] + 127) >> 7;
+      tiles += (etotal[e] + tile_rows - 1) >> tile_shift;
     }
     eoffs[E] = pos;
     tbase[E] = tiles;
@@ -201,13 +203,13 @@ __global__ void __launch_bounds__(kSortThreads) expert_sort_kernel(
     tile_base[e] = tbase[e];
     if (e < E) {
       expert_counts[e] = etotal[e];
-      const int nt = (etotal[e] + 127) >> 7;
+      const int nt = (etotal[e] + tile_rows - 1) >> tile_shift;
       for (int t = 0; t < nt; ++t) {
         const int mt = tbase[e] + t;
         if (mt < mtile_cap) {
           mtile_expert[mt] = e;
-          mtile_row0[mt] = eoffs[e] + t * 128;
-          mtile_rows[mt] = min(128, etotal[e] - t * 128);
+          mtile_row0[mt] = eoffs[e] + t * tile_rows;
+          mtile_rows[mt] = min(tile_rows, etotal[e] - t * tile_rows);
         }
       }
     }
@@ -294,7 +296,8 @@ extern "C" int b200moe_expert_sort(const b200moe_sort_args* a, void* stream) {
       reinterpret_cast<int32_t*>(base + L.mtile_row0),
       reinterpret_cast<int32_t*>(base + L.mtile_rows),
       reinterpret_cast<int32_t*>(base + L.sorted_route_ids),
-      reinterpret_cast<int32_t*>(base + L.inv_perm), L.mtile_cap);
+      reinterpret_cast<int32_t*>(base + L.inv_perm), L.mtile_cap,
+      L.tile_rows == 64 ? 64 : 128);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 
@@ -371,6 +374,6 @@ extern "C" int b200moe_expert_sort_static(const int32_t* topk_ids, const int32_t
       topk_ids, expert_map, expert_map_len, rows, num_experts, w + kStaticOffStatus,
       w + kStaticOffCounts, expert_offsets, w + kStaticOffTileBase, w + kStaticOffMtileExpert,
       w + kStaticOffMtileRow0, w + kStaticOffMtileRows, sorted_route_ids, inv_perm,
-      kStaticSortMtileCap);
+      kStaticSortMtileCap, 128);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }

@@ -60,8 +60,11 @@ class PeerExpertParallelMoE(_LayerBase):
         self.rank_of_expert = (torch.arange(shp.experts, dtype=torch.int32, device=dev) // self.e_local).contiguous()
         self.done_counter = torch.zeros(1, dtype=torch.int32, device=dev)
         # expert side: one plan over all slots, top-1, scratch in symmetric memory
+        # the slot capacity is the worst case; with balanced routing an expert receives
+        # world * tokens * top_k / experts rows, which decides the tile height of the plan
+        expected_rows = world * t * k // shp.experts
         caps = fused_moe.Caps(max_tokens=slots, num_topk=1, device=dev, weight_plan=experts.plan,
-                              quant_mode=shp.recipe)
+                              quant_mode=shp.recipe, tile_rows=64 if expected_rows <= 48 else 128)
         self.plan = fused_moe.plan(caps)
         nbytes = self.plan.scratch_specs()[0].shape[0]
         self.scratch, self.scratch_ptrs, self._h0 = _symm_empty((nbytes,), torch.uint8, dev)

@@ -90,6 +90,9 @@ class B12XFP4ExpertWeights:
     w2_fp4: torch.Tensor
     w2_blockscale: torch.Tensor
     w2_alphas: torch.Tensor
+    # nvfp4 with a gated activation: FC1 scales as 128-row atoms in the checkpoint's row order
+    # (the caller's own tensor, kept by reference), read by the small-batch kernel
+    w1_blockscale_rows: torch.Tensor | None = None
 
     def __post_init__(self) -> None:
         if not isinstance(self.plan, MoEWeightPreparationPlan):
@@ -206,6 +209,7 @@ def prepare_b12x_fp4_moe_weights(
     else:
         alphas1, alphas2 = g1.clone(), g2.clone()
     s1, s2 = w1_blockscale, w2_blockscale
+    s1_rows = None
     if WeightPreparationTransform.SWIZZLE_MX_SCALES in plan.transforms:
         if tuple(s1.shape) != (e, plan.w1_rows, plan.hidden_size // 32):
             raise ValueError("fp4_e8m0_k32 w1_blockscale must be [E, w1_rows, K/32] E8M0 bytes")
@@ -229,6 +233,9 @@ def prepare_b12x_fp4_moe_weights(
                 "modelopt_nvfp4 block scales must be 128x4-swizzled "
                 f"{exp1} / {exp2}, got {tuple(s1.shape)} / {tuple(s2.shape)}")
         s1, s2 = s1.view(torch.uint8), s2.view(torch.uint8)
+        if ("nvfp4" in plan.quant_modes and is_gated_moe_activation(plan.activation)
+                and plan.intermediate_size % 128 == 0):
+            s1_rows = s1.contiguous()
         if "nvfp4" in plan.quant_modes and is_gated_moe_activation(plan.activation):
             if "w4a16" in plan.quant_modes:
                 raise ValueError("one weight plan cannot serve both nvfp4 and w4a16: they need "
@@ -239,7 +246,7 @@ def prepare_b12x_fp4_moe_weights(
     return B12XFP4ExpertWeights(
         plan=plan, a1_gscale=a1, w1_fp4=w1_fp4.view(torch.uint8), w1_blockscale=s1.contiguous(),
         w1_alphas=alphas1.contiguous(), a2_gscale=a2, w2_fp4=w2_fp4.view(torch.uint8),
-        w2_blockscale=s2.contiguous(), w2_alphas=alphas2.contiguous())
+        w2_blockscale=s2.contiguous(), w2_alphas=alphas2.contiguous(), w1_blockscale_rows=s1_rows)
 
 
 # =============================================================================================
@@ -263,6 +270,9 @@ class TPMoEScratchCaps:
     swiglu_beta: float | None = None
     collect_activation_amax: bool = False
     deterministic_output: bool | None = None
+    # rows per expert tile: None = chosen from the capacity (64 with the small-batch kernel when
+    # the plan averages <= 48 routed rows per expert, else 128); 64 / 128 force it
+    tile_rows: int | None = None
     w4a16_block_size_m: int | None = None
     w4a16_fast_math: bool = True
     frozen: bool = True
@@ -296,6 +306,8 @@ class TPMoEScratchCaps:
             raise NotImplementedError("collect_activation_amax is not built")
         if self.num_topk > 32:
             raise ValueError("num_topk > 32 is not supported")
+        if self.tile_rows not in (None, 0, 64, 128):
+            raise ValueError("tile_rows must be 64 or 128")
 
     @property
     def weight_E(self) -> int:
@@ -372,7 +384,7 @@ def _route_workspace_nbytes(caps: TPMoEScratchCaps) -> int:
 
 def _layout_for(caps: TPMoEScratchCaps) -> ext.ScratchLayout:
     return ext.scratch_layout(caps.max_tokens, caps.num_topk, caps.weight_E, caps.k, caps.n,
-                              caps.quant_mode, _ACT_CODE[caps.activation])
+                              caps.quant_mode, _ACT_CODE[caps.activation], caps.tile_rows or 0)
 
 
 def plan_tp_moe_execution(caps: TPMoEScratchCaps, num_tokens: int | None = None) -> TPMoEPlan:
@@ -657,8 +669,8 @@ def b12x_moe_fp4(*, binding: TPMoEFP4Binding, stage_timer=None) -> torch.Tensor:
     mark("quant")
 
     gargs = ext.GemmArgs(
-        ex.w1_fp4.data_ptr(), ex.w1_blockscale.data_ptr(), ex.w1_alphas.data_ptr(),
-        ex.w2_fp4.data_ptr(), ex.w2_blockscale.data_ptr(), ex.w2_alphas.data_ptr(),
+        ex.w1_fp4.data_ptr(), ex.w1_blockscale.data_ptr(), _ptr(ex.w1_blockscale_rows),
+        ex.w1_alphas.data_ptr(), ex.w2_fp4.data_ptr(), ex.w2_blockscale.data_ptr(), ex.w2_alphas.data_ptr(),
         ex.a2_gscale.data_ptr(), b.a.data_ptr(), scratch, lp, _ptr(b.fc1_tap), b.a.stride(0),
         tokens, b.num_topk, b.weight_E, b.k, b.n, recipe, act,
         1 if (b.w13_layout == "w31" and is_gated_moe_activation(b.activation)) else 0,

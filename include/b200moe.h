@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 1
+#define B200MOE_ABI_VERSION 2
 
 /* ---- status codes ------------------------------------------------------ */
 #define B200MOE_OK            0
@@ -58,7 +58,9 @@ typedef struct {
   int32_t intermediate;  /* I                                                 */
   int32_t recipe;        /* B200MOE_RECIPE_*                                  */
   int32_t activation;    /* B200MOE_ACT_*                                     */
-  int32_t reserved;
+  int32_t tile_rows;     /* rows per expert tile: 0 = choose (64 when the plan
+                            averages <= 48 routed rows per expert and the
+                            recipe has the small-batch kernel, else 128)      */
 } b200moe_caps;
 
 /* Byte offsets of every view inside the single uint8 scratch arena.  The
@@ -69,10 +71,10 @@ typedef struct {
   int64_t status;            /* int32[16]; word 0: device error, word 1: where  */
   int64_t expert_counts;     /* int32[E]                                        */
   int64_t expert_offsets;    /* int32[E+1]  first sorted position per expert    */
-  int64_t tile_base;         /* int32[E+1]  first 128-row tile per expert       */
+  int64_t tile_base;         /* int32[E+1]  first row tile per expert           */
   int64_t mtile_expert;      /* int32[mtile_cap]                                */
   int64_t mtile_row0;        /* int32[mtile_cap] sorted position of tile row 0  */
-  int64_t mtile_rows;        /* int32[mtile_cap] valid rows (1..128)            */
+  int64_t mtile_rows;        /* int32[mtile_cap] valid rows (1..tile_rows)      */
   int64_t sorted_route_ids;  /* int32[rows]  flat route id (t*k+slot) per position */
   int64_t inv_perm;          /* int32[rows]  position per flat route id, -1 = dropped */
   int64_t act_q;             /* FC1 input: codes [rows][K/2] (nvfp4) / [rows][K] (mxfp8) / bf16 [rows][K] (w4a16) */
@@ -81,7 +83,9 @@ typedef struct {
   int64_t mid_sf;            /* FC2 input scales atoms                                         */
   int64_t routed;            /* float32 [rows][K] per-route FC2 output (alpha applied)         */
   int32_t rows;              /* T*k                                             */
-  int32_t mtile_cap;         /* ceil(rows/128) + min(E, rows)                   */
+  int32_t mtile_cap;         /* ceil(rows/tile_rows) + min(E, rows)             */
+  int32_t tile_rows;         /* 64 or 128: rows per expert tile of this plan    */
+  int32_t reserved;
 } b200moe_scratch_layout;
 
 int b200moe_abi_version(void);
@@ -193,6 +197,9 @@ int b200moe_gather_rows(const b200moe_gather_args* a, void* stream);
 typedef struct {
   const uint8_t* w13;        /* FC1 weights                                     */
   const uint8_t* w13_sf;     /* FC1 block scales (swizzled atoms)               */
+  const uint8_t* w13_sf_rows;/* nvfp4, gated: the same scales as 128-row atoms in the
+                                checkpoint's row order [E][2I/128][K/64][512] (what the
+                                small-batch kernel reads), or NULL                 */
   const float* w1_alphas;    /* [E]                                             */
   const uint8_t* w2;         /* FC2 weights [E][K][I/2]                         */
   const uint8_t* w2_sf;

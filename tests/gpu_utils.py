@@ -59,13 +59,13 @@ def route_on_gpu(inp: synth.MoEInputs, dev):
 
 
 def run_layer(inp: synth.MoEInputs, *, topk_ids=None, topk_weights=None, expert_map=None, poison=0xFF,
-              max_tokens=None, w13_layout="w13", want_fc1=True) -> LayerRun:
+              max_tokens=None, w13_layout="w13", want_fc1=True, tile_rows=None) -> LayerRun:
     dev = torch.device("cuda")
     shp = inp.shape
     ex = prepare_experts(inp, dev, w13_layout=w13_layout)
     t = inp.x.shape[0]
     caps = fused_moe.Caps(max_tokens=max_tokens or max(t, 1), num_topk=shp.topk, device=dev,
-                          weight_plan=ex.plan, quant_mode=shp.recipe)
+                          weight_plan=ex.plan, quant_mode=shp.recipe, tile_rows=tile_rows)
     plan = fused_moe.plan(caps)
     spec = plan.scratch_specs()[0]
     # poison the arena: a kernel that reads something it did not write shows up as garbage

@@ -27,7 +27,7 @@ def test_every_declared_symbol_is_exported(lib):
     assert declared == set(ext.EXPORTS), declared ^ set(ext.EXPORTS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.b200moe_abi_version() == 1
+    assert lib.b200moe_abi_version() == 2
     assert lib.b200moe_strerror(-2).decode().startswith("problem exceeds")
 
 
@@ -36,8 +36,8 @@ def test_struct_sizes_match_header_layout():
     for st in (ext.RouteArgs, ext.SortArgs, ext.QuantArgs, ext.GatherArgs, ext.GemmArgs, ext.CombineArgs,
                ext.ScratchLayout, ext.CapsC):
         assert C.sizeof(st) % 8 == 0, st
-    assert C.sizeof(ext.ScratchLayout) == 15 * 8 + 8
-    assert C.sizeof(ext.GemmArgs) == 12 * 8 + 14 * 4
+    assert C.sizeof(ext.ScratchLayout) == 15 * 8 + 16
+    assert C.sizeof(ext.GemmArgs) == 13 * 8 + 14 * 4
 
 
 def test_scratch_layout_is_monotone_and_aligned(lib):
@@ -46,7 +46,16 @@ def test_scratch_layout_is_monotone_and_aligned(lib):
              "mtile_rows", "sorted_route_ids", "inv_perm", "act_q", "act_sf", "mid_q", "mid_sf", "routed"]
     offs = [int(getattr(L, n)) for n in names]
     assert offs == sorted(offs) and all(o % 1024 == 0 for o in offs)
-    assert L.rows == 512 and L.mtile_cap == 4 + 256
+    # 512 routed rows over 256 experts: a small-batch plan, experts cut into 64-row tiles
+    assert L.rows == 512 and L.tile_rows == 64 and L.mtile_cap == 8 + 256
+    wide = ext.scratch_layout(64, 8, 256, 7168, 2048, "nvfp4", "silu", tile_rows=128)
+    assert wide.tile_rows == 128 and wide.mtile_cap == 4 + 256
+    # 16384 routed rows over 8 experts: 128-row tiles; other recipes have no small-batch kernel
+    assert ext.scratch_layout(8192, 2, 8, 4096, 14336, "nvfp4", "silu").tile_rows == 128
+    assert ext.scratch_layout(64, 8, 256, 7168, 2048, "w4a8_mx", "silu").tile_rows == 128
+    assert ext.scratch_layout(64, 8, 256, 7168, 2048, "w4a8_mx", "silu", tile_rows=64).tile_rows == 128
+    with pytest.raises(ValueError):
+        ext.scratch_layout(64, 8, 256, 7168, 2048, "nvfp4", "silu", tile_rows=32)
     assert L.total_nbytes >= offs[-1] + 512 * 7168 * 4
     with pytest.raises(ValueError):
         ext.scratch_layout(64, 8, 256, 7170, 2048, "nvfp4", "silu")

@@ -81,6 +81,8 @@ def _check_sort(run, taps):
 def _check_nvfp4_layer(run, *, expert_map=None, out_tol=OUT_TOL):
     shp = run.inp.shape
     ref, taps = oracle_layer(run.inp, run.topk_ids, run.topk_weights, expert_map)
+    # the row-tile tables follow the plan's tile height (64 in small-batch plans)
+    taps.sort = O.retile(taps.sort, int(run.binding.core_layout.tile_rows))
     b, s = run.binding, taps.sort
     rows = _check_sort(run, taps)
     if rows == 0:
