@@ -98,7 +98,7 @@ PeerArray = C.c_void_p * MAX_RANKS
 class EpDispatchArgs(C.Structure):
     _fields_ = [("x", C.c_void_p), ("topk_ids", C.c_void_p), ("peer_rows", PeerArray),
                 ("peer_ids", PeerArray), ("peer_flags", PeerArray), ("done_counter", C.c_void_p),
-                ("scratch", C.c_void_p), ("layout", C.POINTER(ScratchLayout)), ("x_row_stride", C.c_int64),
+                ("epoch_dev", C.c_void_p), ("scratch", C.c_void_p), ("layout", C.POINTER(ScratchLayout)), ("x_row_stride", C.c_int64),
                 ("num_tokens", C.c_int32), ("num_topk", C.c_int32), ("world", C.c_int32), ("rank", C.c_int32),
                 ("hidden_size", C.c_int32), ("local_modulus", C.c_int32), ("cap_rows", C.c_int32),
                 ("epoch", C.c_int32)]
@@ -137,8 +137,8 @@ EXPORTS = {
     "b200moe_grouped_gemm2": ([C.POINTER(GemmArgs), C.c_void_p], C.c_int),
     "b200moe_combine": ([C.POINTER(CombineArgs), C.c_void_p], C.c_int),
     "b200moe_ep_dispatch": ([C.POINTER(EpDispatchArgs), C.c_void_p], C.c_int),
-    "b200moe_ep_signal": ([C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_void_p], C.c_int),
-    "b200moe_ep_wait": ([C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p], C.c_int),
+    "b200moe_ep_signal": ([C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p], C.c_int),
+    "b200moe_ep_wait": ([C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p], C.c_int),
     "b200moe_ep_combine": ([C.POINTER(EpCombineArgs), C.c_void_p], C.c_int),
 }
 

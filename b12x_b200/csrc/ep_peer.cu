@@ -37,7 +37,11 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
     const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, const int32_t* __restrict__ topk_ids,
     const int32_t* __restrict__ group_offsets, const int32_t* __restrict__ sorted_route_ids,
     PeerPtrs rows, PeerPtrs ids, PeerPtrs flags, int32_t* done_counter, int world, int rank,
-    int num_topk, int K, int local_modulus, int cap, int epoch) {
+    int num_topk, int K, int local_modulus, int cap, int epoch_arg, int32_t* epoch_dev) {
+  // Epoch kept on the device (a captured CUDA graph replays with fixed arguments): this step is
+  // *epoch_dev + 1.  Every block reads it on entry; the last block out stores it back after all
+  // others have left, and the later kernels of the step read the stored value.
+  const int epoch = epoch_dev != nullptr ? *static_cast<volatile int32_t*>(epoch_dev) + 1 : epoch_arg;
   __shared__ int offs[B200MOE_MAX_RANKS + 1];
   if (threadIdx.x <= world) offs[threadIdx.x] = group_offsets[threadIdx.x];
   __syncthreads();
@@ -67,21 +71,25 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
     const int prev = atomicAdd(done_counter, 1);
     if (prev == static_cast<int>(gridDim.x) - 1) {
       *done_counter = 0;
+      if (epoch_dev != nullptr) *epoch_dev = epoch;
       __threadfence_system();
       for (int d = 0; d < world; ++d) st_release_sys(static_cast<int32_t*>(flags.p[d]) + rank, epoch);
     }
   }
 }
 
-__global__ void ep_signal_kernel(PeerPtrs flags, int world, int rank, int epoch) {
+__global__ void ep_signal_kernel(PeerPtrs flags, int world, int rank, int epoch_arg,
+                                 const int32_t* epoch_dev) {
+  const int epoch = epoch_dev != nullptr ? *epoch_dev : epoch_arg;
   if (threadIdx.x < world) {
     __threadfence_system();
     st_release_sys(static_cast<int32_t*>(flags.p[threadIdx.x]) + rank, epoch);
   }
 }
 
-__global__ void ep_wait_kernel(const int32_t* __restrict__ flags, int world, int epoch,
-                               int32_t* __restrict__ status) {
+__global__ void ep_wait_kernel(const int32_t* __restrict__ flags, int world, int epoch_arg,
+                               const int32_t* epoch_dev, int32_t* __restrict__ status) {
+  const int epoch = epoch_dev != nullptr ? *epoch_dev : epoch_arg;
   const int r = threadIdx.x;
   if (r >= world) return;
   unsigned long long t0 = 0;
@@ -187,24 +195,24 @@ extern "C" int b200moe_ep_dispatch(const b200moe_ep_dispatch_args* a, void* stre
       reinterpret_cast<const int32_t*>(base + L.expert_offsets),
       reinterpret_cast<const int32_t*>(base + L.sorted_route_ids), rows_p, ids_p, flags_p,
       a->done_counter, a->world, a->rank, a->num_topk, a->hidden_size, a->local_modulus, a->cap_rows,
-      a->epoch);
+      a->epoch, a->epoch_dev);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 
 extern "C" int b200moe_ep_signal(void* const* peer_flags, int32_t world, int32_t rank, int32_t epoch,
-                                 void* stream) {
+                                 const int32_t* epoch_dev, void* stream) {
   if (peer_flags == nullptr || world < 1 || world > B200MOE_MAX_RANKS || rank < 0 || rank >= world)
     return B200MOE_EINVAL;
   PeerPtrs flags_p;
   if (!fill_peers(flags_p, peer_flags, world)) return B200MOE_EINVAL;
-  ep_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags_p, world, rank, epoch);
+  ep_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags_p, world, rank, epoch, epoch_dev);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 
-extern "C" int b200moe_ep_wait(const int32_t* flags, int32_t world, int32_t epoch, int32_t* status,
-                               void* stream) {
+extern "C" int b200moe_ep_wait(const int32_t* flags, int32_t world, int32_t epoch,
+                               const int32_t* epoch_dev, int32_t* status, void* stream) {
   if (flags == nullptr || world < 1 || world > B200MOE_MAX_RANKS) return B200MOE_EINVAL;
-  ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, epoch, status);
+  ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, epoch, epoch_dev, status);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 

@@ -76,6 +76,7 @@ class _LayerBase:
         self.x_stage = torch.empty((t, shp.hidden), dtype=torch.bfloat16, device=dev)
         self.lg_stage = torch.empty((t, shp.experts), dtype=torch.float32, device=dev)
         self.last_binding = None
+        self.graph = None     # a captured step on (x_stage, lg_stage), where the layer offers one
 
     def route(self, logits: torch.Tensor) -> None:
         shp = self.shape
@@ -89,7 +90,11 @@ class _LayerBase:
         """Host buffers in, host buffer out: H2D copies, the layer, D2H copy, all on the current stream."""
         self.x_stage.copy_(x_host, non_blocking=True)
         self.lg_stage.copy_(logits_host, non_blocking=True)
-        out = self.forward(self.x_stage, self.lg_stage)
+        if self.graph is not None:
+            self.graph.replay()
+            out = self.out
+        else:
+            out = self.forward(self.x_stage, self.lg_stage)
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream(self.dev).synchronize()
 

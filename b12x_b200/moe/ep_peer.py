@@ -59,6 +59,8 @@ class PeerExpertParallelMoE(_LayerBase):
         self.home = StageArena(t, k, world, shp.hidden, dev)
         self.rank_of_expert = (torch.arange(shp.experts, dtype=torch.int32, device=dev) // self.e_local).contiguous()
         self.done_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        # the step counter lives on the device, so that a captured step can be replayed
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=dev)
         # expert side: one plan over all slots, top-1, scratch in symmetric memory
         # the slot capacity is the worst case; with balanced routing an expert receives
         # world * tokens * top_k / experts rows, which decides the tile height of the plan
@@ -76,7 +78,6 @@ class PeerExpertParallelMoE(_LayerBase):
         self.flag1_ptrs = flag_ptrs
         self.flag2_ptrs = [p + 4 * ext.MAX_RANKS for p in flag_ptrs]
         self.ones = torch.ones((slots, 1), dtype=torch.float32, device=dev)
-        self.epoch = 0
         self._flag2_arr = (C.c_void_p * world)(*self.flag2_ptrs)
         core = self.plan._core_layout
         self._inv_perm_off = self.plan.layout.route_workspace_nbytes + int(core.inv_perm)
@@ -111,23 +112,23 @@ class PeerExpertParallelMoE(_LayerBase):
         lib = ext.load()
         shp, home, world, rank = self.shape, self.home, self.world, self.rank
         stream = torch.cuda.current_stream(self.dev).cuda_stream
-        self.epoch += 1
         self.route(logits)
         home.sort(self.topk_ids, self.rank_of_expert)
         d = ext.EpDispatchArgs(
             x.data_ptr(), self.topk_ids.data_ptr(), ext.peer_array(self.rows_ptrs),
             ext.peer_array(self.ids_ptrs), ext.peer_array(self.flag1_ptrs), self.done_counter.data_ptr(),
-            home.scratch.data_ptr(), C.pointer(home.layout), x.stride(0), x.shape[0], shp.topk, world, rank,
-            shp.hidden, self.e_local, self.cap, self.epoch)
+            self.epoch_dev.data_ptr(), home.scratch.data_ptr(), C.pointer(home.layout), x.stride(0), x.shape[0], shp.topk, world, rank,
+            shp.hidden, self.e_local, self.cap, 0)
         ext.check(lib.b200moe_ep_dispatch(C.byref(d), stream), "ep_dispatch")
         b = fused_moe.bind(self.plan, scratch=self.scratch, a=self.recv_rows, experts=self.experts,
                            topk_weights=self.ones, topk_ids=self.recv_ids, skip_combine=True)
         self.last_binding = b
-        ext.check(lib.b200moe_ep_wait(self.flags.data_ptr(), world, self.epoch, self.home_status.data_ptr(), stream),
+        ep = self.epoch_dev.data_ptr()
+        ext.check(lib.b200moe_ep_wait(self.flags.data_ptr(), world, 0, ep, self.home_status.data_ptr(), stream),
                   "ep_wait")
         fused_moe.run(binding=b, stage_timer=stage_timer)
-        ext.check(lib.b200moe_ep_signal(self._flag2_arr, world, rank, self.epoch, stream), "ep_signal")
-        ext.check(lib.b200moe_ep_wait(self.flags.data_ptr() + 4 * ext.MAX_RANKS, world, self.epoch,
+        ext.check(lib.b200moe_ep_signal(self._flag2_arr, world, rank, 0, ep, stream), "ep_signal")
+        ext.check(lib.b200moe_ep_wait(self.flags.data_ptr() + 4 * ext.MAX_RANKS, world, 0, ep,
                                       self.home_status.data_ptr(), stream), "ep_wait")
         c = ext.EpCombineArgs(
             self.topk_weights.data_ptr(), self.out.data_ptr(), ext.peer_array(self.scratch_ptrs),
@@ -135,6 +136,18 @@ class PeerExpertParallelMoE(_LayerBase):
             self.out.stride(0), x.shape[0], shp.topk, world, rank, shp.hidden, self.cap, 1.0, 0)
         ext.check(lib.b200moe_ep_combine(C.byref(c), stream), "ep_combine")
         return self.out
+
+    def capture(self) -> torch.cuda.CUDAGraph:
+        """Record one step on the staging buffers (``x_stage``, ``lg_stage``) into a CUDA graph.
+        Nothing in the step depends on a host value that changes between steps, so
+        ``graph.replay()`` is a full layer pass on whatever the staging buffers hold; the result is
+        in ``self.out``.  All ranks must replay the same number of times."""
+        torch.cuda.synchronize(self.dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.forward(self.x_stage, self.lg_stage)
+        self.graph = g
+        return g
 
     def work_stats(self) -> dict:
         counts = self.last_binding.expert_counts.cpu()

@@ -245,7 +245,9 @@ int b200moe_combine(const b200moe_combine_args* a, void* stream);
  * named peer_* live in symmetric memory, i.e. the caller holds a device pointer to every rank's
  * copy.  Rank r owns slots [r*cap_rows, (r+1)*cap_rows) of every receive buffer.  Flags are int32
  * arrays of B200MOE_MAX_RANKS entries per rank, zero before the first step; `epoch` must grow by
- * one per step.  The only device-side wait (b200moe_ep_wait) is bounded: after 2 s it writes
+ * one per step.  With `epoch_dev` (a device int32, zero before the first step) the epoch lives on
+ * the device instead: the dispatch advances it, the signal and the waits read it, and the whole
+ * step can be captured once in a CUDA graph and replayed.  The only device-side wait (b200moe_ep_wait) is bounded: after 2 s it writes
  * status[0] = 1, status[1] = 16 + the missing peer, and returns. */
 #define B200MOE_MAX_RANKS 16
 typedef struct {
@@ -255,6 +257,7 @@ typedef struct {
   void* peer_ids[B200MOE_MAX_RANKS];    /* int32 [world*cap_rows] on each rank          */
   void* peer_flags[B200MOE_MAX_RANKS];  /* int32 [B200MOE_MAX_RANKS] on each rank       */
   int32_t* done_counter;     /* local int32, zero; the kernel leaves it zero    */
+  int32_t* epoch_dev;        /* device epoch counter, or NULL to use `epoch`    */
   void* scratch;             /* home arena, already sorted by destination rank  */
   const b200moe_scratch_layout* layout; /* HOST pointer                        */
   int64_t x_row_stride;
@@ -266,9 +269,10 @@ typedef struct {
 int b200moe_ep_dispatch(const b200moe_ep_dispatch_args* a, void* stream);
 /* Raise peer_flags[d][rank] = epoch on every rank once the stream's earlier work is done. */
 int b200moe_ep_signal(void* const* peer_flags /* HOST array */, int32_t world, int32_t rank,
-                      int32_t epoch, void* stream);
+                      int32_t epoch, const int32_t* epoch_dev /* or NULL */, void* stream);
 /* Return (on the stream) when flags[r] >= epoch for every r < world, or after the time limit. */
-int b200moe_ep_wait(const int32_t* flags, int32_t world, int32_t epoch, int32_t* status, void* stream);
+int b200moe_ep_wait(const int32_t* flags, int32_t world, int32_t epoch,
+                    const int32_t* epoch_dev /* or NULL */, int32_t* status, void* stream);
 
 typedef struct {
   const float* topk_weights; /* [T][k]                                          */

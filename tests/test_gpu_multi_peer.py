@@ -50,6 +50,25 @@ def _worker(rank: int, world: int, port: int, ret: dict):
                       f"ref max {ref.abs().max().item():.4e}, rows differing "
                       f"{int(((out - ref).abs().amax(dim=1) > 0).sum())}/{out.shape[0]}", flush=True)
             ok = ok and same
+        # the same step replayed from a CUDA graph on new tokens: bit-identical to the eager pass
+        graph = layer.capture()
+        for step in range(2):
+            g = torch.Generator().manual_seed(200 + step)
+            xs = torch.randn(tpr * world, shp.hidden, generator=g).to(torch.bfloat16)
+            lgs = torch.randn(tpr * world, shp.experts, generator=g)
+            lo = rank * tpr
+            layer.x_stage.copy_(xs[lo:lo + tpr])
+            layer.lg_stage.copy_(lgs[lo:lo + tpr])
+            graph.replay()
+            torch.cuda.synchronize()
+            replayed = layer.out.clone()
+            layer.graph = None
+            eager = layer.forward(layer.x_stage, layer.lg_stage).clone()
+            torch.cuda.synchronize()
+            layer.check_status()
+            if not torch.equal(replayed, eager):
+                print(f"rank {rank}: graph replay {step} differs from the eager pass", flush=True)
+                ok = False
         ret[rank] = ok
     finally:
         dist.destroy_process_group()
