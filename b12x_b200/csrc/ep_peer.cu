@@ -88,7 +88,8 @@ __global__ void ep_signal_kernel(PeerPtrs flags, int world, int rank, int epoch_
 }
 
 __global__ void ep_wait_kernel(const int32_t* __restrict__ flags, int world, int epoch_arg,
-                               const int32_t* epoch_dev, int32_t* __restrict__ status) {
+                               const int32_t* epoch_dev, int32_t* __restrict__ status,
+                               unsigned long long limit_ns) {
   const int epoch = epoch_dev != nullptr ? *epoch_dev : epoch_arg;
   const int r = threadIdx.x;
   if (r >= world) return;
@@ -98,7 +99,7 @@ __global__ void ep_wait_kernel(const int32_t* __restrict__ flags, int world, int
     if ((++spins & 0x3ffu) == 0) {
       const unsigned long long now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
+      if (now - t0 > limit_ns) {
         if (status != nullptr) {
           atomicCAS(status, 0, 1);
           atomicCAS(status + 1, 0, 16 + r);   // 16 + peer rank: that peer never arrived
@@ -210,9 +211,13 @@ extern "C" int b200moe_ep_signal(void* const* peer_flags, int32_t world, int32_t
 }
 
 extern "C" int b200moe_ep_wait(const int32_t* flags, int32_t world, int32_t epoch,
-                               const int32_t* epoch_dev, int32_t* status, void* stream) {
-  if (flags == nullptr || world < 1 || world > B200MOE_MAX_RANKS) return B200MOE_EINVAL;
-  ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, epoch, epoch_dev, status);
+                               const int32_t* epoch_dev, int32_t* status, int32_t timeout_ms,
+                               void* stream) {
+  if (flags == nullptr || world < 1 || world > B200MOE_MAX_RANKS || timeout_ms < 0 || timeout_ms > 10000)
+    return B200MOE_EINVAL;
+  const unsigned long long limit_ns =
+      timeout_ms > 0 ? static_cast<unsigned long long>(timeout_ms) * 1000000ull : kWaitLimitNs;
+  ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, epoch, epoch_dev, status, limit_ns);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 

@@ -124,12 +124,12 @@ class PeerExpertParallelMoE(_LayerBase):
                            topk_weights=self.ones, topk_ids=self.recv_ids, skip_combine=True)
         self.last_binding = b
         ep = self.epoch_dev.data_ptr()
-        ext.check(lib.b200moe_ep_wait(self.flags.data_ptr(), world, 0, ep, self.home_status.data_ptr(), stream),
+        ext.check(lib.b200moe_ep_wait(self.flags.data_ptr(), world, 0, ep, self.home_status.data_ptr(), 0, stream),
                   "ep_wait")
         fused_moe.run(binding=b, stage_timer=stage_timer)
         ext.check(lib.b200moe_ep_signal(self._flag2_arr, world, rank, 0, ep, stream), "ep_signal")
         ext.check(lib.b200moe_ep_wait(self.flags.data_ptr() + 4 * ext.MAX_RANKS, world, 0, ep,
-                                      self.home_status.data_ptr(), stream), "ep_wait")
+                                      self.home_status.data_ptr(), 0, stream), "ep_wait")
         c = ext.EpCombineArgs(
             self.topk_weights.data_ptr(), self.out.data_ptr(), ext.peer_array(self.scratch_ptrs),
             home.scratch.data_ptr(), C.pointer(home.layout), self._inv_perm_off, self._routed_off,

@@ -270,9 +270,11 @@ int b200moe_ep_dispatch(const b200moe_ep_dispatch_args* a, void* stream);
 /* Raise peer_flags[d][rank] = epoch on every rank once the stream's earlier work is done. */
 int b200moe_ep_signal(void* const* peer_flags /* HOST array */, int32_t world, int32_t rank,
                       int32_t epoch, const int32_t* epoch_dev /* or NULL */, void* stream);
-/* Return (on the stream) when flags[r] >= epoch for every r < world, or after the time limit. */
+/* Return (on the stream) when flags[r] >= epoch for every r < world, or after the time limit
+ * (timeout_ms, 0 = the default 2000, at most 10000). */
 int b200moe_ep_wait(const int32_t* flags, int32_t world, int32_t epoch,
-                    const int32_t* epoch_dev /* or NULL */, int32_t* status, void* stream);
+                    const int32_t* epoch_dev /* or NULL */, int32_t* status, int32_t timeout_ms,
+                    void* stream);
 
 typedef struct {
   const float* topk_weights; /* [T][k]                                          */
