@@ -135,16 +135,26 @@ __global__ void __launch_bounds__(256) ep_combine_pull_kernel(
   }
   __syncthreads();
   const int nvec = K >> 2;
-  for (int j = threadIdx.x; j < nvec; j += blockDim.x) {
+  for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < nvec; j += gridDim.y * blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < num_topk; ++s) {
-      if (rowp[s] == nullptr) continue;
-      const float4 v = *(reinterpret_cast<const float4*>(rowp[s]) + j);
-      const float ws = w[s];
-      acc.x = __fadd_rn(acc.x, __fmul_rn(ws, v.x));
-      acc.y = __fadd_rn(acc.y, __fmul_rn(ws, v.y));
-      acc.z = __fadd_rn(acc.z, __fmul_rn(ws, v.z));
-      acc.w = __fadd_rn(acc.w, __fmul_rn(ws, v.w));
+    // slots in order, eight at a time: the (peer) loads of a batch are issued before the first add
+    for (int s0 = 0; s0 < num_topk; s0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float* rp = s0 + q < num_topk ? rowp[s0 + q] : nullptr;
+        v[q] = rp != nullptr ? *(reinterpret_cast<const float4*>(rp) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        if (s0 + q < num_topk && rowp[s0 + q] != nullptr) {
+          const float ws = w[s0 + q];
+          acc.x = __fadd_rn(acc.x, __fmul_rn(ws, v[q].x));
+          acc.y = __fadd_rn(acc.y, __fmul_rn(ws, v[q].y));
+          acc.z = __fadd_rn(acc.z, __fmul_rn(ws, v[q].z));
+          acc.w = __fadd_rn(acc.w, __fmul_rn(ws, v[q].w));
+        }
+      }
     }
     __nv_bfloat16 b[4] = {__float2bfloat16_rn(acc.x), __float2bfloat16_rn(acc.y),
                           __float2bfloat16_rn(acc.z), __float2bfloat16_rn(acc.w)};
@@ -235,7 +245,11 @@ extern "C" int b200moe_ep_combine(const b200moe_ep_combine_args* a, void* stream
   if (!fill_peers(arenas, a->peer_scratch, a->world)) return B200MOE_EINVAL;
   const b200moe_scratch_layout& L = *a->layout;
   char* base = static_cast<char*>(a->scratch);
-  ep_combine_pull_kernel<<<a->num_tokens, 256, a->num_topk * 16, static_cast<cudaStream_t>(stream)>>>(
+  int ysplit = (2 * 148 + a->num_tokens - 1) / a->num_tokens;
+  const int ymax = (a->hidden_size / 4 + 255) / 256;
+  ysplit = ysplit < 1 ? 1 : (ysplit > ymax ? ymax : ysplit);
+  ep_combine_pull_kernel<<<dim3(a->num_tokens, ysplit), 256, a->num_topk * 16,
+                           static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const int32_t*>(base + L.expert_offsets),
       reinterpret_cast<const int32_t*>(base + L.inv_perm), a->topk_weights, arenas,
       a->peer_inv_perm_off, a->peer_routed_off, static_cast<__nv_bfloat16*>(a->out), a->out_row_stride,

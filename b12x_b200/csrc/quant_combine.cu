@@ -48,13 +48,19 @@ __global__ void __launch_bounds__(256) permute_quant_nvfp4_kernel(
   const int atoms = (nblk + 3) >> 2;          // 512-byte scale atoms per tile
   uint8_t* sf_tile = act_sf + static_cast<size_t>(mt) * atoms * 512;
 
-  for (int i = blockIdx.y * 8 + warp; i < nrows; i += gridDim.y * 8) {
+  // All eight warps work on the same row (a decode tile holds two or three rows: one warp per
+  // row would leave the others idle and walk the row in 14 dependent steps).
+  // (a short row takes only some of the warps; the others start on the next row)
+  const int wpr = min(8, (nblk + 31) >> 5);     // warps per row
+  const int rows_par = 8 / wpr;                 // rows in flight per CTA
+  const int wrow = warp / wpr, wchunk = warp - wrow * wpr;
+  for (int i = blockIdx.y * rows_par + wrow; wrow < rows_par && i < nrows; i += gridDim.y * rows_par) {
     const int pos = row0 + i;
     const int r = sorted_route_ids[pos];
     const int t = r / num_topk;
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(t) * x_row_stride);
     uint2* dst = reinterpret_cast<uint2*>(act_q + static_cast<size_t>(pos) * (K >> 1));
-    for (int b0 = 0; b0 < nblk; b0 += 32) {
+    for (int b0 = wchunk * 32; b0 < nblk; b0 += wpr * 32) {
       const int b = b0 + lane;
       uint8_t sfb = 0;
       if (b < nblk) {
@@ -112,13 +118,16 @@ __global__ void __launch_bounds__(256) permute_quant_mxfp8_kernel(
   const int atoms = (nblk + 3) >> 2;
   uint8_t* sf_tile = act_sf + static_cast<size_t>(mt) * atoms * 512;
 
-  for (int i = blockIdx.y * 8 + warp; i < nrows; i += gridDim.y * 8) {
+  const int wpr = min(8, (nblk + 31) >> 5);     // warps per row
+  const int rows_par = 8 / wpr;                 // rows in flight per CTA
+  const int wrow = warp / wpr, wchunk = warp - wrow * wpr;
+  for (int i = blockIdx.y * rows_par + wrow; wrow < rows_par && i < nrows; i += gridDim.y * rows_par) {
     const int pos = row0 + i;
     const int r = sorted_route_ids[pos];
     const int t = r / num_topk;
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(t) * x_row_stride);
     uint4* dst = reinterpret_cast<uint4*>(act_q + static_cast<size_t>(pos) * K);
-    for (int b0 = 0; b0 < nblk; b0 += 32) {
+    for (int b0 = wchunk * 32; b0 < nblk; b0 += wpr * 32) {
       const int b = b0 + lane;
       uint8_t sfb = 0;
       if (b < nblk) {
@@ -168,6 +177,7 @@ __global__ void __launch_bounds__(256) permute_quant_mxfp8_kernel(
 // and each sum rounded to fp32 separately (no fused multiply-add), one final rounding to bf16.
 // This is the accumulation of the reference oracle (reference.py:408-411, 988-990).
 // ------------------------------------------------------------------------------------------
+template <int BATCH>
 __global__ void __launch_bounds__(256) combine_kernel(
     const float* __restrict__ routed, const int32_t* __restrict__ inv_perm,
     const float* __restrict__ topk_weights, void* __restrict__ out, int64_t out_row_stride,
@@ -182,17 +192,27 @@ __global__ void __launch_bounds__(256) combine_kernel(
   }
   __syncthreads();
   const int nvec = K >> 2;
-  for (int j = threadIdx.x; j < nvec; j += blockDim.x) {
+  for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < nvec; j += gridDim.y * blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < num_topk; ++s) {
-      const int p = pos[s];
-      if (p < 0) continue;
-      const float4 v = __ldg(reinterpret_cast<const float4*>(routed + static_cast<size_t>(p) * K) + j);
-      const float ws = w[s];
-      acc.x = __fadd_rn(acc.x, __fmul_rn(ws, v.x));
-      acc.y = __fadd_rn(acc.y, __fmul_rn(ws, v.y));
-      acc.z = __fadd_rn(acc.z, __fmul_rn(ws, v.z));
-      acc.w = __fadd_rn(acc.w, __fmul_rn(ws, v.w));
+    // slots in order, BATCH at a time: the loads of a batch are issued before the first add
+    for (int s0 = 0; s0 < num_topk; s0 += BATCH) {
+      float4 v[BATCH];
+#pragma unroll
+      for (int q = 0; q < BATCH; ++q) {
+        const int p = s0 + q < num_topk ? pos[s0 + q] : -1;
+        v[q] = p >= 0 ? __ldg(reinterpret_cast<const float4*>(routed + static_cast<size_t>(p) * K) + j)
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int q = 0; q < BATCH; ++q) {
+        if (s0 + q < num_topk && pos[s0 + q] >= 0) {
+          const float ws = w[s0 + q];
+          acc.x = __fadd_rn(acc.x, __fmul_rn(ws, v[q].x));
+          acc.y = __fadd_rn(acc.y, __fmul_rn(ws, v[q].y));
+          acc.z = __fadd_rn(acc.z, __fmul_rn(ws, v[q].z));
+          acc.w = __fadd_rn(acc.w, __fmul_rn(ws, v[q].w));
+        }
+      }
     }
     if (out_f32) {
       float* o = reinterpret_cast<float*>(out) + static_cast<int64_t>(t) * out_row_stride;
@@ -295,7 +315,10 @@ extern "C" int b200moe_permute_quant_nvfp4(const b200moe_quant_args* a, void* st
   const int tr = L.tile_rows == 64 ? 64 : 128;
   const int mtiles = (rows + tr - 1) / tr + (a->num_experts < rows ? a->num_experts : rows);
   // tiles of a decode batch hold few rows: one CTA per tile; large batches: 4 CTAs per tile
-  const dim3 grid(mtiles < L.mtile_cap ? mtiles : L.mtile_cap, a->num_tokens >= 256 ? 4 : 1);
+  const int gx = mtiles < L.mtile_cap ? mtiles : L.mtile_cap;
+  int gy = (4 * 148 + gx - 1) / gx;    // enough CTAs per tile to fill the GPU about four times
+  gy = gy < 1 ? 1 : (gy > 16 ? 16 : gy);
+  const dim3 grid(gx, gy);
   permute_quant_nvfp4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride, a->a1_gscale, a->gscale_len,
       a->num_topk, a->hidden_size, reinterpret_cast<const int32_t*>(base + L.tile_base),
@@ -316,7 +339,10 @@ extern "C" int b200moe_permute_quant_mxfp8(const b200moe_quant_args* a, void* st
   const int rows = a->num_tokens * a->num_topk;
   const int tr = L.tile_rows == 64 ? 64 : 128;
   const int mtiles = (rows + tr - 1) / tr + (a->num_experts < rows ? a->num_experts : rows);
-  const dim3 grid(mtiles < L.mtile_cap ? mtiles : L.mtile_cap, a->num_tokens >= 256 ? 4 : 1);
+  const int gx = mtiles < L.mtile_cap ? mtiles : L.mtile_cap;
+  int gy = (4 * 148 + gx - 1) / gx;    // enough CTAs per tile to fill the GPU about four times
+  gy = gy < 1 ? 1 : (gy > 16 ? 16 : gy);
+  const dim3 grid(gx, gy);
   permute_quant_mxfp8_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride, a->num_topk, a->hidden_size,
       reinterpret_cast<const int32_t*>(base + L.tile_base), a->num_experts,
@@ -338,9 +364,19 @@ extern "C" int b200moe_combine(const b200moe_combine_args* a, void* stream) {
   if (a->num_tokens == 0) return B200MOE_OK;
   const b200moe_scratch_layout& L = *a->layout;
   char* base = static_cast<char*>(a->scratch);
-  combine_kernel<<<a->num_tokens, 256, a->num_topk * 8, static_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const float*>(base + L.routed),
-      reinterpret_cast<const int32_t*>(base + L.inv_perm), a->topk_weights, a->out,
-      a->out_row_stride, a->num_topk, a->hidden_size, a->out_f32, a->output_scale);
+  // small batches: several CTAs per token (slices of K), so that the grid fills the GPU
+  int ysplit = (2 * 148 + a->num_tokens - 1) / a->num_tokens;
+  const int ymax = (a->hidden_size / 4 + 255) / 256;
+  ysplit = ysplit < 1 ? 1 : (ysplit > ymax ? ymax : ysplit);
+  const dim3 grid(a->num_tokens, ysplit);
+  const size_t smem = a->num_topk * 8;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+#define B200MOE_COMBINE_ARGS \
+  reinterpret_cast<const float*>(base + L.routed), reinterpret_cast<const int32_t*>(base + L.inv_perm), \
+      a->topk_weights, a->out, a->out_row_stride, a->num_topk, a->hidden_size, a->out_f32, a->output_scale
+  if (a->num_topk <= 2) combine_kernel<2><<<grid, 256, smem, cs>>>(B200MOE_COMBINE_ARGS);
+  else if (a->num_topk <= 4) combine_kernel<4><<<grid, 256, smem, cs>>>(B200MOE_COMBINE_ARGS);
+  else combine_kernel<8><<<grid, 256, smem, cs>>>(B200MOE_COMBINE_ARGS);
+#undef B200MOE_COMBINE_ARGS
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
