@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(256) permute_quant_nvfp4_kernel(
     int gscale_len, int num_topk, int K, const int32_t* __restrict__ tile_base, int E,
     const int32_t* __restrict__ mtile_expert, const int32_t* __restrict__ mtile_row0,
     const int32_t* __restrict__ mtile_rows, const int32_t* __restrict__ sorted_route_ids,
-    uint8_t* __restrict__ act_q, uint8_t* __restrict__ act_sf) {
+    uint8_t* __restrict__ act_q, uint8_t* __restrict__ act_sf, int wpr_cap) {
   const int mt = blockIdx.x;
   if (mt >= tile_base[E]) return;
   const int e = mtile_expert[mt];
@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(256) permute_quant_nvfp4_kernel(
   // All eight warps work on the same row (a decode tile holds two or three rows: one warp per
   // row would leave the others idle and walk the row in 14 dependent steps).
   // (a short row takes only some of the warps; the others start on the next row)
-  const int wpr = min(8, (nblk + 31) >> 5);     // warps per row
+  const int wpr = min(wpr_cap, (nblk + 31) >> 5);     // warps per row
   const int rows_par = 8 / wpr;                 // rows in flight per CTA
   const int wrow = warp / wpr, wchunk = warp - wrow * wpr;
   for (int i = blockIdx.y * rows_par + wrow; wrow < rows_par && i < nrows; i += gridDim.y * rows_par) {
@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(256) permute_quant_mxfp8_kernel(
     const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, int num_topk, int K,
     const int32_t* __restrict__ tile_base, int E, const int32_t* __restrict__ mtile_row0,
     const int32_t* __restrict__ mtile_rows, const int32_t* __restrict__ sorted_route_ids,
-    uint8_t* __restrict__ act_q, uint8_t* __restrict__ act_sf) {
+    uint8_t* __restrict__ act_q, uint8_t* __restrict__ act_sf, int wpr_cap) {
   const int mt = blockIdx.x;
   if (mt >= tile_base[E]) return;
   const int row0 = mtile_row0[mt];
@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(256) permute_quant_mxfp8_kernel(
   const int atoms = (nblk + 3) >> 2;
   uint8_t* sf_tile = act_sf + static_cast<size_t>(mt) * atoms * 512;
 
-  const int wpr = min(8, (nblk + 31) >> 5);     // warps per row
+  const int wpr = min(wpr_cap, (nblk + 31) >> 5);     // warps per row
   const int rows_par = 8 / wpr;                 // rows in flight per CTA
   const int wrow = warp / wpr, wchunk = warp - wrow * wpr;
   for (int i = blockIdx.y * rows_par + wrow; wrow < rows_par && i < nrows; i += gridDim.y * rows_par) {
@@ -315,9 +315,13 @@ extern "C" int b200moe_permute_quant_nvfp4(const b200moe_quant_args* a, void* st
   const int tr = L.tile_rows == 64 ? 64 : 128;
   const int mtiles = (rows + tr - 1) / tr + (a->num_experts < rows ? a->num_experts : rows);
   // tiles of a decode batch hold few rows: one CTA per tile; large batches: 4 CTAs per tile
+  // Small batches: the eight warps of a CTA share a row and a tile's rows are spread over enough
+  // CTAs to fill the GPU about four times.  Large batches: one warp per row, four CTAs per tile.
   const int gx = mtiles < L.mtile_cap ? mtiles : L.mtile_cap;
-  int gy = (4 * 148 + gx - 1) / gx;    // enough CTAs per tile to fill the GPU about four times
+  const bool large = rows >= 2048;
+  int gy = large ? 4 : (4 * 148 + gx - 1) / gx;
   gy = gy < 1 ? 1 : (gy > 16 ? 16 : gy);
+  const int wpr_cap = large ? 1 : 8;
   const dim3 grid(gx, gy);
   permute_quant_nvfp4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride, a->a1_gscale, a->gscale_len,
@@ -326,7 +330,7 @@ extern "C" int b200moe_permute_quant_nvfp4(const b200moe_quant_args* a, void* st
       reinterpret_cast<const int32_t*>(base + L.mtile_row0),
       reinterpret_cast<const int32_t*>(base + L.mtile_rows),
       reinterpret_cast<const int32_t*>(base + L.sorted_route_ids),
-      reinterpret_cast<uint8_t*>(base + L.act_q), reinterpret_cast<uint8_t*>(base + L.act_sf));
+      reinterpret_cast<uint8_t*>(base + L.act_q), reinterpret_cast<uint8_t*>(base + L.act_sf), wpr_cap);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 
@@ -339,9 +343,13 @@ extern "C" int b200moe_permute_quant_mxfp8(const b200moe_quant_args* a, void* st
   const int rows = a->num_tokens * a->num_topk;
   const int tr = L.tile_rows == 64 ? 64 : 128;
   const int mtiles = (rows + tr - 1) / tr + (a->num_experts < rows ? a->num_experts : rows);
+  // Small batches: the eight warps of a CTA share a row and a tile's rows are spread over enough
+  // CTAs to fill the GPU about four times.  Large batches: one warp per row, four CTAs per tile.
   const int gx = mtiles < L.mtile_cap ? mtiles : L.mtile_cap;
-  int gy = (4 * 148 + gx - 1) / gx;    // enough CTAs per tile to fill the GPU about four times
+  const bool large = rows >= 2048;
+  int gy = large ? 4 : (4 * 148 + gx - 1) / gx;
   gy = gy < 1 ? 1 : (gy > 16 ? 16 : gy);
+  const int wpr_cap = large ? 1 : 8;
   const dim3 grid(gx, gy);
   permute_quant_mxfp8_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride, a->num_topk, a->hidden_size,
@@ -349,7 +357,7 @@ extern "C" int b200moe_permute_quant_mxfp8(const b200moe_quant_args* a, void* st
       reinterpret_cast<const int32_t*>(base + L.mtile_row0),
       reinterpret_cast<const int32_t*>(base + L.mtile_rows),
       reinterpret_cast<const int32_t*>(base + L.sorted_route_ids),
-      reinterpret_cast<uint8_t*>(base + L.act_q), reinterpret_cast<uint8_t*>(base + L.act_sf));
+      reinterpret_cast<uint8_t*>(base + L.act_q), reinterpret_cast<uint8_t*>(base + L.act_sf), wpr_cap);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 

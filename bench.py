@@ -6,8 +6,9 @@
 One step = one pass of the layer (route -> sort -> quantise -> FC1+activation -> FC2 -> combine)
 over one batch of seeded synthetic input.  The default workload is the DeepSeek-V3-shaped decode
 layer (hidden 7168, intermediate 2048, 256 experts, top-8, NVFP4 W4A4, 64 tokens per GPU); with
-N > 1 the experts are block-partitioned over the ranks (expert parallelism, token all-to-all over
-NCCL) and every rank brings its own batch (weak scaling).  Rank 0 prints ONE JSON line.
+N > 1 the experts are block-partitioned over the ranks (expert parallelism; tokens are exchanged by
+the library's own kernels over NVLink peer memory, `--ep nccl` selects the NCCL all-to-all variant)
+and every rank brings its own batch (weak scaling).  Rank 0 prints ONE JSON line.
 
 `--impl reference` times the CPU oracle (the restatement of the reference library's own torch
 implementation of this layer) on the host cores for the same configuration.
@@ -33,6 +34,7 @@ sys.path.insert(0, str(ROOT))
 from b12x_b200 import synth  # noqa: E402
 
 KERNELS_PER_STEP = 6  # route_topk, expert_sort, permute_quant, gemm1, gemm2, combine
+NCU_FC1_TRAFFIC_RATIO = 1.014
 
 
 def parse_args():
@@ -354,6 +356,10 @@ def main():
         else:
             achieved = dom["flops"] / (dom_ms * 1e-3) / 1e12
             peak, unit = peaks["bf16_tflops"] * dom["bf16_rate_multiple"], "TFLOP/s"
+        # DRAM bytes per FC1 launch: ncu on the 32-expert case of this workload read 1.014 x the
+        # algorithmic bytes (dram__bytes_read + write; summary under profiles/); every active
+        # expert's weights are read once per launch, so the traffic scales with the algorithmic bytes
+        traffic = dom["bytes"] * NCU_FC1_TRAFFIC_RATIO if (dom["bound"] == "hbm" and shp.recipe == "nvfp4") else None
         line = {
             "metric": "moe_layer_tokens_per_s", "value": total_tokens / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
@@ -367,7 +373,7 @@ def main():
             "stage_ms": stages,
             "roofline": {"kernel": dom["kernel"], "bound": dom["bound"], "achieved": achieved, "peak": peak,
                          "unit": unit, "frac": achieved / peak, "peak_source": peaks["source"] + dom.get("peak_note", ""),
-                         "traffic": dom.get("traffic"), "algorithmic_bytes": dom["bytes"],
+                         "traffic": traffic, "algorithmic_bytes": dom["bytes"],
                          "algorithmic_flops": dom["flops"], "ms_per_launch": dom_ms,
                          "active_experts": stats.get("active_experts")},
         }
