@@ -19,6 +19,7 @@ SOURCES = (
     "quant_combine.cu",
     "grouped_gemm_bs.cu",
     "grouped_gemm_small.cu",
+    "grouped_gemm_pair.cu",
     "grouped_gemm_other.cu",
     "ep_peer.cu",
 )

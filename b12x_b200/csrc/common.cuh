@@ -176,6 +176,42 @@ __device__ __forceinline__ void tc_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[1
       : "memory");
 }
 
+// Each thread of the warp writes N consecutive 32-bit columns of its own TMEM lane.
+__device__ __forceinline__ void tc_st_32x32b_x4(uint32_t taddr, const uint32_t (&r)[4]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3])
+               : "memory");
+}
+__device__ __forceinline__ void tc_st_32x32b_x8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+               "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+__device__ __forceinline__ void tc_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// Scale atoms (512 bytes each, `natoms` of them back to back in shared memory) -> `4 * natoms`
+// TMEM columns of this warp's sub-partition, atom j at columns [col_stride * j, +4): lane i takes
+// the 16 bytes of atom row i, as tcgen05.cp.32x128b.warpx4 would place them.  Called by one warp
+// per sub-partition; the tensor pipe is not involved.
+template <int NATOMS>
+__device__ __forceinline__ void sf_atoms_to_tmem(uint32_t taddr, const uint8_t* atoms, int lane, int col_stride) {
+#pragma unroll
+  for (int j = 0; j < NATOMS; ++j) {
+    const uint4 v = *(reinterpret_cast<const uint4*>(atoms + 512 * j) + lane);
+    const uint32_t r[4] = {v.x, v.y, v.z, v.w};
+    tc_st_32x32b_x4(taddr + col_stride * j, r);
+  }
+}
+
 // Shared-memory matrix descriptor (sm_100 "version 1"), K-major operand tile whose rows are
 // 128 bytes long and stored with the 128-byte swizzle (what a SWIZZLE_128B TMA box writes).
 // 8-row groups are 1024 bytes apart.  The tile base must be 1024-byte aligned; advancing along

@@ -104,6 +104,281 @@ __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
 
+// Same arithmetic as quant_block16 in the activation quantiser, with a cheap common path: the
+// quotient x / denom is first approximated by x * rcp(denom) (error < 2 ulp); if the values 2^-21
+// below and above it round to the same E2M1 code, the correctly rounded quotient does too.
+// Only a block with a value that close to a rounding boundary takes the exact division.
+// `rgs` = RN(1 / gs), computed once per tile.
+__device__ __forceinline__ void requant_block16(const float (&v)[16], float gs, float rgs, uint32_t& lo,
+                                                uint32_t& hi, uint8_t& sf_byte) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const float raw = fminf(div_rn_normal(__fmul_rn(amax, gs), 6.0f, 0.16666667163372039794921875f), 448.0f);
+  sf_byte = f32_to_e4m3_rn_sat(raw);
+  const float sf = e4m3_to_f32(sf_byte);
+  const float denom = fmaxf(div_rn_normal(sf, gs, rgs), 1e-30f);
+  const float r = rcp_approx(denom);
+  float a0[8], a1[8], b0[8], b1[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float q0 = __fmul_rn(v[i], r), q1 = __fmul_rn(v[8 + i], r);
+    a0[i] = __fmul_rn(q0, 1.0f - 4.76837158e-7f);
+    b0[i] = __fmul_rn(q0, 1.0f + 4.76837158e-7f);
+    a1[i] = __fmul_rn(q1, 1.0f - 4.76837158e-7f);
+    b1[i] = __fmul_rn(q1, 1.0f + 4.76837158e-7f);
+  }
+  lo = pack_e2m1x8(a0);
+  hi = pack_e2m1x8(a1);
+  if (lo != pack_e2m1x8(b0) || hi != pack_e2m1x8(b1)) {
+    float q0[8], q1[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      q0[i] = __fdiv_rn(v[i], denom);
+      q1[i] = __fdiv_rn(v[8 + i], denom);
+    }
+    lo = pack_e2m1x8(q0);
+    hi = pack_e2m1x8(q1);
+  }
+}
+
+// MXFP8 quantisation of 32 values (b12x/_lib/intrinsics.py:223-265): E8M0 byte = exponent of
+// pow2_ceil(amax / 448), payload = e4m3_rn_sat(x * 2^(127 - byte)).
+__device__ __forceinline__ void requant_block32_mx(const float (&v)[32], uint32_t (&o)[8],
+                                                   uint8_t& sf_byte) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  uint32_t bits = __float_as_uint(__fmul_rn(amax, static_cast<float>(1.0 / 448.0)));
+  if (bits & 0x007fffffu) bits = (bits + 0x00800000u) & 0x7f800000u;
+  sf_byte = static_cast<uint8_t>((bits >> 23) & 0xffu);
+  const int ex = 254 - static_cast<int>(sf_byte);
+  const float inv = sf_byte == 0 ? 0.f : __uint_as_float(static_cast<uint32_t>(ex < 0 ? 0 : ex) << 23);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint32_t acc = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float q = fminf(fmaxf(__fmul_rn(v[4 * j + k], inv), -448.f), 448.f);
+      acc |= static_cast<uint32_t>(f32_to_e4m3_rn_sat(q)) << (8 * k);
+    }
+    o[j] = acc;
+  }
+}
+
+// n scale bytes (n = 1, 2 or 4, packed in `word`) -> the tile's atom chain at scale column `col`
+template <int N>
+__device__ __forceinline__ void store_sf(uint8_t* sf_tile, uint32_t m, uint32_t col, uint32_t word) {
+  uint8_t* dst = sf_tile + sf_atom_offset(m, col);
+  if (N == 4) *reinterpret_cast<uint32_t*>(dst) = word;
+  else if (N == 2) *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(word);
+  else *dst = static_cast<uint8_t>(word);
+}
+
+// Epilogue of one 128 x BN accumulator tile, run by each of the eight epilogue warps: warp w may
+// only read TMEM sub-partition (w & 3), i.e. tile rows 32*(w&3) .. +31 (m = that row, t_lane =
+// the accumulator's TMEM address with the sub-partition's lane in the upper half); the two warps
+// that share a sub-partition split the tile's columns (half = 0 / 1).  release() is called once
+// per warp when its TMEM reads are done.  nrows == 0 (a tile that does not exist) stores nothing.
+template <int KIND, int EPI, int BN, class Release>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, int e, int mt, int nt, int row0, int nrows,
+                                              uint32_t t_lane, int m, int half, int lane, Release release) {
+  constexpr bool kGated = EPI == EPI_FC1_GATED || EPI == EPI_FC1_SILU;
+  constexpr int kPairs = BN / 2;                  // gated: output columns per tile
+  constexpr int kGatedChunks = kPairs / 32;       // 16-column chunks per warp (gated)
+  constexpr int kPlainChunks = BN / 32;           // 16-column chunks per warp (FC2 / relu2)
+  const float alpha = p.alphas[e];
+  const bool valid = m < nrows;
+  const size_t pos = static_cast<size_t>(row0 + m);
+  uint8_t* sft = p.out_sf + static_cast<size_t>(mt) * p.out_atoms * 512;
+  if (KIND == KIND_MX && kGated) {
+    // w4a8_mx: the activation output goes straight into the MXFP8 quantiser (no bf16 staging)
+    constexpr int kBlocks = kPairs / 64;      // 32-column blocks per warp
+    constexpr int kUpCol = BN == 256 ? 128 : 32;   // TMEM column of this warp's up values, per half
+    const int col0 = nt * kPairs + half * (kPairs / 2);
+    uint8_t* qrow = p.out_q + pos * p.out_cols + col0;
+    uint32_t sfw = 0u;
+    const bool cols_ok = col0 < p.out_cols;
+#pragma unroll 1
+    for (int blk = 0; blk < kBlocks; ++blk) {
+      float h[32];
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2) {
+        uint32_t ru[16], rg[16];
+        tc_ld_32x32b_x16(t_lane + half * kUpCol + blk * 32 + c2 * 16, ru);
+        tc_ld_32x32b_x16(t_lane + half * kUpCol + 64 + blk * 32 + c2 * 16, rg);
+        tc_wait_ld();
+        float up[16], gate[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          up[i] = __fmul_rn(__uint_as_float(ru[i]), alpha);
+          gate[i] = __fmul_rn(__uint_as_float(rg[i]), alpha);
+        }
+        if (p.tap != nullptr && valid && cols_ok) {
+          float* trow = p.tap + pos * p.w_rows + col0 + blk * 32 + c2 * 16;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            trow[p.sub0_base + i] = up[i];
+            trow[p.sub1_base + i] = gate[i];
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          h[c2 * 16 + i] = act_gated<EPI == EPI_FC1_GATED>(gate[i], up[i], p);
+      }
+      uint32_t o[8];
+      uint8_t sfb;
+      requant_block32_mx(h, o, sfb);
+      if (valid && cols_ok) {
+        uint4* dst = reinterpret_cast<uint4*>(qrow + blk * 32);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+      sfw |= static_cast<uint32_t>(sfb) << (8 * blk);
+    }
+    tc_fence_before();
+    __syncwarp();
+    release();
+    if (cols_ok && nrows > 0) store_sf<kBlocks>(sft, m, col0 >> 5, sfw);
+  } else if (KIND == KIND_MX && EPI == EPI_FC1_RELU2) {
+    constexpr int kBlocks = BN / 64;
+    const int col0 = nt * BN + half * (BN / 2);
+    if (col0 < p.out_cols) {
+      uint8_t* qrow = p.out_q + pos * p.out_cols + col0;
+      uint32_t sfw = 0u;
+#pragma unroll 1
+      for (int blk = 0; blk < kBlocks; ++blk) {
+        float h[32];
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2) {
+          uint32_t rr[16];
+          tc_ld_32x32b_x16(t_lane + half * (BN / 2) + blk * 32 + c2 * 16, rr);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float v = __fmul_rn(__uint_as_float(rr[i]), alpha);
+            if (p.tap != nullptr && valid && col0 + blk * 32 < p.out_cols)
+              p.tap[pos * p.w_rows + col0 + blk * 32 + c2 * 16 + i] = v;
+            const float r = fmaxf(v, 0.f);
+            h[c2 * 16 + i] = __fmul_rn(r, r);
+          }
+        }
+        uint32_t o[8];
+        uint8_t sfb;
+        requant_block32_mx(h, o, sfb);
+        if (valid && col0 + blk * 32 < p.out_cols) {
+          uint4* dst = reinterpret_cast<uint4*>(qrow + blk * 32);
+          dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+          dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+        sfw |= static_cast<uint32_t>(sfb) << (8 * blk);
+      }
+      store_sf<kBlocks>(sft, m, col0 >> 5, sfw);
+    }
+    tc_fence_before();
+    __syncwarp();
+    release();
+  } else if (kGated) {
+    const float gs2 = p.gscale2[p.gscale_len > 1 ? e : 0];
+    const float rgs2 = __frcp_rn(gs2);
+    // TMEM columns of a pair group: 64 up values then the 64 gate values of the same columns
+    constexpr int kUpCol = BN == 256 ? 128 : 32;
+    const int col0 = nt * kPairs + half * (kPairs / 2);   // first intermediate column of this warp
+    uint8_t* qrow = p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1);
+    uint32_t sfw = 0u;
+#pragma unroll 2
+    for (int ch = 0; ch < kGatedChunks; ++ch) {
+      uint32_t ru[16], rg[16];
+      tc_ld_32x32b_x16(t_lane + half * kUpCol + ch * 16, ru);
+      tc_ld_32x32b_x16(t_lane + half * kUpCol + 64 + ch * 16, rg);
+      tc_wait_ld();
+      float up[16], gate[16], h[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        up[i] = __fmul_rn(__uint_as_float(ru[i]), alpha);
+        gate[i] = __fmul_rn(__uint_as_float(rg[i]), alpha);
+      }
+      if (p.tap != nullptr && valid && col0 < p.out_cols) {
+        float* trow = p.tap + pos * p.w_rows + col0 + ch * 16;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          trow[p.sub0_base + i] = up[i];
+          trow[p.sub1_base + i] = gate[i];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        h[i] = round_bf16(act_gated<EPI == EPI_FC1_GATED>(gate[i], up[i], p));
+      uint32_t lo, hi;
+      uint8_t sfb;
+      requant_block16(h, gs2, rgs2, lo, hi, sfb);
+      if (valid && col0 < p.out_cols) *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
+      sfw |= static_cast<uint32_t>(sfb) << (8 * ch);
+    }
+    tc_fence_before();
+    __syncwarp();
+    release();
+    // scale atoms are per tile: padding rows are written too (their values are never used)
+    if (col0 < p.out_cols && nrows > 0) store_sf<kGatedChunks>(sft, m, col0 >> 4, sfw);
+  } else if (EPI == EPI_FC1_RELU2) {
+    const float gs2 = p.gscale2[p.gscale_len > 1 ? e : 0];
+    const float rgs2 = __frcp_rn(gs2);
+    const int col0 = nt * BN + half * (BN / 2);
+    if (col0 < p.out_cols) {
+      uint8_t* qrow = p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1);
+      uint32_t sfw[2] = {0u, 0u};
+#pragma unroll 1
+      for (int ch = 0; ch < kPlainChunks; ++ch) {
+        uint32_t rr[16];
+        tc_ld_32x32b_x16(t_lane + half * (BN / 2) + ch * 16, rr);
+        tc_wait_ld();
+        float h[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float v = __fmul_rn(__uint_as_float(rr[i]), alpha);
+          if (p.tap != nullptr && valid && col0 + ch * 16 < p.out_cols)
+            p.tap[pos * p.w_rows + col0 + ch * 16 + i] = v;
+          const float r = fmaxf(v, 0.f);
+          h[i] = round_bf16(__fmul_rn(r, r));
+        }
+        uint32_t lo, hi;
+        uint8_t sfb;
+        requant_block16(h, gs2, rgs2, lo, hi, sfb);
+        if (valid && col0 + ch * 16 < p.out_cols)
+          *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
+        if (ch < 4) sfw[0] |= static_cast<uint32_t>(sfb) << (8 * ch);
+        else sfw[1] |= static_cast<uint32_t>(sfb) << (8 * (ch - 4));
+      }
+      if (nrows > 0) store_sf<4>(sft, m, col0 >> 4, sfw[0]);
+      if (nrows > 0 && kPlainChunks == 8 && col0 + 64 < p.out_cols) store_sf<4>(sft, m, (col0 >> 4) + 4, sfw[1]);
+    }
+    tc_fence_before();
+    __syncwarp();
+    release();
+  } else {
+    const int col0 = nt * BN + half * (BN / 2);
+    float* orow = p.out_f32 + pos * p.out_cols + col0;
+#pragma unroll 2
+    for (int ch = 0; ch < kPlainChunks; ++ch) {
+      uint32_t rr[16];
+      tc_ld_32x32b_x16(t_lane + half * (BN / 2) + ch * 16, rr);
+      tc_wait_ld();
+      if (valid && col0 + ch * 16 < p.out_cols) {
+        float4* dst = reinterpret_cast<float4*>(orow + ch * 16);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          dst[q] = make_float4(__fmul_rn(__uint_as_float(rr[4 * q]), alpha),
+                               __fmul_rn(__uint_as_float(rr[4 * q + 1]), alpha),
+                               __fmul_rn(__uint_as_float(rr[4 * q + 2]), alpha),
+                               __fmul_rn(__uint_as_float(rr[4 * q + 3]), alpha));
+      }
+    }
+    tc_fence_before();
+    __syncwarp();
+    release();
+  }
+}
+
 // ---- host helpers (defined in grouped_gemm_bs.cu) ------------------------------------------
 // 2-D byte matrix [rows][row_bytes], box = box_rows x 128 bytes, 128-byte swizzle.
 int make_tmap_bytes_2d(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,

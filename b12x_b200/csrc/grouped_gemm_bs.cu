@@ -8,7 +8,7 @@
 // One persistent CTA per SM walks the (expert, n-tile, m-tile) work list that the sort kernel left
 // in the scratch arena.  Warp 0 feeds a TMA pipeline (SWIZZLE_128B operand tiles + plain bulk
 // copies of the 512-byte scale atoms), warp 1 issues the block-scaled tcgen05.mma, warps 2..9
-// drain the TMEM accumulator, warp 10 copies the scale atoms into TMEM with tcgen05.cp.
+// drain the TMEM accumulator, warps 10..13 move the scale atoms into TMEM with tcgen05.st.
 //
 // Two tile shapes: BN = 128 (six pipeline stages, the accumulator double-buffered in TMEM so the
 // epilogue of one tile runs under the main loop of the next) and BN = 256 (four stages, one
@@ -24,7 +24,7 @@ constexpr int kBM = 128;            // tile rows (MMA M)
 constexpr int kRowBytes = 128;      // one swizzled operand row per stage
 constexpr int kKPerStage = 256;     // nvfp4: reduction elements per stage
 constexpr int kKPerMma = 64;
-constexpr int kGemmThreads = 352;   // TMA warp, MMA warp, 8 epilogue warps, scale-copy warp
+constexpr int kGemmThreads = 448;   // TMA warp, MMA warp, 8 epilogue warps, 4 scale warps
 constexpr int kTmemCols = 512;
 constexpr int kTmemSf = 256;        // first scale column (accumulators use columns 0..255)
 constexpr int kMaxStages = 6;
@@ -59,77 +59,6 @@ constexpr int gemm_smem_bytes() {
 }
 
 
-// Same arithmetic as quant_block16 in the activation quantiser, with a cheap common path: the
-// quotient x / denom is first approximated by x * rcp(denom) (error < 2 ulp); if the values 2^-21
-// below and above it round to the same E2M1 code, the correctly rounded quotient does too.
-// Only a block with a value that close to a rounding boundary takes the exact division.
-// `rgs` = RN(1 / gs), computed once per tile.
-__device__ __forceinline__ void requant_block16(const float (&v)[16], float gs, float rgs, uint32_t& lo,
-                                                uint32_t& hi, uint8_t& sf_byte) {
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  const float raw = fminf(div_rn_normal(__fmul_rn(amax, gs), 6.0f, 0.16666667163372039794921875f), 448.0f);
-  sf_byte = f32_to_e4m3_rn_sat(raw);
-  const float sf = e4m3_to_f32(sf_byte);
-  const float denom = fmaxf(div_rn_normal(sf, gs, rgs), 1e-30f);
-  const float r = rcp_approx(denom);
-  float a0[8], a1[8], b0[8], b1[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float q0 = __fmul_rn(v[i], r), q1 = __fmul_rn(v[8 + i], r);
-    a0[i] = __fmul_rn(q0, 1.0f - 4.76837158e-7f);
-    b0[i] = __fmul_rn(q0, 1.0f + 4.76837158e-7f);
-    a1[i] = __fmul_rn(q1, 1.0f - 4.76837158e-7f);
-    b1[i] = __fmul_rn(q1, 1.0f + 4.76837158e-7f);
-  }
-  lo = pack_e2m1x8(a0);
-  hi = pack_e2m1x8(a1);
-  if (lo != pack_e2m1x8(b0) || hi != pack_e2m1x8(b1)) {
-    float q0[8], q1[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      q0[i] = __fdiv_rn(v[i], denom);
-      q1[i] = __fdiv_rn(v[8 + i], denom);
-    }
-    lo = pack_e2m1x8(q0);
-    hi = pack_e2m1x8(q1);
-  }
-}
-
-// MXFP8 quantisation of 32 values (b12x/_lib/intrinsics.py:223-265): E8M0 byte = exponent of
-// pow2_ceil(amax / 448), payload = e4m3_rn_sat(x * 2^(127 - byte)).
-__device__ __forceinline__ void requant_block32_mx(const float (&v)[32], uint32_t (&o)[8],
-                                                   uint8_t& sf_byte) {
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  uint32_t bits = __float_as_uint(__fmul_rn(amax, static_cast<float>(1.0 / 448.0)));
-  if (bits & 0x007fffffu) bits = (bits + 0x00800000u) & 0x7f800000u;
-  sf_byte = static_cast<uint8_t>((bits >> 23) & 0xffu);
-  const int ex = 254 - static_cast<int>(sf_byte);
-  const float inv = sf_byte == 0 ? 0.f : __uint_as_float(static_cast<uint32_t>(ex < 0 ? 0 : ex) << 23);
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    uint32_t acc = 0;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float q = fminf(fmaxf(__fmul_rn(v[4 * j + k], inv), -448.f), 448.f);
-      acc |= static_cast<uint32_t>(f32_to_e4m3_rn_sat(q)) << (8 * k);
-    }
-    o[j] = acc;
-  }
-}
-
-// n scale bytes (n = 1, 2 or 4, packed in `word`) -> the tile's atom chain at scale column `col`
-template <int N>
-__device__ __forceinline__ void store_sf(uint8_t* sf_tile, uint32_t m, uint32_t col, uint32_t word) {
-  uint8_t* dst = sf_tile + sf_atom_offset(m, col);
-  if (N == 4) *reinterpret_cast<uint32_t*>(dst) = word;
-  else if (N == 2) *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(word);
-  else *dst = static_cast<uint8_t>(word);
-}
-
 template <int KIND, int EPI, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -155,7 +84,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&tail->full[s], 1);
       mbar_init(&tail->empty[s], 1);
-      mbar_init(&tail->sf_full[s], 1);
+      mbar_init(&tail->sf_full[s], 4);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tail->tmem_full[b], 1);
@@ -321,47 +250,47 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         if (Cfg::kBufs == 2) buf ^= 1;
       }
     }
-  } else if (warp == 10) {
-    // ------------------------------ scale copies -------------------------------
-    // One thread moves the scale atoms of every landed stage from shared memory into TMEM
-    // (tcgen05.cp) and commits them to a barrier of their own.  An MMA that follows a
-    // tcgen05.cp in the SAME thread's instruction stream waits out the copy's latency in the
-    // tensor pipe (about 0.15 us per dependent MMA, measured); from this thread the copies run
-    // stages ahead of the MMA issuer.
-    if (lane == 0) {
-      constexpr int kSfbStep = 4 * (BN / 128);   // scale columns of B per MMA step
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const int ksteps = min(4, (p.kdim - kb * kPerStage) / kPerMma);
-          const uint32_t sfa_t = tmem_base + kTmemSf + stage * Cfg::kSfCols;
-          const uint32_t sfb_t = sfa_t + 16;
-          const uint32_t sfa_s = smem_u32(sSfa + stage * kSmemSfa);
-          const uint32_t sfb_s = smem_u32(sSfb + stage * kSmemSfb);
-          if (KIND == KIND_MX) {
-            tc_cp_32x128b_warpx4(sfa_t, make_desc_sf(sfa_s));
-            tc_cp_32x128b_warpx4(sfb_t, make_desc_sf(sfb_s));
-            if (Cfg::kSfbChains == 2) tc_cp_32x128b_warpx4(sfb_t + 4, make_desc_sf(sfb_s + 2048));
-          } else {
-            for (int j = 0; j < ksteps; ++j) {
-              tc_cp_32x128b_warpx4(sfa_t + 4 * j, make_desc_sf(sfa_s + 512 * j));
-              tc_cp_32x128b_warpx4(sfb_t + kSfbStep * j, make_desc_sf(sfb_s + 512 * j));
-              if (Cfg::kSfbChains == 2)
-                tc_cp_32x128b_warpx4(sfb_t + kSfbStep * j + 4, make_desc_sf(sfb_s + 2048 + 512 * j));
-            }
-          }
-          tc_commit(&tail->sf_full[stage]);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1;
-          }
+  } else if (warp >= 10) {
+    // ------------------------------ scale atoms -> TMEM ---------------------------
+    // Four warps, one per TMEM sub-partition: every landed stage's scale atoms go from shared
+    // memory through registers into the stage's TMEM columns (tcgen05.st), then the warp arrives
+    // on the stage's scale barrier.  The tensor pipe sees only MMAs: a tcgen05.cp per scale atom
+    // costs it about 70 ns (12 per stage at BN = 256 were the whole stage time, measured), and
+    // an MMA issued right behind a tcgen05.cp by the same thread stalls on it.
+    constexpr int kSfbStep = 4 * (BN / 128);   // scale columns of B per MMA step
+    const int sub = warp & 3;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL)) {
+          ok = false;
+          break;
+        }
+        const uint32_t sfa_t =
+            tmem_base + kTmemSf + stage * Cfg::kSfCols + (static_cast<uint32_t>(sub * 32) << 16);
+        const uint32_t sfb_t = sfa_t + 16;
+        const uint8_t* sfa_s = sSfa + stage * kSmemSfa;
+        const uint8_t* sfb_s = sSfb + stage * kSmemSfb;
+        if (KIND == KIND_MX) {
+          // one atom = the four per-32 scales of the stage
+          sf_atoms_to_tmem<1>(sfa_t, sfa_s, lane, 4);
+          sf_atoms_to_tmem<1>(sfb_t, sfb_s, lane, 4);
+          if (Cfg::kSfbChains == 2) sf_atoms_to_tmem<1>(sfb_t + 4, sfb_s + 2048, lane, 4);
+        } else {
+          // one atom per MMA step (copied for all four steps; a short last stage leaves stale atoms unused)
+          sf_atoms_to_tmem<4>(sfa_t, sfa_s, lane, 4);
+          sf_atoms_to_tmem<4>(sfb_t, sfb_s, lane, kSfbStep);
+          if (Cfg::kSfbChains == 2) sf_atoms_to_tmem<4>(sfb_t + 4, sfb_s + 2048, lane, kSfbStep);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->sf_full[stage]);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
         }
       }
     }
@@ -369,9 +298,6 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
     // ------------------------------ epilogue ----------------------------------
     // Eight warps.  Warp w may only read TMEM sub-partition (w & 3), i.e. tile rows
     // 32*(w&3) .. +31; the two warps that share a sub-partition split the tile's columns.
-    constexpr int kPairs = BN / 2;                  // gated: output columns per tile
-    constexpr int kGatedChunks = kPairs / 32;       // 16-column chunks per warp (gated)
-    constexpr int kPlainChunks = BN / 32;           // 16-column chunks per warp (FC2 / relu2)
     const int sub = warp & 3;
     const int half = (warp - 2) >> 2;
     const int m = sub * 32 + lane;            // tile row = TMEM lane
@@ -381,203 +307,15 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
       const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
       const int row0 = p.mtile_row0[c.mt];
       const int nrows = p.mtile_rows[c.mt];
-      const float alpha = p.alphas[c.e];
       if (!mbar_wait_bounded(&tail->tmem_full[buf], acc_phase[buf], abort_flag, p.status,
                              WAIT_TMEM_FULL))
         break;
       acc_phase[buf] ^= 1;
       tc_fence_after();
       const uint32_t t_lane = tmem_base + buf * BN + (static_cast<uint32_t>(sub * 32) << 16);
-      const bool valid = m < nrows;
-      const size_t pos = static_cast<size_t>(row0 + m);
-      uint8_t* sft = p.out_sf + static_cast<size_t>(c.mt) * p.out_atoms * 512;
-
-      if (KIND == KIND_MX && kGated) {
-        // w4a8_mx: the activation output goes straight into the MXFP8 quantiser (no bf16 staging)
-        constexpr int kBlocks = kPairs / 64;      // 32-column blocks per warp
-        constexpr int kUpCol = BN == 256 ? 128 : 32;   // TMEM column of this warp's up values, per half
-        const int col0 = c.nt * kPairs + half * (kPairs / 2);
-        uint8_t* qrow = p.out_q + pos * p.out_cols + col0;
-        uint32_t sfw = 0u;
-        const bool cols_ok = col0 < p.out_cols;
-#pragma unroll 1
-        for (int blk = 0; blk < kBlocks; ++blk) {
-          float h[32];
-#pragma unroll
-          for (int c2 = 0; c2 < 2; ++c2) {
-            uint32_t ru[16], rg[16];
-            tc_ld_32x32b_x16(t_lane + half * kUpCol + blk * 32 + c2 * 16, ru);
-            tc_ld_32x32b_x16(t_lane + half * kUpCol + 64 + blk * 32 + c2 * 16, rg);
-            tc_wait_ld();
-            float up[16], gate[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              up[i] = __fmul_rn(__uint_as_float(ru[i]), alpha);
-              gate[i] = __fmul_rn(__uint_as_float(rg[i]), alpha);
-            }
-            if (p.tap != nullptr && valid && cols_ok) {
-              float* trow = p.tap + pos * p.w_rows + col0 + blk * 32 + c2 * 16;
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                trow[p.sub0_base + i] = up[i];
-                trow[p.sub1_base + i] = gate[i];
-              }
-            }
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              h[c2 * 16 + i] = act_gated<EPI == EPI_FC1_GATED>(gate[i], up[i], p);
-          }
-          uint32_t o[8];
-          uint8_t sfb;
-          requant_block32_mx(h, o, sfb);
-          if (valid && cols_ok) {
-            uint4* dst = reinterpret_cast<uint4*>(qrow + blk * 32);
-            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-          }
-          sfw |= static_cast<uint32_t>(sfb) << (8 * blk);
-        }
-        tc_fence_before();
-        __syncwarp();
+      epilogue_tile<KIND, EPI, BN>(p, c.e, c.mt, c.nt, row0, nrows, t_lane, m, half, lane, [&]() {
         if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
-        if (cols_ok) store_sf<kBlocks>(sft, m, col0 >> 5, sfw);
-      } else if (KIND == KIND_MX && EPI == EPI_FC1_RELU2) {
-        constexpr int kBlocks = BN / 64;
-        const int col0 = c.nt * BN + half * (BN / 2);
-        if (col0 < p.out_cols) {
-          uint8_t* qrow = p.out_q + pos * p.out_cols + col0;
-          uint32_t sfw = 0u;
-#pragma unroll 1
-          for (int blk = 0; blk < kBlocks; ++blk) {
-            float h[32];
-#pragma unroll
-            for (int c2 = 0; c2 < 2; ++c2) {
-              uint32_t rr[16];
-              tc_ld_32x32b_x16(t_lane + half * (BN / 2) + blk * 32 + c2 * 16, rr);
-              tc_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const float v = __fmul_rn(__uint_as_float(rr[i]), alpha);
-                if (p.tap != nullptr && valid && col0 + blk * 32 < p.out_cols)
-                  p.tap[pos * p.w_rows + col0 + blk * 32 + c2 * 16 + i] = v;
-                const float r = fmaxf(v, 0.f);
-                h[c2 * 16 + i] = __fmul_rn(r, r);
-              }
-            }
-            uint32_t o[8];
-            uint8_t sfb;
-            requant_block32_mx(h, o, sfb);
-            if (valid && col0 + blk * 32 < p.out_cols) {
-              uint4* dst = reinterpret_cast<uint4*>(qrow + blk * 32);
-              dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-              dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-            }
-            sfw |= static_cast<uint32_t>(sfb) << (8 * blk);
-          }
-          store_sf<kBlocks>(sft, m, col0 >> 5, sfw);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
-      } else if (kGated) {
-        const float gs2 = p.gscale2[p.gscale_len > 1 ? c.e : 0];
-        const float rgs2 = __frcp_rn(gs2);
-        // TMEM columns of a pair group: 64 up values then the 64 gate values of the same columns
-        constexpr int kUpCol = BN == 256 ? 128 : 32;
-        const int col0 = c.nt * kPairs + half * (kPairs / 2);   // first intermediate column of this warp
-        uint8_t* qrow = p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1);
-        uint32_t sfw = 0u;
-#pragma unroll 2
-        for (int ch = 0; ch < kGatedChunks; ++ch) {
-          uint32_t ru[16], rg[16];
-          tc_ld_32x32b_x16(t_lane + half * kUpCol + ch * 16, ru);
-          tc_ld_32x32b_x16(t_lane + half * kUpCol + 64 + ch * 16, rg);
-          tc_wait_ld();
-          float up[16], gate[16], h[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            up[i] = __fmul_rn(__uint_as_float(ru[i]), alpha);
-            gate[i] = __fmul_rn(__uint_as_float(rg[i]), alpha);
-          }
-          if (p.tap != nullptr && valid && col0 < p.out_cols) {
-            float* trow = p.tap + pos * p.w_rows + col0 + ch * 16;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              trow[p.sub0_base + i] = up[i];
-              trow[p.sub1_base + i] = gate[i];
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            h[i] = round_bf16(act_gated<EPI == EPI_FC1_GATED>(gate[i], up[i], p));
-          uint32_t lo, hi;
-          uint8_t sfb;
-          requant_block16(h, gs2, rgs2, lo, hi, sfb);
-          if (valid && col0 < p.out_cols) *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
-          sfw |= static_cast<uint32_t>(sfb) << (8 * ch);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
-        // scale atoms are per tile: padding rows are written too (their values are never used)
-        if (col0 < p.out_cols) store_sf<kGatedChunks>(sft, m, col0 >> 4, sfw);
-      } else if (EPI == EPI_FC1_RELU2) {
-        const float gs2 = p.gscale2[p.gscale_len > 1 ? c.e : 0];
-        const float rgs2 = __frcp_rn(gs2);
-        const int col0 = c.nt * BN + half * (BN / 2);
-        if (col0 < p.out_cols) {
-          uint8_t* qrow = p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1);
-          uint32_t sfw[2] = {0u, 0u};
-#pragma unroll 1
-          for (int ch = 0; ch < kPlainChunks; ++ch) {
-            uint32_t rr[16];
-            tc_ld_32x32b_x16(t_lane + half * (BN / 2) + ch * 16, rr);
-            tc_wait_ld();
-            float h[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float v = __fmul_rn(__uint_as_float(rr[i]), alpha);
-              if (p.tap != nullptr && valid && col0 + ch * 16 < p.out_cols)
-                p.tap[pos * p.w_rows + col0 + ch * 16 + i] = v;
-              const float r = fmaxf(v, 0.f);
-              h[i] = round_bf16(__fmul_rn(r, r));
-            }
-            uint32_t lo, hi;
-            uint8_t sfb;
-            requant_block16(h, gs2, rgs2, lo, hi, sfb);
-            if (valid && col0 + ch * 16 < p.out_cols)
-              *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
-            if (ch < 4) sfw[0] |= static_cast<uint32_t>(sfb) << (8 * ch);
-            else sfw[1] |= static_cast<uint32_t>(sfb) << (8 * (ch - 4));
-          }
-          store_sf<4>(sft, m, col0 >> 4, sfw[0]);
-          if (kPlainChunks == 8 && col0 + 64 < p.out_cols) store_sf<4>(sft, m, (col0 >> 4) + 4, sfw[1]);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
-      } else {
-        const int col0 = c.nt * BN + half * (BN / 2);
-        float* orow = p.out_f32 + pos * p.out_cols + col0;
-#pragma unroll 2
-        for (int ch = 0; ch < kPlainChunks; ++ch) {
-          uint32_t rr[16];
-          tc_ld_32x32b_x16(t_lane + half * (BN / 2) + ch * 16, rr);
-          tc_wait_ld();
-          if (valid && col0 + ch * 16 < p.out_cols) {
-            float4* dst = reinterpret_cast<float4*>(orow + ch * 16);
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              dst[q] = make_float4(__fmul_rn(__uint_as_float(rr[4 * q]), alpha),
-                                   __fmul_rn(__uint_as_float(rr[4 * q + 1]), alpha),
-                                   __fmul_rn(__uint_as_float(rr[4 * q + 2]), alpha),
-                                   __fmul_rn(__uint_as_float(rr[4 * q + 3]), alpha));
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
-      }
+      });
       if (Cfg::kBufs == 2) buf ^= 1;
     }
   }

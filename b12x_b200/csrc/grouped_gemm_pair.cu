@@ -1,0 +1,455 @@
+// Stages 4 and 5 for large batches (recipe nvfp4) on CTA PAIRS: tcgen05 with cta_group::2.
+//
+// Two CTAs of a cluster share one 256 x 256 tile: each owns 128 token rows (its own row tile of the
+// expert) and loads only HALF of the 256 weight rows; the pair's MMA (M = 256, N = 256, issued by
+// one thread of the even CTA) reads the weight halves out of both CTAs' shared memory and writes a
+// 128 x 256 accumulator into each CTA's tensor memory.  Per CTA and 256-value k-block that is
+// 16 KiB of token rows + 16 KiB of weight rows + 6 KiB of scale atoms from L2 instead of 16 + 32 + 6:
+// the wide single-CTA kernel is limited by exactly that operand stream.
+//
+// Roles per CTA (448 threads): warp 0 TMA producer (the operand copies of either CTA complete on
+// the EVEN CTA's stage barrier, the scale atoms on a barrier of the CTA itself), warps 2..9
+// epilogue of the CTA's own accumulator, warps 10..13 move the CTA's scale atoms into its tensor
+// memory (tcgen05.st) and arrive on the even CTA's scale barrier.  Even CTA only: warp 1 issues the
+// MMAs and commits (multicast) to both CTAs' barriers.  The odd CTA's epilogue warps release the
+// accumulator with remote arrives on the even CTA's barrier.  Every wait is bounded; the two cluster-wide
+// barriers (after set-up, before tear-down) are reached by both CTAs unconditionally.
+#include <stdlib.h>
+
+#include "gemm_shared.cuh"
+
+namespace b200moe {
+namespace pair {
+
+constexpr int kThreads = 448;
+constexpr int kStages = 5;
+constexpr int kRowBytes = 128;
+constexpr int kSmemA = 128 * kRowBytes;       // this CTA's 128 token rows, one k-block
+constexpr int kSmemB = 128 * kRowBytes;       // this CTA's half of the 256 weight rows
+constexpr int kSmemSfa = 4 * 512;             // scale atoms of the token rows
+constexpr int kSmemSfb = 2 * 4 * 512;         // scale atoms of all 256 weight rows (two chains)
+constexpr int kStageBytes = kSmemA + kSmemB + kSmemSfa + kSmemSfb;
+constexpr int kTmemCols = 512;
+constexpr int kTmemSf = 256;                  // accumulator: columns 0..255
+constexpr int kSfCols = 48;                   // per stage: 16 (tokens) + 32 (weights)
+constexpr uint32_t kStageTxBytes = 2u * (kSmemA + kSmemB);   // both CTAs' operand copies of one stage
+
+struct __align__(8) SmemTail {
+  uint64_t full[kStages];       // used in the even CTA: all copies of the pair have landed
+  uint64_t empty[kStages];      // per CTA: the MMAs that read the stage have retired
+  uint64_t sf_landed[kStages];  // per CTA: the stage's scale atoms are in this CTA's shared memory
+  uint64_t sf_full[kStages];    // even CTA: both CTAs' scale atoms are in tensor memory
+  uint64_t tmem_full;           // per CTA: the accumulator is complete
+  uint64_t tmem_empty;          // even CTA: all 16 epilogue warps of the pair have drained it
+  uint32_t tmem_base;
+  int abort_flag;
+  int32_t tile_base[kMaxExperts + 1];
+  int32_t pair_base[kMaxExperts + 1];
+};
+constexpr int kSmemBytes = 1024 + kStages * kStageBytes + static_cast<int>(sizeof(SmemTail));
+
+// ---- cluster / cta_group::2 PTX -------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared-window address of `saddr` (an address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// 2-D tiled load into THIS CTA's shared memory, completing on a barrier of the even CTA.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr,
+                                                 int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+// arrive on the barrier at this offset in both CTAs of the pair when the pair's earlier tcgen05
+// operations have retired
+__device__ __forceinline__ void tc_commit_pair_both(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(mask)
+      : "memory");
+}
+__device__ __forceinline__ void mma_nvf4_4x_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X "
+      "[%0], %1, %2, %3, [%5], [%6], p;\n\t}\n"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+
+// Work item of a CTA pair: (expert, n-tile, pair of row tiles).  This CTA's row tile is
+// first + rank; an expert with an odd number of row tiles leaves the odd CTA of its last pair
+// without one (rows = 0: it multiplies the neighbour's rows again and stores nothing).
+struct PairCoord {
+  int e, nt, mt_load, mt, rows;
+};
+__device__ __forceinline__ PairCoord decode_pair(int w, const GemmParams& p, const SmemTail* tail, int rank) {
+  const TileCoord c = decode_tile(w, p.n_tiles, tail->pair_base, p.E);
+  PairCoord r;
+  r.e = c.e;
+  r.nt = c.nt;
+  const int last = tail->tile_base[c.e + 1] - 1;
+  r.mt = tail->tile_base[c.e] + 2 * (c.mt - tail->pair_base[c.e]) + rank;
+  r.mt_load = r.mt <= last ? r.mt : last;
+  r.rows = r.mt <= last ? p.mtile_rows[r.mt] : 0;
+  return r;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                               const GemmParams p) {
+  constexpr bool kGated = EPI == EPI_FC1_GATED || EPI == EPI_FC1_SILU;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + kStages * kSmemA;
+  uint8_t* sSfa = sB + kStages * kSmemB;
+  uint8_t* sSfb = sSfa + kStages * kSmemSfa;
+  SmemTail* tail = reinterpret_cast<SmemTail*>(sSfb + kStages * kSmemSfb);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_ctarank());     // 0 = even CTA (issues the MMAs)
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->empty[s], 1);
+      mbar_init(&tail->sf_landed[s], 1);
+      mbar_init(&tail->sf_full[s], 8);
+    }
+    mbar_init(&tail->tmem_full, 1);
+    mbar_init(&tail->tmem_empty, 16);
+    tail->abort_flag = 0;
+    fence_mbar_init();
+    // row tiles and tile pairs per expert (prefix sums)
+    int acc = 0;
+    for (int e = 0; e < p.E; ++e) {
+      const int t0 = p.tile_base[e], t1 = p.tile_base[e + 1];
+      tail->tile_base[e] = t0;
+      tail->pair_base[e] = acc;
+      acc += (t1 - t0 + 1) >> 1;
+      if (e == p.E - 1) tail->tile_base[p.E] = t1;
+    }
+    tail->pair_base[p.E] = acc;
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&tail->tmem_base, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // both CTAs' barriers are initialised before anyone signals them
+  tc_fence_after();
+
+  const uint32_t tmem_base = tail->tmem_base;
+  volatile int* abort_flag = &tail->abort_flag;
+  const int total_work = tail->pair_base[p.E] * p.n_tiles;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ---------------------
+    // lane 0: (even CTA) arms the stage barrier; token rows.  lanes 1, 2: the two 64-row boxes
+    // of this CTA's weight half.  lane 3: token scale atoms.  lanes 4, 5: the two weight scale
+    // chains (both CTAs fetch both).
+    if (lane < 6) {
+      if (lane == 0) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+        const PairCoord c = decode_pair(w, p, tail, rank);
+        const int row0 = p.mtile_row0[c.mt_load];
+        int y = 0;                      // row coordinate of this lane's operand copy
+        const uint8_t* my_sf = nullptr; // atom chain of this lane's scale copy
+        if (lane == 0) {
+          y = row0;
+        } else if (lane <= 2) {
+          const int b = lane - 1;
+          int wrow;
+          if (kGated) {
+            int g = 2 * c.nt + rank;                               // pair group of this CTA
+            if (g * 64 >= p.out_cols) g = 2 * c.nt;                // half-empty last tile
+            wrow = (b ? p.sub1_base : p.sub0_base) + g * 64;       // 64 up rows / 64 gate rows
+          } else {
+            wrow = c.nt * 256 + rank * 128 + b * 64;
+            if (wrow >= p.w_rows) wrow = c.nt * 256 + b * 64;
+          }
+          y = c.e * p.w_rows + wrow;
+        } else if (lane == 3) {
+          my_sf = p.sfa + static_cast<size_t>(c.mt_load) * p.atoms_k * 512;
+        } else {
+          int rg = 2 * c.nt + (lane - 4);
+          if (rg >= p.sfb_rowgroups) rg = 2 * c.nt;
+          my_sf = p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + rg) * p.atoms_k * 512;
+        }
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status, WAIT_SMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          // operand rows complete on the EVEN CTA's barrier, scale atoms on this CTA's own
+          const uint32_t bar = map_to_cta(smem_u32(&tail->full[stage]), 0);
+          const int ksteps = min(4, (p.kdim - kb * 256) / 64);
+          const uint32_t sf_bytes = static_cast<uint32_t>(ksteps) * 512u;
+          const size_t sf_off = static_cast<size_t>(kb) * 2048;
+          if (lane == 0) {
+            if (rank == 0) mbar_expect_tx(&tail->full[stage], kStageTxBytes);
+            tma_load_2d_pair(sA + stage * kSmemA, &tmA, bar, kb * kRowBytes, y);
+          } else if (lane <= 2) {
+            tma_load_2d_pair(sB + stage * kSmemB + (lane - 1) * 64 * kRowBytes, &tmB, bar, kb * kRowBytes, y);
+          } else if (lane == 3) {
+            mbar_expect_tx(&tail->sf_landed[stage], 3u * sf_bytes);
+            bulk_load(sSfa + stage * kSmemSfa, my_sf + sf_off, sf_bytes, &tail->sf_landed[stage]);
+          } else {
+            bulk_load(sSfb + stage * kSmemSfb + (lane - 4) * 2048, my_sf + sf_off, sf_bytes, &tail->sf_landed[stage]);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);   // let copies in flight land
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even CTA) -------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_block_scaled(256, 256, /*a*/ 1, /*b*/ 1, /*ue4m3*/ 0);
+      int stage = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+        if (!mbar_wait_bounded(&tail->tmem_empty, acc_phase ^ 1, abort_flag, p.status, WAIT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL) ||
+              !mbar_wait_bounded(&tail->sf_full[stage], phase, abort_flag, p.status, WAIT_SF_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const int ksteps = min(4, (p.kdim - kb * 256) / 64);
+          const uint32_t sfa_t = tmem_base + kTmemSf + stage * kSfCols;
+          const uint32_t sfb_t = sfa_t + 16;
+          const uint64_t adesc = make_desc_sw128(smem_u32(sA + stage * kSmemA));
+          const uint64_t bdesc = make_desc_sw128(smem_u32(sB + stage * kSmemB));
+          for (int j = 0; j < ksteps; ++j)
+            mma_nvf4_4x_pair(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j, sfb_t + 8 * j,
+                             (kb > 0 || j > 0) ? 1u : 0u);
+          tc_commit_pair_both(&tail->empty[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit_pair_both(&tail->tmem_full);
+        acc_phase ^= 1;
+      }
+    }
+  } else if (warp >= 10) {
+    // ------------------------------ scale atoms -> TMEM (both CTAs) ---------------
+    // Four warps, one per TMEM sub-partition, move every landed stage's scale atoms from this
+    // CTA's shared memory into this CTA's tensor memory (tcgen05.st) and arrive on the even
+    // CTA's scale barrier (8 arrivals: 4 warps of each CTA).
+    const int sub = warp & 3;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        if (!mbar_wait_bounded(&tail->sf_landed[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL)) {
+          ok = false;
+          break;
+        }
+        const uint32_t sfa_t = tmem_base + kTmemSf + stage * kSfCols + (static_cast<uint32_t>(sub * 32) << 16);
+        const uint32_t sfb_t = sfa_t + 16;
+        sf_atoms_to_tmem<4>(sfa_t, sSfa + stage * kSmemSfa, lane, 4);
+        sf_atoms_to_tmem<4>(sfb_t, sSfb + stage * kSmemSfb, lane, 8);
+        sf_atoms_to_tmem<4>(sfb_t + 4, sSfb + stage * kSmemSfb + 2048, lane, 8);
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tail->sf_full[stage]), 0));
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) --------------------------
+    const int sub = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int m = sub * 32 + lane;
+    const uint32_t release_addr = map_to_cta(smem_u32(&tail->tmem_empty), 0);
+    uint32_t acc_phase = 0;
+    for (int w = cluster_id; w < total_work; w += num_clusters) {
+      const PairCoord c = decode_pair(w, p, tail, rank);
+      const int row0 = p.mtile_row0[c.mt_load];
+      if (!mbar_wait_bounded(&tail->tmem_full, acc_phase, abort_flag, p.status, WAIT_TMEM_FULL)) break;
+      acc_phase ^= 1;
+      tc_fence_after();
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(sub * 32) << 16);
+      epilogue_tile<KIND_NVFP4, EPI, 256>(p, c.e, c.mt_load, c.nt, row0, c.rows, t_lane, m, half, lane, [&]() {
+        if (lane == 0) mbar_arrive_cluster(release_addr);
+      });
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // nobody signals the other CTA's shared memory after this
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+template <int EPI>
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int max_ctas,
+                  cudaStream_t s) {
+  auto kern = grouped_gemm_nvfp4_pair_kernel<EPI>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+    return B200MOE_ECUDA;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = s;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  // persistent grid: as many CTA pairs as can be resident at once
+  cfg.gridDim = dim3(static_cast<unsigned>(max_ctas & ~1));
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess || clusters < 1) return B200MOE_ECUDA;
+  if (2 * clusters < max_ctas) cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p) == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+}  // namespace pair
+
+// The CTA-pair kernels serve nvfp4 plans with 128-row tiles and gated FC1 (or FC2).  They are
+// correct but, as measured, slower than the single-CTA wide kernel (the stage hand-shake crosses
+// the CTA pair twice per stage and the pipeline of five stages does not cover that latency), so
+// they only run when B200MOE_PAIR=1 asks for them.
+bool nvfp4_pair_ok(const b200moe_gemm_args* a, bool fc1) {
+  static int mode = -2;
+  if (mode == -2) {
+    const char* e = getenv("B200MOE_PAIR");
+    mode = e == nullptr ? -1 : (atoi(e) != 0 ? 1 : 0);
+  }
+  if (mode == 0 || a->layout->tile_rows != 128) return false;
+  if (a->hidden_size % 64 != 0 || a->intermediate % 64 != 0 || a->num_experts > kMaxExperts) return false;
+  if (fc1 && a->activation == B200MOE_ACT_RELU2) return false;
+  return mode == 1;
+}
+
+int nvfp4_pair_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
+  const b200moe_scratch_layout& L = *a->layout;
+  const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
+  if (a->a2_gscale == nullptr || a->w13_sf == nullptr) return B200MOE_EINVAL;
+  char* base = static_cast<char*>(a->scratch);
+  GemmParams p = {};
+  fill_common(p, a, base);
+  p.atoms_k = ceil_div_i(K, 64);
+  p.sfb_rowgroups = I / 64;              // pair atoms: 64 up rows + 64 gate rows
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_bytes_2d(&tmA, base + L.act_q, K / 2, L.rows, 128);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_tmap_bytes_2d(&tmB, a->w13, K / 2, static_cast<uint64_t>(E) * 2 * I, 64);
+  if (rc != B200MOE_OK) return rc;
+  p.sfa = reinterpret_cast<const uint8_t*>(base + L.act_sf);
+  p.sfb = a->w13_sf;
+  p.alphas = a->w1_alphas;
+  p.gscale2 = a->a2_gscale;
+  p.out_q = reinterpret_cast<uint8_t*>(base + L.mid_q);
+  p.out_sf = reinterpret_cast<uint8_t*>(base + L.mid_sf);
+  p.tap = a->fc1_tap;
+  p.kdim = K;
+  p.k_blocks = ceil_div_i(K, 256);
+  p.w_rows = 2 * I;
+  p.sub0_base = a->gate_first ? I : 0;   // up rows
+  p.sub1_base = a->gate_first ? 0 : I;   // gate rows
+  p.n_step = 128;
+  p.n_tiles = ceil_div_i(I, 128);
+  p.out_cols = I;
+  p.out_atoms = ceil_div_i(I, 64);
+  const int ctas = a->num_sms > 0 ? a->num_sms : num_sms_cached();
+  if (!p.swigluoai && !(p.limit > 0.f))
+    return pair::launch<EPI_FC1_SILU>(tmA, tmB, p, ctas, stream);
+  return pair::launch<EPI_FC1_GATED>(tmA, tmB, p, ctas, stream);
+}
+
+int nvfp4_pair_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
+  const b200moe_scratch_layout& L = *a->layout;
+  const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
+  if (a->w2_sf == nullptr) return B200MOE_EINVAL;
+  char* base = static_cast<char*>(a->scratch);
+  GemmParams p = {};
+  fill_common(p, a, base);
+  p.atoms_k = ceil_div_i(I, 64);
+  p.sfb_rowgroups = ceil_div_i(K, 128);
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_bytes_2d(&tmA, base + L.mid_q, I / 2, L.rows, 128);
+  if (rc != B200MOE_OK) return rc;
+  rc = make_tmap_bytes_2d(&tmB, a->w2, I / 2, static_cast<uint64_t>(E) * K, 64);
+  if (rc != B200MOE_OK) return rc;
+  p.sfa = reinterpret_cast<const uint8_t*>(base + L.mid_sf);
+  p.sfb = a->w2_sf;
+  p.alphas = a->w2_alphas;
+  p.out_f32 = reinterpret_cast<float*>(base + L.routed);
+  p.kdim = I;
+  p.k_blocks = ceil_div_i(I, 256);
+  p.w_rows = K;
+  p.out_cols = K;
+  p.n_step = 256;
+  p.n_tiles = ceil_div_i(K, 256);
+  const int ctas = a->num_sms > 0 ? a->num_sms : num_sms_cached();
+  return pair::launch<EPI_FC2>(tmA, tmB, p, ctas, stream);
+}
+
+}  // namespace b200moe

@@ -1,0 +1,56 @@
+"""-m gpu: large NVFP4 batches (several 128-row tiles per expert, odd and even tile counts) against
+the CPU oracle.  In-process they run on the wide single-CTA kernels; `test_pair_variant...` re-runs
+this file in a child process with B200MOE_PAIR=1, which puts the same cases on the CTA-pair kernels
+(tcgen05 cta_group::2)."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from b12x_b200 import synth
+from tests.gpu_utils import run_layer
+from tests.test_gpu_parity import _check_nvfp4_layer, _tiny
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("tokens,experts,topk,hidden,inter,act", [
+    (700, 4, 2, 512, 256, "silu"),          # 2-3 row tiles per expert, odd and even counts
+    (1100, 2, 1, 512, 256, "silu"),         # ~4 tiles per expert
+    (600, 2, 2, 640, 192, "silu"),          # K tail (640 = 2.5 k-blocks), half-empty last FC1 tile, FC2 tail
+    (520, 2, 2, 256, 128, "swigluoai"),     # clamp + SwiGLU-OAI epilogue
+])
+def test_pair_kernels_match_oracle(tokens, experts, topk, hidden, inter, act):
+    shp = _tiny(tokens=tokens, experts=experts, topk=topk, hidden=hidden, intermediate=inter, activation=act)
+    assert tokens * topk >= 256 * experts      # at least two full row tiles per expert on average
+    run = run_layer(synth.make_inputs(shp, seed=tokens + hidden), want_fc1=True)
+    assert int(run.binding.core_layout.tile_rows) == 128
+    _check_nvfp4_layer(run)
+
+
+def test_pair_single_expert_odd_tile_count():
+    shp = _tiny(tokens=300, experts=1, topk=1, hidden=512, intermediate=256)
+    inp = synth.make_inputs(shp, seed=31)
+    ids = torch.zeros((300, 1), dtype=torch.int32)
+    w = torch.rand(300, 1) + 0.5
+    _check_nvfp4_layer(run_layer(inp, topk_ids=ids, topk_weights=w))
+
+
+def test_pair_repeat_runs_bitwise_identical():
+    inp = synth.make_inputs(_tiny(tokens=640, experts=2, topk=2, hidden=512, intermediate=256), seed=32)
+    a = run_layer(inp, poison=0x00)
+    b = run_layer(inp, poison=0xFF)
+    assert torch.equal(a.out, b.out) and torch.equal(a.out_f32, b.out_f32)
+
+
+@pytest.mark.timeout(600)
+def test_pair_variant_passes_these_cases():
+    if os.environ.get("B200MOE_PAIR") == "1":
+        pytest.skip("already the child run")
+    env = dict(os.environ, B200MOE_PAIR="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-m", "gpu", "-x", "-q", "-p", "no:cacheprovider"],
+                       env=env, capture_output=True, text=True, timeout=550)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
