@@ -347,7 +347,9 @@ def main():
     peaks = load_peaks()
     stats = layer.work_stats()   # algorithmic bytes / flops of the dominant kernel on this rank
     if rank == 0:
-        total_tokens = shp.tokens * world
+        # tensor parallelism replicates the tokens (strong scaling); expert parallelism gives every rank its own batch
+        tp = world > 1 and shp.parallelism == "tp"
+        total_tokens = shp.tokens if tp else shp.tokens * world
         dom = stats["dominant"]
         dom_ms = stages.get(dom["stage"], float("nan"))
         if dom["bound"] == "hbm":
@@ -363,13 +365,13 @@ def main():
         line = {
             "metric": "moe_layer_tokens_per_s", "value": total_tokens / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_of(shp),
+            "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": dtype_of(shp),
             "data": "synthetic", "config": config_of(shp, world, args.ep, graph is not None and args.ep == "peer"), "clocks": clocks,
             "e2e": {"value": total_tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2 + lg_host.numel() * 4,
                     "d2h_bytes_per_step": out_host.numel() * 2},
             "gpu_launches": args.steps * layer.kernels_per_step,
-            "tflops": shp.flops * world / (ms * 1e-3) / 1e12,
+            "tflops": shp.flops * (1 if tp else world) / (ms * 1e-3) / 1e12,
             "stage_ms": stages,
             "roofline": {"kernel": dom["kernel"], "bound": dom["bound"], "achieved": achieved, "peak": peak,
                          "unit": unit, "frac": achieved / peak, "peak_source": peaks["source"] + dom.get("peak_note", ""),
