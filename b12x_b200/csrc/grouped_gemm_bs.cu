@@ -47,6 +47,7 @@ struct __align__(8) GemmSmemTail {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t sf_landed[kMaxStages]; // scale atoms of the stage are in shared memory
   uint64_t sf_full[kMaxStages];   // scale atoms of the stage are in TMEM
   uint32_t tmem_base;
   int abort_flag;
@@ -84,6 +85,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&tail->full[s], 1);
       mbar_init(&tail->empty[s], 1);
+      mbar_init(&tail->sf_landed[s], 1);
       mbar_init(&tail->sf_full[s], 4);
     }
     for (int b = 0; b < 2; ++b) {
@@ -165,16 +167,20 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
           // the unpacking TMA type counts the packed bytes it reads (64 per 128-value row)
           const uint32_t b_bytes = KIND == KIND_MX ? kSmemB / 2 : kSmemB;
           uint64_t* bar = &tail->full[stage];
+          // the (small) scale atoms complete on a barrier of their own, so that their way into
+          // TMEM starts before the operand rows of the stage have all landed
+          uint64_t* sf_bar = &tail->sf_landed[stage];
           if (lane == 0) {
-            mbar_expect_tx(bar, a_bytes + b_bytes + (1u + Cfg::kSfbChains) * sf_bytes);
+            mbar_expect_tx(bar, a_bytes + b_bytes);
             tma_load_2d(sA + stage * kSmemA, tma_a, bar, kb * kRowBytes, row0);
           } else if (lane <= kBoxes) {
             tma_load_2d(sB + stage * kSmemB + (lane - 1) * 64 * kRowBytes, &tmB, bar, kb * kRowBytes,
                         c.e * p.w_rows + my_row);
           } else if (lane == kBoxes + 1) {
-            bulk_load(sSfa + stage * kSmemSfa, my_sf + sf_off, sf_bytes, bar);
+            mbar_expect_tx(sf_bar, (1u + Cfg::kSfbChains) * sf_bytes);
+            bulk_load(sSfa + stage * kSmemSfa, my_sf + sf_off, sf_bytes, sf_bar);
           } else {
-            bulk_load(sSfb + stage * kSmemSfb + (lane - kBoxes - 2) * 2048, my_sf + sf_off, sf_bytes, bar);
+            bulk_load(sSfb + stage * kSmemSfb + (lane - kBoxes - 2) * 2048, my_sf + sf_off, sf_bytes, sf_bar);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -264,7 +270,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
     bool ok = true;
     for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL)) {
+        if (!mbar_wait_bounded(&tail->sf_landed[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL)) {
           ok = false;
           break;
         }
