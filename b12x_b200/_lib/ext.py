@@ -140,6 +140,10 @@ EXPORTS = {
     "b200moe_ep_signal": ([C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p], C.c_int),
     "b200moe_ep_wait": ([C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p], C.c_int),
     "b200moe_ep_combine": ([C.POINTER(EpCombineArgs), C.c_void_p], C.c_int),
+    "b200moe_quantize_rows_nvfp4": ([C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                     C.c_void_p, C.c_void_p], C.c_int),
+    "b200moe_quantize_rows_mxfp8": ([C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                     C.c_void_p, C.c_void_p], C.c_int),
 }
 
 

@@ -244,6 +244,115 @@ __global__ void __launch_bounds__(256) combine_kernel(
 }
 
 // ------------------------------------------------------------------------------------------
+// Standalone row quantisers (the reference's quantization.nvfp4 / quantization.mxfp8 ops): a
+// dense [M, K] bf16 matrix, no permutation; codes row-major, scales as 128-row atom chains
+// ([row group][k atom][512 bytes], the 128x4-swizzled layout) and, for MXFP8, also row-major.
+//
+// NVFP4 here is the "reciprocal" arithmetic of the reference's grouped quantiser
+// (b12x/_lib/intrinsics.py:149-193), which differs from the MoE path's direct division:
+//   sf   = e4m3_rn(gs * (amax / 6))
+//   out  = 1 / (sf * (1 / gs))          (a zero factor gives zero, not infinity)
+//   code = e2m1_rte(clamp(x * out, -6, 6))
+// A scale beyond the E4M3 range saturates to 448 (torch yields NaN there; the op's contract
+// gs = 448 * 6 / amax(tensor) keeps scales in range).
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float recip_or_zero(float v) { return v == 0.f ? 0.f : __fdiv_rn(1.0f, v); }
+
+__global__ void __launch_bounds__(256) quantize_rows_nvfp4_kernel(
+    const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, int M, int K, const float* __restrict__ gscale,
+    uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf) {
+  const int nblk = K >> 4;
+  const int atoms = (nblk + 3) >> 2;
+  const float gs = gscale[0];
+  const float rgs = recip_or_zero(gs);
+  const int lane = threadIdx.x & 31;
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(row) * x_row_stride);
+    uint2* dst = reinterpret_cast<uint2*>(out_q + static_cast<size_t>(row) * (K >> 1));
+    uint8_t* sf_tile = out_sf + static_cast<size_t>(row >> 7) * atoms * 512;
+    for (int b0 = (threadIdx.x >> 5) * 32; b0 < nblk; b0 += 256) {
+      const int b = b0 + lane;
+      uint8_t sfb = 0;
+      if (b < nblk) {
+        const uint4 p0 = __ldg(src + 2 * b), p1 = __ldg(src + 2 * b + 1);
+        const uint32_t w[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+        float v[16];
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[2 * j] = __uint_as_float(w[j] << 16);
+          v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+          amax = fmaxf(amax, fmaxf(fabsf(v[2 * j]), fabsf(v[2 * j + 1])));
+        }
+        sfb = f32_to_e4m3_rn_sat(__fmul_rn(gs, __fdiv_rn(amax, 6.0f)));
+        const float out = recip_or_zero(__fmul_rn(e4m3_to_f32(sfb), rgs));
+        float q0[8], q1[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          q0[i] = fminf(fmaxf(__fmul_rn(v[i], out), -6.0f), 6.0f);
+          q1[i] = fminf(fmaxf(__fmul_rn(v[8 + i], out), -6.0f), 6.0f);
+        }
+        dst[b] = make_uint2(pack_e2m1x8(q0), pack_e2m1x8(q1));
+      }
+      uint32_t word = sfb;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 1) << 8;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 2) << 16;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 3) << 24;
+      if ((lane & 3) == 0 && b < nblk)
+        *reinterpret_cast<uint32_t*>(sf_tile + sf_atom_offset(row & 127, b)) = word;
+    }
+  }
+}
+
+// MXFP8 rows (b12x/_lib/intrinsics.py:223-312): the arithmetic of permute_quant_mxfp8_kernel.
+// Scale bytes go row-major to `scale_rows` and / or swizzled to `scale_mma` (either may be null);
+// only the bytes of live rows and real columns are written.
+__global__ void __launch_bounds__(256) quantize_rows_mxfp8_kernel(
+    const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, int M, int K, uint8_t* __restrict__ values,
+    uint8_t* __restrict__ scale_rows, uint8_t* __restrict__ scale_mma) {
+  const int nblk = K >> 5;
+  const int atoms = (nblk + 3) >> 2;
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(row) * x_row_stride);
+    uint4* dst = reinterpret_cast<uint4*>(values + static_cast<size_t>(row) * K);
+    for (int b = threadIdx.x; b < nblk; b += blockDim.x) {
+      float v[32];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 p = __ldg(src + 4 * b + q);
+        const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[q * 8 + 2 * j] = __uint_as_float(w[j] << 16);
+          v[q * 8 + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
+      const uint8_t sfb = ue8m0_ceil_byte(__fmul_rn(amax, static_cast<float>(1.0 / 448.0)));
+      const float inv = ue8m0_inv_scale(sfb);
+      uint32_t o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float sc = fminf(fmaxf(__fmul_rn(v[4 * j + k], inv), -448.f), 448.f);
+          acc |= static_cast<uint32_t>(f32_to_e4m3_rn_sat(sc)) << (8 * k);
+        }
+        o[j] = acc;
+      }
+      dst[2 * b] = make_uint4(o[0], o[1], o[2], o[3]);
+      dst[2 * b + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+      if (scale_rows != nullptr) scale_rows[static_cast<size_t>(row) * nblk + b] = sfb;
+      if (scale_mma != nullptr)
+        scale_mma[static_cast<size_t>(row >> 7) * atoms * 512 + sf_atom_offset(row & 127, b)] = sfb;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // gather_rows: send-side packing of the expert-parallel dispatch (one warp per row, 16-byte
 // vectors).  Rows are ordered by the preceding sort (destination rank, then flat route id).
 // ------------------------------------------------------------------------------------------
@@ -386,5 +495,36 @@ extern "C" int b200moe_combine(const b200moe_combine_args* a, void* stream) {
   else if (a->num_topk <= 4) combine_kernel<4><<<grid, 256, smem, cs>>>(B200MOE_COMBINE_ARGS);
   else combine_kernel<8><<<grid, 256, smem, cs>>>(B200MOE_COMBINE_ARGS);
 #undef B200MOE_COMBINE_ARGS
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+extern "C" int b200moe_quantize_rows_nvfp4(const void* x, int64_t x_row_stride, int32_t m, int32_t k,
+                                           const float* global_scale, uint8_t* out_q, uint8_t* out_sf,
+                                           void* stream) {
+  if (x == nullptr || global_scale == nullptr || out_q == nullptr || out_sf == nullptr) return B200MOE_EINVAL;
+  if (m < 0 || k <= 0 || k % 16 != 0) return B200MOE_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (x_row_stride % 8) != 0 ||
+      (reinterpret_cast<uintptr_t>(out_q) & 7) != 0 || (reinterpret_cast<uintptr_t>(out_sf) & 3) != 0)
+    return B200MOE_EALIGN;
+  if (m == 0) return B200MOE_OK;
+  const int grid = m < 148 * 8 ? m : 148 * 8;
+  quantize_rows_nvfp4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), x_row_stride, m, k, global_scale, out_q, out_sf);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+extern "C" int b200moe_quantize_rows_mxfp8(const void* x, int64_t x_row_stride, int32_t m, int32_t k,
+                                           uint8_t* values, uint8_t* scale_rows, uint8_t* scale_mma,
+                                           void* stream) {
+  if (x == nullptr || values == nullptr) return B200MOE_EINVAL;
+  if (m < 0 || k <= 0 || k % 32 != 0) return B200MOE_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (x_row_stride % 8) != 0 ||
+      (reinterpret_cast<uintptr_t>(values) & 15) != 0)
+    return B200MOE_EALIGN;
+  if (m == 0) return B200MOE_OK;
+  const int grid = m < 148 * 8 ? m : 148 * 8;
+  const int threads = k / 32 >= 256 ? 256 : (k / 32 >= 128 ? 128 : 64);
+  quantize_rows_mxfp8_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), x_row_stride, m, k, values, scale_rows, scale_mma);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }

@@ -293,6 +293,20 @@ typedef struct {
  * it), fp32, slot order, one bf16 rounding: the return all-to-all and the combine in one kernel. */
 int b200moe_ep_combine(const b200moe_ep_combine_args* a, void* stream);
 
+/* ---- standalone activation quantisers ------------------------------------- */
+/* Replace the reference's quantization.nvfp4 op (b12x/quantization/nvfp4/api.py:24-62; numerics of
+ * quantize_grouped_nvfp4_torch, b12x/_lib/intrinsics.py:149-193: sf = e4m3(gs * (amax / 6)),
+ * code = e2m1_rte(clamp(x / (sf / gs), +-6)) evaluated with reciprocals) and quantization.mxfp8
+ * (b12x/quantization/mxfp8/api.py:5-18; b12x/_lib/intrinsics.py:223-312).  x: bf16 [m][k], row
+ * stride in elements.  out_q: [m][k/2] (two E2M1 per byte) resp. values [m][k] E4M3.  Scales: 128x4
+ * swizzled atoms [ceil(m/128)][ceil(k/64 | k/128)][512] (out_sf, scale_mma) and row-major UE8M0
+ * [m][k/32] (scale_rows); scale_rows / scale_mma may be NULL.  Only bytes of live rows are written. */
+int b200moe_quantize_rows_nvfp4(const void* x, int64_t x_row_stride, int32_t m, int32_t k,
+                                const float* global_scale /* device, 1 value */, uint8_t* out_q,
+                                uint8_t* out_sf, void* stream);
+int b200moe_quantize_rows_mxfp8(const void* x, int64_t x_row_stride, int32_t m, int32_t k, uint8_t* values,
+                                uint8_t* scale_rows, uint8_t* scale_mma, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
