@@ -1,2 +1,2 @@
 """Mixture-of-experts operators."""
-from . import fused_moe  # noqa: F401
+from . import ep_moe, fused_moe  # noqa: F401
