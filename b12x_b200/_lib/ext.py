@@ -51,7 +51,8 @@ class SortArgs(C.Structure):
     _fields_ = [("topk_ids", C.c_void_p), ("expert_map", C.c_void_p), ("scratch", C.c_void_p),
                 ("layout", C.POINTER(ScratchLayout)),
                 ("num_tokens", C.c_int32), ("num_topk", C.c_int32), ("num_experts", C.c_int32),
-                ("expert_map_len", C.c_int32)]
+                ("expert_map_len", C.c_int32), ("wait_flags", C.c_void_p), ("wait_epoch_dev", C.c_void_p),
+                ("wait_status", C.c_void_p), ("wait_world", C.c_int32), ("wait_timeout_ms", C.c_int32)]
 
 
 class QuantArgs(C.Structure):
@@ -110,7 +111,8 @@ class EpCombineArgs(C.Structure):
                 ("peer_inv_perm_off", C.c_int64), ("peer_routed_off", C.c_int64), ("out_row_stride", C.c_int64),
                 ("num_tokens", C.c_int32), ("num_topk", C.c_int32), ("world", C.c_int32), ("rank", C.c_int32),
                 ("hidden_size", C.c_int32), ("cap_rows", C.c_int32), ("output_scale", C.c_float),
-                ("reserved", C.c_int32)]
+                ("timeout_ms", C.c_int32), ("signal_flags", PeerArray), ("wait_flags", C.c_void_p),
+                ("epoch_dev", C.c_void_p), ("status", C.c_void_p)]
 
 
 def peer_array(ptrs) -> PeerArray:

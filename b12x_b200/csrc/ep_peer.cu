@@ -114,8 +114,38 @@ __global__ void __launch_bounds__(256) ep_combine_pull_kernel(
     const int32_t* __restrict__ group_offsets, const int32_t* __restrict__ inv_perm,
     const float* __restrict__ topk_weights, PeerPtrs arenas, int64_t peer_inv_perm_off,
     int64_t peer_routed_off, __nv_bfloat16* __restrict__ out, int64_t out_row_stride, int world,
-    int rank, int num_topk, int K, int cap, float output_scale) {
+    int rank, int num_topk, int K, int cap, float output_scale, PeerPtrs signal_flags,
+    const int32_t* __restrict__ wait_flags, const int32_t* epoch_dev, int32_t* __restrict__ status,
+    unsigned long long limit_ns) {
   extern __shared__ unsigned char sm_raw[];
+  // Optional hand-shake folded into this kernel (saves two launches per step): block (0,0) tells
+  // every peer that this rank's FC2 rows are complete (the FC2 kernel ended before this one
+  // began), then every block waits until all peers have said the same.  The wait is bounded.
+  if (wait_flags != nullptr) {
+    const int epoch = *epoch_dev;
+    if (threadIdx.x < world) {
+      if (blockIdx.x == 0 && blockIdx.y == 0) {
+        __threadfence_system();
+        st_release_sys(static_cast<int32_t*>(signal_flags.p[threadIdx.x]) + rank, epoch);
+      }
+      unsigned long long t0 = 0;
+      uint32_t spins = 0;
+      while (ld_acquire_sys(wait_flags + threadIdx.x) < epoch) {
+        if ((++spins & 0x3ffu) == 0) {
+          const unsigned long long now = global_timer_ns();
+          if (t0 == 0) t0 = now;
+          if (now - t0 > limit_ns) {
+            if (status != nullptr) {
+              atomicCAS(status, 0, 1);
+              atomicCAS(status + 1, 0, 16 + static_cast<int>(threadIdx.x));
+            }
+            break;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
   const float** rowp = reinterpret_cast<const float**>(sm_raw);
   float* w = reinterpret_cast<float*>(sm_raw + num_topk * sizeof(float*));
   const int t = blockIdx.x;
@@ -241,8 +271,15 @@ extern "C" int b200moe_ep_combine(const b200moe_ep_combine_args* a, void* stream
   if ((reinterpret_cast<uintptr_t>(a->out) & 7) != 0 || (a->out_row_stride % 4) != 0) return B200MOE_EALIGN;
   if (a->num_tokens * a->num_topk > a->layout->rows) return B200MOE_ECAPACITY;
   if (a->num_tokens == 0) return B200MOE_OK;
-  PeerPtrs arenas;
+  PeerPtrs arenas, sig = {};
   if (!fill_peers(arenas, a->peer_scratch, a->world)) return B200MOE_EINVAL;
+  if (a->wait_flags != nullptr) {
+    if (a->epoch_dev == nullptr || a->timeout_ms < 0 || a->timeout_ms > 10000 ||
+        !fill_peers(sig, a->signal_flags, a->world))
+      return B200MOE_EINVAL;
+  }
+  const unsigned long long limit_ns =
+      a->timeout_ms > 0 ? static_cast<unsigned long long>(a->timeout_ms) * 1000000ull : kWaitLimitNs;
   const b200moe_scratch_layout& L = *a->layout;
   char* base = static_cast<char*>(a->scratch);
   int ysplit = (2 * 148 + a->num_tokens - 1) / a->num_tokens;
@@ -253,6 +290,7 @@ extern "C" int b200moe_ep_combine(const b200moe_ep_combine_args* a, void* stream
       reinterpret_cast<const int32_t*>(base + L.expert_offsets),
       reinterpret_cast<const int32_t*>(base + L.inv_perm), a->topk_weights, arenas,
       a->peer_inv_perm_off, a->peer_routed_off, static_cast<__nv_bfloat16*>(a->out), a->out_row_stride,
-      a->world, a->rank, a->num_topk, a->hidden_size, a->cap_rows, a->output_scale);
+      a->world, a->rank, a->num_topk, a->hidden_size, a->cap_rows, a->output_scale, sig, a->wait_flags,
+      a->epoch_dev, a->status, limit_ns);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }

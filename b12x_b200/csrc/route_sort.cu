@@ -142,8 +142,34 @@ __global__ void __launch_bounds__(kSortThreads) expert_sort_kernel(
     int32_t* __restrict__ tile_base, int32_t* __restrict__ mtile_expert,
     int32_t* __restrict__ mtile_row0, int32_t* __restrict__ mtile_rows,
     int32_t* __restrict__ sorted_route_ids, int32_t* __restrict__ inv_perm, int mtile_cap,
-    int tile_rows) {
+    int tile_rows, const int32_t* wait_flags, const int32_t* wait_epoch_dev, int32_t* wait_status,
+    int wait_world, unsigned long long wait_limit_ns) {
   extern __shared__ int32_t smem[];
+  if (wait_flags != nullptr) {
+    // the ids come from peers: wait (bounded) until every peer has flagged this step
+    const int epoch = *wait_epoch_dev;
+    if (static_cast<int>(threadIdx.x) < wait_world) {
+      unsigned long long t0 = 0;
+      uint32_t spins = 0;
+      int v;
+      while (true) {
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(wait_flags + threadIdx.x) : "memory");
+        if (v >= epoch) break;
+        if ((++spins & 0x3ffu) == 0) {
+          const unsigned long long now = global_timer_ns();
+          if (t0 == 0) t0 = now;
+          if (now - t0 > wait_limit_ns) {
+            if (wait_status != nullptr) {
+              atomicCAS(wait_status, 0, 1);
+              atomicCAS(wait_status + 1, 0, 16 + static_cast<int>(threadIdx.x));
+            }
+            break;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
   const int nwarps = blockDim.x >> 5;
   int32_t* wcount = smem;                 // [nwarps][E]
   int32_t* etotal = smem + nwarps * E;    // [E]
@@ -276,6 +302,10 @@ extern "C" int b200moe_expert_sort(const b200moe_sort_args* a, void* stream) {
   const int rows = a->num_tokens * a->num_topk;
   const int E = a->num_experts;
   if (E <= 0 || E > 1024 || rows < 0) return B200MOE_EINVAL;
+  if (a->wait_flags != nullptr && (a->wait_epoch_dev == nullptr || a->wait_world < 1 ||
+                                   a->wait_world > B200MOE_MAX_RANKS || a->wait_timeout_ms < 0 ||
+                                   a->wait_timeout_ms > 10000))
+    return B200MOE_EINVAL;
   if (rows > L.rows) return B200MOE_ECAPACITY;
   char* base = static_cast<char*>(a->scratch);
   // fewer warps for small problems keeps the shared-memory clear short
@@ -297,7 +327,8 @@ extern "C" int b200moe_expert_sort(const b200moe_sort_args* a, void* stream) {
       reinterpret_cast<int32_t*>(base + L.mtile_rows),
       reinterpret_cast<int32_t*>(base + L.sorted_route_ids),
       reinterpret_cast<int32_t*>(base + L.inv_perm), L.mtile_cap,
-      L.tile_rows == 64 ? 64 : 128);
+      L.tile_rows == 64 ? 64 : 128, a->wait_flags, a->wait_epoch_dev, a->wait_status, a->wait_world,
+      a->wait_timeout_ms > 0 ? static_cast<unsigned long long>(a->wait_timeout_ms) * 1000000ull : kWaitLimitNs);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 
@@ -374,6 +405,6 @@ extern "C" int b200moe_expert_sort_static(const int32_t* topk_ids, const int32_t
       topk_ids, expert_map, expert_map_len, rows, num_experts, w + kStaticOffStatus,
       w + kStaticOffCounts, expert_offsets, w + kStaticOffTileBase, w + kStaticOffMtileExpert,
       w + kStaticOffMtileRow0, w + kStaticOffMtileRows, sorted_route_ids, inv_perm,
-      kStaticSortMtileCap, 128);
+      kStaticSortMtileCap, 128, nullptr, nullptr, nullptr, 0, 0ull);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }

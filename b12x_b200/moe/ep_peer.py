@@ -4,8 +4,10 @@ NVLink peer memory (no NCCL call and no host synchronisation on the step).
 Per step, all on one CUDA stream per rank::
 
     route -> sort by destination rank -> ep_dispatch (peer stores + flags)
-          -> ep_wait -> expert sort / quantise / FC1 / FC2 on the received slots
-          -> ep_signal -> ep_wait -> ep_combine (peer loads of the fp32 FC2 rows + weighted sum)
+          -> expert sort (first waits, bounded, for every peer's flag) / quantise / FC1 / FC2 on
+             the received slots
+          -> ep_combine (signal "FC2 done", bounded wait for all peers, then peer loads of the
+             fp32 FC2 rows + weighted sum, one launch)
 
 Receive buffers, flags and the expert-side scratch arena live in symmetric memory
 (``torch.distributed._symmetric_memory``); every rank therefore holds device pointers to all
@@ -44,7 +46,7 @@ def _symm_empty(shape, dtype, device):
 
 
 class PeerExpertParallelMoE(_LayerBase):
-    kernels_per_step = 12
+    kernels_per_step = 9
 
     def __init__(self, shp, inputs, experts, dev, rank: int, world: int):
         super().__init__(shp, inputs, experts, dev, rank, world)
@@ -112,29 +114,35 @@ class PeerExpertParallelMoE(_LayerBase):
         lib = ext.load()
         shp, home, world, rank = self.shape, self.home, self.world, self.rank
         stream = torch.cuda.current_stream(self.dev).cuda_stream
+        mark = stage_timer if stage_timer is not None else (lambda _name: None)
+        mark("begin")
         self.route(logits)
+        mark("route")
         home.sort(self.topk_ids, self.rank_of_expert)
+        mark("home_sort")
         d = ext.EpDispatchArgs(
             x.data_ptr(), self.topk_ids.data_ptr(), ext.peer_array(self.rows_ptrs),
             ext.peer_array(self.ids_ptrs), ext.peer_array(self.flag1_ptrs), self.done_counter.data_ptr(),
             self.epoch_dev.data_ptr(), home.scratch.data_ptr(), C.pointer(home.layout), x.stride(0), x.shape[0], shp.topk, world, rank,
             shp.hidden, self.e_local, self.cap, 0)
         ext.check(lib.b200moe_ep_dispatch(C.byref(d), stream), "ep_dispatch")
-        b = fused_moe.bind(self.plan, scratch=self.scratch, a=self.recv_rows, experts=self.experts,
-                           topk_weights=self.ones, topk_ids=self.recv_ids, skip_combine=True)
-        self.last_binding = b
+        mark("dispatch")
         ep = self.epoch_dev.data_ptr()
-        ext.check(lib.b200moe_ep_wait(self.flags.data_ptr(), world, 0, ep, self.home_status.data_ptr(), 0, stream),
-                  "ep_wait")
-        fused_moe.run(binding=b, stage_timer=stage_timer)
-        ext.check(lib.b200moe_ep_signal(self._flag2_arr, world, rank, 0, ep, stream), "ep_signal")
-        ext.check(lib.b200moe_ep_wait(self.flags.data_ptr() + 4 * ext.MAX_RANKS, world, 0, ep,
-                                      self.home_status.data_ptr(), 0, stream), "ep_wait")
+        # the expert-side sort waits for all peers' dispatch flags before it reads the received ids
+        b = fused_moe.bind(self.plan, scratch=self.scratch, a=self.recv_rows, experts=self.experts,
+                           topk_weights=self.ones, topk_ids=self.recv_ids, skip_combine=True,
+                           sort_wait=(self.flags.data_ptr(), world, ep, self.home_status.data_ptr()))
+        self.last_binding = b
+        fused_moe.run(binding=b, stage_timer=(lambda n: None if n == "begin" else mark(n)) if stage_timer else None)
+        # "my FC2 rows are complete" + "wait for everybody's" are folded into the combine launch
         c = ext.EpCombineArgs(
             self.topk_weights.data_ptr(), self.out.data_ptr(), ext.peer_array(self.scratch_ptrs),
             home.scratch.data_ptr(), C.pointer(home.layout), self._inv_perm_off, self._routed_off,
-            self.out.stride(0), x.shape[0], shp.topk, world, rank, shp.hidden, self.cap, 1.0, 0)
+            self.out.stride(0), x.shape[0], shp.topk, world, rank, shp.hidden, self.cap, 1.0, 0,
+            ext.peer_array(self.flag2_ptrs), self.flags.data_ptr() + 4 * ext.MAX_RANKS, ep,
+            self.home_status.data_ptr())
         ext.check(lib.b200moe_ep_combine(C.byref(c), stream), "ep_combine")
+        mark("combine")
         return self.out
 
     def capture(self) -> torch.cuda.CUDAGraph:

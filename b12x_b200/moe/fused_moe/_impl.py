@@ -439,6 +439,7 @@ class TPMoEScratchPlan:
         output_scale: float = 1.0,
         f32_only: bool = False,
         skip_combine: bool = False,
+        sort_wait: tuple | None = None,
     ) -> "TPMoEFP4Binding":
         """Validate the call and map the caller's scratch into kernel-argument views.
 
@@ -490,7 +491,7 @@ class TPMoEScratchPlan:
             swiglu_beta=caps.swiglu_beta, route_expert_map=route_expert_map,
             kernel_workspace=core, core_layout=self._core_layout, fc1_tap=fc1_tap,
             output_f32=output_f32, output_scale=float(output_scale), f32_only=bool(f32_only),
-            skip_combine=bool(skip_combine))
+            skip_combine=bool(skip_combine), sort_wait=sort_wait)
 
 
 def plan_tp_moe_scratch(caps: TPMoEScratchCaps) -> TPMoEScratchPlan:
@@ -548,6 +549,9 @@ class TPMoEFP4Binding:
     output_scale: float = 1.0
     f32_only: bool = False     # write only ``output_f32`` (un-rounded sums), skip the bf16 output
     skip_combine: bool = False  # stop after FC2: the per-route rows stay in ``route_output``
+    # (flags ptr, world, epoch ptr, status ptr): the sort first waits for the peers' flags (the
+    # expert side of the peer-memory expert parallelism, whose ids are stored by other ranks)
+    sort_wait: tuple | None = None
 
     # ---- scratch views (valid after run) ----
     def _v(self, name: str, count: int, dtype: torch.dtype) -> torch.Tensor:
@@ -656,8 +660,10 @@ def b12x_moe_fp4(*, binding: TPMoEFP4Binding, stage_timer=None) -> torch.Tensor:
     mark = stage_timer if stage_timer is not None else (lambda _name: None)
     mark("begin")
     emap = b.route_expert_map
+    sw = b.sort_wait or (None, 0, None, None)
     sort_args = ext.SortArgs(b.topk_ids.data_ptr(), _ptr(emap), scratch, lp, tokens, b.num_topk,
-                             b.weight_E, 0 if emap is None else int(emap.numel()))
+                             b.weight_E, 0 if emap is None else int(emap.numel()),
+                             sw[0], sw[2], sw[3], int(sw[1]), 0)
     ext.check(lib.b200moe_expert_sort(C.byref(sort_args), stream), "expert_sort")
     mark("sort")
 

@@ -129,6 +129,13 @@ typedef struct {
   void* scratch;             /* arena base                                      */
   const b200moe_scratch_layout* layout; /* HOST pointer                        */
   int32_t num_tokens, num_topk, num_experts, expert_map_len;
+  /* Optional (expert parallelism over peer memory): before reading topk_ids, wait (bounded) until
+   * wait_flags[r] >= *wait_epoch_dev for every r < wait_world -- the ids were stored by peers.
+   * On expiry wait_status[0] = 1, wait_status[1] = 16 + r, and the sort goes on. */
+  const int32_t* wait_flags; /* or NULL                                         */
+  const int32_t* wait_epoch_dev;
+  int32_t* wait_status;
+  int32_t wait_world, wait_timeout_ms;
 } b200moe_sort_args;
 int b200moe_expert_sort(const b200moe_sort_args* a, void* stream);
 
@@ -287,7 +294,14 @@ typedef struct {
   int32_t num_tokens, num_topk, world, rank;
   int32_t hidden_size, cap_rows;
   float output_scale;
-  int32_t reserved;
+  int32_t timeout_ms;        /* of the folded wait, 0 = default                 */
+  /* Optional: fold "signal + wait" into this launch.  With wait_flags set, the kernel first raises
+   * signal_flags[d][rank] = *epoch_dev on every rank d (this rank's FC2 rows are complete), then
+   * waits (bounded, status as for b200moe_ep_wait) until wait_flags[r] >= *epoch_dev for all r. */
+  void* signal_flags[B200MOE_MAX_RANKS];
+  const int32_t* wait_flags; /* this rank's flags, or NULL for no hand-shake    */
+  const int32_t* epoch_dev;
+  int32_t* status;
 } b200moe_ep_combine_args;
 /* out[t] = sum over slots of w[t,slot] * (FC2 row of that route, read from the rank that computed
  * it), fp32, slot order, one bf16 rounding: the return all-to-all and the combine in one kernel. */
