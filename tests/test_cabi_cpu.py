@@ -72,6 +72,21 @@ def test_host_side_argument_errors_need_no_gpu(lib):
     a.logits = a.topk_ids = a.topk_weights = 16
     a.num_experts, a.num_topk, a.num_tokens = 2000, 2, 1
     assert lib.b200moe_route_topk(C.byref(a), None) == ext.EINVAL   # > 1024 experts
+    # the sort's optional wait needs its epoch pointer and a sane rank count
+    L = ext.scratch_layout(8, 2, 4, 256, 128, "nvfp4", "silu")
+    s = ext.SortArgs(16, None, 16, C.pointer(L), 8, 2, 4, 0, 16, None, None, 2, 0)
+    assert lib.b200moe_expert_sort(C.byref(s), None) == ext.EINVAL
+    s = ext.SortArgs(16, None, 16, C.pointer(L), 8, 2, 4, 0, 16, 16, None, 64, 0)
+    assert lib.b200moe_expert_sort(C.byref(s), None) == ext.EINVAL
+    # standalone quantisers and the peer-memory entry points validate before they launch
+    assert lib.b200moe_quantize_rows_nvfp4(None, 0, 1, 16, None, None, None, None) == ext.EINVAL
+    assert lib.b200moe_quantize_rows_nvfp4(16, 8, 4, 24, 16, 16, 16, None) == ext.EINVAL      # K % 16
+    assert lib.b200moe_quantize_rows_mxfp8(16, 8, 4, 48, 16, None, None, None) == ext.EINVAL  # K % 32
+    assert lib.b200moe_quantize_rows_mxfp8(24, 8, 4, 64, 16, None, None, None) == ext.EALIGN
+    assert lib.b200moe_ep_wait(None, 2, 1, None, None, 0, None) == ext.EINVAL
+    assert lib.b200moe_ep_wait(16, 2, 1, None, None, 20000, None) == ext.EINVAL               # timeout too long
+    assert lib.b200moe_ep_dispatch(None, None) == ext.EINVAL
+    assert lib.b200moe_ep_combine(None, None) == ext.EINVAL
 
 
 def _wplan(**kw):
