@@ -126,21 +126,31 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+      // Where this lane's copy of tile `w` comes from.  Tiles of a decode batch hold a few rows:
+      // they fetch 32 activation rows instead of 128 (the other rows of the shared-memory tile
+      // keep stale data; MMA rows are independent).  A gated tile is BN/128 pair groups: box 2g =
+      // 64 up rows, box 2g+1 = the 64 gate rows of the same columns; its scale chain g is the pair
+      // atom of those columns.  A plain tile is BN consecutive rows.
+      struct LaneSrc {
+        const CUtensorMap* tm;   // operand lanes
+        int y;                   // row coordinate
+        const uint8_t* sf;       // scale lanes: atom chain
+        uint32_t a_bytes;
+      };
+      auto locate = [&](int w) {
         const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
-        const int row0 = p.mtile_row0[c.mt];
-        // tiles of a decode batch hold a few rows: fetch 32 activation rows instead of 128 (the
-        // other rows of the shared-memory tile keep stale data; MMA rows are independent)
+        LaneSrc r;
         const bool small_a = p.mtile_rows[c.mt] <= 32;
-        const CUtensorMap* tma_a = small_a ? &tmA_small : &tmA;
-        const uint32_t a_bytes = (small_a ? 32u : 128u) * kRowBytes;
-        // weight rows of this lane's box / scale chain of this lane.  A gated tile is BN/128 pair
-        // groups: box 2g = 64 up rows, box 2g+1 = the 64 gate rows of the same columns; its scale
-        // chain g is the pair atom of those columns.  A plain tile is BN consecutive rows.
-        int my_row = 0;
-        const uint8_t* my_sf = p.sfa + static_cast<size_t>(c.mt) * p.atoms_k * 512;
-        if (lane >= 1 && lane <= kBoxes) {
+        r.a_bytes = (small_a ? 32u : 128u) * kRowBytes;
+        r.tm = &tmB;
+        r.y = 0;
+        r.sf = p.sfa + static_cast<size_t>(c.mt) * p.atoms_k * 512;
+        if (lane == 0) {
+          r.tm = small_a ? &tmA_small : &tmA;
+          r.y = p.mtile_row0[c.mt];
+        } else if (lane <= kBoxes) {
           const int b = lane - 1;
+          int my_row;
           if (kGated) {
             int g = b >> 1;
             if (c.nt * p.n_step + g * 64 >= p.out_cols) g = 0;       // half-empty last tile
@@ -149,17 +159,50 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
             my_row = c.nt * p.n_step + b * 64;
             if (my_row >= p.w_rows) my_row = c.nt * p.n_step;
           }
+          r.y = c.e * p.w_rows + my_row;
         } else if (lane > kBoxes + 1) {
           int rg = c.nt * Cfg::kSfbChains + (lane - kBoxes - 2);
           if (rg >= p.sfb_rowgroups) rg = c.nt * Cfg::kSfbChains;
-          my_sf = p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + rg) * p.atoms_k * 512;
+          r.sf = p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + rg) * p.atoms_k * 512;
         }
+        return r;
+      };
+      // A second cursor runs p.prefetch k-blocks ahead (across tile boundaries) and asks L2 for
+      // the same copies: with large batches the pipeline is bound by the round trip of a stage,
+      // and the part of a stage that misses L2 sets that round trip.
+      int pf_w = blockIdx.x, pf_kb = 0;
+      LaneSrc pf = {};
+      if (p.prefetch > 0 && pf_w < total_work) pf = locate(pf_w);
+      auto pf_step = [&]() {
+        if (p.prefetch <= 0 || pf_w >= total_work) return;
+        if (lane <= kBoxes) {
+          tma_prefetch_2d(pf.tm, pf_kb * kRowBytes, pf.y);
+        } else {
+          const int ks = min(4, (p.kdim - pf_kb * kPerStage) / kPerMma);
+          bulk_prefetch(pf.sf + static_cast<size_t>(pf_kb) * (KIND == KIND_MX ? 512 : 2048),
+                        KIND == KIND_MX ? 512u : static_cast<uint32_t>(ks) * 512u);
+        }
+        if (++pf_kb == p.k_blocks) {
+          pf_kb = 0;
+          pf_w += gridDim.x;
+          if (pf_w < total_work) pf = locate(pf_w);
+        }
+      };
+      for (int i = 0; i < p.prefetch; ++i) pf_step();
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        const LaneSrc src = locate(w);
+        const CUtensorMap* tma_a = src.tm;
+        const uint32_t a_bytes = src.a_bytes;
+        const int row0 = src.y;
+        const int my_row_y = src.y;
+        const uint8_t* my_sf = src.sf;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status,
                                  WAIT_SMEM_EMPTY)) {
             ok = false;
             break;
           }
+          pf_step();
           const int ksteps = min(4, (p.kdim - kb * kPerStage) / kPerMma);
           // NVFP4: one scale atom per MMA step; MX: one atom covers the whole stage
           const uint32_t sf_bytes = KIND == KIND_MX ? 512u : static_cast<uint32_t>(ksteps) * 512u;
@@ -174,8 +217,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
             mbar_expect_tx(bar, a_bytes + b_bytes);
             tma_load_2d(sA + stage * kSmemA, tma_a, bar, kb * kRowBytes, row0);
           } else if (lane <= kBoxes) {
-            tma_load_2d(sB + stage * kSmemB + (lane - 1) * 64 * kRowBytes, &tmB, bar, kb * kRowBytes,
-                        c.e * p.w_rows + my_row);
+            tma_load_2d(sB + stage * kSmemB + (lane - 1) * 64 * kRowBytes, &tmB, bar, kb * kRowBytes, my_row_y);
           } else if (lane == kBoxes + 1) {
             mbar_expect_tx(sf_bar, (1u + Cfg::kSfbChains) * sf_bytes);
             bulk_load(sSfa + stage * kSmemSfa, my_sf + sf_off, sf_bytes, sf_bar);
@@ -414,7 +456,20 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmA_small,
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 
+// k-blocks that the wide kernel's producer asks L2 for ahead of its shared-memory pipeline when
+// the batch is large (B200MOE_PREFETCH overrides; 0 = off).
+static int prefetch_distance() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200MOE_PREFETCH");
+    v = e != nullptr ? atoi(e) : 0;
+    if (v < 0 || v > 64) v = 0;
+  }
+  return v;
+}
+
 void fill_common(GemmParams& p, const b200moe_gemm_args* a, char* base) {
+  p.prefetch = prefetch_distance();
   const b200moe_scratch_layout& L = *a->layout;
   p.tile_base = reinterpret_cast<const int32_t*>(base + L.tile_base);
   p.mtile_expert = reinterpret_cast<const int32_t*>(base + L.mtile_expert);

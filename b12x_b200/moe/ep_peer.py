@@ -20,6 +20,7 @@ layer (fp32 per-route rows, combined in slot order).
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import replace
 
 import torch
@@ -46,7 +47,7 @@ def _symm_empty(shape, dtype, device):
 
 
 class PeerExpertParallelMoE(_LayerBase):
-    kernels_per_step = 9
+    kernels_per_step = 12
 
     def __init__(self, shp, inputs, experts, dev, rank: int, world: int):
         super().__init__(shp, inputs, experts, dev, rank, world)
@@ -60,6 +61,10 @@ class PeerExpertParallelMoE(_LayerBase):
         slots = world * self.cap
         self.home = StageArena(t, k, world, shp.hidden, dev)
         self.rank_of_expert = (torch.arange(shp.experts, dtype=torch.int32, device=dev) // self.e_local).contiguous()
+        # the two cross-rank waits of a step either ride inside the expert sort and the combine
+        # kernel (9 launches per step) or are launches of their own (12)
+        self.fold_waits = os.environ.get("B200MOE_FOLD_WAITS", "0") == "1"
+        self.kernels_per_step = 9 if self.fold_waits else 12
         self.done_counter = torch.zeros(1, dtype=torch.int32, device=dev)
         # the step counter lives on the device, so that a captured step can be replayed
         self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -128,18 +133,29 @@ class PeerExpertParallelMoE(_LayerBase):
         ext.check(lib.b200moe_ep_dispatch(C.byref(d), stream), "ep_dispatch")
         mark("dispatch")
         ep = self.epoch_dev.data_ptr()
-        # the expert-side sort waits for all peers' dispatch flags before it reads the received ids
+        fold = self.fold_waits
+        # folded: the expert-side sort waits for all peers' dispatch flags before it reads the ids
         b = fused_moe.bind(self.plan, scratch=self.scratch, a=self.recv_rows, experts=self.experts,
                            topk_weights=self.ones, topk_ids=self.recv_ids, skip_combine=True,
-                           sort_wait=(self.flags.data_ptr(), world, ep, self.home_status.data_ptr()))
+                           sort_wait=(self.flags.data_ptr(), world, ep, self.home_status.data_ptr()) if fold else None)
         self.last_binding = b
+        if not fold:
+            ext.check(lib.b200moe_ep_wait(self.flags.data_ptr(), world, 0, ep, self.home_status.data_ptr(), 0,
+                                          stream), "ep_wait")
+            mark("wait_tokens")
         fused_moe.run(binding=b, stage_timer=(lambda n: None if n == "begin" else mark(n)) if stage_timer else None)
-        # "my FC2 rows are complete" + "wait for everybody's" are folded into the combine launch
+        # "my FC2 rows are complete" + "wait for everybody's": folded into the combine launch, or
+        # two launches of their own
+        flags2 = self.flags.data_ptr() + 4 * ext.MAX_RANKS
+        if not fold:
+            ext.check(lib.b200moe_ep_signal(self._flag2_arr, world, rank, 0, ep, stream), "ep_signal")
+            ext.check(lib.b200moe_ep_wait(flags2, world, 0, ep, self.home_status.data_ptr(), 0, stream), "ep_wait")
+            mark("wait_results")
         c = ext.EpCombineArgs(
             self.topk_weights.data_ptr(), self.out.data_ptr(), ext.peer_array(self.scratch_ptrs),
             home.scratch.data_ptr(), C.pointer(home.layout), self._inv_perm_off, self._routed_off,
             self.out.stride(0), x.shape[0], shp.topk, world, rank, shp.hidden, self.cap, 1.0, 0,
-            ext.peer_array(self.flag2_ptrs), self.flags.data_ptr() + 4 * ext.MAX_RANKS, ep,
+            ext.peer_array(self.flag2_ptrs), flags2 if fold else None, ep if fold else None,
             self.home_status.data_ptr())
         ext.check(lib.b200moe_ep_combine(C.byref(c), stream), "ep_combine")
         mark("combine")
