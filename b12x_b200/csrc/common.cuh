@@ -130,17 +130,6 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
       : "memory");
 }
 
-// The same two kinds of copy as prefetches into L2 only (no shared memory, no barrier).
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* m, int32_t x, int32_t y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
-               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_prefetch(const void* gsrc, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes)
-               : "memory");
-}
-
 // ---- tcgen05 / TMEM ---------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(

@@ -46,8 +46,9 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
   if (threadIdx.x <= world) offs[threadIdx.x] = group_offsets[threadIdx.x];
   __syncthreads();
   const int total = offs[world];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int pos = blockIdx.x * 8 + warp; pos < total; pos += gridDim.x * 8) {
+  // one row per block at a time: all 256 threads copy it, so a row is a handful of independent
+  // 16-byte loads and (peer) stores per thread instead of a 28-step walk by one warp
+  for (int pos = blockIdx.x; pos < total; pos += gridDim.x) {
     int d = 0;
     while (d + 1 < world && pos >= offs[d + 1]) ++d;
     const int slot = rank * cap + (pos - offs[d]);
@@ -56,8 +57,8 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(t) * x_row_stride);
     uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(rows.p[d]) +
                                           static_cast<size_t>(slot) * K);
-    for (int j = lane; j < (K >> 3); j += 32) dst[j] = __ldg(src + j);
-    if (lane == 0) static_cast<int32_t*>(ids.p[d])[slot] = topk_ids[r] % local_modulus;
+    for (int j = threadIdx.x; j < (K >> 3); j += blockDim.x) dst[j] = __ldg(src + j);
+    if (threadIdx.x == 0) static_cast<int32_t*>(ids.p[d])[slot] = topk_ids[r] % local_modulus;
   }
   // unused slots of this rank's region on every peer: no route
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < world * cap; i += gridDim.x * blockDim.x) {
@@ -229,8 +230,8 @@ extern "C" int b200moe_ep_dispatch(const b200moe_ep_dispatch_args* a, void* stre
     return B200MOE_EINVAL;
   const b200moe_scratch_layout& L = *a->layout;
   char* base = static_cast<char*>(a->scratch);
-  int grid = (rows + 7) / 8;
-  grid = grid < 1 ? 1 : (grid > 148 * 2 ? 148 * 2 : grid);
+  int grid = rows;
+  grid = grid < 1 ? 1 : (grid > 148 * 8 ? 148 * 8 : grid);
   ep_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride, a->topk_ids,
       reinterpret_cast<const int32_t*>(base + L.expert_offsets),

@@ -38,7 +38,6 @@ struct GemmParams {
   int gscale_len;
   float limit, act_alpha, act_beta;
   int swigluoai;
-  int prefetch;                  // k-blocks requested into L2 ahead of the shared-memory pipeline
 };
 
 struct TileCoord {

@@ -167,28 +167,6 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         }
         return r;
       };
-      // A second cursor runs p.prefetch k-blocks ahead (across tile boundaries) and asks L2 for
-      // the same copies: with large batches the pipeline is bound by the round trip of a stage,
-      // and the part of a stage that misses L2 sets that round trip.
-      int pf_w = blockIdx.x, pf_kb = 0;
-      LaneSrc pf = {};
-      if (p.prefetch > 0 && pf_w < total_work) pf = locate(pf_w);
-      auto pf_step = [&]() {
-        if (p.prefetch <= 0 || pf_w >= total_work) return;
-        if (lane <= kBoxes) {
-          tma_prefetch_2d(pf.tm, pf_kb * kRowBytes, pf.y);
-        } else {
-          const int ks = min(4, (p.kdim - pf_kb * kPerStage) / kPerMma);
-          bulk_prefetch(pf.sf + static_cast<size_t>(pf_kb) * (KIND == KIND_MX ? 512 : 2048),
-                        KIND == KIND_MX ? 512u : static_cast<uint32_t>(ks) * 512u);
-        }
-        if (++pf_kb == p.k_blocks) {
-          pf_kb = 0;
-          pf_w += gridDim.x;
-          if (pf_w < total_work) pf = locate(pf_w);
-        }
-      };
-      for (int i = 0; i < p.prefetch; ++i) pf_step();
       for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
         const LaneSrc src = locate(w);
         const CUtensorMap* tma_a = src.tm;
@@ -202,7 +180,6 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
             ok = false;
             break;
           }
-          pf_step();
           const int ksteps = min(4, (p.kdim - kb * kPerStage) / kPerMma);
           // NVFP4: one scale atom per MMA step; MX: one atom covers the whole stage
           const uint32_t sf_bytes = KIND == KIND_MX ? 512u : static_cast<uint32_t>(ksteps) * 512u;
@@ -456,20 +433,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmA_small,
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 
-// k-blocks that the wide kernel's producer asks L2 for ahead of its shared-memory pipeline when
-// the batch is large (B200MOE_PREFETCH overrides; 0 = off).
-static int prefetch_distance() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("B200MOE_PREFETCH");
-    v = e != nullptr ? atoi(e) : 0;
-    if (v < 0 || v > 64) v = 0;
-  }
-  return v;
-}
-
 void fill_common(GemmParams& p, const b200moe_gemm_args* a, char* base) {
-  p.prefetch = prefetch_distance();
   const b200moe_scratch_layout& L = *a->layout;
   p.tile_base = reinterpret_cast<const int32_t*>(base + L.tile_base);
   p.mtile_expert = reinterpret_cast<const int32_t*>(base + L.mtile_expert);
