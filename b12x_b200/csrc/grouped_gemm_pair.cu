@@ -63,8 +63,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
   return r;
 }
+// Arrive on a barrier of another CTA of the cluster.  Relaxed: what the arrival publishes are
+// tensor-memory reads / writes, ordered by tcgen05.fence::before_thread_sync on this side and
+// ::after_thread_sync on the waiting side; a release at cluster scope cost about a microsecond
+// per arrival here and doubled the kernel's time.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
@@ -373,9 +377,10 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmPara
 }  // namespace pair
 
 // The CTA-pair kernels serve nvfp4 plans with 128-row tiles and gated FC1 (or FC2).  They are
-// correct but, as measured, slower than the single-CTA wide kernel (the stage hand-shake crosses
-// the CTA pair twice per stage and the pipeline of five stages does not cover that latency), so
-// they only run when B200MOE_PAIR=1 asks for them.
+// correct but, as measured, not faster than the single-CTA wide kernel yet (each CTA streams 38 KB
+// per stage instead of 54 KB, but the round trip of a stage across the pair is about a
+// microsecond longer and five stages are all the shared memory holds), so they only run when
+// B200MOE_PAIR=1 asks for them.
 bool nvfp4_pair_ok(const b200moe_gemm_args* a, bool fc1) {
   static int mode = -2;
   if (mode == -2) {
