@@ -7,10 +7,11 @@
 // 16 KiB of token rows + 16 KiB of weight rows + 6 KiB of scale atoms from L2 instead of 16 + 32 + 6:
 // the wide single-CTA kernel is limited by exactly that operand stream.
 //
-// Roles per CTA (448 threads): warp 0 TMA producer (the operand copies of either CTA complete on
-// the EVEN CTA's stage barrier, the scale atoms on a barrier of the CTA itself), warps 2..9
-// epilogue of the CTA's own accumulator, warps 10..13 move the CTA's scale atoms into its tensor
-// memory (tcgen05.st) and arrive on the even CTA's scale barrier.  Even CTA only: warp 1 issues the
+// Roles per CTA (480 threads): warp 0 operand producer (the operand copies of either CTA complete
+// on the EVEN CTA's stage barrier), warp 14 scale-atom producer (a ring of eight slots of its own,
+// completing on barriers of the CTA itself), warps 2..9 epilogue of the CTA's own accumulator,
+// warps 10..13 move the CTA's scale atoms into its tensor memory (tcgen05.st) and arrive on the
+// even CTA's scale barrier.  Even CTA only: warp 1 issues the
 // MMAs and commits (multicast) to both CTAs' barriers.  The odd CTA's epilogue warps release the
 // accumulator with remote arrives on the even CTA's barrier.  Every wait is bounded; the two cluster-wide
 // barriers (after set-up, before tear-down) are reached by both CTAs unconditionally.
@@ -21,14 +22,16 @@
 namespace b200moe {
 namespace pair {
 
-constexpr int kThreads = 448;
+constexpr int kThreads = 480;
 constexpr int kStages = 5;
 constexpr int kRowBytes = 128;
 constexpr int kSmemA = 128 * kRowBytes;       // this CTA's 128 token rows, one k-block
 constexpr int kSmemB = 128 * kRowBytes;       // this CTA's half of the 256 weight rows
 constexpr int kSmemSfa = 4 * 512;             // scale atoms of the token rows
 constexpr int kSmemSfb = 2 * 4 * 512;         // scale atoms of all 256 weight rows (two chains)
-constexpr int kStageBytes = kSmemA + kSmemB + kSmemSfa + kSmemSfb;
+constexpr int kStageBytes = kSmemA + kSmemB;                  // operand rows of one stage
+constexpr int kSfSlots = 8;                   // ring of scale-atom slots, deeper than the stages
+constexpr int kSfSlotBytes = kSmemSfa + kSmemSfb;
 constexpr int kTmemCols = 512;
 constexpr int kTmemSf = 256;                  // accumulator: columns 0..255
 constexpr int kSfCols = 48;                   // per stage: 16 (tokens) + 32 (weights)
@@ -37,7 +40,8 @@ constexpr uint32_t kStageTxBytes = 2u * (kSmemA + kSmemB);   // both CTAs' opera
 struct __align__(8) SmemTail {
   uint64_t full[kStages];       // used in the even CTA: all copies of the pair have landed
   uint64_t empty[kStages];      // per CTA: the MMAs that read the stage have retired
-  uint64_t sf_landed[kStages];  // per CTA: the stage's scale atoms are in this CTA's shared memory
+  uint64_t sf_landed[kSfSlots]; // per CTA: the slot's scale atoms are in this CTA's shared memory
+  uint64_t sf_empty[kSfSlots];  // per CTA: the four scale warps have read the slot
   uint64_t sf_full[kStages];    // even CTA: both CTAs' scale atoms are in tensor memory
   uint64_t tmem_full;           // per CTA: the accumulator is complete
   uint64_t tmem_empty;          // even CTA: all 16 epilogue warps of the pair have drained it
@@ -46,7 +50,8 @@ struct __align__(8) SmemTail {
   int32_t tile_base[kMaxExperts + 1];
   int32_t pair_base[kMaxExperts + 1];
 };
-constexpr int kSmemBytes = 1024 + kStages * kStageBytes + static_cast<int>(sizeof(SmemTail));
+constexpr int kSmemBytes =
+    1024 + kStages * kStageBytes + kSfSlots * kSfSlotBytes + static_cast<int>(sizeof(SmemTail));
 
 // ---- cluster / cta_group::2 PTX -------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -138,9 +143,8 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sA = smem;
   uint8_t* sB = sA + kStages * kSmemA;
-  uint8_t* sSfa = sB + kStages * kSmemB;
-  uint8_t* sSfb = sSfa + kStages * kSmemSfa;
-  SmemTail* tail = reinterpret_cast<SmemTail*>(sSfb + kStages * kSmemSfb);
+  uint8_t* sSf = sB + kStages * kSmemB;          // [slot][token atoms 2 KiB | weight atoms 4 KiB]
+  SmemTail* tail = reinterpret_cast<SmemTail*>(sSf + kSfSlots * kSfSlotBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = static_cast<int>(cluster_ctarank());     // 0 = even CTA (issues the MMAs)
@@ -150,8 +154,11 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&tail->full[s], 1);
       mbar_init(&tail->empty[s], 1);
-      mbar_init(&tail->sf_landed[s], 1);
       mbar_init(&tail->sf_full[s], 8);
+    }
+    for (int s = 0; s < kSfSlots; ++s) {
+      mbar_init(&tail->sf_landed[s], 1);
+      mbar_init(&tail->sf_empty[s], 4);
     }
     mbar_init(&tail->tmem_full, 1);
     mbar_init(&tail->tmem_empty, 16);
@@ -182,11 +189,10 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
   const int total_work = tail->pair_base[p.E] * p.n_tiles;
 
   if (warp == 0) {
-    // ------------------------------ TMA producer (both CTAs) ---------------------
+    // ------------------------------ operand producer (both CTAs) -----------------
     // lane 0: (even CTA) arms the stage barrier; token rows.  lanes 1, 2: the two 64-row boxes
-    // of this CTA's weight half.  lane 3: token scale atoms.  lanes 4, 5: the two weight scale
-    // chains (both CTAs fetch both).
-    if (lane < 6) {
+    // of this CTA's weight half.  All operand copies complete on the EVEN CTA's barrier.
+    if (lane < 3) {
       if (lane == 0) {
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
@@ -196,12 +202,10 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       bool ok = true;
       for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
         const PairCoord c = decode_pair(w, p, tail, rank);
-        const int row0 = p.mtile_row0[c.mt_load];
-        int y = 0;                      // row coordinate of this lane's operand copy
-        const uint8_t* my_sf = nullptr; // atom chain of this lane's scale copy
+        int y;                          // row coordinate of this lane's copy
         if (lane == 0) {
-          y = row0;
-        } else if (lane <= 2) {
+          y = p.mtile_row0[c.mt_load];
+        } else {
           const int b = lane - 1;
           int wrow;
           if (kGated) {
@@ -213,33 +217,18 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
             if (wrow >= p.w_rows) wrow = c.nt * 256 + b * 64;
           }
           y = c.e * p.w_rows + wrow;
-        } else if (lane == 3) {
-          my_sf = p.sfa + static_cast<size_t>(c.mt_load) * p.atoms_k * 512;
-        } else {
-          int rg = 2 * c.nt + (lane - 4);
-          if (rg >= p.sfb_rowgroups) rg = 2 * c.nt;
-          my_sf = p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + rg) * p.atoms_k * 512;
         }
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status, WAIT_SMEM_EMPTY)) {
             ok = false;
             break;
           }
-          // operand rows complete on the EVEN CTA's barrier, scale atoms on this CTA's own
           const uint32_t bar = map_to_cta(smem_u32(&tail->full[stage]), 0);
-          const int ksteps = min(4, (p.kdim - kb * 256) / 64);
-          const uint32_t sf_bytes = static_cast<uint32_t>(ksteps) * 512u;
-          const size_t sf_off = static_cast<size_t>(kb) * 2048;
           if (lane == 0) {
             if (rank == 0) mbar_expect_tx(&tail->full[stage], kStageTxBytes);
             tma_load_2d_pair(sA + stage * kSmemA, &tmA, bar, kb * kRowBytes, y);
-          } else if (lane <= 2) {
-            tma_load_2d_pair(sB + stage * kSmemB + (lane - 1) * 64 * kRowBytes, &tmB, bar, kb * kRowBytes, y);
-          } else if (lane == 3) {
-            mbar_expect_tx(&tail->sf_landed[stage], 3u * sf_bytes);
-            bulk_load(sSfa + stage * kSmemSfa, my_sf + sf_off, sf_bytes, &tail->sf_landed[stage]);
           } else {
-            bulk_load(sSfb + stage * kSmemSfb + (lane - 4) * 2048, my_sf + sf_off, sf_bytes, &tail->sf_landed[stage]);
+            tma_load_2d_pair(sB + stage * kSmemB + (lane - 1) * 64 * kRowBytes, &tmB, bar, kb * kRowBytes, y);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -249,6 +238,51 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       }
       if (!ok) {
         for (int i = 0; i < 1000; ++i) __nanosleep(1000);   // let copies in flight land
+      }
+    }
+  } else if (warp == 14) {
+    // ------------------------------ scale-atom producer (both CTAs) --------------
+    // The scale atoms travel through a ring of their own that is deeper than the operand stages:
+    // they are in shared memory before the stage's tensor-memory columns are free again, so their
+    // load is off the round trip that bounds the pipeline.  lane 0: token atoms, lanes 1, 2: the
+    // two weight chains (both CTAs fetch both); they complete on this CTA's own barrier.
+    if (lane < 3) {
+      int slot = 0;
+      uint32_t sphase = 0;
+      bool ok = true;
+      for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+        const PairCoord c = decode_pair(w, p, tail, rank);
+        const uint8_t* my_sf;
+        if (lane == 0) {
+          my_sf = p.sfa + static_cast<size_t>(c.mt_load) * p.atoms_k * 512;
+        } else {
+          int rg = 2 * c.nt + (lane - 1);
+          if (rg >= p.sfb_rowgroups) rg = 2 * c.nt;
+          my_sf = p.sfb + (static_cast<size_t>(c.e) * p.sfb_rowgroups + rg) * p.atoms_k * 512;
+        }
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&tail->sf_empty[slot], sphase ^ 1, abort_flag, p.status, WAIT_SMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const int ksteps = min(4, (p.kdim - kb * 256) / 64);
+          const uint32_t sf_bytes = static_cast<uint32_t>(ksteps) * 512u;
+          const size_t sf_off = static_cast<size_t>(kb) * 2048;
+          uint8_t* dst = sSf + slot * kSfSlotBytes;
+          if (lane == 0) {
+            mbar_expect_tx(&tail->sf_landed[slot], 3u * sf_bytes);
+            bulk_load(dst, my_sf + sf_off, sf_bytes, &tail->sf_landed[slot]);
+          } else {
+            bulk_load(dst + kSmemSfa + (lane - 1) * 2048, my_sf + sf_off, sf_bytes, &tail->sf_landed[slot]);
+          }
+          if (++slot == kSfSlots) {
+            slot = 0;
+            sphase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
       }
     }
   } else if (warp == 1) {
@@ -291,31 +325,43 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
     }
   } else if (warp >= 10) {
     // ------------------------------ scale atoms -> TMEM (both CTAs) ---------------
-    // Four warps, one per TMEM sub-partition, move every landed stage's scale atoms from this
-    // CTA's shared memory into this CTA's tensor memory (tcgen05.st) and arrive on the even
+    // Four warps, one per TMEM sub-partition.  Per k-block: the slot's atoms have landed and the
+    // stage's tensor-memory columns are free again (the MMAs of the stage's previous use have
+    // retired: the same barrier the operand producer waits on); then shared memory -> registers
+    // -> tensor memory (tcgen05.st), the slot is handed back, and the warp arrives on the even
     // CTA's scale barrier (8 arrivals: 4 warps of each CTA).
     const int sub = warp & 3;
-    int stage = 0;
-    uint32_t phase = 0;
+    int stage = 0, slot = 0;
+    uint32_t phase = 0, sphase = 0;
     bool ok = true;
     for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        if (!mbar_wait_bounded(&tail->sf_landed[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL)) {
+        if (!mbar_wait_bounded(&tail->sf_landed[slot], sphase, abort_flag, p.status, WAIT_SMEM_FULL) ||
+            !mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status, WAIT_SMEM_EMPTY)) {
           ok = false;
           break;
         }
+        tc_fence_after();
         const uint32_t sfa_t = tmem_base + kTmemSf + stage * kSfCols + (static_cast<uint32_t>(sub * 32) << 16);
         const uint32_t sfb_t = sfa_t + 16;
-        sf_atoms_to_tmem<4>(sfa_t, sSfa + stage * kSmemSfa, lane, 4);
-        sf_atoms_to_tmem<4>(sfb_t, sSfb + stage * kSmemSfb, lane, 8);
-        sf_atoms_to_tmem<4>(sfb_t + 4, sSfb + stage * kSmemSfb + 2048, lane, 8);
+        const uint8_t* src = sSf + slot * kSfSlotBytes;
+        sf_atoms_to_tmem<4>(sfa_t, src, lane, 4);
+        sf_atoms_to_tmem<4>(sfb_t, src + kSmemSfa, lane, 8);
+        sf_atoms_to_tmem<4>(sfb_t + 4, src + kSmemSfa + 2048, lane, 8);
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tail->sf_full[stage]), 0));
+        if (lane == 0) {
+          mbar_arrive(&tail->sf_empty[slot]);
+          mbar_arrive_cluster(map_to_cta(smem_u32(&tail->sf_full[stage]), 0));
+        }
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1;
+        }
+        if (++slot == kSfSlots) {
+          slot = 0;
+          sphase ^= 1;
         }
       }
     }
