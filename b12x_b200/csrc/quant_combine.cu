@@ -427,7 +427,7 @@ extern "C" int b200moe_permute_quant_nvfp4(const b200moe_quant_args* a, void* st
   // Small batches: the eight warps of a CTA share a row and a tile's rows are spread over enough
   // CTAs to fill the GPU about four times.  Large batches: one warp per row, four CTAs per tile.
   const int gx = mtiles < L.mtile_cap ? mtiles : L.mtile_cap;
-  const bool large = rows >= 2048;
+  const bool large = rows >= 2048 && L.tile_rows != 64;   // a 64-row plan expects few rows per expert
   int gy = large ? 4 : (4 * 148 + gx - 1) / gx;
   gy = gy < 1 ? 1 : (gy > 16 ? 16 : gy);
   const int wpr_cap = large ? 1 : 8;
@@ -455,7 +455,7 @@ extern "C" int b200moe_permute_quant_mxfp8(const b200moe_quant_args* a, void* st
   // Small batches: the eight warps of a CTA share a row and a tile's rows are spread over enough
   // CTAs to fill the GPU about four times.  Large batches: one warp per row, four CTAs per tile.
   const int gx = mtiles < L.mtile_cap ? mtiles : L.mtile_cap;
-  const bool large = rows >= 2048;
+  const bool large = rows >= 2048 && L.tile_rows != 64;   // a 64-row plan expects few rows per expert
   int gy = large ? 4 : (4 * 148 + gx - 1) / gx;
   gy = gy < 1 ? 1 : (gy > 16 ? 16 : gy);
   const int wpr_cap = large ? 1 : 8;
