@@ -82,7 +82,7 @@ class GemmArgs(C.Structure):
                 ("recipe", C.c_int32), ("activation", C.c_int32), ("gate_first", C.c_int32),
                 ("gscale_len", C.c_int32), ("swiglu_limit", C.c_float),
                 ("swiglu_alpha", C.c_float), ("swiglu_beta", C.c_float),
-                ("num_sms", C.c_int32), ("reserved", C.c_int32)]
+                ("num_sms", C.c_int32), ("sf_e8m0", C.c_int32)]
 
 
 class CombineArgs(C.Structure):

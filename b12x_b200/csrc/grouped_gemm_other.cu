@@ -58,6 +58,7 @@ struct Params {
   int sub0_base, sub1_base, n_step, out_cols;
   float limit, act_alpha, act_beta;
   int swigluoai;
+  int sf_e8m0;                   // scale bytes are E8M0 (2^(b-127)) instead of E4M3
 };
 
 struct TileCoord {
@@ -280,7 +281,10 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
         uint8_t* brow = sB + stage * kSmemB + t * 128;
 #pragma unroll
         for (int blk = 0; blk < 4; ++blk) {                 // 16 values per scale
-          const __nv_bfloat16 s = __float2bfloat16_rn(e4m3_to_f32((sfw >> (8 * blk)) & 0xffu));
+          const uint32_t sb = (sfw >> (8 * blk)) & 0xffu;
+          // E8M0: 2^(b-127) is the f32 with exponent field b (b = 0: the subnormal 2^-127)
+          const float sv = p.sf_e8m0 ? __uint_as_float(sb != 0u ? sb << 23 : 0x00400000u) : e4m3_to_f32(sb);
+          const __nv_bfloat16 s = __float2bfloat16_rn(sv);
           const __nv_bfloat162 sc = __halves2bfloat162(s, s);
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
@@ -537,6 +541,7 @@ int w4a16_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
   Params p = {};
   fill_common(p, a, base);
   p.sf = a->w13_sf;
+  p.sf_e8m0 = a->sf_e8m0;
   p.alphas = a->w1_alphas;
   p.out_bf16 = reinterpret_cast<__nv_bfloat16*>(base + L.mid_q);
   p.tap = a->fc1_tap;
@@ -575,6 +580,7 @@ int w4a16_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
   Params p = {};
   fill_common(p, a, base);
   p.sf = a->w2_sf;
+  p.sf_e8m0 = a->sf_e8m0;
   p.alphas = a->w2_alphas;
   p.out_f32 = reinterpret_cast<float*>(base + L.routed);
   p.kdim = I;

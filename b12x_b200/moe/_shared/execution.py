@@ -19,11 +19,11 @@ GATED_ACTIVATIONS = frozenset({"silu", SWIGLUOAI})
 KNOWN_UNBUILT_ACTIVATIONS = frozenset({"situ"})
 
 QUANT_MODES = frozenset({"nvfp4", "w4a16", "w4a8_mx"})
-SOURCE_FORMATS = frozenset({"modelopt_nvfp4", "fp4_e8m0_k32"})
+SOURCE_FORMATS = frozenset({"modelopt_nvfp4", "fp4_e8m0_k32", "compressed_tensors"})
 SOURCES_BY_QUANT_MODE = {
     "nvfp4": frozenset({"modelopt_nvfp4"}),
     "w4a8_mx": frozenset({"fp4_e8m0_k32"}),
-    "w4a16": frozenset({"modelopt_nvfp4"}),
+    "w4a16": frozenset({"modelopt_nvfp4", "fp4_e8m0_k32", "compressed_tensors"}),
 }
 
 
@@ -35,6 +35,8 @@ class WeightStoragePolicy(str, Enum):
 class WeightPreparationTransform(str, Enum):
     RUNTIME_ALPHAS = "runtime_alphas"          # alphas = weight global scale / input gscale
     SWIZZLE_MX_SCALES = "swizzle_mx_scales"    # plain E8M0 grids -> 128x4 atoms for tcgen05
+    EXPAND_E8M0_K32 = "expand_e8m0_k32"        # w4a16: plain E8M0 K/32 grids -> per-16 atoms
+    INVERT_GLOBAL_SCALES = "invert_global_scales"  # compressed-tensors stores 1 / global scale
 
 
 def normalize_moe_activation(activation: str) -> str:
@@ -202,8 +204,15 @@ def plan_moe_weight_preparation(specs, *, num_experts, hidden_size, intermediate
         elif spec.quant_mode == "w4a16":
             if k % 64 != 0 or n % 64 != 0:
                 raise ValueError("w4a16 requires hidden_size and intermediate_size divisible by 64")
-    policy = (WeightStoragePolicy.TRANSFER_SOURCE
-              if WeightPreparationTransform.SWIZZLE_MX_SCALES in transforms
+            if spec.source_format == "fp4_e8m0_k32":
+                transforms.add(WeightPreparationTransform.EXPAND_E8M0_K32)
+            elif spec.source_format == "compressed_tensors":
+                transforms.add(WeightPreparationTransform.INVERT_GLOBAL_SCALES)
+    both = {WeightPreparationTransform.SWIZZLE_MX_SCALES, WeightPreparationTransform.EXPAND_E8M0_K32}
+    if both <= transforms:
+        raise ValueError("one weight plan cannot serve both w4a8_mx and w4a16: they need different "
+                         "block-scale layouts")
+    policy = (WeightStoragePolicy.TRANSFER_SOURCE if transforms & both
               else WeightStoragePolicy.KEEP_SOURCE)
     return MoEWeightPreparationPlan(specs=specs, num_experts=num_experts, hidden_size=k,
                                     intermediate_size=n, transforms=frozenset(transforms),

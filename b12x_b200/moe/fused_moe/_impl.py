@@ -202,6 +202,10 @@ def prepare_b12x_fp4_moe_weights(
     a2 = ones if a2_gscale is None else _expert_vector(a2_gscale, e, "a2_gscale").to(dev)
     g1 = ones if w1_global_scale is None else _expert_vector(w1_global_scale, e, "w1_global_scale").to(dev)
     g2 = ones if w2_global_scale is None else _expert_vector(w2_global_scale, e, "w2_global_scale").to(dev)
+    if WeightPreparationTransform.INVERT_GLOBAL_SCALES in plan.transforms:
+        # compressed-tensors keeps the reciprocal of the ModelOpt weight global scale
+        # (w4a16/prepare.py:460-465)
+        g1, g2 = torch.reciprocal(g1), torch.reciprocal(g2)
     if "nvfp4" in plan.quant_modes:
         if a1_gscale is None or a2_gscale is None or w1_global_scale is None or w2_global_scale is None:
             raise ValueError("nvfp4 needs w*_global_scale and a*_gscale")
@@ -225,6 +229,16 @@ def prepare_b12x_fp4_moe_weights(
         # such tensors into storage with slack (one-time copy, the source may be freed)
         w1_fp4 = _with_tail_slack(w1_fp4, plan.hidden_size)
         w2_fp4 = _with_tail_slack(w2_fp4, plan.intermediate_size)
+    elif WeightPreparationTransform.EXPAND_E8M0_K32 in plan.transforms:
+        # w4a16 over an E8M0 K/32 source (w4a16/prepare.py:1289-1325): the kernel's scale stage
+        # holds one byte per 16 values, so every per-32 byte is written twice and the kernel is
+        # told to decode the bytes as E8M0
+        if tuple(s1.shape) != (e, plan.w1_rows, plan.hidden_size // 32):
+            raise ValueError("fp4_e8m0_k32 w1_blockscale must be [E, w1_rows, K/32] E8M0 bytes")
+        if tuple(s2.shape) != (e, plan.hidden_size, plan.intermediate_size // 32):
+            raise ValueError("fp4_e8m0_k32 w2_blockscale must be [E, K, I/32] E8M0 bytes")
+        s1 = _swizzle_scale_grid(s1.view(torch.uint8).repeat_interleave(2, dim=-1))
+        s2 = _swizzle_scale_grid(s2.view(torch.uint8).repeat_interleave(2, dim=-1))
     else:
         exp1 = (e, _align_up(plan.w1_rows, 128), _align_up(plan.hidden_size // 16, 4))
         exp2 = (e, _align_up(plan.hidden_size, 128), _align_up(plan.intermediate_size // 16, 4))
@@ -683,7 +697,8 @@ def b12x_moe_fp4(*, binding: TPMoEFP4Binding, stage_timer=None) -> torch.Tensor:
         int(ex.a2_gscale.numel()),
         float(b.swiglu_limit) if b.swiglu_limit is not None else 0.0,
         float(b.swiglu_alpha if b.swiglu_alpha is not None else 1.0),
-        float(b.swiglu_beta if b.swiglu_beta is not None else 0.0), 0, 0)
+        float(b.swiglu_beta if b.swiglu_beta is not None else 0.0), 0,
+        1 if (b.quant_mode == "w4a16" and ex.plan.source_format == "fp4_e8m0_k32") else 0)
     ext.check(lib.b200moe_grouped_gemm1_act(C.byref(gargs), stream), "grouped_gemm1_act")
     mark("gemm1")
     ext.check(lib.b200moe_grouped_gemm2(C.byref(gargs), stream), "grouped_gemm2")

@@ -224,7 +224,9 @@ typedef struct {
   float swiglu_limit;        /* <=0: none                                       */
   float swiglu_alpha, swiglu_beta;
   int32_t num_sms;           /* persistent grid size, 0 = all SMs               */
-  int32_t reserved;
+  int32_t sf_e8m0;           /* w4a16 only: 1 = the per-16 block-scale bytes are E8M0
+                                (an fp4_e8m0_k32 source, each per-32 scale written twice;
+                                b12x/moe/_shared/kernels/w4a16/prepare.py:1289-1325), 0 = E4M3 */
 } b200moe_gemm_args;
 int b200moe_grouped_gemm1_act(const b200moe_gemm_args* a, void* stream);
 int b200moe_grouped_gemm2(const b200moe_gemm_args* a, void* stream);
