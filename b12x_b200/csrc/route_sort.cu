@@ -127,11 +127,12 @@ __global__ void __launch_bounds__(128) route_topk_kernel(b200moe_route_args a) {
 }
 
 // ------------------------------------------------------------------------------------------
-// expert_sort: one CTA, up to 32 warps.  Warp w owns the contiguous route range
-// [w*chunk, (w+1)*chunk).  Pass 1 counts per (warp, expert) in shared memory, a scan over
-// warps then experts gives every (warp, expert) its first position, pass 2 walks the range
+// expert_sort: one CTA, up to 32 warps.  The first `count_warps` warps each own the contiguous
+// route range [w*chunk, (w+1)*chunk).  Pass 1 counts per (warp, expert) in shared memory, a scan
+// over warps then experts gives every (warp, expert) its first position, pass 2 walks the range
 // again 32 routes at a time and ranks equal experts inside the step with match_any, which
-// keeps the order of flat route ids.
+// keeps the order of flat route ids.  The block has at least 256 threads whatever the number of
+// routes, so that the per-expert tables of a small batch are not walked by a single warp.
 // ------------------------------------------------------------------------------------------
 constexpr int kSortThreads = 1024;
 
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(kSortThreads) expert_sort_kernel(
     int32_t* __restrict__ tile_base, int32_t* __restrict__ mtile_expert,
     int32_t* __restrict__ mtile_row0, int32_t* __restrict__ mtile_rows,
     int32_t* __restrict__ sorted_route_ids, int32_t* __restrict__ inv_perm, int mtile_cap,
-    int tile_rows, const int32_t* wait_flags, const int32_t* wait_epoch_dev, int32_t* wait_status,
+    int tile_rows, int count_warps, const int32_t* wait_flags, const int32_t* wait_epoch_dev, int32_t* wait_status,
     int wait_world, unsigned long long wait_limit_ns) {
   extern __shared__ int32_t smem[];
   if (wait_flags != nullptr) {
@@ -170,7 +171,7 @@ __global__ void __launch_bounds__(kSortThreads) expert_sort_kernel(
     }
     __syncthreads();
   }
-  const int nwarps = blockDim.x >> 5;
+  const int nwarps = count_warps;
   int32_t* wcount = smem;                 // [nwarps][E]
   int32_t* etotal = smem + nwarps * E;    // [E]
   int32_t* eoffs = etotal + E;            // [E+1]
@@ -184,7 +185,7 @@ __global__ void __launch_bounds__(kSortThreads) expert_sort_kernel(
 
   // routes per warp, a multiple of 32 so that steps never straddle two warps
   const int chunk = ((rows + nwarps - 1) / nwarps + 31) & ~31;
-  const int r_begin = warp * chunk;
+  const int r_begin = warp < nwarps ? warp * chunk : rows;   // the other warps own no routes
   const int r_end = min(rows, r_begin + chunk);
 
   auto local_expert = [&](int r) -> int {
@@ -211,17 +212,36 @@ __global__ void __launch_bounds__(kSortThreads) expert_sort_kernel(
     etotal[e] = run;
   }
   __syncthreads();
-  // scan over experts (E <= 1024: a single thread is enough and keeps this simple)
-  if (threadIdx.x == 0) {
-    int pos = 0, tiles = 0;
-    for (int e = 0; e < E; ++e) {
+  // scan over experts by one warp: every lane sums a contiguous span, a shuffle scan over the
+  // lanes gives each span its base
+  if (warp == 0) {
+    const int per = (E + 31) >> 5;
+    const int e0 = min(E, lane * per), e1 = min(E, e0 + per);
+    int cnt = 0, tl = 0;
+    for (int e = e0; e < e1; ++e) {
+      cnt += etotal[e];
+      tl += (etotal[e] + tile_rows - 1) >> tile_shift;
+    }
+    int pc = cnt, pt = tl;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, pc, d), b = __shfl_up_sync(0xffffffffu, pt, d);
+      if (lane >= d) {
+        pc += a;
+        pt += b;
+      }
+    }
+    int pos = pc - cnt, tiles = pt - tl;
+    for (int e = e0; e < e1; ++e) {
       eoffs[e] = pos;
       tbase[e] = tiles;
       pos += etotal[e];
       tiles += (etotal[e] + tile_rows - 1) >> tile_shift;
     }
-    eoffs[E] = pos;
-    tbase[E] = tiles;
+    if (lane == 31) {
+      eoffs[E] = pc;
+      tbase[E] = pt;
+    }
   }
   __syncthreads();
   for (int e = threadIdx.x; e <= E; e += blockDim.x) {
@@ -316,7 +336,7 @@ extern "C" int b200moe_expert_sort(const b200moe_sort_args* a, void* stream) {
       cudaFuncSetAttribute(expert_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (32 * 1024 + 3 * 1024 + 2) * 4) != cudaSuccess)
     return B200MOE_ECUDA;
-  expert_sort_kernel<<<1, nwarps * 32, smem, static_cast<cudaStream_t>(stream)>>>(
+  expert_sort_kernel<<<1, (nwarps < 8 ? 8 : nwarps) * 32, smem, static_cast<cudaStream_t>(stream)>>>(
       a->topk_ids, a->expert_map, a->expert_map_len, rows, E,
       reinterpret_cast<int32_t*>(base + L.status),
       reinterpret_cast<int32_t*>(base + L.expert_counts),
@@ -327,7 +347,7 @@ extern "C" int b200moe_expert_sort(const b200moe_sort_args* a, void* stream) {
       reinterpret_cast<int32_t*>(base + L.mtile_rows),
       reinterpret_cast<int32_t*>(base + L.sorted_route_ids),
       reinterpret_cast<int32_t*>(base + L.inv_perm), L.mtile_cap,
-      L.tile_rows == 64 ? 64 : 128, a->wait_flags, a->wait_epoch_dev, a->wait_status, a->wait_world,
+      L.tile_rows == 64 ? 64 : 128, nwarps, a->wait_flags, a->wait_epoch_dev, a->wait_status, a->wait_world,
       a->wait_timeout_ms > 0 ? static_cast<unsigned long long>(a->wait_timeout_ms) * 1000000ull : kWaitLimitNs);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
@@ -401,10 +421,10 @@ extern "C" int b200moe_expert_sort_static(const int32_t* topk_ids, const int32_t
       cudaFuncSetAttribute(expert_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (32 * 1024 + 3 * 1024 + 2) * 4) != cudaSuccess)
     return B200MOE_ECUDA;
-  expert_sort_kernel<<<1, nwarps * 32, smem, static_cast<cudaStream_t>(stream)>>>(
+  expert_sort_kernel<<<1, (nwarps < 8 ? 8 : nwarps) * 32, smem, static_cast<cudaStream_t>(stream)>>>(
       topk_ids, expert_map, expert_map_len, rows, num_experts, w + kStaticOffStatus,
       w + kStaticOffCounts, expert_offsets, w + kStaticOffTileBase, w + kStaticOffMtileExpert,
       w + kStaticOffMtileRow0, w + kStaticOffMtileRows, sorted_route_ids, inv_perm,
-      kStaticSortMtileCap, 128, nullptr, nullptr, nullptr, 0, 0ull);
+      kStaticSortMtileCap, 128, nwarps, nullptr, nullptr, nullptr, 0, 0ull);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }

@@ -98,6 +98,26 @@ class _LayerBase:
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream(self.dev).synchronize()
 
+    @property
+    def can_capture(self) -> bool:
+        """True where one step has no host-dependent argument and no host sync, so that it can be
+        recorded into a CUDA graph (the reference times its layer the same way: graph replay,
+        benchmarks/benchmark_moe.py:155-222)."""
+        return False
+
+    def capture(self) -> torch.cuda.CUDAGraph:
+        """Record one step on the staging buffers (``x_stage``, ``lg_stage``) into a CUDA graph;
+        ``graph.replay()`` is then a full layer pass on whatever those buffers hold, its result in
+        ``self.out``.  With several ranks, all must replay the same number of times."""
+        if not self.can_capture:
+            raise RuntimeError("this layer's step needs the host between its kernels and cannot be captured")
+        torch.cuda.synchronize(self.dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.forward(self.x_stage, self.lg_stage)
+        self.graph = g
+        return g
+
     def check_status(self) -> None:
         if self.last_binding is not None:
             fused_moe.check_device_status(self.last_binding)
@@ -155,6 +175,10 @@ class ExpertParallelMoE(_LayerBase):
         self.recv_out = torch.empty((cap, shp.hidden), dtype=torch.float32, device=dev)
         self.plan, self.scratch = self._local_plan(cap, 1)
         self.kernels_per_step = 9  # route, rank sort, gather, expert sort, quant, gemm1, gemm2, un-permute, combine
+
+    @property
+    def can_capture(self) -> bool:
+        return self.world == 1      # the NCCL exchange reads the split sizes on the host
 
     @classmethod
     def from_synthetic(cls, shp: synth.MoEShape, dev, rank: int, world: int):

@@ -48,7 +48,7 @@ def parse_args():
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
                     help="expert-parallel exchange: own kernels over peer memory, or NCCL all-to-all")
     ap.add_argument("--no-graph", action="store_true",
-                    help="launch the expert-parallel step kernel by kernel instead of replaying a CUDA graph")
+                    help="launch the step kernel by kernel instead of replaying a CUDA graph")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-experts", type=int, default=8, help="experts in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -231,8 +231,8 @@ def config_of(shp, n_gpus: int, ep: str = "peer", graph: bool = False) -> dict:
             "intermediate": shp.intermediate, "experts": shp.experts, "top_k": shp.topk,
             "recipe": shp.recipe, "activation": shp.activation, "router": shp.router,
             "parallelism": ("single" if n_gpus == 1 else f"{shp.parallelism}{n_gpus}"),
-            "exchange": ("none" if n_gpus == 1 else ("nccl all-reduce" if shp.parallelism == "tp" else
-                                                     (ep + (", step replayed from a CUDA graph" if graph else "")))),
+            "exchange": ("none" if n_gpus == 1 else ("nccl all-reduce" if shp.parallelism == "tp" else ep)),
+            "launch": "step replayed from a CUDA graph" if graph else "kernel by kernel",
             "l2": "no flush: the expert weights read per step exceed the 126 MB L2"}
 
 
@@ -294,10 +294,11 @@ def main():
     for i in range(args.warmup):
         layer.forward(x_dev, lg_dev, stage_timer=timer if i >= args.warmup // 2 else None)
     barrier()
-    # the peer-memory expert-parallel step has no host-dependent argument: it is captured once in
-    # a CUDA graph and replayed (per-stage events then come from the eager warm-up passes above)
+    # a step without host-dependent arguments (one GPU; the peer-memory expert-parallel step) is
+    # captured once in a CUDA graph and replayed, the way the reference times its layer
+    # (per-stage events then come from the eager warm-up passes above)
     graph = None
-    if hasattr(layer, "capture") and not args.no_graph:
+    if layer.can_capture and not args.no_graph:
         layer.x_stage.copy_(x_dev)
         layer.lg_stage.copy_(lg_dev)
         graph = layer.capture()
@@ -366,7 +367,7 @@ def main():
             "metric": "moe_layer_tokens_per_s", "value": total_tokens / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": dtype_of(shp),
-            "data": "synthetic", "config": config_of(shp, world, args.ep, graph is not None and args.ep == "peer"), "clocks": clocks,
+            "data": "synthetic", "config": config_of(shp, world, args.ep, graph is not None), "clocks": clocks,
             "e2e": {"value": total_tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2 + lg_host.numel() * 4,
                     "d2h_bytes_per_step": out_host.numel() * 2},
