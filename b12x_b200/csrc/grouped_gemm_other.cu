@@ -1,12 +1,24 @@
 // Grouped expert GEMMs of the w4a16 recipe: BF16 activations x NVFP4 weights that are expanded to
-// BF16 on the fly, on tcgen05.mma.kind::f16 with FP32 accumulation in TMEM.
+// a 16-bit float on the fly, on tcgen05.mma.kind::f16 with FP32 accumulation in TMEM.
 //
 // The tensor core cannot read 4-bit operands next to 16-bit ones, so each pipeline stage has a
-// conversion step: the TMA producer lands the packed codes (128 rows x 32 bytes per sub-tile) and the
-// E4M3 scale atoms in a staging area, eight converter warps expand them to BF16 (code value x block
-// scale is exact in BF16: 2 + 4 significant bits) straight into the 128-byte-swizzled operand tile
-// the MMA reads, and hand the stage to the MMA warp through an mbarrier.  The accumulator is double
-// buffered in TMEM (2 x 256 columns), so the epilogue of one tile overlaps the main loop of the next.
+// conversion step: the TMA producer lands the token rows, the packed codes (128 rows x 32 bytes per
+// sub-tile) and the scale atoms in a ring of load stages, eight converter warps expand the codes
+// straight into one of the 128-byte-swizzled operand tiles the MMA reads, and hand it to the MMA
+// warp through an mbarrier.  The two rings are separate (three load stages of 26 KiB, four converted
+// tiles of 32 KiB): what limits the kernel once the conversion is cheap is the hand-off latency
+// converter -> MMA -> tcgen05.commit -> converter, and four tiles in flight cover it, while deeper
+// load rings (tried: 3, 4, 6) change nothing.  The accumulator is double buffered in TMEM
+// (2 x 256 columns), so the epilogue of one tile overlaps the main loop of the next.
+//
+// Conversion (E4M3 block scales).  The hardware conversion cvt.rn.f16x2.e2m1x2 turns a byte into
+// two FP16 code values, a half2 multiply applies the block scale (2 + 4 significant bits, between
+// 2^-10 and 2688: exact in FP16 as in BF16), and FP16 -> FP32 -> BF16 re-encodes the pair.  The
+// integer pipe issues at half rate, and the byte-permute look-up used before (about ten integer
+// instructions per two values) held this kernel at 0.28 of the BF16 peak.  Both operands stay
+// BF16: an instruction descriptor with BF16 tokens and FP16 weights, which would save the
+// re-encoding, faulted on B200.  Power-of-two (E8M0) scales exceed the FP16 range; for them the
+// weights are expanded with the look-up.
 //
 // Numerics follow the reference's W4A16 oracle (tests/_reference/w4a16_reference.py:266-359):
 // weights de-quantised then held in BF16, x in BF16, FP32 accumulation, activation in FP32, BF16
@@ -20,27 +32,37 @@ int make_tmap_bytes_2d(CUtensorMap* out, const void* base, uint64_t row_bytes, u
 
 namespace w4a16 {
 
-constexpr int kStages = 3;
+#ifndef W4A16_LOAD_STAGES
+#define W4A16_LOAD_STAGES 3
+#endif
+constexpr int kStages = W4A16_LOAD_STAGES;  // load ring: token rows, packed codes, scale atoms
+#ifndef W4A16_B_STAGES
+#define W4A16_B_STAGES 4
+#endif
+constexpr int kBStages = W4A16_B_STAGES;    // converted weight tiles
 constexpr int kKPerStage = 64;              // BF16 elements per 128-byte operand row
 constexpr int kThreads = 18 * 32;           // TMA, MMA, 8 converter warps, 8 epilogue warps
 constexpr int kSmemA = 128 * 128;           // 16 KiB
 constexpr int kSmemB = 256 * 128;           // 32 KiB
 constexpr int kSmemRaw = 2 * 128 * 32;      // packed codes of the two sub-tiles
 constexpr int kSmemSf = 4 * 512;            // two scale atoms per sub-tile (a sub-tile may straddle)
-constexpr int kStageBytes = kSmemA + kSmemB + kSmemRaw + kSmemSf;
+constexpr int kStageBytes = kSmemA + kSmemRaw + kSmemSf;
 constexpr int kMaxExperts = 1024;
 
 struct __align__(8) SmemTail {
-  uint64_t full[kStages];
-  uint64_t conv[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kStages];        // load stage landed (TMA transaction bytes)
+  uint64_t empty[kStages];       // load stage free: 8 converter warps + the MMAs that read its rows
+  uint64_t bfull[kBStages];      // converted tile written (8 converter warps)
+  uint64_t bempty[kBStages];     // converted tile read by its MMAs
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
   int32_t tile_base[kMaxExperts + 1];
 };
-constexpr int kSmemBytes = 1024 + kStages * kStageBytes + static_cast<int>(sizeof(SmemTail));
+constexpr int kSmemBytes =
+    1024 + kStages * kStageBytes + kBStages * kSmemB + static_cast<int>(sizeof(SmemTail));
+static_assert(kSmemBytes <= 227 * 1024, "shared memory of the W4A16 kernel");
 
 enum { EPI_FC1_GATED = 0, EPI_FC1_RELU2 = 1, EPI_FC2 = 2 };
 
@@ -121,6 +143,68 @@ __device__ __forceinline__ void cvt_e2m1x8_bf16(uint32_t w, __nv_bfloat162 sc, u
   }
 }
 
+// Eight E2M1 codes (one 32-bit word, element 0 in the low nibble) times a block scale -> four
+// bf16x2 words.  The hardware conversion takes a byte (two codes, low nibble -> low half) to f16x2.
+#ifndef W4A16_CVT_MODE
+#define W4A16_CVT_MODE 0
+#endif
+#if W4A16_CVT_MODE == 0
+// `sc` = the scale as an f16x2 pair.  The product is exact in FP16 (2 + 4 significant bits, between
+// 2^-10 and 2688), so FP16 -> FP32 -> BF16 rounds nothing.
+__device__ __forceinline__ void cvt_e2m1x8_scaled(uint32_t w, uint32_t sc, uint32_t (&out)[4]) {
+  uint32_t v[4];
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}\n"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+      : "r"(w));
+  const __half2 s2 = *reinterpret_cast<const __half2*>(&sc);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(__hmul2(*reinterpret_cast<const __half2*>(&v[j]), s2));
+    const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+    out[j] = *reinterpret_cast<const uint32_t*>(&b);
+  }
+}
+#else
+// `sc` = the scale times 2^112 as a bf16x2 pair.  The f16 bits of a code value, shifted right by
+// three with the sign put back, read as BF16 are that value times 2^-112 (the exponent fields
+// differ by 127 - 15; zero stays zero; code values are normal in FP16), and the multiplication
+// by the scale takes the 2^112 back: one BF16 multiply, exact.
+__device__ __forceinline__ void cvt_e2m1x8_scaled(uint32_t w, uint32_t sc, uint32_t (&out)[4]) {
+  uint32_t v[4];
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}\n"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+      : "r"(w));
+  const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&sc);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t x = ((v[j] & 0x7fff7fffu) >> 3) | (v[j] & 0x80008000u);
+    const __nv_bfloat162 b = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&x), s2);
+    out[j] = *reinterpret_cast<const uint32_t*>(&b);
+  }
+}
+#endif
+// Four E4M3 scale bytes -> two f16x2 words (bytes 0,1 and 2,3; low byte -> low half).
+__device__ __forceinline__ void cvt_e4m3x4_f16(uint32_t w, uint32_t& s01, uint32_t& s23) {
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "mov.b32 {lo, hi}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}\n"
+      : "=r"(s01), "=r"(s23)
+      : "r"(w));
+}
+
+__device__ constexpr uint32_t kTwo112 = 0x77807780u;   // 2^112 as a bf16x2 pair
+
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -130,7 +214,7 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sA = smem;
   uint8_t* sB = sA + kStages * kSmemA;
-  uint8_t* sRaw = sB + kStages * kSmemB;
+  uint8_t* sRaw = sB + kBStages * kSmemB;
   uint8_t* sSf = sRaw + kStages * kSmemRaw;
   SmemTail* tail = reinterpret_cast<SmemTail*>(sSf + kStages * kSmemSf);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -138,8 +222,11 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&tail->full[s], 1);
-      mbar_init(&tail->conv[s], 8);
-      mbar_init(&tail->empty[s], 1);
+      mbar_init(&tail->empty[s], 9);
+    }
+    for (int b = 0; b < kBStages; ++b) {
+      mbar_init(&tail->bfull[b], 8);
+      mbar_init(&tail->bempty[b], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tail->tmem_full[b], 1);
@@ -215,8 +302,8 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(128, 256);
-      int stage = 0;
-      uint32_t phase = 0;
+      int stage = 0, bstage = 0;
+      uint32_t phase = 0, bphase = 0;
       uint32_t acc_phase[2] = {0, 0};
       int buf = 0;
       bool ok = true;
@@ -230,20 +317,25 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
         const uint32_t d_tmem = tmem_base + buf * 256;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL) ||
-              !mbar_wait_bounded(&tail->conv[stage], phase, abort_flag, p.status, WAIT_CONVERT)) {
+              !mbar_wait_bounded(&tail->bfull[bstage], bphase, abort_flag, p.status, WAIT_CONVERT)) {
             ok = false;
             break;
           }
           tc_fence_after();
           const uint64_t adesc = make_desc_sw128(smem_u32(sA + stage * kSmemA));
-          const uint64_t bdesc = make_desc_sw128(smem_u32(sB + stage * kSmemB));
+          const uint64_t bdesc = make_desc_sw128(smem_u32(sB + bstage * kSmemB));
 #pragma unroll
           for (int j = 0; j < 4; ++j)   // 16 bf16 = 32 bytes per MMA step
             mma_bf16(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
           tc_commit(&tail->empty[stage]);
+          tc_commit(&tail->bempty[bstage]);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
+          }
+          if (++bstage == kBStages) {
+            bstage = 0;
+            bphase ^= 1;
           }
         }
         if (ok) tc_commit(&tail->tmem_full[buf]);
@@ -256,8 +348,8 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
     // thread t expands weight row t of the 256-row operand tile: 64 codes -> 64 bf16 = 128 bytes
     const int t = threadIdx.x - 64;
     const int sub_tile = t >> 7, rr = t & 127;
-    int stage = 0;
-    uint32_t phase = 0;
+    int stage = 0, bstage = 0;
+    uint32_t phase = 0, bphase = 0;
     bool ok = true;
     for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
       const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
@@ -270,36 +362,73 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
       const int atom_sel = (wrow >> 7) - first_group;       // 0 or 1
       const uint32_t sf_off = sub_tile * 1024 + atom_sel * 512 + (wrow & 31) * 16 + ((wrow >> 5) & 3) * 4;
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_CONVERT)) {
+        if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_CONVERT) ||
+            !mbar_wait_bounded(&tail->bempty[bstage], bphase ^ 1, abort_flag, p.status,
+                               WAIT_CONVERT)) {
           ok = false;
           break;
         }
+        tc_fence_after();
         const uint4* raw = reinterpret_cast<const uint4*>(sRaw + stage * kSmemRaw + t * 32);
         const uint4 c0 = raw[0], c1 = raw[1];
         const uint32_t sfw = *reinterpret_cast<const uint32_t*>(sSf + stage * kSmemSf + sf_off);
         const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-        uint8_t* brow = sB + stage * kSmemB + t * 128;
+        uint8_t* brow = sB + bstage * kSmemB + t * 128;
+        if (!p.sf_e8m0) {
+          uint32_t s01, s23;
+          cvt_e4m3x4_f16(sfw, s01, s23);
+#if W4A16_CVT_MODE != 0
+          {  // f16 pairs -> bf16 pairs times 2^112 (0x7780 = 2^112 in BF16)
+            const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&s01));
+            const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&s23));
+            const __nv_bfloat162 k = *reinterpret_cast<const __nv_bfloat162*>(&kTwo112);
+            const __nv_bfloat162 b01 = __hmul2(__floats2bfloat162_rn(f01.x, f01.y), k);
+            const __nv_bfloat162 b23 = __hmul2(__floats2bfloat162_rn(f23.x, f23.y), k);
+            s01 = *reinterpret_cast<const uint32_t*>(&b01);
+            s23 = *reinterpret_cast<const uint32_t*>(&b23);
+          }
+#endif
 #pragma unroll
-        for (int blk = 0; blk < 4; ++blk) {                 // 16 values per scale
-          const uint32_t sb = (sfw >> (8 * blk)) & 0xffu;
-          // E8M0: 2^(b-127) is the f32 with exponent field b (b = 0: the subnormal 2^-127)
-          const float sv = p.sf_e8m0 ? __uint_as_float(sb != 0u ? sb << 23 : 0x00400000u) : e4m3_to_f32(sb);
-          const __nv_bfloat16 s = __float2bfloat16_rn(sv);
-          const __nv_bfloat162 sc = __halves2bfloat162(s, s);
+          for (int blk = 0; blk < 4; ++blk) {               // 16 values per scale
+            const uint32_t sc = __byte_perm(blk < 2 ? s01 : s23, 0u, (blk & 1) ? 0x3232u : 0x1010u);
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t o[4];
-            cvt_e2m1x8_bf16(words[blk * 2 + h], sc, o);
-            const int chunk = blk * 2 + h;                   // 16-byte chunk of the 128-byte row
-            *reinterpret_cast<uint4*>(brow + ((chunk ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            for (int h = 0; h < 2; ++h) {
+              uint32_t o[4];
+              cvt_e2m1x8_scaled(words[blk * 2 + h], sc, o);
+              const int chunk = blk * 2 + h;                 // 16-byte chunk of the 128-byte row
+              *reinterpret_cast<uint4*>(brow + ((chunk ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int blk = 0; blk < 4; ++blk) {               // 16 values per scale
+            const uint32_t sb = (sfw >> (8 * blk)) & 0xffu;
+            // E8M0: 2^(b-127) is the f32 with exponent field b (b = 0: the subnormal 2^-127)
+            const float sv = __uint_as_float(sb != 0u ? sb << 23 : 0x00400000u);
+            const __nv_bfloat16 s = __float2bfloat16_rn(sv);
+            const __nv_bfloat162 sc = __halves2bfloat162(s, s);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t o[4];
+              cvt_e2m1x8_bf16(words[blk * 2 + h], sc, o);
+              const int chunk = blk * 2 + h;
+              *reinterpret_cast<uint4*>(brow + ((chunk ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
           }
         }
         fence_proxy_async_smem();                            // generic writes -> tensor-core reads
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tail->conv[stage]);
+        if (lane == 0) {
+          mbar_arrive(&tail->bfull[bstage]);
+          mbar_arrive(&tail->empty[stage]);
+        }
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1;
+        }
+        if (++bstage == kBStages) {
+          bstage = 0;
+          bphase ^= 1;
         }
       }
     }
