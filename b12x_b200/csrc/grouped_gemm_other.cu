@@ -1,24 +1,35 @@
 // Grouped expert GEMMs of the w4a16 recipe: BF16 activations x NVFP4 weights that are expanded to
 // a 16-bit float on the fly, on tcgen05.mma.kind::f16 with FP32 accumulation in TMEM.
 //
-// The tensor core cannot read 4-bit operands next to 16-bit ones, so each pipeline stage has a
-// conversion step: the TMA producer lands the token rows, the packed codes (128 rows x 32 bytes per
-// sub-tile) and the scale atoms in a ring of load stages, eight converter warps expand the codes
-// straight into one of the 128-byte-swizzled operand tiles the MMA reads, and hand it to the MMA
-// warp through an mbarrier.  The two rings are separate (three load stages of 26 KiB, four converted
-// tiles of 32 KiB): what limits the kernel once the conversion is cheap is the hand-off latency
-// converter -> MMA -> tcgen05.commit -> converter, and four tiles in flight cover it, while deeper
-// load rings (tried: 3, 4, 6) change nothing.  The accumulator is double buffered in TMEM
-// (2 x 256 columns), so the epilogue of one tile overlaps the main loop of the next.
+// The tensor core cannot read 4-bit operands next to 16-bit ones, so the main loop has a conversion
+// step.  Three rings in shared memory: (1) per k-block of 64, the token rows (16 KiB) and the scale
+// atoms (2 KiB); (2) the packed codes of FOUR k-blocks, one TMA box of 128 rows x 128 bytes per
+// sub-tile (the path from L2 takes about as long for a 32-byte row as for a 128-byte one, so a box of
+// 32-byte rows per k-block cost four times the requests; 128-byte swizzle, so the converters'
+// 16-byte reads, one row per thread, spread over the banks); (3) two converted weight tiles of
+// 32 KiB, 128-byte-swizzled as the MMA reads them.  Eight converter warps expand a k-block's codes
+// into a converted tile and hand it to the MMA warp through an mbarrier; tcgen05.commit gives the
+// tile and the load stage back.  The accumulator is double buffered in TMEM (2 x 256 columns), so
+// the epilogue of one tile overlaps the main loop of the next.
 //
 // Conversion (E4M3 block scales).  The hardware conversion cvt.rn.f16x2.e2m1x2 turns a byte into
 // two FP16 code values, a half2 multiply applies the block scale (2 + 4 significant bits, between
 // 2^-10 and 2688: exact in FP16 as in BF16), and FP16 -> FP32 -> BF16 re-encodes the pair.  The
 // integer pipe issues at half rate, and the byte-permute look-up used before (about ten integer
 // instructions per two values) held this kernel at 0.28 of the BF16 peak.  Both operands stay
-// BF16: an instruction descriptor with BF16 tokens and FP16 weights, which would save the
-// re-encoding, faulted on B200.  Power-of-two (E8M0) scales exceed the FP16 range; for them the
-// weights are expanded with the look-up.
+// BF16: a launch whose instruction descriptor named BF16 tokens and FP16 weights, which would
+// save the re-encoding, ended with a CUDA error on B200, and with both BF16 the same code runs.
+// Power-of-two (E8M0) scales exceed the FP16 range; for them the weights are expanded with the
+// look-up.
+//
+// What bounds it now is shared-memory bandwidth (128 bytes per clock): per k-block the MMAs read
+// 48 KiB of operands, the TMA writes 26 KiB, the converters read 10 KiB and write 32 KiB, about
+// 930 clocks against 544 clocks of tensor-pipe time.  Measured with the conversion removed
+// (timing only) the kernel takes 76 % of its time, without the token-row loads as well 70 %;
+// ring depths (3 / 4 / 6 load stages, 2 / 3 / 4 converted tiles) and sixteen converter warps
+// that take alternate k-blocks (W4A16_CONV_GROUPS=2) change nothing.  The way further is the
+// weights as the TMEM-resident operand of the MMA (written by tcgen05.st, never through shared
+// memory), which halves that traffic.
 //
 // Numerics follow the reference's W4A16 oracle (tests/_reference/w4a16_reference.py:266-359):
 // weights de-quantised then held in BF16, x in BF16, FP32 accumulation, activation in FP32, BF16
@@ -33,25 +44,34 @@ int make_tmap_bytes_2d(CUtensorMap* out, const void* base, uint64_t row_bytes, u
 namespace w4a16 {
 
 #ifndef W4A16_LOAD_STAGES
-#define W4A16_LOAD_STAGES 3
+#define W4A16_LOAD_STAGES 4
 #endif
-constexpr int kStages = W4A16_LOAD_STAGES;  // load ring: token rows, packed codes, scale atoms
+constexpr int kStages = W4A16_LOAD_STAGES;  // load ring: token rows and scale atoms of one k-block
+constexpr int kRawStages = 2;               // ring of packed codes, kKBlocksPerRaw k-blocks each
+constexpr int kKBlocksPerRaw = 4;
 #ifndef W4A16_B_STAGES
-#define W4A16_B_STAGES 4
+#define W4A16_B_STAGES 2
 #endif
 constexpr int kBStages = W4A16_B_STAGES;    // converted weight tiles
 constexpr int kKPerStage = 64;              // BF16 elements per 128-byte operand row
-constexpr int kThreads = 18 * 32;           // TMA, MMA, 8 converter warps, 8 epilogue warps
+#ifndef W4A16_CONV_GROUPS
+#define W4A16_CONV_GROUPS 1
+#endif
+constexpr int kConvGroups = W4A16_CONV_GROUPS;   // groups of 8 converter warps; group g takes stages g, g + groups, ...
+constexpr int kConvWarps = 8 * kConvGroups;
+constexpr int kThreads = (2 + kConvWarps + 8) * 32;   // TMA, MMA, converter warps, 8 epilogue warps
 constexpr int kSmemA = 128 * 128;           // 16 KiB
 constexpr int kSmemB = 256 * 128;           // 32 KiB
-constexpr int kSmemRaw = 2 * 128 * 32;      // packed codes of the two sub-tiles
+constexpr int kSmemRaw = 2 * 128 * 128;     // packed codes of the two sub-tiles, 128 bytes = 4 k-blocks per row
 constexpr int kSmemSf = 4 * 512;            // two scale atoms per sub-tile (a sub-tile may straddle)
-constexpr int kStageBytes = kSmemA + kSmemRaw + kSmemSf;
+constexpr int kStageBytes = kSmemA + kSmemSf;
 constexpr int kMaxExperts = 1024;
 
 struct __align__(8) SmemTail {
   uint64_t full[kStages];        // load stage landed (TMA transaction bytes)
   uint64_t empty[kStages];       // load stage free: 8 converter warps + the MMAs that read its rows
+  uint64_t rfull[kRawStages];    // packed codes landed
+  uint64_t rempty[kRawStages];   // packed codes read by every converter warp
   uint64_t bfull[kBStages];      // converted tile written (8 converter warps)
   uint64_t bempty[kBStages];     // converted tile read by its MMAs
   uint64_t tmem_full[2];
@@ -61,7 +81,8 @@ struct __align__(8) SmemTail {
   int32_t tile_base[kMaxExperts + 1];
 };
 constexpr int kSmemBytes =
-    1024 + kStages * kStageBytes + kBStages * kSmemB + static_cast<int>(sizeof(SmemTail));
+    1024 + kStages * kStageBytes + kRawStages * kSmemRaw + kBStages * kSmemB +
+    static_cast<int>(sizeof(SmemTail));
 static_assert(kSmemBytes <= 227 * 1024, "shared memory of the W4A16 kernel");
 
 enum { EPI_FC1_GATED = 0, EPI_FC1_RELU2 = 1, EPI_FC2 = 2 };
@@ -145,10 +166,6 @@ __device__ __forceinline__ void cvt_e2m1x8_bf16(uint32_t w, __nv_bfloat162 sc, u
 
 // Eight E2M1 codes (one 32-bit word, element 0 in the low nibble) times a block scale -> four
 // bf16x2 words.  The hardware conversion takes a byte (two codes, low nibble -> low half) to f16x2.
-#ifndef W4A16_CVT_MODE
-#define W4A16_CVT_MODE 0
-#endif
-#if W4A16_CVT_MODE == 0
 // `sc` = the scale as an f16x2 pair.  The product is exact in FP16 (2 + 4 significant bits, between
 // 2^-10 and 2688), so FP16 -> FP32 -> BF16 rounds nothing.
 __device__ __forceinline__ void cvt_e2m1x8_scaled(uint32_t w, uint32_t sc, uint32_t (&out)[4]) {
@@ -169,30 +186,6 @@ __device__ __forceinline__ void cvt_e2m1x8_scaled(uint32_t w, uint32_t sc, uint3
     out[j] = *reinterpret_cast<const uint32_t*>(&b);
   }
 }
-#else
-// `sc` = the scale times 2^112 as a bf16x2 pair.  The f16 bits of a code value, shifted right by
-// three with the sign put back, read as BF16 are that value times 2^-112 (the exponent fields
-// differ by 127 - 15; zero stays zero; code values are normal in FP16), and the multiplication
-// by the scale takes the 2^112 back: one BF16 multiply, exact.
-__device__ __forceinline__ void cvt_e2m1x8_scaled(uint32_t w, uint32_t sc, uint32_t (&out)[4]) {
-  uint32_t v[4];
-  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
-      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
-      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
-      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
-      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
-      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}\n"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
-      : "r"(w));
-  const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&sc);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const uint32_t x = ((v[j] & 0x7fff7fffu) >> 3) | (v[j] & 0x80008000u);
-    const __nv_bfloat162 b = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&x), s2);
-    out[j] = *reinterpret_cast<const uint32_t*>(&b);
-  }
-}
-#endif
 // Four E4M3 scale bytes -> two f16x2 words (bytes 0,1 and 2,3; low byte -> low half).
 __device__ __forceinline__ void cvt_e4m3x4_f16(uint32_t w, uint32_t& s01, uint32_t& s23) {
   asm("{\n\t.reg .b16 lo, hi;\n\t"
@@ -202,8 +195,6 @@ __device__ __forceinline__ void cvt_e4m3x4_f16(uint32_t w, uint32_t& s01, uint32
       : "=r"(s01), "=r"(s23)
       : "r"(w));
 }
-
-__device__ constexpr uint32_t kTwo112 = 0x77807780u;   // 2^112 as a bf16x2 pair
 
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -215,7 +206,7 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
   uint8_t* sA = smem;
   uint8_t* sB = sA + kStages * kSmemA;
   uint8_t* sRaw = sB + kBStages * kSmemB;
-  uint8_t* sSf = sRaw + kStages * kSmemRaw;
+  uint8_t* sSf = sRaw + kRawStages * kSmemRaw;
   SmemTail* tail = reinterpret_cast<SmemTail*>(sSf + kStages * kSmemSf);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -223,6 +214,10 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&tail->full[s], 1);
       mbar_init(&tail->empty[s], 9);
+    }
+    for (int r = 0; r < kRawStages; ++r) {
+      mbar_init(&tail->rfull[r], 1);
+      mbar_init(&tail->rempty[r], kConvWarps);
     }
     for (int b = 0; b < kBStages; ++b) {
       mbar_init(&tail->bfull[b], 8);
@@ -256,8 +251,8 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmW);
       }
-      int stage = 0;
-      uint32_t phase = 0;
+      int stage = 0, rs = 0;
+      uint32_t phase = 0, rphase = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
         const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
@@ -270,6 +265,28 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
         const int g[4] = {r0 >> 7, min((r0 + 127) >> 7, p.sf_rowgroups - 1), r1 >> 7,
                           min((r1 + 127) >> 7, p.sf_rowgroups - 1)};
         for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if ((kb & (kKBlocksPerRaw - 1)) == 0 && (lane == 1 || lane == 2)) {
+            // the codes of four k-blocks in one box of 128-byte rows: the path from L2 takes
+            // about as long for a 32-byte row as for a 128-byte one
+            if (!mbar_wait_bounded(&tail->rempty[rs], rphase ^ 1, abort_flag, p.status,
+                                   WAIT_SMEM_EMPTY)) {
+              ok = false;
+              break;
+            }
+            uint64_t* rbar = &tail->rfull[rs];
+            if (lane == 1) {
+              mbar_expect_tx(rbar, kSmemRaw);
+              tma_load_2d(sRaw + rs * kSmemRaw, &tmW, rbar, kb * 32, c.e * p.w_rows + r0);
+            } else {
+              tma_load_2d(sRaw + rs * kSmemRaw + 128 * 128, &tmW, rbar, kb * 32, c.e * p.w_rows + r1);
+            }
+          }
+          if ((kb & (kKBlocksPerRaw - 1)) == kKBlocksPerRaw - 1 || kb == p.k_blocks - 1) {
+            if (++rs == kRawStages) {
+              rs = 0;
+              rphase ^= 1;
+            }
+          }
           if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status,
                                  WAIT_SMEM_EMPTY)) {
             ok = false;
@@ -277,13 +294,9 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           uint64_t* bar = &tail->full[stage];
           if (lane == 0) {
-            mbar_expect_tx(bar, kSmemA + kSmemRaw + kSmemSf);
+            mbar_expect_tx(bar, kSmemA + kSmemSf);
             tma_load_2d(sA + stage * kSmemA, &tmA, bar, kb * kKPerStage, row0);
-          } else if (lane == 1) {
-            tma_load_2d(sRaw + stage * kSmemRaw, &tmW, bar, kb * 32, c.e * p.w_rows + r0);
-          } else if (lane == 2) {
-            tma_load_2d(sRaw + stage * kSmemRaw + 128 * 32, &tmW, bar, kb * 32, c.e * p.w_rows + r1);
-          } else {
+          } else if (lane >= 3) {
             const int q = lane - 3;
             bulk_load(sSf + stage * kSmemSf + q * 512,
                       sf_e + (static_cast<size_t>(g[q]) * p.atoms_k + kb) * 512, 512, bar);
@@ -343,13 +356,17 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
         buf ^= 1;
       }
     }
-  } else if (warp < 10) {
+  } else if (warp < 2 + kConvWarps) {
     // ------------------------------ converters --------------------------------
-    // thread t expands weight row t of the 256-row operand tile: 64 codes -> 64 bf16 = 128 bytes
-    const int t = threadIdx.x - 64;
+    // thread t of a group expands weight row t of the 256-row operand tile: 64 codes -> 64 bf16
+    // = 128 bytes.  The groups take alternate stages, so the fixed latencies of a stage (barrier
+    // wake-up, shared-memory loads, the proxy fence) of one group lie under the arithmetic of the other.
+    const int group = (threadIdx.x - 64) >> 8;
+    const int t = (threadIdx.x - 64) & 255;
     const int sub_tile = t >> 7, rr = t & 127;
-    int stage = 0, bstage = 0;
-    uint32_t phase = 0, bphase = 0;
+    int it = 0;
+    int stage = 0, bstage = 0, rs = 0;
+    uint32_t phase = 0, bphase = 0, rphase = 0;
     bool ok = true;
     for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
       const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
@@ -361,33 +378,28 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
       // scale bytes of this row inside the two staged atoms of its sub-tile
       const int atom_sel = (wrow >> 7) - first_group;       // 0 or 1
       const uint32_t sf_off = sub_tile * 1024 + atom_sel * 512 + (wrow & 31) * 16 + ((wrow >> 5) & 3) * 4;
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
+      for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+        if (kConvGroups == 1 || it % kConvGroups == group) {
         if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_CONVERT) ||
+            !mbar_wait_bounded(&tail->rfull[rs], rphase, abort_flag, p.status, WAIT_CONVERT) ||
             !mbar_wait_bounded(&tail->bempty[bstage], bphase ^ 1, abort_flag, p.status,
                                WAIT_CONVERT)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint4* raw = reinterpret_cast<const uint4*>(sRaw + stage * kSmemRaw + t * 32);
-        const uint4 c0 = raw[0], c1 = raw[1];
+        // 128-byte rows, 16-byte chunks swizzled by the row (as the TMA wrote them); this k-block
+        // owns chunks 2q and 2q + 1
+        const uint8_t* raw = sRaw + rs * kSmemRaw + t * 128;
+        const int q2 = (kb & (kKBlocksPerRaw - 1)) * 2;
+        const uint4 c0 = *reinterpret_cast<const uint4*>(raw + ((q2 ^ (t & 7)) << 4));
+        const uint4 c1 = *reinterpret_cast<const uint4*>(raw + (((q2 + 1) ^ (t & 7)) << 4));
         const uint32_t sfw = *reinterpret_cast<const uint32_t*>(sSf + stage * kSmemSf + sf_off);
         const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
         uint8_t* brow = sB + bstage * kSmemB + t * 128;
         if (!p.sf_e8m0) {
           uint32_t s01, s23;
           cvt_e4m3x4_f16(sfw, s01, s23);
-#if W4A16_CVT_MODE != 0
-          {  // f16 pairs -> bf16 pairs times 2^112 (0x7780 = 2^112 in BF16)
-            const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&s01));
-            const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&s23));
-            const __nv_bfloat162 k = *reinterpret_cast<const __nv_bfloat162*>(&kTwo112);
-            const __nv_bfloat162 b01 = __hmul2(__floats2bfloat162_rn(f01.x, f01.y), k);
-            const __nv_bfloat162 b23 = __hmul2(__floats2bfloat162_rn(f23.x, f23.y), k);
-            s01 = *reinterpret_cast<const uint32_t*>(&b01);
-            s23 = *reinterpret_cast<const uint32_t*>(&b23);
-          }
-#endif
 #pragma unroll
           for (int blk = 0; blk < 4; ++blk) {               // 16 values per scale
             const uint32_t sc = __byte_perm(blk < 2 ? s01 : s23, 0u, (blk & 1) ? 0x3232u : 0x1010u);
@@ -422,6 +434,16 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
           mbar_arrive(&tail->bfull[bstage]);
           mbar_arrive(&tail->empty[stage]);
         }
+        }
+        if ((kb & (kKBlocksPerRaw - 1)) == kKBlocksPerRaw - 1 || kb == p.k_blocks - 1) {
+          // this warp has read all it needs of the packed codes
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tail->rempty[rs]);
+          if (++rs == kRawStages) {
+            rs = 0;
+            rphase ^= 1;
+          }
+        }
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1;
@@ -435,7 +457,7 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
   } else {
     // ------------------------------ epilogue ----------------------------------
     const int sub = warp & 3;
-    const int half = (warp - 10) >> 2;
+    const int half = (warp - 2 - kConvWarps) >> 2;
     const int m = sub * 32 + lane;
     uint32_t acc_phase[2] = {0, 0};
     int buf = 0;
@@ -594,17 +616,18 @@ static int make_tmap_bf16(CUtensorMap* out, const void* base, uint64_t cols, uin
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? B200MOE_OK : B200MOE_ECUDA;
 }
-// packed weight codes [rows][row_bytes], box = 128 rows x 32 bytes, no swizzle (staging only)
+// packed weight codes [rows][row_bytes], box = 128 rows x 128 bytes (four k-blocks), 128-byte
+// swizzle so that the converters' 16-byte reads, one row per thread, spread over the banks
 static int make_tmap_codes(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return B200MOE_ECUDA;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_bytes & 15) != 0) return B200MOE_EALIGN;
   const cuuint64_t dims[2] = {row_bytes, rows};
   const cuuint64_t strides[1] = {row_bytes};
-  const cuuint32_t box[2] = {32, 128};
+  const cuuint32_t box[2] = {128, 128};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
-                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? B200MOE_OK : B200MOE_ECUDA;
 }
