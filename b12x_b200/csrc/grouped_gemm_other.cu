@@ -19,8 +19,8 @@
 // instructions per two values) held this kernel at 0.28 of the BF16 peak.  Both operands stay
 // BF16: a launch whose instruction descriptor named BF16 tokens and FP16 weights, which would
 // save the re-encoding, ended with a CUDA error on B200, and with both BF16 the same code runs.
-// Power-of-two (E8M0) scales exceed the FP16 range; for them the weights are expanded with the
-// look-up.
+// Power-of-two (E8M0) scales exceed the FP16 range; for them the code values are re-encoded first and
+// multiplied by the scale in BF16.
 //
 // What bounds it now is shared-memory bandwidth (128 bytes per clock): per k-block the MMAs read
 // 48 KiB of operands, the TMA writes 26 KiB, the converters read 10 KiB and write 32 KiB, about
@@ -136,40 +136,9 @@ __device__ __forceinline__ float act_gated(float gate, float up, const Params& p
   return (gate * s) * up;
 }
 
-// Eight E2M1 codes (one 32-bit word, element 0 in the low nibble) -> four bf16x2 words, each value
-// multiplied by the bf16 scale pair `sc`.  The magnitude (3 bits) indexes two 8-entry byte tables
-// with prmt; the sign bit is moved to bit 15 of each half.
-__device__ __forceinline__ void cvt_e2m1x8_bf16(uint32_t w, __nv_bfloat162 sc, uint32_t (&out)[4]) {
-  // bf16 of {0, .5, 1, 1.5, 2, 3, 4, 6}: 0000 3F00 3F80 3FC0 4000 4040 4080 40C0
-  constexpr uint32_t kHiA = 0x3F3F3F00u, kHiB = 0x40404040u;   // high bytes, entries 0-3 / 4-7
-  constexpr uint32_t kLoA = 0xC0800000u, kLoB = 0xC0804000u;   // low bytes
-  const uint32_t sel0 = w & 0x7777u, sel1 = (w >> 16) & 0x7777u;
-  const uint32_t hi0 = __byte_perm(kHiA, kHiB, sel0), lo0 = __byte_perm(kLoA, kLoB, sel0);
-  const uint32_t hi1 = __byte_perm(kHiA, kHiB, sel1), lo1 = __byte_perm(kLoA, kLoB, sel1);
-  uint32_t v[4];
-  v[0] = __byte_perm(lo0, hi0, 0x5140);   // elements 0,1
-  v[1] = __byte_perm(lo0, hi0, 0x7362);   // elements 2,3
-  v[2] = __byte_perm(lo1, hi1, 0x5140);   // elements 4,5
-  v[3] = __byte_perm(lo1, hi1, 0x7362);   // elements 6,7
-  // sign bits: nibble bit 3 of element 2j -> bit 15, of element 2j+1 -> bit 31
-  v[0] |= ((w << 12) & 0x8000u) | ((w << 24) & 0x80000000u);
-  v[1] |= ((w << 4) & 0x8000u) | ((w << 16) & 0x80000000u);
-  v[2] |= ((w >> 4) & 0x8000u) | ((w << 8) & 0x80000000u);
-  v[3] |= ((w >> 12) & 0x8000u) | (w & 0x80000000u);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&v[j]);
-    x = __hmul2(x, sc);
-    out[j] = *reinterpret_cast<uint32_t*>(&x);
-  }
-}
-
-// Eight E2M1 codes (one 32-bit word, element 0 in the low nibble) times a block scale -> four
-// bf16x2 words.  The hardware conversion takes a byte (two codes, low nibble -> low half) to f16x2.
-// `sc` = the scale as an f16x2 pair.  The product is exact in FP16 (2 + 4 significant bits, between
-// 2^-10 and 2688), so FP16 -> FP32 -> BF16 rounds nothing.
-__device__ __forceinline__ void cvt_e2m1x8_scaled(uint32_t w, uint32_t sc, uint32_t (&out)[4]) {
-  uint32_t v[4];
+// Four bytes of E2M1 codes (element 0 in the low nibble) -> four f16x2 words of code values: the
+// hardware conversion takes a byte (two codes, low nibble -> low half).
+__device__ __forceinline__ void cvt_e2m1x8_f16(uint32_t w, uint32_t (&v)[4]) {
   asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
       "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
       "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
@@ -178,6 +147,27 @@ __device__ __forceinline__ void cvt_e2m1x8_scaled(uint32_t w, uint32_t sc, uint3
       "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}\n"
       : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
       : "r"(w));
+}
+
+// Eight E2M1 codes -> four bf16x2 words, each value multiplied in BF16 by the bf16 scale pair `sc`
+// (power-of-two scales: the product is exact unless it leaves the BF16 range).
+__device__ __forceinline__ void cvt_e2m1x8_bf16(uint32_t w, __nv_bfloat162 sc, uint32_t (&out)[4]) {
+  uint32_t v[4];
+  cvt_e2m1x8_f16(w, v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v[j]));
+    const __nv_bfloat162 x = __hmul2(__floats2bfloat162_rn(f.x, f.y), sc);
+    out[j] = *reinterpret_cast<const uint32_t*>(&x);
+  }
+}
+
+// Eight E2M1 codes times an E4M3 block scale -> four bf16x2 words.  `sc` = the scale as an f16x2
+// pair.  The product is exact in FP16 (2 + 4 significant bits, between 2^-10 and 2688), so
+// FP16 -> FP32 -> BF16 rounds nothing.
+__device__ __forceinline__ void cvt_e2m1x8_scaled(uint32_t w, uint32_t sc, uint32_t (&out)[4]) {
+  uint32_t v[4];
+  cvt_e2m1x8_f16(w, v);
   const __half2 s2 = *reinterpret_cast<const __half2*>(&sc);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
