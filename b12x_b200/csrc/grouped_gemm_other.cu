@@ -22,18 +22,19 @@
 // Power-of-two (E8M0) scales exceed the FP16 range; for them the code values are re-encoded first and
 // multiplied by the scale in BF16.
 //
-// What bounds it now is shared-memory bandwidth (128 bytes per clock): per k-block the MMAs read
-// 48 KiB of operands, the TMA writes 26 KiB, the converters read 10 KiB and write 32 KiB, about
-// 930 clocks against 544 clocks of tensor-pipe time.  Measured with the conversion removed
-// (timing only) the kernel takes 76 % of its time, without the token-row loads as well 70 %;
-// ring depths (3 / 4 / 6 load stages, 2 / 3 / 4 converted tiles) and sixteen converter warps
-// that take alternate k-blocks (W4A16_CONV_GROUPS=2) change nothing.  The way further is the
-// weights as the TMEM-resident operand of the MMA (written by tcgen05.st, never through shared
-// memory), which halves that traffic.
+// Where the time goes is not settled.  Shared memory is busy (per k-block the MMAs read 48 KiB of
+// operands, the TMA writes 26 KiB, the converters read 10 KiB and write 32 KiB: about 930 of the
+// ~1400 clocks a k-block takes, against 544 clocks of tensor-pipe time), but the FC2 kernel at the
+// end of this file, which keeps the weights out of shared memory altogether, is no faster.  With
+// the conversion removed (timing only) the kernel takes 76 % of its time, without the token-row
+// loads as well 70 %; ring depths (3 / 4 / 6 load stages, 2 / 3 / 4 converted tiles) and sixteen
+// converter warps that take alternate k-blocks (W4A16_CONV_GROUPS=2) change nothing.
 //
 // Numerics follow the reference's W4A16 oracle (tests/_reference/w4a16_reference.py:266-359):
 // weights de-quantised then held in BF16, x in BF16, FP32 accumulation, activation in FP32, BF16
 // intermediate.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -560,6 +561,357 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// FC2 with the weights as the TENSOR-MEMORY operand of the MMA.
+//
+// Operand roles swapped against the kernel above: the tile is 128 weight rows (output features,
+// the MMA's M) x the 128 token rows of one row tile (the MMA's N).  The converter warps write the
+// expanded weights straight into tensor memory (tcgen05.st: lane = weight row, eight 32-bit columns
+// = sixteen BF16 values of K per MMA), so they are neither written to nor re-read from shared
+// memory; per k-block shared memory sees 16 KiB of token rows written and read once, 4 KiB of
+// codes and one scale atom.  Opt-in (B200MOE_W4A16_TS=1): it passes the same parity tests and, as
+// measured on the Qwen3-shaped workload, runs FC2 in 0.80 ms against 0.77 ms for the kernel above
+// - shared-memory traffic is therefore not what holds either back.  Unchanged by: 6 or 10 token
+// stages, sixteen converter warps on alternate k-blocks, one commit per k-block instead of two,
+// the epilogue's stores removed, the MMA thread not waiting for the token rows.
+//
+// Tensor memory: columns 0..255 two 128-column accumulators (the epilogue of a tile runs under the
+// main loop of the next), columns 256..511 a ring of eight 32-column slots of converted weights.
+// Accumulator lanes are output features and columns tokens, so a warp's store of one accumulator
+// column is 128 contiguous bytes of a routed row.
+namespace ts {
+
+#ifndef W4A16_TS_TOK_STAGES
+#define W4A16_TS_TOK_STAGES 6
+#endif
+#ifndef W4A16_TS_GROUPS
+#define W4A16_TS_GROUPS 1
+#endif
+constexpr int kTokStages = W4A16_TS_TOK_STAGES;   // token rows + scale atom of one k-block
+constexpr int kRawStages = 3;                // packed codes of four k-blocks
+constexpr int kASlots = 8;                   // converted weights in tensor memory, one k-block each
+constexpr int kGroups = W4A16_TS_GROUPS;     // groups of 8 converter warps taking alternate k-blocks
+constexpr int kCvtWarps = 8 * kGroups;
+constexpr int kCodesWarp = 2 + kCvtWarps + 8;        // its own warp: see the producers
+constexpr int kThreads = (kCodesWarp + 1) * 32;      // TMA, MMA, converter warps, 8 epilogue warps, codes TMA
+constexpr int kSmemTok = 128 * 128;
+constexpr int kSmemAtom = 512;
+constexpr int kSmemCodes = 128 * 128;
+constexpr int kAccCols = 128;
+constexpr int kSlotCols = 32;
+
+struct __align__(8) SmemTail {
+  uint64_t full[kTokStages];     // token rows and scale atom landed
+  uint64_t empty[kTokStages];    // 8 converter warps (scale atom) + the MMAs that read the rows
+  uint64_t rfull[kRawStages];
+  uint64_t rempty[kRawStages];   // 8 converter warps
+  uint64_t afull[kASlots];       // 8 converter warps wrote the slot
+  uint64_t aempty[kASlots];      // the MMAs that read the slot retired
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int32_t tile_base[kMaxExperts + 1];
+};
+constexpr int kSmemBytes = 1024 + kTokStages * (kSmemTok + kSmemAtom) + kRawStages * kSmemCodes +
+                           static_cast<int>(sizeof(SmemTail));
+
+// D[tmem] (+)= A[tmem] * B[smem], kind::f16
+__device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm2_w4a16_ts_kernel(const __grid_constant__ CUtensorMap tmTok,
+                              const __grid_constant__ CUtensorMap tmW, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sTok = smem;
+  uint8_t* sCodes = sTok + kTokStages * kSmemTok;
+  uint8_t* sAtom = sCodes + kRawStages * kSmemCodes;
+  SmemTail* tail = reinterpret_cast<SmemTail*>(sAtom + kTokStages * kSmemAtom);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTokStages; ++s) {
+      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->empty[s], 9);
+    }
+    for (int r = 0; r < kRawStages; ++r) {
+      mbar_init(&tail->rfull[r], 1);
+      mbar_init(&tail->rempty[r], kCvtWarps);
+    }
+    for (int a = 0; a < kASlots; ++a) {
+      mbar_init(&tail->afull[a], 8);
+      mbar_init(&tail->aempty[a], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tail->tmem_full[b], 1);
+      mbar_init(&tail->tmem_empty[b], 8);
+    }
+    tail->abort_flag = 0;
+    fence_mbar_init();
+  }
+  for (int i = threadIdx.x; i <= p.E; i += blockDim.x) tail->tile_base[i] = p.tile_base[i];
+  if (warp == 1) {
+    tmem_alloc(&tail->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  const uint32_t tmem_base = tail->tmem_base;
+  volatile int* abort_flag = &tail->abort_flag;
+  const int total_work = tail->tile_base[p.E] * p.n_tiles;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producers -----------------------------
+    // One thread brings the token rows and the scale atom of every k-block; the packed codes
+    // (every fourth k-block) have a warp of their own (below): two lanes of ONE warp that wait
+    // on different barriers hold each other up, a lane parked in its wait keeps the other from
+    // running when its barrier fires.
+    if (lane == 0) {
+      tma_prefetch_desc(&tmTok);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
+        const int row0 = p.mtile_row0[c.mt];
+        const uint8_t* sf_e = p.sf + (static_cast<size_t>(c.e) * p.sf_rowgroups + c.nt) * p.atoms_k * 512;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status, WAIT_SMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint64_t* bar = &tail->full[stage];
+          mbar_expect_tx(bar, kSmemTok + kSmemAtom);
+          tma_load_2d(sTok + stage * kSmemTok, &tmTok, bar, kb * kKPerStage, row0);
+          bulk_load(sAtom + stage * kSmemAtom, sf_e + static_cast<size_t>(kb) * 512, 512, bar);
+          if (++stage == kTokStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == kCodesWarp) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmW);
+      int rs = 0;
+      uint32_t rphase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
+        const int r0 = c.nt * 128;                           // first weight row of the tile
+        for (int kb = 0; kb < p.k_blocks; kb += kKBlocksPerRaw) {
+          if (!mbar_wait_bounded(&tail->rempty[rs], rphase ^ 1, abort_flag, p.status, WAIT_SMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&tail->rfull[rs], kSmemCodes);
+          tma_load_2d(sCodes + rs * kSmemCodes, &tmW, &tail->rfull[rs], kb * 32, c.e * p.w_rows + r0);
+          if (++rs == kRawStages) {
+            rs = 0;
+            rphase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, 128);
+      int stage = 0, slot = 0;
+      uint32_t phase = 0, aphase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int buf = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        if (!mbar_wait_bounded(&tail->tmem_empty[buf], acc_phase[buf] ^ 1, abort_flag, p.status,
+                               WAIT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * kAccCols;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL) ||
+              !mbar_wait_bounded(&tail->afull[slot], aphase, abort_flag, p.status, WAIT_CONVERT)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t bdesc = make_desc_sw128(smem_u32(sTok + stage * kSmemTok));
+          const uint32_t a_tmem = tmem_base + 2 * kAccCols + slot * kSlotCols;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)   // 16 values of K per MMA: 8 columns of the slot, 32 bytes of a token row
+            mma_bf16_ts(d_tmem, a_tmem + 8 * j, bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          tc_commit(&tail->empty[stage]);
+          tc_commit(&tail->aempty[slot]);
+          if (++stage == kTokStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+          if (++slot == kASlots) {
+            slot = 0;
+            aphase ^= 1;
+          }
+        }
+        if (ok) tc_commit(&tail->tmem_full[buf]);
+        acc_phase[buf] ^= 1;
+        buf ^= 1;
+      }
+    }
+  } else if (warp < 2 + kCvtWarps) {
+    // ------------------------------ converters --------------------------------
+    // A warp may touch the 32 tensor-memory lanes of its sub-partition (warp % 4): thread = one
+    // weight row; the two warps of a sub-partition take the two halves (32 values) of the k-block.
+    const int sub = warp & 3, khalf = ((warp - 2) >> 2) & 1, group = (warp - 2) >> 3;
+    int it = 0;
+    const int row = sub * 32 + lane;
+    const uint32_t atom_off = static_cast<uint32_t>(row & 31) * 16u + static_cast<uint32_t>(row >> 5) * 4u;
+    int stage = 0, slot = 0, rs = 0;
+    uint32_t phase = 0, aphase = 0, rphase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+      for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+        if (kGroups == 1 || it % kGroups == group) {
+        if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_CONVERT) ||
+            !mbar_wait_bounded(&tail->rfull[rs], rphase, abort_flag, p.status, WAIT_CONVERT) ||
+            !mbar_wait_bounded(&tail->aempty[slot], aphase ^ 1, abort_flag, p.status, WAIT_CONVERT)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const int chunk = (kb & (kKBlocksPerRaw - 1)) * 2 + khalf;      // 16 bytes = 32 codes
+        const uint4 cw = *reinterpret_cast<const uint4*>(sCodes + rs * kSmemCodes + row * 128 +
+                                                         ((chunk ^ (row & 7)) << 4));
+        const uint32_t sfw = *reinterpret_cast<const uint32_t*>(sAtom + stage * kSmemAtom + atom_off);
+        const uint32_t sf2 = (sfw >> (16 * khalf)) & 0xffffu;            // this half's two scale bytes
+        const uint32_t words[4] = {cw.x, cw.y, cw.z, cw.w};
+        uint32_t r[16];
+        if (!p.sf_e8m0) {
+          uint32_t s01, unused;
+          cvt_e4m3x4_f16(sf2, s01, unused);
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk) {
+            const uint32_t sc = __byte_perm(s01, 0u, blk ? 0x3232u : 0x1010u);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t o[4];
+              cvt_e2m1x8_scaled(words[blk * 2 + h], sc, o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) r[(blk * 2 + h) * 4 + j] = o[j];
+            }
+          }
+        } else {
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk) {
+            const uint32_t sb = (sf2 >> (8 * blk)) & 0xffu;
+            const float sv = __uint_as_float(sb != 0u ? sb << 23 : 0x00400000u);
+            const __nv_bfloat16 s = __float2bfloat16_rn(sv);
+            const __nv_bfloat162 sc = __halves2bfloat162(s, s);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t o[4];
+              cvt_e2m1x8_bf16(words[blk * 2 + h], sc, o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) r[(blk * 2 + h) * 4 + j] = o[j];
+            }
+          }
+        }
+        tc_st_32x32b_x16(tmem_base + 2 * kAccCols + slot * kSlotCols + khalf * 16 +
+                             (static_cast<uint32_t>(sub * 32) << 16),
+                         r);
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&tail->afull[slot]);
+          mbar_arrive(&tail->empty[stage]);
+        }
+        }
+        if ((kb & (kKBlocksPerRaw - 1)) == kKBlocksPerRaw - 1 || kb == p.k_blocks - 1) {
+          if (lane == 0) mbar_arrive(&tail->rempty[rs]);
+          if (++rs == kRawStages) {
+            rs = 0;
+            rphase ^= 1;
+          }
+        }
+        if (++stage == kTokStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+        if (++slot == kASlots) {
+          slot = 0;
+          aphase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    // lane = output feature, accumulator column = token of the row tile
+    const int sub = warp & 3;
+    const int half = (warp - 2 - kCvtWarps) >> 2;
+    uint32_t acc_phase[2] = {0, 0};
+    int buf = 0;
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+      const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
+      const int row0 = p.mtile_row0[c.mt];
+      const int nrows = p.mtile_rows[c.mt];
+      const float alpha = p.alphas[c.e];
+      if (!mbar_wait_bounded(&tail->tmem_full[buf], acc_phase[buf], abort_flag, p.status, WAIT_TMEM_FULL))
+        break;
+      acc_phase[buf] ^= 1;
+      tc_fence_after();
+      const uint32_t t_lane = tmem_base + buf * kAccCols + (static_cast<uint32_t>(sub * 32) << 16);
+      const int feature = c.nt * 128 + sub * 32 + lane;
+      const bool valid = feature < p.out_cols;
+      float* ocol = p.out_f32 + static_cast<size_t>(row0) * p.out_cols + feature;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        const int tok0 = half * 64 + ch * 16;
+        if (tok0 >= nrows) break;                            // warp-uniform
+        uint32_t rr2[16];
+        tc_ld_32x32b_x16(t_lane + tok0, rr2);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (valid && tok0 + i < nrows)
+            ocol[static_cast<size_t>(tok0 + i) * p.out_cols] = __fmul_rn(__uint_as_float(rr2[i]), alpha);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
+      buf ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace ts
+
 // x rows -> sorted-position order (the A operand of FC1), one warp per row
 __global__ void __launch_bounds__(256) permute_rows_bf16_kernel(
     const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, const int32_t* __restrict__ expert_offsets,
@@ -736,6 +1088,19 @@ int w4a16_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
   p.sub0_base = 0;
   p.sub1_base = 128;
   const int grid = a->num_sms > 0 ? a->num_sms : sm_count();
+  static const bool use_ts = [] {
+    const char* e = getenv("B200MOE_W4A16_TS");             // 1: weights as the tensor-memory operand
+    return e != nullptr && atoi(e) != 0;
+  }();
+  if (use_ts) {
+    // weights as the tensor-memory operand: tiles of 128 output features
+    p.n_tiles = ceil_div_i(K, 128);
+    if (cudaFuncSetAttribute(ts::grouped_gemm2_w4a16_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             ts::kSmemBytes) != cudaSuccess)
+      return B200MOE_ECUDA;
+    ts::grouped_gemm2_w4a16_ts_kernel<<<grid, ts::kThreads, ts::kSmemBytes, stream>>>(tmA, tmW, p);
+    return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+  }
   return launch<EPI_FC2>(tmA, tmW, p, grid, stream);
 }
 
