@@ -45,6 +45,44 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+
+// ---- per-role timeline (debug builds only: -DB200MOE_TIMELINE) -------------------------------
+// One CTA's roles stamp the SM clock at every pipeline event of a window of k-blocks / tiles into
+// a buffer the host registered with b200moe_debug_set_timeline: [kernel 2][cta 2][event 16][kTlN].
+// The product build compiles none of this.
+#ifdef B200MOE_TIMELINE
+constexpr int kTlN = 96;          // k-blocks (or tiles) recorded per event
+constexpr int kTlSkip = 160;      // k-blocks skipped first (steady state)
+constexpr int kTlSkipTiles = 8;
+enum TlEvent : int {
+  TL_P_EMPTY = 0, TL_P_ISSUED = 1, TL_M_FULL = 2, TL_M_SF = 3, TL_M_COMMIT = 4, TL_S_LANDED = 5,
+  TL_S_DONE = 6, TL_S_SLOTFREE = 7, TL_M_TMEM_EMPTY = 8, TL_E_FULL = 9, TL_E_RELEASED = 10, TL_E_DONE = 11,
+  TL_M_MMA0 = 13, TL_M_ISSUED = 14, TL_M_PEEKED = 15,
+  TL_O_LANDED = 12   // an otherwise idle lane that watches the stage's `full` barrier
+};
+static __device__ long long* g_timeline = nullptr;   // one per translation unit
+__device__ __forceinline__ long long sm_clock() {
+  long long t;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
+  return t;
+}
+// `buf` = this role's copy of the buffer pointer (null: this CTA is not recorded), read once at
+// the top of the role so that a stamp costs one clock read and one store
+__device__ __forceinline__ void tl_stamp(long long* buf, int kernel, int slot, int ev, int n, int skip) {
+  if (buf == nullptr || n < skip || n >= skip + kTlN) return;
+  buf[((kernel * 2 + slot) * 16 + ev) * kTlN + (n - skip)] = sm_clock();
+}
+#define TL_STAGE(kernel, slot, ev, n) tl_stamp(tl_buf, kernel, slot, ev, n, kTlSkip)
+#define TL_TILE(kernel, slot, ev, n) tl_stamp(tl_buf, kernel, slot, ev, n, kTlSkipTiles)
+#define TL_DECL(x) int x = 0
+#define TL_INC(x) (++(x))
+#else
+#define TL_STAGE(kernel, slot, ev, n) ((void)0)
+#define TL_TILE(kernel, slot, ev, n) ((void)0)
+#define TL_DECL(x) ((void)0)
+#define TL_INC(x) ((void)0)
+#endif
+
 // ---- mbarrier ---------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -71,6 +109,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Non-suspending look at a barrier phase (try_wait may park the thread for a while).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}\n"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)

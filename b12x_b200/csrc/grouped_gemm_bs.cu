@@ -48,7 +48,6 @@ struct __align__(8) GemmSmemTail {
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t sf_landed[kMaxStages]; // scale atoms of the stage are in shared memory
-  uint64_t sf_full[kMaxStages];   // scale atoms of the stage are in TMEM
   uint32_t tmem_base;
   int abort_flag;
   int32_t tile_base[kMaxExperts + 1];
@@ -83,10 +82,9 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->full[s], 1 + 4);   // the producer's arrive + the four scale warps
       mbar_init(&tail->empty[s], 1);
       mbar_init(&tail->sf_landed[s], 1);
-      mbar_init(&tail->sf_full[s], 4);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tail->tmem_full[b], 1);
@@ -109,6 +107,11 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
   const uint32_t tmem_base = tail->tmem_base;
   volatile int* abort_flag = &tail->abort_flag;
   const int total_work = tail->tile_base[p.E] * p.n_tiles;
+#ifdef B200MOE_TIMELINE
+  const int tl_slot = blockIdx.x == 0 ? 0 : (blockIdx.x == gridDim.x / 2 + 1 ? 1 : -1);
+  constexpr int tl_k = EPI == EPI_FC2 ? 1 : 0;
+  long long* const tl_buf = tl_slot >= 0 ? g_timeline : nullptr;
+#endif
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -126,6 +129,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      TL_DECL(tl_n);
       // Where this lane's copy of tile `w` comes from.  Tiles of a decode batch hold a few rows:
       // they fetch 32 activation rows instead of 128 (the other rows of the shared-memory tile
       // keep stale data; MMA rows are independent).  A gated tile is BN/128 pair groups: box 2g =
@@ -175,11 +179,11 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         const int my_row_y = src.y;
         const uint8_t* my_sf = src.sf;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status,
-                                 WAIT_SMEM_EMPTY)) {
+          if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status, WAIT_SMEM_EMPTY)) {
             ok = false;
             break;
           }
+          if (lane == 0) TL_STAGE(tl_k, tl_slot, TL_P_EMPTY, tl_n);
           const int ksteps = min(4, (p.kdim - kb * kPerStage) / kPerMma);
           // NVFP4: one scale atom per MMA step; MX: one atom covers the whole stage
           const uint32_t sf_bytes = KIND == KIND_MX ? 512u : static_cast<uint32_t>(ksteps) * 512u;
@@ -201,6 +205,8 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
           } else {
             bulk_load(sSfb + stage * kSmemSfb + (lane - kBoxes - 2) * 2048, my_sf + sf_off, sf_bytes, sf_bar);
           }
+          if (lane == 0) TL_STAGE(tl_k, tl_slot, TL_P_ISSUED, tl_n);
+          TL_INC(tl_n);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -212,6 +218,23 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         for (int i = 0; i < 1000; ++i) __nanosleep(1000);
       }
     }
+#ifdef B200MOE_TIMELINE
+    else if (lane == 31 && tl_buf != nullptr) {
+      // observer: when did the operand rows of each stage land?
+      int stage = 0, n = 0;
+      uint32_t phase = 0;
+      for (int w = blockIdx.x; w < total_work && n < kTlSkip + kTlN; w += gridDim.x) {
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++n) {
+          if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, nullptr, 0)) break;
+          TL_STAGE(tl_k, tl_slot, TL_O_LANDED, n);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+#endif
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
@@ -224,51 +247,53 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t acc_phase[2] = {0, 0};
       int buf = 0;
       bool ok = true;
+      TL_DECL(tl_n);
+      TL_DECL(tl_t);
       for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
         if (!mbar_wait_bounded(&tail->tmem_empty[buf], acc_phase[buf] ^ 1, abort_flag, p.status,
                                WAIT_TMEM_EMPTY)) {
           ok = false;
           break;
         }
+        TL_TILE(tl_k, tl_slot, TL_M_TMEM_EMPTY, tl_t);
+        TL_INC(tl_t);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
+          // one barrier per stage: the operand rows have landed (TMA byte count) and the four scale
+          // warps have put the stage's scale atoms into TMEM (their arrivals)
           if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL)) {
             ok = false;
             break;
           }
+          TL_STAGE(tl_k, tl_slot, TL_M_FULL, tl_n);
+          TL_STAGE(tl_k, tl_slot, TL_M_SF, tl_n);
           tc_fence_after();
           const int ksteps = min(4, (p.kdim - kb * kPerStage) / kPerMma);
-          // the scale-copy warp has put this stage's scale atoms into TMEM
-          if (!mbar_wait_bounded(&tail->sf_full[stage], phase, abort_flag, p.status, WAIT_SF_FULL)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
           const uint32_t sfa_t = tmem_base + kTmemSf + stage * Cfg::kSfCols;
           const uint32_t sfb_t = sfa_t + 16;
           const uint64_t adesc = make_desc_sw128(smem_u32(sA + stage * kSmemA));
           const uint64_t bdesc = make_desc_sw128(smem_u32(sB + stage * kSmemB));
-          if (KIND == KIND_MX) {
-            // one atom = the four per-32 scales of this stage; MMA step j uses byte j of each word
-            for (int j = 0; j < ksteps; ++j) {
-              const uint32_t ju = static_cast<uint32_t>(j);
+          const int nstage = stage + 1 == kStages ? 0 : stage + 1;
+          const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
+          for (int j = 0; j < ksteps; ++j) {
+            if (KIND == KIND_MX) {
+              // one atom = the four per-32 scales of this stage; MMA step j uses byte j of each word;
               // 32 one-byte slots further along the swizzled row -> +2 in 16-byte units
+              const uint32_t ju = static_cast<uint32_t>(j);
               mma_mxf8f6f4(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc | (ju << 29) | (ju << 4),
                            sfa_t + (ju << 30), sfb_t + (ju << 30), (kb > 0 || j > 0) ? 1u : 0u);
-            }
-          } else {
-            for (int j = 0; j < ksteps; ++j) {
+            } else {
               // 64 FP4 values = 32 bytes further along the swizzled row -> +2 in 16-byte units
               mma_nvf4_4x(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j,
                           sfb_t + kSfbStep * j, (kb > 0 || j > 0) ? 1u : 0u);
             }
           }
           tc_commit(&tail->empty[stage]);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1;
-          }
+          TL_STAGE(tl_k, tl_slot, TL_M_COMMIT, tl_n);
+          TL_INC(tl_n);
+          stage = nstage;
+          phase = nphase;
         }
         if (ok) tc_commit(&tail->tmem_full[buf]);
         acc_phase[buf] ^= 1;
@@ -287,12 +312,14 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    TL_DECL(tl_n);
     for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         if (!mbar_wait_bounded(&tail->sf_landed[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL)) {
           ok = false;
           break;
         }
+        if (warp == 10 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_LANDED, tl_n);
         const uint32_t sfa_t =
             tmem_base + kTmemSf + stage * Cfg::kSfCols + (static_cast<uint32_t>(sub * 32) << 16);
         const uint32_t sfb_t = sfa_t + 16;
@@ -312,7 +339,9 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tail->sf_full[stage]);
+        if (lane == 0) mbar_arrive(&tail->full[stage]);
+        if (warp == 10 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_DONE, tl_n);
+        TL_INC(tl_n);
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1;
@@ -328,19 +357,24 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
     const int m = sub * 32 + lane;            // tile row = TMEM lane
     uint32_t acc_phase[2] = {0, 0};
     int buf = 0;
+    TL_DECL(tl_t);
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
       const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
       const int row0 = p.mtile_row0[c.mt];
       const int nrows = p.mtile_rows[c.mt];
       if (!mbar_wait_bounded(&tail->tmem_full[buf], acc_phase[buf], abort_flag, p.status,
-                             WAIT_TMEM_FULL))
+                          WAIT_TMEM_FULL))
         break;
+      if (warp == 2 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_FULL, tl_t);
       acc_phase[buf] ^= 1;
       tc_fence_after();
       const uint32_t t_lane = tmem_base + buf * BN + (static_cast<uint32_t>(sub * 32) << 16);
       epilogue_tile<KIND, EPI, BN>(p, c.e, c.mt, c.nt, row0, nrows, t_lane, m, half, lane, [&]() {
         if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
+        if (warp == 2 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_RELEASED, tl_t);
       });
+      if (warp == 2 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_DONE, tl_t);
+      TL_INC(tl_t);
       if (Cfg::kBufs == 2) buf ^= 1;
     }
   }
@@ -564,3 +598,11 @@ int mx_gemm1(const b200moe_gemm_args* a, cudaStream_t s) { return gemm1_any<KIND
 int mx_gemm2(const b200moe_gemm_args* a, cudaStream_t s) { return gemm2_any<KIND_MX>(a, s); }
 
 }  // namespace b200moe
+
+#ifdef B200MOE_TIMELINE
+// Debug builds only: register the device buffer ([2][2][16][96] int64) the timeline stamps go to.
+extern "C" int b200moe_debug_set_timeline(void* device_buffer) {
+  long long* ptr = static_cast<long long*>(device_buffer);
+  return cudaMemcpyToSymbol(b200moe::g_timeline, &ptr, sizeof(ptr)) == cudaSuccess ? 0 : -3;
+}
+#endif

@@ -42,7 +42,6 @@ struct __align__(8) SmemTail {
   uint64_t empty[kStages];      // per CTA: the MMAs that read the stage have retired
   uint64_t sf_landed[kSfSlots]; // per CTA: the slot's scale atoms are in this CTA's shared memory
   uint64_t sf_empty[kSfSlots];  // per CTA: the four scale warps have read the slot
-  uint64_t sf_full[kStages];    // even CTA: both CTAs' scale atoms are in tensor memory
   uint64_t tmem_full;           // per CTA: the accumulator is complete
   uint64_t tmem_empty;          // even CTA: all 16 epilogue warps of the pair have drained it
   uint32_t tmem_base;
@@ -152,9 +151,8 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->full[s], 1 + 8);   // the producer's arrive + the scale warps of both CTAs
       mbar_init(&tail->empty[s], 1);
-      mbar_init(&tail->sf_full[s], 8);
     }
     for (int s = 0; s < kSfSlots; ++s) {
       mbar_init(&tail->sf_landed[s], 1);
@@ -187,6 +185,11 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
   const uint32_t tmem_base = tail->tmem_base;
   volatile int* abort_flag = &tail->abort_flag;
   const int total_work = tail->pair_base[p.E] * p.n_tiles;
+#ifdef B200MOE_TIMELINE
+  const int tl_slot = cluster_id == 0 ? rank : -1;
+  constexpr int tl_k = EPI == EPI_FC2 ? 1 : 0;
+  long long* const tl_buf = tl_slot >= 0 ? g_timeline : nullptr;
+#endif
 
   if (warp == 0) {
     // ------------------------------ operand producer (both CTAs) -----------------
@@ -200,6 +203,7 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      TL_DECL(tl_n);
       for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
         const PairCoord c = decode_pair(w, p, tail, rank);
         int y;                          // row coordinate of this lane's copy
@@ -223,6 +227,7 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
             ok = false;
             break;
           }
+          if (lane == 0) TL_STAGE(tl_k, tl_slot, TL_P_EMPTY, tl_n);
           const uint32_t bar = map_to_cta(smem_u32(&tail->full[stage]), 0);
           if (lane == 0) {
             if (rank == 0) mbar_expect_tx(&tail->full[stage], kStageTxBytes);
@@ -230,6 +235,8 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           } else {
             tma_load_2d_pair(sB + stage * kSmemB + (lane - 1) * 64 * kRowBytes, &tmB, bar, kb * kRowBytes, y);
           }
+          if (lane == 0) TL_STAGE(tl_k, tl_slot, TL_P_ISSUED, tl_n);
+          TL_INC(tl_n);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -240,6 +247,22 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         for (int i = 0; i < 1000; ++i) __nanosleep(1000);   // let copies in flight land
       }
     }
+#ifdef B200MOE_TIMELINE
+    else if (lane == 31 && tl_buf != nullptr && rank == 0) {
+      int stage = 0, n = 0;
+      uint32_t phase = 0;
+      for (int w = cluster_id; w < total_work && n < kTlSkip + kTlN; w += num_clusters) {
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++n) {
+          if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, nullptr, 0)) break;
+          TL_STAGE(tl_k, tl_slot, TL_O_LANDED, n);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+#endif
   } else if (warp == 14) {
     // ------------------------------ scale-atom producer (both CTAs) --------------
     // The scale atoms travel through a ring of their own that is deeper than the operand stages:
@@ -292,32 +315,43 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       int stage = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
+      TL_DECL(tl_n);
+      TL_DECL(tl_t);
       for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
         if (!mbar_wait_bounded(&tail->tmem_empty, acc_phase ^ 1, abort_flag, p.status, WAIT_TMEM_EMPTY)) {
           ok = false;
           break;
         }
+        TL_TILE(tl_k, tl_slot, TL_M_TMEM_EMPTY, tl_t);
+        TL_INC(tl_t);
         tc_fence_after();
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL) ||
-              !mbar_wait_bounded(&tail->sf_full[stage], phase, abort_flag, p.status, WAIT_SF_FULL)) {
+          // one barrier per stage: both CTAs' operand rows have landed (TMA byte count) and their
+          // eight scale warps have put the scale atoms into tensor memory (their arrivals)
+          if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL)) {
             ok = false;
             break;
           }
+          TL_STAGE(tl_k, tl_slot, TL_M_SF, tl_n);
           tc_fence_after();
           const int ksteps = min(4, (p.kdim - kb * 256) / 64);
           const uint32_t sfa_t = tmem_base + kTmemSf + stage * kSfCols;
           const uint32_t sfb_t = sfa_t + 16;
           const uint64_t adesc = make_desc_sw128(smem_u32(sA + stage * kSmemA));
           const uint64_t bdesc = make_desc_sw128(smem_u32(sB + stage * kSmemB));
-          for (int j = 0; j < ksteps; ++j)
+          const int nstage = stage + 1 == kStages ? 0 : stage + 1;
+          const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
+          for (int j = 0; j < ksteps; ++j) {
             mma_nvf4_4x_pair(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j, sfb_t + 8 * j,
                              (kb > 0 || j > 0) ? 1u : 0u);
-          tc_commit_pair_both(&tail->empty[stage]);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1;
+            if (j == 0) TL_STAGE(tl_k, tl_slot, TL_M_MMA0, tl_n);
           }
+          TL_STAGE(tl_k, tl_slot, TL_M_ISSUED, tl_n);
+          tc_commit_pair_both(&tail->empty[stage]);
+          TL_STAGE(tl_k, tl_slot, TL_M_COMMIT, tl_n);
+          TL_INC(tl_n);
+          stage = nstage;
+          phase = nphase;
         }
         if (ok) tc_commit_pair_both(&tail->tmem_full);
         acc_phase ^= 1;
@@ -334,13 +368,19 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
     int stage = 0, slot = 0;
     uint32_t phase = 0, sphase = 0;
     bool ok = true;
+    TL_DECL(tl_n);
     for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        if (!mbar_wait_bounded(&tail->sf_landed[slot], sphase, abort_flag, p.status, WAIT_SMEM_FULL) ||
-            !mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status, WAIT_SMEM_EMPTY)) {
+        if (!mbar_wait_bounded(&tail->sf_landed[slot], sphase, abort_flag, p.status, WAIT_SMEM_FULL)) {
           ok = false;
           break;
         }
+        if (warp == 10 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_LANDED, tl_n);
+        if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status, WAIT_SMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        if (warp == 10 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_SLOTFREE, tl_n);
         tc_fence_after();
         const uint32_t sfa_t = tmem_base + kTmemSf + stage * kSfCols + (static_cast<uint32_t>(sub * 32) << 16);
         const uint32_t sfb_t = sfa_t + 16;
@@ -353,8 +393,10 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(&tail->sf_empty[slot]);
-          mbar_arrive_cluster(map_to_cta(smem_u32(&tail->sf_full[stage]), 0));
+          mbar_arrive_cluster(map_to_cta(smem_u32(&tail->full[stage]), 0));
         }
+        if (warp == 10 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_DONE, tl_n);
+        TL_INC(tl_n);
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1;
@@ -372,16 +414,21 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
     const int m = sub * 32 + lane;
     const uint32_t release_addr = map_to_cta(smem_u32(&tail->tmem_empty), 0);
     uint32_t acc_phase = 0;
+    TL_DECL(tl_t);
     for (int w = cluster_id; w < total_work; w += num_clusters) {
       const PairCoord c = decode_pair(w, p, tail, rank);
       const int row0 = p.mtile_row0[c.mt_load];
       if (!mbar_wait_bounded(&tail->tmem_full, acc_phase, abort_flag, p.status, WAIT_TMEM_FULL)) break;
+      if (warp == 2 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_FULL, tl_t);
       acc_phase ^= 1;
       tc_fence_after();
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(sub * 32) << 16);
       epilogue_tile<KIND_NVFP4, EPI, 256>(p, c.e, c.mt_load, c.nt, row0, c.rows, t_lane, m, half, lane, [&]() {
         if (lane == 0) mbar_arrive_cluster(release_addr);
+        if (warp == 2 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_RELEASED, tl_t);
       });
+      if (warp == 2 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_DONE, tl_t);
+      TL_INC(tl_t);
     }
   }
 
@@ -504,3 +551,11 @@ int nvfp4_pair_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
 }
 
 }  // namespace b200moe
+
+#ifdef B200MOE_TIMELINE
+// Debug builds only: the buffer the CTA-pair kernels' timeline stamps go to.
+extern "C" int b200moe_debug_set_timeline_pair(void* device_buffer) {
+  long long* ptr = static_cast<long long*>(device_buffer);
+  return cudaMemcpyToSymbol(b200moe::g_timeline, &ptr, sizeof(ptr)) == cudaSuccess ? 0 : -3;
+}
+#endif
