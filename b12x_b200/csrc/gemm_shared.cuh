@@ -176,208 +176,181 @@ __device__ __forceinline__ void store_sf(uint8_t* sf_tile, uint32_t m, uint32_t 
   else *dst = static_cast<uint8_t>(word);
 }
 
-// Epilogue of one 128 x BN accumulator tile, run by each of the eight epilogue warps: warp w may
+// Epilogue of one 128 x 256 accumulator tile, run by each of the eight epilogue warps: warp w may
 // only read TMEM sub-partition (w & 3), i.e. tile rows 32*(w&3) .. +31 (m = that row, t_lane =
 // the accumulator's TMEM address with the sub-partition's lane in the upper half); the two warps
-// that share a sub-partition split the tile's columns (half = 0 / 1).  release() is called once
-// per warp when its TMEM reads are done.  nrows == 0 (a tile that does not exist) stores nothing.
+// that share a sub-partition split the tile's columns (half = 0 / 1: columns [128*half, +128)).
+//
+// The warp first drains its 32 x 128 share of the accumulator into registers (128 per thread: the
+// kernels raise the epilogue warps' register allowance with setmaxnreg for this) and calls
+// release() -- the MMA thread may then start the next tile -- and only then does the arithmetic
+// and the stores, under the next tile's main loop.  nrows == 0 (a tile that does not exist)
+// stores nothing.
 template <int KIND, int EPI, int BN, class Release>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, int e, int mt, int nt, int row0, int nrows,
                                               uint32_t t_lane, int m, int half, int lane, Release release) {
+  static_assert(BN == 256, "the epilogue is written for 256-column tiles");
   constexpr bool kGated = EPI == EPI_FC1_GATED || EPI == EPI_FC1_SILU;
-  constexpr int kPairs = BN / 2;                  // gated: output columns per tile
-  constexpr int kGatedChunks = kPairs / 32;       // 16-column chunks per warp (gated)
-  constexpr int kPlainChunks = BN / 32;           // 16-column chunks per warp (FC2 / relu2)
+  uint32_t acc[128];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint32_t r[16];
+    tc_ld_32x32b_x16(t_lane + half * 128 + c * 16, r);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[c * 16 + i] = r[i];
+  }
+  tc_wait_ld();
+  tc_fence_before();
+  __syncwarp();
+  release();
+
   const float alpha = p.alphas[e];
   const bool valid = m < nrows;
   const size_t pos = static_cast<size_t>(row0 + m);
   uint8_t* sft = p.out_sf + static_cast<size_t>(mt) * p.out_atoms * 512;
-  if (KIND == KIND_MX && kGated) {
-    // w4a8_mx: the activation output goes straight into the MXFP8 quantiser (no bf16 staging)
-    constexpr int kBlocks = kPairs / 64;      // 32-column blocks per warp
-    constexpr int kUpCol = BN == 256 ? 128 : 32;   // TMEM column of this warp's up values, per half
-    const int col0 = nt * kPairs + half * (kPairs / 2);
-    uint8_t* qrow = p.out_q + pos * p.out_cols + col0;
-    uint32_t sfw = 0u;
+  if (kGated) {
+    // a gated tile is two pair groups; this warp's group: acc[0..63] = up, acc[64..127] = gate of
+    // the intermediate columns col0 .. col0 + 63
+    const int col0 = nt * 128 + half * 64;
     const bool cols_ok = col0 < p.out_cols;
-#pragma unroll 1
-    for (int blk = 0; blk < kBlocks; ++blk) {
-      float h[32];
-#pragma unroll
-      for (int c2 = 0; c2 < 2; ++c2) {
-        uint32_t ru[16], rg[16];
-        tc_ld_32x32b_x16(t_lane + half * kUpCol + blk * 32 + c2 * 16, ru);
-        tc_ld_32x32b_x16(t_lane + half * kUpCol + 64 + blk * 32 + c2 * 16, rg);
-        tc_wait_ld();
-        float up[16], gate[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          up[i] = __fmul_rn(__uint_as_float(ru[i]), alpha);
-          gate[i] = __fmul_rn(__uint_as_float(rg[i]), alpha);
-        }
-        if (p.tap != nullptr && valid && cols_ok) {
-          float* trow = p.tap + pos * p.w_rows + col0 + blk * 32 + c2 * 16;
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            trow[p.sub0_base + i] = up[i];
-            trow[p.sub1_base + i] = gate[i];
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-          h[c2 * 16 + i] = act_gated<EPI == EPI_FC1_GATED>(gate[i], up[i], p);
-      }
-      uint32_t o[8];
-      uint8_t sfb;
-      requant_block32_mx(h, o, sfb);
-      if (valid && cols_ok) {
-        uint4* dst = reinterpret_cast<uint4*>(qrow + blk * 32);
-        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-      }
-      sfw |= static_cast<uint32_t>(sfb) << (8 * blk);
-    }
-    tc_fence_before();
-    __syncwarp();
-    release();
-    if (cols_ok && nrows > 0) store_sf<kBlocks>(sft, m, col0 >> 5, sfw);
-  } else if (KIND == KIND_MX && EPI == EPI_FC1_RELU2) {
-    constexpr int kBlocks = BN / 64;
-    const int col0 = nt * BN + half * (BN / 2);
-    if (col0 < p.out_cols) {
+    if (KIND == KIND_MX) {
+      // w4a8_mx: the activation output goes straight into the MXFP8 quantiser (no bf16 staging)
       uint8_t* qrow = p.out_q + pos * p.out_cols + col0;
       uint32_t sfw = 0u;
-#pragma unroll 1
-      for (int blk = 0; blk < kBlocks; ++blk) {
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
         float h[32];
 #pragma unroll
-        for (int c2 = 0; c2 < 2; ++c2) {
-          uint32_t rr[16];
-          tc_ld_32x32b_x16(t_lane + half * (BN / 2) + blk * 32 + c2 * 16, rr);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float v = __fmul_rn(__uint_as_float(rr[i]), alpha);
-            if (p.tap != nullptr && valid && col0 + blk * 32 < p.out_cols)
-              p.tap[pos * p.w_rows + col0 + blk * 32 + c2 * 16 + i] = v;
-            const float r = fmaxf(v, 0.f);
-            h[c2 * 16 + i] = __fmul_rn(r, r);
+        for (int i = 0; i < 32; ++i) {
+          const float up = __fmul_rn(__uint_as_float(acc[blk * 32 + i]), alpha);
+          const float gate = __fmul_rn(__uint_as_float(acc[64 + blk * 32 + i]), alpha);
+          if (p.tap != nullptr && valid && cols_ok) {
+            float* trow = p.tap + pos * p.w_rows + col0 + blk * 32 + i;
+            trow[p.sub0_base] = up;
+            trow[p.sub1_base] = gate;
           }
+          h[i] = act_gated<EPI == EPI_FC1_GATED>(gate, up, p);
         }
         uint32_t o[8];
         uint8_t sfb;
         requant_block32_mx(h, o, sfb);
-        if (valid && col0 + blk * 32 < p.out_cols) {
+        if (valid && cols_ok) {
           uint4* dst = reinterpret_cast<uint4*>(qrow + blk * 32);
           dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
           dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
         }
         sfw |= static_cast<uint32_t>(sfb) << (8 * blk);
       }
-      store_sf<kBlocks>(sft, m, col0 >> 5, sfw);
-    }
-    tc_fence_before();
-    __syncwarp();
-    release();
-  } else if (kGated) {
-    const float gs2 = p.gscale2[p.gscale_len > 1 ? e : 0];
-    const float rgs2 = __frcp_rn(gs2);
-    // TMEM columns of a pair group: 64 up values then the 64 gate values of the same columns
-    constexpr int kUpCol = BN == 256 ? 128 : 32;
-    const int col0 = nt * kPairs + half * (kPairs / 2);   // first intermediate column of this warp
-    uint8_t* qrow = p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1);
-    uint32_t sfw = 0u;
-#pragma unroll 2
-    for (int ch = 0; ch < kGatedChunks; ++ch) {
-      uint32_t ru[16], rg[16];
-      tc_ld_32x32b_x16(t_lane + half * kUpCol + ch * 16, ru);
-      tc_ld_32x32b_x16(t_lane + half * kUpCol + 64 + ch * 16, rg);
-      tc_wait_ld();
-      float up[16], gate[16], h[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        up[i] = __fmul_rn(__uint_as_float(ru[i]), alpha);
-        gate[i] = __fmul_rn(__uint_as_float(rg[i]), alpha);
-      }
-      if (p.tap != nullptr && valid && col0 < p.out_cols) {
-        float* trow = p.tap + pos * p.w_rows + col0 + ch * 16;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          trow[p.sub0_base + i] = up[i];
-          trow[p.sub1_base + i] = gate[i];
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < 16; ++i)
-        h[i] = round_bf16(act_gated<EPI == EPI_FC1_GATED>(gate[i], up[i], p));
-      uint32_t lo, hi;
-      uint8_t sfb;
-      requant_block16(h, gs2, rgs2, lo, hi, sfb);
-      if (valid && col0 < p.out_cols) *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
-      sfw |= static_cast<uint32_t>(sfb) << (8 * ch);
-    }
-    tc_fence_before();
-    __syncwarp();
-    release();
-    // scale atoms are per tile: padding rows are written too (their values are never used)
-    if (col0 < p.out_cols && nrows > 0) store_sf<kGatedChunks>(sft, m, col0 >> 4, sfw);
-  } else if (EPI == EPI_FC1_RELU2) {
-    const float gs2 = p.gscale2[p.gscale_len > 1 ? e : 0];
-    const float rgs2 = __frcp_rn(gs2);
-    const int col0 = nt * BN + half * (BN / 2);
-    if (col0 < p.out_cols) {
+      if (cols_ok && nrows > 0) store_sf<2>(sft, m, col0 >> 5, sfw);
+    } else {
+      const float gs2 = p.gscale2[p.gscale_len > 1 ? e : 0];
+      const float rgs2 = __frcp_rn(gs2);
       uint8_t* qrow = p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1);
-      uint32_t sfw[2] = {0u, 0u};
-#pragma unroll 1
-      for (int ch = 0; ch < kPlainChunks; ++ch) {
-        uint32_t rr[16];
-        tc_ld_32x32b_x16(t_lane + half * (BN / 2) + ch * 16, rr);
-        tc_wait_ld();
+      uint32_t sfw = 0u;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
         float h[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float v = __fmul_rn(__uint_as_float(rr[i]), alpha);
-          if (p.tap != nullptr && valid && col0 + ch * 16 < p.out_cols)
-            p.tap[pos * p.w_rows + col0 + ch * 16 + i] = v;
-          const float r = fmaxf(v, 0.f);
-          h[i] = round_bf16(__fmul_rn(r, r));
+          const float up = __fmul_rn(__uint_as_float(acc[ch * 16 + i]), alpha);
+          const float gate = __fmul_rn(__uint_as_float(acc[64 + ch * 16 + i]), alpha);
+          if (p.tap != nullptr && valid && cols_ok) {
+            float* trow = p.tap + pos * p.w_rows + col0 + ch * 16 + i;
+            trow[p.sub0_base] = up;
+            trow[p.sub1_base] = gate;
+          }
+          h[i] = round_bf16(act_gated<EPI == EPI_FC1_GATED>(gate, up, p));
         }
         uint32_t lo, hi;
         uint8_t sfb;
         requant_block16(h, gs2, rgs2, lo, hi, sfb);
-        if (valid && col0 + ch * 16 < p.out_cols)
-          *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
-        if (ch < 4) sfw[0] |= static_cast<uint32_t>(sfb) << (8 * ch);
-        else sfw[1] |= static_cast<uint32_t>(sfb) << (8 * (ch - 4));
+        if (valid && cols_ok) *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
+        sfw |= static_cast<uint32_t>(sfb) << (8 * ch);
       }
-      if (nrows > 0) store_sf<4>(sft, m, col0 >> 4, sfw[0]);
-      if (nrows > 0 && kPlainChunks == 8 && col0 + 64 < p.out_cols) store_sf<4>(sft, m, (col0 >> 4) + 4, sfw[1]);
+      // scale atoms are per tile: padding rows are written too (their values are never used)
+      if (cols_ok && nrows > 0) store_sf<4>(sft, m, col0 >> 4, sfw);
     }
-    tc_fence_before();
-    __syncwarp();
-    release();
+  } else if (EPI == EPI_FC1_RELU2) {
+    const int col0 = nt * 256 + half * 128;
+    if (col0 < p.out_cols) {
+      if (KIND == KIND_MX) {
+        uint8_t* qrow = p.out_q + pos * p.out_cols + col0;
+        uint32_t sfw = 0u;
+#pragma unroll
+        for (int blk = 0; blk < 4; ++blk) {
+          float h[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = __fmul_rn(__uint_as_float(acc[blk * 32 + i]), alpha);
+            if (p.tap != nullptr && valid && col0 + blk * 32 < p.out_cols)
+              p.tap[pos * p.w_rows + col0 + blk * 32 + i] = v;
+            const float r = fmaxf(v, 0.f);
+            h[i] = __fmul_rn(r, r);
+          }
+          uint32_t o[8];
+          uint8_t sfb;
+          requant_block32_mx(h, o, sfb);
+          if (valid && col0 + blk * 32 < p.out_cols) {
+            uint4* dst = reinterpret_cast<uint4*>(qrow + blk * 32);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          }
+          sfw |= static_cast<uint32_t>(sfb) << (8 * blk);
+        }
+        if (nrows > 0) store_sf<4>(sft, m, col0 >> 5, sfw);
+      } else {
+        const float gs2 = p.gscale2[p.gscale_len > 1 ? e : 0];
+        const float rgs2 = __frcp_rn(gs2);
+        uint8_t* qrow = p.out_q + pos * (p.out_cols >> 1) + (col0 >> 1);
+        uint32_t sfw[2] = {0u, 0u};
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          float h[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float v = __fmul_rn(__uint_as_float(acc[ch * 16 + i]), alpha);
+            if (p.tap != nullptr && valid && col0 + ch * 16 < p.out_cols)
+              p.tap[pos * p.w_rows + col0 + ch * 16 + i] = v;
+            const float r = fmaxf(v, 0.f);
+            h[i] = round_bf16(__fmul_rn(r, r));
+          }
+          uint32_t lo, hi;
+          uint8_t sfb;
+          requant_block16(h, gs2, rgs2, lo, hi, sfb);
+          if (valid && col0 + ch * 16 < p.out_cols)
+            *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
+          sfw[ch >> 2] |= static_cast<uint32_t>(sfb) << (8 * (ch & 3));
+        }
+        if (nrows > 0) store_sf<4>(sft, m, col0 >> 4, sfw[0]);
+        if (nrows > 0 && col0 + 64 < p.out_cols) store_sf<4>(sft, m, (col0 >> 4) + 4, sfw[1]);
+      }
+    }
   } else {
-    const int col0 = nt * BN + half * (BN / 2);
+    const int col0 = nt * 256 + half * 128;
     float* orow = p.out_f32 + pos * p.out_cols + col0;
-#pragma unroll 2
-    for (int ch = 0; ch < kPlainChunks; ++ch) {
-      uint32_t rr[16];
-      tc_ld_32x32b_x16(t_lane + half * (BN / 2) + ch * 16, rr);
-      tc_wait_ld();
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
       if (valid && col0 + ch * 16 < p.out_cols) {
         float4* dst = reinterpret_cast<float4*>(orow + ch * 16);
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-          dst[q] = make_float4(__fmul_rn(__uint_as_float(rr[4 * q]), alpha),
-                               __fmul_rn(__uint_as_float(rr[4 * q + 1]), alpha),
-                               __fmul_rn(__uint_as_float(rr[4 * q + 2]), alpha),
-                               __fmul_rn(__uint_as_float(rr[4 * q + 3]), alpha));
+          dst[q] = make_float4(__fmul_rn(__uint_as_float(acc[ch * 16 + 4 * q]), alpha),
+                               __fmul_rn(__uint_as_float(acc[ch * 16 + 4 * q + 1]), alpha),
+                               __fmul_rn(__uint_as_float(acc[ch * 16 + 4 * q + 2]), alpha),
+                               __fmul_rn(__uint_as_float(acc[ch * 16 + 4 * q + 3]), alpha));
       }
     }
-    tc_fence_before();
-    __syncwarp();
-    release();
   }
+}
+
+// Register allowance per warp group (the four warps of a group execute this together).
+template <int N>
+__device__ __forceinline__ void regs_release_to() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void regs_raise_to() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 // ---- host helpers (defined in grouped_gemm_bs.cu) ------------------------------------------

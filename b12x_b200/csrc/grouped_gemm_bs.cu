@@ -6,14 +6,14 @@
 //   FC2:  acc[128 x BN] = Hq . W2q[BN rows]^T ; epilogue: x alpha2 -> float32 routed rows
 //
 // One persistent CTA per SM walks the (expert, n-tile, m-tile) work list that the sort kernel left
-// in the scratch arena.  Warp 0 feeds a TMA pipeline (SWIZZLE_128B operand tiles + plain bulk
-// copies of the 512-byte scale atoms), warp 1 issues the block-scaled tcgen05.mma, warps 2..9
-// drain the TMEM accumulator, warps 10..13 move the scale atoms into TMEM with tcgen05.st.
-//
-// Two tile shapes: BN = 128 (six pipeline stages, the accumulator double-buffered in TMEM so the
-// epilogue of one tile runs under the main loop of the next) and BN = 256 (four stages, one
-// accumulator).  Every wait is bounded; a wait that runs out marks the status block and every role
-// leaves its loop.
+// in the scratch arena.  Four warp groups: warp 0 feeds a TMA pipeline (SWIZZLE_128B operand tiles +
+// plain bulk copies of the 512-byte scale atoms) and warp 1 issues the block-scaled tcgen05.mma
+// (warps 2, 3 idle); warps 4..7 move the scale atoms into TMEM with tcgen05.st; warps 8..15 are the
+// epilogue.  Tile = 128 x 256 with one accumulator (two would leave no TMEM columns for the scale
+// atoms): the epilogue warps drain it into registers first -- the first two warp groups hand most
+// of their registers to them (setmaxnreg) -- and release it, so the arithmetic and the stores of a
+// tile run under the main loop of the next.  Every wait is bounded; a wait that runs out marks the
+// status block and every role leaves its loop.
 #include <stdlib.h>
 
 #include "gemm_shared.cuh"
@@ -24,7 +24,9 @@ constexpr int kBM = 128;            // tile rows (MMA M)
 constexpr int kRowBytes = 128;      // one swizzled operand row per stage
 constexpr int kKPerStage = 256;     // nvfp4: reduction elements per stage
 constexpr int kKPerMma = 64;
-constexpr int kGemmThreads = 448;   // TMA warp, MMA warp, 8 epilogue warps, 4 scale warps
+constexpr int kGemmThreads = 512;   // four warp groups: TMA + MMA (+2 idle), 4 scale warps, 2 x 4 epilogue warps
+constexpr int kRegsSmall = 48;      // register allowance of the first two warp groups ...
+constexpr int kRegsEpilogue = 208;  // ... and of the epilogue warp groups (2 x 128 x 48 + 2 x 128 x 208 = 64 Ki)
 constexpr int kTmemCols = 512;
 constexpr int kTmemSf = 256;        // first scale column (accumulators use columns 0..255)
 constexpr int kMaxStages = 6;
@@ -33,8 +35,8 @@ constexpr int kSmemSfa = 4 * 512;              // up to 4 scale atoms per stage
 
 template <int BN>
 struct TileCfg {
-  static constexpr int kStages = BN == 128 ? 6 : 4;
-  static constexpr int kBufs = BN == 128 ? 2 : 1;       // accumulators in TMEM
+  static constexpr int kStages = 4;
+  static constexpr int kBufs = 1;                       // accumulators in TMEM
   static constexpr int kSmemB = BN * kRowBytes;
   static constexpr int kSfbChains = BN / 128;           // scale-atom chains per stage for B
   static constexpr int kSmemSfb = kSfbChains * 4 * 512;
@@ -113,6 +115,8 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
   long long* const tl_buf = tl_slot >= 0 ? g_timeline : nullptr;
 #endif
 
+  if (warp < 8) {
+  regs_release_to<kRegsSmall>();
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     // A few lanes walk the same loop and each issues ONE of the stage's copies: lane 0 arms the
@@ -300,7 +304,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         if (Cfg::kBufs == 2) buf ^= 1;
       }
     }
-  } else if (warp >= 10) {
+  } else if (warp >= 4 && warp < 8) {
     // ------------------------------ scale atoms -> TMEM ---------------------------
     // Four warps, one per TMEM sub-partition: every landed stage's scale atoms go from shared
     // memory through registers into the stage's TMEM columns (tcgen05.st), then the warp arrives
@@ -319,7 +323,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
           ok = false;
           break;
         }
-        if (warp == 10 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_LANDED, tl_n);
+        if (warp == 4 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_LANDED, tl_n);
         const uint32_t sfa_t =
             tmem_base + kTmemSf + stage * Cfg::kSfCols + (static_cast<uint32_t>(sub * 32) << 16);
         const uint32_t sfb_t = sfa_t + 16;
@@ -340,7 +344,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tail->full[stage]);
-        if (warp == 10 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_DONE, tl_n);
+        if (warp == 4 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_DONE, tl_n);
         TL_INC(tl_n);
         if (++stage == kStages) {
           stage = 0;
@@ -348,12 +352,14 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         }
       }
     }
+  }
   } else {
     // ------------------------------ epilogue ----------------------------------
+    regs_raise_to<kRegsEpilogue>();
     // Eight warps.  Warp w may only read TMEM sub-partition (w & 3), i.e. tile rows
     // 32*(w&3) .. +31; the two warps that share a sub-partition split the tile's columns.
     const int sub = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = (warp - 8) >> 2;
     const int m = sub * 32 + lane;            // tile row = TMEM lane
     uint32_t acc_phase[2] = {0, 0};
     int buf = 0;
@@ -365,15 +371,15 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
       if (!mbar_wait_bounded(&tail->tmem_full[buf], acc_phase[buf], abort_flag, p.status,
                           WAIT_TMEM_FULL))
         break;
-      if (warp == 2 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_FULL, tl_t);
+      if (warp == 8 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_FULL, tl_t);
       acc_phase[buf] ^= 1;
       tc_fence_after();
       const uint32_t t_lane = tmem_base + buf * BN + (static_cast<uint32_t>(sub * 32) << 16);
       epilogue_tile<KIND, EPI, BN>(p, c.e, c.mt, c.nt, row0, nrows, t_lane, m, half, lane, [&]() {
         if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
-        if (warp == 2 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_RELEASED, tl_t);
+        if (warp == 8 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_RELEASED, tl_t);
       });
-      if (warp == 2 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_DONE, tl_t);
+      if (warp == 8 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_DONE, tl_t);
       TL_INC(tl_t);
       if (Cfg::kBufs == 2) buf ^= 1;
     }
@@ -482,22 +488,10 @@ void fill_common(GemmParams& p, const b200moe_gemm_args* a, char* base) {
   p.swigluoai = a->activation == B200MOE_ACT_SWIGLUOAI;
 }
 
-// Tile width: 256 unless the shape does not allow it (a gated FC1 needs I % 128 == 0 for it) or
-// B200MOE_TILE_N=128 asks for the narrow, double-buffered tile.
-static int preferred_tile_n() {
-  static int v = 0;
-  if (v == 0) {
-    const char* e = getenv("B200MOE_TILE_N");
-    v = (e != nullptr && atoi(e) == 128) ? 128 : 256;
-  }
-  return v;
-}
-
 template <int KIND, int EPI>
-static int launch_any(int bn, const CUtensorMap& tmA, const CUtensorMap& tmA_small,
+static int launch_any(int /*bn*/, const CUtensorMap& tmA, const CUtensorMap& tmA_small,
                       const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t s) {
-  if (bn == 256) return launch_gemm<KIND, EPI, 256>(tmA, tmA_small, tmB, p, grid, s);
-  return launch_gemm<KIND, EPI, 128>(tmA, tmA_small, tmB, p, grid, s);
+  return launch_gemm<KIND, EPI, 256>(tmA, tmA_small, tmB, p, grid, s);
 }
 
 // The first projection.  Gated activations: the weight scales are stored as PAIR atoms -- for every
@@ -540,7 +534,7 @@ static int gemm1_any(const b200moe_gemm_args* a, cudaStream_t stream) {
   p.out_cols = I;
   p.out_atoms = ceil_div_i(I, mx ? 128 : 64);
   const int grid = a->num_sms > 0 ? a->num_sms : num_sms_cached();
-  int bn = preferred_tile_n();
+  const int bn = 256;
   if (gated) {
     p.sfb_rowgroups = I / 64;              // pair atoms
     p.n_step = bn / 2;                     // intermediate columns per tile
@@ -585,7 +579,7 @@ static int gemm2_any(const b200moe_gemm_args* a, cudaStream_t stream) {
   p.w_rows = K;
   p.sfb_rowgroups = ceil_div_i(K, 128);
   p.out_cols = K;
-  const int bn = preferred_tile_n();
+  const int bn = 256;
   p.n_step = bn;
   p.n_tiles = ceil_div_i(K, bn);
   const int grid = a->num_sms > 0 ? a->num_sms : num_sms_cached();

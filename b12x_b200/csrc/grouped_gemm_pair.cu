@@ -7,12 +7,13 @@
 // 16 KiB of token rows + 16 KiB of weight rows + 6 KiB of scale atoms from L2 instead of 16 + 32 + 6:
 // the wide single-CTA kernel is limited by exactly that operand stream.
 //
-// Roles per CTA (480 threads): warp 0 operand producer (the operand copies of either CTA complete
-// on the EVEN CTA's stage barrier), warp 14 scale-atom producer (a ring of eight slots of its own,
-// completing on barriers of the CTA itself), warps 2..9 epilogue of the CTA's own accumulator,
-// warps 10..13 move the CTA's scale atoms into its tensor memory (tcgen05.st) and arrive on the
-// even CTA's scale barrier.  Even CTA only: warp 1 issues the
-// MMAs and commits (multicast) to both CTAs' barriers.  The odd CTA's epilogue warps release the
+// Roles per CTA (512 threads, four warp groups): warp 0 operand producer (the operand copies of
+// either CTA complete on the EVEN CTA's stage barrier), warp 2 scale-atom producer (a ring of eight
+// slots of its own, completing on barriers of the CTA itself), warps 4..7 move the CTA's scale atoms
+// into its tensor memory (tcgen05.st) and arrive on the even CTA's stage barrier, warps 8..15
+// epilogue of the CTA's own accumulator (drained into registers first, so that it overlaps the
+// next tile's main loop; the other warp groups hand over registers for that).  Even CTA only:
+// warp 1 issues the MMAs and commits (multicast) to both CTAs' barriers.  The odd CTA's epilogue warps release the
 // accumulator with remote arrives on the even CTA's barrier.  Every wait is bounded; the two cluster-wide
 // barriers (after set-up, before tear-down) are reached by both CTAs unconditionally.
 #include <stdlib.h>
@@ -22,7 +23,9 @@
 namespace b200moe {
 namespace pair {
 
-constexpr int kThreads = 480;
+constexpr int kThreads = 512;                 // four warp groups
+constexpr int kRegsSmall = 48;                // register allowance: producers, MMA, scale warps ...
+constexpr int kRegsEpilogue = 208;            // ... and the epilogue warp groups
 constexpr int kStages = 5;
 constexpr int kRowBytes = 128;
 constexpr int kSmemA = 128 * kRowBytes;       // this CTA's 128 token rows, one k-block
@@ -191,6 +194,8 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
   long long* const tl_buf = tl_slot >= 0 ? g_timeline : nullptr;
 #endif
 
+  if (warp < 8) {
+  regs_release_to<kRegsSmall>();
   if (warp == 0) {
     // ------------------------------ operand producer (both CTAs) -----------------
     // lane 0: (even CTA) arms the stage barrier; token rows.  lanes 1, 2: the two 64-row boxes
@@ -263,7 +268,7 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       }
     }
 #endif
-  } else if (warp == 14) {
+  } else if (warp == 2) {
     // ------------------------------ scale-atom producer (both CTAs) --------------
     // The scale atoms travel through a ring of their own that is deeper than the operand stages:
     // they are in shared memory before the stage's tensor-memory columns are free again, so their
@@ -357,7 +362,7 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         acc_phase ^= 1;
       }
     }
-  } else if (warp >= 10) {
+  } else if (warp >= 4) {
     // ------------------------------ scale atoms -> TMEM (both CTAs) ---------------
     // Four warps, one per TMEM sub-partition.  Per k-block: the slot's atoms have landed and the
     // stage's tensor-memory columns are free again (the MMAs of the stage's previous use have
@@ -375,12 +380,12 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           ok = false;
           break;
         }
-        if (warp == 10 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_LANDED, tl_n);
+        if (warp == 4 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_LANDED, tl_n);
         if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status, WAIT_SMEM_EMPTY)) {
           ok = false;
           break;
         }
-        if (warp == 10 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_SLOTFREE, tl_n);
+        if (warp == 4 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_SLOTFREE, tl_n);
         tc_fence_after();
         const uint32_t sfa_t = tmem_base + kTmemSf + stage * kSfCols + (static_cast<uint32_t>(sub * 32) << 16);
         const uint32_t sfb_t = sfa_t + 16;
@@ -395,7 +400,7 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           mbar_arrive(&tail->sf_empty[slot]);
           mbar_arrive_cluster(map_to_cta(smem_u32(&tail->full[stage]), 0));
         }
-        if (warp == 10 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_DONE, tl_n);
+        if (warp == 4 && lane == 0) TL_STAGE(tl_k, tl_slot, TL_S_DONE, tl_n);
         TL_INC(tl_n);
         if (++stage == kStages) {
           stage = 0;
@@ -407,10 +412,12 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         }
       }
     }
+  }
   } else {
     // ------------------------------ epilogue (both CTAs) --------------------------
+    regs_raise_to<kRegsEpilogue>();
     const int sub = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = (warp - 8) >> 2;
     const int m = sub * 32 + lane;
     const uint32_t release_addr = map_to_cta(smem_u32(&tail->tmem_empty), 0);
     uint32_t acc_phase = 0;
@@ -419,15 +426,15 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       const PairCoord c = decode_pair(w, p, tail, rank);
       const int row0 = p.mtile_row0[c.mt_load];
       if (!mbar_wait_bounded(&tail->tmem_full, acc_phase, abort_flag, p.status, WAIT_TMEM_FULL)) break;
-      if (warp == 2 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_FULL, tl_t);
+      if (warp == 8 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_FULL, tl_t);
       acc_phase ^= 1;
       tc_fence_after();
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(sub * 32) << 16);
       epilogue_tile<KIND_NVFP4, EPI, 256>(p, c.e, c.mt_load, c.nt, row0, c.rows, t_lane, m, half, lane, [&]() {
         if (lane == 0) mbar_arrive_cluster(release_addr);
-        if (warp == 2 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_RELEASED, tl_t);
+        if (warp == 8 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_RELEASED, tl_t);
       });
-      if (warp == 2 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_DONE, tl_t);
+      if (warp == 8 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_DONE, tl_t);
       TL_INC(tl_t);
     }
   }
