@@ -476,11 +476,12 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmPara
 
 }  // namespace pair
 
-// The CTA-pair kernels serve nvfp4 plans with 128-row tiles and gated FC1 (or FC2).  They are
-// correct but, as measured, not faster than the single-CTA wide kernel yet (each CTA streams 38 KB
-// per stage instead of 54 KB, but the round trip of a stage across the pair is about a
-// microsecond longer and five stages are all the shared memory holds), so they only run when
-// B200MOE_PAIR=1 asks for them.
+// The CTA-pair kernels serve nvfp4 plans with 128-row tiles and gated FC1 (or FC2).  A pair
+// streams 38 KB per stage and CTA instead of 54 KB; with the accumulator released early they are the
+// faster kernels once experts have several row tiles (C4: FC1 1.02 against 1.10 ms, FC2 0.50 against
+// 0.55 ms).  Default: plans whose capacity averages at least two row tiles per expert; an expert
+// with an odd number of row tiles leaves half a pair idle, so smaller plans stay on the single-CTA
+// kernel.  B200MOE_PAIR=1 / 0 forces them on (where the shape allows) / off.
 bool nvfp4_pair_ok(const b200moe_gemm_args* a, bool fc1) {
   static int mode = -2;
   if (mode == -2) {
@@ -490,7 +491,8 @@ bool nvfp4_pair_ok(const b200moe_gemm_args* a, bool fc1) {
   if (mode == 0 || a->layout->tile_rows != 128) return false;
   if (a->hidden_size % 64 != 0 || a->intermediate % 64 != 0 || a->num_experts > kMaxExperts) return false;
   if (fc1 && a->activation == B200MOE_ACT_RELU2) return false;
-  return mode == 1;
+  if (mode == 1) return true;
+  return static_cast<int64_t>(a->layout->rows) >= 256ll * a->num_experts;
 }
 
 int nvfp4_pair_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {

@@ -78,6 +78,11 @@ class _LayerBase:
         self.last_binding = None
         self.graph = None     # a captured step on (x_stage, lg_stage), where the layer offers one
 
+    @property
+    def local_intermediate(self) -> int:
+        """Intermediate columns this rank holds (the whole of it unless the layer is tensor-parallel)."""
+        return int(self.inputs.w2_fp4.shape[2]) * 2
+
     def route(self, logits: torch.Tensor) -> None:
         shp = self.shape
         if shp.router == "sigmoid":

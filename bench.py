@@ -1,22 +1,31 @@
 #!/usr/bin/env python
 """Benchmark of the fused MoE layer on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--tokens T] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4] [--sub c2,c5,c3] [--impl reference]
 
 One step = one pass of the layer (route -> sort -> quantise -> FC1+activation -> FC2 -> combine)
-over one batch of seeded synthetic input.  The default workload is the DeepSeek-V3-shaped decode
-layer (hidden 7168, intermediate 2048, 256 experts, top-8, NVFP4 W4A4, 64 tokens per GPU); with
-N > 1 the experts are block-partitioned over the ranks (expert parallelism; tokens are exchanged by
-the library's own kernels over NVLink peer memory, `--ep nccl` selects the NCCL all-to-all variant)
-and every rank brings its own batch (weak scaling).  Rank 0 prints ONE JSON line.
+over one batch of seeded synthetic input.  The headline workload is the Mixtral-shaped NVFP4 prefill
+layer with skewed routing (hidden 4096, intermediate 14336, 8 experts, top-2, 8192 tokens per GPU):
+the large-batch, tensor-bound configuration.  The other benchmark shapes (DeepSeek-V3-shaped decode,
+GPT-OSS-shaped w4a8_mx, Qwen3-shaped W4A16) are timed in the same run and reported as compact
+sub-records under ``"workloads"``.  With N > 1 the expert-parallel shapes block-partition their
+experts over the ranks (tokens are exchanged by the library's own kernels over NVLink peer memory;
+``--ep nccl`` selects the NCCL all-to-all variant) and every rank brings its own batch; the Qwen3
+shape shards the intermediate dimension (tensor parallelism, NCCL all-reduce).  Rank 0 prints ONE
+JSON line.
 
-`--impl reference` times the CPU oracle (the restatement of the reference library's own torch
-implementation of this layer) on the host cores for the same configuration.
+Every timed shape is also checked: after the timed loop the CPU oracle evaluates the routed rows of
+a few experts and is compared with the rows the kernels left in the scratch arena (the whole
+permutation bit for bit, the FC2 rows within 1e-2 x their RMS); a failed check exits non-zero.
+
+``--impl reference`` times the CPU oracle (the restatement of the reference library's own torch
+implementation of this layer) on the host cores for the headline configuration.
 """
 
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -24,6 +33,7 @@ import subprocess
 import sys
 import tempfile
 import time
+from dataclasses import replace
 from pathlib import Path
 
 import torch
@@ -33,25 +43,35 @@ sys.path.insert(0, str(ROOT))
 
 from b12x_b200 import synth  # noqa: E402
 
-KERNELS_PER_STEP = 6  # route_topk, expert_sort, permute_quant, gemm1, gemm2, combine
-NCU_FC1_TRAFFIC_RATIO = 1.014
+# DRAM bytes per FC1 launch of the decode shape: an ncu capture of its 32-expert case read 1.014 x
+# the algorithmic bytes (dram__bytes_read + write; summary under profiles/); every active expert's
+# weights are read once per launch, so the traffic scales with the algorithmic bytes
+NCU_FC1_TRAFFIC_RATIO = {"c2_dsv3_decode_nvfp4": 1.014}
+# experts of the CPU-baseline sample: a pass over them takes a few seconds on 16 cores
+CPU_EXPERTS = {"c1": 8, "c2": 8, "c3": 8, "c4": 4, "c5": 8}
+PARITY_EXPERTS = 4
+PARITY_ROWS_PER_EXPERT = 48
+PARITY_TOL = 1e-2
 
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="c2", choices=sorted(synth.SHAPES))
-    ap.add_argument("--tokens", type=int, default=None, help="tokens per GPU (default: the workload's)")
+    ap.add_argument("--workload", default="c4", choices=sorted(synth.SHAPES))
+    ap.add_argument("--sub", default="c2,c5,c3",
+                    help="comma-separated workloads reported as sub-records ('none' to skip them)")
+    ap.add_argument("--tokens", type=int, default=None, help="tokens per GPU of the headline workload")
     ap.add_argument("--experts", type=int, default=None, help="override the expert count (small profiling cases)")
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
                     help="expert-parallel exchange: own kernels over peer memory, or NCCL all-to-all")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the step kernel by kernel instead of replaying a CUDA graph")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cpu-experts", type=int, default=8, help="experts in the CPU-baseline sample")
+    ap.add_argument("--cpu-experts", type=int, default=None, help="experts in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the sampled oracle check (profiling runs)")
     return ap.parse_args()
 
 
@@ -65,7 +85,7 @@ def load_peaks() -> dict:
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle sampling during the timed region."""
+    """nvidia-smi clock / throttle sampling during the timed region (read-only queries)."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -89,7 +109,7 @@ class ClockSampler:
     def _lines(self):
         try:
             return Path(self.path).read_text().splitlines()
-        except OSError:
+        except (OSError, TypeError):
             return []
 
     def wait_first(self, timeout_s: float = 4.0) -> None:
@@ -99,24 +119,18 @@ class ClockSampler:
             time.sleep(0.02)
 
     def mark(self) -> int:
-        """Index of the next sample: brackets the timed region."""
+        """Index of the next sample: brackets a timed region."""
         return len(self._lines())
 
-    def stop(self, lo: int = 0, hi: int | None = None) -> dict:
+    def window(self, lo: int, hi: int) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
         lines = self._lines()
-        hi = len(lines) if hi is None else hi
         # a region shorter than the sampling period: take the samples either side of it
-        window = lines[lo:hi] if hi > lo else lines[max(lo - 1, 0):hi + 1]
+        win = lines[lo:hi] if hi > lo else lines[max(lo - 1, 0):hi + 1]
         sm, smax, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in window:
+        for line in win:
             c = [x.strip() for x in line.split(",")]
             if len(c) < 9:
                 continue
@@ -128,9 +142,21 @@ class ClockSampler:
             for name, val in zip(names, c[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        os.unlink(self.path)
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(smax) if smax else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+    def stop(self) -> None:
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        try:
+            os.unlink(self.path)
+        except OSError:
+            pass
 
 
 class StageTimer:
@@ -157,52 +183,65 @@ class StageTimer:
         return {k: sum(v) / len(v) for k, v in acc.items()}
 
 
-def oracle_sample(shp, inp_cpu, ids, weights, n_experts: int):
-    """CPU oracle on the routes of the batch that land on the first ``n_experts`` experts."""
+# ---------------------------------------------------------------------------------------------
+# CPU oracle legs (the only places this file touches oracle/)
+# ---------------------------------------------------------------------------------------------
+def _oracle_call(shp, x, w1, s1, g1, w2, s2, g2, a1, a2, ids, weights, expert_map=None, taps=None):
     from oracle import moe_oracle as O
-    emap = torch.full((shp.experts,), -1, dtype=torch.int32)
-    emap[:n_experts] = torch.arange(n_experts, dtype=torch.int32)
-    kept = int((ids < n_experts).sum())
-    t0 = time.perf_counter()
     if shp.recipe == "nvfp4":
-        a1 = inp_cpu.w1_global_scale / inp_cpu.a1_gscale
-        a2 = inp_cpu.w2_global_scale / inp_cpu.a2_gscale
-        O.moe_nvfp4(inp_cpu.x, inp_cpu.w1_fp4, inp_cpu.w1_blockscale, a1, inp_cpu.w2_fp4, inp_cpu.w2_blockscale,
-                    a2, inp_cpu.a1_gscale, inp_cpu.a2_gscale, ids, weights, activation=shp.activation,
-                    expert_map=emap)
-    elif shp.recipe == "w4a16":
-        O.moe_w4a16(inp_cpu.x, inp_cpu.w1_fp4, inp_cpu.w1_blockscale, inp_cpu.w1_global_scale, inp_cpu.w2_fp4,
-                    inp_cpu.w2_blockscale, inp_cpu.w2_global_scale, ids, weights, activation=shp.activation,
-                    expert_map=emap)
-    else:
-        ones = torch.ones(n_experts)
-        O.moe_w4a8_mx(inp_cpu.x, inp_cpu.w1_fp4, inp_cpu.w1_blockscale, ones, inp_cpu.w2_fp4,
-                      inp_cpu.w2_blockscale, ones, ids, weights, activation=shp.activation, expert_map=emap)
+        return O.moe_nvfp4(x, w1, s1, g1 / a1, w2, s2, g2 / a2, a1, a2, ids, weights, activation=shp.activation,
+                           expert_map=expert_map, taps=taps)
+    if shp.recipe == "w4a16":
+        return O.moe_w4a16(x, w1, s1, g1, w2, s2, g2, ids, weights, activation=shp.activation,
+                           expert_map=expert_map, taps=taps)
+    ones = torch.ones(w1.shape[0])
+    return O.moe_w4a8_mx(x, w1, s1, ones, w2, s2, ones, ids, weights, activation=shp.activation,
+                         expert_map=expert_map, taps=taps)
+
+
+def oracle_sample(shp, inp_cpu, ids, weights, experts_lo: int, n_experts: int):
+    """CPU oracle on the routes of the batch that land on experts [experts_lo, experts_lo + n)."""
+    emap = torch.full((shp.experts,), -1, dtype=torch.int32)
+    emap[experts_lo:experts_lo + n_experts] = torch.arange(n_experts, dtype=torch.int32)
+    kept = int(((ids >= experts_lo) & (ids < experts_lo + n_experts)).sum())
+    t0 = time.perf_counter()
+    _oracle_call(shp, inp_cpu.x, inp_cpu.w1_fp4, inp_cpu.w1_blockscale, inp_cpu.w1_global_scale, inp_cpu.w2_fp4,
+                 inp_cpu.w2_blockscale, inp_cpu.w2_global_scale, inp_cpu.a1_gscale, inp_cpu.a2_gscale, ids, weights,
+                 expert_map=emap)
     return time.perf_counter() - t0, kept
 
 
-def cpu_inputs(shp, n_experts: int, seed: int):
-    """Host copy of the workload restricted to ``n_experts`` experts' weights (seeded on the host)."""
-    return synth.make_inputs(shp, seed=seed, device="cpu", experts=n_experts)
+def cpu_sample_inputs(shp, n_experts: int):
+    """Host copy of the workload restricted to the sample's experts, its routing, and where the sample
+    sits: the first experts, or -- where routing is skewed and the first experts are the hot ones --
+    the last, so that one pass stays within seconds."""
+    from oracle import moe_oracle as O
+    n_e = min(n_experts, shp.experts)
+    inp = synth.make_inputs(shp, seed=0, device="cpu", experts=n_e)
+    if shp.router == "sigmoid":
+        _, ids, w = O.route_topk(inp.router_logits, shp.topk, mode="sigmoid", route_scale=shp.route_scale)
+    else:
+        _, ids, w = O.route_topk(inp.router_logits, shp.topk)
+    lo = shp.experts - n_e if shp.zipf_s > 0 else 0
+    return inp, ids, w, lo, n_e
+
+
+def sample_text(shp, lo, n_e, kept) -> str:
+    return (f"routes of one {shp.tokens}-token batch that land on experts {lo}..{lo + n_e - 1} "
+            f"({kept} of {shp.rows} routed rows); tokens = rows / top-k")
 
 
 def run_reference(args, shp):
     """The reference's CPU implementation of the path (oracle port), all host threads."""
-    from oracle import moe_oracle as O
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    n_e = min(args.cpu_experts, shp.experts)
-    inp = cpu_inputs(shp, n_e, seed=0)
-    if shp.router == "sigmoid":
-        _, ids, w = O.route_topk(inp.router_logits, shp.topk, mode="sigmoid", route_scale=shp.route_scale)
-    else:
-        _, ids, w = O.route_topk(inp.router_logits, shp.topk)
+    inp, ids, w, lo, n_e = cpu_sample_inputs(shp, args.cpu_experts or CPU_EXPERTS.get(args.workload, 8))
     times, kept = [], 0
     for i in range(args.warmup + args.steps):
-        dt, kept = oracle_sample(shp, inp, ids, w, n_e)
+        dt, kept = oracle_sample(shp, inp, ids, w, lo, n_e)
         if i >= args.warmup:
             times.append(dt)
     sec = sum(times) / len(times)
@@ -213,14 +252,66 @@ def run_reference(args, shp):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_of(shp),
         "data": "synthetic", "config": config_of(shp, args.gpus),
         "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port",
-                         "sample": f"routes of one {shp.tokens}-token batch that land on experts 0..{n_e - 1} "
-                                   f"({kept} of {shp.rows} routed rows); tokens = rows / top-k"},
+                         "sample": sample_text(shp, lo, n_e, kept)},
         "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "tflops": kept * shp.flops / shp.rows / sec / 1e12,
     }
     print(json.dumps(line), flush=True)
 
 
+def parity_sample(layer) -> dict:
+    """Check the last step of ``layer`` against the CPU oracle on a sample.
+
+    The whole permutation the kernels left in the scratch arena is compared bit for bit with the
+    oracle's canonical one; the per-route FC2 rows (fp32, before router weights) of up to
+    ``PARITY_ROWS_PER_EXPERT`` routes of ``PARITY_EXPERTS`` experts are compared with the oracle's."""
+    from oracle import moe_oracle as O
+    b = layer.last_binding
+    inp = layer.inputs
+    shp = replace(inp.shape, experts=b.weight_E)
+    torch.cuda.synchronize(b.device)
+    ids_dev = b.topk_ids
+    tokens, k = ids_dev.shape
+    ids = ids_dev.cpu()
+    emap = None if b.route_expert_map is None else b.route_expert_map.cpu()
+    srt = O.expert_sort(ids, b.weight_E, emap, tile_rows=int(b.core_layout.tile_rows))
+    kept = int(srt.sorted_route_ids.numel())
+    perm_ok = bool(torch.equal(b.packed_route_indices[:kept].cpu(), srt.sorted_route_ids)
+                   and torch.equal(b.inv_perm.cpu(), srt.inv_perm)
+                   and torch.equal(b.expert_counts.cpu(), srt.expert_counts))
+    active = [e for e in range(b.weight_E) if int(srt.expert_counts[e]) > 0]
+    if not active:
+        return {"experts": 0, "rows": 0, "permutation_rows": kept, "permutation_ok": perm_ok,
+                "max_abs_over_rms": 0.0, "ok": perm_ok}
+    step = max(len(active) // PARITY_EXPERTS, 1)
+    chosen = active[::step][:PARITY_EXPERTS]
+    pos, local = [], []
+    for j, e in enumerate(chosen):
+        lo, hi = int(srt.expert_offsets[e]), int(srt.expert_offsets[e + 1])
+        n = min(hi - lo, PARITY_ROWS_PER_EXPERT)
+        pos.extend(range(lo, lo + n))
+        local.extend([j] * n)
+    pos_t = torch.tensor(pos, dtype=torch.int64)
+    tok = (srt.sorted_route_ids.to(torch.int64)[pos_t] // k).to(b.device)
+    x_sub = b.a.index_select(0, tok).cpu()
+    got = b.route_output.index_select(0, pos_t.to(b.device)).cpu()
+    sel = torch.tensor(chosen, dtype=torch.int64)
+    cpu = lambda t: t.index_select(0, sel.to(t.device)).cpu()
+    taps = O.MoETaps()
+    n = len(pos)
+    _oracle_call(shp, x_sub, cpu(inp.w1_fp4), cpu(inp.w1_blockscale), cpu(inp.w1_global_scale), cpu(inp.w2_fp4),
+                 cpu(inp.w2_blockscale), cpu(inp.w2_global_scale), cpu(inp.a1_gscale), cpu(inp.a2_gscale),
+                 torch.tensor(local, dtype=torch.int32).reshape(n, 1), torch.ones(n, 1), taps=taps)
+    # the sub-batch is ordered by (expert, position), which the oracle's stable sort keeps
+    ref = taps.routed
+    rms = ref.square().mean().sqrt().item()
+    err = (got - ref).abs().max().item()
+    ratio = err / max(rms, 1e-30)
+    return {"experts": len(chosen), "rows": n, "permutation_rows": kept, "permutation_ok": perm_ok,
+            "max_abs_over_rms": ratio, "tolerance": PARITY_TOL, "ok": bool(perm_ok and ratio <= PARITY_TOL)}
+
+
+# ---------------------------------------------------------------------------------------------
 def dtype_of(shp) -> str:
     return {"nvfp4": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)", "w4a8_mx": "mxfp8 x mxfp4 (fp32 accumulate)",
             "w4a16": "bf16 x fp4-dequant (fp32 accumulate)"}[shp.recipe]
@@ -233,7 +324,156 @@ def config_of(shp, n_gpus: int, ep: str = "peer", graph: bool = False) -> dict:
             "parallelism": ("single" if n_gpus == 1 else f"{shp.parallelism}{n_gpus}"),
             "exchange": ("none" if n_gpus == 1 else ("nccl all-reduce" if shp.parallelism == "tp" else ep)),
             "launch": "step replayed from a CUDA graph" if graph else "kernel by kernel",
-            "l2": "no flush: the expert weights read per step exceed the 126 MB L2"}
+            "l2": "no flush: the operands read per step (weights, or tokens x weights at prefill) exceed the 126 MB L2"}
+
+
+def make_layer(shp, dev, rank, world, ep):
+    from b12x_b200.moe.distributed import ExpertParallelMoE, TensorParallelMoE
+    if world > 1 and shp.parallelism == "tp":
+        return TensorParallelMoE.from_synthetic(shp, dev, rank, world)
+    if world > 1 and ep == "peer":
+        # dispatch / combine by this library's kernels over NVLink peer memory
+        from b12x_b200.moe.ep_peer import PeerExpertParallelMoE
+        return PeerExpertParallelMoE.from_synthetic(shp, dev, rank, world)
+    return ExpertParallelMoE.from_synthetic(shp, dev, rank, world)
+
+
+def run_workload(key, shp, args, dev, rank, world, sampler, *, steps, warmup) -> dict:
+    """Time one workload: device-resident leg (graph replay where the step allows it), a short eager
+    leg for per-stage times, the end-to-end leg with host buffers, the sampled oracle check."""
+    layer = make_layer(shp, dev, rank, world, args.ep)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    # host-side inputs (pinned) for the end-to-end leg, device-resident copies for the kernel leg
+    x_host = layer.inputs.x.cpu().pin_memory()
+    lg_host = layer.inputs.router_logits.cpu().pin_memory()
+    out_host = torch.empty((shp.tokens, shp.hidden), dtype=torch.bfloat16).pin_memory()
+    x_dev = layer.inputs.x.to(dev)
+    lg_dev = layer.inputs.router_logits.to(dev)
+
+    for _ in range(max(warmup, 3)):
+        layer.forward(x_dev, lg_dev)
+    barrier()
+    # a step without host-dependent arguments (one GPU; the peer-memory expert-parallel step) is
+    # captured once in a CUDA graph and replayed, the way the reference times its layer
+    graph = None
+    if layer.can_capture and not args.no_graph:
+        layer.x_stage.copy_(x_dev)
+        layer.lg_stage.copy_(lg_dev)
+        graph = layer.capture()
+        for _ in range(3):
+            graph.replay()
+        barrier()
+    sampler.wait_first()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    mark_lo = sampler.mark()
+    e0.record()
+    if graph is not None:
+        for _ in range(steps):
+            graph.replay()
+    else:
+        for _ in range(steps):
+            layer.forward(x_dev, lg_dev)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / steps
+    # per-stage times: a short kernel-by-kernel leg with an event at every stage boundary, inside
+    # the clock-sampled region
+    timer = StageTimer()
+    for _ in range(max(min(steps // 4, 16), 4)):
+        layer.forward(x_dev, lg_dev, stage_timer=timer)
+    barrier()
+    layer.check_status()
+
+    # ---------------- end-to-end leg: host buffers in, host buffer out ----------------
+    for _ in range(3):
+        layer.forward_host(x_host, lg_host, out_host)
+    barrier()
+    h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(steps // 2, 1)
+    barrier()
+    h0.record()
+    for _ in range(e2e_steps):
+        layer.forward_host(x_host, lg_host, out_host)
+    h1.record()
+    barrier()
+    ms_e2e = h0.elapsed_time(h1) / e2e_steps
+    clocks = sampler.window(mark_lo, sampler.mark())   # all timed legs run between the marks
+
+    stages = timer.mean_ms()
+    stats = layer.work_stats()   # algorithmic bytes / flops of the dominant kernel on this rank
+    peaks = load_peaks()
+    # per-GPU step roofline: what this rank's share of the work needs at the peak that bounds it
+    dom = stats["dominant"]
+    rate = dom["bf16_rate_multiple"]
+    step_flops = stats["rows"] * shp.flops / shp.rows * (1.0 / world if (world > 1 and shp.parallelism == "tp") else 1.0)
+    step_bytes = stats["active_experts"] * replace(shp, intermediate=layer.local_intermediate).expert_weight_bytes()
+    ideal_ms = max(step_flops / (peaks["bf16_tflops"] * rate * 1e12), step_bytes / (peaks["hbm_gbs"] * 1e9)) * 1e3
+    if world > 1:
+        red = torch.tensor([ms, ms_e2e, ideal_ms, float(stats["rows"])], device=dev, dtype=torch.float64)
+        mx = red.clone()
+        torch.distributed.all_reduce(mx, op=torch.distributed.ReduceOp.MAX)
+        torch.distributed.all_reduce(red, op=torch.distributed.ReduceOp.SUM)
+        ms, ms_e2e, ideal_max, rows_max = mx.tolist()
+        ideal_mean, rows_mean = red[2].item() / world, red[3].item() / world
+    else:
+        ideal_max = ideal_mean = ideal_ms
+        rows_max = rows_mean = float(stats["rows"])
+
+    parity = None if args.no_parity else parity_sample(layer)
+
+    tp = world > 1 and shp.parallelism == "tp"
+    total_tokens = shp.tokens if tp else shp.tokens * world
+    dom_ms = stages.get(dom["stage"], float("nan"))
+    if dom["bound"] == "hbm":
+        achieved = dom["bytes"] / (dom_ms * 1e-3) / 1e9
+        peak, unit = peaks["hbm_gbs"], "GB/s"
+    else:
+        achieved = dom["flops"] / (dom_ms * 1e-3) / 1e12
+        peak, unit = peaks["bf16_tflops"] * rate, "TFLOP/s"
+    ratio = NCU_FC1_TRAFFIC_RATIO.get(shp.name)
+    traffic = dom["bytes"] * ratio if (ratio is not None and dom["bound"] == "hbm") else None
+    rec = {
+        "value": total_tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+        "scaling": "strong" if tp else "weak", "dtype": dtype_of(shp),
+        "config": config_of(shp, world, args.ep, graph is not None), "clocks": clocks,
+        "e2e": {"value": total_tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": x_host.numel() * 2 + lg_host.numel() * 4,
+                "d2h_bytes_per_step": out_host.numel() * 2},
+        "gpu_launches": steps * layer.kernels_per_step,
+        "tflops": shp.flops * (1 if tp else world) / (ms * 1e-3) / 1e12,
+        "stage_ms": stages,
+        "roofline": {"kernel": dom["kernel"], "bound": dom["bound"], "achieved": achieved, "peak": peak,
+                     "unit": unit, "frac": achieved / peak, "peak_source": peaks["source"] + dom.get("peak_note", ""),
+                     "traffic": traffic, "algorithmic_bytes": dom["bytes"],
+                     "algorithmic_flops": dom["flops"], "ms_per_launch": dom_ms,
+                     "launches_timed": len(timer.steps), "active_experts": stats.get("active_experts")},
+        # the whole step of one GPU against the peak that bounds it (expert weights owned / HBM peak,
+        # or flops owned / tensor peak): the slowest rank's ideal over the measured step time
+        "step_roofline": {"ideal_ms_max_rank": ideal_max, "ideal_ms_mean_rank": ideal_mean,
+                          "frac": ideal_max / ms, "frac_balanced": ideal_mean / ms,
+                          "load_balance": rows_mean / max(rows_max, 1.0)},
+        "parity_sample": parity,
+    }
+    del layer, x_dev, lg_dev
+    gc.collect()
+    torch.cuda.empty_cache()
+    return rec
+
+
+def compact(rec: dict) -> dict:
+    r = rec["roofline"]
+    return {"workload": rec["config"]["workload"], "parallelism": rec["config"]["parallelism"],
+            "tokens_per_gpu": rec["config"]["tokens_per_gpu"], "value": rec["value"], "unit": rec["unit"],
+            "scaling": rec["scaling"], "ms_per_step": rec["ms_per_step"], "tflops": rec["tflops"],
+            "e2e_ms_per_step": rec["e2e"]["ms_per_step"], "stage_ms": rec["stage_ms"],
+            "roofline": {k: r[k] for k in ("kernel", "bound", "achieved", "peak", "unit", "frac", "ms_per_launch")},
+            "step_roofline": rec["step_roofline"], "clocks": rec["clocks"], "parity_sample": rec["parity_sample"]}
 
 
 def main():
@@ -252,7 +492,7 @@ def main():
         return
 
     from b12x_b200.moe import fused_moe
-    from b12x_b200.moe.distributed import ExpertParallelMoE, TensorParallelMoE, init_process_group
+    from b12x_b200.moe.distributed import init_process_group
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -266,145 +506,55 @@ def main():
     if not fused_moe.is_supported(dev):
         raise SystemExit("this benchmark needs an sm_100 GPU and the built extension (no fallback)")
 
-    if world > 1 and shp.parallelism == "tp":
-        layer = TensorParallelMoE.from_synthetic(shp, dev, rank, world)
-    elif world > 1 and args.ep == "peer":
-        # dispatch / combine by this library's kernels over NVLink peer memory
-        from b12x_b200.moe.ep_peer import PeerExpertParallelMoE
-        layer = PeerExpertParallelMoE.from_synthetic(shp, dev, rank, world)
-    else:
-        layer = ExpertParallelMoE.from_synthetic(shp, dev, rank, world)
-
-    # host-side inputs (pinned) for the end-to-end leg, device-resident copies for the kernel leg
-    x_host = layer.inputs.x.cpu().pin_memory()
-    lg_host = layer.inputs.router_logits.cpu().pin_memory()
-    out_host = torch.empty((shp.tokens, shp.hidden), dtype=torch.bfloat16).pin_memory()
-    x_dev = layer.inputs.x.to(dev)
-    lg_dev = layer.inputs.router_logits.to(dev)
-
-    def barrier():
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-
-    # ---------------- device-resident leg ----------------
     sampler = ClockSampler(local_rank)
     sampler.start()
-    timer = StageTimer()
-    for i in range(args.warmup):
-        layer.forward(x_dev, lg_dev, stage_timer=timer if i >= args.warmup // 2 else None)
-    barrier()
-    # a step without host-dependent arguments (one GPU; the peer-memory expert-parallel step) is
-    # captured once in a CUDA graph and replayed, the way the reference times its layer
-    # (per-stage events then come from the eager warm-up passes above)
-    graph = None
-    if layer.can_capture and not args.no_graph:
-        layer.x_stage.copy_(x_dev)
-        layer.lg_stage.copy_(lg_dev)
-        graph = layer.capture()
-        for _ in range(3):
-            graph.replay()
-        barrier()
-        timer.steps = timer.steps[-max(args.warmup - args.warmup // 2, 1):]
-    else:
-        timer = StageTimer()
-    sampler.wait_first()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    mark_lo = sampler.mark()
-    e0.record()
-    if graph is not None:
-        for _ in range(args.steps):
-            graph.replay()
-    else:
-        for _ in range(args.steps):
-            layer.forward(x_dev, lg_dev, stage_timer=timer)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1) / args.steps
-    layer.check_status()
+    head = run_workload(args.workload, shp, args, dev, rank, world, sampler, steps=args.steps, warmup=args.warmup)
+    subs = []
+    if args.sub.lower() != "none":
+        for key in [k.strip() for k in args.sub.split(",") if k.strip()]:
+            if key == args.workload or key not in synth.SHAPES:
+                continue
+            s_shp = synth.shape(key)
+            if world > 1 and s_shp.parallelism != "tp" and s_shp.experts % world:
+                continue
+            sub_steps = max(args.steps // 2, 5)
+            subs.append(compact(run_workload(key, s_shp, args, dev, rank, world, sampler, steps=sub_steps,
+                                             warmup=args.warmup)))
+    sampler.stop()
 
-    # ---------------- end-to-end leg: host buffers in, host buffer out ----------------
-    for _ in range(min(args.warmup, 5)):
-        layer.forward_host(x_host, lg_host, out_host)
-    barrier()
-    h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_steps = max(args.steps // 2, 1)
-    barrier()
-    h0.record()
-    for _ in range(e2e_steps):
-        layer.forward_host(x_host, lg_host, out_host)
-    h1.record()
-    barrier()
-    ms_e2e = h0.elapsed_time(h1) / e2e_steps
-    clocks = sampler.stop(mark_lo, sampler.mark())   # both timed legs run between the marks
-
-    if world > 1:
-        tmax = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
-        torch.distributed.all_reduce(tmax, op=torch.distributed.ReduceOp.MAX)
-        ms, ms_e2e = tmax.tolist()
-
-    stages = timer.mean_ms()
-    peaks = load_peaks()
-    stats = layer.work_stats()   # algorithmic bytes / flops of the dominant kernel on this rank
+    failed = []
     if rank == 0:
-        # tensor parallelism replicates the tokens (strong scaling); expert parallelism gives every rank its own batch
-        tp = world > 1 and shp.parallelism == "tp"
-        total_tokens = shp.tokens if tp else shp.tokens * world
-        dom = stats["dominant"]
-        dom_ms = stages.get(dom["stage"], float("nan"))
-        if dom["bound"] == "hbm":
-            achieved = dom["bytes"] / (dom_ms * 1e-3) / 1e9
-            peak, unit = peaks["hbm_gbs"], "GB/s"
-        else:
-            achieved = dom["flops"] / (dom_ms * 1e-3) / 1e12
-            peak, unit = peaks["bf16_tflops"] * dom["bf16_rate_multiple"], "TFLOP/s"
-        # DRAM bytes per FC1 launch: ncu on the 32-expert case of this workload read 1.014 x the
-        # algorithmic bytes (dram__bytes_read + write; summary under profiles/); every active
-        # expert's weights are read once per launch, so the traffic scales with the algorithmic bytes
-        traffic = dom["bytes"] * NCU_FC1_TRAFFIC_RATIO if (dom["bound"] == "hbm" and shp.recipe == "nvfp4") else None
-        line = {
-            "metric": "moe_layer_tokens_per_s", "value": total_tokens / (ms * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": dtype_of(shp),
-            "data": "synthetic", "config": config_of(shp, world, args.ep, graph is not None), "clocks": clocks,
-            "e2e": {"value": total_tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": x_host.numel() * 2 + lg_host.numel() * 4,
-                    "d2h_bytes_per_step": out_host.numel() * 2},
-            "gpu_launches": args.steps * layer.kernels_per_step,
-            "tflops": shp.flops * (1 if tp else world) / (ms * 1e-3) / 1e12,
-            "stage_ms": stages,
-            "roofline": {"kernel": dom["kernel"], "bound": dom["bound"], "achieved": achieved, "peak": peak,
-                         "unit": unit, "frac": achieved / peak, "peak_source": peaks["source"] + dom.get("peak_note", ""),
-                         "traffic": traffic, "algorithmic_bytes": dom["bytes"],
-                         "algorithmic_flops": dom["flops"], "ms_per_launch": dom_ms,
-                         "active_experts": stats.get("active_experts")},
-        }
-        if not args.no_cpu_baseline:
+        line = {"metric": "moe_layer_tokens_per_s", "value": head["value"], "unit": head["unit"], "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": head["ms_per_step"],
+                "higher_is_better": True, "scaling": head["scaling"], "vs_baseline": None, "dtype": head["dtype"],
+                "data": "synthetic"}
+        line.update({k: head[k] for k in ("config", "clocks", "e2e", "gpu_launches", "tflops", "stage_ms",
+                                          "roofline", "step_roofline", "parity_sample")})
+        line["workloads"] = subs
+        if not args.no_cpu_baseline and world == 1:
             cores = os.cpu_count() or 1
             torch.set_num_threads(cores)
-            n_e = min(args.cpu_experts, shp.experts)
-            inp_cpu = cpu_inputs(shp, n_e, seed=0)
-            from oracle import moe_oracle as O
-            if shp.router == "sigmoid":
-                _, ids, w = O.route_topk(inp_cpu.router_logits, shp.topk, mode="sigmoid", route_scale=shp.route_scale)
-            else:
-                _, ids, w = O.route_topk(inp_cpu.router_logits, shp.topk)
+            inp, ids, w, lo, n_e = cpu_sample_inputs(shp, args.cpu_experts or CPU_EXPERTS.get(args.workload, 8))
             # bounded sample: repeat the pass until about ten seconds of CPU work are on the clock
             total, reps, kept = 0.0, 0, 0
             while total < 10.0 and reps < 64:
-                sec, kept = oracle_sample(shp, inp_cpu, ids, w, n_e)
+                sec, kept = oracle_sample(shp, inp, ids, w, lo, n_e)
                 total += sec
                 reps += 1
             sec = total / reps
-            line["cpu_baseline"] = {
-                "value": (kept / shp.topk) / sec, "unit": "tokens/s", "cores": cores, "kind": "port",
-                "seconds": total, "passes": reps,
-                "sample": f"routes of one {shp.tokens}-token batch that land on experts 0..{n_e - 1} "
-                          f"({kept} of {shp.rows} routed rows), {reps} passes; tokens = rows / top-k"}
+            line["cpu_baseline"] = {"value": (kept / shp.topk) / sec, "unit": "tokens/s", "cores": cores,
+                                    "kind": "port", "seconds": total, "passes": reps,
+                                    "sample": sample_text(shp, lo, n_e, kept) + f", {reps} passes"}
         print(json.dumps(line), flush=True)
+        for rec in [head] + subs:
+            p = rec.get("parity_sample")
+            if p is not None and not p["ok"]:
+                failed.append((rec.get("workload") or rec["config"]["workload"], p))
     if world > 1:
         torch.distributed.destroy_process_group()
+    if failed:
+        print(f"parity sample failed: {failed}", file=sys.stderr)
+        raise SystemExit(3)
 
 
 if __name__ == "__main__":

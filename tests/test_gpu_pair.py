@@ -1,7 +1,8 @@
 """-m gpu: large NVFP4 batches (several 128-row tiles per expert, odd and even tile counts) against
-the CPU oracle.  In-process they run on the wide single-CTA kernels; `test_pair_variant...` re-runs
-this file in a child process with B200MOE_PAIR=1, which puts the same cases on the CTA-pair kernels
-(tcgen05 cta_group::2)."""
+the CPU oracle.  In-process the library picks the kernel itself (plans that average two or more row
+tiles per expert run on the CTA-pair kernels, tcgen05 cta_group::2); `test_both_kernel_families...`
+re-runs this file in child processes with B200MOE_PAIR=1 and =0, which forces every case onto the
+CTA-pair and onto the single-CTA kernels."""
 
 import os
 import subprocess
@@ -46,11 +47,12 @@ def test_pair_repeat_runs_bitwise_identical():
     assert torch.equal(a.out, b.out) and torch.equal(a.out_f32, b.out_f32)
 
 
-@pytest.mark.timeout(600)
-def test_pair_variant_passes_these_cases():
-    if os.environ.get("B200MOE_PAIR") == "1":
-        pytest.skip("already the child run")
-    env = dict(os.environ, B200MOE_PAIR="1")
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("forced", ["1", "0"])
+def test_both_kernel_families_pass_these_cases(forced):
+    if os.environ.get("B200MOE_PAIR") is not None:
+        pytest.skip("already a child run")
+    env = dict(os.environ, B200MOE_PAIR=forced)
     r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-m", "gpu", "-x", "-q", "-p", "no:cacheprovider"],
-                       env=env, capture_output=True, text=True, timeout=550)
+                       env=env, capture_output=True, text=True, timeout=800)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
