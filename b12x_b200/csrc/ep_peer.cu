@@ -271,13 +271,21 @@ extern "C" int b200moe_ep_combine(const b200moe_ep_combine_args* a, void* stream
     return B200MOE_EINVAL;
   if ((reinterpret_cast<uintptr_t>(a->out) & 7) != 0 || (a->out_row_stride % 4) != 0) return B200MOE_EALIGN;
   if (a->num_tokens * a->num_topk > a->layout->rows) return B200MOE_ECAPACITY;
-  if (a->num_tokens == 0) return B200MOE_OK;
   PeerPtrs arenas, sig = {};
   if (!fill_peers(arenas, a->peer_scratch, a->world)) return B200MOE_EINVAL;
   if (a->wait_flags != nullptr) {
     if (a->epoch_dev == nullptr || a->timeout_ms < 0 || a->timeout_ms > 10000 ||
         !fill_peers(sig, a->signal_flags, a->world))
       return B200MOE_EINVAL;
+  }
+  if (a->num_tokens == 0) {
+    // a rank without tokens of its own still owes its peers the "my FC2 rows are complete" signal
+    // when the hand-shake rides in this call (they would otherwise wait out their limit)
+    if (a->wait_flags != nullptr) {
+      ep_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(sig, a->world, a->rank, 0, a->epoch_dev);
+      return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+    }
+    return B200MOE_OK;
   }
   const unsigned long long limit_ns =
       a->timeout_ms > 0 ? static_cast<unsigned long long>(a->timeout_ms) * 1000000ull : kWaitLimitNs;

@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(128) route_topk_kernel(b200moe_route_args a) {
 constexpr int kSortThreads = 1024;
 
 __global__ void __launch_bounds__(kSortThreads) expert_sort_kernel(
-    const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map,
+    const int32_t* topk_ids, const int32_t* __restrict__ expert_map,
     int expert_map_len, int rows, int E, int32_t* __restrict__ status,
     int32_t* __restrict__ expert_counts, int32_t* __restrict__ expert_offsets,
     int32_t* __restrict__ tile_base, int32_t* __restrict__ mtile_expert,
@@ -188,8 +188,10 @@ __global__ void __launch_bounds__(kSortThreads) expert_sort_kernel(
   const int r_begin = warp < nwarps ? warp * chunk : rows;   // the other warps own no routes
   const int r_end = min(rows, r_begin + chunk);
 
+  // The ids may have been stored by peer GPUs while this kernel was already resident (it then
+  // spun on their flags above): they are read past L1 and never through the read-only path.
   auto local_expert = [&](int r) -> int {
-    int e = topk_ids[r];
+    int e = __ldcg(topk_ids + r);
     if (expert_map != nullptr) e = (e >= 0 && e < expert_map_len) ? expert_map[e] : -1;
     return (e >= 0 && e < E) ? e : -1;
   };

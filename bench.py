@@ -260,55 +260,12 @@ def run_reference(args, shp):
 
 
 def parity_sample(layer) -> dict:
-    """Check the last step of ``layer`` against the CPU oracle on a sample.
-
-    The whole permutation the kernels left in the scratch arena is compared bit for bit with the
-    oracle's canonical one; the per-route FC2 rows (fp32, before router weights) of up to
-    ``PARITY_ROWS_PER_EXPERT`` routes of ``PARITY_EXPERTS`` experts are compared with the oracle's."""
-    from oracle import moe_oracle as O
-    b = layer.last_binding
-    inp = layer.inputs
-    shp = replace(inp.shape, experts=b.weight_E)
-    torch.cuda.synchronize(b.device)
-    ids_dev = b.topk_ids
-    tokens, k = ids_dev.shape
-    ids = ids_dev.cpu()
-    emap = None if b.route_expert_map is None else b.route_expert_map.cpu()
-    srt = O.expert_sort(ids, b.weight_E, emap, tile_rows=int(b.core_layout.tile_rows))
-    kept = int(srt.sorted_route_ids.numel())
-    perm_ok = bool(torch.equal(b.packed_route_indices[:kept].cpu(), srt.sorted_route_ids)
-                   and torch.equal(b.inv_perm.cpu(), srt.inv_perm)
-                   and torch.equal(b.expert_counts.cpu(), srt.expert_counts))
-    active = [e for e in range(b.weight_E) if int(srt.expert_counts[e]) > 0]
-    if not active:
-        return {"experts": 0, "rows": 0, "permutation_rows": kept, "permutation_ok": perm_ok,
-                "max_abs_over_rms": 0.0, "ok": perm_ok}
-    step = max(len(active) // PARITY_EXPERTS, 1)
-    chosen = active[::step][:PARITY_EXPERTS]
-    pos, local = [], []
-    for j, e in enumerate(chosen):
-        lo, hi = int(srt.expert_offsets[e]), int(srt.expert_offsets[e + 1])
-        n = min(hi - lo, PARITY_ROWS_PER_EXPERT)
-        pos.extend(range(lo, lo + n))
-        local.extend([j] * n)
-    pos_t = torch.tensor(pos, dtype=torch.int64)
-    tok = (srt.sorted_route_ids.to(torch.int64)[pos_t] // k).to(b.device)
-    x_sub = b.a.index_select(0, tok).cpu()
-    got = b.route_output.index_select(0, pos_t.to(b.device)).cpu()
-    sel = torch.tensor(chosen, dtype=torch.int64)
-    cpu = lambda t: t.index_select(0, sel.to(t.device)).cpu()
-    taps = O.MoETaps()
-    n = len(pos)
-    _oracle_call(shp, x_sub, cpu(inp.w1_fp4), cpu(inp.w1_blockscale), cpu(inp.w1_global_scale), cpu(inp.w2_fp4),
-                 cpu(inp.w2_blockscale), cpu(inp.w2_global_scale), cpu(inp.a1_gscale), cpu(inp.a2_gscale),
-                 torch.tensor(local, dtype=torch.int32).reshape(n, 1), torch.ones(n, 1), taps=taps)
-    # the sub-batch is ordered by (expert, position), which the oracle's stable sort keeps
-    ref = taps.routed
-    rms = ref.square().mean().sqrt().item()
-    err = (got - ref).abs().max().item()
-    ratio = err / max(rms, 1e-30)
-    return {"experts": len(chosen), "rows": n, "permutation_rows": kept, "permutation_ok": perm_ok,
-            "max_abs_over_rms": ratio, "tolerance": PARITY_TOL, "ok": bool(perm_ok and ratio <= PARITY_TOL)}
+    """Check the last step of ``layer`` against the CPU oracle on a sample: the whole permutation
+    bit for bit, and the activation codes and fp32 FC2 rows of up to ``PARITY_ROWS_PER_EXPERT``
+    routes of ``PARITY_EXPERTS`` experts (``tests/gpu_utils.sampled_parity``)."""
+    from tests.gpu_utils import sampled_parity
+    return sampled_parity(layer.last_binding, layer.inputs, experts=PARITY_EXPERTS,
+                          rows_per_expert=PARITY_ROWS_PER_EXPERT, tolerance=PARITY_TOL)
 
 
 # ---------------------------------------------------------------------------------------------

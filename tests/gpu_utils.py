@@ -104,3 +104,91 @@ def oracle_layer(inp: synth.MoEInputs, ids, weights, expert_map=None):
         out = O.moe_w4a8_mx(inp.x, inp.w1_fp4, inp.w1_blockscale, ones, inp.w2_fp4, inp.w2_blockscale, ones,
                             ids, weights, activation=shp.activation, expert_map=expert_map, taps=taps)
     return out, taps
+
+
+def oracle_call(shp, x, w1, s1, g1, w2, s2, g2, a1, a2, ids, weights, expert_map=None, taps=None):
+    """The oracle layer for ``shp.recipe`` on explicit tensors (source-format weights)."""
+    if shp.recipe == "nvfp4":
+        return O.moe_nvfp4(x, w1, s1, g1 / a1, w2, s2, g2 / a2, a1, a2, ids, weights, activation=shp.activation,
+                           expert_map=expert_map, taps=taps)
+    if shp.recipe == "w4a16":
+        return O.moe_w4a16(x, w1, s1, g1, w2, s2, g2, ids, weights, activation=shp.activation,
+                           expert_map=expert_map, taps=taps)
+    ones = torch.ones(w1.shape[0])
+    return O.moe_w4a8_mx(x, w1, s1, ones, w2, s2, ones, ids, weights, activation=shp.activation,
+                         expert_map=expert_map, taps=taps)
+
+
+def sampled_parity(binding, inp: synth.MoEInputs, *, experts: int = 4, rows_per_expert: int = 48,
+                   tolerance: float = 1e-2) -> dict:
+    """Check what the last ``run`` of ``binding`` left in its scratch arena against the CPU oracle.
+
+    Full-size shapes are too large for the oracle as a whole, so: (1) the WHOLE permutation
+    (sorted route ids, inverse permutation, per-expert counts) is compared bit for bit with the
+    oracle's canonical sort; (2) for up to ``rows_per_expert`` routes of ``experts`` experts (spread
+    over the experts that received rows) the oracle evaluates the route from the input row on: the
+    activation codes and scale bytes must be bit-identical, the fp32 FC2 rows (alpha applied,
+    router weight not) within ``tolerance`` x their RMS.  ``inp`` holds the source-format weights of
+    the experts this binding's layer owns (in its local numbering)."""
+    b = binding
+    shp = inp.shape
+    torch.cuda.synchronize(b.device)
+    tokens, k = b.topk_ids.shape
+    ids = b.topk_ids.cpu()
+    emap = None if b.route_expert_map is None else b.route_expert_map.cpu()
+    srt = O.expert_sort(ids, b.weight_E, emap, tile_rows=int(b.core_layout.tile_rows))
+    kept = int(srt.sorted_route_ids.numel())
+    perm_ok = bool(torch.equal(b.packed_route_indices[:kept].cpu(), srt.sorted_route_ids)
+                   and torch.equal(b.inv_perm.cpu(), srt.inv_perm)
+                   and torch.equal(b.expert_counts.cpu(), srt.expert_counts))
+    active = [e for e in range(b.weight_E) if int(srt.expert_counts[e]) > 0]
+    res = {"experts": 0, "rows": 0, "permutation_rows": kept, "permutation_ok": perm_ok, "codes_ok": True,
+           "max_abs_over_rms": 0.0, "tolerance": tolerance, "ok": perm_ok}
+    if not active or experts <= 0:
+        return res
+    step = max(len(active) // experts, 1)
+    chosen = active[::step][:experts]
+    pos, local = [], []
+    for j, e in enumerate(chosen):
+        lo, hi = int(srt.expert_offsets[e]), int(srt.expert_offsets[e + 1])
+        n = min(hi - lo, rows_per_expert)
+        pos.extend(range(lo, lo + n))
+        local.extend([j] * n)
+    n = len(pos)
+    pos_t = torch.tensor(pos, dtype=torch.int64)
+    pos_d = pos_t.to(b.device)
+    tok = (srt.sorted_route_ids.to(torch.int64)[pos_t] // k).to(b.device)
+    x_sub = b.a.index_select(0, tok).cpu()
+    got = b.route_output.index_select(0, pos_d).cpu()
+    sel = torch.tensor(chosen, dtype=torch.int64)
+    pick = lambda t: t.index_select(0, sel.to(t.device)).cpu()
+    taps = O.MoETaps()
+    # the sub-batch is ordered by (expert, position), which the oracle's stable sort keeps
+    oracle_call(shp, x_sub, pick(inp.w1_fp4), pick(inp.w1_blockscale), pick(inp.w1_global_scale),
+                pick(inp.w2_fp4), pick(inp.w2_blockscale), pick(inp.w2_global_scale), pick(inp.a1_gscale),
+                pick(inp.a2_gscale), torch.tensor(local, dtype=torch.int32).reshape(n, 1), torch.ones(n, 1), taps=taps)
+    codes_ok = True
+    if taps.act_codes is not None:
+        codes_ok = bool(torch.equal(b.packed_input.index_select(0, pos_d).cpu(), taps.act_codes))
+    ref = taps.routed
+    rms = ref.square().mean().sqrt().item()
+    ratio = (got - ref).abs().max().item() / max(rms, 1e-30)
+    res.update(experts=len(chosen), rows=n, codes_ok=codes_ok, max_abs_over_rms=ratio,
+               ok=bool(perm_ok and codes_ok and ratio <= tolerance))
+    return res
+
+
+def combine_matches(binding, topk_weights: torch.Tensor, out_bf16: torch.Tensor, tokens: int = 128) -> bool:
+    """The weighted combine of the first ``tokens`` tokens, recomputed on the CPU from the fp32 FC2
+    rows the kernels left behind (products and sums in slot order, one bf16 rounding): bit-equal."""
+    b = binding
+    t = min(tokens, b.tokens)
+    k = b.num_topk
+    inv = b.inv_perm[: t * k].to(torch.int64)
+    rows = b.route_output.index_select(0, inv.clamp(min=0)).cpu().reshape(t, k, -1)
+    ok = (inv >= 0).cpu().reshape(t, k, 1)
+    w = topk_weights[:t].cpu().float().reshape(t, k, 1)
+    acc = torch.zeros(t, rows.shape[-1])
+    for s in range(k):
+        acc = acc + torch.where(ok[:, s], rows[:, s] * w[:, s], torch.zeros_like(rows[:, s]))
+    return bool(torch.equal(acc.to(torch.bfloat16), out_bf16[:t].cpu()))

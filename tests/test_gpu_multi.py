@@ -1,5 +1,5 @@
 """-m gpu, needs >= 2 GPUs: expert-parallel and tensor-parallel layers as one process per GPU over
-NCCL, against the single-process CPU oracle."""
+NCCL, against the single-process CPU oracle, at 2, 4 and 8 ranks (as many as the box has)."""
 
 import os
 import socket
@@ -60,13 +60,13 @@ def _worker(rank: int, world: int, port: int, mode: str, ret: dict):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("mode", ["ep", "tp"])
-@pytest.mark.timeout(600)
-def test_two_rank_layer_matches_oracle(mode):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    world = 2
+@pytest.mark.timeout(900)
+def test_multi_rank_layer_matches_oracle(mode, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     with mp.Manager() as mgr:
         ret = mgr.dict()
         mp.spawn(_worker, args=(world, _free_port(), mode, ret), nprocs=world, join=True)
-        assert dict(ret) == {0: True, 1: True}
+        assert dict(ret) == {r: True for r in range(world)}

@@ -1,5 +1,7 @@
 """-m gpu, needs >= 2 GPUs: expert parallelism with this library's own dispatch / combine kernels
-over NVLink peer memory, against the single-process CPU oracle, several steps in a row."""
+over NVLink peer memory, against the single-process CPU oracle, several steps in a row, at 2, 4
+and 8 ranks, with the cross-rank waits as launches of their own and folded into the sort and the
+combine kernel (B200MOE_FOLD_WAITS=1).  Peer memory is only touched with plain loads / stores."""
 
 import os
 
@@ -14,8 +16,9 @@ from tests.test_gpu_multi import _free_port
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank: int, world: int, port: int, ret: dict):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+def _worker(rank: int, world: int, port: int, fold: str, ret: dict):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      B200MOE_FOLD_WAITS=fold, NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     from b12x_b200.moe.distributed import init_process_group
@@ -74,12 +77,13 @@ def _worker(rank: int, world: int, port: int, ret: dict):
         dist.destroy_process_group()
 
 
-@pytest.mark.timeout(600)
-def test_peer_memory_expert_parallel_matches_oracle():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    world = 2
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("fold", ["0", "1"])
+@pytest.mark.timeout(900)
+def test_peer_memory_expert_parallel_matches_oracle(fold, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     with mp.Manager() as mgr:
         ret = mgr.dict()
-        mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
-        assert dict(ret) == {0: True, 1: True}
+        mp.spawn(_worker, args=(world, _free_port(), fold, ret), nprocs=world, join=True)
+        assert dict(ret) == {r: True for r in range(world)}
