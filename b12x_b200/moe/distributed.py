@@ -16,7 +16,9 @@ the caller sum partial outputs (b12x/moe/ep_moe/_impl.py:1-14).
 from __future__ import annotations
 
 import os
+import time
 from dataclasses import replace
+from datetime import timedelta
 
 import torch
 import torch.distributed as dist
@@ -29,13 +31,91 @@ _ACT_API = {"silu": "silu", "relu2": "relu2", "swigluoai": "swigluoai_uninterlea
 _SOURCE = {"nvfp4": "modelopt_nvfp4", "w4a16": "modelopt_nvfp4", "w4a8_mx": "fp4_e8m0_k32"}
 
 
-def init_process_group(device: torch.device) -> None:
+def init_process_group(device: torch.device, timeout_s: float | None = None) -> None:
+    """One process per GPU over NCCL (gloo for CPU ranks).  ``timeout_s`` bounds every collective:
+    a rank that never joins one ends it with an error on the others instead of a hang."""
     if dist.is_initialized():
         return
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     backend = "nccl" if device.type == "cuda" else "gloo"
     kw = {"device_id": device} if device.type == "cuda" else {}
+    if timeout_s is not None:
+        kw["timeout"] = timedelta(seconds=float(timeout_s))
     dist.init_process_group(backend=backend, **kw)
+
+
+# ---------------------------------------------------------------------------------------------
+# host-side failure detection (no device involvement: everything here runs before a launch)
+# ---------------------------------------------------------------------------------------------
+ERR_OVERFLOW = 1      # a rank would receive more rows than its receive capacity
+ERR_BAD_TABLE = 2     # a rank's split table is malformed
+
+
+def validate_split_tables(send_counts, recv_counts, world: int, max_send_rows: int) -> None:
+    """Shape and range checks of one rank's split tables (rows it sends to / receives from every
+    rank).  Raises ``ValueError`` naming the defect."""
+    for name, tab in (("send", send_counts), ("recv", recv_counts)):
+        if len(tab) != world:
+            raise ValueError(f"{name} split table has {len(tab)} entries for {world} ranks")
+        if any(int(c) < 0 for c in tab):
+            raise ValueError(f"{name} split table holds a negative count: {list(tab)}")
+    if sum(int(c) for c in send_counts) > max_send_rows:
+        raise ValueError(f"send split table sums to {sum(send_counts)} rows, this rank has {max_send_rows}")
+
+
+def agree_on_error(code: int, device: torch.device) -> int:
+    """All ranks learn the largest error code any of them raised (one tiny all-reduce): a failure
+    that one rank sees on the host becomes an exception on every rank BEFORE any of them enters the
+    row exchange, instead of leaving the others inside a collective that never completes."""
+    flag = torch.tensor([int(code)], dtype=torch.int32, device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    return int(flag.item())
+
+
+def check_same_plan(signature: tuple, device: torch.device) -> None:
+    """Every rank must have built the layer from the same plan (shape, top-k, expert count,
+    recipe ...).  Raises ``ValueError`` on all ranks if any two signatures differ."""
+    mine = torch.tensor([int(v) for v in signature], dtype=torch.int64, device=device)
+    world = dist.get_world_size()
+    every = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    base = every[0].tolist()
+    for r, sig in enumerate(every):
+        if sig.tolist() != base:
+            raise ValueError(f"rank {r} planned the layer as {sig.tolist()}, rank 0 as {base}")
+
+
+class PeerLiveness:
+    """Heartbeat over the rendezvous store: every rank records the step it is about to run; before
+    launching, a rank checks that all peers got there too.  A rank that left between steps is found
+    on the host, within ``timeout_s``, with none of this rank's kernels or collectives in flight."""
+
+    def __init__(self, store, rank: int, world: int, *, prefix: str = "b200moe/alive", timeout_s: float = 5.0):
+        self.store, self.rank, self.world = store, rank, world
+        self.prefix, self.timeout_s = prefix, float(timeout_s)
+
+    def beat(self, step: int) -> None:
+        self.store.set(f"{self.prefix}/{self.rank}", str(int(step)))
+
+    def check(self, step: int) -> None:
+        deadline = time.monotonic() + self.timeout_s
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            key = f"{self.prefix}/{r}"
+            while True:
+                seen = -1
+                try:
+                    if self.store.check([key]):
+                        seen = int(self.store.get(key).decode())
+                except (RuntimeError, ValueError):
+                    seen = -1
+                if seen >= step:
+                    break
+                if time.monotonic() > deadline:
+                    raise RuntimeError(f"rank {r} did not reach step {step} within {self.timeout_s:g} s "
+                                       f"(last seen at step {seen})")
+                time.sleep(0.01)
 
 
 def prepare_experts(inp: synth.MoEInputs, dev: torch.device):
@@ -180,6 +260,11 @@ class ExpertParallelMoE(_LayerBase):
         self.recv_out = torch.empty((cap, shp.hidden), dtype=torch.float32, device=dev)
         self.plan, self.scratch = self._local_plan(cap, 1)
         self.kernels_per_step = 9  # route, rank sort, gather, expert sort, quant, gemm1, gemm2, un-permute, combine
+        self.bounded_capacity = recv_capacity_factor is not None
+        self.liveness: PeerLiveness | None = None     # set by the caller to have peers checked before every step
+        self.step = 0
+        check_same_plan((shp.tokens, shp.hidden, shp.intermediate, shp.experts, shp.topk,
+                         sorted(synth.SHAPES_RECIPES).index(shp.recipe), cap), dev)
 
     @property
     def can_capture(self) -> bool:
@@ -211,6 +296,11 @@ class ExpertParallelMoE(_LayerBase):
             return fused_moe.run(binding=b, stage_timer=stage_timer)
         shp = self.shape
         home = self.home
+        if self.liveness is not None:
+            # a peer that left since the last step is found here, on the host, before anything is launched
+            self.liveness.beat(self.step)
+            self.liveness.check(self.step)
+        self.step += 1
         home.sort(self.topk_ids, self.rank_of_expert)
         send_counts = home.group_counts
         recv_counts = split_counts_exchange(send_counts)
@@ -218,8 +308,22 @@ class ExpertParallelMoE(_LayerBase):
         counts = torch.stack([send_counts, recv_counts]).cpu()     # the one host sync of the step
         sc, rc = counts[0].tolist(), counts[1].tolist()
         n_send, n_recv = sum(sc), sum(rc)
-        if n_recv > self.recv_cap:
-            raise RuntimeError(f"received {n_recv} rows, capacity {self.recv_cap}")
+        if self.bounded_capacity:
+            # With a receive capacity below the worst case a rank can overflow.  The decision to stop
+            # is collective: every rank raises, none is left inside the row exchange.
+            code = 0
+            try:
+                validate_split_tables(sc, rc, self.world, shp.tokens * shp.topk)
+            except ValueError:
+                code = ERR_BAD_TABLE
+            if n_recv > self.recv_cap:
+                code = max(code, ERR_OVERFLOW)
+            worst = agree_on_error(code, self.dev)
+            if worst == ERR_OVERFLOW:
+                raise RuntimeError(f"a rank would receive more rows than its capacity (this rank: "
+                                   f"{n_recv} of {self.recv_cap}); no row was exchanged")
+            if worst != 0:
+                raise RuntimeError("a rank's split table is malformed; no row was exchanged")
         dist.all_to_all_single(self.recv_rows[:n_recv], self.send_rows[:n_send], rc, sc)
         dist.all_to_all_single(self.recv_ids.view(-1)[:n_recv], self.send_ids[:n_send], rc, sc)
         if n_recv > 0:

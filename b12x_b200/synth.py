@@ -60,6 +60,9 @@ SHAPES = {
 }
 
 
+SHAPES_RECIPES = ("nvfp4", "w4a16", "w4a8_mx")
+
+
 def shape(key: str, **overrides) -> MoEShape:
     return replace(SHAPES[key], **overrides)
 
