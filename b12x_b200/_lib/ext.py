@@ -13,7 +13,7 @@ _LIB_PATH = Path(__file__).resolve().parents[1] / "csrc" / "libb200moe.so"
 _lib = None
 
 RECIPES = {"nvfp4": 0, "w4a8_mx": 1, "w4a16": 2}
-ACTIVATIONS = {"silu": 0, "relu2": 1, "swigluoai": 2}
+ACTIVATIONS = {"silu": 0, "relu2": 1, "swigluoai": 2, "situ": 3}
 ROUTE_MODES = {"softmax_topk": 0, "raw": 1, "sigmoid": 2}
 
 OK, EINVAL, ECAPACITY, ECUDA, EUNSUPPORTED, EALIGN = 0, -1, -2, -3, -4, -5
@@ -45,6 +45,20 @@ class RouteArgs(C.Structure):
                 ("num_tokens", C.c_int32), ("num_experts", C.c_int32), ("num_topk", C.c_int32),
                 ("logits_dtype", C.c_int32), ("mode", C.c_int32), ("renormalize", C.c_int32),
                 ("route_scale", C.c_float), ("reserved", C.c_int32)]
+
+
+class GateRouteArgs(C.Structure):
+    _fields_ = [("hidden", C.c_void_p), ("gate_weight", C.c_void_p), ("gate_bias", C.c_void_p),
+                ("logits_out", C.c_void_p), ("tile_counters", C.c_void_p), ("selection_bias", C.c_void_p),
+                ("topk_logits", C.c_void_p), ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p),
+                ("status", C.c_void_p), ("hidden_row_stride", C.c_int64),
+                ("num_tokens", C.c_int32), ("num_experts", C.c_int32), ("hidden_size", C.c_int32),
+                ("num_topk", C.c_int32), ("hidden_dtype", C.c_int32), ("weight_dtype", C.c_int32),
+                ("bias_dtype", C.c_int32), ("mode", C.c_int32), ("renormalize", C.c_int32),
+                ("route_scale", C.c_float), ("kernel", C.c_int32), ("reserved", C.c_int32)]
+
+
+GATE_KERNELS = {"auto": 0, "simt": 1, "tc": 2}
 
 
 class SortArgs(C.Structure):
@@ -129,6 +143,7 @@ EXPORTS = {
     "b200moe_query_device": ([C.c_int, C.POINTER(DeviceInfo)], C.c_int),
     "b200moe_scratch_nbytes": ([C.POINTER(CapsC), C.POINTER(ScratchLayout)], C.c_int),
     "b200moe_route_topk": ([C.POINTER(RouteArgs), C.c_void_p], C.c_int),
+    "b200moe_gate_route": ([C.POINTER(GateRouteArgs), C.c_void_p], C.c_int),
     "b200moe_expert_sort": ([C.POINTER(SortArgs), C.c_void_p], C.c_int),
     "b200moe_expert_sort_static": ([C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p], C.c_int),
@@ -167,7 +182,7 @@ def load():
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = restype
-    if lib.b200moe_abi_version() != 2:
+    if lib.b200moe_abi_version() != 3:
         raise RuntimeError("libb200moe.so ABI version mismatch; rebuild it")
     _lib = lib
     return lib

@@ -1,10 +1,13 @@
-"""Caller-owned scratch specs (same contract as the reference's ``b12x/_lib/scratch.py:12-77``):
-a plan names ONE contiguous uint8 buffer; the caller allocates it, ``bind`` only views it."""
+"""Caller-owned scratch: a plan names ONE contiguous uint8 buffer, the caller allocates it, ``bind``
+only takes views of it.  The public names and the accepted container forms are the contract of the
+reference's ``b12x/_lib/scratch.py:12-77`` (a tensor, a mapping by spec name, or a one-element
+sequence); the checking itself is this library's."""
 
 from __future__ import annotations
 
 from collections.abc import Mapping, Sequence
 from dataclasses import dataclass
+from math import prod
 
 import torch
 
@@ -18,38 +21,47 @@ class ScratchBufferSpec:
 
     @property
     def nbytes(self) -> int:
-        numel = 1
-        for dim in self.shape:
-            numel *= int(dim)
-        return numel * torch.empty((), dtype=self.dtype).element_size()
+        return prod(int(d) for d in self.shape) * torch.empty((), dtype=self.dtype).element_size()
 
 
 def scratch_buffer_spec(name: str, *, nbytes: int, device: torch.device) -> ScratchBufferSpec:
+    """Spec of an opaque byte buffer (never empty: a zero-byte plan still names one byte)."""
     return ScratchBufferSpec(name=name, shape=(max(int(nbytes), 1),), dtype=torch.uint8, device=device)
 
 
-def scratch_tensor(scratch, specs: tuple[ScratchBufferSpec, ...], *, owner: str) -> torch.Tensor:
-    if len(specs) != 1:
-        raise RuntimeError(f"{owner} scratch plans currently expect exactly one scratch buffer")
-    spec = specs[0]
+def _pick(scratch, name: str) -> torch.Tensor:
+    """The tensor the caller meant, out of the three accepted container forms."""
     if isinstance(scratch, torch.Tensor):
-        tensor = scratch
-    elif isinstance(scratch, Mapping):
-        if spec.name not in scratch:
-            raise KeyError(f"scratch mapping is missing {spec.name!r}")
-        tensor = scratch[spec.name]
-    elif isinstance(scratch, Sequence):
-        if len(scratch) != 1:
-            raise ValueError(f"scratch sequence must contain exactly one tensor, got {len(scratch)}")
-        tensor = scratch[0]
-    else:
-        raise TypeError("scratch must be a tensor, a mapping or a sequence of tensors")
-    if tensor.dtype != spec.dtype:
-        raise TypeError(f"{spec.name} scratch must have dtype {spec.dtype}, got {tensor.dtype}")
-    if tensor.device != spec.device:
-        raise ValueError(f"{spec.name} scratch device {tensor.device} does not match {spec.device}")
-    if int(tensor.numel()) < int(spec.shape[0]):
-        raise ValueError(f"{spec.name} scratch has {int(tensor.numel())} bytes, requires {int(spec.shape[0])}")
-    if not tensor.is_contiguous():
-        raise ValueError(f"{spec.name} scratch must be contiguous")
-    return tensor.reshape(-1)
+        return scratch
+    if isinstance(scratch, Mapping):
+        try:
+            return scratch[name]
+        except KeyError:
+            raise KeyError(f"scratch mapping has no entry {name!r}") from None
+    if isinstance(scratch, Sequence):
+        if len(scratch) == 1:
+            return scratch[0]
+        raise ValueError(f"a scratch sequence holds exactly one tensor, got {len(scratch)}")
+    raise TypeError(f"scratch must be a tensor, a mapping or a sequence of tensors, not {type(scratch).__name__}")
+
+
+def scratch_tensor(scratch, specs: tuple[ScratchBufferSpec, ...], *, owner: str) -> torch.Tensor:
+    """Resolve and check the caller's buffer against ``specs``; returns it flattened.  Nothing is
+    allocated or copied."""
+    if len(specs) != 1:
+        raise RuntimeError(f"{owner} plans use exactly one scratch buffer, this one names {len(specs)}")
+    (spec,) = specs
+    buf = _pick(scratch, spec.name)
+    problems = []
+    if buf.dtype != spec.dtype:
+        raise TypeError(f"{owner} scratch {spec.name!r} has dtype {buf.dtype}, the plan needs {spec.dtype}")
+    if buf.device != spec.device:
+        problems.append(f"is on {buf.device}, the plan is for {spec.device}")
+    needed = int(spec.shape[0])
+    if buf.numel() < needed:
+        problems.append(f"holds {buf.numel()} bytes, the plan needs {needed}")
+    if not buf.is_contiguous():
+        problems.append("is not contiguous")
+    if problems:
+        raise ValueError(f"{owner} scratch {spec.name!r} " + "; ".join(problems))
+    return buf.reshape(-1)

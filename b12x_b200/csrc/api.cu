@@ -115,7 +115,7 @@ static int check_gemm_args(const b200moe_gemm_args* a) {
     return B200MOE_EINVAL;
   if (a->num_tokens < 0 || a->num_topk <= 0 || a->num_experts <= 0) return B200MOE_EINVAL;
   if (a->num_tokens * a->num_topk > a->layout->rows) return B200MOE_ECAPACITY;
-  if (a->activation < B200MOE_ACT_SILU || a->activation > B200MOE_ACT_SWIGLUOAI)
+  if (a->activation < B200MOE_ACT_SILU || a->activation > B200MOE_ACT_SITU)
     return B200MOE_EINVAL;
   return B200MOE_OK;
 }

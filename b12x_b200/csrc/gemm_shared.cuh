@@ -37,7 +37,7 @@ struct GemmParams {
   int out_atoms;                 // FC1: scale atoms per tile of the output
   int gscale_len;
   float limit, act_alpha, act_beta;
-  int swigluoai;
+  int act_kind;                  // gated FC1: 0 SwiGLU, 1 SwiGLU-OAI, 2 SiTU
 };
 
 struct TileCoord {
@@ -83,7 +83,10 @@ __device__ __forceinline__ float div_rn_normal(float a, float b, float rb) {
   return q;
 }
 
-// GENERIC = false: plain SwiGLU (no clamp); true: clamp and/or the SwiGLU-OAI form, chosen at run time.
+// SiTU (b12x/moe/_shared/kernels/reference.py:160-172): 4 tanh(g / 4) sigmoid(g) * 25 tanh(u / 25)
+constexpr float kSituBeta = 4.0f, kSituLinearBeta = 25.0f;
+
+// GENERIC = false: plain SwiGLU (no clamp); true: clamp and/or the SwiGLU-OAI / SiTU forms, chosen at run time.
 template <bool GENERIC>
 __device__ __forceinline__ float act_gated(float gate, float up, const GemmParams& p) {
   if (GENERIC) {
@@ -91,9 +94,15 @@ __device__ __forceinline__ float act_gated(float gate, float up, const GemmParam
       gate = fminf(gate, p.limit);
       up = fminf(fmaxf(up, -p.limit), p.limit);
     }
-    if (p.swigluoai) {
+    if (p.act_kind == 1) {
       const float s = rcp_newton(1.0f + expf(fminf(-(p.act_alpha * gate), 80.0f)));
       return (gate * s) * (up + p.act_beta);
+    }
+    if (p.act_kind == 2) {
+      const float s = rcp_newton(1.0f + expf(fminf(-gate, 80.0f)));
+      const float sg = __fmul_rn(__fmul_rn(kSituBeta, tanhf(__fdiv_rn(gate, kSituBeta))), s);
+      const float su = __fmul_rn(kSituLinearBeta, tanhf(__fdiv_rn(up, kSituLinearBeta)));
+      return __fmul_rn(sg, su);
     }
   }
   // the exponent is capped so that 1 + e stays finite (sigmoid below 2e-35 instead of 0)

@@ -485,7 +485,7 @@ void fill_common(GemmParams& p, const b200moe_gemm_args* a, char* base) {
   p.limit = a->swiglu_limit;
   p.act_alpha = a->swiglu_alpha;
   p.act_beta = a->swiglu_beta;
-  p.swigluoai = a->activation == B200MOE_ACT_SWIGLUOAI;
+  p.act_kind = a->activation == B200MOE_ACT_SWIGLUOAI ? 1 : (a->activation == B200MOE_ACT_SITU ? 2 : 0);
 }
 
 template <int KIND, int EPI>
@@ -541,7 +541,7 @@ static int gemm1_any(const b200moe_gemm_args* a, cudaStream_t stream) {
     p.n_tiles = ceil_div_i(I, p.n_step);
     p.sub0_base = a->gate_first ? I : 0;   // up rows
     p.sub1_base = a->gate_first ? 0 : I;   // gate rows
-    if (!p.swigluoai && !(p.limit > 0.f))
+    if (p.act_kind == 0 && !(p.limit > 0.f))
       return launch_any<KIND, EPI_FC1_SILU>(bn, tmA, tmA_small, tmB, p, grid, stream);
     return launch_any<KIND, EPI_FC1_GATED>(bn, tmA, tmA_small, tmB, p, grid, stream);
   }

@@ -1010,6 +1010,7 @@ static void fill_common(Params& p, const b200moe_gemm_args* a, char* base) {
 }  // namespace w4a16
 
 int w4a16_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
+  if (a->activation == B200MOE_ACT_SITU) return B200MOE_EUNSUPPORTED;   // no W4A16 oracle for it
   using namespace w4a16;
   const b200moe_scratch_layout& L = *a->layout;
   const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;

@@ -526,7 +526,7 @@ int nvfp4_pair_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
   p.out_cols = I;
   p.out_atoms = ceil_div_i(I, 64);
   const int ctas = a->num_sms > 0 ? a->num_sms : num_sms_cached();
-  if (!p.swigluoai && !(p.limit > 0.f))
+  if (p.act_kind == 0 && !(p.limit > 0.f))
     return pair::launch<EPI_FC1_SILU>(tmA, tmB, p, ctas, stream);
   return pair::launch<EPI_FC1_GATED>(tmA, tmB, p, ctas, stream);
 }

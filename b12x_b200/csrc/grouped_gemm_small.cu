@@ -473,7 +473,7 @@ int nvfp4_small_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
   p.out_cols = I;
   p.out_atoms = I / 64;
   const int grid = a->num_sms > 0 ? a->num_sms : num_sms_cached();
-  if (!p.swigluoai && !(p.limit > 0.f)) return small::launch<EPI_FC1_SILU>(tmW, tmX, p, grid, stream);
+  if (p.act_kind == 0 && !(p.limit > 0.f)) return small::launch<EPI_FC1_SILU>(tmW, tmX, p, grid, stream);
   return small::launch<EPI_FC1_GATED>(tmW, tmX, p, grid, stream);
 }
 

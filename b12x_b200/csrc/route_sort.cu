@@ -1,129 +1,15 @@
 // Stage 1 (top-k routing) and stage 2 (stable expert sort) of the fused MoE layer.
 // Both are tiny integer/compare kernels; the sort is a single-CTA stable counting sort so that
 // the permutation is canonical: positions ordered by (expert asc, flat route id asc).
-#include "common.cuh"
+#include "route_shared.cuh"
 
 namespace b200moe {
-
-// ------------------------------------------------------------------------------------------
-// route_topk: one warp per token.  Lane l holds experts l, l+32, ... (E <= 1024 -> 32 values).
-// Selection repeats "max, ties to the LARGEST expert index" k times, which is the tie rule of
-// the reference router (b12x/moe/_shared/routing.py:38-46).
-// ------------------------------------------------------------------------------------------
-constexpr int kRouteMaxPerLane = 32;  // 1024 experts
 
 template <int MODE>
 __global__ void __launch_bounds__(128) route_topk_kernel(b200moe_route_args a) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
   if (warp >= a.num_tokens) return;
-  const int E = a.num_experts;
-  const int per_lane = (E + 31) >> 5;
-  const float NEG_INF = __int_as_float(0xff800000);
-
-  float raw[kRouteMaxPerLane];  // raw logit
-  float sel[kRouteMaxPerLane];  // value used for selection
-#pragma unroll
-  for (int i = 0; i < kRouteMaxPerLane; ++i) {
-    raw[i] = NEG_INF;
-    sel[i] = NEG_INF;
-    if (i < per_lane) {
-      const int e = i * 32 + lane;
-      if (e < E) {
-        float v;
-        if (a.logits_dtype == B200MOE_DT_BF16) {
-          v = __bfloat162float(
-              reinterpret_cast<const __nv_bfloat16*>(a.logits)[warp * a.logits_row_stride + e]);
-        } else {
-          v = reinterpret_cast<const float*>(a.logits)[warp * a.logits_row_stride + e];
-        }
-        raw[i] = v;
-        if (MODE == B200MOE_ROUTE_SIGMOID) {
-          const float s = 1.0f / (1.0f + expf(-v));
-          raw[i] = s;  // "original score"
-          sel[i] = a.bias ? s + a.bias[e] : s;
-        } else {
-          sel[i] = v;
-        }
-      }
-    }
-  }
-
-  float my_val = 0.f;   // lane `slot` keeps the slot's weight source (k <= 32 per pass)
-  float my_logit = 0.f;
-  int my_id = 0;
-  for (int slot = 0; slot < a.num_topk; ++slot) {
-    // lane-local best (ties -> larger index: scan ascending with >=)
-    float best = NEG_INF;
-    int best_e = -1;
-#pragma unroll
-    for (int i = 0; i < kRouteMaxPerLane; ++i) {
-      if (i < per_lane) {
-        const int e = i * 32 + lane;
-        if (e < E && sel[i] >= best) {
-          best = sel[i];
-          best_e = e;
-        }
-      }
-    }
-    // warp arg-max with the same tie rule
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
-      const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
-      if (ob > best || (ob == best && oe > best_e)) {
-        best = ob;
-        best_e = oe;
-      }
-    }
-    // fetch the weight source of the winner and retire it
-    float win_raw = 0.f;
-    if (best_e >= 0 && (best_e & 31) == lane) {
-      const int i = best_e >> 5;
-#pragma unroll
-      for (int j = 0; j < kRouteMaxPerLane; ++j) {
-        if (j == i) {
-          win_raw = raw[j];
-          sel[j] = NEG_INF;
-          raw[j] = NEG_INF;
-        }
-      }
-    }
-    win_raw = __shfl_sync(0xffffffffu, win_raw, best_e >= 0 ? (best_e & 31) : 0);
-    if ((slot & 31) == lane) {
-      my_val = win_raw;
-      my_logit = (MODE == B200MOE_ROUTE_SIGMOID) ? win_raw : best;
-      my_id = best_e < 0 ? 0 : best_e;
-    }
-    // write out (k <= 32, so this runs once, after the last slot)
-    if ((slot & 31) == 31 || slot == a.num_topk - 1) {
-      const int base = slot & ~31;
-      const int n_here = slot - base + 1;
-      const bool active = lane < n_here;
-      float w = my_val;
-      if (MODE == B200MOE_ROUTE_SOFTMAX_TOPK) {
-        // softmax over the selected logits, max-shifted (slot 0 holds the maximum)
-        const float mx = __shfl_sync(0xffffffffu, my_val, 0);
-        float ex = active ? expf(my_val - mx) : 0.f;
-        float sum = ex;
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-        w = ex / sum;
-      } else if (MODE == B200MOE_ROUTE_SIGMOID) {
-        float sum = active ? my_val : 0.f;
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-        if (a.renormalize) w = my_val / fmaxf(sum, 1e-20f);
-        w = w * a.route_scale;
-      }
-      if (active) {
-        const int64_t o = static_cast<int64_t>(warp) * a.num_topk + base + lane;
-        a.topk_ids[o] = my_id;
-        a.topk_weights[o] = w;
-        if (a.topk_logits) a.topk_logits[o] = my_logit;
-      }
-    }
-  }
+  route_topk_token<MODE>(a, warp, threadIdx.x & 31);
 }
 
 // ------------------------------------------------------------------------------------------

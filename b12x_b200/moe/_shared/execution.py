@@ -13,10 +13,9 @@ from dataclasses import dataclass
 from enum import Enum
 
 SWIGLUOAI = "swigluoai_uninterleave"
-SUPPORTED_ACTIVATIONS = frozenset({"silu", "relu2", SWIGLUOAI})
-GATED_ACTIVATIONS = frozenset({"silu", SWIGLUOAI})
-# "situ" is part of the reference's activation set; it is not built here.
-KNOWN_UNBUILT_ACTIVATIONS = frozenset({"situ"})
+SITU = "situ"
+SUPPORTED_ACTIVATIONS = frozenset({"silu", SITU, "relu2", SWIGLUOAI})
+GATED_ACTIVATIONS = frozenset({"silu", SITU, SWIGLUOAI})
 
 QUANT_MODES = frozenset({"nvfp4", "w4a16", "w4a8_mx"})
 SOURCE_FORMATS = frozenset({"modelopt_nvfp4", "fp4_e8m0_k32", "compressed_tensors"})
@@ -41,8 +40,6 @@ class WeightPreparationTransform(str, Enum):
 
 def normalize_moe_activation(activation: str) -> str:
     activation = str(activation)
-    if activation in KNOWN_UNBUILT_ACTIVATIONS:
-        raise NotImplementedError(f"activation {activation!r} is not built in this library")
     if activation not in SUPPORTED_ACTIVATIONS:
         raise ValueError(f"unsupported activation {activation!r}")
     return activation
@@ -62,6 +59,8 @@ def normalize_swiglu_params(activation, limit, alpha, beta):
     if limit is None:
         limit = 7.0 if activation == SWIGLUOAI else None
     else:
+        if activation == SITU:
+            raise ValueError("swiglu_limit is not part of the situ activation contract")
         if activation not in GATED_ACTIVATIONS:
             raise ValueError("swiglu_limit requires a gated MoE activation")
         limit = float(limit)
@@ -202,6 +201,8 @@ def plan_moe_weight_preparation(specs, *, num_experts, hidden_size, intermediate
                 raise ValueError("w4a8_mx requires hidden_size and intermediate_size divisible by 32")
             transforms.add(WeightPreparationTransform.SWIZZLE_MX_SCALES)
         elif spec.quant_mode == "w4a16":
+            if spec.activation == SITU:
+                raise NotImplementedError("activation='situ' is not supported for W4A16 MoE")
             if k % 64 != 0 or n % 64 != 0:
                 raise ValueError("w4a16 requires hidden_size and intermediate_size divisible by 64")
             if spec.source_format == "fp4_e8m0_k32":
@@ -217,3 +218,121 @@ def plan_moe_weight_preparation(specs, *, num_experts, hidden_size, intermediate
     return MoEWeightPreparationPlan(specs=specs, num_experts=num_experts, hidden_size=k,
                                     intermediate_size=n, transforms=frozenset(transforms),
                                     storage_policy=policy)
+
+
+# ---------------------------------------------------------------------------------------------
+# execution lowering (reference ``MoEExecutionPlan`` :578-653 and ``lower_moe_execution`` :994-1118)
+# ---------------------------------------------------------------------------------------------
+class MoERegime(str, Enum):
+    """Which kernel family a plan runs on B200 (the reference's regimes -- direct / streaming /
+    materialized -- describe its SM120 kernels; every regime here materialises the routes with a
+    separate sort and walks them with a persistent grid)."""
+
+    SMALL_BATCH = "small_batch_swap_ab"      # 64-row expert tiles, weights as the MMA rows (decode)
+    WIDE_TILE = "wide_tile"                  # 128 x 256 tiles, one CTA per tile
+    WIDE_TILE_CTA_PAIR = "wide_tile_cta_pair"  # 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2)
+    W4A16_CONVERTER = "w4a16_converter"      # bf16 activations, FP4 weights expanded in shared memory
+
+
+class RouteLayout(str, Enum):
+    SORTED_COMPACT_EXPERT = "sorted_compact_expert"   # stable (expert, route id) order, no per-expert padding
+
+
+class WorkAvailability(str, Enum):
+    PRECOMPUTED = "precomputed"
+
+
+class WorkScheduler(str, Enum):
+    PERSISTENT_GRID = "persistent_grid"
+
+
+class GraphPartition(str, Enum):
+    SPLIT_FC1_FC2 = "split_fc1_fc2"          # FC1+activation+requantisation and FC2 are two launches
+
+
+class GemmEngine(str, Enum):
+    TCGEN05_MXF4NVF4 = "tcgen05_mxf4nvf4"    # nvfp4: E2M1 x E2M1, UE4M3 scale per 16
+    TCGEN05_MXF8F6F4 = "tcgen05_mxf8f6f4"    # w4a8_mx: E4M3 x E2M1, UE8M0 scale per 32
+    TCGEN05_F16 = "tcgen05_f16"              # w4a16: bf16 x bf16 after in-kernel FP4 expansion
+
+
+class PreparedWeightLayout(str, Enum):
+    SOURCE_NATIVE = "source_native"
+
+
+class OutputReduction(str, Enum):
+    ROUTE_BUFFER_TOPK_SUM = "route_buffer_topk_sum"   # fp32 rows per route, fixed-order weighted sum
+
+
+@dataclass(frozen=True, kw_only=True)
+class MoEExecutionPlan:
+    """A lowering of :class:`MoESpec` onto one concrete execution regime (same fields as the
+    reference's dataclass; the enum values name this library's kernels)."""
+
+    regime: MoERegime
+    route_layout: RouteLayout
+    work_availability: WorkAvailability
+    scheduler: WorkScheduler
+    graph_partition: GraphPartition
+    gemm_engine: GemmEngine
+    weight_layout: PreparedWeightLayout
+    reduction: OutputReduction
+    tile_m: int | None = None
+    tile_n: int | None = None
+    route_block_rows: int | None = None
+
+    def __post_init__(self) -> None:
+        for name, enum_type in (("regime", MoERegime), ("route_layout", RouteLayout),
+                                ("work_availability", WorkAvailability), ("scheduler", WorkScheduler),
+                                ("graph_partition", GraphPartition), ("gemm_engine", GemmEngine),
+                                ("weight_layout", PreparedWeightLayout), ("reduction", OutputReduction)):
+            object.__setattr__(self, name, enum_type(getattr(self, name)))
+        for name in ("tile_m", "tile_n", "route_block_rows"):
+            value = getattr(self, name)
+            if value is not None and int(value) <= 0:
+                raise ValueError(f"{name} must be positive, got {value}")
+
+    @property
+    def work_is_streamed(self) -> bool:
+        return False
+
+    @property
+    def grid_addressable(self) -> bool:
+        """All compute work is known before the GEMM kernels start (no in-kernel waiting for routes)."""
+        return True
+
+    @property
+    def uses_explicit_task_queue(self) -> bool:
+        return False
+
+
+def lower_moe_execution(spec: MoESpec, *, routed_rows_capacity: int, num_experts: int, intermediate_size: int,
+                        hidden_size: int, tile_rows: int | None = None) -> MoEExecutionPlan:
+    """Regime and tile choice for one recipe and capacity -- the host-side statement of what the
+    C ABI decides (``b200moe_scratch_nbytes`` for the tile height, the GEMM entry points for the
+    kernel family).  ``tile_rows`` overrides the tile height (64 / 128)."""
+    rows, e = int(routed_rows_capacity), int(num_experts)
+    gated = spec.activation in GATED_ACTIVATIONS
+    small_ok = spec.quant_mode == "nvfp4" and intermediate_size % 128 == 0 and hidden_size % 64 == 0
+    tm = int(tile_rows) if tile_rows else (64 if (small_ok and rows <= 48 * e) else 128)
+    if tm == 64 and not small_ok:
+        tm = 128
+    if spec.quant_mode == "w4a16":
+        regime, engine = MoERegime.W4A16_CONVERTER, GemmEngine.TCGEN05_F16
+    elif spec.quant_mode == "w4a8_mx":
+        regime, engine = MoERegime.WIDE_TILE, GemmEngine.TCGEN05_MXF8F6F4
+    else:
+        engine = GemmEngine.TCGEN05_MXF4NVF4
+        if tm == 64:
+            regime = MoERegime.SMALL_BATCH
+        elif gated and rows >= 256 * e:
+            regime = MoERegime.WIDE_TILE_CTA_PAIR
+        else:
+            regime = MoERegime.WIDE_TILE
+    return MoEExecutionPlan(
+        regime=regime, route_layout=RouteLayout.SORTED_COMPACT_EXPERT,
+        work_availability=WorkAvailability.PRECOMPUTED, scheduler=WorkScheduler.PERSISTENT_GRID,
+        graph_partition=GraphPartition.SPLIT_FC1_FC2, gemm_engine=engine,
+        weight_layout=PreparedWeightLayout.SOURCE_NATIVE, reduction=OutputReduction.ROUTE_BUFFER_TOPK_SUM,
+        tile_m=256 if regime is MoERegime.WIDE_TILE_CTA_PAIR else tm,
+        tile_n=256, route_block_rows=tm)

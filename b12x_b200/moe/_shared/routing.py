@@ -27,33 +27,29 @@ def route_topk(
     softmax over the k selected logits when ``renormalize`` else the logits themselves.
     ``score_func="sigmoid"``: scores = sigmoid(logits), selection on scores + ``selection_bias``,
     weights = selected scores (divided by their sum when ``renormalize``) times ``route_scale``."""
+    outs = {"topk_logits": (topk_logits, torch.float32), "topk_ids": (topk_ids, torch.int32),
+            "topk_weights": (topk_weights, torch.float32)}
     if router_logits.ndim != 2:
         raise ValueError(f"expected router_logits with rank 2, got shape {tuple(router_logits.shape)}")
-    if topk_logits.ndim != 2 or topk_ids.ndim != 2 or topk_weights.ndim != 2:
-        raise ValueError("top-k outputs must all have rank 2")
-    if topk_logits.shape != topk_ids.shape or topk_logits.shape != topk_weights.shape:
-        raise ValueError(
-            "top-k outputs must share a shape, got "
-            f"{tuple(topk_logits.shape)}, {tuple(topk_ids.shape)}, {tuple(topk_weights.shape)}")
-    if router_logits.shape[0] != topk_logits.shape[0]:
-        raise ValueError(
-            f"router_logits batch mismatch: expected {router_logits.shape[0]}, got {topk_logits.shape[0]}")
-    if topk_ids.dtype != torch.int32:
-        raise ValueError(f"expected topk_ids dtype int32, got {topk_ids.dtype}")
-    if topk_logits.dtype != torch.float32:
-        raise ValueError(f"expected topk_logits dtype float32, got {topk_logits.dtype}")
-    if topk_weights.dtype != torch.float32:
-        raise ValueError(f"expected topk_weights dtype float32, got {topk_weights.dtype}")
+    shapes = {tuple(t.shape) for t, _ in outs.values()}
+    if any(t.ndim != 2 for t, _ in outs.values()) or len(shapes) != 1:
+        raise ValueError("topk_logits, topk_ids and topk_weights must be rank-2 tensors of one shape, got "
+                         + ", ".join(f"{n}{tuple(t.shape)}" for n, (t, _) in outs.items()))
+    if topk_ids.shape[0] != router_logits.shape[0]:
+        raise ValueError(f"router_logits batch mismatch: expected {router_logits.shape[0]}, got {topk_ids.shape[0]}")
+    for name, (t, dt) in outs.items():
+        if t.dtype != dt:
+            raise ValueError(f"expected {name} dtype {str(dt).removeprefix('torch.')}, got {t.dtype}")
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
     if not router_logits.is_cuda:
         raise ValueError("route_topk requires CUDA tensors")
-    if router_logits.shape[1] > 1024:
-        raise ValueError(f"route_topk currently supports up to 1024 experts, got {router_logits.shape[1]}")
-    if router_logits.stride(-1) != 1:
-        raise ValueError("router_logits must be contiguous in the expert dimension")
-    if not (topk_logits.is_contiguous() and topk_ids.is_contiguous() and topk_weights.is_contiguous()):
-        raise ValueError("top-k outputs must be contiguous")
     if router_logits.dtype not in (torch.float32, torch.bfloat16):
         raise ValueError(f"router_logits must be float32 or bfloat16, got {router_logits.dtype}")
+    if router_logits.stride(-1) != 1:
+        raise ValueError("router_logits must be contiguous in the expert dimension")
+    if router_logits.shape[1] > 1024:
+        raise ValueError(f"route_topk currently supports up to 1024 experts, got {router_logits.shape[1]}")
     num_tokens, num_experts = router_logits.shape
     top_k = topk_logits.shape[1]
     if top_k <= 0:

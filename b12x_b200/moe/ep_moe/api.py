@@ -13,74 +13,75 @@ from .._shared.execution import MoEWeightPreparationPlan
 from ..fused_moe import _impl as F
 
 
-def _tensor_version(t: torch.Tensor) -> int | None:
-    try:
-        return int(t._version)
-    except RuntimeError:      # tensors made in inference mode have no version counter
-        return None
-
-
 @dataclass(frozen=True)
 class ExpertMap:
-    """A validated, static global-to-local expert map (reference ``EPExpertMap`` _impl.py:62-83)."""
+    """One rank's frozen global-to-local expert map (the role of the reference's ``EPExpertMap``,
+    b12x/moe/ep_moe/_impl.py:62-83).  ``validate_static`` detects a map that was replaced, moved or
+    written to since it was prepared: the kernels read it on every call, and a captured graph keeps
+    its address."""
 
     tensor: torch.Tensor
     global_num_experts: int
     local_num_experts: int
     device: torch.device
-    _data_ptr: int
-    _version: int | None
+    _fingerprint: tuple
+
+    @staticmethod
+    def _fingerprint_of(t: torch.Tensor) -> tuple:
+        try:
+            version = int(t._version)
+        except RuntimeError:          # inference-mode tensors carry no version counter
+            version = None
+        return (t.data_ptr(), str(t.device), version)
 
     def validate_static(self) -> None:
-        if self.tensor.data_ptr() != self._data_ptr:
+        then, now = self._fingerprint, self._fingerprint_of(self.tensor)
+        if now[0] != then[0]:
             raise RuntimeError("EP expert_map storage changed after preparation")
-        version = _tensor_version(self.tensor)
-        if self._version is not None and version != self._version:
-            raise RuntimeError("EP expert_map was mutated after preparation")
-        if self.tensor.device != self.device:
+        if now[1] != then[1]:
             raise RuntimeError("EP expert_map device changed after preparation")
+        if then[2] is not None and now[2] != then[2]:
+            raise RuntimeError("EP expert_map was mutated after preparation")
 
 
 def prepare_expert_map(expert_map: torch.Tensor, *, local_num_experts: int,
                        global_num_experts: int | None = None,
                        device: torch.device | str | None = None) -> ExpertMap:
-    """Validate and freeze one rank's global-to-local expert map: every local id must occur exactly
-    once, other entries are -1 (reference ``prepare_ep_expert_map`` _impl.py:86-153; may
-    synchronise with the device, so call it before graph capture)."""
-    if not isinstance(expert_map, torch.Tensor):
-        raise TypeError("expert_map must be a torch.Tensor")
-    if expert_map.dtype != torch.int32:
-        raise TypeError("expert_map must have dtype torch.int32")
+    """Check and freeze a rank's expert map: an int32 vector over the GLOBAL experts whose entries
+    are a local expert id or -1, every local id used exactly once (a bijection from this rank's
+    global experts onto ``range(local_num_experts)``; contract of the reference's
+    ``prepare_ep_expert_map``, b12x/moe/ep_moe/_impl.py:86-153).  Reads the map on the host, so it
+    must run before CUDA graph capture."""
+    if not isinstance(expert_map, torch.Tensor) or expert_map.dtype != torch.int32:
+        raise TypeError("expert_map must be a torch.Tensor of dtype torch.int32")
     if expert_map.ndim != 1 or not expert_map.is_contiguous():
         raise ValueError("expert_map must be a contiguous rank-1 tensor")
-    if expert_map.device.type == "cuda" and torch.cuda.is_current_stream_capturing():
+    if expert_map.is_cuda and torch.cuda.is_current_stream_capturing():
         raise RuntimeError("EP expert_map must be prepared before CUDA graph capture")
-    expected_device = expert_map.device if device is None else torch.device(device)
-    if expected_device.type == "cuda" and expected_device.index is None:
-        expected_device = torch.device("cuda", expert_map.device.index or 0)
-    if expert_map.device != expected_device:
-        raise ValueError(f"expert_map must be on {expected_device}, got {expert_map.device}")
-    global_e = int(expert_map.numel())
-    if global_num_experts is not None and global_e != int(global_num_experts):
-        raise ValueError(f"expert_map global expert count mismatch: expected {int(global_num_experts)}, got {global_e}")
-    local_e = int(local_num_experts)
-    if global_e <= 0:
-        raise ValueError("global_num_experts must be positive")
-    if local_e <= 0:
-        raise ValueError("local_num_experts must be positive")
-    if local_e > global_e:
-        raise ValueError(f"local_num_experts={local_e} exceeds global_num_experts={global_e}")
-    values = expert_map.detach().cpu().tolist()
-    invalid = [v for v in values if v < -1 or v >= local_e]
-    if invalid:
+    want = expert_map.device if device is None else torch.device(device)
+    if want.type == "cuda" and want.index is None:
+        want = torch.device("cuda", expert_map.device.index or 0)
+    if expert_map.device != want:
+        raise ValueError(f"expert_map must be on {want}, got {expert_map.device}")
+    n_global, n_local = int(expert_map.numel()), int(local_num_experts)
+    if global_num_experts is not None and int(global_num_experts) != n_global:
+        raise ValueError(f"expert_map global expert count mismatch: expected {int(global_num_experts)}, got {n_global}")
+    if n_global <= 0 or n_local <= 0:
+        raise ValueError("global_num_experts and local_num_experts must be positive")
+    if n_local > n_global:
+        raise ValueError(f"local_num_experts={n_local} exceeds global_num_experts={n_global}")
+    host = expert_map.detach().to("cpu", torch.int64)
+    out_of_range = host[(host < -1) | (host >= n_local)]
+    if out_of_range.numel():
         raise ValueError("expert_map values must be -1 or valid local expert ids; "
-                         f"found {invalid[0]} for local_num_experts={local_e}")
-    mapped = sorted(v for v in values if v >= 0)
-    if mapped != list(range(local_e)):
-        raise ValueError(f"expert_map must map every local expert id exactly once: expected "
-                         f"{list(range(local_e))}, got {mapped}")
-    return ExpertMap(tensor=expert_map, global_num_experts=global_e, local_num_experts=local_e,
-                     device=expected_device, _data_ptr=expert_map.data_ptr(), _version=_tensor_version(expert_map))
+                         f"found {int(out_of_range[0])} for local_num_experts={n_local}")
+    uses = torch.bincount(host[host >= 0], minlength=n_local)
+    if not bool((uses == 1).all()):
+        bad = int((uses != 1).nonzero()[0])
+        raise ValueError(f"expert_map must map every local expert id exactly once: local id {bad} "
+                         f"occurs {int(uses[bad])} times")
+    return ExpertMap(tensor=expert_map, global_num_experts=n_global, local_num_experts=n_local, device=want,
+                     _fingerprint=ExpertMap._fingerprint_of(expert_map))
 
 
 @dataclass(frozen=True, kw_only=True)

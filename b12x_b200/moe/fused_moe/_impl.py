@@ -22,7 +22,10 @@ from ..._lib import ext
 from ..._lib.scratch import ScratchBufferSpec, scratch_buffer_spec, scratch_tensor
 from .._shared.execution import (
     SWIGLUOAI,
+    MoEExecutionPlan,
+    MoESpec,
     MoEWeightPreparationPlan,
+    lower_moe_execution,
     WeightPreparationTransform,
     is_gated_moe_activation,
     make_moe_spec,
@@ -33,7 +36,7 @@ from .._shared.execution import (
 )
 from .._shared.routing import route_topk
 
-_ACT_CODE = {"silu": "silu", "relu2": "relu2", SWIGLUOAI: "swigluoai"}
+_ACT_CODE = {"silu": "silu", "relu2": "relu2", SWIGLUOAI: "swigluoai", "situ": "situ"}
 
 
 def _stream_ptr(device: torch.device) -> int:
@@ -362,14 +365,18 @@ class TPMoEArenaLayout:
 
 @dataclass(frozen=True, kw_only=True)
 class TPMoEPlan:
-    """What will be launched for a token count (reference ``TPMoEPlan`` _impl.py:717-744)."""
+    """Logical launch plan plus the precision-neutral execution descriptors (reference ``TPMoEPlan``
+    _impl.py:717-744): ``spec`` is the numeric contract, ``execution`` the regime / tile choice."""
 
-    implementation: str      # always "tcgen05_grouped"
+    spec: MoESpec
+    execution: MoEExecutionPlan
+    implementation: str      # the kernel family: execution.regime.value
     quant_mode: str
     activation: str
-    swiglu_limit: float | None
-    swiglu_alpha: float
-    swiglu_beta: float
+    swiglu_limit: float | None = None
+    swiglu_alpha: float = 1.0
+    swiglu_beta: float = 0.0
+    state_E: int
     weight_E: int
     routed_rows: int
     max_rows: int
@@ -378,22 +385,34 @@ class TPMoEPlan:
     num_topk: int
     device: torch.device
     dtype: torch.dtype
-    tile_m: int = 128
-    tile_n: int = 256
+    max_tokens_per_launch: int
     max_m_tiles: int = 0
-    deterministic_output: bool = True
+
+    @property
+    def deterministic_output(self) -> bool:
+        return True          # fp32 rows per route, combined in slot order
+
+    @property
+    def tile_m(self) -> int:
+        return int(self.execution.tile_m)
+
+    @property
+    def tile_n(self) -> int:
+        return int(self.execution.tile_n)
 
 
 _ROUTE_ALIGN = 1024
 
 
 def _route_workspace_nbytes(caps: TPMoEScratchCaps) -> int:
-    """Router logits (when a gate GEMM is requested) + top-k logits/ids/weights."""
+    """Router logits (when a gate GEMM is requested) + top-k logits/ids/weights + the gate kernel's
+    arrival counters (laid out by ``TPMoEWorkspace.route_views``)."""
     e = caps.route_num_experts or 0
     if e <= 0:
         return 0
     t, k = caps.max_tokens, caps.num_topk
-    return (_align_up(t * e * 4, _ROUTE_ALIGN) + 3 * _align_up(t * k * 4, _ROUTE_ALIGN))
+    return (_align_up(t * e * 4, _ROUTE_ALIGN) + 3 * _align_up(t * k * 4, _ROUTE_ALIGN)
+            + _align_up(((t + 3) // 4) * 4, _ROUTE_ALIGN))
 
 
 def _layout_for(caps: TPMoEScratchCaps) -> ext.ScratchLayout:
@@ -401,20 +420,54 @@ def _layout_for(caps: TPMoEScratchCaps) -> ext.ScratchLayout:
                               caps.quant_mode, _ACT_CODE[caps.activation], caps.tile_rows or 0)
 
 
-def plan_tp_moe_execution(caps: TPMoEScratchCaps, num_tokens: int | None = None) -> TPMoEPlan:
-    """Regime / tile choice for a token count (reference ``plan_tp_moe_execution``
-    _impl.py:5647-5840).  One regime here: grouped tcgen05 GEMMs with 128-row tiles; the bound on
-    m-tiles is ceil(rows/128) + min(E, rows) (reference _impl.py:2134-2152)."""
-    t = caps.max_tokens if num_tokens is None else int(num_tokens)
-    if t > caps.max_tokens:
-        raise ValueError(f"{t} tokens exceed the planned capacity {caps.max_tokens}")
-    rows = t * caps.num_topk
+def plan_tp_moe_execution(
+    *,
+    num_tokens: int,
+    num_topk: int,
+    device: torch.device | str,
+    weight_plan: MoEWeightPreparationPlan,
+    quant_mode: str,
+    swiglu_limit: float | None = None,
+    swiglu_alpha: float | None = None,
+    swiglu_beta: float | None = None,
+    apply_router_weight_on_input: bool = False,
+    deterministic_output: bool | None = None,
+    tile_rows: int | None = None,
+) -> TPMoEPlan:
+    """Lower one recipe from an authoritative weight-preparation plan (reference
+    ``plan_tp_moe_execution`` _impl.py:5647-5840, same keywords): which kernel family and tile a
+    launch over ``num_tokens`` tokens uses.  ``deterministic_output=False`` is accepted: the output
+    reduction here is always the deterministic one."""
+    if not isinstance(weight_plan, MoEWeightPreparationPlan):
+        raise TypeError("weight_plan must be a MoEWeightPreparationPlan")
+    mode = str(quant_mode).lower()
+    spec = next((sp for sp in weight_plan.specs if sp.quant_mode == mode), None)
+    if spec is None:
+        raise ValueError(f"quant_mode={mode!r} is absent from the weight plan")
+    if apply_router_weight_on_input:
+        raise NotImplementedError("apply_router_weight_on_input is not implemented in b12x_moe_fp4")
+    limit, alpha, beta = normalize_swiglu_params(weight_plan.activation, swiglu_limit, swiglu_alpha, swiglu_beta)
+    t, k_ = max(int(num_tokens), 1), max(int(num_topk), 1)
+    rows = t * k_
+    ex = lower_moe_execution(spec, routed_rows_capacity=rows, num_experts=weight_plan.num_experts,
+                             intermediate_size=weight_plan.intermediate_size, hidden_size=weight_plan.hidden_size,
+                             tile_rows=tile_rows)
+    dev = torch.device(device)
+    tm = int(ex.route_block_rows)
     return TPMoEPlan(
-        implementation="tcgen05_grouped", quant_mode=caps.quant_mode, activation=caps.activation,
-        swiglu_limit=caps.swiglu_limit, swiglu_alpha=caps.swiglu_alpha, swiglu_beta=caps.swiglu_beta,
-        weight_E=caps.weight_E, routed_rows=rows, max_rows=caps.max_tokens * caps.num_topk,
-        k=caps.k, n=caps.n, num_topk=caps.num_topk, device=caps.device, dtype=caps.dtype,
-        max_m_tiles=(rows + 127) // 128 + min(caps.weight_E, rows))
+        spec=spec, execution=ex, implementation=ex.regime.value, quant_mode=mode, activation=weight_plan.activation,
+        swiglu_limit=limit, swiglu_alpha=alpha, swiglu_beta=beta, state_E=weight_plan.num_experts,
+        weight_E=weight_plan.num_experts, routed_rows=rows, max_rows=rows, k=weight_plan.hidden_size,
+        n=weight_plan.intermediate_size, num_topk=k_, device=dev,
+        dtype={"bfloat16": torch.bfloat16}[weight_plan.io_dtype], max_tokens_per_launch=t,
+        max_m_tiles=(rows + tm - 1) // tm + min(weight_plan.num_experts, rows))
+
+
+def _plan_execution_for_caps(caps: TPMoEScratchCaps) -> TPMoEPlan:
+    return plan_tp_moe_execution(
+        num_tokens=caps.max_tokens, num_topk=caps.num_topk, device=caps.device, weight_plan=caps.weight_plan,
+        quant_mode=caps.quant_mode, swiglu_limit=caps.swiglu_limit, swiglu_alpha=caps.swiglu_alpha,
+        swiglu_beta=caps.swiglu_beta, tile_rows=caps.tile_rows or None)
 
 
 def tp_moe_required_nbytes(caps: TPMoEScratchCaps) -> int:
@@ -447,7 +500,11 @@ class TPMoEScratchPlan:
         output: torch.Tensor | None = None,
         input_scales_static: bool = False,
         fast_math: bool | None = None,
+        unit_scale_contract: bool = False,
+        activation_amax: torch.Tensor | None = None,
+        layer_idx: int | None = None,
         route_expert_map: torch.Tensor | None = None,
+        output_expert_map: torch.Tensor | None = None,
         fc1_tap: torch.Tensor | None = None,
         output_f32: torch.Tensor | None = None,
         output_scale: float = 1.0,
@@ -463,6 +520,12 @@ class TPMoEScratchPlan:
         caps = self.caps
         if not isinstance(experts, B12XFP4ExpertWeights):
             raise TypeError("experts must come from prepare_b12x_fp4_moe_weights")
+        if output_expert_map is not None:
+            # reference _impl.py:2333-2334: only its trellis full-rotation plans take one
+            raise ValueError("output_expert_map requires a full-rotation Trellis plan")
+        if activation_amax is not None:
+            # reference _impl.py:10601-10604 (calibration sidecars are not part of this library)
+            raise NotImplementedError("activation_amax calibration is not supported")
         if experts.plan != caps.weight_plan:
             raise ValueError("experts do not match the plan used to size TP MoE scratch")
         if a.ndim != 2 or topk_ids.ndim != 2 or topk_weights.ndim != 2:
@@ -500,6 +563,7 @@ class TPMoEScratchPlan:
             max_rows=caps.max_tokens * caps.num_topk, k=caps.k, n=caps.n, num_topk=caps.num_topk,
             device=caps.device, dtype=caps.dtype, output=output,
             input_scales_static=bool(input_scales_static), fast_math=fast_math,
+            unit_scale_contract=bool(unit_scale_contract and caps.quant_mode == "w4a16"), layer_idx=layer_idx,
             quant_mode=caps.quant_mode, activation=caps.activation, w13_layout=caps.w13_layout,
             swiglu_limit=caps.swiglu_limit, swiglu_alpha=caps.swiglu_alpha,
             swiglu_beta=caps.swiglu_beta, route_expert_map=route_expert_map,
@@ -519,7 +583,7 @@ def plan_tp_moe_scratch(caps: TPMoEScratchCaps) -> TPMoEScratchPlan:
                               total_nbytes=total,
                               core_token_counts=caps.core_token_counts or (caps.max_tokens,))
     spec = scratch_buffer_spec("tp_moe.scratch", nbytes=total, device=caps.device)
-    return TPMoEScratchPlan(caps, layout, plan_tp_moe_execution(caps), core, (spec,))
+    return TPMoEScratchPlan(caps, layout, _plan_execution_for_caps(caps), core, (spec,))
 
 
 def _view(core: torch.Tensor, offset: int, count: int, dtype: torch.dtype) -> torch.Tensor:
@@ -548,6 +612,8 @@ class TPMoEFP4Binding:
     output: torch.Tensor | None = None
     input_scales_static: bool = False
     fast_math: bool | None = None
+    unit_scale_contract: bool = False
+    layer_idx: int | None = None
     quant_mode: str | None = None
     activation: str = "silu"
     w13_layout: str = "w13"
@@ -729,7 +795,7 @@ def check_device_status(binding: TPMoEFP4Binding) -> None:
 
 
 # =============================================================================================
-# routing wrappers
+# routing and the sparse block (gate -> top-k -> experts)
 # =============================================================================================
 @dataclass(frozen=True, kw_only=True)
 class B12XTopKRouting:
@@ -742,14 +808,86 @@ class B12XTopKRouting:
     flat_weights: torch.Tensor | None = None
 
 
+@dataclass(frozen=True)
+class TPMoERouteWorkspace:
+    """Views into the route part of a scratch arena: gate logits, top-k outputs, arrival counters."""
+
+    router_logits: torch.Tensor
+    topk_logits: torch.Tensor
+    topk_ids: torch.Tensor
+    topk_weights: torch.Tensor
+    counters: torch.Tensor
+
+
+@dataclass(frozen=True)
+class TPMoEWorkspace:
+    """The caller-owned scratch of the sparse block: a scratch plan and the ONE uint8 tensor sized by
+    it.  It stands where the reference passes its workspace objects as ``scratch`` to
+    ``bind_route`` / ``bind_sparse`` (_impl.py:7849-7958); nothing in it is allocated after
+    construction."""
+
+    plan: TPMoEScratchPlan
+    storage: torch.Tensor
+
+    def __post_init__(self) -> None:
+        if not isinstance(self.plan, TPMoEScratchPlan):
+            raise TypeError("plan must be a TPMoEScratchPlan")
+        scratch_tensor(self.storage, self.plan.scratch_specs(), owner="TP MoE")
+
+    @classmethod
+    def allocate(cls, plan: TPMoEScratchPlan) -> "TPMoEWorkspace":
+        spec = plan.scratch_specs()[0]
+        return cls(plan, torch.empty(spec.shape, dtype=spec.dtype, device=spec.device))
+
+    def route_views(self, tokens: int, num_experts: int, top_k: int,
+                    logits_dtype: torch.dtype) -> TPMoERouteWorkspace | None:
+        """Route buffers for ``tokens`` tokens carved from the arena, or None when the plan did not
+        price them (``Caps.route_num_experts``) or they do not fit."""
+        caps = self.plan.caps
+        e_cap = caps.route_num_experts or 0
+        if e_cap <= 0 or num_experts > e_cap or tokens > caps.max_tokens or top_k > caps.num_topk:
+            return None
+        if logits_dtype not in (torch.float32, torch.bfloat16):
+            return None
+        t_cap, k_cap = caps.max_tokens, caps.num_topk
+        base = self.storage
+        off = 0
+
+        def take(nbytes_cap: int, count: int, dtype: torch.dtype, shape) -> torch.Tensor:
+            nonlocal off
+            v = _view(base, off, count, dtype).view(shape)
+            off += _align_up(nbytes_cap, _ROUTE_ALIGN)
+            return v
+
+        logits = take(t_cap * e_cap * 4, tokens * num_experts, logits_dtype, (tokens, num_experts))
+        tl = take(t_cap * k_cap * 4, tokens * top_k, torch.float32, (tokens, top_k))
+        ti = take(t_cap * k_cap * 4, tokens * top_k, torch.int32, (tokens, top_k))
+        tw = take(t_cap * k_cap * 4, tokens * top_k, torch.float32, (tokens, top_k))
+        cnt = take(((t_cap + 3) // 4) * 4, (tokens + 3) // 4, torch.int32, ((tokens + 3) // 4,))
+        return TPMoERouteWorkspace(logits, tl, ti, tw, cnt)
+
+
+def _alloc_route_workspace(tokens: int, num_experts: int, top_k: int, device, logits_dtype) -> TPMoERouteWorkspace:
+    if torch.cuda.is_current_stream_capturing():
+        raise RuntimeError("route buffers must come from caller-owned scratch during CUDA graph capture "
+                           "(plan with Caps.route_num_experts and pass the workspace as scratch)")
+    return TPMoERouteWorkspace(
+        torch.empty((tokens, num_experts), dtype=logits_dtype, device=device),
+        torch.empty((tokens, top_k), dtype=torch.float32, device=device),
+        torch.empty((tokens, top_k), dtype=torch.int32, device=device),
+        torch.empty((tokens, top_k), dtype=torch.float32, device=device),
+        torch.empty(((tokens + 3) // 4,), dtype=torch.int32, device=device))
+
+
 @dataclass(frozen=True, kw_only=True)
 class TPMoERouteBinding:
-    """Reference ``TPMoERouteBinding`` (_impl.py:1059-1070) plus the score-function options the
-    reference only has in its benchmark (benchmarks/benchmark_moe.py:1282-1322)."""
+    """Reference ``TPMoERouteBinding`` (_impl.py:1059-1070).  The last four fields are not in the
+    reference's binding: they select the sigmoid scoring the reference only has in its benchmark
+    (benchmarks/benchmark_moe.py:1282-1322) and the kernel used for the gate projection."""
 
     hidden_states: torch.Tensor
     top_k: int
-    scratch: torch.Tensor | None = None
+    scratch: TPMoEWorkspace | None = None
     gate_weight: torch.Tensor | None = None
     gate_bias: torch.Tensor | None = None
     router_logits: torch.Tensor | None = None
@@ -757,90 +895,263 @@ class TPMoERouteBinding:
     score_func: str = "softmax"          # "softmax" | "sigmoid"
     selection_bias: torch.Tensor | None = None
     route_scale: float = 1.0
+    gate_kernel: str = "auto"            # "auto" | "simt" | "tc"
 
     def run(self) -> B12XTopKRouting:
         return b12x_route_experts_fast(binding=self)
 
 
-def build_tp_moe_route_binding(**kwargs) -> TPMoERouteBinding:
-    return TPMoERouteBinding(**kwargs)
+def _check_route_request(hidden_states, top_k, gate_weight, router_logits) -> None:
+    if hidden_states.ndim != 2:
+        raise ValueError(f"expected hidden_states with rank 2, got shape {tuple(hidden_states.shape)}")
+    if int(top_k) <= 0:
+        raise ValueError(f"top_k must be positive, got {top_k}")
+    if router_logits is not None and gate_weight is not None:
+        raise ValueError("pass either router_logits or gate_weight, not both")
+    if router_logits is None and gate_weight is None:
+        raise ValueError("expected router_logits or gate_weight")
+
+
+def build_tp_moe_route_binding(
+    *,
+    scratch: TPMoEWorkspace | None = None,
+    hidden_states: torch.Tensor,
+    top_k: int,
+    gate_weight: torch.Tensor | None = None,
+    gate_bias: torch.Tensor | None = None,
+    router_logits: torch.Tensor | None = None,
+    renormalize: bool = True,
+    score_func: str = "softmax",
+    selection_bias: torch.Tensor | None = None,
+    route_scale: float = 1.0,
+    gate_kernel: str = "auto",
+) -> TPMoERouteBinding:
+    """Reference ``build_tp_moe_route_binding`` (_impl.py:7849-7883)."""
+    if scratch is not None and not isinstance(scratch, TPMoEWorkspace):
+        raise TypeError("scratch must be a TP MoE scratch object or None")
+    _check_route_request(hidden_states, top_k, gate_weight, router_logits)
+    if gate_kernel not in ext.GATE_KERNELS:
+        raise ValueError(f"unsupported gate_kernel {gate_kernel!r}")
+    return TPMoERouteBinding(hidden_states=hidden_states, top_k=int(top_k), scratch=scratch, gate_weight=gate_weight,
+                             gate_bias=gate_bias, router_logits=router_logits, renormalize=bool(renormalize),
+                             score_func=score_func, selection_bias=selection_bias, route_scale=float(route_scale),
+                             gate_kernel=gate_kernel)
+
+
+_DT_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
 
 def b12x_route_experts_fast(*, binding: TPMoERouteBinding) -> B12XTopKRouting:
-    """Gate GEMM (optional, ``torch.mm``) then the top-k kernel (reference _impl.py:11356-11490)."""
+    """Gate projection (optional) and top-k routing (reference ``b12x_route_experts_fast``
+    _impl.py:11356-11490).  With ``gate_weight`` the projection and the router are ONE launch
+    (``b200moe_gate_route``); with ``router_logits`` only the router runs.  With a workspace as
+    ``scratch`` every buffer is a view into it: nothing is allocated and the call can be captured."""
+    if not isinstance(binding, TPMoERouteBinding):
+        raise TypeError("binding must be a TPMoERouteBinding")
     b = binding
-    hs = b.hidden_states
-    if hs.ndim != 2:
-        raise ValueError(f"expected hidden_states with rank 2, got shape {tuple(hs.shape)}")
-    if b.top_k <= 0:
-        raise ValueError(f"top_k must be positive, got {b.top_k}")
-    if b.router_logits is not None and b.gate_weight is not None:
-        raise ValueError("pass either router_logits or gate_weight, not both")
-    if b.router_logits is None and b.gate_weight is None:
-        raise ValueError("expected router_logits or gate_weight")
-    if b.router_logits is None:
-        gw = b.gate_weight
-        if gw.ndim != 2 or gw.shape[1] != hs.shape[1]:
-            raise ValueError("gate_weight must be [experts, hidden]")
-        logits = torch.mm(hs, gw.t())
-        if b.gate_bias is not None:
-            logits = logits + b.gate_bias
+    hs, top_k, gw, gb, logits = b.hidden_states, b.top_k, b.gate_weight, b.gate_bias, b.router_logits
+    _check_route_request(hs, top_k, gw, logits)
+    if logits is None:
+        if gw.ndim != 2:
+            raise ValueError(f"expected gate_weight with rank 2, got shape {tuple(gw.shape)}")
+        if gw.shape[1] != hs.shape[1]:
+            raise ValueError(f"gate_weight hidden-size mismatch: expected {hs.shape[1]}, got {gw.shape[1]}")
+        if gb is not None:
+            if gb.ndim != 1:
+                raise ValueError(f"expected gate_bias with rank 1, got shape {tuple(gb.shape)}")
+            if gb.shape[0] != gw.shape[0]:
+                raise ValueError(f"gate_bias expert mismatch: expected {gw.shape[0]}, got {gb.shape[0]}")
+        num_experts = int(gw.shape[0])
+        logits_dtype = torch.result_type(hs, gw)
     else:
-        logits = b.router_logits
-        if logits.ndim != 2 or logits.shape[0] != hs.shape[0]:
-            raise ValueError("router_logits must be [tokens, experts]")
-    if b.top_k > logits.shape[1]:
-        raise ValueError(f"top_k={b.top_k} exceeds num_experts={logits.shape[1]}")
-    t = logits.shape[0]
-    dev = logits.device
-    tl = torch.empty((t, b.top_k), dtype=torch.float32, device=dev)
-    ti = torch.empty((t, b.top_k), dtype=torch.int32, device=dev)
-    tw = torch.empty((t, b.top_k), dtype=torch.float32, device=dev)
-    lg = logits if logits.dtype in (torch.float32, torch.bfloat16) else logits.float()
-    route_topk(lg, tl, ti, tw, renormalize=b.renormalize, score_func=b.score_func,
-               selection_bias=b.selection_bias, route_scale=b.route_scale)
-    return B12XTopKRouting(topk_weights=tw, topk_ids=ti, router_logits=logits,
-                           flat_ids=ti.view(-1), flat_weights=tw.view(-1))
+        if logits.ndim != 2:
+            raise ValueError(f"expected router_logits with rank 2, got shape {tuple(logits.shape)}")
+        if logits.shape[0] != hs.shape[0]:
+            raise ValueError(f"router_logits batch mismatch: expected {hs.shape[0]}, got {logits.shape[0]}")
+        num_experts = int(logits.shape[1])
+        logits_dtype = logits.dtype
+    if top_k > num_experts:
+        raise ValueError(f"top_k={top_k} exceeds num_experts={num_experts}")
+    if not hs.is_cuda:
+        raise ValueError("route requires CUDA tensors (there is no CPU path)")
+    if num_experts > 1024:
+        raise ValueError(f"route supports up to 1024 experts, got {num_experts}")
+    if b.score_func not in ("softmax", "sigmoid"):
+        raise ValueError(f"unsupported score_func {b.score_func!r}")
+    tokens = int(hs.shape[0])
+    ws = None if b.scratch is None else b.scratch.route_views(tokens, num_experts, top_k, logits_dtype)
+    if ws is None:
+        ws = _alloc_route_workspace(tokens, num_experts, top_k, hs.device, logits_dtype)
+    if logits is not None:
+        if not logits.is_contiguous():
+            ws.router_logits.copy_(logits)
+            logits = ws.router_logits
+        route_topk(logits, ws.topk_logits, ws.topk_ids, ws.topk_weights, renormalize=b.renormalize,
+                   score_func=b.score_func, selection_bias=b.selection_bias, route_scale=b.route_scale)
+    else:
+        for name, t in (("hidden_states", hs), ("gate_weight", gw)):
+            if t.dtype not in _DT_CODE:
+                raise ValueError(f"{name} must be float32 or bfloat16, got {t.dtype}")
+        if gb is not None and gb.dtype not in _DT_CODE:
+            raise ValueError(f"gate_bias must be float32 or bfloat16, got {gb.dtype}")
+        if hs.stride(1) != 1 or not gw.is_contiguous() or (gb is not None and not gb.is_contiguous()):
+            raise ValueError("hidden_states must be row-contiguous; gate_weight and gate_bias contiguous")
+        if b.score_func == "sigmoid":
+            mode = "sigmoid"
+        else:
+            mode = "softmax_topk" if b.renormalize else "raw"
+        sel = b.selection_bias
+        if sel is not None:
+            if mode != "sigmoid":
+                raise ValueError("selection_bias is only used with score_func='sigmoid'")
+            if sel.dtype != torch.float32 or sel.numel() != num_experts or not sel.is_contiguous():
+                raise ValueError("selection_bias must be contiguous float32 [experts]")
+        args = ext.GateRouteArgs(
+            hs.data_ptr(), gw.data_ptr(), _ptr(gb), ws.router_logits.data_ptr(), ws.counters.data_ptr(), _ptr(sel),
+            ws.topk_logits.data_ptr(), ws.topk_ids.data_ptr(), ws.topk_weights.data_ptr(), None, hs.stride(0),
+            tokens, num_experts, int(hs.shape[1]), top_k, _DT_CODE[hs.dtype], _DT_CODE[gw.dtype],
+            _DT_CODE[gb.dtype] if gb is not None else 0, ext.ROUTE_MODES[mode], 1 if b.renormalize else 0,
+            float(b.route_scale), ext.GATE_KERNELS[b.gate_kernel], 0)
+        ext.check(ext.load().b200moe_gate_route(C.byref(args), _stream_ptr(hs.device)), "gate_route")
+        logits = ws.router_logits
+    return B12XTopKRouting(topk_weights=ws.topk_weights, topk_ids=ws.topk_ids, router_logits=logits,
+                           flat_ids=ws.topk_ids.view(-1), flat_weights=ws.topk_weights.view(-1))
 
 
 @dataclass(frozen=True, kw_only=True)
 class TPMoESparseFP4Binding:
-    """Route + experts in one binding (reference ``TPMoESparseFP4Binding`` _impl.py:1073)."""
+    """Route + experts in one binding (reference ``TPMoESparseFP4Binding`` _impl.py:1073-1097)."""
 
-    plan: TPMoEScratchPlan
-    scratch: torch.Tensor
     hidden_states: torch.Tensor
     experts: B12XFP4ExpertWeights
-    top_k: int
+    scratch: TPMoEWorkspace
+    routing: B12XTopKRouting | None = None
+    top_k: int | None = None
     gate_weight: torch.Tensor | None = None
     gate_bias: torch.Tensor | None = None
     router_logits: torch.Tensor | None = None
-    renormalize: bool = True
+    renormalize_topk: bool = True
+    routed_scaling_factor: float = 1.0
+    output: torch.Tensor | None = None
+    return_routing: bool = False
+    input_scales_static: bool = False
+    fast_math: bool | None = None
+    quant_mode: str | None = None
+    swiglu_limit: float | None = None
+    swiglu_alpha: float | None = None
+    swiglu_beta: float | None = None
+    activation_amax: torch.Tensor | None = None
+    layer_idx: int | None = None
     score_func: str = "softmax"
     selection_bias: torch.Tensor | None = None
     route_scale: float = 1.0
-    routed_scaling_factor: float = 1.0
-    output: torch.Tensor | None = None
 
-    def run(self) -> torch.Tensor:
+    def run(self):
         return b12x_sparse_moe_fp4(binding=self)
 
 
-def build_tp_moe_sparse_fp4_binding(**kwargs) -> TPMoESparseFP4Binding:
-    return TPMoESparseFP4Binding(**kwargs)
+def _select_prepared_quant_mode(experts: B12XFP4ExpertWeights, quant_mode: str | None) -> str:
+    modes = experts.plan.quant_modes
+    if quant_mode is None:
+        if len(modes) != 1:
+            raise ValueError(f"quant_mode is required: the experts were prepared for {sorted(modes)}")
+        return next(iter(modes))
+    mode = str(quant_mode).lower()
+    if mode not in modes:
+        raise ValueError(f"quant_mode={mode!r} was not prepared (prepared: {sorted(modes)})")
+    return mode
 
 
-def b12x_sparse_moe_fp4(*, binding: TPMoESparseFP4Binding) -> torch.Tensor:
-    """route -> bind -> run -> multiply by ``routed_scaling_factor`` (reference _impl.py:11493-11575)."""
+def build_tp_moe_sparse_fp4_binding(
+    *,
+    scratch: TPMoEWorkspace,
+    hidden_states: torch.Tensor,
+    experts: B12XFP4ExpertWeights,
+    routing: B12XTopKRouting | None = None,
+    top_k: int | None = None,
+    gate_weight: torch.Tensor | None = None,
+    gate_bias: torch.Tensor | None = None,
+    router_logits: torch.Tensor | None = None,
+    renormalize_topk: bool = True,
+    routed_scaling_factor: float = 1.0,
+    output: torch.Tensor | None = None,
+    return_routing: bool = False,
+    input_scales_static: bool = False,
+    fast_math: bool | None = None,
+    quant_mode: str | None = None,
+    swiglu_limit: float | None = None,
+    swiglu_alpha: float | None = None,
+    swiglu_beta: float | None = None,
+    activation_amax: torch.Tensor | None = None,
+    layer_idx: int | None = None,
+    score_func: str = "softmax",
+    selection_bias: torch.Tensor | None = None,
+    route_scale: float = 1.0,
+) -> TPMoESparseFP4Binding:
+    """Reference ``build_tp_moe_sparse_fp4_binding`` (_impl.py:7886-7958), same keywords."""
+    if not isinstance(scratch, TPMoEWorkspace):
+        raise TypeError("scratch must be a TP MoE scratch object")
+    if hidden_states.ndim != 2:
+        raise ValueError(f"expected hidden_states with rank 2, got shape {tuple(hidden_states.shape)}")
+    if not isinstance(experts, B12XFP4ExpertWeights):
+        raise TypeError("experts must be a B12XFP4ExpertWeights")
+    limit, alpha, beta = normalize_swiglu_params(experts.plan.activation, swiglu_limit, swiglu_alpha, swiglu_beta)
+    _select_prepared_quant_mode(experts, quant_mode)
+    if routing is not None:
+        if top_k is not None or gate_weight is not None or gate_bias is not None or router_logits is not None:
+            raise ValueError("routing is mutually exclusive with top_k/gate_weight/gate_bias/router_logits")
+    elif top_k is None:
+        raise ValueError("top_k is required when routing is not provided")
+    return TPMoESparseFP4Binding(
+        hidden_states=hidden_states, experts=experts, scratch=scratch, routing=routing,
+        top_k=None if top_k is None else int(top_k), gate_weight=gate_weight, gate_bias=gate_bias,
+        router_logits=router_logits, renormalize_topk=bool(renormalize_topk),
+        routed_scaling_factor=float(routed_scaling_factor), output=output, return_routing=bool(return_routing),
+        input_scales_static=bool(input_scales_static), fast_math=fast_math, quant_mode=quant_mode,
+        swiglu_limit=limit, swiglu_alpha=alpha, swiglu_beta=beta, activation_amax=activation_amax,
+        layer_idx=layer_idx, score_func=score_func, selection_bias=selection_bias, route_scale=float(route_scale))
+
+
+def _validate_sparse_routing(hidden_states: torch.Tensor, routing: B12XTopKRouting) -> None:
+    ids, w = routing.topk_ids, routing.topk_weights
+    if ids.ndim != 2 or w.ndim != 2 or ids.shape != w.shape:
+        raise ValueError("routing.topk_ids and routing.topk_weights must be matching rank-2 tensors")
+    if ids.shape[0] != hidden_states.shape[0]:
+        raise ValueError(f"routing batch mismatch: expected {hidden_states.shape[0]}, got {ids.shape[0]}")
+
+
+def b12x_sparse_moe_fp4(*, binding: TPMoESparseFP4Binding):
+    """A fully bound ``gate -> top-k -> routed experts`` block (reference ``b12x_sparse_moe_fp4``
+    _impl.py:11493-11575).  ``routed_scaling_factor`` rides in the combine kernel instead of a
+    separate in-place multiply.  Returns the output, or ``(output, routing)`` with ``return_routing``."""
+    if not isinstance(binding, TPMoESparseFP4Binding):
+        raise TypeError("binding must be a TPMoESparseFP4Binding")
     b = binding
-    routing = b12x_route_experts_fast(binding=TPMoERouteBinding(
-        hidden_states=b.hidden_states, top_k=b.top_k, gate_weight=b.gate_weight,
-        gate_bias=b.gate_bias, router_logits=b.router_logits, renormalize=b.renormalize,
-        score_func=b.score_func, selection_bias=b.selection_bias, route_scale=b.route_scale))
-    core = b.plan.bind(scratch=b.scratch, a=b.hidden_states, experts=b.experts,
-                       topk_weights=routing.topk_weights, topk_ids=routing.topk_ids,
-                       output=b.output, output_scale=b.routed_scaling_factor)
-    return b12x_moe_fp4(binding=core)
+    mode = _select_prepared_quant_mode(b.experts, b.quant_mode)
+    if b.routing is not None:
+        if b.top_k is not None or b.gate_weight is not None or b.gate_bias is not None or b.router_logits is not None:
+            raise ValueError("routing is mutually exclusive with top_k/gate_weight/gate_bias/router_logits")
+        selected = b.routing
+    else:
+        if b.top_k is None:
+            raise ValueError("top_k is required when routing is not provided")
+        selected = b12x_route_experts_fast(binding=build_tp_moe_route_binding(
+            scratch=b.scratch, hidden_states=b.hidden_states, top_k=b.top_k, gate_weight=b.gate_weight,
+            gate_bias=b.gate_bias, router_logits=b.router_logits, renormalize=b.renormalize_topk,
+            score_func=b.score_func, selection_bias=b.selection_bias, route_scale=b.route_scale))
+    _validate_sparse_routing(b.hidden_states, selected)
+    plan = b.scratch.plan
+    if plan.caps.quant_mode != mode:
+        raise ValueError(f"the scratch was planned for quant_mode={plan.caps.quant_mode!r}, the call asks for {mode!r}")
+    core = plan.bind(scratch=b.scratch.storage, a=b.hidden_states, experts=b.experts,
+                     topk_weights=selected.topk_weights, topk_ids=selected.topk_ids, output=b.output,
+                     input_scales_static=b.input_scales_static, fast_math=b.fast_math,
+                     activation_amax=b.activation_amax, layer_idx=b.layer_idx,
+                     output_scale=b.routed_scaling_factor)
+    out = b12x_moe_fp4(binding=core)
+    if b.return_routing:
+        return out, selected
+    return out
 
 
 def clear_tp_moe_caches() -> None:

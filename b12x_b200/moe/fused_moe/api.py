@@ -16,6 +16,7 @@ from ._impl import TPMoERouteBinding as RouteBinding
 from ._impl import TPMoEScratchCaps as Caps
 from ._impl import TPMoEScratchPlan as Plan
 from ._impl import TPMoESparseFP4Binding as SparseBinding
+from ._impl import TPMoEWorkspace as Workspace
 from ._impl import b12x_moe_fp4 as run
 from ._impl import b12x_route_experts_fast as route
 from ._impl import b12x_sparse_moe_fp4 as run_sparse
@@ -45,7 +46,7 @@ def is_supported(device=None) -> bool:
 
 
 __all__ = [
-    "Caps", "Plan", "ExecutionPlan", "Binding", "SparseBinding", "RouteBinding", "ExpertWeights",
+    "Caps", "Plan", "ExecutionPlan", "Binding", "SparseBinding", "RouteBinding", "ExpertWeights", "Workspace",
     "Routing", "WeightsPlan", "plan", "required_nbytes", "plan_execution", "plan_weights",
     "prepare_weights", "bind", "bind_sparse", "bind_route", "run", "run_sparse", "route",
     "route_topk", "is_supported", "clear_caches", "check_device_status",

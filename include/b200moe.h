@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 2
+#define B200MOE_ABI_VERSION 3
 
 /* ---- status codes ------------------------------------------------------ */
 #define B200MOE_OK            0
@@ -33,7 +33,7 @@ extern "C" {
 
 /* ---- enums (int32 in the structs) --------------------------------------- */
 enum { B200MOE_RECIPE_NVFP4 = 0, B200MOE_RECIPE_W4A8_MX = 1, B200MOE_RECIPE_W4A16 = 2 };
-enum { B200MOE_ACT_SILU = 0, B200MOE_ACT_RELU2 = 1, B200MOE_ACT_SWIGLUOAI = 2 };
+enum { B200MOE_ACT_SILU = 0, B200MOE_ACT_RELU2 = 1, B200MOE_ACT_SWIGLUOAI = 2, B200MOE_ACT_SITU = 3 };
 /* score function of the router */
 enum {
   B200MOE_ROUTE_SOFTMAX_TOPK = 0, /* top-k on raw logits, softmax over the k selected */
@@ -116,6 +116,39 @@ typedef struct {
   int32_t reserved;
 } b200moe_route_args;
 int b200moe_route_topk(const b200moe_route_args* a, void* stream);
+
+/* ---- the step in front of stage 1: router gate GEMM + top-k in one launch ---- */
+/* Replaces the gate projection and routing of b12x_route_experts_fast
+ * (b12x/moe/fused_moe/_impl.py:11356-11490: torch.mm into the route workspace,
+ * bias add, then the top-k kernel).  logits_out receives hidden . gate_weight^T
+ * (+ gate_bias) in the operands' common type: bf16 when both are bf16, else f32
+ * (fp32 accumulation; one rounding for the product, one more for the bias).
+ * The router then runs on the stored logits with the semantics of
+ * b200moe_route_topk.  `kernel` picks the implementation: AUTO = tensor cores for
+ * bf16 operands with E % 16 == 0, E <= 256, K % 8 == 0 and at least 128 tokens,
+ * else the CUDA-core kernel. */
+enum { B200MOE_GATE_AUTO = 0, B200MOE_GATE_SIMT = 1, B200MOE_GATE_TC = 2 };
+typedef struct {
+  const void* hidden;        /* [T][hidden_row_stride] bf16 or f32                */
+  const void* gate_weight;   /* [E][K] contiguous, bf16 or f32                    */
+  const void* gate_bias;     /* [E] bf16 or f32, or NULL                          */
+  void* logits_out;          /* [T][E] contiguous, bf16 or f32 (see above)        */
+  int32_t* tile_counters;    /* int32[ceil(T/4)] work space (cleared by the call on its stream)  */
+  const float* selection_bias; /* SIGMOID mode, [E] or NULL                      */
+  float* topk_logits;        /* [T][k] or NULL                                    */
+  int32_t* topk_ids;         /* [T][k]                                            */
+  float* topk_weights;       /* [T][k]                                            */
+  int32_t* status;           /* int32[16] status block for bounded waits, or NULL */
+  int64_t hidden_row_stride; /* elements                                          */
+  int32_t num_tokens, num_experts, hidden_size, num_topk;
+  int32_t hidden_dtype, weight_dtype, bias_dtype; /* B200MOE_DT_*                  */
+  int32_t mode;              /* B200MOE_ROUTE_*                                   */
+  int32_t renormalize;
+  float route_scale;
+  int32_t kernel;            /* B200MOE_GATE_*                                    */
+  int32_t reserved;
+} b200moe_gate_route_args;
+int b200moe_gate_route(const b200moe_gate_route_args* a, void* stream);
 
 /* ---- stage 2: expert sort / permutation -------------------------------- */
 /* Replaces the histogram / prefix / route-pack phases of the reference's

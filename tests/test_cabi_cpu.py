@@ -27,7 +27,7 @@ def test_every_declared_symbol_is_exported(lib):
     assert declared == set(ext.EXPORTS), declared ^ set(ext.EXPORTS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.b200moe_abi_version() == 2
+    assert lib.b200moe_abi_version() == 3
     assert lib.b200moe_strerror(-2).decode().startswith("problem exceeds")
 
 
@@ -105,8 +105,12 @@ def test_weight_plan_contracts():
         _wplan(source_format="fp4_e8m0_k32")                     # nvfp4 needs a ModelOpt source
     with pytest.raises(ValueError):
         _wplan(activation="gelu")
+    assert _wplan(activation="situ").w1_rows == 1024 and _wplan(activation="situ").w13_layout == "w13"
     with pytest.raises(NotImplementedError):
-        _wplan(activation="situ")
+        _wplan(activation="situ", quant_modes="w4a16")          # no W4A16 oracle for situ
+    with pytest.raises(ValueError):
+        fused_moe.Caps(max_tokens=4, num_topk=1, device="cpu", quant_mode="nvfp4",
+                       weight_plan=_wplan(activation="situ"), swiglu_limit=7.0)
     with pytest.raises(ValueError):
         _wplan(hidden_size=1000)
     with pytest.raises(TypeError):
@@ -124,7 +128,9 @@ def test_caps_plan_and_required_nbytes_agree(lib):
     assert spec.dtype == torch.uint8 and spec.shape == (fused_moe.required_nbytes(caps),)
     assert plan.shapes_and_dtypes() == ((spec.shape, torch.uint8),)
     assert plan.launch_plan.max_m_tiles == 1 + 8
-    assert fused_moe.plan_execution(caps, 3).routed_rows == 6
+    ep = fused_moe.plan_execution(num_tokens=3, num_topk=caps.num_topk, device="cpu", weight_plan=caps.weight_plan,
+                                  quant_mode=caps.quant_mode)
+    assert ep.routed_rows == 6 and ep.execution.regime.value == ep.implementation
     with pytest.raises(ValueError):
         fused_moe.Caps(max_tokens=16, num_topk=2, device="cpu", weight_plan=wp, quant_mode="w4a16")
     with pytest.raises(ValueError):

@@ -1,9 +1,6 @@
 """-m gpu: shapes that leave partial tiles (K and I that are multiples of 64 but not of 128 / 256),
-for the nvfp4 recipe, and both tile widths of the grouped GEMM kernel."""
+for the nvfp4 recipe."""
 
-import os
-import subprocess
-import sys
 from pathlib import Path
 
 import pytest
@@ -22,11 +19,3 @@ def test_nvfp4_partial_tiles(tokens, hidden, inter, act):
     shp = synth.shape("c1", name="tail", tokens=tokens, hidden=hidden, intermediate=inter, experts=4, topk=2,
                       activation=act)
     _check_nvfp4_layer(run_layer(synth.make_inputs(shp, seed=hidden + inter)))
-
-
-def test_narrow_tile_variant_passes_the_parity_suite():
-    """The 128-wide, double-buffered tile is selected with B200MOE_TILE_N=128 (read once per process)."""
-    env = dict(os.environ, B200MOE_TILE_N="128")
-    res = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-m", "gpu", "tests/test_gpu_parity.py",
-                          "-k", "nvfp4 or mx or c1"], cwd=ROOT, env=env, capture_output=True, text=True)
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
