@@ -27,7 +27,7 @@ from .. import synth
 from . import fused_moe
 from .fused_moe.stages import StageArena
 
-_ACT_API = {"silu": "silu", "relu2": "relu2", "swigluoai": "swigluoai_uninterleave"}
+_ACT_API = {"silu": "silu", "relu2": "relu2", "swigluoai": "swigluoai_uninterleave", "situ": "situ"}
 _SOURCE = {"nvfp4": "modelopt_nvfp4", "w4a16": "modelopt_nvfp4", "w4a8_mx": "fp4_e8m0_k32"}
 
 

@@ -11,7 +11,7 @@ from b12x_b200 import synth
 from b12x_b200.moe import fused_moe
 from oracle import moe_oracle as O
 
-ACT_API = {"silu": "silu", "relu2": "relu2", "swigluoai": "swigluoai_uninterleave"}
+ACT_API = {"silu": "silu", "relu2": "relu2", "swigluoai": "swigluoai_uninterleave", "situ": "situ"}
 SOURCE = {"nvfp4": "modelopt_nvfp4", "w4a16": "modelopt_nvfp4", "w4a8_mx": "fp4_e8m0_k32"}
 
 

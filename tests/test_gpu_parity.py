@@ -142,6 +142,20 @@ def test_nvfp4_golden_swigluoai_inputs():
     assert (run.out_f32 - ref).abs().max().item() <= OUT_TOL * ref.square().mean().sqrt().item()
 
 
+@pytest.mark.parametrize("tile_rows", [64, 128])
+def test_nvfp4_situ_against_oracle_and_reference_fixture(tile_rows):
+    """The SiTU activation on both kernel families, stage by stage against the oracle, and on the
+    fixture's inputs against the output of the reference's own oracle."""
+    _check_nvfp4_layer(run_layer(synth.make_inputs(_tiny(tokens=40, activation="situ"), seed=13), tile_rows=tile_rows))
+    g = load_golden("tiny_nvfp4_situ.npz")
+    inp = synth.make_inputs(synth.shape("c1", name="tiny_situ", tokens=8, hidden=256, intermediate=128, experts=4,
+                                        activation="situ"), seed=6)
+    assert torch.equal(inp.w1_fp4, t(g["in_w1_fp4"])) and torch.equal(inp.x.view(torch.int16), t(g["in_x"]))
+    run = run_layer(inp, topk_ids=t(g["topk_ids"]), topk_weights=t(g["topk_weights"]), tile_rows=tile_rows)
+    ref = t(g["out_f32"])
+    assert (run.out_f32 - ref).abs().max().item() <= OUT_TOL * ref.square().mean().sqrt().item()
+
+
 def test_relu2_reference_bit_exact_case():
     """E=1, K=N=128: the reference requires max_abs == 0 between its kernel and its oracle
     (tests/moe/test_tp_moe_relu2_reference.py:240-274)."""

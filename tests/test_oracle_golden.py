@@ -113,6 +113,27 @@ def test_tiny_nvfp4_silu_and_swigluoai_match_reference_oracle():
     _check_nvfp4_case(g, _stored_inputs(g), "swigluoai")
 
 
+def test_tiny_nvfp4_situ_matches_reference_oracle():
+    """SiTU (4 tanh(g/4) sigmoid(g) * 25 tanh(u/25)) against ``moe_reference_nvfp4(activation="situ")``
+    of the reference (fixture made by tests/golden/make_golden_routing.py)."""
+    g = load_golden("tiny_nvfp4_situ.npz")
+    inp = _stored_inputs(g)
+    a1 = inp["w1_global_scale"] / inp["a1_gscale"]
+    a2 = inp["w2_global_scale"] / inp["a2_gscale"]
+    ids, tw = t(g["topk_ids"]), t(g["topk_weights"])
+    taps = O.MoETaps()
+    out = O.moe_nvfp4(inp["x"], inp["w1_fp4"], inp["w1_blockscale"], a1, inp["w2_fp4"], inp["w2_blockscale"], a2,
+                      inp["a1_gscale"], inp["a2_gscale"], ids, tw, activation="situ", taps=taps)
+    tt, topk = ids.shape
+    inv = taps.sort.inv_perm.reshape(tt, topk).long()
+    flips = (taps.mid[inv] != t(g["mid"])).float().mean().item()
+    assert flips < 2e-3, f"bf16 intermediate differs in {flips:.2%} of elements"
+    ref = t(g["out_f32"])
+    assert (taps.out_f32 - ref).abs().max().item() <= 1e-2 * ref.square().mean().sqrt().item()
+    ref_bf16 = t(g["out_bf16"], torch.bfloat16).float()
+    assert (out.float() - ref_bf16).abs().max().item() <= 2 * 2.0 ** -8 * ref_bf16.abs().max().item()
+
+
 def test_relu2_bit_exact_case():
     g = load_golden("relu2_e1_k128.npz")
     out = O.moe_nvfp4(t(g["x"], torch.bfloat16), t(g["w1_fp4"]), t(g["w1_blockscale"]), t(g["w1_alphas"]),
