@@ -8,7 +8,10 @@ namespace b200moe {
 
 constexpr int kMaxExperts = 1024;
 
-enum { EPI_FC1_GATED = 0, EPI_FC1_RELU2 = 1, EPI_FC2 = 2, EPI_FC1_SILU = 3 };
+// FC1 epilogues: GATED = SwiGLU with a clamp and/or the SwiGLU-OAI form (chosen at run time), SILU = plain
+// SwiGLU, SITU = the SiTU form; each is its own instantiation so that none carries the others' code.
+enum { EPI_FC1_GATED = 0, EPI_FC1_RELU2 = 1, EPI_FC2 = 2, EPI_FC1_SILU = 3, EPI_FC1_SITU = 4 };
+__host__ __device__ constexpr bool epi_is_gated(int epi) { return epi == EPI_FC1_GATED || epi == EPI_FC1_SILU || epi == EPI_FC1_SITU; }
 // KIND_NVFP4: A and B packed E2M1, E4M3 scale per 16, kind::mxf4nvf4 (K = 64 per MMA, 256 per stage).
 // KIND_MX:    A E4M3 bytes, B E2M1 expanded by TMA to one value per byte slot, E8M0 scale per 32,
 //             kind::mxf8f6f4 (K = 32 per MMA, 128 per stage; one scale atom per stage).
@@ -86,10 +89,17 @@ __device__ __forceinline__ float div_rn_normal(float a, float b, float rb) {
 // SiTU (b12x/moe/_shared/kernels/reference.py:160-172): 4 tanh(g / 4) sigmoid(g) * 25 tanh(u / 25)
 constexpr float kSituBeta = 4.0f, kSituLinearBeta = 25.0f;
 
-// GENERIC = false: plain SwiGLU (no clamp); true: clamp and/or the SwiGLU-OAI / SiTU forms, chosen at run time.
-template <bool GENERIC>
+// EPI selects the form: EPI_FC1_SILU plain SwiGLU (no clamp); EPI_FC1_GATED clamp and/or SwiGLU-OAI, chosen
+// at run time; EPI_FC1_SITU the SiTU form.
+template <int EPI>
 __device__ __forceinline__ float act_gated(float gate, float up, const GemmParams& p) {
-  if (GENERIC) {
+  if (EPI == EPI_FC1_SITU) {
+    const float s = rcp_newton(1.0f + expf(fminf(-gate, 80.0f)));
+    const float sg = __fmul_rn(__fmul_rn(kSituBeta, tanhf(__fdiv_rn(gate, kSituBeta))), s);
+    const float su = __fmul_rn(kSituLinearBeta, tanhf(__fdiv_rn(up, kSituLinearBeta)));
+    return __fmul_rn(sg, su);
+  }
+  if (EPI == EPI_FC1_GATED) {
     if (p.limit > 0.f) {
       gate = fminf(gate, p.limit);
       up = fminf(fmaxf(up, -p.limit), p.limit);
@@ -97,12 +107,6 @@ __device__ __forceinline__ float act_gated(float gate, float up, const GemmParam
     if (p.act_kind == 1) {
       const float s = rcp_newton(1.0f + expf(fminf(-(p.act_alpha * gate), 80.0f)));
       return (gate * s) * (up + p.act_beta);
-    }
-    if (p.act_kind == 2) {
-      const float s = rcp_newton(1.0f + expf(fminf(-gate, 80.0f)));
-      const float sg = __fmul_rn(__fmul_rn(kSituBeta, tanhf(__fdiv_rn(gate, kSituBeta))), s);
-      const float su = __fmul_rn(kSituLinearBeta, tanhf(__fdiv_rn(up, kSituLinearBeta)));
-      return __fmul_rn(sg, su);
     }
   }
   // the exponent is capped so that 1 + e stays finite (sigmoid below 2e-35 instead of 0)
@@ -199,7 +203,7 @@ template <int KIND, int EPI, int BN, class Release>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, int e, int mt, int nt, int row0, int nrows,
                                               uint32_t t_lane, int m, int half, int lane, Release release) {
   static_assert(BN == 256, "the epilogue is written for 256-column tiles");
-  constexpr bool kGated = EPI == EPI_FC1_GATED || EPI == EPI_FC1_SILU;
+  constexpr bool kGated = epi_is_gated(EPI);
   uint32_t acc[128];
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
@@ -238,7 +242,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, int e, int mt
             trow[p.sub0_base] = up;
             trow[p.sub1_base] = gate;
           }
-          h[i] = act_gated<EPI == EPI_FC1_GATED>(gate, up, p);
+          h[i] = act_gated<EPI>(gate, up, p);
         }
         uint32_t o[8];
         uint8_t sfb;
@@ -268,7 +272,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, int e, int mt
             trow[p.sub0_base] = up;
             trow[p.sub1_base] = gate;
           }
-          h[i] = round_bf16(act_gated<EPI == EPI_FC1_GATED>(gate, up, p));
+          h[i] = round_bf16(act_gated<EPI>(gate, up, p));
         }
         uint32_t lo, hi;
         uint8_t sfb;

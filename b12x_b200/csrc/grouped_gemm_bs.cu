@@ -70,7 +70,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
   constexpr int kStages = Cfg::kStages;
   constexpr int kSmemB = Cfg::kSmemB;
   constexpr int kSmemSfb = Cfg::kSmemSfb;
-  constexpr bool kGated = EPI == EPI_FC1_GATED || EPI == EPI_FC1_SILU;
+  constexpr bool kGated = epi_is_gated(EPI);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -251,6 +251,10 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t acc_phase[2] = {0, 0};
       int buf = 0;
       bool ok = true;
+      const uint64_t adesc0 = make_desc_sw128(smem_u32(sA)), bdesc0 = make_desc_sw128(smem_u32(sB));
+      const uint32_t sf0_t = tmem_base + kTmemSf;
+      // MMAs of a tile's last k-block (a K that is not a multiple of the stage leaves fewer)
+      const int last_ksteps = min(4, (p.kdim - (p.k_blocks - 1) * kPerStage) / kPerMma);
       TL_DECL(tl_n);
       TL_DECL(tl_t);
       for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
@@ -273,31 +277,50 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
           TL_STAGE(tl_k, tl_slot, TL_M_FULL, tl_n);
           TL_STAGE(tl_k, tl_slot, TL_M_SF, tl_n);
           tc_fence_after();
-          const int ksteps = min(4, (p.kdim - kb * kPerStage) / kPerMma);
-          const uint32_t sfa_t = tmem_base + kTmemSf + stage * Cfg::kSfCols;
+          // the stage's descriptors differ from stage 0's only in the start-address field (16-byte units)
+          const uint32_t sfa_t = sf0_t + stage * Cfg::kSfCols;
           const uint32_t sfb_t = sfa_t + 16;
-          const uint64_t adesc = make_desc_sw128(smem_u32(sA + stage * kSmemA));
-          const uint64_t bdesc = make_desc_sw128(smem_u32(sB + stage * kSmemB));
-          const int nstage = stage + 1 == kStages ? 0 : stage + 1;
-          const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
-          for (int j = 0; j < ksteps; ++j) {
+          const uint64_t adesc = adesc0 + static_cast<uint32_t>(stage * (kSmemA >> 4));
+          const uint64_t bdesc = bdesc0 + static_cast<uint32_t>(stage * (kSmemB >> 4));
+          // This thread shares its scheduler with busy epilogue warps: the fewer instructions between
+          // two MMAs, the shorter the tensor pipe waits for it.  A full k-block is four MMAs, each 32
+          // bytes further along the swizzled rows (+2 in 16-byte units): 64 FP4 values, or 32 bytes
+          // of the MX kind, whose scale atom holds the four per-32 scales of the stage (MMA step j
+          // uses byte j of each word).
+          if (kb + 1 < p.k_blocks || last_ksteps == 4) {
             if (KIND == KIND_MX) {
-              // one atom = the four per-32 scales of this stage; MMA step j uses byte j of each word;
-              // 32 one-byte slots further along the swizzled row -> +2 in 16-byte units
-              const uint32_t ju = static_cast<uint32_t>(j);
-              mma_mxf8f6f4(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc | (ju << 29) | (ju << 4),
-                           sfa_t + (ju << 30), sfb_t + (ju << 30), (kb > 0 || j > 0) ? 1u : 0u);
+              mma_mxf8f6f4(d_tmem, adesc, bdesc, idesc, sfa_t, sfb_t, kb > 0 ? 1u : 0u);
+              mma_mxf8f6f4(d_tmem, adesc + 2, bdesc + 2, idesc | (1u << 29) | (1u << 4), sfa_t + (1u << 30),
+                           sfb_t + (1u << 30), 1u);
+              mma_mxf8f6f4(d_tmem, adesc + 4, bdesc + 4, idesc | (2u << 29) | (2u << 4), sfa_t + (2u << 30),
+                           sfb_t + (2u << 30), 1u);
+              mma_mxf8f6f4(d_tmem, adesc + 6, bdesc + 6, idesc | (3u << 29) | (3u << 4), sfa_t + (3u << 30),
+                           sfb_t + (3u << 30), 1u);
             } else {
-              // 64 FP4 values = 32 bytes further along the swizzled row -> +2 in 16-byte units
-              mma_nvf4_4x(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j,
-                          sfb_t + kSfbStep * j, (kb > 0 || j > 0) ? 1u : 0u);
+              mma_nvf4_4x(d_tmem, adesc, bdesc, idesc, sfa_t, sfb_t, kb > 0 ? 1u : 0u);
+              mma_nvf4_4x(d_tmem, adesc + 2, bdesc + 2, idesc, sfa_t + 4, sfb_t + kSfbStep, 1u);
+              mma_nvf4_4x(d_tmem, adesc + 4, bdesc + 4, idesc, sfa_t + 8, sfb_t + 2 * kSfbStep, 1u);
+              mma_nvf4_4x(d_tmem, adesc + 6, bdesc + 6, idesc, sfa_t + 12, sfb_t + 3 * kSfbStep, 1u);
+            }
+          } else {
+            for (int j = 0; j < last_ksteps; ++j) {
+              if (KIND == KIND_MX) {
+                const uint32_t ju = static_cast<uint32_t>(j);
+                mma_mxf8f6f4(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc | (ju << 29) | (ju << 4),
+                             sfa_t + (ju << 30), sfb_t + (ju << 30), (kb > 0 || j > 0) ? 1u : 0u);
+              } else {
+                mma_nvf4_4x(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j,
+                            sfb_t + kSfbStep * j, (kb > 0 || j > 0) ? 1u : 0u);
+              }
             }
           }
           tc_commit(&tail->empty[stage]);
           TL_STAGE(tl_k, tl_slot, TL_M_COMMIT, tl_n);
           TL_INC(tl_n);
-          stage = nstage;
-          phase = nphase;
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
         }
         if (ok) tc_commit(&tail->tmem_full[buf]);
         acc_phase[buf] ^= 1;
@@ -543,6 +566,7 @@ static int gemm1_any(const b200moe_gemm_args* a, cudaStream_t stream) {
     p.sub1_base = a->gate_first ? 0 : I;   // gate rows
     if (p.act_kind == 0 && !(p.limit > 0.f))
       return launch_any<KIND, EPI_FC1_SILU>(bn, tmA, tmA_small, tmB, p, grid, stream);
+    if (p.act_kind == 2) return launch_any<KIND, EPI_FC1_SITU>(bn, tmA, tmA_small, tmB, p, grid, stream);
     return launch_any<KIND, EPI_FC1_GATED>(bn, tmA, tmA_small, tmB, p, grid, stream);
   }
   p.sfb_rowgroups = ceil_div_i(I, 128);

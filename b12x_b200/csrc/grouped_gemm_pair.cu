@@ -139,7 +139,7 @@ template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                                const GemmParams p) {
-  constexpr bool kGated = EPI == EPI_FC1_GATED || EPI == EPI_FC1_SILU;
+  constexpr bool kGated = epi_is_gated(EPI);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -320,6 +320,9 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       int stage = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
+      const uint64_t adesc0 = make_desc_sw128(smem_u32(sA)), bdesc0 = make_desc_sw128(smem_u32(sB));
+      const uint32_t sf0_t = tmem_base + kTmemSf;
+      const int last_ksteps = min(4, (p.kdim - (p.k_blocks - 1) * 256) / 64);   // MMAs of a tile's last k-block
       TL_DECL(tl_n);
       TL_DECL(tl_t);
       for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
@@ -339,24 +342,32 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           }
           TL_STAGE(tl_k, tl_slot, TL_M_SF, tl_n);
           tc_fence_after();
-          const int ksteps = min(4, (p.kdim - kb * 256) / 64);
-          const uint32_t sfa_t = tmem_base + kTmemSf + stage * kSfCols;
+          // the stage's descriptors differ from stage 0's only in the start-address field (16-byte units)
+          const uint32_t sfa_t = sf0_t + stage * kSfCols;
           const uint32_t sfb_t = sfa_t + 16;
-          const uint64_t adesc = make_desc_sw128(smem_u32(sA + stage * kSmemA));
-          const uint64_t bdesc = make_desc_sw128(smem_u32(sB + stage * kSmemB));
-          const int nstage = stage + 1 == kStages ? 0 : stage + 1;
-          const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
-          for (int j = 0; j < ksteps; ++j) {
-            mma_nvf4_4x_pair(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j, sfb_t + 8 * j,
-                             (kb > 0 || j > 0) ? 1u : 0u);
-            if (j == 0) TL_STAGE(tl_k, tl_slot, TL_M_MMA0, tl_n);
+          const uint64_t adesc = adesc0 + static_cast<uint32_t>(stage * (kSmemA >> 4));
+          const uint64_t bdesc = bdesc0 + static_cast<uint32_t>(stage * (kSmemB >> 4));
+          if (kb + 1 < p.k_blocks || last_ksteps == 4) {
+            // this thread shares its scheduler with busy epilogue warps: the fewer instructions
+            // between two MMAs, the shorter the tensor pipe waits for it
+            mma_nvf4_4x_pair(tmem_base, adesc, bdesc, idesc, sfa_t, sfb_t, kb > 0 ? 1u : 0u);
+            TL_STAGE(tl_k, tl_slot, TL_M_MMA0, tl_n);
+            mma_nvf4_4x_pair(tmem_base, adesc + 2, bdesc + 2, idesc, sfa_t + 4, sfb_t + 8, 1u);
+            mma_nvf4_4x_pair(tmem_base, adesc + 4, bdesc + 4, idesc, sfa_t + 8, sfb_t + 16, 1u);
+            mma_nvf4_4x_pair(tmem_base, adesc + 6, bdesc + 6, idesc, sfa_t + 12, sfb_t + 24, 1u);
+          } else {
+            for (int j = 0; j < last_ksteps; ++j)
+              mma_nvf4_4x_pair(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j, sfb_t + 8 * j,
+                               (kb > 0 || j > 0) ? 1u : 0u);
           }
           TL_STAGE(tl_k, tl_slot, TL_M_ISSUED, tl_n);
           tc_commit_pair_both(&tail->empty[stage]);
           TL_STAGE(tl_k, tl_slot, TL_M_COMMIT, tl_n);
           TL_INC(tl_n);
-          stage = nstage;
-          phase = nphase;
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
         }
         if (ok) tc_commit_pair_both(&tail->tmem_full);
         acc_phase ^= 1;
@@ -528,6 +539,7 @@ int nvfp4_pair_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
   const int ctas = a->num_sms > 0 ? a->num_sms : num_sms_cached();
   if (p.act_kind == 0 && !(p.limit > 0.f))
     return pair::launch<EPI_FC1_SILU>(tmA, tmB, p, ctas, stream);
+  if (p.act_kind == 2) return pair::launch<EPI_FC1_SITU>(tmA, tmB, p, ctas, stream);
   return pair::launch<EPI_FC1_GATED>(tmA, tmB, p, ctas, stream);
 }
 

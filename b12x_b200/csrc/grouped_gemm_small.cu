@@ -108,7 +108,7 @@ grouped_gemm_nvfp4_small_kernel(const __grid_constant__ CUtensorMap tmW,
                                 const __grid_constant__ CUtensorMap tmX16,
                                 const __grid_constant__ CUtensorMap tmX32,
                                 const __grid_constant__ CUtensorMap tmX64, const GemmParams p) {
-  constexpr bool kGated = EPI == EPI_FC1_GATED || EPI == EPI_FC1_SILU;
+  constexpr bool kGated = epi_is_gated(EPI);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -342,7 +342,7 @@ grouped_gemm_nvfp4_small_kernel(const __grid_constant__ CUtensorMap tmW,
                 trow[p.sub0_base] = up;
                 trow[p.sub1_base] = gate;
               }
-              h[t] = round_bf16(act_gated<EPI == EPI_FC1_GATED>(gate, up, p));
+              h[t] = round_bf16(act_gated<EPI>(gate, up, p));
             }
             uint32_t codes[2], sfw[4];
             requant_lane16(h, gs2, rgs2, codes, sfw);
@@ -474,6 +474,7 @@ int nvfp4_small_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
   p.out_atoms = I / 64;
   const int grid = a->num_sms > 0 ? a->num_sms : num_sms_cached();
   if (p.act_kind == 0 && !(p.limit > 0.f)) return small::launch<EPI_FC1_SILU>(tmW, tmX, p, grid, stream);
+  if (p.act_kind == 2) return small::launch<EPI_FC1_SITU>(tmW, tmX, p, grid, stream);
   return small::launch<EPI_FC1_GATED>(tmW, tmX, p, grid, stream);
 }
 
