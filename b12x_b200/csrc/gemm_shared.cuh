@@ -114,6 +114,13 @@ __device__ __forceinline__ float act_gated(float gate, float up, const GemmParam
   return (gate * s) * up;
 }
 
+// One 32-byte store (sm_100 has 256-bit global stores); `p` must be 32-byte aligned.
+__device__ __forceinline__ void st_global_f32x8(float* p, const float (&v)[8]) {
+  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]),
+               "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+               : "memory");
+}
+
 __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
@@ -341,16 +348,18 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, int e, int mt
   } else {
     const int col0 = nt * 256 + half * 128;
     float* orow = p.out_f32 + pos * p.out_cols + col0;
+    // 32-byte stores: a lane writes whole sectors of its own row (rows are 32-byte aligned: the row
+    // length is a multiple of 16 floats and the arena's views start on 1 KiB boundaries)
 #pragma unroll
     for (int ch = 0; ch < 8; ++ch) {
       if (valid && col0 + ch * 16 < p.out_cols) {
-        float4* dst = reinterpret_cast<float4*>(orow + ch * 16);
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          dst[q] = make_float4(__fmul_rn(__uint_as_float(acc[ch * 16 + 4 * q]), alpha),
-                               __fmul_rn(__uint_as_float(acc[ch * 16 + 4 * q + 1]), alpha),
-                               __fmul_rn(__uint_as_float(acc[ch * 16 + 4 * q + 2]), alpha),
-                               __fmul_rn(__uint_as_float(acc[ch * 16 + 4 * q + 3]), alpha));
+        for (int q = 0; q < 2; ++q) {
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__uint_as_float(acc[ch * 16 + 8 * q + i]), alpha);
+          st_global_f32x8(orow + ch * 16 + 8 * q, v);
+        }
       }
     }
   }

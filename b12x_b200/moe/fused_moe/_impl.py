@@ -555,8 +555,8 @@ class TPMoEScratchPlan:
                 raise ValueError("output must be [tokens, K] in the plan dtype, row-contiguous")
         storage = scratch_tensor(scratch, self._scratch_specs, owner="TP MoE")
         core = storage.narrow(0, self.layout.route_workspace_nbytes, self.layout.core_workspace_nbytes)
-        if core.data_ptr() % 16 != 0:
-            raise ValueError("scratch must be 16-byte aligned")
+        if core.data_ptr() % 32 != 0:
+            raise ValueError("scratch must be 32-byte aligned")
         return TPMoEFP4Binding(
             a=a, experts=experts, topk_weights=topk_weights, topk_ids=topk_ids,
             implementation=self.launch_plan.implementation, weight_E=caps.weight_E,
