@@ -8,9 +8,11 @@ int nvfp4_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
 bool nvfp4_small_batch_ok(const b200moe_gemm_args* a, bool fc1);
 int nvfp4_small_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
 int nvfp4_small_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
-bool nvfp4_pair_ok(const b200moe_gemm_args* a, bool fc1);
+bool pair_ok(const b200moe_gemm_args* a, bool fc1);
 int nvfp4_pair_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
 int nvfp4_pair_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
+int mx_pair_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
+int mx_pair_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
 int mx_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
 int mx_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
 int w4a16_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
@@ -129,9 +131,10 @@ extern "C" int b200moe_grouped_gemm1_act(const b200moe_gemm_args* a, void* strea
     case B200MOE_RECIPE_NVFP4:
       if (a->w13_sf == nullptr || a->a2_gscale == nullptr) return B200MOE_EINVAL;
       if (b200moe::nvfp4_small_batch_ok(a, /*fc1=*/true)) return b200moe::nvfp4_small_gemm1(a, s);
-      if (b200moe::nvfp4_pair_ok(a, /*fc1=*/true)) return b200moe::nvfp4_pair_gemm1(a, s);
+      if (b200moe::pair_ok(a, /*fc1=*/true)) return b200moe::nvfp4_pair_gemm1(a, s);
       return b200moe::nvfp4_gemm1(a, s);
     case B200MOE_RECIPE_W4A8_MX:
+      if (b200moe::pair_ok(a, /*fc1=*/true)) return b200moe::mx_pair_gemm1(a, s);
       return b200moe::mx_gemm1(a, s);
     case B200MOE_RECIPE_W4A16:
       return b200moe::w4a16_gemm1(a, s);
@@ -149,9 +152,10 @@ extern "C" int b200moe_grouped_gemm2(const b200moe_gemm_args* a, void* stream) {
     case B200MOE_RECIPE_NVFP4:
       if (a->w2_sf == nullptr) return B200MOE_EINVAL;
       if (b200moe::nvfp4_small_batch_ok(a, /*fc1=*/false)) return b200moe::nvfp4_small_gemm2(a, s);
-      if (b200moe::nvfp4_pair_ok(a, /*fc1=*/false)) return b200moe::nvfp4_pair_gemm2(a, s);
+      if (b200moe::pair_ok(a, /*fc1=*/false)) return b200moe::nvfp4_pair_gemm2(a, s);
       return b200moe::nvfp4_gemm2(a, s);
     case B200MOE_RECIPE_W4A8_MX:
+      if (b200moe::pair_ok(a, /*fc1=*/false)) return b200moe::mx_pair_gemm2(a, s);
       return b200moe::mx_gemm2(a, s);
     case B200MOE_RECIPE_W4A16:
       return b200moe::w4a16_gemm2(a, s);

@@ -379,6 +379,8 @@ __device__ __forceinline__ void regs_raise_to() {
 // 2-D byte matrix [rows][row_bytes], box = box_rows x 128 bytes, 128-byte swizzle.
 int make_tmap_bytes_2d(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,
                        uint32_t box_rows);
+// 2-D matrix of packed E2M1 values; the TMA expands every 16 values to a 16-byte slot (kind::mxf8f6f4)
+int make_tmap_fp4_unpack_2d(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows);
 int num_sms_cached();
 void fill_common(GemmParams& p, const b200moe_gemm_args* a, char* base);
 

@@ -1,4 +1,4 @@
-// Stages 4 and 5 for large batches (recipe nvfp4) on CTA PAIRS: tcgen05 with cta_group::2.
+// Stages 4 and 5 for large batches (recipes nvfp4 and w4a8_mx) on CTA PAIRS: tcgen05 with cta_group::2.
 //
 // Two CTAs of a cluster share one 256 x 256 tile: each owns 128 token rows (its own row tile of the
 // expert) and loads only HALF of the 256 weight rows; the pair's MMA (M = 256, N = 256, issued by
@@ -38,7 +38,9 @@ constexpr int kSfSlotBytes = kSmemSfa + kSmemSfb;
 constexpr int kTmemCols = 512;
 constexpr int kTmemSf = 256;                  // accumulator: columns 0..255
 constexpr int kSfCols = 48;                   // per stage: 16 (tokens) + 32 (weights)
-constexpr uint32_t kStageTxBytes = 2u * (kSmemA + kSmemB);   // both CTAs' operand copies of one stage
+// bytes both CTAs' operand copies of one stage report to the barrier (the 4-bit unpacking TMA type of
+// the MX kind counts the packed bytes it reads: half of what it writes)
+__host__ __device__ constexpr uint32_t stage_tx_bytes(int kind) { return 2u * (kSmemA + (kind == KIND_MX ? kSmemB / 2 : kSmemB)); }
 
 struct __align__(8) SmemTail {
   uint64_t full[kStages];       // used in the even CTA: all copies of the pair have landed
@@ -117,6 +119,17 @@ __device__ __forceinline__ void mma_nvf4_4x_pair(uint32_t d_tmem, uint64_t adesc
       : "memory");
 }
 
+__device__ __forceinline__ void mma_mxf8f6f4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                  uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale "
+      "[%0], %1, %2, %3, [%5], [%6], p;\n\t}\n"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+
 // Work item of a CTA pair: (expert, n-tile, pair of row tiles).  This CTA's row tile is
 // first + rank; an expert with an odd number of row tiles leaves the odd CTA of its last pair
 // without one (rows = 0: it multiplies the neighbour's rows again and stores nothing).
@@ -135,11 +148,17 @@ __device__ __forceinline__ PairCoord decode_pair(int w, const GemmParams& p, con
   return r;
 }
 
-template <int EPI>
+// KIND_NVFP4: 256 values per stage, four MMAs of 64, one scale atom per MMA and 128 rows.
+// KIND_MX: 128 values per stage (the weights' FP4 codes expanded to bytes by the TMA), four MMAs of
+// 32, ONE scale atom per stage and 128 rows (its four bytes are the per-32 scales of the stage).
+template <int KIND, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
-grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                                const GemmParams p) {
   constexpr bool kGated = epi_is_gated(EPI);
+  constexpr int kPerStage = KIND == KIND_MX ? 128 : 256;   // reduction elements per stage
+  constexpr int kPerMma = KIND == KIND_MX ? 32 : 64;
+  constexpr uint32_t kAtomBytes = KIND == KIND_MX ? 512u : 2048u;   // scale bytes per stage and 128 rows
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -235,7 +254,7 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           if (lane == 0) TL_STAGE(tl_k, tl_slot, TL_P_EMPTY, tl_n);
           const uint32_t bar = map_to_cta(smem_u32(&tail->full[stage]), 0);
           if (lane == 0) {
-            if (rank == 0) mbar_expect_tx(&tail->full[stage], kStageTxBytes);
+            if (rank == 0) mbar_expect_tx(&tail->full[stage], stage_tx_bytes(KIND));
             tma_load_2d_pair(sA + stage * kSmemA, &tmA, bar, kb * kRowBytes, y);
           } else {
             tma_load_2d_pair(sB + stage * kSmemB + (lane - 1) * 64 * kRowBytes, &tmB, bar, kb * kRowBytes, y);
@@ -293,9 +312,10 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
             ok = false;
             break;
           }
-          const int ksteps = min(4, (p.kdim - kb * 256) / 64);
-          const uint32_t sf_bytes = static_cast<uint32_t>(ksteps) * 512u;
-          const size_t sf_off = static_cast<size_t>(kb) * 2048;
+          const int ksteps = min(4, (p.kdim - kb * kPerStage) / kPerMma);
+          // NVFP4: one scale atom per MMA step; MX: one atom covers the whole stage
+          const uint32_t sf_bytes = KIND == KIND_MX ? 512u : static_cast<uint32_t>(ksteps) * 512u;
+          const size_t sf_off = static_cast<size_t>(kb) * kAtomBytes;
           uint8_t* dst = sSf + slot * kSfSlotBytes;
           if (lane == 0) {
             mbar_expect_tx(&tail->sf_landed[slot], 3u * sf_bytes);
@@ -316,13 +336,15 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (even CTA) -------------------------
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = make_idesc_block_scaled(256, 256, /*a*/ 1, /*b*/ 1, /*ue4m3*/ 0);
+      constexpr uint32_t idesc =
+          KIND == KIND_MX ? make_idesc_block_scaled(256, 256, /*a e4m3*/ 0, /*b e2m1*/ 5, /*ue8m0*/ 1)
+                          : make_idesc_block_scaled(256, 256, /*a*/ 1, /*b*/ 1, /*ue4m3*/ 0);
       int stage = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       const uint64_t adesc0 = make_desc_sw128(smem_u32(sA)), bdesc0 = make_desc_sw128(smem_u32(sB));
       const uint32_t sf0_t = tmem_base + kTmemSf;
-      const int last_ksteps = min(4, (p.kdim - (p.k_blocks - 1) * 256) / 64);   // MMAs of a tile's last k-block
+      const int last_ksteps = min(4, (p.kdim - (p.k_blocks - 1) * kPerStage) / kPerMma);   // MMAs of a tile's last k-block
       TL_DECL(tl_n);
       TL_DECL(tl_t);
       for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
@@ -350,15 +372,34 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
           if (kb + 1 < p.k_blocks || last_ksteps == 4) {
             // this thread shares its scheduler with busy epilogue warps: the fewer instructions
             // between two MMAs, the shorter the tensor pipe waits for it
-            mma_nvf4_4x_pair(tmem_base, adesc, bdesc, idesc, sfa_t, sfb_t, kb > 0 ? 1u : 0u);
-            TL_STAGE(tl_k, tl_slot, TL_M_MMA0, tl_n);
-            mma_nvf4_4x_pair(tmem_base, adesc + 2, bdesc + 2, idesc, sfa_t + 4, sfb_t + 8, 1u);
-            mma_nvf4_4x_pair(tmem_base, adesc + 4, bdesc + 4, idesc, sfa_t + 8, sfb_t + 16, 1u);
-            mma_nvf4_4x_pair(tmem_base, adesc + 6, bdesc + 6, idesc, sfa_t + 12, sfb_t + 24, 1u);
+            if (KIND == KIND_MX) {
+              // MMA step j uses byte j of each word of the stage's one scale atom
+              mma_mxf8f6f4_pair(tmem_base, adesc, bdesc, idesc, sfa_t, sfb_t, kb > 0 ? 1u : 0u);
+              TL_STAGE(tl_k, tl_slot, TL_M_MMA0, tl_n);
+              mma_mxf8f6f4_pair(tmem_base, adesc + 2, bdesc + 2, idesc | (1u << 29) | (1u << 4), sfa_t + (1u << 30),
+                                sfb_t + (1u << 30), 1u);
+              mma_mxf8f6f4_pair(tmem_base, adesc + 4, bdesc + 4, idesc | (2u << 29) | (2u << 4), sfa_t + (2u << 30),
+                                sfb_t + (2u << 30), 1u);
+              mma_mxf8f6f4_pair(tmem_base, adesc + 6, bdesc + 6, idesc | (3u << 29) | (3u << 4), sfa_t + (3u << 30),
+                                sfb_t + (3u << 30), 1u);
+            } else {
+              mma_nvf4_4x_pair(tmem_base, adesc, bdesc, idesc, sfa_t, sfb_t, kb > 0 ? 1u : 0u);
+              TL_STAGE(tl_k, tl_slot, TL_M_MMA0, tl_n);
+              mma_nvf4_4x_pair(tmem_base, adesc + 2, bdesc + 2, idesc, sfa_t + 4, sfb_t + 8, 1u);
+              mma_nvf4_4x_pair(tmem_base, adesc + 4, bdesc + 4, idesc, sfa_t + 8, sfb_t + 16, 1u);
+              mma_nvf4_4x_pair(tmem_base, adesc + 6, bdesc + 6, idesc, sfa_t + 12, sfb_t + 24, 1u);
+            }
           } else {
-            for (int j = 0; j < last_ksteps; ++j)
-              mma_nvf4_4x_pair(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j, sfb_t + 8 * j,
-                               (kb > 0 || j > 0) ? 1u : 0u);
+            for (int j = 0; j < last_ksteps; ++j) {
+              if (KIND == KIND_MX) {
+                const uint32_t ju = static_cast<uint32_t>(j);
+                mma_mxf8f6f4_pair(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc | (ju << 29) | (ju << 4),
+                                  sfa_t + (ju << 30), sfb_t + (ju << 30), (kb > 0 || j > 0) ? 1u : 0u);
+              } else {
+                mma_nvf4_4x_pair(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t + 4 * j, sfb_t + 8 * j,
+                                 (kb > 0 || j > 0) ? 1u : 0u);
+              }
+            }
           }
           TL_STAGE(tl_k, tl_slot, TL_M_ISSUED, tl_n);
           tc_commit_pair_both(&tail->empty[stage]);
@@ -401,9 +442,15 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
         const uint32_t sfa_t = tmem_base + kTmemSf + stage * kSfCols + (static_cast<uint32_t>(sub * 32) << 16);
         const uint32_t sfb_t = sfa_t + 16;
         const uint8_t* src = sSf + slot * kSfSlotBytes;
-        sf_atoms_to_tmem<4>(sfa_t, src, lane, 4);
-        sf_atoms_to_tmem<4>(sfb_t, src + kSmemSfa, lane, 8);
-        sf_atoms_to_tmem<4>(sfb_t + 4, src + kSmemSfa + 2048, lane, 8);
+        if (KIND == KIND_MX) {
+          sf_atoms_to_tmem<1>(sfa_t, src, lane, 4);
+          sf_atoms_to_tmem<1>(sfb_t, src + kSmemSfa, lane, 4);
+          sf_atoms_to_tmem<1>(sfb_t + 4, src + kSmemSfa + 2048, lane, 4);
+        } else {
+          sf_atoms_to_tmem<4>(sfa_t, src, lane, 4);
+          sf_atoms_to_tmem<4>(sfb_t, src + kSmemSfa, lane, 8);
+          sf_atoms_to_tmem<4>(sfb_t + 4, src + kSmemSfa + 2048, lane, 8);
+        }
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
@@ -441,7 +488,7 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       acc_phase ^= 1;
       tc_fence_after();
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(sub * 32) << 16);
-      epilogue_tile<KIND_NVFP4, EPI, 256>(p, c.e, c.mt_load, c.nt, row0, c.rows, t_lane, m, half, lane, [&]() {
+      epilogue_tile<KIND, EPI, 256>(p, c.e, c.mt_load, c.nt, row0, c.rows, t_lane, m, half, lane, [&]() {
         if (lane == 0) mbar_arrive_cluster(release_addr);
         if (warp == 8 && lane == 0) TL_TILE(tl_k, tl_slot, TL_E_RELEASED, tl_t);
       });
@@ -460,10 +507,10 @@ grouped_gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
   }
 }
 
-template <int EPI>
+template <int KIND, int EPI>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int max_ctas,
                   cudaStream_t s) {
-  auto kern = grouped_gemm_nvfp4_pair_kernel<EPI>;
+  auto kern = grouped_gemm_pair_kernel<KIND, EPI>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
     return B200MOE_ECUDA;
   cudaLaunchConfig_t cfg = {};
@@ -487,38 +534,42 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmPara
 
 }  // namespace pair
 
-// The CTA-pair kernels serve nvfp4 plans with 128-row tiles and gated FC1 (or FC2).  A pair
-// streams 38 KB per stage and CTA instead of 54 KB; with the accumulator released early they are the
-// faster kernels once experts have several row tiles (C4: FC1 1.02 against 1.10 ms, FC2 0.50 against
-// 0.55 ms).  Default: plans whose capacity averages at least two row tiles per expert; an expert
-// with an odd number of row tiles leaves half a pair idle, so smaller plans stay on the single-CTA
-// kernel.  B200MOE_PAIR=1 / 0 forces them on (where the shape allows) / off.
-bool nvfp4_pair_ok(const b200moe_gemm_args* a, bool fc1) {
+// The CTA-pair kernels serve nvfp4 and w4a8_mx plans with 128-row tiles and gated FC1 (or FC2).  A
+// pair streams 38 KB per stage and CTA instead of 54 KB (nvfp4); they are the faster kernels once
+// experts have several row tiles (C4: FC1 0.92 against 1.10 ms, FC2 0.41 against 0.52 ms).  Default:
+// plans whose capacity averages at least two row tiles per expert; an expert with an odd number of
+// row tiles leaves half a pair idle, so smaller plans stay on the single-CTA kernel.
+// B200MOE_PAIR=1 / 0 forces them on (where the shape allows) / off.
+bool pair_ok(const b200moe_gemm_args* a, bool fc1) {
   static int mode = -2;
   if (mode == -2) {
     const char* e = getenv("B200MOE_PAIR");
     mode = e == nullptr ? -1 : (atoi(e) != 0 ? 1 : 0);
   }
   if (mode == 0 || a->layout->tile_rows != 128) return false;
+  if (a->recipe != B200MOE_RECIPE_NVFP4 && a->recipe != B200MOE_RECIPE_W4A8_MX) return false;
   if (a->hidden_size % 64 != 0 || a->intermediate % 64 != 0 || a->num_experts > kMaxExperts) return false;
   if (fc1 && a->activation == B200MOE_ACT_RELU2) return false;
   if (mode == 1) return true;
   return static_cast<int64_t>(a->layout->rows) >= 256ll * a->num_experts;
 }
 
-int nvfp4_pair_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
+template <int KIND>
+static int pair_gemm1_any(const b200moe_gemm_args* a, cudaStream_t stream) {
   const b200moe_scratch_layout& L = *a->layout;
   const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
-  if (a->a2_gscale == nullptr || a->w13_sf == nullptr) return B200MOE_EINVAL;
+  constexpr bool mx = KIND == KIND_MX;
+  if (a->w13_sf == nullptr || (!mx && a->a2_gscale == nullptr)) return B200MOE_EINVAL;
   char* base = static_cast<char*>(a->scratch);
   GemmParams p = {};
   fill_common(p, a, base);
-  p.atoms_k = ceil_div_i(K, 64);
+  p.atoms_k = ceil_div_i(K, mx ? 128 : 64);
   p.sfb_rowgroups = I / 64;              // pair atoms: 64 up rows + 64 gate rows
   CUtensorMap tmA, tmB;
-  int rc = make_tmap_bytes_2d(&tmA, base + L.act_q, K / 2, L.rows, 128);
+  int rc = make_tmap_bytes_2d(&tmA, base + L.act_q, mx ? K : K / 2, L.rows, 128);
   if (rc != B200MOE_OK) return rc;
-  rc = make_tmap_bytes_2d(&tmB, a->w13, K / 2, static_cast<uint64_t>(E) * 2 * I, 64);
+  rc = mx ? make_tmap_fp4_unpack_2d(&tmB, a->w13, K, static_cast<uint64_t>(E) * 2 * I, 64)
+          : make_tmap_bytes_2d(&tmB, a->w13, K / 2, static_cast<uint64_t>(E) * 2 * I, 64);
   if (rc != B200MOE_OK) return rc;
   p.sfa = reinterpret_cast<const uint8_t*>(base + L.act_sf);
   p.sfb = a->w13_sf;
@@ -528,55 +579,55 @@ int nvfp4_pair_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
   p.out_sf = reinterpret_cast<uint8_t*>(base + L.mid_sf);
   p.tap = a->fc1_tap;
   p.kdim = K;
-  p.k_blocks = ceil_div_i(K, 256);
+  p.k_blocks = ceil_div_i(K, mx ? 128 : 256);
   p.w_rows = 2 * I;
   p.sub0_base = a->gate_first ? I : 0;   // up rows
   p.sub1_base = a->gate_first ? 0 : I;   // gate rows
   p.n_step = 128;
   p.n_tiles = ceil_div_i(I, 128);
   p.out_cols = I;
-  p.out_atoms = ceil_div_i(I, 64);
+  p.out_atoms = ceil_div_i(I, mx ? 128 : 64);
   const int ctas = a->num_sms > 0 ? a->num_sms : num_sms_cached();
   if (p.act_kind == 0 && !(p.limit > 0.f))
-    return pair::launch<EPI_FC1_SILU>(tmA, tmB, p, ctas, stream);
-  if (p.act_kind == 2) return pair::launch<EPI_FC1_SITU>(tmA, tmB, p, ctas, stream);
-  return pair::launch<EPI_FC1_GATED>(tmA, tmB, p, ctas, stream);
+    return pair::launch<KIND, EPI_FC1_SILU>(tmA, tmB, p, ctas, stream);
+  if (p.act_kind == 2) return pair::launch<KIND, EPI_FC1_SITU>(tmA, tmB, p, ctas, stream);
+  return pair::launch<KIND, EPI_FC1_GATED>(tmA, tmB, p, ctas, stream);
 }
 
-int nvfp4_pair_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
+template <int KIND>
+static int pair_gemm2_any(const b200moe_gemm_args* a, cudaStream_t stream) {
   const b200moe_scratch_layout& L = *a->layout;
   const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
+  constexpr bool mx = KIND == KIND_MX;
   if (a->w2_sf == nullptr) return B200MOE_EINVAL;
   char* base = static_cast<char*>(a->scratch);
   GemmParams p = {};
   fill_common(p, a, base);
-  p.atoms_k = ceil_div_i(I, 64);
+  p.atoms_k = ceil_div_i(I, mx ? 128 : 64);
   p.sfb_rowgroups = ceil_div_i(K, 128);
   CUtensorMap tmA, tmB;
-  int rc = make_tmap_bytes_2d(&tmA, base + L.mid_q, I / 2, L.rows, 128);
+  int rc = make_tmap_bytes_2d(&tmA, base + L.mid_q, mx ? I : I / 2, L.rows, 128);
   if (rc != B200MOE_OK) return rc;
-  rc = make_tmap_bytes_2d(&tmB, a->w2, I / 2, static_cast<uint64_t>(E) * K, 64);
+  rc = mx ? make_tmap_fp4_unpack_2d(&tmB, a->w2, I, static_cast<uint64_t>(E) * K, 64)
+          : make_tmap_bytes_2d(&tmB, a->w2, I / 2, static_cast<uint64_t>(E) * K, 64);
   if (rc != B200MOE_OK) return rc;
   p.sfa = reinterpret_cast<const uint8_t*>(base + L.mid_sf);
   p.sfb = a->w2_sf;
   p.alphas = a->w2_alphas;
   p.out_f32 = reinterpret_cast<float*>(base + L.routed);
   p.kdim = I;
-  p.k_blocks = ceil_div_i(I, 256);
+  p.k_blocks = ceil_div_i(I, mx ? 128 : 256);
   p.w_rows = K;
   p.out_cols = K;
   p.n_step = 256;
   p.n_tiles = ceil_div_i(K, 256);
   const int ctas = a->num_sms > 0 ? a->num_sms : num_sms_cached();
-  return pair::launch<EPI_FC2>(tmA, tmB, p, ctas, stream);
+  return pair::launch<KIND, EPI_FC2>(tmA, tmB, p, ctas, stream);
 }
+
+int nvfp4_pair_gemm1(const b200moe_gemm_args* a, cudaStream_t s) { return pair_gemm1_any<KIND_NVFP4>(a, s); }
+int nvfp4_pair_gemm2(const b200moe_gemm_args* a, cudaStream_t s) { return pair_gemm2_any<KIND_NVFP4>(a, s); }
+int mx_pair_gemm1(const b200moe_gemm_args* a, cudaStream_t s) { return pair_gemm1_any<KIND_MX>(a, s); }
+int mx_pair_gemm2(const b200moe_gemm_args* a, cudaStream_t s) { return pair_gemm2_any<KIND_MX>(a, s); }
 
 }  // namespace b200moe
-
-#ifdef B200MOE_TIMELINE
-// Debug builds only: the buffer the CTA-pair kernels' timeline stamps go to.
-extern "C" int b200moe_debug_set_timeline_pair(void* device_buffer) {
-  long long* ptr = static_cast<long long*>(device_buffer);
-  return cudaMemcpyToSymbol(b200moe::g_timeline, &ptr, sizeof(ptr)) == cudaSuccess ? 0 : -3;
-}
-#endif

@@ -13,7 +13,7 @@ import torch
 
 from b12x_b200 import synth
 from tests.gpu_utils import run_layer
-from tests.test_gpu_parity import _check_nvfp4_layer, _tiny
+from tests.test_gpu_parity import _check_mx_layer, _check_nvfp4_layer, _mx, _tiny
 
 pytestmark = pytest.mark.gpu
 
@@ -30,6 +30,19 @@ def test_pair_kernels_match_oracle(tokens, experts, topk, hidden, inter, act):
     run = run_layer(synth.make_inputs(shp, seed=tokens + hidden), want_fc1=True)
     assert int(run.binding.core_layout.tile_rows) == 128
     _check_nvfp4_layer(run)
+
+
+@pytest.mark.parametrize("tokens,experts,topk,hidden,inter,act", [
+    (700, 4, 2, 512, 256, "silu"),          # 2-3 row tiles per expert
+    (600, 2, 2, 320, 192, "swigluoai"),     # K tail (320 = 2.5 k-blocks of 128), half-empty last FC1 tile, FC2 tail
+    (1100, 2, 1, 2880, 192, "swigluoai"),   # the GPT-OSS hidden size: 22 k-blocks and a 64-wide tail
+])
+def test_pair_kernels_w4a8_mx_match_oracle(tokens, experts, topk, hidden, inter, act):
+    shp = _mx(tokens=tokens, experts=experts, topk=topk, hidden=hidden, intermediate=inter, activation=act)
+    assert tokens * topk >= 256 * experts
+    run = run_layer(synth.make_inputs(shp, seed=tokens + hidden), want_fc1=True)
+    assert int(run.binding.core_layout.tile_rows) == 128
+    _check_mx_layer(run)
 
 
 def test_pair_single_expert_odd_tile_count():
