@@ -34,7 +34,7 @@ class ScratchLayout(C.Structure):
     _fields_ = [(n, C.c_int64) for n in (
         "total_nbytes", "status", "expert_counts", "expert_offsets", "tile_base", "mtile_expert",
         "mtile_row0", "mtile_rows", "sorted_route_ids", "inv_perm", "act_q", "act_sf", "mid_q",
-        "mid_sf", "routed")] + [("rows", C.c_int32), ("mtile_cap", C.c_int32),
+        "mid_sf", "routed", "sort_tmp")] + [("rows", C.c_int32), ("mtile_cap", C.c_int32),
                                     ("tile_rows", C.c_int32), ("reserved", C.c_int32)]
 
 

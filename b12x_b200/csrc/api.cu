@@ -103,6 +103,7 @@ extern "C" int b200moe_scratch_nbytes(const b200moe_caps* c, b200moe_scratch_lay
   L->mid_q = take(rows64 * mid_row);
   L->mid_sf = take(mtile_cap * mid_atoms * 512);
   L->routed = take(rows64 * K * 4);
+  L->sort_tmp = take(((rows64 + 2047) / 2048) * E * 4);
   L->total_nbytes = off;
   L->rows = static_cast<int32_t>(rows64);
   L->mtile_cap = static_cast<int32_t>(mtile_cap);

@@ -173,6 +173,187 @@ __global__ void __launch_bounds__(kSortThreads) expert_sort_kernel(
   }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// The same stable sort for many routes (tens of thousands and more: prefill batches, the expert
+// side of expert parallelism), spread over many CTAs in three launches:
+//   count   : CTA c owns routes [c * kChunk, (c + 1) * kChunk); per-expert counts of the chunk go
+//             to chunk_counts[c][E] (it also waits for the peers' flags and clears the status block
+//             where the single-CTA kernel would)
+//   scan    : one CTA turns the chunk counts into per-chunk bases (exclusive over chunks, per
+//             expert) and builds the per-expert offsets and the row-tile tables
+//   scatter : CTA c walks its chunk again, warp by warp and 32 routes at a time, exactly as the
+//             single-CTA kernel does, so that positions keep the order of flat route ids
+// ------------------------------------------------------------------------------------------
+constexpr int kChunk = 2048;          // routes per CTA
+constexpr int kMultiCtaSortRows = 16384;   // from this many routes on the three-launch sort is used
+constexpr int kChunkThreads = 256;    // 8 warps x 256 routes
+
+__device__ __forceinline__ int sort_local_expert(const int32_t* topk_ids, const int32_t* expert_map,
+                                                 int expert_map_len, int E, int r) {
+  int e = __ldcg(topk_ids + r);       // may have been stored by peer GPUs: never the read-only path
+  if (expert_map != nullptr) e = (e >= 0 && e < expert_map_len) ? expert_map[e] : -1;
+  return (e >= 0 && e < E) ? e : -1;
+}
+
+__global__ void __launch_bounds__(kChunkThreads) sort_count_kernel(
+    const int32_t* topk_ids, const int32_t* __restrict__ expert_map, int expert_map_len, int rows, int E,
+    int32_t* __restrict__ status, int32_t* __restrict__ chunk_counts, const int32_t* wait_flags,
+    const int32_t* wait_epoch_dev, int32_t* wait_status, int wait_world, unsigned long long wait_limit_ns) {
+  extern __shared__ int32_t smem[];   // [E]
+  if (wait_flags != nullptr) {
+    const int epoch = *wait_epoch_dev;
+    if (static_cast<int>(threadIdx.x) < wait_world) {
+      unsigned long long t0 = 0;
+      uint32_t spins = 0;
+      int v;
+      while (true) {
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(wait_flags + threadIdx.x) : "memory");
+        if (v >= epoch) break;
+        if ((++spins & 0x3ffu) == 0) {
+          const unsigned long long now = global_timer_ns();
+          if (t0 == 0) t0 = now;
+          if (now - t0 > wait_limit_ns) {
+            if (wait_status != nullptr) {
+              atomicCAS(wait_status, 0, 1);
+              atomicCAS(wait_status + 1, 0, 16 + static_cast<int>(threadIdx.x));
+            }
+            break;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (blockIdx.x == 0 && threadIdx.x < 16) status[threadIdx.x] = 0;   // the sort opens every layer call
+  for (int i = threadIdx.x; i < E; i += blockDim.x) smem[i] = 0;
+  __syncthreads();
+  const int r0 = blockIdx.x * kChunk, r1 = min(rows, r0 + kChunk);
+  for (int r = r0 + threadIdx.x; r < r1; r += blockDim.x) {
+    const int e = sort_local_expert(topk_ids, expert_map, expert_map_len, E, r);
+    if (e >= 0) atomicAdd(&smem[e], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < E; i += blockDim.x) chunk_counts[static_cast<size_t>(blockIdx.x) * E + i] = smem[i];
+}
+
+__global__ void __launch_bounds__(1024) sort_scan_kernel(
+    int chunks, int E, int32_t* __restrict__ chunk_counts, int32_t* __restrict__ expert_counts,
+    int32_t* __restrict__ expert_offsets, int32_t* __restrict__ tile_base, int32_t* __restrict__ mtile_expert,
+    int32_t* __restrict__ mtile_row0, int32_t* __restrict__ mtile_rows, int mtile_cap, int tile_rows) {
+  extern __shared__ int32_t smem[];
+  int32_t* etotal = smem;             // [E]
+  int32_t* eoffs = etotal + E;        // [E+1]
+  int32_t* tbase = eoffs + (E + 1);   // [E+1]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_shift = tile_rows == 64 ? 6 : 7;
+  // per expert: exclusive scan over the chunks (counts become the chunk's first position inside the expert)
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < chunks; ++c) {
+      const size_t i = static_cast<size_t>(c) * E + e;
+      const int n = chunk_counts[i];
+      chunk_counts[i] = run;
+      run += n;
+    }
+    etotal[e] = run;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int per = (E + 31) >> 5;
+    const int e0 = min(E, lane * per), e1 = min(E, e0 + per);
+    int cnt = 0, tl = 0;
+    for (int e = e0; e < e1; ++e) {
+      cnt += etotal[e];
+      tl += (etotal[e] + tile_rows - 1) >> tile_shift;
+    }
+    int pc = cnt, pt = tl;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, pc, d), b = __shfl_up_sync(0xffffffffu, pt, d);
+      if (lane >= d) {
+        pc += a;
+        pt += b;
+      }
+    }
+    int pos = pc - cnt, tiles = pt - tl;
+    for (int e = e0; e < e1; ++e) {
+      eoffs[e] = pos;
+      tbase[e] = tiles;
+      pos += etotal[e];
+      tiles += (etotal[e] + tile_rows - 1) >> tile_shift;
+    }
+    if (lane == 31) {
+      eoffs[E] = pc;
+      tbase[E] = pt;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+    expert_offsets[e] = eoffs[e];
+    tile_base[e] = tbase[e];
+    if (e < E) expert_counts[e] = etotal[e];
+  }
+  // row tiles: one warp per expert at a time (an expert of a large batch has many tiles)
+  for (int e = warp; e < E; e += (blockDim.x >> 5)) {
+    const int nt = (etotal[e] + tile_rows - 1) >> tile_shift;
+    for (int t = lane; t < nt; t += 32) {
+      const int mt = tbase[e] + t;
+      if (mt < mtile_cap) {
+        mtile_expert[mt] = e;
+        mtile_row0[mt] = eoffs[e] + t * tile_rows;
+        mtile_rows[mt] = min(tile_rows, etotal[e] - t * tile_rows);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kChunkThreads) sort_scatter_kernel(
+    const int32_t* topk_ids, const int32_t* __restrict__ expert_map, int expert_map_len, int rows, int E,
+    const int32_t* __restrict__ chunk_base, const int32_t* __restrict__ expert_offsets,
+    int32_t* __restrict__ sorted_route_ids, int32_t* __restrict__ inv_perm) {
+  extern __shared__ int32_t smem[];   // [8 warps][E] counts -> bases
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kWarps = kChunkThreads / 32, kPerWarp = kChunk / kWarps;
+  for (int i = threadIdx.x; i < kWarps * E; i += blockDim.x) smem[i] = 0;
+  __syncthreads();
+  const int c0 = blockIdx.x * kChunk;
+  const int r_begin = min(rows, c0 + warp * kPerWarp), r_end = min(rows, r_begin + kPerWarp);
+  for (int r0 = r_begin; r0 < r_end; r0 += 32) {
+    const int r = r0 + lane;
+    const int e = r < r_end ? sort_local_expert(topk_ids, expert_map, expert_map_len, E, r) : -1;
+    if (e >= 0) atomicAdd(&smem[warp * E + e], 1);
+  }
+  __syncthreads();
+  // per expert: exclusive scan over this CTA's warps, on top of the chunk's base and the expert's offset
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = expert_offsets[e] + chunk_base[static_cast<size_t>(blockIdx.x) * E + e];
+    for (int w = 0; w < kWarps; ++w) {
+      const int n = smem[w * E + e];
+      smem[w * E + e] = run;
+      run += n;
+    }
+  }
+  __syncthreads();
+  for (int r0 = r_begin; r0 < r_end; r0 += 32) {
+    const int r = r0 + lane;
+    const int e = r < r_end ? sort_local_expert(topk_ids, expert_map, expert_map_len, E, r) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    if (r < r_end) {
+      if (e >= 0) {
+        const int pos = smem[warp * E + e] + __popc(peers & ((1u << lane) - 1u));   // read before the leader bumps it
+        sorted_route_ids[pos] = r;
+        inv_perm[r] = pos;
+      } else {
+        inv_perm[r] = -1;
+      }
+    }
+    __syncwarp();
+    if (e >= 0 && r < r_end && (peers & ((1u << lane) - 1u)) == 0) smem[warp * E + e] += __popc(peers);
+    __syncwarp();
+  }
+}
+
 }  // namespace b200moe
 
 using namespace b200moe;
@@ -216,6 +397,27 @@ extern "C" int b200moe_expert_sort(const b200moe_sort_args* a, void* stream) {
     return B200MOE_EINVAL;
   if (rows > L.rows) return B200MOE_ECAPACITY;
   char* base = static_cast<char*>(a->scratch);
+  const unsigned long long limit_ns =
+      a->wait_timeout_ms > 0 ? static_cast<unsigned long long>(a->wait_timeout_ms) * 1000000ull : kWaitLimitNs;
+  if (rows >= kMultiCtaSortRows) {
+    // many routes: count per chunk, scan, scatter (three launches over many CTAs)
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int chunks = (rows + kChunk - 1) / kChunk;
+    int32_t* chunk_counts = reinterpret_cast<int32_t*>(base + L.sort_tmp);
+    sort_count_kernel<<<chunks, kChunkThreads, static_cast<size_t>(E) * 4, s>>>(
+        a->topk_ids, a->expert_map, a->expert_map_len, rows, E, reinterpret_cast<int32_t*>(base + L.status),
+        chunk_counts, a->wait_flags, a->wait_epoch_dev, a->wait_status, a->wait_world, limit_ns);
+    sort_scan_kernel<<<1, 1024, (3 * static_cast<size_t>(E) + 2) * 4, s>>>(
+        chunks, E, chunk_counts, reinterpret_cast<int32_t*>(base + L.expert_counts),
+        reinterpret_cast<int32_t*>(base + L.expert_offsets), reinterpret_cast<int32_t*>(base + L.tile_base),
+        reinterpret_cast<int32_t*>(base + L.mtile_expert), reinterpret_cast<int32_t*>(base + L.mtile_row0),
+        reinterpret_cast<int32_t*>(base + L.mtile_rows), L.mtile_cap, L.tile_rows == 64 ? 64 : 128);
+    sort_scatter_kernel<<<chunks, kChunkThreads, static_cast<size_t>(kChunkThreads / 32) * E * 4, s>>>(
+        a->topk_ids, a->expert_map, a->expert_map_len, rows, E, chunk_counts,
+        reinterpret_cast<const int32_t*>(base + L.expert_offsets), reinterpret_cast<int32_t*>(base + L.sorted_route_ids),
+        reinterpret_cast<int32_t*>(base + L.inv_perm));
+    return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+  }
   // fewer warps for small problems keeps the shared-memory clear short
   int nwarps = (rows + 31) / 32;
   nwarps = nwarps < 1 ? 1 : (nwarps > 32 ? 32 : nwarps);
@@ -235,8 +437,7 @@ extern "C" int b200moe_expert_sort(const b200moe_sort_args* a, void* stream) {
       reinterpret_cast<int32_t*>(base + L.mtile_rows),
       reinterpret_cast<int32_t*>(base + L.sorted_route_ids),
       reinterpret_cast<int32_t*>(base + L.inv_perm), L.mtile_cap,
-      L.tile_rows == 64 ? 64 : 128, nwarps, a->wait_flags, a->wait_epoch_dev, a->wait_status, a->wait_world,
-      a->wait_timeout_ms > 0 ? static_cast<unsigned long long>(a->wait_timeout_ms) * 1000000ull : kWaitLimitNs);
+      L.tile_rows == 64 ? 64 : 128, nwarps, a->wait_flags, a->wait_epoch_dev, a->wait_status, a->wait_world, limit_ns);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 

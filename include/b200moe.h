@@ -82,6 +82,7 @@ typedef struct {
   int64_t mid_q;             /* FC2 input codes  [rows][I/2] / [rows][I] / bf16 [rows][I]     */
   int64_t mid_sf;            /* FC2 input scales atoms                                         */
   int64_t routed;            /* float32 [rows][K] per-route FC2 output (alpha applied)         */
+  int64_t sort_tmp;          /* int32 [ceil(rows/2048)][E] per-chunk counts of the multi-CTA sort */
   int32_t rows;              /* T*k                                             */
   int32_t mtile_cap;         /* ceil(rows/tile_rows) + min(E, rows)             */
   int32_t tile_rows;         /* 64 or 128: rows per expert tile of this plan    */

@@ -36,7 +36,7 @@ def test_struct_sizes_match_header_layout():
     for st in (ext.RouteArgs, ext.SortArgs, ext.QuantArgs, ext.GatherArgs, ext.GemmArgs, ext.CombineArgs,
                ext.ScratchLayout, ext.CapsC):
         assert C.sizeof(st) % 8 == 0, st
-    assert C.sizeof(ext.ScratchLayout) == 15 * 8 + 16
+    assert C.sizeof(ext.ScratchLayout) == 16 * 8 + 16
     assert C.sizeof(ext.GemmArgs) == 13 * 8 + 14 * 4
 
 

@@ -306,3 +306,43 @@ def test_w4a16_matches_reference_golden():
     ref = t(g["out_bf16"], torch.bfloat16).float()
     # the reference rounds every route's contribution to bf16 and sums in bf16 (w4a16_reference.py:619-621)
     assert (run.out.float() - ref).abs().max().item() <= 4 * 2.0 ** -8 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("tokens,topk,experts,tile_rows", [(4096, 4, 128, 128), (16384, 1, 8, 128), (9000, 2, 37, 128),
+                                                           (2048, 8, 256, 64), (65536, 8, 16, 128)])
+def test_large_sorts_use_the_multi_cta_path_and_stay_canonical(tokens, topk, experts, tile_rows):
+    """From 16 384 routes on the sort runs as three launches over many CTAs: counts, offsets, row
+    tiles and the whole permutation must equal the oracle's stable sort bit for bit (ids outside the
+    expert range and a route-expert map with holes included)."""
+    import ctypes as C
+
+    from b12x_b200._lib import ext
+    gen = torch.Generator().manual_seed(tokens + experts)
+    ids = torch.randint(-2, experts + 3, (tokens, topk), generator=gen, dtype=torch.int32)
+    emap = torch.arange(experts + 3, dtype=torch.int32)
+    emap[::5] = -1
+    emap[experts:] = -1
+    layout = ext.scratch_layout(tokens, topk, experts, 256, 128, "nvfp4", "silu", tile_rows)
+    scratch = torch.full((int(layout.total_nbytes),), 0xFF, dtype=torch.uint8, device="cuda")
+    for use_map in (False, True):
+        args = ext.SortArgs(ids.cuda().data_ptr(), emap.cuda().data_ptr() if use_map else None, scratch.data_ptr(),
+                            C.pointer(layout), tokens, topk, experts, emap.numel() if use_map else 0, None, None, None, 0, 0)
+        ids_dev = ids.cuda()
+        emap_dev = emap.cuda()
+        args = ext.SortArgs(ids_dev.data_ptr(), emap_dev.data_ptr() if use_map else None, scratch.data_ptr(),
+                            C.pointer(layout), tokens, topk, experts, emap.numel() if use_map else 0, None, None, None, 0, 0)
+        ext.check(ext.load().b200moe_expert_sort(C.byref(args), torch.cuda.current_stream().cuda_stream), "sort")
+        torch.cuda.synchronize()
+        srt = O.expert_sort(ids, experts, emap if use_map else None, tile_rows=int(layout.tile_rows))
+        view = lambda name, n: scratch[int(getattr(layout, name)): int(getattr(layout, name)) + 4 * n].view(torch.int32).cpu()
+        kept = srt.sorted_route_ids.numel()
+        assert torch.equal(view("expert_counts", experts), srt.expert_counts)
+        assert torch.equal(view("expert_offsets", experts + 1), srt.expert_offsets)
+        assert torch.equal(view("tile_base", experts + 1), srt.tile_base)
+        assert torch.equal(view("sorted_route_ids", kept), srt.sorted_route_ids)
+        assert torch.equal(view("inv_perm", tokens * topk), srt.inv_perm)
+        nt = int(srt.tile_base[-1])
+        assert torch.equal(view("mtile_expert", nt), srt.mtile_expert)
+        assert torch.equal(view("mtile_row0", nt), srt.mtile_row0)
+        assert torch.equal(view("mtile_rows", nt), srt.mtile_rows)
+        assert view("status", 16).tolist() == [0] * 16
