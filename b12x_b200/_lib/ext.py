@@ -116,7 +116,19 @@ class EpDispatchArgs(C.Structure):
                 ("epoch_dev", C.c_void_p), ("scratch", C.c_void_p), ("layout", C.POINTER(ScratchLayout)), ("x_row_stride", C.c_int64),
                 ("num_tokens", C.c_int32), ("num_topk", C.c_int32), ("world", C.c_int32), ("rank", C.c_int32),
                 ("hidden_size", C.c_int32), ("local_modulus", C.c_int32), ("cap_rows", C.c_int32),
-                ("epoch", C.c_int32)]
+                ("epoch", C.c_int32), ("payload", C.c_int32), ("sf_row_stride", C.c_int32),
+                ("gscale_len", C.c_int32), ("reserved", C.c_int32), ("peer_sf", PeerArray),
+                ("a1_gscale", C.c_void_p), ("status", C.c_void_p)]
+
+
+EP_PAYLOADS = {"bf16": 0, "nvfp4": 1, "mxfp8": 2}
+
+
+class PackedArgs(C.Structure):
+    _fields_ = [("q_rows", C.c_void_p), ("sf_rows", C.c_void_p), ("scratch", C.c_void_p),
+                ("layout", C.POINTER(ScratchLayout)), ("num_rows", C.c_int32), ("num_experts", C.c_int32),
+                ("hidden_size", C.c_int32), ("payload", C.c_int32), ("sf_row_stride", C.c_int32),
+                ("reserved", C.c_int32)]
 
 
 class EpCombineArgs(C.Structure):
@@ -154,6 +166,7 @@ EXPORTS = {
     "b200moe_grouped_gemm2": ([C.POINTER(GemmArgs), C.c_void_p], C.c_int),
     "b200moe_combine": ([C.POINTER(CombineArgs), C.c_void_p], C.c_int),
     "b200moe_ep_dispatch": ([C.POINTER(EpDispatchArgs), C.c_void_p], C.c_int),
+    "b200moe_permute_packed": ([C.POINTER(PackedArgs), C.c_void_p], C.c_int),
     "b200moe_ep_signal": ([C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p], C.c_int),
     "b200moe_ep_wait": ([C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p], C.c_int),
     "b200moe_ep_combine": ([C.POINTER(EpCombineArgs), C.c_void_p], C.c_int),
@@ -182,7 +195,7 @@ def load():
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = restype
-    if lib.b200moe_abi_version() != 3:
+    if lib.b200moe_abi_version() != 4:
         raise RuntimeError("libb200moe.so ABI version mismatch; rebuild it")
     _lib = lib
     return lib

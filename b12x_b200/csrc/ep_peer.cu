@@ -16,7 +16,7 @@
 // No kernel here uses multimem or cluster features; peers are only touched with ld/st.global.
 // The reference library has no counterpart (its ep_moe replicates the input and lets the caller
 // sum partial outputs, b12x/moe/ep_moe/_impl.py:1-14).
-#include "common.cuh"
+#include "quant_shared.cuh"
 
 namespace b200moe {
 
@@ -33,11 +33,18 @@ struct PeerPtrs {
   void* p[B200MOE_MAX_RANKS];
 };
 
+// PAYLOAD 0: bf16 rows as they are.  1: NVFP4 codes + E4M3 scale bytes, quantised here with the
+// destination expert's input scale (the bytes the expert rank's own quantiser would have made, so
+// 9K/16 bytes cross the link per route instead of 2K).  2: MXFP8 values + E8M0 scale bytes (K + K/32).
+// Scale bytes travel row-major, `sf_row_stride` (a multiple of 4) per slot; the expert rank files them
+// into scale atoms when it puts the rows in expert order (permute_packed_kernel).
+template <int PAYLOAD>
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(
     const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, const int32_t* __restrict__ topk_ids,
     const int32_t* __restrict__ group_offsets, const int32_t* __restrict__ sorted_route_ids,
-    PeerPtrs rows, PeerPtrs ids, PeerPtrs flags, int32_t* done_counter, int world, int rank,
-    int num_topk, int K, int local_modulus, int cap, int epoch_arg, int32_t* epoch_dev) {
+    PeerPtrs rows, PeerPtrs sfs, PeerPtrs ids, PeerPtrs flags, const float* __restrict__ a1_gscale,
+    int gscale_len, int sf_row_stride, int32_t* done_counter, int32_t* __restrict__ status, int world,
+    int rank, int num_topk, int K, int local_modulus, int cap, int epoch_arg, int32_t* epoch_dev) {
   // Epoch kept on the device (a captured CUDA graph replays with fixed arguments): this step is
   // *epoch_dev + 1.  Every block reads it on entry; the last block out stores it back after all
   // others have left, and the later kernels of the step read the stored value.
@@ -46,19 +53,77 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
   if (threadIdx.x <= world) offs[threadIdx.x] = group_offsets[threadIdx.x];
   __syncthreads();
   const int total = offs[world];
-  // one row per block at a time: all 256 threads copy it, so a row is a handful of independent
-  // 16-byte loads and (peer) stores per thread instead of a 28-step walk by one warp
+  const int lane = threadIdx.x & 31;
+  // one row per block at a time: all 256 threads work on it, so a row is a handful of independent
+  // 16-byte loads and (peer) stores per thread instead of a long walk by one warp
   for (int pos = blockIdx.x; pos < total; pos += gridDim.x) {
     int d = 0;
     while (d + 1 < world && pos >= offs[d + 1]) ++d;
-    const int slot = rank * cap + (pos - offs[d]);
+    const int j = pos - offs[d];
+    if (j >= cap) {
+      // more rows for rank d than its receive region holds: the row is not sent, the step is invalid
+      if (threadIdx.x == 0 && status != nullptr) {
+        atomicCAS(status, 0, 1);
+        atomicCAS(status + 1, 0, 48 + d);     // 48 + destination rank: receive capacity exceeded
+      }
+      continue;
+    }
+    const int slot = rank * cap + j;
     const int r = sorted_route_ids[pos];
     const int t = r / num_topk;
+    const int expert = topk_ids[r];
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(t) * x_row_stride);
-    uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(rows.p[d]) +
-                                          static_cast<size_t>(slot) * K);
-    for (int j = threadIdx.x; j < (K >> 3); j += blockDim.x) dst[j] = __ldg(src + j);
-    if (threadIdx.x == 0) static_cast<int32_t*>(ids.p[d])[slot] = topk_ids[r] % local_modulus;
+    if constexpr (PAYLOAD == 0) {
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(rows.p[d]) +
+                                            static_cast<size_t>(slot) * K);
+      for (int q = threadIdx.x; q < (K >> 3); q += blockDim.x) dst[q] = __ldg(src + q);
+    } else if constexpr (PAYLOAD == 1) {
+      const int nblk = K >> 4;
+      const float gs = a1_gscale[gscale_len == 1 ? 0 : expert];
+      uint2* dst = reinterpret_cast<uint2*>(static_cast<uint8_t*>(rows.p[d]) + static_cast<size_t>(slot) * (K >> 1));
+      uint8_t* dsf = static_cast<uint8_t*>(sfs.p[d]) + static_cast<size_t>(slot) * sf_row_stride;
+      for (int b0 = 0; b0 < nblk; b0 += blockDim.x) {
+        const int b = b0 + threadIdx.x;
+        uint8_t sfb = 0;
+        if (b < nblk) {
+          float v[16];
+          bf16x8_to_f32(__ldg(src + 2 * b), v);
+          bf16x8_to_f32(__ldg(src + 2 * b + 1), v + 8);
+          uint32_t lo, hi;
+          quant_block16(v, gs, lo, hi, sfb);
+          dst[b] = make_uint2(lo, hi);
+        }
+        // four neighbouring lanes hold the four scale bytes of one 32-bit word
+        uint32_t word = sfb;
+        word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 1) << 8;
+        word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 2) << 16;
+        word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 3) << 24;
+        if ((lane & 3) == 0 && b < nblk) *reinterpret_cast<uint32_t*>(dsf + b) = word;
+      }
+    } else {
+      const int nblk = K >> 5;
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(rows.p[d]) + static_cast<size_t>(slot) * K);
+      uint8_t* dsf = static_cast<uint8_t*>(sfs.p[d]) + static_cast<size_t>(slot) * sf_row_stride;
+      for (int b0 = 0; b0 < nblk; b0 += blockDim.x) {
+        const int b = b0 + threadIdx.x;
+        uint8_t sfb = 0;
+        if (b < nblk) {
+          float v[32];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) bf16x8_to_f32(__ldg(src + 4 * b + q), v + 8 * q);
+          uint32_t o[8];
+          quant_block32_mx(v, o, sfb);
+          dst[2 * b] = make_uint4(o[0], o[1], o[2], o[3]);
+          dst[2 * b + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+        uint32_t word = sfb;      // lanes past the row's end contribute 0: the padding bytes are defined
+        word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 1) << 8;
+        word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 2) << 16;
+        word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 3) << 24;
+        if ((lane & 3) == 0 && b < nblk) *reinterpret_cast<uint32_t*>(dsf + b) = word;
+      }
+    }
+    if (threadIdx.x == 0) static_cast<int32_t*>(ids.p[d])[slot] = expert % local_modulus;
   }
   // unused slots of this rank's region on every peer: no route
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < world * cap; i += gridDim.x * blockDim.x) {
@@ -76,6 +141,36 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
       __threadfence_system();
       for (int d = 0; d < world; ++d) st_release_sys(static_cast<int32_t*>(flags.p[d]) + rank, epoch);
     }
+  }
+}
+
+// Expert side of the quantised dispatch: rows arrive in slot order, already quantised; copy each
+// into its place in expert order and file its scale bytes into the tile's 128x4 scale atoms --
+// what the permute + quantise kernel leaves behind, without the arithmetic.
+template <int PAYLOAD>
+__global__ void __launch_bounds__(256) permute_packed_kernel(
+    const uint8_t* __restrict__ q_rows, const uint8_t* __restrict__ sf_rows, int sf_row_stride, int K,
+    const int32_t* __restrict__ tile_base, int E, const int32_t* __restrict__ mtile_row0,
+    const int32_t* __restrict__ mtile_rows, const int32_t* __restrict__ sorted_route_ids,
+    uint8_t* __restrict__ act_q, uint8_t* __restrict__ act_sf) {
+  const int mt = blockIdx.x;
+  if (mt >= tile_base[E]) return;
+  const int row0 = mtile_row0[mt];
+  const int nrows = mtile_rows[mt];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_bytes = PAYLOAD == 1 ? K >> 1 : K;
+  const int nblk = PAYLOAD == 1 ? K >> 4 : K >> 5;
+  const int nwords = (nblk + 3) >> 2;          // one word = the four scale bytes of one atom column group
+  uint8_t* sf_tile = act_sf + static_cast<size_t>(mt) * nwords * 512;
+  for (int i = blockIdx.y * 8 + warp; i < nrows; i += gridDim.y * 8) {
+    const int pos = row0 + i;
+    const int r = sorted_route_ids[pos];
+    const uint4* src = reinterpret_cast<const uint4*>(q_rows + static_cast<size_t>(r) * row_bytes);
+    uint4* dst = reinterpret_cast<uint4*>(act_q + static_cast<size_t>(pos) * row_bytes);
+    for (int q = lane; q < (row_bytes >> 4); q += 32) dst[q] = __ldcg(src + q);
+    const uint32_t* ssrc = reinterpret_cast<const uint32_t*>(sf_rows + static_cast<size_t>(r) * sf_row_stride);
+    for (int w = lane; w < nwords; w += 32)
+      *reinterpret_cast<uint32_t*>(sf_tile + sf_atom_offset(i, 4 * w)) = __ldcg(ssrc + w);
   }
 }
 
@@ -156,9 +251,11 @@ __global__ void __launch_bounds__(256) ep_combine_pull_kernel(
     if (pos >= 0) {
       int d = 0;
       while (d + 1 < world && pos >= group_offsets[d + 1]) ++d;
-      const int slot = rank * cap + (pos - group_offsets[d]);
+      const int j = pos - group_offsets[d];
+      const int slot = rank * cap + j;
       const char* arena = static_cast<const char*>(arenas.p[d]);
-      const int p = reinterpret_cast<const int32_t*>(arena + peer_inv_perm_off)[slot];
+      // a route beyond the receive capacity was never sent (the dispatch raised the status word)
+      const int p = j < cap ? reinterpret_cast<const int32_t*>(arena + peer_inv_perm_off)[slot] : -1;
       if (p >= 0) rp = reinterpret_cast<const float*>(arena + peer_routed_off) + static_cast<size_t>(p) * K;
     }
     rowp[s] = rp;
@@ -214,6 +311,19 @@ static bool fill_peers(PeerPtrs& dst, void* const* src, int world) {
   return true;
 }
 
+template <int PAYLOAD>
+static void launch_dispatch(const b200moe_ep_dispatch_args* a, const PeerPtrs& rows_p, const PeerPtrs& sf_p,
+                            const PeerPtrs& ids_p, const PeerPtrs& flags_p, int grid, cudaStream_t stream) {
+  const b200moe_scratch_layout& L = *a->layout;
+  char* base = static_cast<char*>(a->scratch);
+  ep_dispatch_kernel<PAYLOAD><<<grid, 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride, a->topk_ids,
+      reinterpret_cast<const int32_t*>(base + L.expert_offsets),
+      reinterpret_cast<const int32_t*>(base + L.sorted_route_ids), rows_p, sf_p, ids_p, flags_p,
+      a->a1_gscale, a->gscale_len, a->sf_row_stride, a->done_counter, a->status, a->world, a->rank,
+      a->num_topk, a->hidden_size, a->local_modulus, a->cap_rows, a->epoch, a->epoch_dev);
+}
+
 extern "C" int b200moe_ep_dispatch(const b200moe_ep_dispatch_args* a, void* stream) {
   if (a == nullptr || a->x == nullptr || a->topk_ids == nullptr || a->scratch == nullptr ||
       a->layout == nullptr || a->done_counter == nullptr)
@@ -223,21 +333,68 @@ extern "C" int b200moe_ep_dispatch(const b200moe_ep_dispatch_args* a, void* stre
     return B200MOE_EINVAL;
   if ((reinterpret_cast<uintptr_t>(a->x) & 15) != 0 || (a->x_row_stride % 8) != 0) return B200MOE_EALIGN;
   const int rows = a->num_tokens * a->num_topk;
-  if (rows > a->layout->rows || rows > a->cap_rows) return B200MOE_ECAPACITY;
-  PeerPtrs rows_p, ids_p, flags_p;
+  if (rows > a->layout->rows) return B200MOE_ECAPACITY;
+  // fewer slots per source rank than its routes: allowed only with a status word for the overflow
+  if (rows > a->cap_rows && a->status == nullptr) return B200MOE_ECAPACITY;
+  PeerPtrs rows_p, ids_p, flags_p, sf_p = {};
   if (!fill_peers(rows_p, a->peer_rows, a->world) || !fill_peers(ids_p, a->peer_ids, a->world) ||
       !fill_peers(flags_p, a->peer_flags, a->world))
     return B200MOE_EINVAL;
-  const b200moe_scratch_layout& L = *a->layout;
-  char* base = static_cast<char*>(a->scratch);
+  if (a->payload != B200MOE_EP_PAYLOAD_BF16) {
+    const int blk = a->payload == B200MOE_EP_PAYLOAD_NVFP4 ? 64 : 32;   // values per scale word / per block
+    if (a->payload != B200MOE_EP_PAYLOAD_NVFP4 && a->payload != B200MOE_EP_PAYLOAD_MXFP8) return B200MOE_EINVAL;
+    if (a->hidden_size % blk != 0 || !fill_peers(sf_p, a->peer_sf, a->world)) return B200MOE_EINVAL;
+    const int nsf = a->hidden_size / (a->payload == B200MOE_EP_PAYLOAD_NVFP4 ? 16 : 32);
+    if (a->sf_row_stride % 4 != 0 || a->sf_row_stride < ((nsf + 3) & ~3)) return B200MOE_EALIGN;
+    if (a->payload == B200MOE_EP_PAYLOAD_NVFP4 && (a->a1_gscale == nullptr || a->gscale_len < 1))
+      return B200MOE_EINVAL;
+  }
   int grid = rows;
   grid = grid < 1 ? 1 : (grid > 148 * 8 ? 148 * 8 : grid);
-  ep_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride, a->topk_ids,
-      reinterpret_cast<const int32_t*>(base + L.expert_offsets),
-      reinterpret_cast<const int32_t*>(base + L.sorted_route_ids), rows_p, ids_p, flags_p,
-      a->done_counter, a->world, a->rank, a->num_topk, a->hidden_size, a->local_modulus, a->cap_rows,
-      a->epoch, a->epoch_dev);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->payload == B200MOE_EP_PAYLOAD_NVFP4) launch_dispatch<1>(a, rows_p, sf_p, ids_p, flags_p, grid, st);
+  else if (a->payload == B200MOE_EP_PAYLOAD_MXFP8) launch_dispatch<2>(a, rows_p, sf_p, ids_p, flags_p, grid, st);
+  else launch_dispatch<0>(a, rows_p, sf_p, ids_p, flags_p, grid, st);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+extern "C" int b200moe_permute_packed(const b200moe_packed_args* a, void* stream) {
+  if (a == nullptr || a->q_rows == nullptr || a->sf_rows == nullptr || a->scratch == nullptr ||
+      a->layout == nullptr)
+    return B200MOE_EINVAL;
+  if (a->payload != B200MOE_EP_PAYLOAD_NVFP4 && a->payload != B200MOE_EP_PAYLOAD_MXFP8) return B200MOE_EINVAL;
+  const int blk = a->payload == B200MOE_EP_PAYLOAD_NVFP4 ? 64 : 32;
+  if (a->num_rows < 0 || a->num_experts <= 0 || a->hidden_size <= 0 || a->hidden_size % blk != 0)
+    return B200MOE_EINVAL;
+  const int nsf = a->hidden_size / (a->payload == B200MOE_EP_PAYLOAD_NVFP4 ? 16 : 32);
+  if (a->sf_row_stride % 4 != 0 || a->sf_row_stride < ((nsf + 3) & ~3) ||
+      (reinterpret_cast<uintptr_t>(a->q_rows) & 15) != 0 || (reinterpret_cast<uintptr_t>(a->sf_rows) & 3) != 0)
+    return B200MOE_EALIGN;
+  const b200moe_scratch_layout& L = *a->layout;
+  if (a->num_rows > L.rows) return B200MOE_ECAPACITY;
+  if (a->num_rows == 0) return B200MOE_OK;
+  char* base = static_cast<char*>(a->scratch);
+  const int tr = L.tile_rows == 64 ? 64 : 128;
+  const int mtiles = (a->num_rows + tr - 1) / tr + (a->num_experts < a->num_rows ? a->num_experts : a->num_rows);
+  const int gx = mtiles < L.mtile_cap ? mtiles : L.mtile_cap;
+  int gy = (4 * 148 + gx - 1) / gx;
+  gy = gy < 2 ? 2 : (gy > 16 ? 16 : gy);
+  const dim3 grid(gx, gy);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int32_t* tile_base = reinterpret_cast<const int32_t*>(base + L.tile_base);
+  const int32_t* row0 = reinterpret_cast<const int32_t*>(base + L.mtile_row0);
+  const int32_t* nrows = reinterpret_cast<const int32_t*>(base + L.mtile_rows);
+  const int32_t* sorted = reinterpret_cast<const int32_t*>(base + L.sorted_route_ids);
+  uint8_t* q = reinterpret_cast<uint8_t*>(base + L.act_q);
+  uint8_t* sf = reinterpret_cast<uint8_t*>(base + L.act_sf);
+  if (a->payload == B200MOE_EP_PAYLOAD_NVFP4)
+    permute_packed_kernel<1><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(a->q_rows),
+        static_cast<const uint8_t*>(a->sf_rows), a->sf_row_stride, a->hidden_size, tile_base, a->num_experts,
+        row0, nrows, sorted, q, sf);
+  else
+    permute_packed_kernel<2><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(a->q_rows),
+        static_cast<const uint8_t*>(a->sf_rows), a->sf_row_stride, a->hidden_size, tile_base, a->num_experts,
+        row0, nrows, sorted, q, sf);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 

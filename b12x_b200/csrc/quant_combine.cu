@@ -1,35 +1,8 @@
 // Stage 3 (permute + activation quantisation) and stage 6 (top-k weighted combine).
 // Both are HBM-bound streaming kernels: 16-byte vector accesses, one warp per row.
-#include "common.cuh"
+#include "quant_shared.cuh"
 
 namespace b200moe {
-
-// ------------------------------------------------------------------------------------------
-// NVFP4 activation quantiser, exact ("direct division") variant of the reference oracle
-// (b12x/moe/_shared/kernels/reference.py:269-300):
-//   sf    = e4m3_rn(min(amax * gs / 6, 448))
-//   code  = e2m1_rte(x / max(sf / gs, 1e-30))
-// One lane owns one 16-element block at a time.  Codes go to act_q[pos][K/2]; scales go to the
-// 512-byte atoms of the row's 128-row tile, which is the layout tcgen05 block-scaled MMA reads.
-// ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void quant_block16(const float (&v)[16], float gs, uint32_t& lo,
-                                              uint32_t& hi, uint8_t& sf_byte) {
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  const float raw = fminf(__fdiv_rn(__fmul_rn(amax, gs), 6.0f), 448.0f);
-  sf_byte = f32_to_e4m3_rn_sat(raw);
-  const float sf = e4m3_to_f32(sf_byte);
-  const float denom = fmaxf(__fdiv_rn(sf, gs), 1e-30f);
-  float q0[8], q1[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    q0[i] = __fdiv_rn(v[i], denom);
-    q1[i] = __fdiv_rn(v[8 + i], denom);
-  }
-  lo = pack_e2m1x8(q0);
-  hi = pack_e2m1x8(q1);
-}
 
 __global__ void __launch_bounds__(256) permute_quant_nvfp4_kernel(
     const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, const float* __restrict__ gscale,
@@ -88,22 +61,6 @@ __global__ void __launch_bounds__(256) permute_quant_nvfp4_kernel(
   }
 }
 
-// ------------------------------------------------------------------------------------------
-// MXFP8 activation quantiser (b12x/_lib/intrinsics.py:223-265): per 32 elements
-//   byte  = exponent of pow2_ceil(amax * (1/448))   (mantissa != 0 -> exponent + 1; 0 -> byte 0)
-//   code  = e4m3_rn_sat(x * 2^(127 - byte))
-// ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint8_t ue8m0_ceil_byte(float s) {
-  uint32_t bits = __float_as_uint(s);
-  if (bits & 0x007fffffu) bits = (bits + 0x00800000u) & 0x7f800000u;
-  return static_cast<uint8_t>((bits >> 23) & 0xffu);
-}
-__device__ __forceinline__ float ue8m0_inv_scale(uint8_t byte) {
-  if (byte == 0) return 0.f;
-  const int ex = 254 - static_cast<int>(byte);
-  return __uint_as_float(static_cast<uint32_t>(ex < 0 ? 0 : ex) << 23);
-}
-
 __global__ void __launch_bounds__(256) permute_quant_mxfp8_kernel(
     const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, int num_topk, int K,
     const int32_t* __restrict__ tile_base, int E, const int32_t* __restrict__ mtile_row0,
@@ -142,22 +99,8 @@ __global__ void __launch_bounds__(256) permute_quant_mxfp8_kernel(
             v[q * 8 + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
           }
         }
-        float amax = 0.f;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
-        sfb = ue8m0_ceil_byte(__fmul_rn(amax, static_cast<float>(1.0 / 448.0)));
-        const float inv = ue8m0_inv_scale(sfb);
         uint32_t o[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint32_t acc = 0;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const float s = fminf(fmaxf(__fmul_rn(v[4 * j + k], inv), -448.f), 448.f);
-            acc |= static_cast<uint32_t>(f32_to_e4m3_rn_sat(s)) << (8 * k);
-          }
-          o[j] = acc;
-        }
+        quant_block32_mx(v, o, sfb);
         dst[2 * b] = make_uint4(o[0], o[1], o[2], o[3]);
         dst[2 * b + 1] = make_uint4(o[4], o[5], o[6], o[7]);
       }
@@ -327,22 +270,9 @@ __global__ void __launch_bounds__(256) quantize_rows_mxfp8_kernel(
           v[q * 8 + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
         }
       }
-      float amax = 0.f;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
-      const uint8_t sfb = ue8m0_ceil_byte(__fmul_rn(amax, static_cast<float>(1.0 / 448.0)));
-      const float inv = ue8m0_inv_scale(sfb);
       uint32_t o[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        uint32_t acc = 0;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float sc = fminf(fmaxf(__fmul_rn(v[4 * j + k], inv), -448.f), 448.f);
-          acc |= static_cast<uint32_t>(f32_to_e4m3_rn_sat(sc)) << (8 * k);
-        }
-        o[j] = acc;
-      }
+      uint8_t sfb;
+      quant_block32_mx(v, o, sfb);
       dst[2 * b] = make_uint4(o[0], o[1], o[2], o[3]);
       dst[2 * b + 1] = make_uint4(o[4], o[5], o[6], o[7]);
       if (scale_rows != nullptr) scale_rows[static_cast<size_t>(row) * nblk + b] = sfb;

@@ -46,10 +46,32 @@ def _symm_empty(shape, dtype, device):
     return t, [p + off for p in base], hdl
 
 
+_PAYLOAD_OF_RECIPE = {"nvfp4": "nvfp4", "w4a8_mx": "mxfp8", "w4a16": "bf16"}
+
+
+class _ReceivedRows:
+    """The bf16 rows behind this rank's receive slots, looked up in the ranks' gathered inputs
+    (checking aid: with a quantised dispatch the expert rank never holds them)."""
+
+    def __init__(self, xs, sorted_ids, offsets, me: int, cap: int, topk: int):
+        self.xs, self.sorted_ids, self.offsets, self.me, self.cap, self.topk = xs, sorted_ids, offsets, me, cap, topk
+
+    def index_select(self, dim: int, slots: torch.Tensor) -> torch.Tensor:
+        assert dim == 0
+        slots = slots.cpu().long()
+        out = torch.empty((slots.numel(), self.xs[0].shape[1]), dtype=self.xs[0].dtype)
+        for i, s in enumerate(slots.tolist()):
+            src, j = divmod(s, self.cap)
+            route = int(self.sorted_ids[src][int(self.offsets[src][self.me]) + j])
+            out[i] = self.xs[src][route // self.topk]
+        return out
+
+
 class PeerExpertParallelMoE(_LayerBase):
     kernels_per_step = 12
 
-    def __init__(self, shp, inputs, experts, dev, rank: int, world: int):
+    def __init__(self, shp, inputs, experts, dev, rank: int, world: int, *,
+                 recv_capacity_factor: float | None = None, payload: str | None = None):
         super().__init__(shp, inputs, experts, dev, rank, world)
         if world < 2 or world > ext.MAX_RANKS:
             raise ValueError(f"needs 2..{ext.MAX_RANKS} ranks")
@@ -57,14 +79,27 @@ class PeerExpertParallelMoE(_LayerBase):
             raise ValueError("experts must divide evenly over the ranks")
         self.e_local = shp.experts // world
         t, k = shp.tokens, shp.topk
+        # Slots one source rank owns in every receive buffer.  Worst case (every route of a rank
+        # to one destination) by default; with a capacity factor f, f x the balanced share
+        # t*k/world -- a route beyond it is not sent and the step ends with an error status.
         self.cap = t * k
+        if recv_capacity_factor is not None:
+            if recv_capacity_factor <= 0:
+                raise ValueError("recv_capacity_factor must be positive")
+            self.cap = max(1, min(t * k, -(-int(t * k * recv_capacity_factor) // world)))
+        self.bounded_capacity = self.cap < t * k
         slots = world * self.cap
         self.home = StageArena(t, k, world, shp.hidden, dev)
         self.rank_of_expert = (torch.arange(shp.experts, dtype=torch.int32, device=dev) // self.e_local).contiguous()
-        # the two cross-rank waits of a step either ride inside the expert sort and the combine
-        # kernel (9 launches per step) or are launches of their own (12)
-        self.fold_waits = os.environ.get("B200MOE_FOLD_WAITS", "0") == "1"
+        # the two cross-rank waits of a step ride inside the expert sort and the combine kernel
+        # (9 launches per step) unless B200MOE_FOLD_WAITS=0 makes them launches of their own (12)
+        self.fold_waits = os.environ.get("B200MOE_FOLD_WAITS", "1") == "1"
         self.kernels_per_step = 9 if self.fold_waits else 12
+        # what crosses the link per route: the row quantised on this rank (the recipe's activation
+        # format) or, for recipes whose GEMM reads bf16 rows, the row as it is
+        self.payload = payload or os.environ.get("B200MOE_EP_PAYLOAD") or _PAYLOAD_OF_RECIPE[shp.recipe]
+        if self.payload not in ext.EP_PAYLOADS or (self.payload != "bf16" and self.payload != _PAYLOAD_OF_RECIPE[shp.recipe]):
+            raise ValueError(f"payload {self.payload!r} does not fit recipe {shp.recipe!r}")
         self.done_counter = torch.zeros(1, dtype=torch.int32, device=dev)
         # the step counter lives on the device, so that a captured step can be replayed
         self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -77,7 +112,17 @@ class PeerExpertParallelMoE(_LayerBase):
         self.plan = fused_moe.plan(caps)
         nbytes = self.plan.scratch_specs()[0].shape[0]
         self.scratch, self.scratch_ptrs, self._h0 = _symm_empty((nbytes,), torch.uint8, dev)
-        self.recv_rows, self.rows_ptrs, self._h1 = _symm_empty((slots, shp.hidden), torch.bfloat16, dev)
+        if self.payload == "bf16":
+            self.recv_rows, self.rows_ptrs, self._h1 = _symm_empty((slots, shp.hidden), torch.bfloat16, dev)
+            self.recv_sf, self.sf_ptrs, self.packed = None, [0] * world, None
+        else:
+            row_bytes = shp.hidden // 2 if self.payload == "nvfp4" else shp.hidden
+            nsf = shp.hidden // (16 if self.payload == "nvfp4" else 32)
+            self.recv_q, self.rows_ptrs, self._h1 = _symm_empty((slots, row_bytes), torch.uint8, dev)
+            self.recv_sf, self.sf_ptrs, self._h4 = _symm_empty((slots, (nsf + 3) // 4 * 4), torch.uint8, dev)
+            self.packed = (self.recv_q, self.recv_sf)
+            # the binding wants a [slots, K] bf16 tensor; it is never read on this path
+            self.recv_rows = torch.zeros((1, shp.hidden), dtype=torch.bfloat16, device=dev).expand(slots, shp.hidden)
         self.recv_ids, self.ids_ptrs, self._h2 = _symm_empty((slots, 1), torch.int32, dev)
         self.flags, flag_ptrs, self._h3 = _symm_empty((2 * ext.MAX_RANKS,), torch.int32, dev)
         self.flags.zero_()
@@ -90,6 +135,14 @@ class PeerExpertParallelMoE(_LayerBase):
         self._inv_perm_off = self.plan.layout.route_workspace_nbytes + int(core.inv_perm)
         self._routed_off = self.plan.layout.route_workspace_nbytes + int(core.routed)
         self.home_status = self.home._view("status", 16, torch.int32)
+        # the senders quantise with the destination expert's input scale: every rank holds all of them
+        gs = experts.a1_gscale.reshape(-1).float()
+        gs = gs.expand(self.e_local).contiguous() if gs.numel() == 1 else gs.contiguous()
+        if gs.numel() != self.e_local:
+            raise ValueError("a1_gscale must hold one value or one per local expert")
+        parts = [torch.empty_like(gs) for _ in range(world)]
+        dist.all_gather(parts, gs)
+        self.a1_gscale_all = torch.cat(parts).contiguous()
         torch.cuda.synchronize(dev)
         dist.barrier()
 
@@ -97,23 +150,44 @@ class PeerExpertParallelMoE(_LayerBase):
         super().check_status()
         st = self.home_status.cpu()
         if int(st[0]) != 0:
-            raise RuntimeError(f"expert-parallel wait gave up (code {int(st[1])}: 16 + missing peer rank)")
+            code = int(st[1])
+            if code >= 48:
+                raise RuntimeError(f"rank {code - 48} was sent more rows than its receive capacity "
+                                   f"({self.cap} per source rank) holds; the step's output is invalid")
+            raise RuntimeError(f"expert-parallel wait gave up (code {code}: 16 + missing peer rank)")
 
     @classmethod
-    def from_synthetic(cls, shp: synth.MoEShape, dev, rank: int, world: int):
+    def from_synthetic(cls, shp: synth.MoEShape, dev, rank: int, world: int, **kw):
         e_local = shp.experts // world
         inp = synth.make_inputs(shp, seed=1000 + rank, device=dev, experts=e_local)
-        return cls(shp, inp, prepare_experts(inp, dev), dev, rank, world)
+        return cls(shp, inp, prepare_experts(inp, dev), dev, rank, world, **kw)
 
     @classmethod
-    def from_global(cls, full: synth.MoEInputs, dev, rank: int, world: int, tokens_per_rank: int):
+    def from_global(cls, full: synth.MoEInputs, dev, rank: int, world: int, tokens_per_rank: int, **kw):
         shp = replace(full.shape, tokens=tokens_per_rank)
         e_local = shp.experts // world
         local = synth.slice_experts(full, rank * e_local, (rank + 1) * e_local)
         lo = rank * tokens_per_rank
         local = replace(local, shape=shp, x=full.x[lo:lo + tokens_per_rank].contiguous(),
                         router_logits=full.router_logits[lo:lo + tokens_per_rank].contiguous())
-        return cls(shp, local, prepare_experts(local, dev), dev, rank, world)
+        return cls(shp, local, prepare_experts(local, dev), dev, rank, world, **kw)
+
+    def received_rows(self, x: torch.Tensor) -> _ReceivedRows:
+        """COLLECTIVE checking aid: the bf16 rows behind this rank's receive slots after a step on
+        ``x``, rebuilt from every rank's input and destination sort (a quantised dispatch leaves
+        only codes on the expert rank).  Slot s = source rank * cap + j."""
+        torch.cuda.synchronize(self.dev)
+        n = self.shape.tokens * self.shape.topk
+
+        def gather(t):
+            parts = [torch.empty_like(t) for _ in range(self.world)]
+            dist.all_gather(parts, t.contiguous())
+            return [p.cpu() for p in parts]
+
+        xs = gather(x)
+        sorted_ids = gather(self.home.sorted_route_ids[:n])
+        offsets = gather(self.home.group_offsets)
+        return _ReceivedRows(xs, sorted_ids, offsets, self.rank, self.cap, self.shape.topk)
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, stage_timer=None) -> torch.Tensor:
         lib = ext.load()
@@ -121,6 +195,7 @@ class PeerExpertParallelMoE(_LayerBase):
         stream = torch.cuda.current_stream(self.dev).cuda_stream
         mark = stage_timer if stage_timer is not None else (lambda _name: None)
         mark("begin")
+        self.last_x = x
         self.route(logits)
         mark("route")
         home.sort(self.topk_ids, self.rank_of_expert)
@@ -129,14 +204,16 @@ class PeerExpertParallelMoE(_LayerBase):
             x.data_ptr(), self.topk_ids.data_ptr(), ext.peer_array(self.rows_ptrs),
             ext.peer_array(self.ids_ptrs), ext.peer_array(self.flag1_ptrs), self.done_counter.data_ptr(),
             self.epoch_dev.data_ptr(), home.scratch.data_ptr(), C.pointer(home.layout), x.stride(0), x.shape[0], shp.topk, world, rank,
-            shp.hidden, self.e_local, self.cap, 0)
+            shp.hidden, self.e_local, self.cap, 0, ext.EP_PAYLOADS[self.payload],
+            0 if self.recv_sf is None else int(self.recv_sf.shape[1]), int(self.a1_gscale_all.numel()), 0,
+            ext.peer_array(self.sf_ptrs), self.a1_gscale_all.data_ptr(), self.home_status.data_ptr())
         ext.check(lib.b200moe_ep_dispatch(C.byref(d), stream), "ep_dispatch")
         mark("dispatch")
         ep = self.epoch_dev.data_ptr()
         fold = self.fold_waits
         # folded: the expert-side sort waits for all peers' dispatch flags before it reads the ids
         b = fused_moe.bind(self.plan, scratch=self.scratch, a=self.recv_rows, experts=self.experts,
-                           topk_weights=self.ones, topk_ids=self.recv_ids, skip_combine=True,
+                           topk_weights=self.ones, topk_ids=self.recv_ids, skip_combine=True, a_packed=self.packed,
                            sort_wait=(self.flags.data_ptr(), world, ep, self.home_status.data_ptr()) if fold else None)
         self.last_binding = b
         if not fold:

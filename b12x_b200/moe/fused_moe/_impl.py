@@ -511,6 +511,7 @@ class TPMoEScratchPlan:
         f32_only: bool = False,
         skip_combine: bool = False,
         sort_wait: tuple | None = None,
+        a_packed: tuple | None = None,
     ) -> "TPMoEFP4Binding":
         """Validate the call and map the caller's scratch into kernel-argument views.
 
@@ -553,6 +554,20 @@ class TPMoEScratchPlan:
         if output is not None:
             if tuple(output.shape) != (tokens, caps.k) or output.dtype != caps.dtype or output.stride(1) != 1:
                 raise ValueError("output must be [tokens, K] in the plan dtype, row-contiguous")
+        if a_packed is not None:
+            # rows that arrive already quantised (the expert side of a quantised dispatch): codes
+            # [tokens, K/2 | K] and row-major scale bytes [tokens, stride]; ``a`` is not read
+            if caps.quant_mode not in ("nvfp4", "w4a8_mx") or caps.num_topk != 1:
+                raise ValueError("a_packed needs an nvfp4 or w4a8_mx plan with top_k = 1")
+            q, sf = a_packed
+            row_bytes = caps.k // 2 if caps.quant_mode == "nvfp4" else caps.k
+            nsf = caps.k // (16 if caps.quant_mode == "nvfp4" else 32)
+            if q.dtype != torch.uint8 or sf.dtype != torch.uint8 or not q.is_contiguous() or not sf.is_contiguous():
+                raise TypeError("a_packed tensors must be contiguous uint8")
+            if tuple(q.shape) != (tokens, row_bytes) or sf.ndim != 2 or sf.shape[0] != tokens:
+                raise ValueError(f"a_packed codes must be [tokens, {row_bytes}] with one scale row per token")
+            if sf.shape[1] % 4 or sf.shape[1] < nsf:
+                raise ValueError(f"a_packed scale rows must hold >= {nsf} bytes, padded to a multiple of 4")
         storage = scratch_tensor(scratch, self._scratch_specs, owner="TP MoE")
         core = storage.narrow(0, self.layout.route_workspace_nbytes, self.layout.core_workspace_nbytes)
         if core.data_ptr() % 32 != 0:
@@ -569,7 +584,7 @@ class TPMoEScratchPlan:
             swiglu_beta=caps.swiglu_beta, route_expert_map=route_expert_map,
             kernel_workspace=core, core_layout=self._core_layout, fc1_tap=fc1_tap,
             output_f32=output_f32, output_scale=float(output_scale), f32_only=bool(f32_only),
-            skip_combine=bool(skip_combine), sort_wait=sort_wait)
+            skip_combine=bool(skip_combine), sort_wait=sort_wait, a_packed=a_packed)
 
 
 def plan_tp_moe_scratch(caps: TPMoEScratchCaps) -> TPMoEScratchPlan:
@@ -632,6 +647,8 @@ class TPMoEFP4Binding:
     # (flags ptr, world, epoch ptr, status ptr): the sort first waits for the peers' flags (the
     # expert side of the peer-memory expert parallelism, whose ids are stored by other ranks)
     sort_wait: tuple | None = None
+    # (codes, scale rows): the rows arrive quantised and ``run`` files them instead of quantising ``a``
+    a_packed: tuple | None = None
 
     # ---- scratch views (valid after run) ----
     def _v(self, name: str, count: int, dtype: torch.dtype) -> torch.Tensor:
@@ -747,7 +764,13 @@ def b12x_moe_fp4(*, binding: TPMoEFP4Binding, stage_timer=None) -> torch.Tensor:
     ext.check(lib.b200moe_expert_sort(C.byref(sort_args), stream), "expert_sort")
     mark("sort")
 
-    if b.quant_mode in ("nvfp4", "w4a8_mx"):
+    if b.a_packed is not None:
+        q, sf = b.a_packed
+        pargs = ext.PackedArgs(q.data_ptr(), sf.data_ptr(), scratch, lp, tokens, b.weight_E, b.k,
+                               ext.EP_PAYLOADS["nvfp4" if b.quant_mode == "nvfp4" else "mxfp8"],
+                               int(sf.shape[1]), 0)
+        ext.check(lib.b200moe_permute_packed(C.byref(pargs), stream), "permute_packed")
+    elif b.quant_mode in ("nvfp4", "w4a8_mx"):
         qargs = ext.QuantArgs(b.a.data_ptr(), ex.a1_gscale.data_ptr(), scratch, lp, b.a.stride(0),
                               tokens, b.num_topk, b.weight_E, b.k, int(ex.a1_gscale.numel()), 0)
         fn = lib.b200moe_permute_quant_nvfp4 if b.quant_mode == "nvfp4" else lib.b200moe_permute_quant_mxfp8

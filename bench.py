@@ -264,8 +264,11 @@ def parity_sample(layer) -> dict:
     bit for bit, and the activation codes and fp32 FC2 rows of up to ``PARITY_ROWS_PER_EXPERT``
     routes of ``PARITY_EXPERTS`` experts (``tests/gpu_utils.sampled_parity``)."""
     from tests.gpu_utils import sampled_parity
+    # a quantised expert-parallel dispatch leaves no bf16 rows on the expert rank: look them up
+    # in the ranks' inputs (a collective; every rank gets here)
+    rows = layer.received_rows(layer.last_x) if getattr(layer, "packed", None) is not None else None
     return sampled_parity(layer.last_binding, layer.inputs, experts=PARITY_EXPERTS,
-                          rows_per_expert=PARITY_ROWS_PER_EXPERT, tolerance=PARITY_TOL)
+                          rows_per_expert=PARITY_ROWS_PER_EXPERT, tolerance=PARITY_TOL, a=rows)
 
 
 # ---------------------------------------------------------------------------------------------

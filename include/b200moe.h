@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 3
+#define B200MOE_ABI_VERSION 4
 
 /* ---- status codes ------------------------------------------------------ */
 #define B200MOE_OK            0
@@ -306,10 +306,42 @@ typedef struct {
   int64_t x_row_stride;
   int32_t num_tokens, num_topk, world, rank;
   int32_t hidden_size, local_modulus, cap_rows, epoch;
+  /* What crosses the link per route.  BF16: the row as it is (2K bytes; peer_rows is bf16).
+   * NVFP4 / MXFP8: the row quantised HERE, with the destination expert's input scale
+   * a1_gscale[global expert id] for NVFP4 -- the same bytes the expert rank's permute + quantise
+   * stage would produce -- so that 9K/16 resp. K + K/32 bytes cross instead: peer_rows is then
+   * u8 [world*cap_rows][K/2 | K], peer_sf u8 [world*cap_rows][sf_row_stride] (row-major scale
+   * bytes, zero padded to a multiple of 4), and the expert rank runs b200moe_permute_packed
+   * where it would have run b200moe_permute_quant_*. */
+  int32_t payload;           /* B200MOE_EP_PAYLOAD_*                            */
+  int32_t sf_row_stride;     /* bytes, multiple of 4, >= K/16 resp. K/32        */
+  int32_t gscale_len;        /* 1 or the GLOBAL expert count (nvfp4 payload)    */
+  int32_t reserved;
+  void* peer_sf[B200MOE_MAX_RANKS];
+  const float* a1_gscale;    /* reciprocal input scales of ALL experts, global numbering */
+  /* cap_rows may be smaller than T*k (a capacity factor).  A route beyond the destination's
+   * region is not sent; the kernel then writes status[0] = 1, status[1] = 48 + destination rank.
+   * Required when cap_rows < T*k. */
+  int32_t* status;
 } b200moe_ep_dispatch_args;
+enum { B200MOE_EP_PAYLOAD_BF16 = 0, B200MOE_EP_PAYLOAD_NVFP4 = 1, B200MOE_EP_PAYLOAD_MXFP8 = 2 };
 /* Pack rows by destination rank, store them and their local expert ids into the peers' receive
  * buffers, mark this rank's unused slots with -1, then raise peer_flags[d][rank] = epoch. */
 int b200moe_ep_dispatch(const b200moe_ep_dispatch_args* a, void* stream);
+
+/* Expert side of a quantised dispatch: act_q[pos] = q_rows[sorted_route_ids[pos]] and the scale
+ * bytes of that slot filed into the 128x4 scale atoms of the row's tile -- exactly what
+ * b200moe_permute_quant_nvfp4 / _mxfp8 leave in the arena, for rows that arrive quantised.
+ * Runs after b200moe_expert_sort over the received ids (top-1: route id = slot). */
+typedef struct {
+  const void* q_rows;        /* u8 [num_rows][K/2 | K], 16-byte aligned         */
+  const void* sf_rows;       /* u8 [num_rows][sf_row_stride]                    */
+  void* scratch;
+  const b200moe_scratch_layout* layout; /* HOST pointer                        */
+  int32_t num_rows, num_experts, hidden_size, payload;
+  int32_t sf_row_stride, reserved;
+} b200moe_packed_args;
+int b200moe_permute_packed(const b200moe_packed_args* a, void* stream);
 /* Raise peer_flags[d][rank] = epoch on every rank once the stream's earlier work is done. */
 int b200moe_ep_signal(void* const* peer_flags /* HOST array */, int32_t world, int32_t rank,
                       int32_t epoch, const int32_t* epoch_dev /* or NULL */, void* stream);

@@ -120,7 +120,7 @@ def oracle_call(shp, x, w1, s1, g1, w2, s2, g2, a1, a2, ids, weights, expert_map
 
 
 def sampled_parity(binding, inp: synth.MoEInputs, *, experts: int = 4, rows_per_expert: int = 48,
-                   tolerance: float = 1e-2) -> dict:
+                   tolerance: float = 1e-2, a=None) -> dict:
     """Check what the last ``run`` of ``binding`` left in its scratch arena against the CPU oracle.
 
     Full-size shapes are too large for the oracle as a whole, so: (1) the WHOLE permutation
@@ -129,7 +129,9 @@ def sampled_parity(binding, inp: synth.MoEInputs, *, experts: int = 4, rows_per_
     over the experts that received rows) the oracle evaluates the route from the input row on: the
     activation codes and scale bytes must be bit-identical, the fp32 FC2 rows (alpha applied,
     router weight not) within ``tolerance`` x their RMS.  ``inp`` holds the source-format weights of
-    the experts this binding's layer owns (in its local numbering)."""
+    the experts this binding's layer owns (in its local numbering).  ``a`` (anything with
+    ``index_select(0, rows)``) stands in for the binding's input rows where the layer received them
+    already quantised."""
     b = binding
     shp = inp.shape
     torch.cuda.synchronize(b.device)
@@ -158,7 +160,7 @@ def sampled_parity(binding, inp: synth.MoEInputs, *, experts: int = 4, rows_per_
     pos_t = torch.tensor(pos, dtype=torch.int64)
     pos_d = pos_t.to(b.device)
     tok = (srt.sorted_route_ids.to(torch.int64)[pos_t] // k).to(b.device)
-    x_sub = b.a.index_select(0, tok).cpu()
+    x_sub = (b.a if a is None else a).index_select(0, tok).cpu()
     got = b.route_output.index_select(0, pos_d).cpu()
     sel = torch.tensor(chosen, dtype=torch.int64)
     pick = lambda t: t.index_select(0, sel.to(t.device)).cpu()

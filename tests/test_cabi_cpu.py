@@ -27,7 +27,7 @@ def test_every_declared_symbol_is_exported(lib):
     assert declared == set(ext.EXPORTS), declared ^ set(ext.EXPORTS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.b200moe_abi_version() == 3
+    assert lib.b200moe_abi_version() == 4
     assert lib.b200moe_strerror(-2).decode().startswith("problem exceeds")
 
 
@@ -87,6 +87,7 @@ def test_host_side_argument_errors_need_no_gpu(lib):
     assert lib.b200moe_ep_wait(16, 2, 1, None, None, 20000, None) == ext.EINVAL               # timeout too long
     assert lib.b200moe_ep_dispatch(None, None) == ext.EINVAL
     assert lib.b200moe_ep_combine(None, None) == ext.EINVAL
+    assert lib.b200moe_permute_packed(None, None) == ext.EINVAL
 
 
 def _wplan(**kw):
