@@ -157,31 +157,106 @@ class _LayerBase:
         self.lg_stage = torch.empty((t, shp.experts), dtype=torch.float32, device=dev)
         self.last_binding = None
         self.graph = None     # a captured step on (x_stage, lg_stage), where the layer offers one
+        self._copy_streams = None
+        self._chunk_graphs = None
 
     @property
     def local_intermediate(self) -> int:
         """Intermediate columns this rank holds (the whole of it unless the layer is tensor-parallel)."""
         return int(self.inputs.w2_fp4.shape[2]) * 2
 
-    def route(self, logits: torch.Tensor) -> None:
+    def route(self, logits: torch.Tensor, lo: int = 0) -> None:
         shp = self.shape
+        hi = lo + int(logits.shape[0])
+        tl, ti, tw = self.topk_logits[lo:hi], self.topk_ids[lo:hi], self.topk_weights[lo:hi]
         if shp.router == "sigmoid":
-            fused_moe.route_topk(logits, self.topk_logits, self.topk_ids, self.topk_weights, renormalize=True,
-                                 score_func="sigmoid", route_scale=shp.route_scale)
+            fused_moe.route_topk(logits, tl, ti, tw, renormalize=True, score_func="sigmoid",
+                                 route_scale=shp.route_scale)
         else:
-            fused_moe.route_topk(logits, self.topk_logits, self.topk_ids, self.topk_weights, renormalize=True)
+            fused_moe.route_topk(logits, tl, ti, tw, renormalize=True)
+
+    def host_chunks(self) -> int:
+        """Token chunks ``forward_host`` pipelines (1 = no pipelining).  A layer that can run a token
+        slice on its own overrides ``forward_slice`` and this."""
+        return 1
+
+    def forward_slice(self, lo: int, hi: int) -> None:
+        raise NotImplementedError
+
+    @staticmethod
+    def _chunk_bounds(tokens: int, n: int) -> list:
+        """Token ranges of the pipeline's chunks.  The first and the last chunk are half as large as
+        the others: nothing overlaps the first copy in and the last copy out, so they are kept short."""
+        parts = [1] + [2] * (n - 1) + [1] if n >= 2 else [1]
+        total, acc, bounds = sum(parts), 0, []
+        for p in parts:
+            lo, acc = acc, acc + p
+            bounds.append((lo * tokens // total // 8 * 8, acc * tokens // total // 8 * 8 if acc < total else tokens))
+        return [(lo, hi) for lo, hi in bounds if hi > lo]
+
+    def _capture_chunks(self, bounds) -> dict:
+        """One CUDA graph per token chunk of the staging buffers (the chunk's route + layer)."""
+        torch.cuda.synchronize(self.dev)
+        graphs = {}
+        for lo, hi in bounds:
+            self.forward_slice(lo, hi)          # warm-up outside the capture
+            torch.cuda.synchronize(self.dev)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.forward_slice(lo, hi)
+            graphs[(lo, hi)] = g
+        torch.cuda.synchronize(self.dev)
+        return graphs
 
     def forward_host(self, x_host: torch.Tensor, logits_host: torch.Tensor, out_host: torch.Tensor) -> None:
-        """Host buffers in, host buffer out: H2D copies, the layer, D2H copy, all on the current stream."""
-        self.x_stage.copy_(x_host, non_blocking=True)
-        self.lg_stage.copy_(logits_host, non_blocking=True)
-        if self.graph is not None:
-            self.graph.replay()
-            out = self.out
-        else:
-            out = self.forward(self.x_stage, self.lg_stage)
-        out_host.copy_(out, non_blocking=True)
-        torch.cuda.current_stream(self.dev).synchronize()
+        """Host buffers in, host buffer out.
+
+        One chunk: H2D copies, the layer, D2H copy, all on the current stream.  Several chunks (large
+        batches on one GPU): the copies of chunk c+1 / c-1 run on two side streams while chunk c
+        computes, so the step costs about max(copy in, compute, copy out) plus one chunk's copy at
+        either end instead of their sum.  Every token's result is the same either way: a token's
+        rows meet no other token's data anywhere in the layer."""
+        n = self.host_chunks()
+        main = torch.cuda.current_stream(self.dev)
+        if n <= 1:
+            self.x_stage.copy_(x_host, non_blocking=True)
+            self.lg_stage.copy_(logits_host, non_blocking=True)
+            if self.graph is not None:
+                self.graph.replay()
+                out = self.out
+            else:
+                out = self.forward(self.x_stage, self.lg_stage)
+            out_host.copy_(out, non_blocking=True)
+            main.synchronize()
+            return
+        if self._copy_streams is None:
+            self._copy_streams = (torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev))
+            self._chunk_events = [(torch.cuda.Event(), torch.cuda.Event()) for _ in range(16)]
+        s_in, s_out = self._copy_streams
+        bounds = self._chunk_bounds(int(x_host.shape[0]), n)
+        s_in.wait_stream(main)
+        s_out.wait_stream(main)
+        with torch.cuda.stream(s_in):
+            for c, (lo, hi) in enumerate(bounds):
+                self.x_stage[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
+                self.lg_stage[lo:hi].copy_(logits_host[lo:hi], non_blocking=True)
+                self._chunk_events[c][0].record(s_in)
+        if self._chunk_graphs is None:
+            self._chunk_graphs = self._capture_chunks(bounds) if self.can_capture else {}
+        for c, (lo, hi) in enumerate(bounds):
+            arrived, computed = self._chunk_events[c]
+            main.wait_event(arrived)
+            g = self._chunk_graphs.get((lo, hi))
+            if g is not None:
+                g.replay()          # one launch per chunk: the host never falls behind the GPU
+            else:
+                self.forward_slice(lo, hi)
+            computed.record(main)
+            s_out.wait_event(computed)
+            with torch.cuda.stream(s_out):
+                out_host[lo:hi].copy_(self.out[lo:hi], non_blocking=True)
+        main.wait_stream(s_out)
+        main.synchronize()
 
     @property
     def can_capture(self) -> bool:
@@ -269,6 +344,25 @@ class ExpertParallelMoE(_LayerBase):
     @property
     def can_capture(self) -> bool:
         return self.world == 1      # the NCCL exchange reads the split sizes on the host
+
+    def host_chunks(self) -> int:
+        """On one GPU a large batch is pipelined in up to four token chunks, each with at least 256
+        rows per expert so that the grouped GEMMs keep their large-batch tiles."""
+        if self.world != 1:
+            return 1
+        shp = self.shape
+        chunk_min = max(256 * shp.experts // shp.topk, 1024)
+        cap = int(os.environ.get("B200MOE_HOST_CHUNKS", "4"))
+        return max(1, min(cap, shp.tokens // chunk_min))
+
+    def forward_slice(self, lo: int, hi: int) -> None:
+        """The layer on tokens [lo, hi) of the staging buffers, result into ``out[lo:hi]``."""
+        self.route(self.lg_stage[lo:hi], lo)
+        b = fused_moe.bind(self.plan, scratch=self.scratch, a=self.x_stage[lo:hi], experts=self.experts,
+                           topk_weights=self.topk_weights[lo:hi], topk_ids=self.topk_ids[lo:hi],
+                           output=self.out[lo:hi])
+        self.last_binding = b
+        fused_moe.run(binding=b)
 
     @classmethod
     def from_synthetic(cls, shp: synth.MoEShape, dev, rank: int, world: int):

@@ -86,3 +86,28 @@ def test_c5_gptoss_w4a8_mx_full_shape():
 def test_c5_large_batch_several_tiles_per_expert():
     """The same layer with 4096 tokens: 128 rows per expert on average, partial and full tiles."""
     _run_and_check(synth.shape("c5", tokens=4096), seed=26, rows_per_expert=32)
+
+
+def test_pipelined_host_step_equals_the_whole_batch_step():
+    """``forward_host`` on a large batch copies and computes in token chunks on three streams; the
+    result must be the same bytes as one whole-batch step on device-resident inputs."""
+    from b12x_b200.moe.distributed import prepare_experts
+    dev = torch.device("cuda")
+    shp = synth.shape("c4", tokens=4096)
+    inp = synth.make_inputs(shp, seed=31, device=dev)
+    layer = ExpertParallelMoE(shp, inp, prepare_experts(inp, dev), dev)
+    assert layer.host_chunks() == 4
+    whole = layer.forward(inp.x, inp.router_logits).clone()
+    ids = layer.topk_ids.clone()
+    torch.cuda.synchronize()
+    x_host = inp.x.cpu().pin_memory()
+    lg_host = inp.router_logits.cpu().pin_memory()
+    out_host = torch.zeros((shp.tokens, shp.hidden), dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):
+        layer.forward_host(x_host, lg_host, out_host)
+    layer.check_status()
+    assert torch.equal(layer.topk_ids, ids)
+    assert torch.equal(out_host, whole.cpu())
+    # a decode-sized batch is not chunked
+    small = synth.shape("c2", tokens=64)
+    assert ExpertParallelMoE.host_chunks(type("L", (), {"world": 1, "shape": small})()) == 1
