@@ -48,7 +48,7 @@ def needs_build() -> bool:
     if not LIB_PATH.exists():
         return True
     built = LIB_PATH.stat().st_mtime
-    deps = [CSRC / s for s in SOURCES] + [CSRC / "common.cuh", CSRC / "gemm_shared.cuh", CSRC / "route_shared.cuh", CSRC / "quant_shared.cuh", CSRC.parents[1] / "include" / "b200moe.h"]
+    deps = [CSRC / s for s in SOURCES] + [CSRC / "common.cuh", CSRC / "gemm_shared.cuh", CSRC / "route_shared.cuh", CSRC / "quant_shared.cuh", CSRC / "cluster_pair.cuh", CSRC.parents[1] / "include" / "b200moe.h"]
     return any(d.stat().st_mtime > built for d in deps)
 
 

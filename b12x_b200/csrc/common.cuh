@@ -338,6 +338,13 @@ __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64
       : "memory");
 }
 
+// One 32-byte store (sm_100 has 256-bit global stores); `p` must be 32-byte aligned.
+__device__ __forceinline__ void st_global_f32x8(float* p, const float (&v)[8]) {
+  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]),
+               "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+               : "memory");
+}
+
 // ---- numeric helpers shared by the quantisers ---------------------------------
 // 8 floats -> 8 E2M1 codes (round-to-nearest-even, saturating), v[0] in the low nibble.
 // A negative zero result is stored as +0 (code 0), as the reference packer does.

@@ -114,13 +114,6 @@ __device__ __forceinline__ float act_gated(float gate, float up, const GemmParam
   return (gate * s) * up;
 }
 
-// One 32-byte store (sm_100 has 256-bit global stores); `p` must be 32-byte aligned.
-__device__ __forceinline__ void st_global_f32x8(float* p, const float (&v)[8]) {
-  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]),
-               "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
-               : "memory");
-}
-
 __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }

@@ -22,20 +22,22 @@
 // Power-of-two (E8M0) scales exceed the FP16 range; for them the code values are re-encoded first and
 // multiplied by the scale in BF16.
 //
-// Where the time goes is not settled.  Shared memory is busy (per k-block the MMAs read 48 KiB of
-// operands, the TMA writes 26 KiB, the converters read 10 KiB and write 32 KiB: about 930 of the
-// ~1400 clocks a k-block takes, against 544 clocks of tensor-pipe time), but the FC2 kernel at the
-// end of this file, which keeps the weights out of shared memory altogether, is no faster.  With
-// the conversion removed (timing only) the kernel takes 76 % of its time, without the token-row
-// loads as well 70 %; ring depths (3 / 4 / 6 load stages, 2 / 3 / 4 converted tiles) and sixteen
-// converter warps that take alternate k-blocks (W4A16_CONV_GROUPS=2) change nothing.
+// Where the time goes (timing-only builds of the CTA-pair kernel below, FC1 of the Qwen3 shape,
+// 1.17 ms): without the MMAs 1.06 ms, without the conversion 1.02 ms, with the converters copying
+// instead of converting 1.07 ms, without the epilogue 1.11 ms.  So neither the tensor pipe nor the
+// conversion arithmetic bounds it: the load -> convert -> hand-over chain and the load -> MMA ->
+// commit chain each take about 950 clocks per k-block on their own (four MMAs are 512 clocks at the
+// nominal rate, 690 at the rate a library BF16 GEMM reaches here).  For the single-CTA kernel,
+// earlier: ring depths (3 / 4 / 6 load stages, 2 / 3 / 4 converted tiles), sixteen converter warps
+// on alternate k-blocks, and an FC2 variant with the expanded weights as the tensor-memory operand
+// of the MMA (no shared-memory round trip for them) all changed nothing and were removed.
 //
 // Numerics follow the reference's W4A16 oracle (tests/_reference/w4a16_reference.py:266-359):
 // weights de-quantised then held in BF16, x in BF16, FP32 accumulation, activation in FP32, BF16
 // intermediate.
 #include <stdlib.h>
 
-#include "common.cuh"
+#include "cluster_pair.cuh"
 
 namespace b200moe {
 
@@ -165,7 +167,9 @@ __device__ __forceinline__ void cvt_e2m1x8_bf16(uint32_t w, __nv_bfloat162 sc, u
 
 // Eight E2M1 codes times an E4M3 block scale -> four bf16x2 words.  `sc` = the scale as an f16x2
 // pair.  The product is exact in FP16 (2 + 4 significant bits, between 2^-10 and 2688), so
-// FP16 -> FP32 -> BF16 rounds nothing.
+// FP16 -> FP32 -> BF16 rounds nothing.  (Re-labelling the FP16 code value as a BF16 number by a
+// shift and two masks and multiplying in BF16 by 2^112 x scale is exact too and saves the three
+// conversions, but measured slower: FC1 of the Qwen3 shape 1.38 against 1.29 ms.)
 __device__ __forceinline__ void cvt_e2m1x8_scaled(uint32_t w, uint32_t sc, uint32_t (&out)[4]) {
   uint32_t v[4];
   cvt_e2m1x8_f16(w, v);
@@ -185,6 +189,97 @@ __device__ __forceinline__ void cvt_e4m3x4_f16(uint32_t w, uint32_t& s01, uint32
       "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}\n"
       : "=r"(s01), "=r"(s23)
       : "r"(w));
+}
+
+// Epilogue of one 128-row x 256-column accumulator for the rows of one warp (lane = token row `m`
+// of the tile, `half` = which half of the columns this warp takes): FC1 applies the expert's alpha
+// and the activation and stores BF16, FC2 applies alpha and stores the fp32 routed rows.
+template <int EPI>
+__device__ __forceinline__ void epilogue_rows(const Params& p, float alpha, int nt, size_t pos, bool valid,
+                                              uint32_t t_lane, int half) {
+  if (EPI == EPI_FC1_GATED) {
+    const int col0 = nt * 128 + half * 64;
+    __nv_bfloat16* orow = p.out_bf16 + pos * p.out_cols + col0;
+#pragma unroll 1
+    for (int ch = 0; ch < 4; ++ch) {
+      uint32_t ru[16], rg[16];
+      tc_ld_32x32b_x16(t_lane + half * 64 + ch * 16, ru);
+      tc_ld_32x32b_x16(t_lane + 128 + half * 64 + ch * 16, rg);
+      tc_wait_ld();
+      uint32_t o[8];
+#pragma unroll
+      for (int i = 0; i < 16; i += 2) {
+        float h2[2];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const float up = __fmul_rn(__uint_as_float(ru[i + q]), alpha);
+          const float gate = __fmul_rn(__uint_as_float(rg[i + q]), alpha);
+          if (p.tap != nullptr && valid && col0 + ch * 16 < p.out_cols) {
+            float* trow = p.tap + pos * p.w_rows;
+            trow[p.sub0_base + col0 + ch * 16 + i + q] = up;
+            trow[p.sub1_base + col0 + ch * 16 + i + q] = gate;
+          }
+          h2[q] = act_gated(gate, up, p);
+        }
+        const __nv_bfloat162 b2 = __floats2bfloat162_rn(h2[0], h2[1]);
+        o[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+      }
+      if (valid && col0 + ch * 16 < p.out_cols) {
+        uint4* dst = reinterpret_cast<uint4*>(orow + ch * 16);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+    }
+  } else if (EPI == EPI_FC1_RELU2) {
+    const int col0 = nt * 256 + half * 128;
+    __nv_bfloat16* orow = p.out_bf16 + pos * p.out_cols + col0;
+#pragma unroll 1
+    for (int ch = 0; ch < 8; ++ch) {
+      uint32_t rr2[16];
+      tc_ld_32x32b_x16(t_lane + half * 128 + ch * 16, rr2);
+      tc_wait_ld();
+      uint32_t o[8];
+#pragma unroll
+      for (int i = 0; i < 16; i += 2) {
+        float h2[2];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const float v = __fmul_rn(__uint_as_float(rr2[i + q]), alpha);
+          if (p.tap != nullptr && valid && col0 + ch * 16 < p.out_cols)
+            p.tap[pos * p.w_rows + col0 + ch * 16 + i + q] = v;
+          const float r = fmaxf(v, 0.f);
+          h2[q] = __fmul_rn(r, r);
+        }
+        const __nv_bfloat162 b2 = __floats2bfloat162_rn(h2[0], h2[1]);
+        o[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+      }
+      if (valid && col0 + ch * 16 < p.out_cols) {
+        uint4* dst = reinterpret_cast<uint4*>(orow + ch * 16);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+    }
+  } else {
+    const int col0 = nt * 256 + half * 128;
+    float* orow = p.out_f32 + pos * p.out_cols + col0;
+#pragma unroll 1
+    for (int ch = 0; ch < 8; ++ch) {
+      uint32_t rr2[16];
+      tc_ld_32x32b_x16(t_lane + half * 128 + ch * 16, rr2);
+      tc_wait_ld();
+      if (valid && col0 + ch * 16 < p.out_cols) {
+        // 32 bytes per lane and instruction: half as many store instructions as with 16-byte
+        // stores, and the converter warps need the load/store unit too
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__uint_as_float(rr2[8 * q + i]), alpha);
+          st_global_f32x8(orow + ch * 16 + 8 * q, v);
+        }
+      }
+    }
+  }
 }
 
 template <int EPI>
@@ -465,87 +560,7 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
       const uint32_t t_lane = tmem_base + buf * 256 + (static_cast<uint32_t>(sub * 32) << 16);
       const bool valid = m < nrows;
       const size_t pos = static_cast<size_t>(row0 + m);
-      if (EPI == EPI_FC1_GATED) {
-        const int col0 = c.nt * 128 + half * 64;
-        __nv_bfloat16* orow = p.out_bf16 + pos * p.out_cols + col0;
-#pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t ru[16], rg[16];
-          tc_ld_32x32b_x16(t_lane + half * 64 + ch * 16, ru);
-          tc_ld_32x32b_x16(t_lane + 128 + half * 64 + ch * 16, rg);
-          tc_wait_ld();
-          uint32_t o[8];
-#pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            float h2[2];
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              const float up = __fmul_rn(__uint_as_float(ru[i + q]), alpha);
-              const float gate = __fmul_rn(__uint_as_float(rg[i + q]), alpha);
-              if (p.tap != nullptr && valid && col0 + ch * 16 < p.out_cols) {
-                float* trow = p.tap + pos * p.w_rows;
-                trow[p.sub0_base + col0 + ch * 16 + i + q] = up;
-                trow[p.sub1_base + col0 + ch * 16 + i + q] = gate;
-              }
-              h2[q] = act_gated(gate, up, p);
-            }
-            const __nv_bfloat162 b2 = __floats2bfloat162_rn(h2[0], h2[1]);
-            o[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
-          }
-          if (valid && col0 + ch * 16 < p.out_cols) {
-            uint4* dst = reinterpret_cast<uint4*>(orow + ch * 16);
-            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-          }
-        }
-      } else if (EPI == EPI_FC1_RELU2) {
-        const int col0 = c.nt * 256 + half * 128;
-        __nv_bfloat16* orow = p.out_bf16 + pos * p.out_cols + col0;
-#pragma unroll 1
-        for (int ch = 0; ch < 8; ++ch) {
-          uint32_t rr2[16];
-          tc_ld_32x32b_x16(t_lane + half * 128 + ch * 16, rr2);
-          tc_wait_ld();
-          uint32_t o[8];
-#pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            float h2[2];
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              const float v = __fmul_rn(__uint_as_float(rr2[i + q]), alpha);
-              if (p.tap != nullptr && valid && col0 + ch * 16 < p.out_cols)
-                p.tap[pos * p.w_rows + col0 + ch * 16 + i + q] = v;
-              const float r = fmaxf(v, 0.f);
-              h2[q] = __fmul_rn(r, r);
-            }
-            const __nv_bfloat162 b2 = __floats2bfloat162_rn(h2[0], h2[1]);
-            o[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
-          }
-          if (valid && col0 + ch * 16 < p.out_cols) {
-            uint4* dst = reinterpret_cast<uint4*>(orow + ch * 16);
-            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-          }
-        }
-      } else {
-        const int col0 = c.nt * 256 + half * 128;
-        float* orow = p.out_f32 + pos * p.out_cols + col0;
-#pragma unroll 1
-        for (int ch = 0; ch < 8; ++ch) {
-          uint32_t rr2[16];
-          tc_ld_32x32b_x16(t_lane + half * 128 + ch * 16, rr2);
-          tc_wait_ld();
-          if (valid && col0 + ch * 16 < p.out_cols) {
-            float4* dst = reinterpret_cast<float4*>(orow + ch * 16);
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              dst[q] = make_float4(__fmul_rn(__uint_as_float(rr2[4 * q]), alpha),
-                                   __fmul_rn(__uint_as_float(rr2[4 * q + 1]), alpha),
-                                   __fmul_rn(__uint_as_float(rr2[4 * q + 2]), alpha),
-                                   __fmul_rn(__uint_as_float(rr2[4 * q + 3]), alpha));
-          }
-        }
-      }
+      epilogue_rows<EPI>(p, alpha, c.nt, pos, valid, t_lane, half);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
@@ -562,167 +577,196 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
 }
 
 // ---------------------------------------------------------------------------------------------
-// FC2 with the weights as the TENSOR-MEMORY operand of the MMA.
+// The same GEMMs on CTA PAIRS (clusters of two, tcgen05 cta_group::2), for plans with several row
+// tiles per expert.
 //
-// Operand roles swapped against the kernel above: the tile is 128 weight rows (output features,
-// the MMA's M) x the 128 token rows of one row tile (the MMA's N).  The converter warps write the
-// expanded weights straight into tensor memory (tcgen05.st: lane = weight row, eight 32-bit columns
-// = sixteen BF16 values of K per MMA), so they are neither written to nor re-read from shared
-// memory; per k-block shared memory sees 16 KiB of token rows written and read once, 4 KiB of
-// codes and one scale atom.  Opt-in (B200MOE_W4A16_TS=1): it passes the same parity tests and, as
-// measured on the Qwen3-shaped workload, runs FC2 in 0.80 ms against 0.77 ms for the kernel above
-// - shared-memory traffic is therefore not what holds either back.  Unchanged by: 6 or 10 token
-// stages, sixteen converter warps on alternate k-blocks, one commit per k-block instead of two,
-// the epilogue's stores removed, the MMA thread not waiting for the token rows.
+// A pair shares one 256 x 256 tile: each CTA owns 128 token rows (its own row tile of the expert)
+// and expands only ITS HALF of the 256 weight rows (FC1, gated: the even CTA the 128 "up" rows, the
+// odd CTA the 128 "gate" rows); the pair's MMA (M = 256, N = 256, issued by one thread of the even
+// CTA) reads the halves out of both CTAs' shared memory and writes a 128 x 256 accumulator into each
+// CTA's tensor memory.  Per CTA and k-block of 64 that halves the conversion work (two threads per
+// weight row) and the shared-memory traffic that bounds the single-CTA kernel: the MMAs read
+// 16 + 16 KiB of operands instead of 16 + 32, the converters write 16 KiB instead of 32.
 //
-// Tensor memory: columns 0..255 two 128-column accumulators (the epilogue of a tile runs under the
-// main loop of the next), columns 256..511 a ring of eight 32-column slots of converted weights.
-// Accumulator lanes are output features and columns tokens, so a warp's store of one accumulator
-// column is 128 contiguous bytes of a routed row.
-namespace ts {
+// Roles per CTA (640 threads): warp 0 token-row producer (the copies of both CTAs complete on the
+// EVEN CTA's stage barrier), warp 2 producer of packed codes and scale atoms (four k-blocks per
+// stage, own ring), warps 4..11 converters (arrive on the even CTA's "tile converted" barrier, 16
+// arrivals per k-block), warps 12..19 epilogue of the CTA's own accumulator (double buffered:
+// 2 x 256 columns).  Even CTA only: warp 1 issues the MMAs and commits (multicast) to both CTAs'
+// barriers.  Every wait is bounded; the two cluster-wide barriers (after set-up, before tear-down)
+// are reached by both CTAs unconditionally.
+namespace pr {
 
-#ifndef W4A16_TS_TOK_STAGES
-#define W4A16_TS_TOK_STAGES 6
-#endif
-#ifndef W4A16_TS_GROUPS
-#define W4A16_TS_GROUPS 1
-#endif
-constexpr int kTokStages = W4A16_TS_TOK_STAGES;   // token rows + scale atom of one k-block
-constexpr int kRawStages = 3;                // packed codes of four k-blocks
-constexpr int kASlots = 8;                   // converted weights in tensor memory, one k-block each
-constexpr int kGroups = W4A16_TS_GROUPS;     // groups of 8 converter warps taking alternate k-blocks
-constexpr int kCvtWarps = 8 * kGroups;
-constexpr int kCodesWarp = 2 + kCvtWarps + 8;        // its own warp: see the producers
-constexpr int kThreads = (kCodesWarp + 1) * 32;      // TMA, MMA, converter warps, 8 epilogue warps, codes TMA
-constexpr int kSmemTok = 128 * 128;
-constexpr int kSmemAtom = 512;
-constexpr int kSmemCodes = 128 * 128;
-constexpr int kAccCols = 128;
-constexpr int kSlotCols = 32;
+using namespace ::b200moe::pair;
 
-struct __align__(8) SmemTail {
-  uint64_t full[kTokStages];     // token rows and scale atom landed
-  uint64_t empty[kTokStages];    // 8 converter warps (scale atom) + the MMAs that read the rows
-  uint64_t rfull[kRawStages];
-  uint64_t rempty[kRawStages];   // 8 converter warps
-  uint64_t afull[kASlots];       // 8 converter warps wrote the slot
-  uint64_t aempty[kASlots];      // the MMAs that read the slot retired
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
+constexpr int kAStages = 5;                  // token rows of one k-block
+constexpr int kBStagesP = 4;                 // converted weight rows of one k-block (this CTA's half)
+constexpr int kRawStagesP = 3;               // packed codes + scale atoms of four k-blocks
+constexpr int kSmemAP = 128 * 128;           // 16 KiB
+constexpr int kSmemBP = 128 * 128;           // 16 KiB
+constexpr int kSmemCodes = 128 * 128;        // 128 weight rows x 128 bytes (four k-blocks)
+constexpr int kSmemAtoms = 2 * 4 * 512;      // two scale row-groups (the rows may straddle) x four k-blocks
+constexpr int kRawBytes = kSmemCodes + kSmemAtoms;
+constexpr int kConvWarpsP = 8;
+constexpr int kThreadsP = (4 + kConvWarpsP + 8) * 32;
+
+struct __align__(8) SmemTailP {
+  uint64_t afull[kAStages];      // even CTA: the token rows of both CTAs have landed
+  uint64_t aempty[kAStages];     // per CTA: the MMAs that read the stage have retired
+  uint64_t rfull[kRawStagesP];   // per CTA: codes and scale atoms have landed
+  uint64_t rempty[kRawStagesP];  // per CTA: the eight converter warps have read them
+  uint64_t bfull[kBStagesP];     // even CTA: the 16 converter warps of the pair have written the tile
+  uint64_t bempty[kBStagesP];    // per CTA: the MMAs that read the tile have retired
+  uint64_t tmem_full[2];         // per CTA: accumulator complete
+  uint64_t tmem_empty[2];        // even CTA: the 16 epilogue warps of the pair have drained it
   uint32_t tmem_base;
   int abort_flag;
   int32_t tile_base[kMaxExperts + 1];
+  int32_t pair_base[kMaxExperts + 1];
 };
-constexpr int kSmemBytes = 1024 + kTokStages * (kSmemTok + kSmemAtom) + kRawStages * kSmemCodes +
-                           static_cast<int>(sizeof(SmemTail));
+constexpr int kSmemBytesP = 1024 + kAStages * kSmemAP + kBStagesP * kSmemBP + kRawStagesP * kRawBytes +
+                            static_cast<int>(sizeof(SmemTailP));
+static_assert(kSmemBytesP <= 227 * 1024, "shared memory of the W4A16 CTA-pair kernel");
 
-// D[tmem] (+)= A[tmem] * B[smem], kind::f16
-__device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
+// Work item of a pair: (expert, n-tile, pair of row tiles).  This CTA's row tile is first + rank;
+// an expert with an odd number of row tiles leaves the odd CTA of its last pair without one
+// (rows = 0: it multiplies the neighbour's rows again and stores nothing).
+struct PairCoord {
+  int e, nt, mt_load, rows;
+};
+__device__ __forceinline__ PairCoord decode_pair(int w, const Params& p, const SmemTailP* tail, int rank) {
+  const TileCoord c = decode_tile(w, p.n_tiles, tail->pair_base, p.E);
+  PairCoord r;
+  r.e = c.e;
+  r.nt = c.nt;
+  const int last = tail->tile_base[c.e + 1] - 1;
+  const int mt = tail->tile_base[c.e] + 2 * (c.mt - tail->pair_base[c.e]) + rank;
+  r.mt_load = mt <= last ? mt : last;
+  r.rows = mt <= last ? p.mtile_rows[mt] : 0;
+  return r;
+}
+// first weight row (inside the expert) of the 128 rows this CTA expands for n-tile `nt`
+__device__ __forceinline__ int weight_row0(const Params& p, int nt, int rank) {
+  const int r0 = p.sub0_base + nt * p.n_step;
+  if (rank == 0) return r0;
+  const int r1 = p.sub1_base + nt * p.n_step;
+  return r1 >= p.w_rows ? r0 : r1;
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
-grouped_gemm2_w4a16_ts_kernel(const __grid_constant__ CUtensorMap tmTok,
-                              const __grid_constant__ CUtensorMap tmW, const Params p) {
+template <int EPI>
+__global__ void __launch_bounds__(kThreadsP, 1)
+grouped_gemm_w4a16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
+                               const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* sTok = smem;
-  uint8_t* sCodes = sTok + kTokStages * kSmemTok;
-  uint8_t* sAtom = sCodes + kRawStages * kSmemCodes;
-  SmemTail* tail = reinterpret_cast<SmemTail*>(sAtom + kTokStages * kSmemAtom);
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + kAStages * kSmemAP;
+  uint8_t* sRaw = sB + kBStagesP * kSmemBP;       // [stage][codes 16 KiB | atoms 4 KiB]
+  SmemTailP* tail = reinterpret_cast<SmemTailP*>(sRaw + kRawStagesP * kRawBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_ctarank());     // 0 = even CTA (issues the MMAs)
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kTokStages; ++s) {
-      mbar_init(&tail->full[s], 1);
-      mbar_init(&tail->empty[s], 9);
+    for (int s = 0; s < kAStages; ++s) {
+      mbar_init(&tail->afull[s], 1);
+      mbar_init(&tail->aempty[s], 1);
     }
-    for (int r = 0; r < kRawStages; ++r) {
-      mbar_init(&tail->rfull[r], 1);
-      mbar_init(&tail->rempty[r], kCvtWarps);
+    for (int s = 0; s < kRawStagesP; ++s) {
+      mbar_init(&tail->rfull[s], 1);
+      mbar_init(&tail->rempty[s], kConvWarpsP);
     }
-    for (int a = 0; a < kASlots; ++a) {
-      mbar_init(&tail->afull[a], 8);
-      mbar_init(&tail->aempty[a], 1);
+    for (int s = 0; s < kBStagesP; ++s) {
+      mbar_init(&tail->bfull[s], 2 * kConvWarpsP);
+      mbar_init(&tail->bempty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tail->tmem_full[b], 1);
-      mbar_init(&tail->tmem_empty[b], 8);
+      mbar_init(&tail->tmem_empty[b], 16);
     }
     tail->abort_flag = 0;
     fence_mbar_init();
+    int acc = 0;
+    for (int e = 0; e < p.E; ++e) {
+      const int t0 = p.tile_base[e], t1 = p.tile_base[e + 1];
+      tail->tile_base[e] = t0;
+      tail->pair_base[e] = acc;
+      acc += (t1 - t0 + 1) >> 1;
+      if (e == p.E - 1) tail->tile_base[p.E] = t1;
+    }
+    tail->pair_base[p.E] = acc;
   }
-  for (int i = threadIdx.x; i <= p.E; i += blockDim.x) tail->tile_base[i] = p.tile_base[i];
   if (warp == 1) {
-    tmem_alloc(&tail->tmem_base, 512);
-    tmem_relinquish();
+    tmem_alloc_pair(&tail->tmem_base, 512);
+    tmem_relinquish_pair();
   }
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();          // both CTAs' barriers are initialised before anyone signals them
   tc_fence_after();
 
   const uint32_t tmem_base = tail->tmem_base;
   volatile int* abort_flag = &tail->abort_flag;
-  const int total_work = tail->tile_base[p.E] * p.n_tiles;
+  const int total_work = tail->pair_base[p.E] * p.n_tiles;
 
   if (warp == 0) {
-    // ------------------------------ TMA producers -----------------------------
-    // One thread brings the token rows and the scale atom of every k-block; the packed codes
-    // (every fourth k-block) have a warp of their own (below): two lanes of ONE warp that wait
-    // on different barriers hold each other up, a lane parked in its wait keeps the other from
-    // running when its barrier fires.
+    // ------------------------------ token-row producer (both CTAs) -----------------
     if (lane == 0) {
-      tma_prefetch_desc(&tmTok);
+      tma_prefetch_desc(&tmA);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-        const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
-        const int row0 = p.mtile_row0[c.mt];
-        const uint8_t* sf_e = p.sf + (static_cast<size_t>(c.e) * p.sf_rowgroups + c.nt) * p.atoms_k * 512;
+      for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+        const PairCoord c = decode_pair(w, p, tail, rank);
+        const int row0 = p.mtile_row0[c.mt_load];
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait_bounded(&tail->empty[stage], phase ^ 1, abort_flag, p.status, WAIT_SMEM_EMPTY)) {
+          if (!mbar_wait_bounded(&tail->aempty[stage], phase ^ 1, abort_flag, p.status, WAIT_SMEM_EMPTY)) {
             ok = false;
             break;
           }
-          uint64_t* bar = &tail->full[stage];
-          mbar_expect_tx(bar, kSmemTok + kSmemAtom);
-          tma_load_2d(sTok + stage * kSmemTok, &tmTok, bar, kb * kKPerStage, row0);
-          bulk_load(sAtom + stage * kSmemAtom, sf_e + static_cast<size_t>(kb) * 512, 512, bar);
-          if (++stage == kTokStages) {
+          if (rank == 0) mbar_expect_tx(&tail->afull[stage], 2u * kSmemAP);
+          tma_load_2d_pair(sA + stage * kSmemAP, &tmA, map_to_cta(smem_u32(&tail->afull[stage]), 0),
+                           kb * kKPerStage, row0);
+          if (++stage == kAStages) {
             stage = 0;
             phase ^= 1;
           }
         }
       }
       if (!ok) {
-        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);   // let copies in flight land
       }
     }
-  } else if (warp == kCodesWarp) {
-    if (lane == 0) {
-      tma_prefetch_desc(&tmW);
+  } else if (warp == 2) {
+    // ------------------------------ codes + scale atoms (both CTAs) ----------------
+    // lane 0: the packed codes of this CTA's 128 weight rows, four k-blocks per box; lanes 1, 2: the
+    // scale atoms of the (up to) two row-groups those rows touch, four k-blocks = 2 KiB contiguous
+    if (lane < 3) {
+      if (lane == 0) tma_prefetch_desc(&tmW);
       int rs = 0;
       uint32_t rphase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-        const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
-        const int r0 = c.nt * 128;                           // first weight row of the tile
+      for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+        const PairCoord c = decode_pair(w, p, tail, rank);
+        const int r = weight_row0(p, c.nt, rank);
+        const uint8_t* sf_e = p.sf + static_cast<size_t>(c.e) * p.sf_rowgroups * p.atoms_k * 512;
+        const int g = lane == 2 ? min((r + 127) >> 7, p.sf_rowgroups - 1) : (r >> 7);
         for (int kb = 0; kb < p.k_blocks; kb += kKBlocksPerRaw) {
           if (!mbar_wait_bounded(&tail->rempty[rs], rphase ^ 1, abort_flag, p.status, WAIT_SMEM_EMPTY)) {
             ok = false;
             break;
           }
-          mbar_expect_tx(&tail->rfull[rs], kSmemCodes);
-          tma_load_2d(sCodes + rs * kSmemCodes, &tmW, &tail->rfull[rs], kb * 32, c.e * p.w_rows + r0);
-          if (++rs == kRawStages) {
+          const uint32_t atom_bytes = static_cast<uint32_t>(min(kKBlocksPerRaw, p.atoms_k - kb)) * 512u;
+          uint8_t* dst = sRaw + rs * kRawBytes;
+          if (lane == 0) {
+            mbar_expect_tx(&tail->rfull[rs], kSmemCodes + 2u * atom_bytes);
+            tma_load_2d(dst, &tmW, &tail->rfull[rs], kb * 32, c.e * p.w_rows + r);
+          } else {
+            bulk_load(dst + kSmemCodes + (lane - 1) * 2048,
+                      sf_e + (static_cast<size_t>(g) * p.atoms_k + kb) * 512, atom_bytes, &tail->rfull[rs]);
+          }
+          if (++rs == kRawStagesP) {
             rs = 0;
             rphase ^= 1;
           }
@@ -733,184 +777,156 @@ grouped_gemm2_w4a16_ts_kernel(const __grid_constant__ CUtensorMap tmTok,
       }
     }
   } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(128, 128);
-      int stage = 0, slot = 0;
-      uint32_t phase = 0, aphase = 0;
+    // ------------------------------ MMA issuer (even CTA) --------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(256, 256);
+      int stage = 0, bstage = 0, buf = 0;
+      uint32_t phase = 0, bphase = 0;
       uint32_t acc_phase[2] = {0, 0};
-      int buf = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+      const uint64_t adesc0 = make_desc_sw128(smem_u32(sA)), bdesc0 = make_desc_sw128(smem_u32(sB));
+      for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
         if (!mbar_wait_bounded(&tail->tmem_empty[buf], acc_phase[buf] ^ 1, abort_flag, p.status,
                                WAIT_TMEM_EMPTY)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * kAccCols;
+        const uint32_t d_tmem = tmem_base + buf * 256;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL) ||
-              !mbar_wait_bounded(&tail->afull[slot], aphase, abort_flag, p.status, WAIT_CONVERT)) {
+          if (!mbar_wait_bounded(&tail->afull[stage], phase, abort_flag, p.status, WAIT_SMEM_FULL) ||
+              !mbar_wait_bounded(&tail->bfull[bstage], bphase, abort_flag, p.status, WAIT_CONVERT)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint64_t bdesc = make_desc_sw128(smem_u32(sTok + stage * kSmemTok));
-          const uint32_t a_tmem = tmem_base + 2 * kAccCols + slot * kSlotCols;
-#pragma unroll
-          for (int j = 0; j < 4; ++j)   // 16 values of K per MMA: 8 columns of the slot, 32 bytes of a token row
-            mma_bf16_ts(d_tmem, a_tmem + 8 * j, bdesc + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-          tc_commit(&tail->empty[stage]);
-          tc_commit(&tail->aempty[slot]);
-          if (++stage == kTokStages) {
+          const uint64_t adesc = adesc0 + static_cast<uint32_t>(stage * (kSmemAP >> 4));
+          const uint64_t bdesc = bdesc0 + static_cast<uint32_t>(bstage * (kSmemBP >> 4));
+          mma_bf16_pair(d_tmem, adesc, bdesc, idesc, kb > 0 ? 1u : 0u);     // 16 bf16 = 32 bytes per MMA
+          mma_bf16_pair(d_tmem, adesc + 2, bdesc + 2, idesc, 1u);
+          mma_bf16_pair(d_tmem, adesc + 4, bdesc + 4, idesc, 1u);
+          mma_bf16_pair(d_tmem, adesc + 6, bdesc + 6, idesc, 1u);
+          tc_commit_pair_both(&tail->aempty[stage]);
+          tc_commit_pair_both(&tail->bempty[bstage]);
+          if (++stage == kAStages) {
             stage = 0;
             phase ^= 1;
           }
-          if (++slot == kASlots) {
-            slot = 0;
-            aphase ^= 1;
+          if (++bstage == kBStagesP) {
+            bstage = 0;
+            bphase ^= 1;
           }
         }
-        if (ok) tc_commit(&tail->tmem_full[buf]);
+        if (ok) tc_commit_pair_both(&tail->tmem_full[buf]);
         acc_phase[buf] ^= 1;
         buf ^= 1;
       }
     }
-  } else if (warp < 2 + kCvtWarps) {
-    // ------------------------------ converters --------------------------------
-    // A warp may touch the 32 tensor-memory lanes of its sub-partition (warp % 4): thread = one
-    // weight row; the two warps of a sub-partition take the two halves (32 values) of the k-block.
-    const int sub = warp & 3, khalf = ((warp - 2) >> 2) & 1, group = (warp - 2) >> 3;
-    int it = 0;
-    const int row = sub * 32 + lane;
-    const uint32_t atom_off = static_cast<uint32_t>(row & 31) * 16u + static_cast<uint32_t>(row >> 5) * 4u;
-    int stage = 0, slot = 0, rs = 0;
-    uint32_t phase = 0, aphase = 0, rphase = 0;
+  } else if (warp >= 4 && warp < 4 + kConvWarpsP) {
+    // ------------------------------ converters (both CTAs) -------------------------
+    // Two threads per weight row, 32 codes (16 bytes) -> 32 bf16 (64 bytes) each.  Warps 4..7 take
+    // the first half of the k-block, warps 8..11 the second: a warp touches 32 different rows, so
+    // its 16-byte accesses to the 128-byte-swizzled rows spread over all banks.
+    const int t = threadIdx.x - 128;
+    const int khalf = t >> 7, rr = t & 127;
+    const uint32_t bfull_base = map_to_cta(smem_u32(&tail->bfull[0]), 0);
+    int bstage = 0, rs = 0;
+    uint32_t bphase = 0, rphase = 0;
     bool ok = true;
-    for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-      for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-        if (kGroups == 1 || it % kGroups == group) {
-        if (!mbar_wait_bounded(&tail->full[stage], phase, abort_flag, p.status, WAIT_CONVERT) ||
-            !mbar_wait_bounded(&tail->rfull[rs], rphase, abort_flag, p.status, WAIT_CONVERT) ||
-            !mbar_wait_bounded(&tail->aempty[slot], aphase ^ 1, abort_flag, p.status, WAIT_CONVERT)) {
+    for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+      const PairCoord c = decode_pair(w, p, tail, rank);
+      const int r = weight_row0(p, c.nt, rank);
+      const int wrow = r + rr;                               // weight row inside the expert
+      const int atom_sel = (wrow >> 7) - (r >> 7);           // 0 or 1: which staged row-group
+      const uint32_t sf_off = kSmemCodes + atom_sel * 2048 + (wrow & 31) * 16 + ((wrow >> 5) & 3) * 4;
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        if (!mbar_wait_bounded(&tail->rfull[rs], rphase, abort_flag, p.status, WAIT_CONVERT) ||
+            !mbar_wait_bounded(&tail->bempty[bstage], bphase ^ 1, abort_flag, p.status, WAIT_CONVERT)) {
           ok = false;
           break;
         }
-        tc_fence_after();
-        const int chunk = (kb & (kKBlocksPerRaw - 1)) * 2 + khalf;      // 16 bytes = 32 codes
-        const uint4 cw = *reinterpret_cast<const uint4*>(sCodes + rs * kSmemCodes + row * 128 +
-                                                         ((chunk ^ (row & 7)) << 4));
-        const uint32_t sfw = *reinterpret_cast<const uint32_t*>(sAtom + stage * kSmemAtom + atom_off);
+        const int kq = kb & (kKBlocksPerRaw - 1);
+        const uint8_t* raw = sRaw + rs * kRawBytes;
+        const int chunk = kq * 2 + khalf;                    // 16-byte chunk of the 128-byte code row
+        const uint4 cw = *reinterpret_cast<const uint4*>(raw + rr * 128 + ((chunk ^ (rr & 7)) << 4));
+        const uint32_t sfw = *reinterpret_cast<const uint32_t*>(raw + sf_off + kq * 512);
         const uint32_t sf2 = (sfw >> (16 * khalf)) & 0xffffu;            // this half's two scale bytes
         const uint32_t words[4] = {cw.x, cw.y, cw.z, cw.w};
-        uint32_t r[16];
+        uint8_t* brow = sB + bstage * kSmemBP + rr * 128;
         if (!p.sf_e8m0) {
-          uint32_t s01, unused;
-          cvt_e4m3x4_f16(sf2, s01, unused);
+          uint32_t s01, s23;
+          cvt_e4m3x4_f16(sf2, s01, s23);
 #pragma unroll
-          for (int blk = 0; blk < 2; ++blk) {
-            const uint32_t sc = __byte_perm(s01, 0u, blk ? 0x3232u : 0x1010u);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              uint32_t o[4];
-              cvt_e2m1x8_scaled(words[blk * 2 + h], sc, o);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) r[(blk * 2 + h) * 4 + j] = o[j];
-            }
+          for (int j = 0; j < 4; ++j) {                      // 8 values per word, 16 per scale
+            const uint32_t sc = __byte_perm(s01, 0u, j < 2 ? 0x1010u : 0x3232u);
+            uint32_t o[4];
+            cvt_e2m1x8_scaled(words[j], sc, o);
+            *reinterpret_cast<uint4*>(brow + (((khalf * 4 + j) ^ (rr & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
           }
         } else {
 #pragma unroll
-          for (int blk = 0; blk < 2; ++blk) {
-            const uint32_t sb = (sf2 >> (8 * blk)) & 0xffu;
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t sb = (sf2 >> (j < 2 ? 0 : 8)) & 0xffu;
+            // E8M0: 2^(b-127) is the f32 with exponent field b (b = 0: the subnormal 2^-127)
             const float sv = __uint_as_float(sb != 0u ? sb << 23 : 0x00400000u);
-            const __nv_bfloat16 s = __float2bfloat16_rn(sv);
-            const __nv_bfloat162 sc = __halves2bfloat162(s, s);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              uint32_t o[4];
-              cvt_e2m1x8_bf16(words[blk * 2 + h], sc, o);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) r[(blk * 2 + h) * 4 + j] = o[j];
-            }
+            const __nv_bfloat16 s1 = __float2bfloat16_rn(sv);
+            uint32_t o[4];
+            cvt_e2m1x8_bf16(words[j], __halves2bfloat162(s1, s1), o);
+            *reinterpret_cast<uint4*>(brow + (((khalf * 4 + j) ^ (rr & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
           }
         }
-        tc_st_32x32b_x16(tmem_base + 2 * kAccCols + slot * kSlotCols + khalf * 16 +
-                             (static_cast<uint32_t>(sub * 32) << 16),
-                         r);
-        tc_wait_st();
-        tc_fence_before();
+        fence_proxy_async_smem();                            // generic writes -> tensor-core reads
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&tail->afull[slot]);
-          mbar_arrive(&tail->empty[stage]);
-        }
-        }
-        if ((kb & (kKBlocksPerRaw - 1)) == kKBlocksPerRaw - 1 || kb == p.k_blocks - 1) {
+        if (lane == 0) mbar_arrive_remote(bfull_base + static_cast<uint32_t>(bstage * sizeof(uint64_t)));
+        if (kq == kKBlocksPerRaw - 1 || kb == p.k_blocks - 1) {
+          // this warp has read all it needs of the stage's codes and atoms
           if (lane == 0) mbar_arrive(&tail->rempty[rs]);
-          if (++rs == kRawStages) {
+          if (++rs == kRawStagesP) {
             rs = 0;
             rphase ^= 1;
           }
         }
-        if (++stage == kTokStages) {
-          stage = 0;
-          phase ^= 1;
-        }
-        if (++slot == kASlots) {
-          slot = 0;
-          aphase ^= 1;
+        if (++bstage == kBStagesP) {
+          bstage = 0;
+          bphase ^= 1;
         }
       }
     }
-  } else {
-    // ------------------------------ epilogue ----------------------------------
-    // lane = output feature, accumulator column = token of the row tile
+  } else if (warp >= 4 + kConvWarpsP) {
+    // ------------------------------ epilogue (both CTAs) ---------------------------
     const int sub = warp & 3;
-    const int half = (warp - 2 - kCvtWarps) >> 2;
+    const int half = (warp - 4 - kConvWarpsP) >> 2;
+    const int m = sub * 32 + lane;
+    const uint32_t release_base = map_to_cta(smem_u32(&tail->tmem_empty[0]), 0);
     uint32_t acc_phase[2] = {0, 0};
     int buf = 0;
-    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
-      const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
-      const int row0 = p.mtile_row0[c.mt];
-      const int nrows = p.mtile_rows[c.mt];
+    for (int w = cluster_id; w < total_work; w += num_clusters) {
+      const PairCoord c = decode_pair(w, p, tail, rank);
+      const int row0 = p.mtile_row0[c.mt_load];
       const float alpha = p.alphas[c.e];
-      if (!mbar_wait_bounded(&tail->tmem_full[buf], acc_phase[buf], abort_flag, p.status, WAIT_TMEM_FULL))
-        break;
+      if (!mbar_wait_bounded(&tail->tmem_full[buf], acc_phase[buf], abort_flag, p.status, WAIT_TMEM_FULL)) break;
       acc_phase[buf] ^= 1;
       tc_fence_after();
-      const uint32_t t_lane = tmem_base + buf * kAccCols + (static_cast<uint32_t>(sub * 32) << 16);
-      const int feature = c.nt * 128 + sub * 32 + lane;
-      const bool valid = feature < p.out_cols;
-      float* ocol = p.out_f32 + static_cast<size_t>(row0) * p.out_cols + feature;
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        const int tok0 = half * 64 + ch * 16;
-        if (tok0 >= nrows) break;                            // warp-uniform
-        uint32_t rr2[16];
-        tc_ld_32x32b_x16(t_lane + tok0, rr2);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-          if (valid && tok0 + i < nrows)
-            ocol[static_cast<size_t>(tok0 + i) * p.out_cols] = __fmul_rn(__uint_as_float(rr2[i]), alpha);
-      }
+      const uint32_t t_lane = tmem_base + buf * 256 + (static_cast<uint32_t>(sub * 32) << 16);
+      epilogue_rows<EPI>(p, alpha, c.nt, static_cast<size_t>(row0 + m), m < c.rows, t_lane, half);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tail->tmem_empty[buf]);
+      if (lane == 0) mbar_arrive_cluster(release_base + static_cast<uint32_t>(buf * sizeof(uint64_t)));
       buf ^= 1;
     }
   }
 
+  // ------------------------------ teardown ------------------------------------
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();          // nobody signals the other CTA's shared memory after this
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc_pair(tmem_base, 512);
   }
 }
 
-}  // namespace ts
+}  // namespace pr
 
 // x rows -> sorted-position order (the A operand of FC1), one warp per row
 __global__ void __launch_bounds__(256) permute_rows_bf16_kernel(
@@ -994,6 +1010,44 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmW, const Params& 
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 
+template <int EPI>
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmW, const Params& p, int max_ctas,
+                       cudaStream_t s) {
+  auto kern = pr::grouped_gemm_w4a16_pair_kernel<EPI>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pr::kSmemBytesP) != cudaSuccess)
+    return B200MOE_ECUDA;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.blockDim = dim3(pr::kThreadsP);
+  cfg.dynamicSmemBytes = pr::kSmemBytesP;
+  cfg.stream = s;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  // persistent grid: as many CTA pairs as can be resident at once
+  cfg.gridDim = dim3(static_cast<unsigned>(max_ctas & ~1));
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess || clusters < 1) return B200MOE_ECUDA;
+  if (2 * clusters < max_ctas) cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmW, p) == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+// CTA pairs once the plan averages two row tiles per expert (an expert with an odd number of row
+// tiles leaves half a pair idle); B200MOE_W4A16_PAIR=1 / 0 forces them on / off.
+static bool use_pair(const b200moe_gemm_args* a) {
+  static int mode = -2;
+  if (mode == -2) {
+    const char* e = getenv("B200MOE_W4A16_PAIR");
+    mode = e == nullptr ? -1 : (atoi(e) != 0 ? 1 : 0);
+  }
+  if (mode == 0 || a->layout->tile_rows != 128) return false;
+  if (mode == 1) return true;
+  return static_cast<int64_t>(a->layout->rows) >= 256ll * a->num_experts;
+}
+
 static void fill_common(Params& p, const b200moe_gemm_args* a, char* base) {
   const b200moe_scratch_layout& L = *a->layout;
   p.tile_base = reinterpret_cast<const int32_t*>(base + L.tile_base);
@@ -1052,13 +1106,15 @@ int w4a16_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
     p.n_step = 128;
     p.sub0_base = a->gate_first ? I : 0;
     p.sub1_base = a->gate_first ? 0 : I;
-    return launch<EPI_FC1_GATED>(tmA, tmW, p, grid, stream);
+    return use_pair(a) ? launch_pair<EPI_FC1_GATED>(tmA, tmW, p, grid, stream)
+                       : launch<EPI_FC1_GATED>(tmA, tmW, p, grid, stream);
   }
   p.n_tiles = ceil_div_i(I, 256);
   p.n_step = 256;
   p.sub0_base = 0;
   p.sub1_base = 128;
-  return launch<EPI_FC1_RELU2>(tmA, tmW, p, grid, stream);
+  return use_pair(a) ? launch_pair<EPI_FC1_RELU2>(tmA, tmW, p, grid, stream)
+                     : launch<EPI_FC1_RELU2>(tmA, tmW, p, grid, stream);
 }
 
 int w4a16_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
@@ -1089,20 +1145,7 @@ int w4a16_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
   p.sub0_base = 0;
   p.sub1_base = 128;
   const int grid = a->num_sms > 0 ? a->num_sms : sm_count();
-  static const bool use_ts = [] {
-    const char* e = getenv("B200MOE_W4A16_TS");             // 1: weights as the tensor-memory operand
-    return e != nullptr && atoi(e) != 0;
-  }();
-  if (use_ts) {
-    // weights as the tensor-memory operand: tiles of 128 output features
-    p.n_tiles = ceil_div_i(K, 128);
-    if (cudaFuncSetAttribute(ts::grouped_gemm2_w4a16_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             ts::kSmemBytes) != cudaSuccess)
-      return B200MOE_ECUDA;
-    ts::grouped_gemm2_w4a16_ts_kernel<<<grid, ts::kThreads, ts::kSmemBytes, stream>>>(tmA, tmW, p);
-    return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
-  }
-  return launch<EPI_FC2>(tmA, tmW, p, grid, stream);
+  return use_pair(a) ? launch_pair<EPI_FC2>(tmA, tmW, p, grid, stream) : launch<EPI_FC2>(tmA, tmW, p, grid, stream);
 }
 
 }  // namespace b200moe

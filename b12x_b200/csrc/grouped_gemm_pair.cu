@@ -18,6 +18,7 @@
 // barriers (after set-up, before tear-down) are reached by both CTAs unconditionally.
 #include <stdlib.h>
 
+#include "cluster_pair.cuh"
 #include "gemm_shared.cuh"
 
 namespace b200moe {
@@ -57,57 +58,6 @@ struct __align__(8) SmemTail {
 constexpr int kSmemBytes =
     1024 + kStages * kStageBytes + kSfSlots * kSfSlotBytes + static_cast<int>(sizeof(SmemTail));
 
-// ---- cluster / cta_group::2 PTX -------------------------------------------------------------
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// shared-window address of `saddr` (an address of this CTA) in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
-  return r;
-}
-// Arrive on a barrier of another CTA of the cluster.  Relaxed: what the arrival publishes are
-// tensor-memory reads / writes, ordered by tcgen05.fence::before_thread_sync on this side and
-// ::after_thread_sync on the waiting side; a release at cluster scope cost about a microsecond
-// per arrival here and doubled the kernel's time.
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
-               "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-// 2-D tiled load into THIS CTA's shared memory, completing on a barrier of the even CTA.
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr,
-                                                 int32_t x, int32_t y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
-      : "memory");
-}
-// arrive on the barrier at this offset in both CTAs of the pair when the pair's earlier tcgen05
-// operations have retired
-__device__ __forceinline__ void tc_commit_pair_both(uint64_t* bar) {
-  const uint16_t mask = 3;
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-      ::"r"(smem_u32(bar)), "h"(mask)
-      : "memory");
-}
 __device__ __forceinline__ void mma_nvf4_4x_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                                  uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
   asm volatile(

@@ -1,7 +1,8 @@
 """-m gpu: W4A16 layers with several 128-row tiles per expert against the CPU oracle.  In-process the
-FC2 runs on the kernel that expands the weights into shared memory; `test_ts_variant...` re-runs this
-file and the other W4A16 cases in a child process with B200MOE_W4A16_TS=1, which puts FC2 on the kernel
-that keeps the expanded weights in tensor memory (the switch is read once per process)."""
+kernel family follows the plan (CTA pairs once it averages two row tiles per expert); the two child
+runs repeat this file and the other W4A16 cases with the CTA-pair kernels forced on
+(B200MOE_W4A16_PAIR=1: every shape, also experts with one or an odd number of row tiles) and off
+(=0: the single-CTA kernel).  The switch is read once per process."""
 
 import os
 import subprocess
@@ -28,14 +29,24 @@ def test_w4a16_multi_tile_matches_oracle(tokens, experts, topk, hidden, inter, a
     _check_w4a16_layer(run_layer(synth.make_inputs(shp, seed=tokens + inter), want_fc1=True))
 
 
-@pytest.mark.timeout(600)
-def test_ts_variant_passes_the_w4a16_cases():
-    if os.environ.get("B200MOE_W4A16_TS") == "1":
+@pytest.mark.parametrize("tokens,experts,topk,hidden,inter,act", [
+    (1100, 4, 2, 512, 256, "silu"),         # 4-5 row tiles per expert: full pairs and a half-empty one
+    (640, 1, 1, 256, 192, "silu"),          # exactly five row tiles, one and a half feature tiles
+])
+def test_w4a16_many_row_tiles_matches_oracle(tokens, experts, topk, hidden, inter, act):
+    shp = _w16(tokens=tokens, experts=experts, topk=topk, hidden=hidden, intermediate=inter, activation=act)
+    _check_w4a16_layer(run_layer(synth.make_inputs(shp, seed=tokens + inter), want_fc1=True))
+
+
+@pytest.mark.parametrize("pair", ["1", "0"])
+@pytest.mark.timeout(900)
+def test_both_kernel_families_pass_the_w4a16_cases(pair):
+    if os.environ.get("B200MOE_W4A16_CHILD") == "1":
         pytest.skip("already the child run")
     here = Path(__file__).resolve().parent
-    env = dict(os.environ, B200MOE_W4A16_TS="1")
+    env = dict(os.environ, B200MOE_W4A16_PAIR=pair, B200MOE_W4A16_CHILD="1")
     r = subprocess.run([sys.executable, "-m", "pytest", str(Path(__file__).resolve()),
                         str(here / "test_gpu_parity.py"), str(here / "test_w4a16_sources.py"),
                         "-m", "gpu", "-k", "w4a16", "-x", "-q", "-p", "no:cacheprovider"],
-                       env=env, capture_output=True, text=True, timeout=550, cwd=str(here.parent))
+                       env=env, capture_output=True, text=True, timeout=850, cwd=str(here.parent))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
