@@ -599,6 +599,7 @@ namespace pr {
 
 using namespace ::b200moe::pair;
 
+// ring depths: 7/2/3, 6/3/3, 8/2/2 and 3/3/2 (token rows / converted tiles / code boxes) are all slower
 constexpr int kAStages = 5;                  // token rows of one k-block
 constexpr int kBStagesP = 4;                 // converted weight rows of one k-block (this CTA's half)
 constexpr int kRawStagesP = 3;               // packed codes + scale atoms of four k-blocks
