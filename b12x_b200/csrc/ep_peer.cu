@@ -33,6 +33,24 @@ struct PeerPtrs {
   void* p[B200MOE_MAX_RANKS];
 };
 
+// Scale bytes of one warp item (32 blocks): lanes 0, 4, .., 28 hold one 32-bit word each.  A link
+// packet per 4-byte word would double the packets of a row, so with 16-byte-aligned scale rows
+// lanes 0 and 16 collect four words each and store 16 bytes (bytes past the row's last block are
+// zero and lie inside the padded row); otherwise the words go out one by one.
+__device__ __forceinline__ void store_scale_words(uint8_t* dsf, int b, int nblk, uint32_t word, int lane,
+                                                  int sf_row_stride) {
+  if ((sf_row_stride & 15) == 0) {
+    uint4 q;
+    q.x = word;
+    q.y = __shfl_down_sync(0xffffffffu, word, 4);
+    q.z = __shfl_down_sync(0xffffffffu, word, 8);
+    q.w = __shfl_down_sync(0xffffffffu, word, 12);
+    if ((lane & 15) == 0 && b < nblk) *reinterpret_cast<uint4*>(dsf + b) = q;
+  } else if ((lane & 3) == 0 && b < nblk) {
+    *reinterpret_cast<uint32_t*>(dsf + b) = word;
+  }
+}
+
 // PAYLOAD 0: bf16 rows as they are.  1: NVFP4 codes + E4M3 scale bytes, quantised here with the
 // destination expert's input scale (the bytes the expert rank's own quantiser would have made, so
 // 9K/16 bytes cross the link per route instead of 2K).  2: MXFP8 values + E8M0 scale bytes (K + K/32).
@@ -54,15 +72,21 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
   __syncthreads();
   const int total = offs[world];
   const int lane = threadIdx.x & 31;
-  // one row per block at a time: all 256 threads work on it, so a row is a handful of independent
-  // 16-byte loads and (peer) stores per thread instead of a long walk by one warp
-  for (int pos = blockIdx.x; pos < total; pos += gridDim.x) {
+  // Work item of a WARP: 32 consecutive blocks of one row (512 NVFP4 / 1024 MXFP8 values, or 32
+  // 16-byte pieces of a bf16 row).  Every warp of the grid is busy whatever the row length, and a
+  // warp's loads and (peer) stores of one item are independent of its next item's.
+  const int nblk = PAYLOAD == 0 ? K >> 3 : (PAYLOAD == 1 ? K >> 4 : K >> 5);
+  const int cpr = (nblk + 31) >> 5;                       // items per row
+  const int warps = static_cast<int>(gridDim.x) * (blockDim.x >> 5);
+  for (int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < total * cpr; item += warps) {
+    const int pos = item / cpr;
+    const int b = (item - pos * cpr) * 32 + lane;
     int d = 0;
     while (d + 1 < world && pos >= offs[d + 1]) ++d;
     const int j = pos - offs[d];
     if (j >= cap) {
       // more rows for rank d than its receive region holds: the row is not sent, the step is invalid
-      if (threadIdx.x == 0 && status != nullptr) {
+      if (lane == 0 && status != nullptr) {
         atomicCAS(status, 0, 1);
         atomicCAS(status + 1, 0, 48 + d);     // 48 + destination rank: receive capacity exceeded
       }
@@ -76,54 +100,46 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
     if constexpr (PAYLOAD == 0) {
       uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(rows.p[d]) +
                                             static_cast<size_t>(slot) * K);
-      for (int q = threadIdx.x; q < (K >> 3); q += blockDim.x) dst[q] = __ldg(src + q);
+      if (b < nblk) dst[b] = __ldg(src + b);
     } else if constexpr (PAYLOAD == 1) {
-      const int nblk = K >> 4;
       const float gs = a1_gscale[gscale_len == 1 ? 0 : expert];
       uint2* dst = reinterpret_cast<uint2*>(static_cast<uint8_t*>(rows.p[d]) + static_cast<size_t>(slot) * (K >> 1));
       uint8_t* dsf = static_cast<uint8_t*>(sfs.p[d]) + static_cast<size_t>(slot) * sf_row_stride;
-      for (int b0 = 0; b0 < nblk; b0 += blockDim.x) {
-        const int b = b0 + threadIdx.x;
-        uint8_t sfb = 0;
-        if (b < nblk) {
-          float v[16];
-          bf16x8_to_f32(__ldg(src + 2 * b), v);
-          bf16x8_to_f32(__ldg(src + 2 * b + 1), v + 8);
-          uint32_t lo, hi;
-          quant_block16(v, gs, lo, hi, sfb);
-          dst[b] = make_uint2(lo, hi);
-        }
-        // four neighbouring lanes hold the four scale bytes of one 32-bit word
-        uint32_t word = sfb;
-        word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 1) << 8;
-        word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 2) << 16;
-        word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 3) << 24;
-        if ((lane & 3) == 0 && b < nblk) *reinterpret_cast<uint32_t*>(dsf + b) = word;
+      uint8_t sfb = 0;
+      if (b < nblk) {
+        float v[16];
+        bf16x8_to_f32(__ldg(src + 2 * b), v);
+        bf16x8_to_f32(__ldg(src + 2 * b + 1), v + 8);
+        uint32_t lo, hi;
+        quant_block16(v, gs, lo, hi, sfb);
+        dst[b] = make_uint2(lo, hi);
       }
+      // four neighbouring lanes hold the four scale bytes of one 32-bit word
+      uint32_t word = sfb;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 1) << 8;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 2) << 16;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 3) << 24;
+      store_scale_words(dsf, b, nblk, word, lane, sf_row_stride);
     } else {
-      const int nblk = K >> 5;
       uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(rows.p[d]) + static_cast<size_t>(slot) * K);
       uint8_t* dsf = static_cast<uint8_t*>(sfs.p[d]) + static_cast<size_t>(slot) * sf_row_stride;
-      for (int b0 = 0; b0 < nblk; b0 += blockDim.x) {
-        const int b = b0 + threadIdx.x;
-        uint8_t sfb = 0;
-        if (b < nblk) {
-          float v[32];
+      uint8_t sfb = 0;
+      if (b < nblk) {
+        float v[32];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) bf16x8_to_f32(__ldg(src + 4 * b + q), v + 8 * q);
-          uint32_t o[8];
-          quant_block32_mx(v, o, sfb);
-          dst[2 * b] = make_uint4(o[0], o[1], o[2], o[3]);
-          dst[2 * b + 1] = make_uint4(o[4], o[5], o[6], o[7]);
-        }
-        uint32_t word = sfb;      // lanes past the row's end contribute 0: the padding bytes are defined
-        word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 1) << 8;
-        word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 2) << 16;
-        word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 3) << 24;
-        if ((lane & 3) == 0 && b < nblk) *reinterpret_cast<uint32_t*>(dsf + b) = word;
+        for (int q = 0; q < 4; ++q) bf16x8_to_f32(__ldg(src + 4 * b + q), v + 8 * q);
+        uint32_t o[8];
+        quant_block32_mx(v, o, sfb);
+        dst[2 * b] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[2 * b + 1] = make_uint4(o[4], o[5], o[6], o[7]);
       }
+      uint32_t word = sfb;      // lanes past the row's end contribute 0: the padding bytes are defined
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 1) << 8;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 2) << 16;
+      word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 3) << 24;
+      store_scale_words(dsf, b, nblk, word, lane, sf_row_stride);
     }
-    if (threadIdx.x == 0) static_cast<int32_t*>(ids.p[d])[slot] = expert % local_modulus;
+    if (lane == 0 && b == 0) static_cast<int32_t*>(ids.p[d])[slot] = expert % local_modulus;
   }
   // unused slots of this rank's region on every peer: no route
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < world * cap; i += gridDim.x * blockDim.x) {
@@ -349,8 +365,11 @@ extern "C" int b200moe_ep_dispatch(const b200moe_ep_dispatch_args* a, void* stre
     if (a->payload == B200MOE_EP_PAYLOAD_NVFP4 && (a->a1_gscale == nullptr || a->gscale_len < 1))
       return B200MOE_EINVAL;
   }
-  int grid = rows;
-  grid = grid < 1 ? 1 : (grid > 148 * 8 ? 148 * 8 : grid);
+  // one warp per 32 blocks of a row; eight warps per CTA, at most eight CTAs per SM
+  const int per = a->payload == B200MOE_EP_PAYLOAD_BF16 ? 8 : (a->payload == B200MOE_EP_PAYLOAD_NVFP4 ? 16 : 32);
+  const int64_t items = static_cast<int64_t>(rows) * ((a->hidden_size / per + 31) / 32);
+  int grid = static_cast<int>((items + 7) / 8 < 148 * 8 ? (items + 7) / 8 : 148 * 8);
+  grid = grid < 1 ? 1 : grid;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->payload == B200MOE_EP_PAYLOAD_NVFP4) launch_dispatch<1>(a, rows_p, sf_p, ids_p, flags_p, grid, st);
   else if (a->payload == B200MOE_EP_PAYLOAD_MXFP8) launch_dispatch<2>(a, rows_p, sf_p, ids_p, flags_p, grid, st);

@@ -119,7 +119,8 @@ class PeerExpertParallelMoE(_LayerBase):
             row_bytes = shp.hidden // 2 if self.payload == "nvfp4" else shp.hidden
             nsf = shp.hidden // (16 if self.payload == "nvfp4" else 32)
             self.recv_q, self.rows_ptrs, self._h1 = _symm_empty((slots, row_bytes), torch.uint8, dev)
-            self.recv_sf, self.sf_ptrs, self._h4 = _symm_empty((slots, (nsf + 3) // 4 * 4), torch.uint8, dev)
+            # scale rows padded to 16 bytes: the sender then stores them 16 bytes at a time
+            self.recv_sf, self.sf_ptrs, self._h4 = _symm_empty((slots, (nsf + 15) // 16 * 16), torch.uint8, dev)
             self.packed = (self.recv_q, self.recv_sf)
             # the binding wants a [slots, K] bf16 tensor; it is never read on this path
             self.recv_rows = torch.zeros((1, shp.hidden), dtype=torch.bfloat16, device=dev).expand(slots, shp.hidden)

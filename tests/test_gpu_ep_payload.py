@@ -53,8 +53,9 @@ def _setup(recipe):
     return dev, shp, inp, ex, ti, home
 
 
+@pytest.mark.parametrize("pad", [4, 16])       # scale rows padded to 16 bytes go out 16 bytes at a time
 @pytest.mark.parametrize("recipe", ["nvfp4", "w4a8_mx"])
-def test_quantised_dispatch_is_bit_identical_to_bf16_dispatch(recipe):
+def test_quantised_dispatch_is_bit_identical_to_bf16_dispatch(recipe, pad):
     dev, shp, inp, ex, ti, home = _setup(recipe)
     payload = "nvfp4" if recipe == "nvfp4" else "mxfp8"
     cap = slots = shp.tokens * shp.topk
@@ -63,7 +64,7 @@ def test_quantised_dispatch_is_bit_identical_to_bf16_dispatch(recipe):
     status = torch.zeros(16, dtype=torch.int32, device=dev)
     recv_rows = torch.zeros(slots, shp.hidden, dtype=torch.bfloat16, device=dev)
     recv_q = torch.full((slots, row_bytes), 0xFF, dtype=torch.uint8, device=dev)
-    recv_sf = torch.full((slots, (nsf + 3) // 4 * 4), 0xFF, dtype=torch.uint8, device=dev)
+    recv_sf = torch.full((slots, (nsf + pad - 1) // pad * pad), 0xFF, dtype=torch.uint8, device=dev)
     ids_a = torch.full((slots, 1), -7, dtype=torch.int32, device=dev)
     ids_b = torch.full((slots, 1), -7, dtype=torch.int32, device=dev)
     assert _dispatch(home, inp.x, ti, ex, "bf16", recv_rows, None, ids_a, cap, shp.experts, status) == ext.OK
