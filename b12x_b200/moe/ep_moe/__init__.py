@@ -16,6 +16,23 @@ tokens, see ``b12x_b200.moe.ep_peer``.)
     partial = ep_moe.run(binding=binding)
 """
 
-from .api import Binding, Caps, ExpertMap, Plan, bind, is_supported, plan, prepare_expert_map, run
+from ..._lib.meta import OpMeta, Provenance, install_lazy_api
 
-__all__ = ["Caps", "Plan", "Binding", "ExpertMap", "plan", "bind", "run", "prepare_expert_map", "is_supported"]
+META = OpMeta(
+    name="ep_moe",
+    group="moe",
+    api_style="planned",
+    entry_points=("Caps", "Plan", "Binding", "ExpertMap", "plan", "bind", "run", "prepare_expert_map",
+                  "is_supported"),
+    archs=("sm100a",),
+    dtypes=("bf16",),
+    recipes=("nvfp4", "w4a8_mx", "w4a16"),
+    provenance=Provenance(
+        repo="https://github.com/lukealonso/b12x",
+        commit="6627d342",
+        paths=("b12x/moe/ep_moe/",),
+    ),
+    test_path="tests/test_ep_moe_facade.py",
+)
+
+install_lazy_api(globals(), META)

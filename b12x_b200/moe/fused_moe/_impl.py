@@ -12,6 +12,8 @@ module: without the extension every call raises.
 
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 from collections.abc import Mapping, Sequence
 from dataclasses import dataclass, field
@@ -116,6 +118,78 @@ class B12XFP4ExpertWeights:
         for name in ("w1_fp4", "w2_fp4", "w1_blockscale", "w2_blockscale"):
             if not getattr(self, name).is_contiguous():
                 raise ValueError(f"{name} must be contiguous")
+        dev = self.w1_fp4.device
+        for name in ("a1_gscale", "w1_blockscale", "w1_alphas", "a2_gscale", "w2_fp4", "w2_blockscale",
+                     "w2_alphas"):
+            if getattr(self, name).device != dev:
+                raise ValueError(f"{name} is on {getattr(self, name).device}, w1_fp4 on {dev}")
+        for name in ("a1_gscale", "w1_alphas", "a2_gscale", "w2_alphas"):
+            t = getattr(self, name)
+            if t.dtype != torch.float32 or t.numel() != p.num_experts or not t.is_contiguous():
+                raise ValueError(f"{name} must be contiguous float32 with one value per expert")
+        # Every tensor a kernel reads is its own byte range: a package whose FC1 and FC2 weights (or a
+        # weight and a scale tensor) overlap was assembled from views of the wrong buffer
+        ranges = []
+        for name in ("w1_fp4", "w2_fp4", "w1_blockscale", "w2_blockscale"):
+            t = getattr(self, name)
+            lo = t.data_ptr()
+            ranges.append((lo, lo + t.numel() * t.element_size(), name))
+        ranges.sort()
+        for (lo0, hi0, n0), (lo1, _hi1, n1) in zip(ranges[:-1], ranges[1:]):
+            if lo1 < hi0 and hi0 > lo0:
+                raise ValueError(f"{n0} and {n1} overlap in memory")
+        if self.w1_blockscale_rows is not None:
+            r = self.w1_blockscale_rows
+            want = p.num_experts * _align_up(p.w1_rows, 128) * _align_up(p.hidden_size // 16, 4)
+            if r.dtype != torch.uint8 or not r.is_contiguous() or r.numel() != want or r.device != dev:
+                raise ValueError("w1_blockscale_rows must be the contiguous 128x4-swizzled FC1 scale atoms")
+
+    # the plan's facts, as the reference's package exposes them (_impl.py:542-564)
+    @property
+    def source_format(self) -> str:
+        return self.plan.source_format
+
+    @property
+    def w13_layout(self) -> str:
+        return self.plan.w13_layout
+
+    @property
+    def activation(self) -> str:
+        return self.plan.activation
+
+    @property
+    def num_experts(self) -> int:
+        return self.plan.num_experts
+
+    @property
+    def hidden_size(self) -> int:
+        return self.plan.hidden_size
+
+    @property
+    def intermediate_size(self) -> int:
+        return self.plan.intermediate_size
+
+    def keeps_source(self, source: torch.Tensor) -> bool:
+        """True if ``source`` (a tensor handed to ``prepare_weights``) is used where it lies, i.e.
+        the caller must keep it alive and unchanged; False if the package holds its own copy (the
+        re-laid scale atoms, weights re-homed for tail slack) and the source may be freed."""
+        ptr = source.untyped_storage().data_ptr()
+        return any(getattr(self, n) is not None and getattr(self, n).untyped_storage().data_ptr() == ptr
+                   for n in ("w1_fp4", "w2_fp4", "w1_blockscale", "w2_blockscale", "w1_blockscale_rows"))
+
+    def device_nbytes(self) -> int:
+        """Device bytes this package keeps alive, counting each storage once."""
+        seen, total = set(), 0
+        for n in ("a1_gscale", "w1_fp4", "w1_blockscale", "w1_alphas", "a2_gscale", "w2_fp4", "w2_blockscale",
+                  "w2_alphas", "w1_blockscale_rows"):
+            t = getattr(self, n)
+            if t is None:
+                continue
+            st = t.untyped_storage()
+            if st.data_ptr() not in seen:
+                seen.add(st.data_ptr())
+                total += st.nbytes()
+        return total
 
 
 def _expert_vector(t: torch.Tensor, num_experts: int, name: str) -> torch.Tensor:
@@ -139,10 +213,14 @@ def _swizzle_scale_grid(grid: torch.Tensor) -> torch.Tensor:
 
 
 def _unswizzle_scale_grid(sw: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
-    """Inverse of :func:`_swizzle_scale_grid` for one expert: -> [rows, cols] bytes."""
+    """Inverse of :func:`_swizzle_scale_grid`: ``[E, padded atoms]`` (or one expert's atoms) ->
+    ``[E, rows, cols]`` (``[rows, cols]``) bytes, all experts in one pass."""
     rp, cp = _align_up(rows, 128), _align_up(cols, 4)
-    u = sw.reshape(-1)[: rp * cp].reshape(rp // 128, cp // 4, 32, 4, 4).permute(0, 3, 2, 1, 4)
-    return u.contiguous().reshape(rp, cp)[:rows, :cols]
+    single = sw.numel() == rp * cp and (sw.ndim < 3 or sw.shape[0] != 1)
+    e = 1 if single else int(sw.shape[0])
+    u = sw.reshape(e, -1)[:, : rp * cp].reshape(e, rp // 128, cp // 4, 32, 4, 4).permute(0, 1, 4, 3, 2, 5)
+    out = u.contiguous().reshape(e, rp, cp)[:, :rows, :cols]
+    return out[0] if single else out
 
 
 def _pair_scale_atoms(grid: torch.Tensor, intermediate: int, gate_first: bool) -> torch.Tensor:
@@ -258,7 +336,7 @@ def prepare_b12x_fp4_moe_weights(
                 raise ValueError("one weight plan cannot serve both nvfp4 and w4a16: they need "
                                  "different FC1 scale layouts")
             rows, cols = plan.w1_rows, plan.hidden_size // 16
-            grid = torch.stack([_unswizzle_scale_grid(s1[ei], rows, cols) for ei in range(e)])
+            grid = _unswizzle_scale_grid(s1, rows, cols)        # all experts at once
             s1 = _pair_scale_atoms(grid, plan.intermediate_size, plan.w13_layout == "w31")
     return B12XFP4ExpertWeights(
         plan=plan, a1_gscale=a1, w1_fp4=w1_fp4.view(torch.uint8), w1_blockscale=s1.contiguous(),
@@ -719,6 +797,12 @@ def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+_NVTX = os.environ.get("B200MOE_NVTX", "0") == "1"
+_NEXT_STAGE = {"begin": "expert_sort", "sort": "permute_quant", "quant": "grouped_gemm1_act",
+               "gemm1": "grouped_gemm2", "gemm2": "combine"}
+_LAST_STAGE = {(True, False): "gemm2", (True, True): "gemm2", (False, False): "combine", (False, True): "combine"}
+
+
 def b12x_moe_fp4(*, binding: TPMoEFP4Binding, stage_timer=None) -> torch.Tensor:
     """Run the layer for one binding on the current CUDA stream and return ``[tokens, K]``.
 
@@ -754,7 +838,18 @@ def b12x_moe_fp4(*, binding: TPMoEFP4Binding, stage_timer=None) -> torch.Tensor:
     recipe = ext.RECIPES[b.quant_mode]
     act = ext.ACTIVATIONS[_ACT_CODE[b.activation]]
 
-    mark = stage_timer if stage_timer is not None else (lambda _name: None)
+    timer = stage_timer if stage_timer is not None else (lambda _name: None)
+    if _NVTX:
+        # B200MOE_NVTX=1: one NVTX range per stage, so that a timeline profiler shows the layer's
+        # stages by name (the ranges close at the next stage boundary)
+        def mark(name: str) -> None:
+            if name != "begin":
+                torch.cuda.nvtx.range_pop()
+            timer(name)
+            if name != _LAST_STAGE[(b.skip_combine, b.f32_only)]:
+                torch.cuda.nvtx.range_push("b200moe." + _NEXT_STAGE.get(name, "stage"))
+    else:
+        mark = timer
     mark("begin")
     emap = b.route_expert_map
     sw = b.sort_wait or (None, 0, None, None)

@@ -182,7 +182,9 @@ int b200moe_expert_sort(const b200moe_sort_args* a, void* stream);
  * The built-in array is shared by all calls on a GPU and keeps the previous call's contents; the
  * kernel rewrites what it reads, but calls whose kernels can overlap on the GPU race on it.
  * The first call on each device looks up the array's device address: make it before any stream
- * capture, with the device current. */
+ * capture, with the device current.  The address is cached per device and stays valid for the
+ * lifetime of that device's primary context: after cudaDeviceReset (or once the context is
+ * destroyed some other way) the library must be reloaded before the next call. */
 int b200moe_expert_sort_static(const int32_t* topk_ids, const int32_t* expert_map,
                                int32_t expert_map_len, int32_t num_tokens, int32_t num_topk,
                                int32_t num_experts, int32_t* expert_offsets,

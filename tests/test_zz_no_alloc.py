@@ -13,6 +13,7 @@ import pytest
 import torch
 
 from b12x_b200._lib import ext
+from oracle import moe_oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -63,6 +64,10 @@ def test_static_sort_matches_arena_sort_on_two_calls_in_a_row():
         assert torch.equal(got[0], ref[0])
         assert torch.equal(got[1][:kept], ref[1][:kept])
         assert torch.equal(got[2], ref[2])
+        # and against the CPU oracle's canonical sort, not only against the other CUDA entry point
+        srt = O.expert_sort(ids.cpu(), experts, emap)
+        assert torch.equal(got[0].cpu(), srt.expert_offsets)
+        assert torch.equal(got[1][:kept].cpu(), srt.sorted_route_ids) and torch.equal(got[2].cpu(), srt.inv_perm)
     # beyond the fixed maximum: refused with the capacity status, nothing is launched
     dummy = torch.zeros(8, dtype=torch.int32, device="cuda")
     rc = lib.b200moe_expert_sort_static(dummy.data_ptr(), None, 0, 65537, 1, 8, dummy.data_ptr(),
@@ -71,3 +76,22 @@ def test_static_sort_matches_arena_sort_on_two_calls_in_a_row():
     rc = lib.b200moe_expert_sort_static(dummy.data_ptr(), None, 0, 4, 2, 1025, dummy.data_ptr(),
                                         dummy.data_ptr(), dummy.data_ptr(), None)
     assert rc == ext.ECAPACITY
+
+
+@pytest.mark.parametrize("tokens,topk,experts,one_expert", [
+    (8192, 8, 1024, False),      # both limits at once: 65 536 routes over 1 024 experts
+    (65536, 1, 7, True),         # every route to the same expert: one count carries all 65 536
+    (1, 1, 1, False),            # the smallest call
+])
+def test_static_sort_at_its_limits(tokens, topk, experts, one_expert):
+    g = torch.Generator().manual_seed(tokens + experts)
+    if one_expert:
+        ids = torch.full((tokens, topk), 3, dtype=torch.int32)
+    else:
+        ids = torch.randint(0, experts, (tokens, topk), generator=g, dtype=torch.int32)
+    srt = O.expert_sort(ids, experts, None)
+    for _ in range(2):       # the built-in array is reused as the previous call left it
+        offs, order, inv = _static_sort(ids.cuda(), experts, None)
+        assert torch.equal(offs.cpu(), srt.expert_offsets)
+        assert torch.equal(order.cpu(), srt.sorted_route_ids)
+        assert torch.equal(inv.cpu(), srt.inv_perm)
