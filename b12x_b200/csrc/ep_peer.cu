@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
       if (b < nblk) dst[b] = __ldg(src + b);
     } else if constexpr (PAYLOAD == 1) {
       const float gs = a1_gscale[gscale_len == 1 ? 0 : expert];
+      const float rgs = __frcp_rn(gs);
       uint2* dst = reinterpret_cast<uint2*>(static_cast<uint8_t*>(rows.p[d]) + static_cast<size_t>(slot) * (K >> 1));
       uint8_t* dsf = static_cast<uint8_t*>(sfs.p[d]) + static_cast<size_t>(slot) * sf_row_stride;
       uint8_t sfb = 0;
@@ -111,7 +112,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
         bf16x8_to_f32(__ldg(src + 2 * b), v);
         bf16x8_to_f32(__ldg(src + 2 * b + 1), v + 8);
         uint32_t lo, hi;
-        quant_block16(v, gs, lo, hi, sfb);
+        quant_block16(v, gs, rgs, lo, hi, sfb);
         dst[b] = make_uint2(lo, hi);
       }
       // four neighbouring lanes hold the four scale bytes of one 32-bit word

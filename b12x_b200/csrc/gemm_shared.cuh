@@ -2,7 +2,7 @@
 // decoder, the epilogue arithmetic and the host-side tensor-map helpers.
 #pragma once
 
-#include "common.cuh"
+#include "quant_shared.cuh"
 
 namespace b200moe {
 
@@ -65,27 +65,6 @@ __device__ __forceinline__ TileCoord decode_tile(int w, int n_tiles, const int32
   return c;
 }
 
-// Branch-free reciprocal and division for the epilogues (a call with a slow-path branch per
-// element keeps the compiler from interleaving the 16 independent element chains of a chunk).
-__device__ __forceinline__ float rcp_approx(float x) {
-  float r;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
-  return r;
-}
-// 1/x for normal x: hardware approximation + one Newton step (error <= 0.5 ulp + 2^-46)
-__device__ __forceinline__ float rcp_newton(float x) {
-  const float r = rcp_approx(x);
-  return __fmaf_rn(r, __fmaf_rn(-x, r, 1.0f), r);
-}
-// a / b, correctly rounded when the quotient is a normal number or zero; rb = RN(1 / b).
-// Two residual corrections with exact fma residuals (Markstein).
-__device__ __forceinline__ float div_rn_normal(float a, float b, float rb) {
-  float q = __fmul_rn(a, rb);
-  q = __fmaf_rn(__fmaf_rn(-b, q, a), rb, q);
-  q = __fmaf_rn(__fmaf_rn(-b, q, a), rb, q);
-  return q;
-}
-
 // SiTU (b12x/moe/_shared/kernels/reference.py:160-172): 4 tanh(g / 4) sigmoid(g) * 25 tanh(u / 25)
 constexpr float kSituBeta = 4.0f, kSituLinearBeta = 25.0f;
 
@@ -116,44 +95,6 @@ __device__ __forceinline__ float act_gated(float gate, float up, const GemmParam
 
 __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
-}
-
-// Same arithmetic as quant_block16 in the activation quantiser, with a cheap common path: the
-// quotient x / denom is first approximated by x * rcp(denom) (error < 2 ulp); if the values 2^-21
-// below and above it round to the same E2M1 code, the correctly rounded quotient does too.
-// Only a block with a value that close to a rounding boundary takes the exact division.
-// `rgs` = RN(1 / gs), computed once per tile.
-__device__ __forceinline__ void requant_block16(const float (&v)[16], float gs, float rgs, uint32_t& lo,
-                                                uint32_t& hi, uint8_t& sf_byte) {
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  const float raw = fminf(div_rn_normal(__fmul_rn(amax, gs), 6.0f, 0.16666667163372039794921875f), 448.0f);
-  sf_byte = f32_to_e4m3_rn_sat(raw);
-  const float sf = e4m3_to_f32(sf_byte);
-  const float denom = fmaxf(div_rn_normal(sf, gs, rgs), 1e-30f);
-  const float r = rcp_approx(denom);
-  float a0[8], a1[8], b0[8], b1[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float q0 = __fmul_rn(v[i], r), q1 = __fmul_rn(v[8 + i], r);
-    a0[i] = __fmul_rn(q0, 1.0f - 4.76837158e-7f);
-    b0[i] = __fmul_rn(q0, 1.0f + 4.76837158e-7f);
-    a1[i] = __fmul_rn(q1, 1.0f - 4.76837158e-7f);
-    b1[i] = __fmul_rn(q1, 1.0f + 4.76837158e-7f);
-  }
-  lo = pack_e2m1x8(a0);
-  hi = pack_e2m1x8(a1);
-  if (lo != pack_e2m1x8(b0) || hi != pack_e2m1x8(b1)) {
-    float q0[8], q1[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      q0[i] = __fdiv_rn(v[i], denom);
-      q1[i] = __fdiv_rn(v[8 + i], denom);
-    }
-    lo = pack_e2m1x8(q0);
-    hi = pack_e2m1x8(q1);
-  }
 }
 
 // MXFP8 quantisation of 32 values (b12x/_lib/intrinsics.py:223-265): E8M0 byte = exponent of
@@ -276,7 +217,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, int e, int mt
         }
         uint32_t lo, hi;
         uint8_t sfb;
-        requant_block16(h, gs2, rgs2, lo, hi, sfb);
+        quant_block16(h, gs2, rgs2, lo, hi, sfb);
         if (valid && cols_ok) *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
         sfw |= static_cast<uint32_t>(sfb) << (8 * ch);
       }
@@ -329,7 +270,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, int e, int mt
           }
           uint32_t lo, hi;
           uint8_t sfb;
-          requant_block16(h, gs2, rgs2, lo, hi, sfb);
+          quant_block16(h, gs2, rgs2, lo, hi, sfb);
           if (valid && col0 + ch * 16 < p.out_cols)
             *reinterpret_cast<uint2*>(qrow + ch * 8) = make_uint2(lo, hi);
           sfw[ch >> 2] |= static_cast<uint32_t>(sfb) << (8 * (ch & 3));

@@ -16,6 +16,7 @@ __global__ void __launch_bounds__(256) permute_quant_nvfp4_kernel(
   const int row0 = mtile_row0[mt];
   const int nrows = mtile_rows[mt];
   const float gs = gscale[gscale_len > 1 ? e : 0];
+  const float rgs = __frcp_rn(gs);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nblk = K >> 4;                    // 16-element blocks per row
   const int atoms = (nblk + 3) >> 2;          // 512-byte scale atoms per tile
@@ -46,7 +47,7 @@ __global__ void __launch_bounds__(256) permute_quant_nvfp4_kernel(
           v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
         }
         uint32_t lo, hi;
-        quant_block16(v, gs, lo, hi, sfb);
+        quant_block16(v, gs, rgs, lo, hi, sfb);
         dst[b] = make_uint2(lo, hi);
       }
       // four neighbouring lanes hold the four scales of one 32-bit word of the atom
@@ -358,7 +359,8 @@ extern "C" int b200moe_permute_quant_nvfp4(const b200moe_quant_args* a, void* st
   // CTAs to fill the GPU about four times.  Large batches: one warp per row, four CTAs per tile.
   const int gx = mtiles < L.mtile_cap ? mtiles : L.mtile_cap;
   const bool large = rows >= 2048 && L.tile_rows != 64;   // a 64-row plan expects few rows per expert
-  int gy = large ? 4 : (4 * 148 + gx - 1) / gx;
+  // (large: 16 CTAs per tile keep enough loads in flight; 4 ran the Mixtral shape at 0.064 ms, 16 at 0.051 ms)
+  int gy = large ? 16 : (4 * 148 + gx - 1) / gx;
   gy = gy < 1 ? 1 : (gy > 16 ? 16 : gy);
   const int wpr_cap = large ? 1 : 8;
   const dim3 grid(gx, gy);

@@ -142,6 +142,11 @@ def split_counts_exchange(send_counts: torch.Tensor, group=None) -> torch.Tensor
     return recv
 
 
+def sort_launches(routes: int) -> int:
+    """Kernels of one expert sort: one CTA up to 16 383 routes, count / scan / scatter above."""
+    return 3 if routes >= 16384 else 1
+
+
 class _LayerBase:
     kernels_per_step = 6
 
@@ -319,6 +324,8 @@ class ExpertParallelMoE(_LayerBase):
         t, k = shp.tokens, shp.topk
         if world == 1:
             self.plan, self.scratch = self._local_plan(t, k)
+            # route, sort, quantise (w4a16: row gather), FC1, FC2, combine
+            self.kernels_per_step = 5 + sort_launches(t * k)
             return
         # home side: sort routes by destination rank, pack rows, later combine returned rows
         self.home = StageArena(t, k, world, shp.hidden, dev)
@@ -445,7 +452,7 @@ class TensorParallelMoE(_LayerBase):
         self.local_shape = replace(shp, intermediate=inputs.w2_fp4.shape[2] * 2)
         self.plan, self.scratch = self._local_plan(shp.tokens, shp.topk)
         self.partial = torch.empty((shp.tokens, shp.hidden), dtype=torch.float32, device=dev)
-        self.kernels_per_step = 6
+        self.kernels_per_step = 5 + sort_launches(shp.tokens * shp.topk)
 
     @classmethod
     def from_synthetic(cls, shp: synth.MoEShape, dev, rank: int, world: int):

@@ -29,7 +29,7 @@ import torch.distributed as dist
 from .. import synth
 from .._lib import ext
 from . import fused_moe
-from .distributed import _LayerBase, prepare_experts
+from .distributed import _LayerBase, prepare_experts, sort_launches
 from .fused_moe.stages import StageArena
 
 
@@ -92,9 +92,10 @@ class PeerExpertParallelMoE(_LayerBase):
         self.home = StageArena(t, k, world, shp.hidden, dev)
         self.rank_of_expert = (torch.arange(shp.experts, dtype=torch.int32, device=dev) // self.e_local).contiguous()
         # the two cross-rank waits of a step ride inside the expert sort and the combine kernel
-        # (9 launches per step) unless B200MOE_FOLD_WAITS=0 makes them launches of their own (12)
+        # unless B200MOE_FOLD_WAITS=0 makes them three launches of their own
         self.fold_waits = os.environ.get("B200MOE_FOLD_WAITS", "1") == "1"
-        self.kernels_per_step = 9 if self.fold_waits else 12
+        # route, home sort, dispatch, expert sort, file / quantise rows, FC1, FC2, combine (+ wait, signal, wait)
+        self.kernels_per_step = 6 + sort_launches(t * k) + sort_launches(slots) + (0 if self.fold_waits else 3)
         # what crosses the link per route: the row quantised on this rank (the recipe's activation
         # format) or, for recipes whose GEMM reads bf16 rows, the row as it is
         self.payload = payload or os.environ.get("B200MOE_EP_PAYLOAD") or _PAYLOAD_OF_RECIPE[shp.recipe]
@@ -135,7 +136,10 @@ class PeerExpertParallelMoE(_LayerBase):
         core = self.plan._core_layout
         self._inv_perm_off = self.plan.layout.route_workspace_nbytes + int(core.inv_perm)
         self._routed_off = self.plan.layout.route_workspace_nbytes + int(core.routed)
-        self.home_status = self.home._view("status", 16, torch.int32)
+        # Status words of the cross-rank waits and of the receive-capacity check.  A buffer of its own,
+        # which no kernel clears (the sorts zero the status words of their arenas at every step): an
+        # expiry in step n is still there when check_status() is called after step n + 100.
+        self.home_status = torch.zeros(16, dtype=torch.int32, device=dev)
         # the senders quantise with the destination expert's input scale: every rank holds all of them
         gs = experts.a1_gscale.reshape(-1).float()
         gs = gs.expand(self.e_local).contiguous() if gs.numel() == 1 else gs.contiguous()

@@ -46,7 +46,9 @@ from b12x_b200 import synth  # noqa: E402
 # DRAM bytes per FC1 launch of the decode shape: an ncu capture of its 32-expert case read 1.014 x
 # the algorithmic bytes (dram__bytes_read + write; summary under profiles/); every active expert's
 # weights are read once per launch, so the traffic scales with the algorithmic bytes
-NCU_FC1_TRAFFIC_RATIO = {"c2_dsv3_decode_nvfp4": 1.014}
+# (c4: the 2048-token case read 538 + 35 MB against 528 MB of weights + 9.4 MB of token codes + 33 MB of
+# intermediate codes and scales = 1.005 x algorithmic; more tokens add row bytes one for one)
+NCU_FC1_TRAFFIC_RATIO = {"c2_dsv3_decode_nvfp4": 1.014, "c4_mixtral_skew_nvfp4": 1.005}
 # experts of the CPU-baseline sample: a pass over them takes a few seconds on 16 cores
 CPU_EXPERTS = {"c1": 8, "c2": 8, "c3": 8, "c4": 4, "c5": 8}
 PARITY_EXPERTS = 4
@@ -401,7 +403,7 @@ def run_workload(key, shp, args, dev, rank, world, sampler, *, steps, warmup) ->
         achieved = dom["flops"] / (dom_ms * 1e-3) / 1e12
         peak, unit = peaks["bf16_tflops"] * rate, "TFLOP/s"
     ratio = NCU_FC1_TRAFFIC_RATIO.get(shp.name)
-    traffic = dom["bytes"] * ratio if (ratio is not None and dom["bound"] == "hbm") else None
+    traffic = dom["bytes"] * ratio if ratio is not None else None
     rec = {
         "value": total_tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
         "scaling": "strong" if tp else "weak", "dtype": dtype_of(shp),

@@ -117,6 +117,14 @@ def _capacity_worker(rank: int, world: int, port: int, ret: dict):
             ok = False
         except RuntimeError as e:
             ok = ok and "rank 0 was sent more rows than its receive capacity" in str(e)
+        # the status words are sticky: a later good step does not hide the failed one
+        tight.forward(x, lg)
+        torch.cuda.synchronize()
+        try:
+            tight.check_status()
+            ok = False
+        except RuntimeError:
+            pass
         dist.barrier()
         ret[rank] = ok
     finally:
