@@ -356,7 +356,7 @@ extern "C" int b200moe_permute_quant_nvfp4(const b200moe_quant_args* a, void* st
   const int mtiles = (rows + tr - 1) / tr + (a->num_experts < rows ? a->num_experts : rows);
   // tiles of a decode batch hold few rows: one CTA per tile; large batches: 4 CTAs per tile
   // Small batches: the eight warps of a CTA share a row and a tile's rows are spread over enough
-  // CTAs to fill the GPU about four times.  Large batches: one warp per row, four CTAs per tile.
+  // CTAs to fill the GPU about four times.  Large batches: one warp per row, sixteen CTAs per tile.
   const int gx = mtiles < L.mtile_cap ? mtiles : L.mtile_cap;
   const bool large = rows >= 2048 && L.tile_rows != 64;   // a 64-row plan expects few rows per expert
   // (large: 16 CTAs per tile keep enough loads in flight; 4 ran the Mixtral shape at 0.064 ms, 16 at 0.051 ms)
