@@ -118,7 +118,7 @@ class EpDispatchArgs(C.Structure):
                 ("hidden_size", C.c_int32), ("local_modulus", C.c_int32), ("cap_rows", C.c_int32),
                 ("epoch", C.c_int32), ("payload", C.c_int32), ("sf_row_stride", C.c_int32),
                 ("gscale_len", C.c_int32), ("reserved", C.c_int32), ("peer_sf", PeerArray),
-                ("a1_gscale", C.c_void_p), ("status", C.c_void_p)]
+                ("a1_gscale", C.c_void_p), ("status", C.c_void_p), ("local_ids", C.c_void_p)]
 
 
 EP_PAYLOADS = {"bf16": 0, "nvfp4": 1, "mxfp8": 2}
@@ -167,6 +167,8 @@ EXPORTS = {
     "b200moe_combine": ([C.POINTER(CombineArgs), C.c_void_p], C.c_int),
     "b200moe_ep_dispatch": ([C.POINTER(EpDispatchArgs), C.c_void_p], C.c_int),
     "b200moe_permute_packed": ([C.POINTER(PackedArgs), C.c_void_p], C.c_int),
+    "b200moe_ep_place_routes": ([C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                 C.c_void_p], C.c_int),
     "b200moe_ep_signal": ([C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p], C.c_int),
     "b200moe_ep_wait": ([C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p], C.c_int),
     "b200moe_ep_combine": ([C.POINTER(EpCombineArgs), C.c_void_p], C.c_int),

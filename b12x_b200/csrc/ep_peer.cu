@@ -61,7 +61,8 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
     const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, const int32_t* __restrict__ topk_ids,
     const int32_t* __restrict__ group_offsets, const int32_t* __restrict__ sorted_route_ids,
     PeerPtrs rows, PeerPtrs sfs, PeerPtrs ids, PeerPtrs flags, const float* __restrict__ a1_gscale,
-    int gscale_len, int sf_row_stride, int32_t* done_counter, int32_t* __restrict__ status, int world,
+    const int32_t* __restrict__ local_ids, int gscale_len, int sf_row_stride, int32_t* done_counter,
+    int32_t* __restrict__ status, int world,
     int rank, int num_topk, int K, int local_modulus, int cap, int epoch_arg, int32_t* epoch_dev) {
   // Epoch kept on the device (a captured CUDA graph replays with fixed arguments): this step is
   // *epoch_dev + 1.  Every block reads it on entry; the last block out stores it back after all
@@ -140,7 +141,8 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
       word |= __shfl_down_sync(0xffffffffu, static_cast<uint32_t>(sfb), 3) << 24;
       store_scale_words(dsf, b, nblk, word, lane, sf_row_stride);
     }
-    if (lane == 0 && b == 0) static_cast<int32_t*>(ids.p[d])[slot] = expert % local_modulus;
+    if (lane == 0 && b == 0)
+      static_cast<int32_t*>(ids.p[d])[slot] = local_ids != nullptr ? local_ids[r] : expert % local_modulus;
   }
   // unused slots of this rank's region on every peer: no route
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < world * cap; i += gridDim.x * blockDim.x) {
@@ -158,6 +160,22 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
       __threadfence_system();
       for (int d = 0; d < world; ++d) st_release_sys(static_cast<int32_t*>(flags.p[d]) + rank, epoch);
     }
+  }
+}
+
+// Replicated experts: route i to expert e goes to holder pattern[e][i % 16] of that expert -- a
+// (rank, local expert slot) pair.  An expert held by one rank has sixteen equal entries; a hot
+// expert copied to other ranks spreads its routes over its holders in sixteenths.
+__global__ void ep_place_routes_kernel(const int32_t* __restrict__ topk_ids, int n, int num_experts,
+                                       const int32_t* __restrict__ pattern_rank,
+                                       const int32_t* __restrict__ pattern_local,
+                                       int32_t* __restrict__ dest_rank, int32_t* __restrict__ dest_local) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int e = topk_ids[i];
+    const bool ok = e >= 0 && e < num_experts;
+    const int j = e * 16 + (i & 15);
+    dest_rank[i] = ok ? pattern_rank[j] : -1;
+    dest_local[i] = ok ? pattern_local[j] : -1;
   }
 }
 
@@ -337,7 +355,7 @@ static void launch_dispatch(const b200moe_ep_dispatch_args* a, const PeerPtrs& r
       static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride, a->topk_ids,
       reinterpret_cast<const int32_t*>(base + L.expert_offsets),
       reinterpret_cast<const int32_t*>(base + L.sorted_route_ids), rows_p, sf_p, ids_p, flags_p,
-      a->a1_gscale, a->gscale_len, a->sf_row_stride, a->done_counter, a->status, a->world, a->rank,
+      a->a1_gscale, a->local_ids, a->gscale_len, a->sf_row_stride, a->done_counter, a->status, a->world, a->rank,
       a->num_topk, a->hidden_size, a->local_modulus, a->cap_rows, a->epoch, a->epoch_dev);
 }
 
@@ -375,6 +393,20 @@ extern "C" int b200moe_ep_dispatch(const b200moe_ep_dispatch_args* a, void* stre
   if (a->payload == B200MOE_EP_PAYLOAD_NVFP4) launch_dispatch<1>(a, rows_p, sf_p, ids_p, flags_p, grid, st);
   else if (a->payload == B200MOE_EP_PAYLOAD_MXFP8) launch_dispatch<2>(a, rows_p, sf_p, ids_p, flags_p, grid, st);
   else launch_dispatch<0>(a, rows_p, sf_p, ids_p, flags_p, grid, st);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
+extern "C" int b200moe_ep_place_routes(const int32_t* topk_ids, int32_t num_routes, int32_t num_experts,
+                                       const int32_t* pattern_rank, const int32_t* pattern_local,
+                                       int32_t* dest_rank, int32_t* dest_local, void* stream) {
+  if (topk_ids == nullptr || pattern_rank == nullptr || pattern_local == nullptr || dest_rank == nullptr ||
+      dest_local == nullptr || num_routes < 0 || num_experts <= 0)
+    return B200MOE_EINVAL;
+  if (num_routes == 0) return B200MOE_OK;
+  int grid = (num_routes + 255) / 256;
+  grid = grid > 148 * 4 ? 148 * 4 : grid;
+  ep_place_routes_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      topk_ids, num_routes, num_experts, pattern_rank, pattern_local, dest_rank, dest_local);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 

@@ -31,6 +31,7 @@ from .._lib import ext
 from . import fused_moe
 from .distributed import _LayerBase, prepare_experts, sort_launches
 from .fused_moe.stages import StageArena
+from .placement import plan_expert_replicas
 
 
 def _symm_empty(shape, dtype, device):
@@ -71,13 +72,31 @@ class PeerExpertParallelMoE(_LayerBase):
     kernels_per_step = 12
 
     def __init__(self, shp, inputs, experts, dev, rank: int, world: int, *,
-                 recv_capacity_factor: float | None = None, payload: str | None = None):
+                 recv_capacity_factor: float | None = None, payload: str | None = None,
+                 replica_slots: int = 0, calibration_logits: torch.Tensor | None = None):
         super().__init__(shp, inputs, experts, dev, rank, world)
         if world < 2 or world > ext.MAX_RANKS:
             raise ValueError(f"needs 2..{ext.MAX_RANKS} ranks")
         if shp.experts % world:
             raise ValueError("experts must divide evenly over the ranks")
         self.e_local = shp.experts // world
+        # Spare expert slots against skewed routing: hot experts are copied into cold ranks' spare
+        # slots (placement from the routing of a calibration batch) and their routes spread over
+        # the holders.  Every holder computes the same bytes, so the output does not change.
+        self.replicas = None
+        gs_own = experts.a1_gscale.reshape(-1).float()
+        if replica_slots > 0:
+            loads = self._measure_loads(inputs.router_logits if calibration_logits is None else calibration_logits)
+            self.replicas = plan_expert_replicas(loads, world, int(replica_slots))
+            inputs = self._with_replica_weights(inputs, self.replicas)
+            experts = prepare_experts(inputs, dev)
+            self.inputs, self.experts = inputs, experts
+            pr, pl = self.replicas.pattern_tables()
+            self.pattern_rank = torch.tensor(pr, dtype=torch.int32, device=dev)
+            self.pattern_local = torch.tensor(pl, dtype=torch.int32, device=dev)
+            self.dest_rank = torch.empty((shp.tokens, shp.topk), dtype=torch.int32, device=dev)
+            self.dest_local = torch.empty((shp.tokens, shp.topk), dtype=torch.int32, device=dev)
+        self.n_local = self.e_local + (int(replica_slots) if self.replicas is not None else 0)
         t, k = shp.tokens, shp.topk
         # Slots one source rank owns in every receive buffer.  Worst case (every route of a rank
         # to one destination) by default; with a capacity factor f, f x the balanced share
@@ -95,7 +114,8 @@ class PeerExpertParallelMoE(_LayerBase):
         # unless B200MOE_FOLD_WAITS=0 makes them three launches of their own
         self.fold_waits = os.environ.get("B200MOE_FOLD_WAITS", "1") == "1"
         # route, home sort, dispatch, expert sort, file / quantise rows, FC1, FC2, combine (+ wait, signal, wait)
-        self.kernels_per_step = 6 + sort_launches(t * k) + sort_launches(slots) + (0 if self.fold_waits else 3)
+        self.kernels_per_step = (6 + sort_launches(t * k) + sort_launches(slots) + (0 if self.fold_waits else 3)
+                                 + (1 if self.replicas is not None else 0))
         # what crosses the link per route: the row quantised on this rank (the recipe's activation
         # format) or, for recipes whose GEMM reads bf16 rows, the row as it is
         self.payload = payload or os.environ.get("B200MOE_EP_PAYLOAD") or _PAYLOAD_OF_RECIPE[shp.recipe]
@@ -141,8 +161,7 @@ class PeerExpertParallelMoE(_LayerBase):
         # expiry in step n is still there when check_status() is called after step n + 100.
         self.home_status = torch.zeros(16, dtype=torch.int32, device=dev)
         # the senders quantise with the destination expert's input scale: every rank holds all of them
-        gs = experts.a1_gscale.reshape(-1).float()
-        gs = gs.expand(self.e_local).contiguous() if gs.numel() == 1 else gs.contiguous()
+        gs = gs_own.expand(self.e_local).contiguous() if gs_own.numel() == 1 else gs_own.contiguous()
         if gs.numel() != self.e_local:
             raise ValueError("a1_gscale must hold one value or one per local expert")
         parts = [torch.empty_like(gs) for _ in range(world)]
@@ -150,6 +169,37 @@ class PeerExpertParallelMoE(_LayerBase):
         self.a1_gscale_all = torch.cat(parts).contiguous()
         torch.cuda.synchronize(dev)
         dist.barrier()
+
+    def _measure_loads(self, logits: torch.Tensor) -> list:
+        """COLLECTIVE: routes per global expert over all ranks' calibration batches."""
+        self.route(logits.to(self.dev))
+        counts = torch.bincount(self.topk_ids.reshape(-1).long().clamp(0, self.shape.experts - 1),
+                                minlength=self.shape.experts).to(torch.float32)
+        dist.all_reduce(counts)
+        return counts.cpu().tolist()
+
+    def _with_replica_weights(self, inputs, plan):
+        """COLLECTIVE: the local problem with ``slots_per_rank`` more experts appended -- the weights of
+        the experts this rank holds copies of, broadcast from their owners (unused spare slots repeat
+        the rank's first expert; no route goes there)."""
+        names = ("w1_fp4", "w1_blockscale", "w1_global_scale", "w2_fp4", "w2_blockscale", "w2_global_scale",
+                 "a1_gscale", "a2_gscale")
+        own = {n: getattr(inputs, n).to(self.dev) for n in names}
+        got: dict = {n: [] for n in names}
+        for holder in range(self.world):
+            for e in plan.extra[holder]:
+                owner, idx = divmod(e, self.e_local)
+                for n in names:
+                    t = own[n][idx:idx + 1].contiguous().clone()
+                    raw = t.view(torch.uint8) if t.element_size() == 1 else t
+                    dist.broadcast(raw, src=owner)
+                    if holder == self.rank:
+                        got[n].append(t)
+        out = {}
+        for n in names:
+            pad = [own[n][0:1]] * (plan.slots_per_rank - len(got[n]))
+            out[n] = torch.cat([own[n]] + got[n] + pad, dim=0).contiguous()
+        return replace(inputs, **out)
 
     def check_status(self) -> None:
         super().check_status()
@@ -203,7 +253,14 @@ class PeerExpertParallelMoE(_LayerBase):
         self.last_x = x
         self.route(logits)
         mark("route")
-        home.sort(self.topk_ids, self.rank_of_expert)
+        if self.replicas is not None:
+            ext.check(lib.b200moe_ep_place_routes(
+                self.topk_ids.data_ptr(), self.topk_ids.numel(), shp.experts, self.pattern_rank.data_ptr(),
+                self.pattern_local.data_ptr(), self.dest_rank.data_ptr(), self.dest_local.data_ptr(), stream),
+                "ep_place_routes")
+            home.sort(self.dest_rank, None)
+        else:
+            home.sort(self.topk_ids, self.rank_of_expert)
         mark("home_sort")
         d = ext.EpDispatchArgs(
             x.data_ptr(), self.topk_ids.data_ptr(), ext.peer_array(self.rows_ptrs),
@@ -211,7 +268,8 @@ class PeerExpertParallelMoE(_LayerBase):
             self.epoch_dev.data_ptr(), home.scratch.data_ptr(), C.pointer(home.layout), x.stride(0), x.shape[0], shp.topk, world, rank,
             shp.hidden, self.e_local, self.cap, 0, ext.EP_PAYLOADS[self.payload],
             0 if self.recv_sf is None else int(self.recv_sf.shape[1]), int(self.a1_gscale_all.numel()), 0,
-            ext.peer_array(self.sf_ptrs), self.a1_gscale_all.data_ptr(), self.home_status.data_ptr())
+            ext.peer_array(self.sf_ptrs), self.a1_gscale_all.data_ptr(), self.home_status.data_ptr(),
+            None if self.replicas is None else self.dest_local.data_ptr())
         ext.check(lib.b200moe_ep_dispatch(C.byref(d), stream), "ep_dispatch")
         mark("dispatch")
         ep = self.epoch_dev.data_ptr()
@@ -251,5 +309,5 @@ class PeerExpertParallelMoE(_LayerBase):
         counts = self.last_binding.expert_counts.cpu()
         active = int((counts > 0).sum())
         rows = int(counts.sum())
-        local = replace(self.shape, experts=self.e_local)
+        local = replace(self.shape, experts=self.n_local)
         return {"dominant": self._dominant(local, active, rows), "active_experts": active, "rows": rows}

@@ -296,7 +296,9 @@ def make_layer(shp, dev, rank, world, ep):
     if world > 1 and ep == "peer":
         # dispatch / combine by this library's kernels over NVLink peer memory
         from b12x_b200.moe.ep_peer import PeerExpertParallelMoE
-        return PeerExpertParallelMoE.from_synthetic(shp, dev, rank, world)
+        # skewed routing: one spare expert slot per rank, filled with copies of the hot experts
+        return PeerExpertParallelMoE.from_synthetic(shp, dev, rank, world,
+                                                    replica_slots=1 if shp.zipf_s > 0 else 0)
     return ExpertParallelMoE.from_synthetic(shp, dev, rank, world)
 
 
@@ -407,7 +409,10 @@ def run_workload(key, shp, args, dev, rank, world, sampler, *, steps, warmup) ->
     rec = {
         "value": total_tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
         "scaling": "strong" if tp else "weak", "dtype": dtype_of(shp),
-        "config": config_of(shp, world, args.ep, graph is not None), "clocks": clocks,
+        "config": dict(config_of(shp, world, args.ep, graph is not None),
+                       **({"replicated_experts": {"spare_slots_per_rank": layer.replicas.slots_per_rank,
+                                                  "copies": [list(x) for x in layer.replicas.extra]}}
+                          if getattr(layer, "replicas", None) is not None else {})), "clocks": clocks,
         "e2e": {"value": total_tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": x_host.numel() * 2 + lg_host.numel() * 4,
                 "d2h_bytes_per_step": out_host.numel() * 2},

@@ -325,11 +325,24 @@ typedef struct {
    * region is not sent; the kernel then writes status[0] = 1, status[1] = 48 + destination rank.
    * Required when cap_rows < T*k. */
   int32_t* status;
+  /* Optional [T*k]: the destination-local expert id of every route (replicated experts, see
+   * b200moe_ep_place_routes); NULL = topk_ids[route] % local_modulus. */
+  const int32_t* local_ids;
 } b200moe_ep_dispatch_args;
 enum { B200MOE_EP_PAYLOAD_BF16 = 0, B200MOE_EP_PAYLOAD_NVFP4 = 1, B200MOE_EP_PAYLOAD_MXFP8 = 2 };
 /* Pack rows by destination rank, store them and their local expert ids into the peers' receive
  * buffers, mark this rank's unused slots with -1, then raise peer_flags[d][rank] = epoch. */
 int b200moe_ep_dispatch(const b200moe_ep_dispatch_args* a, void* stream);
+
+/* Expert replication against skewed routing: a hot expert's weights are also held by other ranks,
+ * and its routes are spread over the holders.  pattern_rank / pattern_local are [num_experts][16]:
+ * route i (flat index) to expert e goes to rank pattern_rank[e][i % 16], where the expert is local
+ * id pattern_local[e][i % 16].  Writes dest_rank[i] (the key of the sort by destination; -1 for an
+ * id outside [0, num_experts)) and dest_local[i] (b200moe_ep_dispatch_args.local_ids).  Every copy
+ * of an expert computes the same bytes, so the layer's result does not depend on the placement. */
+int b200moe_ep_place_routes(const int32_t* topk_ids, int32_t num_routes, int32_t num_experts,
+                            const int32_t* pattern_rank, const int32_t* pattern_local,
+                            int32_t* dest_rank, int32_t* dest_local, void* stream);
 
 /* Expert side of a quantised dispatch: act_q[pos] = q_rows[sorted_route_ids[pos]] and the scale
  * bytes of that slot filed into the 128x4 scale atoms of the row's tile -- exactly what

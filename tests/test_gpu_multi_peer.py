@@ -18,7 +18,8 @@ from tests.test_gpu_multi import _free_port
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank: int, world: int, port: int, fold: str, ret: dict, recipe: str = "nvfp4", payload: str | None = None):
+def _worker(rank: int, world: int, port: int, fold: str, ret: dict, recipe: str = "nvfp4", payload: str | None = None,
+            replica_slots: int = 0):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       B200MOE_FOLD_WAITS=fold, NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -31,12 +32,19 @@ def _worker(rank: int, world: int, port: int, fold: str, ret: dict, recipe: str 
     try:
         tpr = 40
         if recipe == "nvfp4":
-            shp = synth.shape("c1", name="ep", tokens=tpr * world, hidden=512, intermediate=256, experts=8, topk=3)
+            shp = synth.shape("c1", name="ep", tokens=tpr * world, hidden=512, intermediate=256, experts=8, topk=3,
+                              zipf_s=1.2 if replica_slots else 0.0)
         else:   # 18 scale bytes per row: the last scale word of a row is half padding
             shp = synth.shape("c5", name="ep_mx", tokens=tpr * world, hidden=576, intermediate=320, experts=8, topk=3)
         full = synth.make_inputs(shp, seed=41)
-        layer = PeerExpertParallelMoE.from_global(full, dev, rank, world, tpr, payload=payload)
+        layer = PeerExpertParallelMoE.from_global(full, dev, rank, world, tpr, payload=payload,
+                                                  replica_slots=replica_slots)
         ok = True
+        if replica_slots:
+            # the skewed calibration batch must have put copies of hot experts on other ranks, and the
+            # planned loads must be flatter than the owners' loads
+            plan = layer.replicas
+            ok = any(len(x) > 0 for x in plan.extra) and layer.n_local == shp.experts // world + replica_slots
         for step in range(3):                 # new tokens every step: slots and flags are reused
             g = torch.Generator().manual_seed(100 + step)
             xs = torch.randn(tpr * world, shp.hidden, generator=g).to(torch.bfloat16)
@@ -164,3 +172,17 @@ def test_receive_capacity_factor_and_overflow_status():
         ret = mgr.dict()
         mp.spawn(_capacity_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.timeout(900)
+def test_replicated_hot_experts_do_not_change_the_result(world):
+    """Spare expert slots filled from a Zipf-skewed calibration batch: routes of the hot experts are
+    spread over their holders, and the output still equals the single-process oracle (every holder
+    computes the same bytes for a route)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker, args=(world, _free_port(), "1", ret, "nvfp4", None, 1), nprocs=world, join=True)
+        assert dict(ret) == {r: True for r in range(world)}
