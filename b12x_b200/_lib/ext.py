@@ -167,6 +167,7 @@ EXPORTS = {
     "b200moe_combine": ([C.POINTER(CombineArgs), C.c_void_p], C.c_int),
     "b200moe_ep_dispatch": ([C.POINTER(EpDispatchArgs), C.c_void_p], C.c_int),
     "b200moe_permute_packed": ([C.POINTER(PackedArgs), C.c_void_p], C.c_int),
+    "b200moe_round_rows_bf16": ([C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p], C.c_int),
     "b200moe_ep_place_routes": ([C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_void_p], C.c_int),
     "b200moe_ep_signal": ([C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p], C.c_int),

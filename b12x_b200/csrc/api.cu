@@ -3,8 +3,9 @@
 #include "common.cuh"
 
 namespace b200moe {
-int nvfp4_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
-int nvfp4_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
+int nvfp4_gemm1(const b200moe_gemm_args* a, cudaStream_t stream, int tile_mode);
+int nvfp4_gemm2(const b200moe_gemm_args* a, cudaStream_t stream, int tile_mode);
+bool tail_split(const b200moe_gemm_args* a);
 bool nvfp4_small_batch_ok(const b200moe_gemm_args* a, bool fc1);
 int nvfp4_small_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
 int nvfp4_small_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
@@ -13,8 +14,8 @@ int nvfp4_pair_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
 int nvfp4_pair_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
 int mx_pair_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
 int mx_pair_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
-int mx_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
-int mx_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
+int mx_gemm1(const b200moe_gemm_args* a, cudaStream_t stream, int tile_mode);
+int mx_gemm2(const b200moe_gemm_args* a, cudaStream_t stream, int tile_mode);
 int w4a16_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
 int w4a16_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
 }  // namespace b200moe
@@ -132,11 +133,18 @@ extern "C" int b200moe_grouped_gemm1_act(const b200moe_gemm_args* a, void* strea
     case B200MOE_RECIPE_NVFP4:
       if (a->w13_sf == nullptr || a->a2_gscale == nullptr) return B200MOE_EINVAL;
       if (b200moe::nvfp4_small_batch_ok(a, /*fc1=*/true)) return b200moe::nvfp4_small_gemm1(a, s);
-      if (b200moe::pair_ok(a, /*fc1=*/true)) return b200moe::nvfp4_pair_gemm1(a, s);
-      return b200moe::nvfp4_gemm1(a, s);
+      if (b200moe::pair_ok(a, /*fc1=*/true)) {
+        // full pairs of row tiles on CTA pairs, then the left-over row tiles on single CTAs
+        const int rc1 = b200moe::nvfp4_pair_gemm1(a, s);
+        return (rc1 != B200MOE_OK || !b200moe::tail_split(a)) ? rc1 : b200moe::nvfp4_gemm1(a, s, 1);
+      }
+      return b200moe::nvfp4_gemm1(a, s, 0);
     case B200MOE_RECIPE_W4A8_MX:
-      if (b200moe::pair_ok(a, /*fc1=*/true)) return b200moe::mx_pair_gemm1(a, s);
-      return b200moe::mx_gemm1(a, s);
+      if (b200moe::pair_ok(a, /*fc1=*/true)) {
+        const int rc1 = b200moe::mx_pair_gemm1(a, s);
+        return (rc1 != B200MOE_OK || !b200moe::tail_split(a)) ? rc1 : b200moe::mx_gemm1(a, s, 1);
+      }
+      return b200moe::mx_gemm1(a, s, 0);
     case B200MOE_RECIPE_W4A16:
       return b200moe::w4a16_gemm1(a, s);
     default:
@@ -153,11 +161,17 @@ extern "C" int b200moe_grouped_gemm2(const b200moe_gemm_args* a, void* stream) {
     case B200MOE_RECIPE_NVFP4:
       if (a->w2_sf == nullptr) return B200MOE_EINVAL;
       if (b200moe::nvfp4_small_batch_ok(a, /*fc1=*/false)) return b200moe::nvfp4_small_gemm2(a, s);
-      if (b200moe::pair_ok(a, /*fc1=*/false)) return b200moe::nvfp4_pair_gemm2(a, s);
-      return b200moe::nvfp4_gemm2(a, s);
+      if (b200moe::pair_ok(a, /*fc1=*/false)) {
+        const int rc1 = b200moe::nvfp4_pair_gemm2(a, s);
+        return (rc1 != B200MOE_OK || !b200moe::tail_split(a)) ? rc1 : b200moe::nvfp4_gemm2(a, s, 1);
+      }
+      return b200moe::nvfp4_gemm2(a, s, 0);
     case B200MOE_RECIPE_W4A8_MX:
-      if (b200moe::pair_ok(a, /*fc1=*/false)) return b200moe::mx_pair_gemm2(a, s);
-      return b200moe::mx_gemm2(a, s);
+      if (b200moe::pair_ok(a, /*fc1=*/false)) {
+        const int rc1 = b200moe::mx_pair_gemm2(a, s);
+        return (rc1 != B200MOE_OK || !b200moe::tail_split(a)) ? rc1 : b200moe::mx_gemm2(a, s, 1);
+      }
+      return b200moe::mx_gemm2(a, s, 0);
     case B200MOE_RECIPE_W4A16:
       return b200moe::w4a16_gemm2(a, s);
     default:

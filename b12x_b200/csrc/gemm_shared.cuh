@@ -17,6 +17,12 @@ __host__ __device__ constexpr bool epi_is_gated(int epi) { return epi == EPI_FC1
 //             kind::mxf8f6f4 (K = 32 per MMA, 128 per stage; one scale atom per stage).
 enum { KIND_NVFP4 = 0, KIND_MX = 1 };
 
+// Which row tiles a launch works on.  Plans with several row tiles per expert run the CTA-pair kernel
+// on every FULL pair of row tiles (TILES_PAIRS) and a single-CTA kernel on the row tile that is left
+// over in experts with an odd number of them (TILES_TAIL): a pair with one empty half costs a whole
+// pair's loads and MMAs, the single tile a little more than half of that on one SM instead of two.
+enum { TILES_ALL = 0, TILES_TAIL = 1, TILES_PAIRS = 2 };
+
 struct GemmParams {
   const uint8_t* sfa;            // activation scale atoms [mtile][atoms_k][512]
   const uint8_t* sfb;            // weight scale atoms [E][rowgroups][atoms_k][512]
@@ -41,6 +47,7 @@ struct GemmParams {
   int gscale_len;
   float limit, act_alpha, act_beta;
   int act_kind;                  // gated FC1: 0 SwiGLU, 1 SwiGLU-OAI, 2 SiTU
+  int tile_mode;                 // TILES_ALL / TILES_TAIL / TILES_PAIRS
 };
 
 struct TileCoord {
@@ -63,6 +70,29 @@ __device__ __forceinline__ TileCoord decode_tile(int w, int n_tiles, const int32
   c.nt = local / me;
   c.mt = tb[lo] + local % me;
   return c;
+}
+// the same through the kernel's shared-memory work list `tb` (see build_tile_base)
+__device__ __forceinline__ TileCoord decode_work(int w, const GemmParams& p, const int32_t* tb) {
+  TileCoord c = decode_tile(w, p.n_tiles, tb, p.E);
+  if (p.tile_mode == TILES_TAIL) c.mt = p.tile_base[c.e + 1] - 1;   // the expert's last row tile
+  return c;
+}
+
+// Shared-memory work list of a single-CTA kernel (all threads call it before the set-up barrier):
+// the row-tile prefix sums as they are, or the prefix sums of "has a left-over row tile".
+__device__ __forceinline__ void build_tile_base(int32_t* dst, const int32_t* __restrict__ src, int E, int tile_mode) {
+  if (tile_mode == TILES_TAIL) {
+    if (threadIdx.x == 0) {
+      int acc = 0;
+      for (int e = 0; e < E; ++e) {
+        dst[e] = acc;
+        acc += (src[e + 1] - src[e]) & 1;
+      }
+      dst[E] = acc;
+    }
+  } else {
+    for (int i = threadIdx.x; i <= E; i += blockDim.x) dst[i] = src[i];
+  }
 }
 
 // SiTU (b12x/moe/_shared/kernels/reference.py:160-172): 4 tanh(g / 4) sigmoid(g) * 25 tanh(u / 25)

@@ -95,7 +95,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
     tail->abort_flag = 0;
     fence_mbar_init();
   }
-  for (int i = threadIdx.x; i <= p.E; i += blockDim.x) tail->tile_base[i] = p.tile_base[i];
+  build_tile_base(tail->tile_base, p.tile_base, p.E, p.tile_mode);
   if (warp == 1) {
     tmem_alloc(&tail->tmem_base, kTmemCols);
     tmem_relinquish();
@@ -146,7 +146,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
         uint32_t a_bytes;
       };
       auto locate = [&](int w) {
-        const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
+        const TileCoord c = decode_work(w, p, tail->tile_base);
         LaneSrc r;
         const bool small_a = p.mtile_rows[c.mt] <= 32;
         r.a_bytes = (small_a ? 32u : 128u) * kRowBytes;
@@ -388,7 +388,7 @@ grouped_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA,
     int buf = 0;
     TL_DECL(tl_t);
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
-      const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
+      const TileCoord c = decode_work(w, p, tail->tile_base);
       const int row0 = p.mtile_row0[c.mt];
       const int nrows = p.mtile_rows[c.mt];
       if (!mbar_wait_bounded(&tail->tmem_full[buf], acc_phase[buf], abort_flag, p.status,
@@ -523,7 +523,7 @@ static int launch_any(int /*bn*/, const CUtensorMap& tmA, const CUtensorMap& tmA
 // pair groups (64 up rows + 64 gate rows) whose scales are one atom per MMA step.  The weight codes
 // are read where the checkpoint left them, with 64-row TMA boxes.
 template <int KIND>
-static int gemm1_any(const b200moe_gemm_args* a, cudaStream_t stream) {
+static int gemm1_any(const b200moe_gemm_args* a, cudaStream_t stream, int tile_mode) {
   const b200moe_scratch_layout& L = *a->layout;
   const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
   const bool gated = a->activation != B200MOE_ACT_RELU2;
@@ -543,6 +543,7 @@ static int gemm1_any(const b200moe_gemm_args* a, cudaStream_t stream) {
   if (rc != B200MOE_OK) return rc;
   GemmParams p = {};
   fill_common(p, a, base);
+  p.tile_mode = tile_mode;
   p.sfa = reinterpret_cast<const uint8_t*>(base + L.act_sf);
   p.sfb = a->w13_sf;
   p.alphas = a->w1_alphas;
@@ -576,7 +577,7 @@ static int gemm1_any(const b200moe_gemm_args* a, cudaStream_t stream) {
 }
 
 template <int KIND>
-static int gemm2_any(const b200moe_gemm_args* a, cudaStream_t stream) {
+static int gemm2_any(const b200moe_gemm_args* a, cudaStream_t stream, int tile_mode) {
   const b200moe_scratch_layout& L = *a->layout;
   const int K = a->hidden_size, I = a->intermediate, E = a->num_experts;
   const bool mx = KIND == KIND_MX;
@@ -593,6 +594,7 @@ static int gemm2_any(const b200moe_gemm_args* a, cudaStream_t stream) {
   if (rc != B200MOE_OK) return rc;
   GemmParams p = {};
   fill_common(p, a, base);
+  p.tile_mode = tile_mode;
   p.sfa = reinterpret_cast<const uint8_t*>(base + L.mid_sf);
   p.sfb = a->w2_sf;
   p.alphas = a->w2_alphas;
@@ -610,10 +612,10 @@ static int gemm2_any(const b200moe_gemm_args* a, cudaStream_t stream) {
   return launch_any<KIND, EPI_FC2>(bn, tmA, tmA_small, tmB, p, grid, stream);
 }
 
-int nvfp4_gemm1(const b200moe_gemm_args* a, cudaStream_t s) { return gemm1_any<KIND_NVFP4>(a, s); }
-int nvfp4_gemm2(const b200moe_gemm_args* a, cudaStream_t s) { return gemm2_any<KIND_NVFP4>(a, s); }
-int mx_gemm1(const b200moe_gemm_args* a, cudaStream_t s) { return gemm1_any<KIND_MX>(a, s); }
-int mx_gemm2(const b200moe_gemm_args* a, cudaStream_t s) { return gemm2_any<KIND_MX>(a, s); }
+int nvfp4_gemm1(const b200moe_gemm_args* a, cudaStream_t s, int tile_mode) { return gemm1_any<KIND_NVFP4>(a, s, tile_mode); }
+int nvfp4_gemm2(const b200moe_gemm_args* a, cudaStream_t s, int tile_mode) { return gemm2_any<KIND_NVFP4>(a, s, tile_mode); }
+int mx_gemm1(const b200moe_gemm_args* a, cudaStream_t s, int tile_mode) { return gemm1_any<KIND_MX>(a, s, tile_mode); }
+int mx_gemm2(const b200moe_gemm_args* a, cudaStream_t s, int tile_mode) { return gemm2_any<KIND_MX>(a, s, tile_mode); }
 
 }  // namespace b200moe
 

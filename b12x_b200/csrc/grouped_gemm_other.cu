@@ -43,6 +43,7 @@ namespace b200moe {
 
 int make_tmap_bytes_2d(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,
                        uint32_t box_rows);
+bool tail_split(const b200moe_gemm_args* a);
 
 namespace w4a16 {
 
@@ -105,6 +106,8 @@ struct Params {
   float limit, act_alpha, act_beta;
   int swigluoai;
   int sf_e8m0;                   // scale bytes are E8M0 (2^(b-127)) instead of E4M3
+  int tile_mode;                 // 0 all row tiles; 1 only the left-over row tile of experts with an odd
+                                 // number of them (after the CTA-pair kernel); 2 full pairs only
 };
 
 struct TileCoord {
@@ -123,6 +126,14 @@ __device__ __forceinline__ TileCoord decode_tile(int w, int n_tiles, const int32
   const int local = w - tb[lo] * n_tiles;
   c.nt = local / me;
   c.mt = tb[lo] + local % me;
+  return c;
+}
+
+// through the single-CTA kernel's shared-memory work list `tb`: the row-tile prefix sums, or (tile
+// mode 1) the prefix sums of "has a left-over row tile"
+__device__ __forceinline__ TileCoord decode_work(int w, const Params& p, const int32_t* tb) {
+  TileCoord c = decode_tile(w, p.n_tiles, tb, p.E);
+  if (p.tile_mode == 1) c.mt = p.tile_base[c.e + 1] - 1;
   return c;
 }
 
@@ -316,7 +327,18 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
     tail->abort_flag = 0;
     fence_mbar_init();
   }
-  for (int i = threadIdx.x; i <= p.E; i += blockDim.x) tail->tile_base[i] = p.tile_base[i];
+  if (p.tile_mode == 1) {
+    if (threadIdx.x == 0) {
+      int acc = 0;
+      for (int e = 0; e < p.E; ++e) {
+        tail->tile_base[e] = acc;
+        acc += (p.tile_base[e + 1] - p.tile_base[e]) & 1;
+      }
+      tail->tile_base[p.E] = acc;
+    }
+  } else {
+    for (int i = threadIdx.x; i <= p.E; i += blockDim.x) tail->tile_base[i] = p.tile_base[i];
+  }
   if (warp == 1) {
     tmem_alloc(&tail->tmem_base, 512);
     tmem_relinquish();
@@ -341,7 +363,7 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t phase = 0, rphase = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-        const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
+        const TileCoord c = decode_work(w, p, tail->tile_base);
         const int row0 = p.mtile_row0[c.mt];
         const int r0 = p.sub0_base + c.nt * p.n_step;
         int r1 = p.sub1_base + c.nt * p.n_step;
@@ -455,7 +477,7 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
     uint32_t phase = 0, bphase = 0, rphase = 0;
     bool ok = true;
     for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-      const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
+      const TileCoord c = decode_work(w, p, tail->tile_base);
       const int r0 = p.sub0_base + c.nt * p.n_step;
       int r1 = p.sub1_base + c.nt * p.n_step;
       if (r1 >= p.w_rows) r1 = r0;
@@ -548,7 +570,7 @@ grouped_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA,
     uint32_t acc_phase[2] = {0, 0};
     int buf = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
-      const TileCoord c = decode_tile(w, p.n_tiles, tail->tile_base, p.E);
+      const TileCoord c = decode_work(w, p, tail->tile_base);
       const int row0 = p.mtile_row0[c.mt];
       const int nrows = p.mtile_rows[c.mt];
       const float alpha = p.alphas[c.e];
@@ -693,7 +715,7 @@ grouped_gemm_w4a16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
       const int t0 = p.tile_base[e], t1 = p.tile_base[e + 1];
       tail->tile_base[e] = t0;
       tail->pair_base[e] = acc;
-      acc += (t1 - t0 + 1) >> 1;
+      acc += (t1 - t0 + (p.tile_mode == 2 ? 0 : 1)) >> 1;   // full pairs only, or the odd tile too
       if (e == p.E - 1) tail->tile_base[p.E] = t1;
     }
     tail->pair_base[p.E] = acc;
@@ -1049,6 +1071,24 @@ static bool use_pair(const b200moe_gemm_args* a) {
   return static_cast<int64_t>(a->layout->rows) >= 256ll * a->num_experts;
 }
 
+// Plans for CTA pairs: full pairs of row tiles on the pair kernel, then the left-over row tile of
+// experts with an odd number of them on the single-CTA kernel (plans with few row tiles per expert;
+// otherwise, or with B200MOE_TAIL_SPLIT=0, the pair kernel takes those too, as half-empty pairs).  Other plans: the single-CTA kernel on every row tile.
+template <int EPI>
+static int launch_split(const b200moe_gemm_args* a, const CUtensorMap& tmA, const CUtensorMap& tmW, Params p,
+                        int grid, cudaStream_t s) {
+  if (!use_pair(a)) {
+    p.tile_mode = 0;
+    return launch<EPI>(tmA, tmW, p, grid, s);
+  }
+  const bool split = ::b200moe::tail_split(a);
+  p.tile_mode = split ? 2 : 0;
+  const int rc = launch_pair<EPI>(tmA, tmW, p, grid, s);
+  if (rc != B200MOE_OK || !split) return rc;
+  p.tile_mode = 1;
+  return launch<EPI>(tmA, tmW, p, grid, s);
+}
+
 static void fill_common(Params& p, const b200moe_gemm_args* a, char* base) {
   const b200moe_scratch_layout& L = *a->layout;
   p.tile_base = reinterpret_cast<const int32_t*>(base + L.tile_base);
@@ -1107,15 +1147,13 @@ int w4a16_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
     p.n_step = 128;
     p.sub0_base = a->gate_first ? I : 0;
     p.sub1_base = a->gate_first ? 0 : I;
-    return use_pair(a) ? launch_pair<EPI_FC1_GATED>(tmA, tmW, p, grid, stream)
-                       : launch<EPI_FC1_GATED>(tmA, tmW, p, grid, stream);
+    return launch_split<EPI_FC1_GATED>(a, tmA, tmW, p, grid, stream);
   }
   p.n_tiles = ceil_div_i(I, 256);
   p.n_step = 256;
   p.sub0_base = 0;
   p.sub1_base = 128;
-  return use_pair(a) ? launch_pair<EPI_FC1_RELU2>(tmA, tmW, p, grid, stream)
-                     : launch<EPI_FC1_RELU2>(tmA, tmW, p, grid, stream);
+  return launch_split<EPI_FC1_RELU2>(a, tmA, tmW, p, grid, stream);
 }
 
 int w4a16_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
@@ -1146,7 +1184,7 @@ int w4a16_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
   p.sub0_base = 0;
   p.sub1_base = 128;
   const int grid = a->num_sms > 0 ? a->num_sms : sm_count();
-  return use_pair(a) ? launch_pair<EPI_FC2>(tmA, tmW, p, grid, stream) : launch<EPI_FC2>(tmA, tmW, p, grid, stream);
+  return launch_split<EPI_FC2>(a, tmA, tmW, p, grid, stream);
 }
 
 }  // namespace b200moe

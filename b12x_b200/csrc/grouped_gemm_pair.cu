@@ -140,7 +140,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       const int t0 = p.tile_base[e], t1 = p.tile_base[e + 1];
       tail->tile_base[e] = t0;
       tail->pair_base[e] = acc;
-      acc += (t1 - t0 + 1) >> 1;
+      acc += (t1 - t0 + (p.tile_mode == TILES_PAIRS ? 0 : 1)) >> 1;   // full pairs only, or the odd tile too
       if (e == p.E - 1) tail->tile_base[p.E] = t1;
     }
     tail->pair_base[p.E] = acc;
@@ -490,6 +490,21 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmPara
 // plans whose capacity averages at least two row tiles per expert; an expert with an odd number of
 // row tiles leaves half a pair idle, so smaller plans stay on the single-CTA kernel.
 // B200MOE_PAIR=1 / 0 forces them on (where the shape allows) / off.
+// Whether the left-over row tile of an expert with an odd number of them goes to a single-CTA launch
+// of its own (after the pair kernel) or into a half-empty pair.  The second launch has wave tails of
+// its own, so it pays while experts hold few row tiles: 128 experts x 4 row tiles FC1 1.21 -> 1.15 ms,
+// 128 x 2 (w4a16) 1.17 -> 1.10 ms, but 8 experts x 16 row tiles 0.915 -> 0.927 ms.  Default: plans
+// that average fewer than eight row tiles per expert; B200MOE_TAIL_SPLIT=1 / 0 forces it on / off.
+bool tail_split(const b200moe_gemm_args* a) {
+  static int mode = -2;
+  if (mode == -2) {
+    const char* e = getenv("B200MOE_TAIL_SPLIT");
+    mode = e == nullptr ? -1 : (atoi(e) != 0 ? 1 : 0);
+  }
+  if (mode >= 0) return mode == 1;
+  return static_cast<int64_t>(a->layout->rows) < 1024ll * a->num_experts;
+}
+
 bool pair_ok(const b200moe_gemm_args* a, bool fc1) {
   static int mode = -2;
   if (mode == -2) {
@@ -513,6 +528,7 @@ static int pair_gemm1_any(const b200moe_gemm_args* a, cudaStream_t stream) {
   char* base = static_cast<char*>(a->scratch);
   GemmParams p = {};
   fill_common(p, a, base);
+  p.tile_mode = tail_split(a) ? TILES_PAIRS : TILES_ALL;
   p.atoms_k = ceil_div_i(K, mx ? 128 : 64);
   p.sfb_rowgroups = I / 64;              // pair atoms: 64 up rows + 64 gate rows
   CUtensorMap tmA, tmB;
@@ -553,6 +569,7 @@ static int pair_gemm2_any(const b200moe_gemm_args* a, cudaStream_t stream) {
   char* base = static_cast<char*>(a->scratch);
   GemmParams p = {};
   fill_common(p, a, base);
+  p.tile_mode = tail_split(a) ? TILES_PAIRS : TILES_ALL;
   p.atoms_k = ceil_div_i(I, mx ? 128 : 64);
   p.sfb_rowgroups = ceil_div_i(K, 128);
   CUtensorMap tmA, tmB;

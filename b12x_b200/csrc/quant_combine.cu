@@ -402,6 +402,36 @@ extern "C" int b200moe_permute_quant_mxfp8(const b200moe_quant_args* a, void* st
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 
+// fp32 -> bf16 (round to nearest even), 8 values per thread: the last step of the tensor-parallel
+// layer, after the fp32 partial outputs of the ranks have been summed
+__global__ void __launch_bounds__(256) round_rows_bf16_kernel(const float* __restrict__ in,
+                                                              __nv_bfloat16* __restrict__ out, int64_t n8) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float4 a = reinterpret_cast<const float4*>(in)[2 * i], b = reinterpret_cast<const float4*>(in)[2 * i + 1];
+    const __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+    const __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+    uint4 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&p0);
+    o.y = *reinterpret_cast<const uint32_t*>(&p1);
+    o.z = *reinterpret_cast<const uint32_t*>(&p2);
+    o.w = *reinterpret_cast<const uint32_t*>(&p3);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
+extern "C" int b200moe_round_rows_bf16(const float* in, void* out, int64_t count, void* stream) {
+  if (in == nullptr || out == nullptr || count < 0 || (count & 7) != 0) return B200MOE_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(in) & 15) != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0) return B200MOE_EALIGN;
+  if (count == 0) return B200MOE_OK;
+  const int64_t n8 = count >> 3;
+  int64_t grid = (n8 + 255) / 256;
+  grid = grid > 148 * 16 ? 148 * 16 : grid;
+  round_rows_bf16_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      in, static_cast<__nv_bfloat16*>(out), n8);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
+}
+
 extern "C" int b200moe_combine(const b200moe_combine_args* a, void* stream) {
   if (a == nullptr || a->topk_weights == nullptr || a->out == nullptr || a->scratch == nullptr ||
       a->layout == nullptr)

@@ -24,6 +24,7 @@ import torch
 import torch.distributed as dist
 
 from .. import synth
+from .._lib import ext
 from . import fused_moe
 from .fused_moe.stages import StageArena
 
@@ -452,7 +453,8 @@ class TensorParallelMoE(_LayerBase):
         self.local_shape = replace(shp, intermediate=inputs.w2_fp4.shape[2] * 2)
         self.plan, self.scratch = self._local_plan(shp.tokens, shp.topk)
         self.partial = torch.empty((shp.tokens, shp.hidden), dtype=torch.float32, device=dev)
-        self.kernels_per_step = 5 + sort_launches(shp.tokens * shp.topk)
+        # route, sort, row gather / quantise, FC1, FC2, fp32 combine, rounding
+        self.kernels_per_step = 6 + sort_launches(shp.tokens * shp.topk)
 
     @classmethod
     def from_synthetic(cls, shp: synth.MoEShape, dev, rank: int, world: int):
@@ -482,7 +484,9 @@ class TensorParallelMoE(_LayerBase):
         fused_moe.run(binding=b, stage_timer=stage_timer)
         if self.world > 1:
             dist.all_reduce(self.partial)
-        self.out.copy_(self.partial)
+        ext.check(ext.load().b200moe_round_rows_bf16(
+            self.partial.data_ptr(), self.out.data_ptr(), self.partial.numel(),
+            torch.cuda.current_stream(self.dev).cuda_stream), "round_rows_bf16")
         return self.out
 
     def work_stats(self) -> dict:

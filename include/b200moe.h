@@ -283,6 +283,10 @@ typedef struct {
   int32_t reserved;
 } b200moe_combine_args;
 int b200moe_combine(const b200moe_combine_args* a, void* stream);
+/* out[i] = bf16_rn(in[i]) for `count` contiguous values (count % 8 == 0, both pointers 16-byte
+ * aligned): the rounding step of the tensor-parallel layer after the ranks' fp32 partial outputs
+ * have been summed (the reference leaves that sum to its caller, b12x/moe/__init__.py:3-8). */
+int b200moe_round_rows_bf16(const float* in, void* out, int64_t count, void* stream);
 
 /* ---- expert parallelism over NVLink peer memory --------------------------- */
 /* No counterpart in the reference (b12x/moe/ep_moe/_impl.py:1-14 replicates the input on every

@@ -88,6 +88,10 @@ def test_host_side_argument_errors_need_no_gpu(lib):
     assert lib.b200moe_ep_dispatch(None, None) == ext.EINVAL
     assert lib.b200moe_ep_combine(None, None) == ext.EINVAL
     assert lib.b200moe_permute_packed(None, None) == ext.EINVAL
+    assert lib.b200moe_round_rows_bf16(None, None, 8, None) == ext.EINVAL
+    assert lib.b200moe_round_rows_bf16(16, 16, 7, None) == ext.EINVAL                          # count % 8
+    assert lib.b200moe_round_rows_bf16(20, 16, 8, None) == ext.EALIGN
+    assert lib.b200moe_ep_place_routes(None, 4, 8, None, None, None, None, None) == ext.EINVAL
 
 
 def _wplan(**kw):

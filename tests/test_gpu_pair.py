@@ -2,7 +2,9 @@
 the CPU oracle.  In-process the library picks the kernel itself (plans that average two or more row
 tiles per expert run on the CTA-pair kernels, tcgen05 cta_group::2); `test_both_kernel_families...`
 re-runs this file in child processes with B200MOE_PAIR=1 and =0, which forces every case onto the
-CTA-pair and onto the single-CTA kernels."""
+CTA-pair and onto the single-CTA kernels; with the pair kernels once with the left-over row tile of
+an odd-tiled expert on a single-CTA launch of its own (B200MOE_TAIL_SPLIT=1) and once as half of a
+pair (=0)."""
 
 import os
 import subprocess
@@ -61,11 +63,11 @@ def test_pair_repeat_runs_bitwise_identical():
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("forced", ["1", "0"])
-def test_both_kernel_families_pass_these_cases(forced):
+@pytest.mark.parametrize("forced,split", [("1", "1"), ("1", "0"), ("0", "1")])
+def test_both_kernel_families_pass_these_cases(forced, split):
     if os.environ.get("B200MOE_PAIR") is not None:
         pytest.skip("already a child run")
-    env = dict(os.environ, B200MOE_PAIR=forced)
+    env = dict(os.environ, B200MOE_PAIR=forced, B200MOE_TAIL_SPLIT=split)
     r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-m", "gpu", "-x", "-q", "-p", "no:cacheprovider"],
                        env=env, capture_output=True, text=True, timeout=800)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]

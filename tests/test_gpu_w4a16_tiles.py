@@ -1,8 +1,9 @@
 """-m gpu: W4A16 layers with several 128-row tiles per expert against the CPU oracle.  In-process the
 kernel family follows the plan (CTA pairs once it averages two row tiles per expert); the two child
 runs repeat this file and the other W4A16 cases with the CTA-pair kernels forced on
-(B200MOE_W4A16_PAIR=1: every shape, also experts with one or an odd number of row tiles) and off
-(=0: the single-CTA kernel).  The switch is read once per process."""
+(B200MOE_W4A16_PAIR=1: every shape, also experts with one or an odd number of row tiles -- once with
+the left-over row tile on a single-CTA launch, B200MOE_TAIL_SPLIT=1, once as half of a pair, =0) and
+off (=0: the single-CTA kernel).  The switch is read once per process."""
 
 import os
 import subprocess
@@ -38,13 +39,13 @@ def test_w4a16_many_row_tiles_matches_oracle(tokens, experts, topk, hidden, inte
     _check_w4a16_layer(run_layer(synth.make_inputs(shp, seed=tokens + inter), want_fc1=True))
 
 
-@pytest.mark.parametrize("pair", ["1", "0"])
+@pytest.mark.parametrize("pair,split", [("1", "1"), ("1", "0"), ("0", "1")])
 @pytest.mark.timeout(900)
-def test_both_kernel_families_pass_the_w4a16_cases(pair):
+def test_both_kernel_families_pass_the_w4a16_cases(pair, split):
     if os.environ.get("B200MOE_W4A16_CHILD") == "1":
         pytest.skip("already the child run")
     here = Path(__file__).resolve().parent
-    env = dict(os.environ, B200MOE_W4A16_PAIR=pair, B200MOE_W4A16_CHILD="1")
+    env = dict(os.environ, B200MOE_W4A16_PAIR=pair, B200MOE_TAIL_SPLIT=split, B200MOE_W4A16_CHILD="1")
     r = subprocess.run([sys.executable, "-m", "pytest", str(Path(__file__).resolve()),
                         str(here / "test_gpu_parity.py"), str(here / "test_w4a16_sources.py"),
                         "-m", "gpu", "-k", "w4a16", "-x", "-q", "-p", "no:cacheprovider"],
