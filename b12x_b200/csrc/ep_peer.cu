@@ -150,16 +150,23 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(
     if (j >= offs[d + 1] - offs[d]) static_cast<int32_t*>(ids.p[d])[rank * cap + j] = -1;
   }
   // last block out raises the flags: every block publishes its peer stores first
+  __shared__ int is_last;
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
     const int prev = atomicAdd(done_counter, 1);
-    if (prev == static_cast<int>(gridDim.x) - 1) {
+    is_last = prev == static_cast<int>(gridDim.x) - 1;
+    if (is_last) {
       *done_counter = 0;
       if (epoch_dev != nullptr) *epoch_dev = epoch;
-      __threadfence_system();
-      for (int d = 0; d < world; ++d) st_release_sys(static_cast<int32_t*>(flags.p[d]) + rank, epoch);
     }
+  }
+  __syncthreads();
+  // one thread per peer: the release stores (a system-scope fence each, i.e. a link round trip)
+  // go out side by side instead of one after the other
+  if (is_last && threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<int32_t*>(flags.p[threadIdx.x]) + rank, epoch);
   }
 }
 

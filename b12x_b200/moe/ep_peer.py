@@ -172,6 +172,9 @@ class PeerExpertParallelMoE(_LayerBase):
 
     def _measure_loads(self, logits: torch.Tensor) -> list:
         """COLLECTIVE: routes per global expert over all ranks' calibration batches."""
+        if tuple(logits.shape) != (self.shape.tokens, self.shape.experts):
+            raise ValueError(f"calibration logits must be [{self.shape.tokens}, {self.shape.experts}], "
+                             f"got {tuple(logits.shape)}")
         self.route(logits.to(self.dev))
         counts = torch.bincount(self.topk_ids.reshape(-1).long().clamp(0, self.shape.experts - 1),
                                 minlength=self.shape.experts).to(torch.float32)
