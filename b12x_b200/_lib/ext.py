@@ -96,14 +96,14 @@ class GemmArgs(C.Structure):
                 ("recipe", C.c_int32), ("activation", C.c_int32), ("gate_first", C.c_int32),
                 ("gscale_len", C.c_int32), ("swiglu_limit", C.c_float),
                 ("swiglu_alpha", C.c_float), ("swiglu_beta", C.c_float),
-                ("num_sms", C.c_int32), ("sf_e8m0", C.c_int32)]
+                ("num_sms", C.c_int32), ("sf_e8m0", C.c_int32), ("fc1_route_weights", C.c_void_p)]
 
 
 class CombineArgs(C.Structure):
     _fields_ = [("topk_weights", C.c_void_p), ("out", C.c_void_p), ("scratch", C.c_void_p),
                 ("layout", C.POINTER(ScratchLayout)), ("out_row_stride", C.c_int64),
                 ("num_tokens", C.c_int32), ("num_topk", C.c_int32), ("hidden_size", C.c_int32),
-                ("out_f32", C.c_int32), ("output_scale", C.c_float), ("reserved", C.c_int32)]
+                ("out_f32", C.c_int32), ("output_scale", C.c_float), ("unit_weights", C.c_int32)]
 
 
 MAX_RANKS = 16

@@ -101,6 +101,7 @@ struct Params {
   __nv_bfloat16* out_bf16;       // FC1: intermediate [rows][out_cols]
   float* out_f32;                // FC2: routed rows [rows][out_cols]
   float* tap;
+  const float* row_scale;        // FC1, optional: per sorted position, multiplies the row with its alpha
   int E, n_tiles, kdim, k_blocks, atoms_k, sf_rowgroups, w_rows;
   int sub0_base, sub1_base, n_step, out_cols;
   float limit, act_alpha, act_beta;
@@ -208,6 +209,7 @@ __device__ __forceinline__ void cvt_e4m3x4_f16(uint32_t w, uint32_t& s01, uint32
 template <int EPI>
 __device__ __forceinline__ void epilogue_rows(const Params& p, float alpha, int nt, size_t pos, bool valid,
                                               uint32_t t_lane, int half) {
+  if (EPI != EPI_FC2 && p.row_scale != nullptr && valid) alpha = __fmul_rn(alpha, p.row_scale[pos]);
   if (EPI == EPI_FC1_GATED) {
     const int col0 = nt * 128 + half * 64;
     __nv_bfloat16* orow = p.out_bf16 + pos * p.out_cols + col0;
@@ -955,11 +957,13 @@ grouped_gemm_w4a16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
 __global__ void __launch_bounds__(256) permute_rows_bf16_kernel(
     const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, const int32_t* __restrict__ expert_offsets,
     int E, const int32_t* __restrict__ sorted_route_ids, int num_topk, int K,
-    __nv_bfloat16* __restrict__ out) {
+    __nv_bfloat16* __restrict__ out, const float* __restrict__ route_weights, float* __restrict__ row_scale) {
   const int total = expert_offsets[E];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int pos = blockIdx.x * 8 + warp; pos < total; pos += gridDim.x * 8) {
-    const int tkn = sorted_route_ids[pos] / num_topk;
+    const int route = sorted_route_ids[pos];
+    const int tkn = route / num_topk;
+    if (route_weights != nullptr && lane == 0) row_scale[pos] = route_weights[route];
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(tkn) * x_row_stride);
     uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(pos) * K);
     for (int j = lane; j < (K >> 3); j += 32) dst[j] = __ldg(src + j);
@@ -1122,7 +1126,8 @@ int w4a16_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
       static_cast<const __nv_bfloat16*>(a->x), a->x_row_stride,
       reinterpret_cast<const int32_t*>(base + L.expert_offsets), E,
       reinterpret_cast<const int32_t*>(base + L.sorted_route_ids), a->num_topk, K,
-      reinterpret_cast<__nv_bfloat16*>(base + L.act_q));
+      reinterpret_cast<__nv_bfloat16*>(base + L.act_q), a->fc1_route_weights,
+      reinterpret_cast<float*>(base + L.act_sf));   // w4a16 has no activation scales: the region holds the row weights
   CUtensorMap tmA, tmW;
   int rc = make_tmap_bf16(&tmA, base + L.act_q, K, L.rows, 128);
   if (rc != B200MOE_OK) return rc;
@@ -1135,6 +1140,7 @@ int w4a16_gemm1(const b200moe_gemm_args* a, cudaStream_t stream) {
   p.alphas = a->w1_alphas;
   p.out_bf16 = reinterpret_cast<__nv_bfloat16*>(base + L.mid_q);
   p.tap = a->fc1_tap;
+  p.row_scale = a->fc1_route_weights != nullptr ? reinterpret_cast<const float*>(base + L.act_sf) : nullptr;
   p.kdim = K;
   p.k_blocks = K / kKPerStage;
   p.atoms_k = ceil_div_i(K, 64);

@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(256) combine_kernel(
   float* w = reinterpret_cast<float*>(sm + num_topk);
   for (int s = threadIdx.x; s < num_topk; s += blockDim.x) {
     pos[s] = inv_perm[static_cast<int64_t>(t) * num_topk + s];
-    w[s] = topk_weights[static_cast<int64_t>(t) * num_topk + s];
+    w[s] = topk_weights != nullptr ? topk_weights[static_cast<int64_t>(t) * num_topk + s] : 1.0f;
   }
   __syncthreads();
   const int nvec = K >> 2;
@@ -452,7 +452,8 @@ extern "C" int b200moe_combine(const b200moe_combine_args* a, void* stream) {
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
 #define B200MOE_COMBINE_ARGS \
   reinterpret_cast<const float*>(base + L.routed), reinterpret_cast<const int32_t*>(base + L.inv_perm), \
-      a->topk_weights, a->out, a->out_row_stride, a->num_topk, a->hidden_size, a->out_f32, a->output_scale
+      (a->unit_weights ? nullptr : a->topk_weights), a->out, a->out_row_stride, a->num_topk, a->hidden_size, a->out_f32, \
+      a->output_scale
   if (a->num_topk <= 2) combine_kernel<2><<<grid, 256, smem, cs>>>(B200MOE_COMBINE_ARGS);
   else if (a->num_topk <= 4) combine_kernel<4><<<grid, 256, smem, cs>>>(B200MOE_COMBINE_ARGS);
   else combine_kernel<8><<<grid, 256, smem, cs>>>(B200MOE_COMBINE_ARGS);

@@ -395,8 +395,9 @@ class TPMoEScratchCaps:
         object.__setattr__(self, "swiglu_limit", limit)
         object.__setattr__(self, "swiglu_alpha", alpha)
         object.__setattr__(self, "swiglu_beta", beta)
-        if self.apply_router_weight_on_input:
-            raise NotImplementedError("apply_router_weight_on_input is not built")
+        if self.apply_router_weight_on_input and str(self.quant_mode).lower() != "w4a16":
+            # as the reference: only its W4A16 path takes it (_impl.py:10631-10634)
+            raise NotImplementedError("apply_router_weight_on_input is not implemented in b12x_moe_fp4")
         if self.collect_activation_amax:
             raise NotImplementedError("collect_activation_amax is not built")
         if self.num_topk > 32:
@@ -522,7 +523,7 @@ def plan_tp_moe_execution(
     spec = next((sp for sp in weight_plan.specs if sp.quant_mode == mode), None)
     if spec is None:
         raise ValueError(f"quant_mode={mode!r} is absent from the weight plan")
-    if apply_router_weight_on_input:
+    if apply_router_weight_on_input and mode != "w4a16":
         raise NotImplementedError("apply_router_weight_on_input is not implemented in b12x_moe_fp4")
     limit, alpha, beta = normalize_swiglu_params(weight_plan.activation, swiglu_limit, swiglu_alpha, swiglu_beta)
     t, k_ = max(int(num_tokens), 1), max(int(num_topk), 1)
@@ -662,7 +663,8 @@ class TPMoEScratchPlan:
             swiglu_beta=caps.swiglu_beta, route_expert_map=route_expert_map,
             kernel_workspace=core, core_layout=self._core_layout, fc1_tap=fc1_tap,
             output_f32=output_f32, output_scale=float(output_scale), f32_only=bool(f32_only),
-            skip_combine=bool(skip_combine), sort_wait=sort_wait, a_packed=a_packed)
+            skip_combine=bool(skip_combine), sort_wait=sort_wait, a_packed=a_packed,
+            apply_router_weight_on_input=bool(caps.apply_router_weight_on_input))
 
 
 def plan_tp_moe_scratch(caps: TPMoEScratchCaps) -> TPMoEScratchPlan:
@@ -727,6 +729,8 @@ class TPMoEFP4Binding:
     sort_wait: tuple | None = None
     # (codes, scale rows): the rows arrive quantised and ``run`` files them instead of quantising ``a``
     a_packed: tuple | None = None
+    # w4a16: the router weights multiply FC1's rows (before the activation) instead of the combine's
+    apply_router_weight_on_input: bool = False
 
     # ---- scratch views (valid after run) ----
     def _v(self, name: str, count: int, dtype: torch.dtype) -> torch.Tensor:
@@ -882,7 +886,11 @@ def b12x_moe_fp4(*, binding: TPMoEFP4Binding, stage_timer=None) -> torch.Tensor:
         float(b.swiglu_limit) if b.swiglu_limit is not None else 0.0,
         float(b.swiglu_alpha if b.swiglu_alpha is not None else 1.0),
         float(b.swiglu_beta if b.swiglu_beta is not None else 0.0), 0,
-        1 if (b.quant_mode == "w4a16" and ex.plan.source_format == "fp4_e8m0_k32") else 0)
+        1 if (b.quant_mode == "w4a16" and ex.plan.source_format == "fp4_e8m0_k32") else 0,
+        # router weights into FC1 (every route's rows times its weight before the activation); the
+        # combine below then adds the routes with unit weights
+        b.topk_weights.data_ptr() if b.apply_router_weight_on_input else None)
+    unit = 1 if b.apply_router_weight_on_input else 0
     ext.check(lib.b200moe_grouped_gemm1_act(C.byref(gargs), stream), "grouped_gemm1_act")
     mark("gemm1")
     ext.check(lib.b200moe_grouped_gemm2(C.byref(gargs), stream), "grouped_gemm2")
@@ -892,13 +900,13 @@ def b12x_moe_fp4(*, binding: TPMoEFP4Binding, stage_timer=None) -> torch.Tensor:
         return out
     if not b.f32_only:
         cargs = ext.CombineArgs(b.topk_weights.data_ptr(), out.data_ptr(), scratch, lp, out.stride(0),
-                                tokens, b.num_topk, b.k, 0, float(b.output_scale), 0)
+                                tokens, b.num_topk, b.k, 0, float(b.output_scale), unit)
         ext.check(lib.b200moe_combine(C.byref(cargs), stream), "combine")
         mark("combine")
     if b.output_f32 is not None:
         targs = ext.CombineArgs(b.topk_weights.data_ptr(), b.output_f32.data_ptr(), scratch, lp,
                                 b.output_f32.stride(0), tokens, b.num_topk, b.k, 1,
-                                float(b.output_scale), 0)
+                                float(b.output_scale), unit)
         ext.check(lib.b200moe_combine(C.byref(targs), stream), "combine(f32 tap)")
         if b.f32_only:
             mark("combine")

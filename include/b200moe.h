@@ -263,6 +263,10 @@ typedef struct {
   int32_t sf_e8m0;           /* w4a16 only: 1 = the per-16 block-scale bytes are E8M0
                                 (an fp4_e8m0_k32 source, each per-32 scale written twice;
                                 b12x/moe/_shared/kernels/w4a16/prepare.py:1289-1325), 0 = E4M3 */
+  /* w4a16 only (reference apply_router_weight_on_input, b12x/moe/fused_moe/_impl.py:10631-10634,
+   * w4a16/kernel.py:5773): [T*k] router weights; FC1 multiplies every route's rows by its weight
+   * before the activation, and the combine must then be called with unit_weights = 1.  NULL = off. */
+  const float* fc1_route_weights;
 } b200moe_gemm_args;
 int b200moe_grouped_gemm1_act(const b200moe_gemm_args* a, void* stream);
 int b200moe_grouped_gemm2(const b200moe_gemm_args* a, void* stream);
@@ -280,7 +284,7 @@ typedef struct {
   int32_t num_tokens, num_topk, hidden_size;
   int32_t out_f32;           /* 1: write un-rounded float32 (parity tap)        */
   float output_scale;        /* multiplies the sum (routed_scaling_factor), 1.0 = none */
-  int32_t reserved;
+  int32_t unit_weights;      /* 1: every route weighs 1 (the router weights went into FC1) */
 } b200moe_combine_args;
 int b200moe_combine(const b200moe_combine_args* a, void* stream);
 /* out[i] = bf16_rn(in[i]) for `count` contiguous values (count % 8 == 0, both pointers 16-byte

@@ -59,13 +59,15 @@ def route_on_gpu(inp: synth.MoEInputs, dev):
 
 
 def run_layer(inp: synth.MoEInputs, *, topk_ids=None, topk_weights=None, expert_map=None, poison=0xFF,
-              max_tokens=None, w13_layout="w13", want_fc1=True, tile_rows=None) -> LayerRun:
+              max_tokens=None, w13_layout="w13", want_fc1=True, tile_rows=None,
+              weight_on_input=False) -> LayerRun:
     dev = torch.device("cuda")
     shp = inp.shape
     ex = prepare_experts(inp, dev, w13_layout=w13_layout)
     t = inp.x.shape[0]
     caps = fused_moe.Caps(max_tokens=max_tokens or max(t, 1), num_topk=shp.topk, device=dev,
-                          weight_plan=ex.plan, quant_mode=shp.recipe, tile_rows=tile_rows)
+                          weight_plan=ex.plan, quant_mode=shp.recipe, tile_rows=tile_rows,
+                          apply_router_weight_on_input=weight_on_input)
     plan = fused_moe.plan(caps)
     spec = plan.scratch_specs()[0]
     # poison the arena: a kernel that reads something it did not write shows up as garbage
@@ -86,7 +88,7 @@ def run_layer(inp: synth.MoEInputs, *, topk_ids=None, topk_weights=None, expert_
     return LayerRun(inp, b, out.cpu(), of32.cpu(), None if fc1 is None else fc1.cpu(), ti.cpu(), tw.cpu(), ex, plan)
 
 
-def oracle_layer(inp: synth.MoEInputs, ids, weights, expert_map=None):
+def oracle_layer(inp: synth.MoEInputs, ids, weights, expert_map=None, weight_on_input=False):
     shp = inp.shape
     taps = O.MoETaps()
     if shp.recipe == "nvfp4":
@@ -98,7 +100,7 @@ def oracle_layer(inp: synth.MoEInputs, ids, weights, expert_map=None):
     elif shp.recipe == "w4a16":
         out = O.moe_w4a16(inp.x, inp.w1_fp4, inp.w1_blockscale, inp.w1_global_scale, inp.w2_fp4,
                           inp.w2_blockscale, inp.w2_global_scale, ids, weights, activation=shp.activation,
-                          expert_map=expert_map, taps=taps)
+                          expert_map=expert_map, taps=taps, apply_router_weight_on_input=weight_on_input)
     else:
         ones = torch.ones(inp.w1_fp4.shape[0])
         out = O.moe_w4a8_mx(inp.x, inp.w1_fp4, inp.w1_blockscale, ones, inp.w2_fp4, inp.w2_blockscale, ones,

@@ -37,7 +37,7 @@ def test_struct_sizes_match_header_layout():
                ext.ScratchLayout, ext.CapsC):
         assert C.sizeof(st) % 8 == 0, st
     assert C.sizeof(ext.ScratchLayout) == 16 * 8 + 16
-    assert C.sizeof(ext.GemmArgs) == 13 * 8 + 14 * 4
+    assert C.sizeof(ext.GemmArgs) == 14 * 8 + 14 * 4
 
 
 def test_scratch_layout_is_monotone_and_aligned(lib):

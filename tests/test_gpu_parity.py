@@ -271,8 +271,8 @@ def _w16(**kw):
     return synth.shape("c3", **base)
 
 
-def _check_w4a16_layer(run, *, expert_map=None):
-    ref, taps = oracle_layer(run.inp, run.topk_ids, run.topk_weights, expert_map)
+def _check_w4a16_layer(run, *, expert_map=None, weight_on_input=False):
+    ref, taps = oracle_layer(run.inp, run.topk_ids, run.topk_weights, expert_map, weight_on_input)
     b = run.binding
     rows = _check_sort(run, taps)
     d = (run.fc1[:rows] - taps.fc1).abs().max().item()
@@ -293,6 +293,21 @@ def _check_w4a16_layer(run, *, expert_map=None):
 def test_w4a16_layer(tokens, hidden, inter, act):
     inp = synth.make_inputs(_w16(tokens=tokens, hidden=hidden, intermediate=inter, activation=act), seed=tokens + inter)
     _check_w4a16_layer(run_layer(inp))
+
+
+@pytest.mark.parametrize("tokens,topk,act", [(48, 1, "silu"), (200, 2, "silu"), (40, 2, "relu2")])
+def test_w4a16_router_weight_on_input(tokens, topk, act):
+    """``Caps.apply_router_weight_on_input`` (W4A16 only, as in the reference): the route's weight
+    multiplies FC1's rows before the activation, the combine adds the routes with unit weights."""
+    inp = synth.make_inputs(_w16(tokens=tokens, topk=topk, hidden=384, intermediate=256, activation=act), seed=tokens)
+    run = run_layer(inp, weight_on_input=True)
+    _check_w4a16_layer(run, weight_on_input=True)
+    plain = run_layer(inp)
+    if topk > 1:                                        # (one renormalised route weighs exactly 1)
+        assert not torch.equal(run.out, plain.out)      # the option is not a no-op
+    with pytest.raises(NotImplementedError):
+        inp4 = synth.make_inputs(synth.shape("c1", name="x", tokens=8, hidden=256, intermediate=128, experts=4, topk=2), seed=1)
+        run_layer(inp4, weight_on_input=True)
 
 
 def test_w4a16_matches_reference_golden():
