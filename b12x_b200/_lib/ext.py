@@ -99,6 +99,12 @@ class GemmArgs(C.Structure):
                 ("num_sms", C.c_int32), ("sf_e8m0", C.c_int32), ("fc1_route_weights", C.c_void_p)]
 
 
+class AmaxArgs(C.Structure):
+    _fields_ = [("scratch", C.c_void_p), ("layout", C.POINTER(ScratchLayout)), ("amax", C.c_void_p),
+                ("num_rows", C.c_int32), ("num_experts", C.c_int32), ("hidden_size", C.c_int32),
+                ("intermediate", C.c_int32), ("layer_idx", C.c_int32), ("recipe", C.c_int32)]
+
+
 class CombineArgs(C.Structure):
     _fields_ = [("topk_weights", C.c_void_p), ("out", C.c_void_p), ("scratch", C.c_void_p),
                 ("layout", C.POINTER(ScratchLayout)), ("out_row_stride", C.c_int64),
@@ -167,6 +173,7 @@ EXPORTS = {
     "b200moe_combine": ([C.POINTER(CombineArgs), C.c_void_p], C.c_int),
     "b200moe_ep_dispatch": ([C.POINTER(EpDispatchArgs), C.c_void_p], C.c_int),
     "b200moe_permute_packed": ([C.POINTER(PackedArgs), C.c_void_p], C.c_int),
+    "b200moe_activation_amax": ([C.POINTER(AmaxArgs), C.c_void_p], C.c_int),
     "b200moe_round_rows_bf16": ([C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p], C.c_int),
     "b200moe_ep_place_routes": ([C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_void_p], C.c_int),

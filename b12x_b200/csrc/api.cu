@@ -18,6 +18,7 @@ int mx_gemm1(const b200moe_gemm_args* a, cudaStream_t stream, int tile_mode);
 int mx_gemm2(const b200moe_gemm_args* a, cudaStream_t stream, int tile_mode);
 int w4a16_gemm1(const b200moe_gemm_args* a, cudaStream_t stream);
 int w4a16_gemm2(const b200moe_gemm_args* a, cudaStream_t stream);
+int w4a16_activation_amax(const b200moe_amax_args* a, cudaStream_t stream);
 }  // namespace b200moe
 
 static inline int64_t align_up64(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
@@ -177,4 +178,15 @@ extern "C" int b200moe_grouped_gemm2(const b200moe_gemm_args* a, void* stream) {
     default:
       return B200MOE_EINVAL;
   }
+}
+
+extern "C" int b200moe_activation_amax(const b200moe_amax_args* a, void* stream) {
+  if (a == nullptr || a->scratch == nullptr || a->layout == nullptr || a->amax == nullptr) return B200MOE_EINVAL;
+  if (a->recipe != B200MOE_RECIPE_W4A16) return B200MOE_EUNSUPPORTED;
+  if (a->num_rows < 0 || a->num_experts <= 0 || a->layer_idx < 0 || a->hidden_size <= 0 || a->intermediate <= 0 ||
+      a->hidden_size % 8 != 0 || a->intermediate % 8 != 0)
+    return B200MOE_EINVAL;
+  if (a->num_rows > a->layout->rows) return B200MOE_ECAPACITY;
+  if (a->num_rows == 0) return B200MOE_OK;
+  return b200moe::w4a16_activation_amax(a, static_cast<cudaStream_t>(stream));
 }

@@ -953,6 +953,47 @@ grouped_gemm_w4a16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __
 
 }  // namespace pr
 
+// Calibration side channel of the w4a16 recipe (reference W4A16FusedMoeKernel._collect_activation_amax_epilogue,
+// b12x/moe/_shared/kernels/w4a16/kernel.py:7288-7365): amax[layer][expert][0] = max(old, max |x| over the
+// rows routed to the expert), [..][1] the same over its activated BF16 intermediate rows.  One CTA per
+// row tile and operand (blockIdx.y: 0 = FC1 input rows, 1 = FC2 input rows); non-negative floats
+// order like their bit patterns, so the running maximum is an integer atomicMax.
+__global__ void __launch_bounds__(256) activation_amax_kernel(
+    const __nv_bfloat16* __restrict__ rows_fc1, const __nv_bfloat16* __restrict__ rows_fc2, int K, int I,
+    const int32_t* __restrict__ tile_base, int E, const int32_t* __restrict__ mtile_expert,
+    const int32_t* __restrict__ mtile_row0, const int32_t* __restrict__ mtile_rows, float* __restrict__ amax,
+    int layer_idx) {
+  const int mt = blockIdx.x;
+  if (mt >= tile_base[E]) return;
+  const int which = blockIdx.y;
+  const int len = which == 0 ? K : I;
+  const __nv_bfloat16* base = (which == 0 ? rows_fc1 : rows_fc2) + static_cast<size_t>(mtile_row0[mt]) * len;
+  const int nvec = (mtile_rows[mt] * len) >> 3;                 // 8 values per 16-byte load; rows are contiguous
+  float m = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    const uint4 p = reinterpret_cast<const uint4*>(base)[i];
+    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      m = fmaxf(m, fabsf(__uint_as_float(w[j] << 16)));
+      m = fmaxf(m, fabsf(__uint_as_float(w[j] & 0xffff0000u)));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  __shared__ float part[8];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int wgt = 1; wgt < 8; ++wgt) m = fmaxf(m, part[wgt]);
+    if (!(m != m)) {      // a NaN row leaves the record alone
+      int* dst = reinterpret_cast<int*>(amax + (static_cast<size_t>(layer_idx) * E + mtile_expert[mt]) * 2 + which);
+      atomicMax(dst, __float_as_int(m));
+    }
+  }
+}
+
 // x rows -> sorted-position order (the A operand of FC1), one warp per row
 __global__ void __launch_bounds__(256) permute_rows_bf16_kernel(
     const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, const int32_t* __restrict__ expert_offsets,
@@ -1191,6 +1232,21 @@ int w4a16_gemm2(const b200moe_gemm_args* a, cudaStream_t stream) {
   p.sub1_base = 128;
   const int grid = a->num_sms > 0 ? a->num_sms : sm_count();
   return launch_split<EPI_FC2>(a, tmA, tmW, p, grid, stream);
+}
+
+int w4a16_activation_amax(const b200moe_amax_args* a, cudaStream_t stream) {
+  const b200moe_scratch_layout& L = *a->layout;
+  char* base = static_cast<char*>(a->scratch);
+  const int tr = L.tile_rows == 64 ? 64 : 128;
+  const int rows = a->num_rows;
+  const int mtiles = (rows + tr - 1) / tr + (a->num_experts < rows ? a->num_experts : rows);
+  const int gx = mtiles < L.mtile_cap ? mtiles : L.mtile_cap;
+  w4a16::activation_amax_kernel<<<dim3(gx, 2), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(base + L.act_q), reinterpret_cast<const __nv_bfloat16*>(base + L.mid_q),
+      a->hidden_size, a->intermediate, reinterpret_cast<const int32_t*>(base + L.tile_base), a->num_experts,
+      reinterpret_cast<const int32_t*>(base + L.mtile_expert), reinterpret_cast<const int32_t*>(base + L.mtile_row0),
+      reinterpret_cast<const int32_t*>(base + L.mtile_rows), a->amax, a->layer_idx);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ECUDA;
 }
 
 }  // namespace b200moe

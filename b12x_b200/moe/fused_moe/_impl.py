@@ -398,8 +398,9 @@ class TPMoEScratchCaps:
         if self.apply_router_weight_on_input and str(self.quant_mode).lower() != "w4a16":
             # as the reference: only its W4A16 path takes it (_impl.py:10631-10634)
             raise NotImplementedError("apply_router_weight_on_input is not implemented in b12x_moe_fp4")
-        if self.collect_activation_amax:
-            raise NotImplementedError("collect_activation_amax is not built")
+        if self.collect_activation_amax and str(self.quant_mode).lower() != "w4a16":
+            # as the reference (_impl.py:10601-10604)
+            raise NotImplementedError("activation_amax calibration is only supported for W4A16")
         if self.num_topk > 32:
             raise ValueError("num_topk > 32 is not supported")
         if self.tile_rows not in (None, 0, 64, 128):
@@ -604,8 +605,16 @@ class TPMoEScratchPlan:
             # reference _impl.py:2333-2334: only its trellis full-rotation plans take one
             raise ValueError("output_expert_map requires a full-rotation Trellis plan")
         if activation_amax is not None:
-            # reference _impl.py:10601-10604 (calibration sidecars are not part of this library)
-            raise NotImplementedError("activation_amax calibration is not supported")
+            # reference _impl.py:10601-10604: a W4A16-only calibration side channel,
+            # float32 [layers, experts, 2] (FC1 input amax, FC2 input amax), maximum kept across calls
+            if caps.quant_mode != "w4a16":
+                raise NotImplementedError("activation_amax calibration is only supported for W4A16")
+            if (activation_amax.dtype != torch.float32 or activation_amax.ndim != 3 or not activation_amax.is_contiguous()
+                    or activation_amax.shape[1] != caps.weight_E or activation_amax.shape[2] != 2
+                    or activation_amax.device != caps.device):
+                raise ValueError(f"activation_amax must be contiguous float32 [layers, {caps.weight_E}, 2] on {caps.device}")
+            if layer_idx is None or not 0 <= int(layer_idx) < activation_amax.shape[0]:
+                raise ValueError("activation_amax needs layer_idx inside its first dimension")
         if experts.plan != caps.weight_plan:
             raise ValueError("experts do not match the plan used to size TP MoE scratch")
         if a.ndim != 2 or topk_ids.ndim != 2 or topk_weights.ndim != 2:
@@ -664,7 +673,8 @@ class TPMoEScratchPlan:
             kernel_workspace=core, core_layout=self._core_layout, fc1_tap=fc1_tap,
             output_f32=output_f32, output_scale=float(output_scale), f32_only=bool(f32_only),
             skip_combine=bool(skip_combine), sort_wait=sort_wait, a_packed=a_packed,
-            apply_router_weight_on_input=bool(caps.apply_router_weight_on_input))
+            apply_router_weight_on_input=bool(caps.apply_router_weight_on_input),
+            activation_amax=activation_amax)
 
 
 def plan_tp_moe_scratch(caps: TPMoEScratchCaps) -> TPMoEScratchPlan:
@@ -731,6 +741,8 @@ class TPMoEFP4Binding:
     a_packed: tuple | None = None
     # w4a16: the router weights multiply FC1's rows (before the activation) instead of the combine's
     apply_router_weight_on_input: bool = False
+    # w4a16 calibration: float32 [layers, experts, 2], updated at row ``layer_idx`` by every run
+    activation_amax: torch.Tensor | None = None
 
     # ---- scratch views (valid after run) ----
     def _v(self, name: str, count: int, dtype: torch.dtype) -> torch.Tensor:
@@ -893,6 +905,10 @@ def b12x_moe_fp4(*, binding: TPMoEFP4Binding, stage_timer=None) -> torch.Tensor:
     unit = 1 if b.apply_router_weight_on_input else 0
     ext.check(lib.b200moe_grouped_gemm1_act(C.byref(gargs), stream), "grouped_gemm1_act")
     mark("gemm1")
+    if b.activation_amax is not None:
+        aargs = ext.AmaxArgs(scratch, lp, b.activation_amax.data_ptr(), tokens * b.num_topk, b.weight_E, b.k, b.n,
+                             int(b.layer_idx), recipe)
+        ext.check(lib.b200moe_activation_amax(C.byref(aargs), stream), "activation_amax")
     ext.check(lib.b200moe_grouped_gemm2(C.byref(gargs), stream), "grouped_gemm2")
     mark("gemm2")
 

@@ -271,6 +271,20 @@ typedef struct {
 int b200moe_grouped_gemm1_act(const b200moe_gemm_args* a, void* stream);
 int b200moe_grouped_gemm2(const b200moe_gemm_args* a, void* stream);
 
+/* Calibration side channel (w4a16 only, as in the reference: b12x/moe/fused_moe/_impl.py:10601-10604,
+ * w4a16/kernel.py:7288-7365).  After b200moe_grouped_gemm1_act of the same arguments:
+ * amax[layer_idx][e][0] = max(old, max |x| over the rows routed to local expert e),
+ * amax[layer_idx][e][1] = the same over the expert's activated BF16 intermediate rows.
+ * amax is a device float32 [layers][num_experts][2] that the caller zeroes once. */
+typedef struct {
+  void* scratch;
+  const b200moe_scratch_layout* layout; /* HOST pointer                        */
+  float* amax;
+  int32_t num_rows;          /* tokens * top_k of the call                      */
+  int32_t num_experts, hidden_size, intermediate, layer_idx, recipe;
+} b200moe_amax_args;
+int b200moe_activation_amax(const b200moe_amax_args* a, void* stream);
+
 /* ---- stage 6: top-k weighted combine ----------------------------------- */
 /* Replaces the bf16 atomic scatter / deterministic top-k sum of the reference
  * (dynamic.py:7737-7750; w4a16/kernel.py:7733-7790): out[t] = sum over slots

@@ -10,7 +10,7 @@ import torch
 from b12x_b200 import synth
 from b12x_b200.moe import fused_moe
 from oracle import moe_oracle as O
-from tests.gpu_utils import oracle_layer, run_layer
+from tests.gpu_utils import oracle_layer, prepare_experts, route_on_gpu, run_layer
 from tests.helpers import atoms_to_rows, load_golden, t
 
 pytestmark = pytest.mark.gpu
@@ -308,6 +308,53 @@ def test_w4a16_router_weight_on_input(tokens, topk, act):
     with pytest.raises(NotImplementedError):
         inp4 = synth.make_inputs(synth.shape("c1", name="x", tokens=8, hidden=256, intermediate=128, experts=4, topk=2), seed=1)
         run_layer(inp4, weight_on_input=True)
+
+
+def test_w4a16_activation_amax_side_channel():
+    """``bind(activation_amax=, layer_idx=)`` (W4A16 only, as in the reference): after a run row
+    ``layer_idx`` holds, per local expert, max |x| over the rows routed to it and max |h| over its
+    BF16 intermediate rows; the maximum is kept across runs; other layers' rows are untouched."""
+    dev = torch.device("cuda")
+    inp = synth.make_inputs(_w16(tokens=150, topk=2, hidden=384, intermediate=256, experts=6), seed=9, device=dev)
+    ex = prepare_experts(inp, dev)
+    caps = fused_moe.Caps(max_tokens=150, num_topk=2, device=dev, weight_plan=ex.plan, quant_mode="w4a16",
+                          collect_activation_amax=True)
+    plan = fused_moe.plan(caps)
+    spec = plan.scratch_specs()[0]
+    scratch = torch.empty(spec.shape, dtype=spec.dtype, device=dev)
+    _, ti, tw = route_on_gpu(inp, dev)
+    amax = torch.zeros(3, 6, 2, device=dev)
+    amax[0].fill_(7.0)
+    b = fused_moe.bind(plan, scratch=scratch, a=inp.x, experts=ex, topk_weights=tw, topk_ids=ti,
+                       activation_amax=amax, layer_idx=1)
+    fused_moe.run(binding=b)
+    torch.cuda.synchronize()
+    fused_moe.check_device_status(b)
+    ids = ti.cpu().long()
+    mid = b.materialized_intermediate.view(torch.bfloat16).float()
+    offs = b.expert_offsets.cpu().tolist()
+    for e in range(6):
+        tok = (ids == e).any(dim=1)
+        want_x = inp.x.cpu().float()[tok].abs().max().item() if bool(tok.any()) else 0.0
+        want_h = mid[offs[e]:offs[e + 1]].abs().max().item() if offs[e + 1] > offs[e] else 0.0
+        assert amax[1, e, 0].item() == want_x and amax[1, e, 1].item() == want_h
+    assert bool((amax[0] == 7.0).all()) and bool((amax[2] == 0.0).all())
+    # a second run on half-sized inputs cannot lower the record
+    before = amax.clone()
+    b2 = fused_moe.bind(plan, scratch=scratch, a=(inp.x * 0.5).to(torch.bfloat16), experts=ex, topk_weights=tw,
+                        topk_ids=ti, activation_amax=amax, layer_idx=1)
+    fused_moe.run(binding=b2)
+    torch.cuda.synchronize()
+    assert torch.equal(amax, before)
+    # W4A16 only
+    inp4 = synth.make_inputs(synth.shape("c1", name="x", tokens=8, hidden=256, intermediate=128, experts=4, topk=2), seed=1, device=dev)
+    ex4 = prepare_experts(inp4, dev)
+    plan4 = fused_moe.plan(fused_moe.Caps(max_tokens=8, num_topk=2, device=dev, weight_plan=ex4.plan, quant_mode="nvfp4"))
+    s4 = torch.empty(plan4.scratch_specs()[0].shape, dtype=torch.uint8, device=dev)
+    _, ti4, tw4 = route_on_gpu(inp4, dev)
+    with pytest.raises(NotImplementedError):
+        fused_moe.bind(plan4, scratch=s4, a=inp4.x, experts=ex4, topk_weights=tw4, topk_ids=ti4,
+                       activation_amax=torch.zeros(1, 4, 2, device=dev), layer_idx=0)
 
 
 def test_w4a16_matches_reference_golden():
