@@ -27,23 +27,29 @@ def _no_provenance() -> Provenance:
 
 @dataclass(frozen=True, kw_only=True)
 class OpMeta:
-    """Header of one operator.  ``api_style``: "planned" = ``Caps -> plan() -> bind() -> run()``
-    (``plan`` on the host, ``bind`` views only, ``run`` safe under CUDA-graph capture); "oneshot" =
-    plain functions; "stateful" = long-lived objects."""
+    """Header of one operator (keyword-only, so the field order carries no meaning).
 
-    name: str
+    ``api_style``: "planned" = ``Caps -> plan() -> bind() -> run()`` (``plan`` on the host, ``bind``
+    views only, ``run`` safe under CUDA-graph capture); "oneshot" = plain functions; "stateful" =
+    long-lived objects."""
+
+    # identity
     group: str
-    api_style: Literal["planned", "oneshot", "stateful"]
+    name: str
+    # what the package exports and how it is driven
     entry_points: tuple[str, ...]
+    api_style: Literal["planned", "oneshot", "stateful"]
+    # what it runs on and with
     archs: tuple[str, ...] = ("sm100a",)
-    dtypes: tuple[str, ...] = ()
     recipes: tuple[str, ...] = ()
+    dtypes: tuple[str, ...] = ()
     requires: tuple[str, ...] = ()
+    # bookkeeping
     status: Literal["experimental"] = "experimental"
-    provenance: Provenance = field(default_factory=_no_provenance)
-    test_path: str = ""
     since: str = ""
+    test_path: str = ""
     notes: str = ""
+    provenance: Provenance = field(default_factory=_no_provenance)
 
     @property
     def qualname(self) -> str:
