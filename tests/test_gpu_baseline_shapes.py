@@ -111,3 +111,14 @@ def test_pipelined_host_step_equals_the_whole_batch_step():
     # a decode-sized batch is not chunked
     small = synth.shape("c2", tokens=64)
     assert ExpertParallelMoE.host_chunks(type("L", (), {"world": 1, "shape": small})()) == 1
+
+
+@pytest.mark.parametrize("key", ["c4", "c5", "c3"])
+@pytest.mark.timeout(900)
+def test_benchmark_configurations_at_full_size(key):
+    """The large-batch configurations at the token counts the benchmark times (c4 8192, c5 16384,
+    c3 4096 tokens): whole permutation bit-exact, sampled routes against the oracle, and the
+    combine of the first tokens recomputed from the kernels' own FC2 rows bit-equal to the output."""
+    shp = synth.shape(key)
+    res = _run_and_check(shp, seed=40, rows_per_expert=24)
+    assert res["permutation_rows"] == shp.tokens * shp.topk
