@@ -256,31 +256,37 @@ __global__ void __launch_bounds__(256) ep_combine_pull_kernel(
     const int32_t* __restrict__ wait_flags, const int32_t* epoch_dev, int32_t* __restrict__ status,
     unsigned long long limit_ns) {
   extern __shared__ unsigned char sm_raw[];
-  // Optional hand-shake folded into this kernel (saves two launches per step): block (0,0) tells
-  // every peer that this rank's FC2 rows are complete (the FC2 kernel ended before this one
-  // began), then every block waits until all peers have said the same.  The wait is bounded.
-  if (wait_flags != nullptr) {
-    const int epoch = *epoch_dev;
-    if (threadIdx.x < world) {
-      if (blockIdx.x == 0 && blockIdx.y == 0) {
-        __threadfence_system();
-        st_release_sys(static_cast<int32_t*>(signal_flags.p[threadIdx.x]) + rank, epoch);
-      }
-      unsigned long long t0 = 0;
-      uint32_t spins = 0;
-      while (ld_acquire_sys(wait_flags + threadIdx.x) < epoch) {
-        if ((++spins & 0x3ffu) == 0) {
-          const unsigned long long now = global_timer_ns();
-          if (t0 == 0) t0 = now;
-          if (now - t0 > limit_ns) {
-            if (status != nullptr) {
-              atomicCAS(status, 0, 1);
-              atomicCAS(status + 1, 0, 16 + static_cast<int>(threadIdx.x));
-            }
-            break;
+  // Optional hand-shake folded into this kernel (saves two launches per step).  Block (0,0) tells
+  // every peer that this rank's FC2 rows are complete (the FC2 kernel ended before this one began)
+  // and then waits for ALL peers: the kernel cannot end before every rank has finished the step's
+  // FC2, which is what allows the next step's dispatch to overwrite the peers' receive buffers.
+  // Every other block waits only for the ranks that hold ITS token's rows, so rows of ranks that are
+  // done are pulled while a slower rank still computes.  All waits are bounded.
+  const bool fold = wait_flags != nullptr;
+  const int epoch = fold ? *epoch_dev : 0;
+  auto wait_for = [&](int peer) -> bool {
+    unsigned long long t0 = 0;
+    uint32_t spins = 0;
+    while (ld_acquire_sys(wait_flags + peer) < epoch) {
+      if ((++spins & 0x3ffu) == 0) {
+        const unsigned long long now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > limit_ns) {
+          if (status != nullptr) {
+            atomicCAS(status, 0, 1);
+            atomicCAS(status + 1, 0, 16 + peer);
           }
+          return false;
         }
       }
+    }
+    return true;
+  };
+  if (fold && blockIdx.x == 0 && blockIdx.y == 0) {
+    if (threadIdx.x < world) {
+      __threadfence_system();
+      st_release_sys(static_cast<int32_t*>(signal_flags.p[threadIdx.x]) + rank, epoch);
+      wait_for(static_cast<int>(threadIdx.x));
     }
     __syncthreads();
   }
@@ -296,9 +302,12 @@ __global__ void __launch_bounds__(256) ep_combine_pull_kernel(
       const int j = pos - group_offsets[d];
       const int slot = rank * cap + j;
       const char* arena = static_cast<const char*>(arenas.p[d]);
-      // a route beyond the receive capacity was never sent (the dispatch raised the status word)
-      const int p = j < cap ? reinterpret_cast<const int32_t*>(arena + peer_inv_perm_off)[slot] : -1;
-      if (p >= 0) rp = reinterpret_cast<const float*>(arena + peer_routed_off) + static_cast<size_t>(p) * K;
+      // a route beyond the receive capacity was never sent (the dispatch raised the status word);
+      // the rows of rank d are read only after rank d has said that they are complete
+      if (j < cap && (!fold || wait_for(d))) {
+        const int p = reinterpret_cast<const int32_t*>(arena + peer_inv_perm_off)[slot];
+        if (p >= 0) rp = reinterpret_cast<const float*>(arena + peer_routed_off) + static_cast<size_t>(p) * K;
+      }
     }
     rowp[s] = rp;
     w[s] = topk_weights[static_cast<int64_t>(t) * num_topk + s];
