@@ -148,6 +148,12 @@ def sort_launches(routes: int) -> int:
     return 3 if routes >= 16384 else 1
 
 
+def gemm_launches(rows: int, experts: int) -> int:
+    """Kernels of FC1 + FC2: one each; plans with two to eight row tiles per expert run the CTA-pair
+    kernel on full pairs and a single-CTA kernel on the left-over row tiles (two each)."""
+    return 4 if 256 * experts <= rows < 1024 * experts else 2
+
+
 class _LayerBase:
     kernels_per_step = 6
 
@@ -326,7 +332,7 @@ class ExpertParallelMoE(_LayerBase):
         if world == 1:
             self.plan, self.scratch = self._local_plan(t, k)
             # route, sort, quantise (w4a16: row gather), FC1, FC2, combine
-            self.kernels_per_step = 5 + sort_launches(t * k)
+            self.kernels_per_step = 3 + sort_launches(t * k) + gemm_launches(t * k, shp.experts)
             return
         # home side: sort routes by destination rank, pack rows, later combine returned rows
         self.home = StageArena(t, k, world, shp.hidden, dev)
@@ -454,7 +460,8 @@ class TensorParallelMoE(_LayerBase):
         self.plan, self.scratch = self._local_plan(shp.tokens, shp.topk)
         self.partial = torch.empty((shp.tokens, shp.hidden), dtype=torch.float32, device=dev)
         # route, sort, row gather / quantise, FC1, FC2, fp32 combine, rounding
-        self.kernels_per_step = 6 + sort_launches(shp.tokens * shp.topk)
+        self.kernels_per_step = (4 + sort_launches(shp.tokens * shp.topk)
+                                 + gemm_launches(shp.tokens * shp.topk, shp.experts))
 
     @classmethod
     def from_synthetic(cls, shp: synth.MoEShape, dev, rank: int, world: int):

@@ -29,7 +29,7 @@ import torch.distributed as dist
 from .. import synth
 from .._lib import ext
 from . import fused_moe
-from .distributed import _LayerBase, prepare_experts, sort_launches
+from .distributed import _LayerBase, gemm_launches, prepare_experts, sort_launches
 from .fused_moe.stages import StageArena
 from .placement import plan_expert_replicas
 
@@ -114,7 +114,8 @@ class PeerExpertParallelMoE(_LayerBase):
         # unless B200MOE_FOLD_WAITS=0 makes them three launches of their own
         self.fold_waits = os.environ.get("B200MOE_FOLD_WAITS", "1") == "1"
         # route, home sort, dispatch, expert sort, file / quantise rows, FC1, FC2, combine (+ wait, signal, wait)
-        self.kernels_per_step = (6 + sort_launches(t * k) + sort_launches(slots) + (0 if self.fold_waits else 3)
+        self.kernels_per_step = (4 + sort_launches(t * k) + sort_launches(slots) + (0 if self.fold_waits else 3)
+                                 + gemm_launches(slots, self.n_local)
                                  + (1 if self.replicas is not None else 0))
         # what crosses the link per route: the row quantised on this rank (the recipe's activation
         # format) or, for recipes whose GEMM reads bf16 rows, the row as it is
