@@ -444,7 +444,8 @@ def compact(rec: dict) -> dict:
             "scaling": rec["scaling"], "ms_per_step": rec["ms_per_step"], "tflops": rec["tflops"],
             "e2e_ms_per_step": rec["e2e"]["ms_per_step"], "stage_ms": rec["stage_ms"],
             "roofline": {k: r[k] for k in ("kernel", "bound", "achieved", "peak", "unit", "frac", "ms_per_launch")},
-            "step_roofline": rec["step_roofline"], "clocks": rec["clocks"], "parity_sample": rec["parity_sample"]}
+            "step_roofline": rec["step_roofline"], "clocks": rec["clocks"], "parity_sample": rec["parity_sample"],
+            "gpu_launches": rec["gpu_launches"], "config": rec["config"]}
 
 
 def main():
